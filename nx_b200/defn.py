@@ -1,0 +1,228 @@
+"""`Nx.Defn.Compiler` for the B200 runtime.
+
+The callbacks mirror nx/lib/nx/defn/compiler.ex:29-101 as EXLA.Defn implements
+them (exla/lib/exla/defn.ex:15-72, :151-191):
+
+``__jit__(key, vars, fun, args_list, opts)``   trace + build (cached), then run
+``__compile__(key, vars, fun, opts)``          returns the runner closure
+``__partitions_options__(opts)``               one option set per visible GPU
+``__to_backend__(opts)``                       where results live
+``__shard_jit__``                              lives in `nx_b200.sharding`
+
+`jit` / `compile` are the ``Nx.Defn.jit/2`` / ``Nx.Defn.compile/3`` entry
+points (nx/lib/nx/defn.ex:240-271, :331-354) bound to this compiler.
+
+Caching follows exla/lib/exla/defn.ex:337-397: the key is the function plus
+the ``{type, shape}`` of every flattened argument — never the values — and the
+traced graph is built into a native program once per key.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+
+from . import backend as B
+from . import expr as E
+from . import nif
+from . import types as T
+from .nx import HostData, Tensor
+
+
+class Program:
+    """A built program: ``%EXLA.Executable{}`` (exla/lib/exla/executable.ex)."""
+
+    def __init__(self, blob):
+        self.blob = blob
+        l = nif.lib()
+        h = C.c_void_p()
+        nif.check(l.nxb200_program_build(blob, len(blob), C.byref(h)))
+        self.handle = h.value
+        n_in, n_out = C.c_int(), C.c_int()
+        nif.check(l.nxb200_program_io(self.handle, C.byref(n_in), C.byref(n_out)))
+        self.n_params, self.n_outputs = n_in.value, n_out.value
+        self.outputs = []
+        for i in range(self.n_outputs):
+            dt, rank = C.c_int(), C.c_int()
+            dims = nif.dims_array([])
+            nif.check(l.nxb200_program_output_info(self.handle, i, C.byref(dt), dims, C.byref(rank)))
+            self.outputs.append((T.CODE_DTYPES[dt.value], tuple(dims[k] for k in range(rank.value))))
+
+    def __del__(self):
+        h, self.handle = getattr(self, "handle", None), None
+        if h and nif._LIB is not None:
+            try:
+                nif._LIB.nxb200_program_release(h)
+            except Exception:
+                pass
+
+    def describe(self):
+        l = nif.lib()
+        n = l.nxb200_program_describe(self.handle, None, 0)
+        buf = C.create_string_buffer(n + 1)
+        l.nxb200_program_describe(self.handle, buf, n + 1)
+        return buf.value.decode()
+
+    def launch_count(self):
+        n = C.c_int()
+        nif.check(nif.lib().nxb200_program_launch_count(self.handle, C.byref(n)))
+        return n.value
+
+    def _arg_array(self, args):
+        if len(args) != self.n_params:
+            raise ValueError(f"program expects {self.n_params} arguments, got {len(args)}")
+        arr = (C.c_void_p * max(1, len(args)))()
+        for i, a in enumerate(args):
+            if not isinstance(a.data, B.DeviceBuffer):
+                raise TypeError("program arguments must be device tensors")
+            arr[i] = a.data.handle
+        return arr
+
+    def run(self, args, device=0):
+        """exla/lib/exla/executable.ex:130-148 (run -> NIF run_io)."""
+        arr = self._arg_array(args)
+        outs = (C.c_void_p * max(1, self.n_outputs))()
+        nif.check(nif.lib().nxb200_program_run(self.handle, device, arr, len(args), outs, self.n_outputs))
+        return [Tensor(B.DeviceBuffer(outs[i], device), t, s) for i, (t, s) in enumerate(self.outputs)]
+
+    def run_into(self, args, outs, device=0):
+        arr = self._arg_array(args)
+        oarr = (C.c_void_p * max(1, len(outs)))(*[o.data.handle for o in outs])
+        nif.check(nif.lib().nxb200_program_run_into(self.handle, device, arr, len(args), oarr, len(outs)))
+        return outs
+
+
+# ---- containers (Nx.Defn.Composite) ------------------------------------------------
+
+def _flatten(c, acc):
+    if isinstance(c, Tensor):
+        acc.append(c)
+        return ("t",)
+    if isinstance(c, (tuple, list)):
+        return ("seq", type(c), [_flatten(x, acc) for x in c])
+    if isinstance(c, dict):
+        return ("map", [(k, _flatten(c[k], acc)) for k in sorted(c)])
+    from . import nx
+    acc.append(nx._as_operand(c))
+    return ("t",)
+
+
+def _unflatten(spec, it):
+    if spec[0] == "t":
+        return next(it)
+    if spec[0] == "seq":
+        return spec[1](_unflatten(s, it) for s in spec[2])
+    return {k: _unflatten(s, it) for k, s in spec[1]}
+
+
+# ---- compiler callbacks ----------------------------------------------------------------
+
+_cache = {}
+_cache_lock = threading.Lock()
+
+
+def trace(fun, templates):
+    """Run ``fun`` with parameter nodes in place of its tensor arguments
+    (nx/lib/nx/defn/compiler.ex:184-205, :890-917) and return
+    ``(flat_outputs, output_spec)``."""
+    flat = []
+    spec = [_flatten(t, flat) for t in templates]
+    params = [E.parameter(t.type, t.shape, i) for i, t in enumerate(flat)]
+    it = iter(params)
+    args = [_unflatten(s, it) for s in spec]
+    with B.trace_scope():
+        result = fun(*args)
+        outs = []
+        ospec = _flatten(result, outs)
+        outs = [B.to_expr(o) for o in outs]
+    return outs, ospec
+
+
+def __compile__(key, templates, fun, opts):
+    """Build (or fetch) the program for ``key`` + argument templates and return
+    a closure that runs it on lists of argument thunks."""
+    flat = []
+    for t in templates:
+        _flatten(t, flat)
+    args_key = tuple((t.type, t.shape) for t in flat)
+    ck = (key, args_key, opts.get("device"))
+    with _cache_lock:
+        entry = _cache.get(ck)
+    if entry is None:
+        outs, ospec = trace(fun, templates)
+        # outputs that are parameters or constants still need a buffer of
+        # their own: results are always fresh tensors (exla/lib/exla/defn.ex:387-393)
+        blob = E.serialize(outs)
+        entry = (Program(blob), ospec)
+        with _cache_lock:
+            _cache.setdefault(ck, entry)
+    prog, ospec = entry
+    device = B._device_of(opts.get("device"))
+
+    def runner(args_list):
+        results = []
+        for thunks in args_list:
+            args = [B.backend_transfer(th() if callable(th) else th, device) for th in thunks]
+            outs = prog.run(args, device)
+            results.append(_unflatten(ospec, iter(outs)))
+        return results
+
+    runner.program = prog
+    return runner
+
+
+def __jit__(key, templates, fun, args_list, opts):
+    return __compile__(key, templates, fun, opts)(args_list)
+
+
+def __partitions_options__(opts):
+    """One option set per device (exla/lib/exla/defn.ex:15-20)."""
+    n = nif.device_count()
+    return [dict(opts, device=i) for i in range(max(1, n))]
+
+
+def __to_backend__(opts):
+    """exla/lib/exla/defn.ex:23-32."""
+    return ("b200", B._device_of(opts.get("device")))
+
+
+# ---- Nx.Defn entry points ------------------------------------------------------------------
+
+def _templates(args):
+    flat = []
+    spec = [_flatten(a, flat) for a in args]
+    return flat, spec
+
+
+def jit(fun, **opts):
+    """``Nx.Defn.jit(fun, compiler: B200)``: returns a function that traces and
+    builds on first call per argument signature, then runs."""
+    def wrapped(*args):
+        flat, _ = _templates(args)
+        res = __jit__(fun, list(args), fun, [flat], opts)
+        return res[0]
+    wrapped.__wrapped__ = fun
+    return wrapped
+
+
+def compile(fun, templates, **opts):
+    """``Nx.Defn.compile/3``: build ahead of time for the given templates."""
+    runner = __compile__(fun, list(templates), fun, opts)
+
+    def compiled(*args):
+        flat, _ = _templates(args)
+        return runner([flat])[0]
+    compiled.program = runner.program
+    return compiled
+
+
+def template(shape, type):
+    """``Nx.template/2``."""
+    return Tensor(None, T.normalize(type), tuple(shape))
+
+
+def build_program(fun, templates):
+    """Trace ``fun`` and return ``(serialised_graph, output_spec)`` without
+    touching the native library (used by tests of the front-end and by the
+    oracle, which interprets the same bytes)."""
+    outs, ospec = trace(fun, list(templates))
+    return E.serialize(outs), ospec

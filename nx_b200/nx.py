@@ -1,0 +1,673 @@
+"""The slice of the ``Nx`` public API that sits above the hot path.
+
+Every function does what nx/lib/nx.ex does before it reaches a backend: infer
+the output type and shape, then hand ``(out_template, operands…)`` to the
+implementation that owns the operands (nx/lib/nx/shared.ex:449-473):
+
+* while a function is being traced (`nx_b200.defn`), operands are expression
+  nodes and the call appends a node to the graph (``Nx.Defn.Expr``);
+* otherwise operands live on a B200 (`nx_b200.backend.Backend`) and the call
+  runs as a one-node program, the way EXLA.Backend runs eager ops
+  (exla/lib/exla/backend.ex:409-431).
+
+There is no host implementation of any operation: a tensor that is still in
+host memory is storage only (the analogue of handing an ``Nx.BinaryBackend``
+tensor to another backend, which transfers it).
+"""
+from __future__ import annotations
+
+import builtins as _b
+import math
+
+import numpy as np
+
+from . import expr as E
+from . import types as T
+
+
+class Tensor:
+    """``%Nx.Tensor{data, type, shape}`` (nx/lib/nx/tensor.ex:41-42).  ``data``
+    is an `expr.Expr` node, a `backend.DeviceBuffer`, or a `HostData`."""
+    __slots__ = ("data", "type", "shape")
+
+    def __init__(self, data, type, shape):
+        self.data, self.type, self.shape = data, type, tuple(int(d) for d in shape)
+
+    @property
+    def rank(self):
+        return len(self.shape)
+
+    @property
+    def size(self):
+        return math.prod(self.shape)
+
+    def __repr__(self):
+        dims = "".join(f"[{d}]" for d in self.shape)
+        return f"#Nx.Tensor<{T.short(self.type)}{dims} {self.data!r}>"
+
+    # the operators `defn` rewrites to Nx calls (nx/lib/nx/defn/kernel.ex)
+    def __add__(self, o): return add(self, o)
+    def __radd__(self, o): return add(o, self)
+    def __sub__(self, o): return subtract(self, o)
+    def __rsub__(self, o): return subtract(o, self)
+    def __mul__(self, o): return multiply(self, o)
+    def __rmul__(self, o): return multiply(o, self)
+    def __truediv__(self, o): return divide(self, o)
+    def __rtruediv__(self, o): return divide(o, self)
+    def __neg__(self): return negate(self)
+    def __pow__(self, o): return pow(self, o)
+    def __gt__(self, o): return greater(self, o)
+    def __ge__(self, o): return greater_equal(self, o)
+    def __lt__(self, o): return less(self, o)
+    def __le__(self, o): return less_equal(self, o)
+
+
+class HostData:
+    """Row-major little-endian bytes in host memory: what a tensor is before
+    `backend_transfer` (the storage half of Nx.BinaryBackend)."""
+    __slots__ = ("raw",)
+
+    def __init__(self, raw):
+        self.raw = bytes(raw)
+
+    def __repr__(self):
+        return f"host<{len(self.raw)} bytes>"
+
+
+# ---- numpy <-> raw bytes (bf16 has no numpy dtype: it travels as uint16) ---------
+
+_NP = {T.U8: np.uint8, T.U16: np.uint16, T.U32: np.uint32, T.U64: np.uint64,
+       T.S8: np.int8, T.S16: np.int16, T.S32: np.int32, T.S64: np.int64,
+       T.F16: np.float16, T.F32: np.float32, T.F64: np.float64, T.BF16: np.uint16}
+
+
+def f32_to_bf16_bits(a):
+    """Round-to-nearest-even f32 -> bf16 bit pattern (NaN stays NaN)."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    u = a.view(np.uint32)
+    rounded = ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+    nan = np.isnan(a)
+    if nan.any():
+        rounded = np.where(nan, ((u >> np.uint32(16)) | np.uint32(0x40)).astype(np.uint16), rounded)
+    return rounded
+
+
+def bf16_bits_to_f32(b):
+    return (np.ascontiguousarray(b, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
+def tensor(value, type=None):
+    """``Nx.tensor/2``: build a tensor from a number, nested list or ndarray.
+    With a default backend configured the data goes straight to the device
+    (nx/lib/nx.ex:5006-5049)."""
+    if isinstance(value, Tensor):
+        return value if type is None else as_type(value, type)
+    arr = np.asarray(value)
+    if type is None:
+        if arr.dtype.kind == "f":
+            type = T.F32 if arr.dtype != np.float64 or not isinstance(value, np.ndarray) else T.F64
+        elif arr.dtype.kind == "b":
+            type = T.U8
+        elif arr.dtype.kind in "iu" and isinstance(value, np.ndarray):
+            type = {v: k for k, v in _NP.items() if k != T.BF16}[arr.dtype.type]
+        else:
+            type = T.S32
+    type = T.normalize(type)
+    if type == T.BF16:
+        raw = f32_to_bf16_bits(arr.astype(np.float32)).tobytes()
+    else:
+        with np.errstate(invalid="ignore"):
+            raw = np.ascontiguousarray(arr).astype(_NP[type]).tobytes()
+    return from_binary(raw, type, arr.shape)
+
+
+def from_binary(raw, type, shape=None):
+    """``Nx.from_binary/3`` followed by placement on the default backend."""
+    type = T.normalize(type)
+    if shape is None:
+        shape = (len(raw) // T.itemsize(type),)
+    t = Tensor(HostData(raw), type, shape)
+    if t.size * T.itemsize(type) != len(raw):
+        raise ValueError(f"binary has {len(raw)} bytes, expected {t.size * T.itemsize(type)} "
+                         f"for {T.short(type)}{list(t.shape)}")
+    from . import backend
+    if backend.default_backend() is not None:
+        return backend.backend_transfer(t)
+    return t
+
+
+def to_binary(t, limit=None):
+    """``Nx.to_binary/2`` (nx/lib/nx/backend.ex:56; EXLA: backend.ex:222-226)."""
+    from . import backend
+    n = t.size if limit is None else _b.min(int(limit), t.size)
+    if isinstance(t.data, HostData):
+        return t.data.raw[: n * T.itemsize(t.type)]
+    if isinstance(t.data, E.Expr):
+        raise TypeError("cannot read the value of a tensor inside defn")
+    return backend.to_binary(t, n)
+
+
+def to_numpy(t):
+    """Convenience over `to_binary`: bf16 comes back widened to float32."""
+    raw = to_binary(t)
+    a = np.frombuffer(raw, dtype=_NP[t.type]).reshape(t.shape)
+    return bf16_bits_to_f32(a).reshape(t.shape) if t.type == T.BF16 else a.copy()
+
+
+def to_number(t):
+    return to_numpy(t).reshape(()).item()
+
+
+# ---- dispatch ----------------------------------------------------------------------
+
+def _is_expr(x):
+    return isinstance(x, Tensor) and isinstance(x.data, E.Expr)
+
+
+def _as_operand(x):
+    """Numbers become constant nodes typed by Nx.Type.infer (nx/lib/nx.ex to_tensor)."""
+    if isinstance(x, Tensor):
+        return x
+    if isinstance(x, (bool, int, float, np.integer, np.floating)):
+        x = x.item() if isinstance(x, np.generic) else x
+        return E.constant(T.infer(x), (), x)
+    return tensor(x)
+
+
+def _dispatch(builder, operands):
+    """Run ``builder(*operands)`` against the graph (tracing) or as a one-node
+    program on the device (eager)."""
+    from . import backend
+    operands = [_as_operand(o) for o in operands]
+    if _b.any(_is_expr(o) and o.data.op != "constant" for o in operands):
+        return builder(*[backend.to_expr(o) for o in operands])
+    if _b.all(_is_expr(o) for o in operands) and operands:
+        return builder(*operands)          # constants only: folds at trace time
+    return backend.eager(builder, operands)
+
+
+def _out(type, shape):
+    return Tensor(None, type, shape)
+
+
+def _type_of(x):
+    return x.type if isinstance(x, Tensor) else None
+
+
+def _binary_type(a, b):
+    """nx/lib/nx/shared.ex:383-388."""
+    na, nb = not isinstance(a, Tensor), not isinstance(b, Tensor)
+    if na and nb:
+        return T.infer(a + b)
+    if na:
+        return T.merge_number(b.type, a)
+    if nb:
+        return T.merge_number(a.type, b)
+    return T.merge(a.type, b.type)
+
+
+def _num(x):
+    if isinstance(x, np.generic):
+        return x.item()
+    if isinstance(x, (list, tuple, np.ndarray)):
+        return tensor(x)
+    return x
+
+
+def _shape_of(x):
+    return x.shape if isinstance(x, Tensor) else ()
+
+
+def binary_broadcast(s1, s2):
+    """nx/lib/nx/shape.ex binary_broadcast: right-aligned, size-1 stretches."""
+    r = _b.max(len(s1), len(s2))
+    a = (1,) * (r - len(s1)) + tuple(s1)
+    b = (1,) * (r - len(s2)) + tuple(s2)
+    out = []
+    for x, y in zip(a, b):
+        if x == y or y == 1:
+            out.append(x)
+        elif x == 1:
+            out.append(y)
+        else:
+            raise ValueError(f"cannot broadcast tensor of dimensions {tuple(s1)} to {tuple(s2)}")
+    return tuple(out)
+
+
+def _bin(op, a, b, type_fun=lambda t: t, pred=False):
+    a, b = _num(a), _num(b)
+    type = T.U8 if pred else type_fun(_binary_type(a, b))
+    shape = binary_broadcast(_shape_of(a), _shape_of(b))
+    out = _out(type, shape)
+    special = {"add": E.add, "multiply": E.multiply, "subtract": E.subtract, "divide": E.divide}
+    if op in special:
+        return _dispatch(lambda x, y: special[op](out, x, y), [a, b])
+    return _dispatch(lambda x, y: E.binary_expr(out, op, x, y), [a, b])
+
+
+def add(a, b): return _bin("add", a, b)
+def subtract(a, b): return _bin("subtract", a, b)
+def multiply(a, b): return _bin("multiply", a, b)
+def divide(a, b): return _bin("divide", a, b, T.to_floating)
+def pow(a, b): return _bin("pow", a, b)
+def remainder(a, b): return _bin("remainder", a, b)
+def atan2(a, b): return _bin("atan2", a, b, T.to_floating)
+def min(a, b): return _bin("min", a, b)
+def max(a, b): return _bin("max", a, b)
+
+
+def _int_only(name, *xs):
+    for x in xs:
+        t = _type_of(x)
+        if (t is not None and not T.is_integer(t)) or isinstance(x, float):
+            raise ValueError(f"{name} expects integer tensors as inputs and outputs an integer tensor, "
+                             f"got: {t}")
+
+
+def quotient(a, b):
+    _int_only("quotient", a, b)
+    return _bin("quotient", a, b)
+
+
+def bitwise_and(a, b): _int_only("bitwise_and", a, b); return _bin("bitwise_and", a, b)
+def bitwise_or(a, b): _int_only("bitwise_or", a, b); return _bin("bitwise_or", a, b)
+def bitwise_xor(a, b): _int_only("bitwise_xor", a, b); return _bin("bitwise_xor", a, b)
+def left_shift(a, b): _int_only("left_shift", a, b); return _bin("left_shift", a, b)
+def right_shift(a, b): _int_only("right_shift", a, b); return _bin("right_shift", a, b)
+
+def equal(a, b): return _bin("equal", a, b, pred=True)
+def not_equal(a, b): return _bin("not_equal", a, b, pred=True)
+def greater(a, b): return _bin("greater", a, b, pred=True)
+def less(a, b): return _bin("less", a, b, pred=True)
+def greater_equal(a, b): return _bin("greater_equal", a, b, pred=True)
+def less_equal(a, b): return _bin("less_equal", a, b, pred=True)
+def logical_and(a, b): return _bin("logical_and", a, b, pred=True)
+def logical_or(a, b): return _bin("logical_or", a, b, pred=True)
+def logical_xor(a, b): return _bin("logical_xor", a, b, pred=True)
+
+
+def _unary(op, x, type_fun):
+    x = _as_operand(_num(x))
+    out = _out(type_fun(x.type), x.shape)
+    return _dispatch(lambda a: E.unary_expr(out, op, a), [x])
+
+
+def _make_math(op):
+    def f(x):
+        return _unary(op, x, T.to_floating)      # nx/lib/nx.ex:8592-8598
+    f.__name__ = op
+    f.__doc__ = f"Element-wise {op} (nx/lib/nx/shared.ex:311-376)."
+    return f
+
+
+for _op in E.UNARY_MATH:
+    globals()[_op] = _make_math(_op)
+
+
+def negate(x): return _unary("negate", x, lambda t: t)
+def abs(x): return _unary("abs", x, lambda t: t)
+def sign(x): return _unary("sign", x, lambda t: t)
+def is_nan(x): return _unary("is_nan", x, lambda t: T.U8)
+def is_infinity(x): return _unary("is_infinity", x, lambda t: T.U8)
+
+
+def _round_like(op, x):
+    x = _as_operand(_num(x))
+    return x if T.is_integer(x.type) else _unary(op, x, lambda t: t)
+
+
+def floor(x): return _round_like("floor", x)
+def ceil(x): return _round_like("ceil", x)
+def round(x): return _round_like("round", x)
+
+
+def bitwise_not(x):
+    _int_only("bitwise_not", x)
+    return _unary("bitwise_not", x, lambda t: t)
+
+
+def population_count(x):
+    _int_only("population_count", x)
+    return _unary("population_count", x, lambda t: t)
+
+
+def count_leading_zeros(x):
+    _int_only("count_leading_zeros", x)
+    return _unary("count_leading_zeros", x, lambda t: t)
+
+
+def logical_not(x):
+    """nx/lib/nx.ex logical_not: ``equal(x, 0)``."""
+    return equal(x, 0)
+
+
+def as_type(x, type):
+    """nx/lib/nx.ex as_type -> backend.ex:68."""
+    type = T.normalize(type)
+    x = _as_operand(_num(x))
+    if x.type == type:
+        return x
+    c = E.maybe_constant(x) if _is_expr(x) else None
+    if c is not None:
+        if T.is_integer(type) and isinstance(c, float):
+            c = 0 if math.isnan(c) else (T.max_value(type) if c == math.inf else
+                                         T.min_value(type) if c == -math.inf else int(c))
+        return E.constant(type, x.shape, c)
+    out = _out(type, x.shape)
+    return _dispatch(lambda a: E.node(out, "as_type", [a]), [x])
+
+
+def select(pred, on_true, on_false):
+    """nx/lib/nx.ex:7782-7830."""
+    pred, on_true, on_false = (_as_operand(_num(v)) for v in (pred, on_true, on_false))
+    type = T.merge(on_true.type, on_false.type)
+    shape = binary_broadcast(on_true.shape, on_false.shape) if pred.shape == () else pred.shape
+    for v in (on_true, on_false):
+        if binary_broadcast(v.shape, shape) != shape:
+            raise ValueError(f"cannot broadcast tensor of dimensions {v.shape} to {shape}")
+    out = _out(type, shape)
+    return _dispatch(lambda p, a, b: E.node(out, "select", [p, a, b]), [pred, on_true, on_false])
+
+
+def clip(x, lo, hi):
+    x, lo, hi = (_as_operand(_num(v)) for v in (x, lo, hi))
+    if lo.shape != () or hi.shape != ():
+        raise ValueError("min/max of clip must be scalars")
+    out = _out(T.merge(T.merge(x.type, lo.type), hi.type), x.shape)
+    return _dispatch(lambda a, b, c: E.node(out, "clip", [a, b, c]), [x, lo, hi])
+
+
+# ---- shape operations --------------------------------------------------------------
+
+def _norm_axis(rank, axis):
+    a = axis + rank if axis < 0 else axis
+    if not 0 <= a < rank:
+        raise ValueError(f"given axis ({axis}) invalid for shape with rank {rank}")
+    return a
+
+
+def _norm_axes(rank, axes):
+    out = [_norm_axis(rank, a) for a in axes]
+    if len(set(out)) != len(out):
+        raise ValueError(f"axes {list(axes)} must be unique integers between 0 and {rank - 1}")
+    return out
+
+
+def reshape(x, shape):
+    x = _as_operand(x)
+    shape = list(shape)
+    if shape.count("auto") + shape.count(-1) == 1:
+        i = shape.index("auto") if "auto" in shape else shape.index(-1)
+        rest = math.prod(d for j, d in enumerate(shape) if j != i)
+        shape[i] = x.size // rest if rest else 0
+    shape = tuple(shape)
+    if math.prod(shape) != x.size:
+        raise ValueError(f"cannot reshape, current shape {x.shape} is not compatible with new shape {shape}")
+    if shape == x.shape:
+        return x
+    out = _out(x.type, shape)
+    return _dispatch(lambda a: E.node(out, "reshape", [a]), [x])
+
+
+def squeeze(x, axes=None):
+    x = _as_operand(x)
+    if axes is None:
+        axes = [i for i, d in enumerate(x.shape) if d == 1]
+    axes = sorted(_norm_axes(x.rank, axes))
+    for a in axes:
+        if x.shape[a] != 1:
+            raise ValueError(f"cannot squeeze dimensions whose sizes are not 1, got {x.shape[a]} for dimension {a}")
+    if not axes:
+        return x
+    out = _out(x.type, tuple(d for i, d in enumerate(x.shape) if i not in axes))
+    if _is_expr(x) and x.data.op == "squeeze":      # expr.ex:1092-1103 merges nested squeezes
+        inner = x.data.args[0]
+        inner_axes = x.data.ints[1:]
+        kept = [i for i in range(inner.rank) if i not in inner_axes]
+        merged = sorted(inner_axes + [kept[a] for a in axes])
+        return E.node(out, "squeeze", [inner], ints=[len(merged)] + merged)
+    return _dispatch(lambda a: E.node(out, "squeeze", [a], ints=[len(axes)] + axes), [x])
+
+
+def new_axis(x, axis):
+    x = _as_operand(x)
+    a = axis + x.rank + 1 if axis < 0 else axis
+    return reshape(x, x.shape[:a] + (1,) + x.shape[a:])
+
+
+def broadcast(x, shape, axes=None):
+    """``Nx.broadcast/3``: ``axes[i]`` is the output axis input axis i lands on;
+    default is right alignment (nx/lib/nx/shape.ex broadcast_axes)."""
+    x = _as_operand(_num(x))
+    shape = tuple(shape)
+    if axes is None:
+        if x.shape == shape:
+            return x
+        axes = list(range(len(shape) - x.rank, len(shape)))
+    axes = _norm_axes(len(shape), axes)
+    if len(axes) != x.rank or _b.any(d != 1 and d != shape[a] for d, a in zip(x.shape, axes)):
+        raise ValueError(f"cannot broadcast tensor of dimensions {x.shape} to {shape} with axes {axes}")
+    if sorted(axes) != axes:
+        raise ValueError("broadcast axes must be ordered")
+    out = _out(x.type, shape)
+    c = E.maybe_constant(x) if _is_expr(x) else None
+    if c is not None:
+        return E.constant(x.type, shape, c)
+    return _dispatch(lambda a: E.node(out, "broadcast", [a], ints=[len(axes)] + axes), [x])
+
+
+def transpose(x, axes=None):
+    x = _as_operand(x)
+    axes = list(range(x.rank))[::-1] if axes is None else _norm_axes(x.rank, axes)
+    if len(axes) != x.rank:
+        raise ValueError(f"expected length of permutation ({len(axes)}) to match rank of shape ({x.rank})")
+    if axes == list(range(x.rank)):
+        return x
+    out = _out(x.type, tuple(x.shape[a] for a in axes))
+    return _dispatch(lambda a: E.node(out, "transpose", [a], ints=axes), [x])
+
+
+def slice(x, starts, lengths, strides=None):
+    """``Nx.slice/4`` with static start indices (nx/lib/nx.ex slice; dynamic
+    starts are outside the five configurations)."""
+    x = _as_operand(x)
+    strides = [1] * x.rank if strides is None else ([strides] * x.rank if isinstance(strides, int) else list(strides))
+    starts, lengths = list(starts), list(lengths)
+    if not (len(starts) == len(lengths) == len(strides) == x.rank):
+        raise ValueError("slice arguments must have one entry per axis")
+    shape = []
+    for d, s, l, st in zip(x.shape, starts, lengths, strides):
+        if l < 1 or l > d or st < 1:
+            raise ValueError(f"length at axis must be in 1..{d} and strides positive, got length {l} stride {st}")
+        shape.append(-(-l // st))
+    starts = [_b.min(_b.max(s, 0), d - l) for s, d, l in zip(starts, x.shape, lengths)]
+    if tuple(shape) == x.shape:
+        return x
+    out = _out(x.type, shape)
+    return _dispatch(lambda a: E.node(out, "slice", [a], ints=starts + lengths + strides), [x])
+
+
+def slice_along_axis(x, start, length, axis=0, strides=1):
+    x = _as_operand(x)
+    a = _norm_axis(x.rank, axis)
+    starts = [0] * x.rank
+    lengths = list(x.shape)
+    st = [1] * x.rank
+    starts[a], lengths[a], st[a] = start, length, strides
+    return slice(x, starts, lengths, st)
+
+
+def concatenate(tensors, axis=0):
+    tensors = [_as_operand(t) for t in tensors]
+    a = _norm_axis(tensors[0].rank, axis)
+    type = tensors[0].type
+    for t in tensors[1:]:
+        type = T.merge(type, t.type)
+        if t.rank != tensors[0].rank or _b.any(i != a and d != e for i, (d, e) in enumerate(zip(t.shape, tensors[0].shape))):
+            raise ValueError("expected all shapes to match except on the concatenation axis")
+    if len(tensors) == 1:
+        return as_type(tensors[0], type)
+    shape = list(tensors[0].shape)
+    shape[a] = _b.sum(t.shape[a] for t in tensors)
+    out = _out(type, shape)
+    return _dispatch(lambda *ts: E.node(out, "concatenate", list(ts), ints=[a]), tensors)
+
+
+def iota(shape, axis=None, type=T.S32):
+    """``Nx.iota/2`` (nx/lib/nx.ex iota; backend.ex:51)."""
+    shape = tuple(shape)
+    type = T.normalize(type)
+    a = -1 if axis is None else _norm_axis(len(shape), axis)
+    out = _out(type, shape)
+    from . import backend
+    t = E.node(out, "iota", [], ints=[a])
+    if backend.tracing():
+        return t
+    return backend.eager(lambda: E.node(out, "iota", [], ints=[a]), [])
+
+
+# ---- aggregates ---------------------------------------------------------------------
+
+
+
+def _aggregate(op, x, type, axes, keep_axes):
+    """nx/lib/nx.ex aggregate_axes_op (:9622-9660)."""
+    x = _as_operand(x)
+    if axes is not None:
+        axes = sorted(_norm_axes(x.rank, axes))
+        if axes == []:
+            return as_type(x, type)
+        shape = tuple((1 if i in axes else d) for i, d in enumerate(x.shape) if keep_axes or i not in axes)
+    else:
+        axes = list(range(x.rank))
+        shape = (1,) * x.rank if keep_axes else ()
+    out = _out(type, shape)
+    ints = [int(bool(keep_axes)), len(axes)] + axes
+    return _dispatch(lambda a: E.node(out, op, [a], ints=ints), [x])
+
+
+def sum(x, axes=None, keep_axes=False):
+    x = _as_operand(x)
+    return _aggregate("sum", x, T.to_aggregate(x.type), axes, keep_axes)
+
+
+def product(x, axes=None, keep_axes=False):
+    x = _as_operand(x)
+    return _aggregate("product", x, T.to_aggregate(x.type), axes, keep_axes)
+
+
+def reduce_max(x, axes=None, keep_axes=False):
+    x = _as_operand(x)
+    return _aggregate("reduce_max", x, x.type, axes, keep_axes)
+
+
+def reduce_min(x, axes=None, keep_axes=False):
+    x = _as_operand(x)
+    return _aggregate("reduce_min", x, x.type, axes, keep_axes)
+
+
+def all(x, axes=None, keep_axes=False):
+    return _aggregate("all", x, T.U8, axes, keep_axes)
+
+
+def any(x, axes=None, keep_axes=False):
+    return _aggregate("any", x, T.U8, axes, keep_axes)
+
+
+def mean(x, axes=None, keep_axes=False):
+    """nx/lib/nx.ex:9745-9756: ``sum / count``."""
+    x = _as_operand(x)
+    den = x.size if axes is None else math.prod(x.shape[a] for a in _norm_axes(x.rank, axes))
+    return divide(sum(x, axes=axes, keep_axes=keep_axes), den)
+
+
+def _arg_reduce(op, x, axis, keep_axis, tie_break, type):
+    """nx/lib/nx.ex:10948-11006."""
+    x = _as_operand(x)
+    if tie_break not in ("low", "high"):
+        raise ValueError(f"unknown value for :tie_break, expected :high or :low, got: {tie_break!r}")
+    type = T.normalize(type)
+    if axis is None:
+        shape = (1,) * x.rank if keep_axis else ()
+        a = -1
+    else:
+        a = _norm_axis(x.rank, axis)
+        shape = tuple((1 if i == a else d) for i, d in enumerate(x.shape) if keep_axis or i != a)
+    out = _out(type, shape)
+    ints = [int(tie_break == "high"), a, int(bool(keep_axis))]
+    return _dispatch(lambda t: E.node(out, op, [t], ints=ints), [x])
+
+
+def argmax(x, axis=None, keep_axis=False, tie_break="low", type=T.S32):
+    return _arg_reduce("argmax", x, axis, keep_axis, tie_break, type)
+
+
+def argmin(x, axis=None, keep_axis=False, tie_break="low", type=T.S32):
+    return _arg_reduce("argmin", x, axis, keep_axis, tie_break, type)
+
+
+def logsumexp(x, axes=None, keep_axes=False, exp_scaling_factor=None):
+    """nx/lib/nx.ex:18400-18433, node for node (minus the gradient-only
+    ``stop_grad`` metadata wrapper, which is an identity for evaluation)."""
+    x = _as_operand(x)
+    mx = reduce_max(x, axes=axes, keep_axes=True)
+    if _is_expr(mx):
+        mx = E.node(mx, "metadata", [mx])
+    mask = is_infinity(mx)
+    mx = select(mask, E.constant(x.type, (), 0), mx)
+    ex = exp(subtract(x, mx))
+    if exp_scaling_factor is not None:
+        ex = multiply(exp_scaling_factor, ex)
+    if not keep_axes:
+        ax = list(range(x.rank)) if axes is None else axes
+        mx = squeeze(mx, axes=ax)
+    return add(log(sum(ex, axes=axes, keep_axes=keep_axes)), mx)
+
+
+# ---- dot ------------------------------------------------------------------------------
+
+def dot(a, *args):
+    """``Nx.dot/2``, ``dot/4`` and ``dot/6`` (nx/lib/nx.ex:12836-13161)."""
+    if len(args) == 1:
+        b = args[0]
+        a, b = _as_operand(_num(a)), _as_operand(_num(b))
+        if a.rank == 0 or b.rank == 0:
+            return multiply(a, b)
+        if b.rank == 1:
+            return dot(a, [a.rank - 1], [], b, [0], [])
+        if a.rank == 1:
+            return dot(a, [0], [], b, [b.rank - 2], [])
+        return dot(a, [a.rank - 1], [], b, [b.rank - 2], [])
+    if len(args) == 3:
+        c1, b, c2 = args
+        return dot(a, c1, [], b, c2, [])
+    c1, b1, b, c2, b2 = args
+    a, b = _as_operand(_num(a)), _as_operand(_num(b))
+    c1, b1 = _norm_axes(a.rank, c1), _norm_axes(a.rank, b1)
+    c2, b2 = _norm_axes(b.rank, c2), _norm_axes(b.rank, b2)
+    # nx/lib/nx/shape.ex:1801-1850
+    if b1 and not b2:
+        raise ValueError("right tensor must be batched if left tensor is batched")
+    if b2 and not b1:
+        raise ValueError("left tensor must be batched if right tensor is batched")
+    if b1 != list(range(len(b1))):
+        raise ValueError("invalid dot batch axis for the left tensor, batch axes must be successive "
+                         f"dimensions starting from 0, got {b1}")
+    if b2 != list(range(len(b2))):
+        raise ValueError("invalid dot batch axis for the right tensor, batch axes must be successive "
+                         f"dimensions starting from 0, got {b2}")
+    if set(b1) & set(c1):
+        raise ValueError(f"dot batch axes for left tensor ({b1}) cannot be in contract axes ({c1})")
+    if set(b2) & set(c2):
+        raise ValueError(f"dot batch axes for right tensor ({b2}) cannot be in contract axes ({c2})")
+    if [a.shape[i] for i in c1] != [b.shape[i] for i in c2]:
+        raise ValueError("dot/zip expects shapes to be compatible, dimensions "
+                         f"{[a.shape[i] for i in c1]} of left do not match {[b.shape[i] for i in c2]} of right")
+    if [a.shape[i] for i in b1] != [b.shape[i] for i in b2]:
+        raise ValueError("dot batch dimensions must match")
+    shape = tuple([a.shape[i] for i in b1]
+                  + [d for i, d in enumerate(a.shape) if i not in c1 and i not in b1]
+                  + [d for i, d in enumerate(b.shape) if i not in c2 and i not in b2])
+    out = _out(T.merge(a.type, b.type), shape)
+    ints = [len(c1)] + c1 + [len(b1)] + b1 + [len(c2)] + c2 + [len(b2)] + b2
+    return _dispatch(lambda x, y: E.node(out, "dot", [x, y], ints=ints), [a, b])

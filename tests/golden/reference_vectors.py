@@ -1,0 +1,174 @@
+"""Known-answer vectors transcribed from the reference's own test files.
+
+Each case names the file and lines it was read from.  ``fun`` builds the graph
+with the nx_b200 front-end exactly as the reference test's ``defn`` does with
+Nx; ``args`` are ``(nested_list, type)`` pairs; ``expect`` is one
+``(nested_list, type)`` per output.  ``exact`` cases must match bit for bit
+(NaN == NaN, as Nx.Testing.assert_equal does, nx/lib/nx/testing.ex:22-68);
+the others use the reference's assert_all_close tolerance
+(atol = rtol = 1e-4, nx/lib/nx/testing.ex:151-154).
+
+The same list is used twice: to pin the CPU oracle (no GPU needed) and, in
+the GPU tests, to check the CUDA path through the C ABI.
+"""
+from nx_b200 import nx
+
+INF, NAN = float("inf"), float("nan")
+
+CASES = []
+
+
+def case(name, cite, fun, args, expect, exact=True, modes=("xla_like", "binary_backend")):
+    CASES.append(dict(name=name, cite=cite, fun=fun, args=args, expect=expect, exact=exact, modes=modes))
+
+
+T3 = [[[1, 2, 3], [4, 5, 6]], [[7, 8, 9], [10, 11, 12]]]
+
+# ---- sum: exla/test/exla/defn/expr_test.exs:1978-2024 ---------------------------------
+case("sum s32", "exla/test/exla/defn/expr_test.exs:1982", lambda t: nx.sum(t), [([1, 2, 3], "s32")], [(6, "s32")])
+case("sum s8 -> s32", "exla/test/exla/defn/expr_test.exs:1983", lambda t: nx.sum(t), [([1, 2, 3], "s8")], [(6, "s32")])
+case("sum u8 -> u32", "exla/test/exla/defn/expr_test.exs:1984", lambda t: nx.sum(t), [([1, 2, 3], "u8")], [(6, "u32")])
+case("sum f32", "exla/test/exla/defn/expr_test.exs:1985-1990", lambda t: nx.sum(t), [([1.0, 2.0, 3.0], "f32")], [(6.0, "f32")])
+case("sum axis 1", "exla/test/exla/defn/expr_test.exs:1997-2000", lambda t: nx.sum(t, axes=[1]), [(T3, "s32")],
+     [([[5, 7, 9], [17, 19, 21]], "s32")])
+case("sum axis -3", "exla/test/exla/defn/expr_test.exs:2001", lambda t: nx.sum(t, axes=[-3]), [(T3, "s32")],
+     [([[8, 10, 12], [14, 16, 18]], "s32")])
+case("sum axes 1,-3", "exla/test/exla/defn/expr_test.exs:2002", lambda t: nx.sum(t, axes=[1, -3]), [(T3, "s32")],
+     [([22, 26, 30], "s32")])
+case("sum of equal does not overflow", "exla/test/exla/defn/expr_test.exs:2005-2011",
+     lambda t: nx.sum(nx.equal(t, 1.0)), [([1, 1, 1], "s32")], [(3, "u32")])
+case("sum keep_axes", "exla/test/exla/defn/expr_test.exs:2017", lambda t: nx.sum(t, keep_axes=True),
+     [([1, 2, 3], "s32")], [([6], "s32")])
+case("sum axes 0,2 keep", "exla/test/exla/defn/expr_test.exs:2020-2023",
+     lambda t: nx.sum(t, axes=[0, 2], keep_axes=True),
+     [([[[1, 2, 3], [4, 5, 6]], [[1, 2, 3], [4, 5, 6]]], "s32")], [([[[12], [30]]], "s32")])
+
+# ---- reduce_max: exla/test/exla/defn/expr_test.exs:2137-2184 ----------------------------
+case("reduce_max s32", "exla/test/exla/defn/expr_test.exs:2141", lambda t: nx.reduce_max(t), [([1, 2, 3], "s32")], [(3, "s32")])
+case("reduce_max s8", "exla/test/exla/defn/expr_test.exs:2143-2146", lambda t: nx.reduce_max(t), [([1, 2, 3], "s8")], [(3, "s8")])
+case("reduce_max u8", "exla/test/exla/defn/expr_test.exs:2148-2151", lambda t: nx.reduce_max(t), [([1, 2, 3], "u8")], [(3, "u8")])
+case("reduce_max f32", "exla/test/exla/defn/expr_test.exs:2153-2158", lambda t: nx.reduce_max(t), [([1.0, 2.0, 3.0], "f32")], [(3.0, "f32")])
+case("reduce_max axis 1", "exla/test/exla/defn/expr_test.exs:2165-2168", lambda t: nx.reduce_max(t, axes=[1]), [(T3, "s32")],
+     [([[4, 5, 6], [10, 11, 12]], "s32")])
+case("reduce_max axes 1,-3", "exla/test/exla/defn/expr_test.exs:2170", lambda t: nx.reduce_max(t, axes=[1, -3]), [(T3, "s32")],
+     [([10, 11, 12], "s32")])
+case("reduce_max axes 0,2 keep", "exla/test/exla/defn/expr_test.exs:2180-2183",
+     lambda t: nx.reduce_max(t, axes=[0, 2], keep_axes=True),
+     [([[[1, 2, 3], [4, 5, 6]], [[1, 2, 3], [4, 5, 6]]], "s32")], [([[[3], [6]]], "s32")])
+
+# ---- argmax / argmin: exla/test/exla/defn/expr_test.exs:2239-2307 -----------------------
+for ty in ("s32", "s8", "u8", "f32", "bf16"):
+    case(f"argmax {ty}", "exla/test/exla/defn/expr_test.exs:2250-2256", lambda t: nx.argmax(t), [([1, 2, 3], ty)], [(2, "s32")])
+    case(f"argmin {ty}", "exla/test/exla/defn/expr_test.exs:2260-2266", lambda t: nx.argmin(t), [([1, 2, 3], ty)], [(0, "s32")])
+case("argmax flat", "exla/test/exla/defn/expr_test.exs:2256", lambda t: nx.argmax(t), [([[1, 2, 3], [4, 5, 6]], "s32")], [(5, "s32")])
+case("argmax axis 1", "exla/test/exla/defn/expr_test.exs:2269-2274", lambda t: nx.argmax(t, axis=1),
+     [([[[1, 1, 1], [1, 1, 3]], [[6, 2, 3], [2, 8, 3]]], "s32")], [([[0, 0, 1], [0, 1, 0]], "s32")])
+case("argmin axis 1", "exla/test/exla/defn/expr_test.exs:2276-2281", lambda t: nx.argmin(t, axis=1),
+     [([[[4, 2, 3], [1, -5, 3]], [[6, 2, 3], [4, 8, 3]]], "s32")], [([[1, 1, 0], [1, 0, 0]], "s32")])
+case("argmax tie low", "exla/test/exla/defn/expr_test.exs:2284", lambda t: nx.argmax(t, axis=1),
+     [([[1, 2, 2], [1, 2, 2]], "s32")], [([1, 1], "s32")])
+case("argmax tie high", "exla/test/exla/defn/expr_test.exs:2285", lambda t: nx.argmax(t, axis=1, tie_break="high"),
+     [([[1, 2, 2], [1, 2, 2]], "s32")], [([2, 2], "s32")])
+case("argmax keep_axis", "exla/test/exla/defn/expr_test.exs:2288-2296", lambda t: nx.argmax(t, axis=1, keep_axis=True),
+     [([[[4, 2, 3], [1, -5, 3]], [[6, 2, 3], [4, 8, 3]]], "s32")], [([[[0, 0, 0]], [[0, 1, 0]]], "s32")])
+case("argmin keep_axis", "exla/test/exla/defn/expr_test.exs:2298-2306", lambda t: nx.argmin(t, axis=1, keep_axis=True),
+     [([[[4, 2, 3], [1, -5, 3]], [[6, 2, 3], [4, 8, 3]]], "s32")], [([[[1, 1, 0]], [[1, 0, 0]]], "s32")])
+
+NONFINITE = [[-INF, INF, 1], [-INF, NAN, 1], [-INF, -INF, 1], [-INF, 0, 1], [INF, INF, 1], [INF, NAN, 1],
+             [INF, -INF, 1], [INF, 0, 1], [NAN, INF, 1], [NAN, NAN, 1], [NAN, -INF, 1], [NAN, 0, 1]]
+# The two-NaN row (index 9) is where BinaryBackend's scan order shows: it
+# returns the last NaN.  EXLA's reducer is order dependent there, so the row is
+# only pinned for the BinaryBackend mode (and the CUDA path follows it).
+case("argmax non-finite", "nx/test/nx_test.exs:1778-1798", lambda t: nx.argmax(t, axis=1), [(NONFINITE, "f32")],
+     [([1, 1, 2, 2, 0, 1, 0, 0, 0, 1, 0, 0], "s32")], modes=("binary_backend",))
+case("argmin non-finite", "nx/test/nx_test.exs:1746-1766", lambda t: nx.argmin(t, axis=1), [(NONFINITE, "f32")],
+     [([0, 1, 0, 0, 2, 1, 1, 1, 0, 1, 0, 0], "s32")], modes=("binary_backend",))
+
+# ---- dot: exla/test/exla/defn/expr_test.exs:2603-2695 ------------------------------------
+case("dot scalars", "exla/test/exla/defn/expr_test.exs:2607-2609", lambda a, b: nx.dot(a, b), [(-2.0, "f32"), (-2, "s32")], [(4.0, "f32")])
+case("dot vectors s32", "exla/test/exla/defn/expr_test.exs:2613-2616", lambda a, b: nx.dot(a, b),
+     [([1, 2, 3], "s32"), ([4, 5, 6], "s32")], [(32, "s32")])
+case("dot vectors f32 x s32", "exla/test/exla/defn/expr_test.exs:2618-2621", lambda a, b: nx.dot(a, b),
+     [([1.0, 2.0, 3.0], "f32"), ([4, 5, 6], "s32")], [(32.0, "f32")])
+case("dot matrices s32", "exla/test/exla/defn/expr_test.exs:2627-2633", lambda a, b: nx.dot(a, b),
+     [([[1, 2, 3], [4, 5, 6]], "s32"), ([[7, 8], [9, 10], [11, 12]], "s32")], [([[58, 64], [139, 154]], "s32")])
+case("dot matrices f32", "exla/test/exla/defn/expr_test.exs:2635-2641", lambda a, b: nx.dot(a, b),
+     [([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], "f32"), ([[7.0, 8.0], [9.0, 10.0], [11.0, 12.0]], "f32")],
+     [([[58.0, 64.0], [139.0, 154.0]], "f32")])
+case("dot matrices f32 x s32", "exla/test/exla/defn/expr_test.exs:2643-2649", lambda a, b: nx.dot(a, b),
+     [([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]], "f32"), ([[7, 8], [9, 10], [11, 12]], "s32")],
+     [([[58.0, 64.0], [139.0, 154.0]], "f32")])
+case("dot tensors", "exla/test/exla/defn/expr_test.exs:2652-2671", lambda a, b: nx.dot(a, b),
+     [([[[1, 2, 3], [4, 5, 6], [7, 8, 9]], [[1, 2, 3], [4, 5, 6], [7, 8, 9]]], "s32"),
+      ([[[1, 2, 3], [3, 4, 5], [5, 6, 7]]], "s32")],
+     [([[[[22, 28, 34]], [[49, 64, 79]], [[76, 100, 124]]], [[[22, 28, 34]], [[49, 64, 79]], [[76, 100, 124]]]], "s32")])
+case("batched dot", "exla/test/exla/defn/expr_test.exs:2673-2684",
+     lambda a, b: nx.dot(a, [1], [0], b, [1], [0]),
+     [([[[0, 1, 2], [3, 4, 5]], [[6, 7, 8], [9, 10, 11]], [[12, 13, 14], [15, 16, 17]]], "f32"),
+      ([[[0, 1], [2, 3]], [[4, 5], [6, 7]], [[8, 9], [10, 11]]], "f32")],
+     [([[[6.0, 9.0], [8.0, 13.0], [10.0, 17.0]], [[78.0, 93.0], [88.0, 105.0], [98.0, 117.0]],
+        [[246.0, 273.0], [264.0, 293.0], [282.0, 313.0]]], "f32")])
+
+
+def _iota_list(shape):
+    import numpy as np
+    return np.arange(int(np.prod(shape))).reshape(shape).tolist()
+
+
+case("general dot", "exla/test/exla/defn/expr_test.exs:2686-2694",
+     lambda a, b: nx.dot(a, [0, 1], [], b, [1, 2], []),
+     [(_iota_list((4, 5, 2)), "f32"), (_iota_list((2, 4, 5)), "f32")], [([[4940.0, 12540.0], [5130.0, 13130.0]], "f32")])
+case("dot/6 batched doc example", "nx/lib/nx.ex:13040-13054",
+     lambda u, v: nx.dot(u, [2], [0], v, [1], [0]),
+     [([[[1, 1]], [[2, 2]]], "s32"), ([[[3], [3]], [[4], [4]]], "s32")], [([[[6]], [[16]]], "s32")])
+case("bf16 dot = 14", "exla/test/exla/defn/expr_test.exs:4275-4283", lambda a, b: nx.dot(a, b),
+     [([1, 2, 3], "bf16"), ([1, 2, 3], "bf16")], [(14, "bf16")])
+
+# ---- as_type, bf16, select: exla/test/exla/defn/expr_test.exs ---------------------------
+case("as_type s32 -> f32", "exla/test/exla/defn/expr_test.exs:1111-1113", lambda t: nx.as_type(t, "f32"),
+     [([1, 2, 3], "s32")], [([1.0, 2.0, 3.0], "f32")])
+case("as_type non-finite -> u8", "exla/test/exla/defn/expr_test.exs:1121-1124", lambda t: nx.as_type(t, "u8"),
+     [([INF, NAN, -INF], "f32")], [([255, 0, 0], "u8")])
+case("as_type non-finite -> s16", "exla/test/exla/defn/expr_test.exs:1126-1129", lambda t: nx.as_type(t, "s16"),
+     [([INF, NAN, -INF], "f32")], [([32767, 0, -32768], "s16")])
+case("bf16 add", "exla/test/exla/defn/expr_test.exs:4247-4255", lambda a, b: a + b,
+     [([1.0, 2.0, 3.0], "bf16"), ([4.0, 5.0, 6.0], "bf16")], [([5.0, 7.0, 9.0], "bf16")])
+case("select scalar pred", "exla/test/exla/defn/expr_test.exs:765-769", lambda p, a, b: nx.select(p, a, b),
+     [(1, "s32"), ([1, 2, 3], "s32"), ([4, 5, 6], "s32")], [([1, 2, 3], "s32")])
+case("select merges types", "exla/test/exla/defn/expr_test.exs:781-788", lambda p, a, b: nx.select(p, a, b),
+     [(1, "s32"), ([1, 2, 3], "u8"), ([4, 5, 6], "f32")], [([1.0, 2.0, 3.0], "f32")])
+case("select broadcast", "exla/test/exla/defn/expr_test.exs:792-795", lambda p, a, b: nx.select(p, a, b),
+     [([1, 0, 1, 0, 1], "s32"), ([10], "s32"), ([1, 2, 3, 4, 5], "s32")], [([10, 2, 10, 4, 10], "s32")])
+case("select non-zero is true", "exla/test/exla/defn/expr_test.exs:797-800", lambda p, a, b: nx.select(p, a, b),
+     [([-2, -1, 0, 1, 2], "s32"), ([10], "s32"), ([1, 2, 3, 4, 5], "s32")], [([10, 10, 3, 10, 10], "s32")])
+case("add s32", "exla/test/exla/defn/expr_test.exs:175", lambda a, b: a + b, [([1, 2], "s32"), ([3, 4], "s32")], [([4, 6], "s32")])
+case("add u8 + (-3) -> s16", "exla/test/exla/defn/expr_test.exs:179-208 (types per nx/lib/nx/type.ex:536-566)",
+     lambda a: a + (-3), [([1, 2], "u8")], [([-2, -1], "s16")])
+case("add u8 + 3.0 -> f32", "exla/test/exla/defn/expr_test.exs:179-208", lambda a: a + 3.0, [([1, 2], "u8")], [([4.0, 5.0], "f32")])
+case("add f32 + u16", "exla/test/exla/defn/expr_test.exs:179-208", lambda a, b: a + b,
+     [([1, 2], "f32"), (3, "u16")], [([4.0, 5.0], "f32")])
+
+# ---- softmax, logsumexp ---------------------------------------------------------------------
+case("softmax", "exla/test/exla/defn/expr_test.exs:3057-3071", lambda t: nx.exp(t) / nx.sum(nx.exp(t)),
+     [([1.0, 2.0, 3.0, 4.0], "f32")],
+     [([0.03205860328008499, 0.08714431874203257, 0.23688281808991013, 0.6439142598879722], "f32")], exact=False)
+case("logsumexp removes axes", "nx/test/nx_test.exs:3516-3530", lambda t: nx.logsumexp(t, axes=[2]),
+     [([[[11.0], [12.0], [13.0]]], "f32")], [([[11.0, 12.0, 13.0]], "f32")])
+LSE_IN = [[INF, INF, INF], [INF, INF, -INF], [INF, INF, 0.0], [INF, -INF, INF], [INF, -INF, -INF], [INF, -INF, 0.0],
+          [INF, 0.0, INF], [INF, 0.0, -INF], [INF, 0.0, 0.0], [-INF, INF, INF], [-INF, INF, -INF], [-INF, INF, 0.0],
+          [-INF, -INF, INF], [-INF, -INF, -INF], [-INF, -INF, 0.0], [-INF, 0.0, INF], [-INF, 0.0, -INF],
+          [-INF, 0.0, 0.0], [0.0, INF, INF], [0.0, INF, -INF], [0.0, INF, 0.0], [0.0, -INF, INF], [0.0, -INF, -INF],
+          [0.0, -INF, 0.0], [0.0, 0.0, INF], [0.0, 0.0, -INF]]
+LSE_OUT = [INF] * 13 + [-INF, 0.0, INF, 0.0, 0.6931471824645996, INF, INF, INF, INF, 0.0, 0.6931471824645996, INF,
+                        0.6931471824645996]
+case("logsumexp infinities", "nx/test/nx_test.exs:3532-3593", lambda t: nx.logsumexp(t, axes=[1]),
+     [(LSE_IN, "f32")], [(LSE_OUT, "f32")])
+case("logsumexp doc all", "nx/lib/nx.ex:18340-18344", lambda t: nx.logsumexp(t), [([[1, 2], [3, 4], [5, 6]], "s32")],
+     [(6.4561934, "f32")], exact=False)
+case("logsumexp doc axis y", "nx/lib/nx.ex:18353-18358", lambda t: nx.logsumexp(t, axes=[1]), [([[1, 2], [3, 4], [5, 6]], "s32")],
+     [([2.3132617, 4.3132615, 6.3132615], "f32")], exact=False)
+case("logsumexp doc axes x,z keep", "nx/lib/nx.ex:18368-18379", lambda t: nx.logsumexp(t, axes=[0, 2], keep_axes=True),
+     [([[[1, 2], [3, 4]], [[5, 6], [7, 8]]], "s32")], [([[[6.3314114], [8.331411]]], "f32")], exact=False)
+case("logsumexp scaling factor", "nx/lib/nx.ex:18333-18339",
+     lambda t, a: nx.logsumexp(t, exp_scaling_factor=a),
+     [([1, 2, 3, 4, 5, 6], "s32"), ([-1, -1, -1, 1, 1, 1], "s32")], [(6.356537, "f32")], exact=False)
