@@ -136,6 +136,9 @@ int nxb200_program_release(nxb200_program *prog);
 /* Human-readable plan: one line per launched kernel with its name, grid and
  * the graph nodes fused into it.  Returns the number of bytes needed. */
 size_t nxb200_program_describe(nxb200_program *prog, char *dst, size_t cap);
+/* Generated CUDA source of the i-th fused kernel (diagnostics; 0 when i is out
+ * of range).  Returns the number of bytes needed. */
+size_t nxb200_program_kernel_source(nxb200_program *prog, int i, char *dst, size_t cap);
 /* Number of kernels one run launches. */
 int nxb200_program_launch_count(nxb200_program *prog, int *count);
 

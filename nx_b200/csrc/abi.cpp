@@ -1,0 +1,466 @@
+// extern "C" surface of libnxb200.so (declared in include/nxb200.h).
+#include <algorithm>
+
+#include "gemm.h"
+#include "program.h"
+
+namespace nxb {
+const std::string& last_error();
+void canonicalize_dots(Graph& g);
+int comm_all_reduce_sum(nxb200_buffer* buf);
+}  // namespace nxb
+
+using namespace nxb;
+
+namespace {
+
+template <typename F> int guarded(F&& f) {
+  try {
+    f();
+    return NXB_OK;
+  } catch (const Error& e) {
+    set_last_error(e.msg);
+    return e.status;
+  } catch (const std::bad_alloc&) {
+    set_last_error("host allocation failed");
+    return NXB_ERR_OUT_OF_MEMORY;
+  } catch (const std::exception& e) {
+    set_last_error(e.what());
+    return NXB_ERR_RUNTIME;
+  }
+}
+
+nxb200_buffer* check_buffer(nxb200_buffer* b, bool need_live = true) {
+  if (!b || b->magic != 0x4e584242) fail(NXB_ERR_INVALID_ARGUMENT, "not a buffer handle");
+  if (need_live && b->deallocated.load()) fail(NXB_ERR_RUNTIME, "buffer has been deallocated (use after free)");
+  return b;
+}
+
+nxb200_program* check_program(nxb200_program* p) {
+  if (!p || p->magic != 0x4e584250) fail(NXB_ERR_INVALID_ARGUMENT, "not a program handle");
+  return p;
+}
+
+nxb200_buffer* make_buffer(Device& d, DType dt, const int64_t* dims, int rank) {
+  if (rank < 0 || rank > NXB_MAX_RANK) fail(NXB_ERR_INVALID_ARGUMENT, "rank out of range");
+  if ((int)dt < 0 || dt > NXB_F64) fail(NXB_ERR_INVALID_ARGUMENT, "unknown element type");
+  auto b = std::make_unique<nxb200_buffer>();
+  b->device = d.id;
+  b->dtype = dt;
+  for (int i = 0; i < rank; ++i) {
+    if (dims[i] < 0) fail(NXB_ERR_INVALID_ARGUMENT, "negative dimension");
+    b->dims.push_back(dims[i]);
+  }
+  b->nbytes = (size_t)shape_numel(b->dims) * dtype_size(dt);
+  {
+    std::lock_guard<std::mutex> g(d.mu);
+    b->ptr = d.alloc.alloc(b->nbytes);
+  }
+  return b.release();
+}
+
+void ensure_loaded(nxb200_program* p, Device& d) {
+  auto it = p->loaded.find(d.id);
+  if (it != p->loaded.end()) return;
+  const DriverApi& drv = driver();
+  if (!drv.cuModuleLoadData || !drv.cuLaunchKernel) fail(NXB_ERR_RUNTIME, "CUDA driver entry points are unavailable");
+  nxb200_program::Loaded L;
+  for (auto& ks : p->plan->kernels) {
+    CUmodule m;
+    check_cu(drv.cuModuleLoadData(&m, ks.cubin.data()), ("loading kernel " + ks.name).c_str());
+    CUfunction f;
+    check_cu(drv.cuModuleGetFunction(&f, m, ks.name.c_str()), ("resolving kernel " + ks.name).c_str());
+    L.modules.push_back(m);
+    L.functions.push_back(f);
+  }
+  for (size_t s = 0; s < p->plan->slots.size(); ++s) {
+    const Slot& sl = p->plan->slots[s];
+    if (sl.kind != Slot::LITERAL) continue;
+    void* ptr = d.alloc.alloc(sl.nbytes);
+    const std::string& blob = p->plan->g.nodes[sl.node].blob;
+    NXB_CUDA(cudaMemcpyAsync(ptr, blob.data(), blob.size(), cudaMemcpyHostToDevice, d.stream));
+    L.literals[(int)s] = ptr;
+  }
+  NXB_CUDA(cudaStreamSynchronize(d.stream));
+  p->loaded.emplace(d.id, std::move(L));
+}
+
+void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int n_args, nxb200_buffer** outs, int n_outs,
+                 bool outs_provided) {
+  Plan& plan = *p->plan;
+  if (n_args != (int)plan.param_slots.size())
+    fail(NXB_ERR_INVALID_ARGUMENT, "program takes " + std::to_string(plan.param_slots.size()) + " arguments, got " + std::to_string(n_args));
+  if (n_outs != (int)plan.output_slots.size())
+    fail(NXB_ERR_INVALID_ARGUMENT, "program has " + std::to_string(plan.output_slots.size()) + " outputs, got room for " + std::to_string(n_outs));
+  Device& d = nxb::device(device);
+  std::vector<void*> ptr(plan.slots.size(), nullptr);
+  for (int i = 0; i < n_args; ++i) {
+    int s = plan.param_slots[i];
+    nxb200_buffer* b = check_buffer(args[i]);
+    if (b->device != device) fail(NXB_ERR_INVALID_ARGUMENT, "argument " + std::to_string(i) + " lives on device " + std::to_string(b->device) + ", program runs on " + std::to_string(device));
+    if (s < 0) continue;
+    const Slot& sl = plan.slots[s];
+    if (b->dtype != sl.dt || b->dims != sl.shape)
+      fail(NXB_ERR_INVALID_ARGUMENT, "argument " + std::to_string(i) + " is " + dtype_name(b->dtype) + shape_str(b->dims) + ", program was built for " +
+                                         dtype_name(sl.dt) + shape_str(sl.shape));
+    ptr[s] = b->ptr;
+  }
+  std::lock_guard<std::mutex> pg(p->mu);
+  std::lock_guard<std::mutex> dg(d.mu);
+  ensure_loaded(p, d);
+  auto& L = p->loaded[device];
+  for (auto& kv : L.literals) ptr[kv.first] = kv.second;
+  std::vector<nxb200_buffer*> made;
+  try {
+    for (int i = 0; i < n_outs; ++i) {
+      const Slot& sl = plan.slots[plan.output_slots[i]];
+      if (outs_provided) {
+        nxb200_buffer* b = check_buffer(outs[i]);
+        if (b->device != device || b->dtype != sl.dt || b->dims != sl.shape)
+          fail(NXB_ERR_INVALID_ARGUMENT, "output buffer " + std::to_string(i) + " does not match " + dtype_name(sl.dt) + shape_str(sl.shape));
+        ptr[plan.output_slots[i]] = b->ptr;
+      } else {
+        auto b = std::make_unique<nxb200_buffer>();
+        b->device = device;
+        b->dtype = sl.dt;
+        b->dims = sl.shape;
+        b->nbytes = sl.nbytes;
+        b->ptr = d.alloc.alloc(sl.nbytes);
+        ptr[plan.output_slots[i]] = b->ptr;
+        made.push_back(b.release());
+      }
+    }
+    const DriverApi& drv = driver();
+    for (size_t st = 0; st < plan.steps.size(); ++st) {
+      for (size_t s = 0; s < plan.slots.size(); ++s)
+        if (plan.slots[s].kind == Slot::TEMP && plan.slots[s].first_step == (int)st && !ptr[s]) ptr[s] = d.alloc.alloc(plan.slots[s].nbytes);
+      const Step& step = plan.steps[st];
+      if (step.kind == Step::KERNEL) {
+        const KernelSpec& ks = plan.kernels[step.index];
+        std::vector<void*> argv(ks.arg_slots.size());
+        std::vector<void*> argp(ks.arg_slots.size());
+        for (size_t a = 0; a < ks.arg_slots.size(); ++a) {
+          void* base = ptr[ks.arg_slots[a]];
+          if (!base) fail(NXB_ERR_RUNTIME, "internal: kernel " + ks.name + " reads a buffer that was never produced");
+          argv[a] = (char*)base + ks.arg_offsets[a];
+          argp[a] = &argv[a];
+        }
+        check_cu(drv.cuLaunchKernel(L.functions[step.index], ks.grid, 1, 1, ks.block, 1, 1, ks.smem, (CUstream)d.stream, argp.data(), nullptr),
+                 ("launching " + ks.name).c_str());
+      } else {
+        const GemmSpec& gs = plan.gemms[step.index];
+        GemmArgs ga{};
+        ga.a = ptr[gs.a.slot];
+        ga.b = ptr[gs.b.slot];
+        ga.c = ptr[gs.out_slot];
+        ga.batch = gs.batch; ga.m = gs.m; ga.n = gs.n; ga.k = gs.k;
+        ga.lda = gs.a.ld; ga.ldb = gs.b.ld; ga.bsa = gs.a.batch_stride; ga.bsb = gs.b.batch_stride;
+        ga.ta = gs.a.trans; ga.tb = gs.b.trans;
+        ga.da = gs.a.dt; ga.db = gs.b.dt; ga.dc = gs.out_dt;
+        ga.epilogue = gs.epilogue;
+        launch_simt_gemm(ga, d.stream);
+      }
+      for (size_t s = 0; s < plan.slots.size(); ++s)
+        if (plan.slots[s].kind == Slot::TEMP && plan.slots[s].last_step == (int)st && ptr[s]) { d.alloc.free(ptr[s]); ptr[s] = nullptr; }
+    }
+  } catch (...) {
+    for (auto* b : made) { d.alloc.free(b->ptr); delete b; }
+    for (size_t s = 0; s < plan.slots.size(); ++s)
+      if (plan.slots[s].kind == Slot::TEMP && ptr[s]) d.alloc.free(ptr[s]);
+    throw;
+  }
+  if (!outs_provided)
+    for (int i = 0; i < n_outs; ++i) outs[i] = made[i];
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t nxb200_last_error(char* dst, size_t cap) {
+  const std::string& e = last_error();
+  if (dst && cap) {
+    size_t n = std::min(cap - 1, e.size());
+    memcpy(dst, e.data(), n);
+    dst[n] = 0;
+  }
+  return e.size();
+}
+
+int nxb200_init(void) {
+  return guarded([] { (void)device_count(); });
+}
+
+int nxb200_device_count(int* count) {
+  return guarded([&] {
+    if (!count) fail(NXB_ERR_INVALID_ARGUMENT, "count is NULL");
+    *count = device_count();
+  });
+}
+
+int nxb200_buffer_alloc(int dev, nxb200_dtype dtype, const int64_t* dims, int rank, nxb200_buffer** out) {
+  return guarded([&] {
+    if (!out) fail(NXB_ERR_INVALID_ARGUMENT, "out is NULL");
+    Device& d = nxb::device(dev);
+    *out = make_buffer(d, dtype, dims, rank);
+  });
+}
+
+int nxb200_buffer_from_host(int dev, nxb200_dtype dtype, const int64_t* dims, int rank, const void* src, size_t nbytes,
+                            nxb200_buffer** out) {
+  return guarded([&] {
+    if (!out) fail(NXB_ERR_INVALID_ARGUMENT, "out is NULL");
+    Device& d = nxb::device(dev);
+    nxb200_buffer* b = make_buffer(d, dtype, dims, rank);
+    if (nbytes != b->nbytes) {
+      size_t want = b->nbytes;
+      { std::lock_guard<std::mutex> g(d.mu); d.alloc.free(b->ptr); }
+      delete b;
+      fail(NXB_ERR_INVALID_ARGUMENT, "binary has " + std::to_string(nbytes) + " bytes, tensor needs " + std::to_string(want));
+    }
+    if (nbytes) {
+      cudaError_t e = cudaMemcpyAsync(b->ptr, src, nbytes, cudaMemcpyHostToDevice, d.stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(d.stream);
+      if (e != cudaSuccess) {
+        { std::lock_guard<std::mutex> g(d.mu); d.alloc.free(b->ptr); }
+        delete b;
+        fail(NXB_ERR_RUNTIME, std::string("host to device copy failed: ") + cudaGetErrorString(e));
+      }
+    }
+    *out = b;
+  });
+}
+
+int nxb200_buffer_to_host(nxb200_buffer* buf, void* dst, size_t nbytes) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf);
+    if (nbytes > b->nbytes) fail(NXB_ERR_INVALID_ARGUMENT, "asked for more bytes than the tensor holds");
+    Device& d = nxb::device(b->device);
+    if (nbytes) NXB_CUDA(cudaMemcpyAsync(dst, b->ptr, nbytes, cudaMemcpyDeviceToHost, d.stream));
+    NXB_CUDA(cudaStreamSynchronize(d.stream));
+  });
+}
+
+int nxb200_buffer_write_async(nxb200_buffer* buf, const void* src, size_t nbytes) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf);
+    if (nbytes > b->nbytes) fail(NXB_ERR_INVALID_ARGUMENT, "more bytes than the tensor holds");
+    Device& d = nxb::device(b->device);
+    NXB_CUDA(cudaMemcpyAsync(b->ptr, src, nbytes, cudaMemcpyHostToDevice, d.stream));
+  });
+}
+
+int nxb200_buffer_read_async(nxb200_buffer* buf, void* dst, size_t nbytes) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf);
+    if (nbytes > b->nbytes) fail(NXB_ERR_INVALID_ARGUMENT, "more bytes than the tensor holds");
+    Device& d = nxb::device(b->device);
+    NXB_CUDA(cudaMemcpyAsync(dst, b->ptr, nbytes, cudaMemcpyDeviceToHost, d.stream));
+  });
+}
+
+int nxb200_buffer_copy_to_device(nxb200_buffer* buf, int dev, nxb200_buffer** out) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf);
+    if (!out) fail(NXB_ERR_INVALID_ARGUMENT, "out is NULL");
+    Device& src = nxb::device(b->device);
+    NXB_CUDA(cudaStreamSynchronize(src.stream));
+    Device& d = nxb::device(dev);
+    nxb200_buffer* nb = make_buffer(d, b->dtype, b->dims.data(), (int)b->dims.size());
+    cudaError_t e = cudaSuccess;
+    if (b->nbytes) {
+      e = cudaMemcpyPeerAsync(nb->ptr, dev, b->ptr, b->device, b->nbytes, d.stream);
+      if (e == cudaSuccess) e = cudaStreamSynchronize(d.stream);
+    }
+    if (e != cudaSuccess) {
+      { std::lock_guard<std::mutex> g(d.mu); d.alloc.free(nb->ptr); }
+      delete nb;
+      fail(NXB_ERR_RUNTIME, std::string("device to device copy failed: ") + cudaGetErrorString(e));
+    }
+    *out = nb;
+  });
+}
+
+int nxb200_buffer_info(nxb200_buffer* buf, nxb200_dtype* dtype, int64_t* dims, int* rank, int* dev) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf, false);
+    if (dtype) *dtype = b->dtype;
+    if (rank) *rank = (int)b->dims.size();
+    if (dims) for (size_t i = 0; i < b->dims.size(); ++i) dims[i] = b->dims[i];
+    if (dev) *dev = b->device;
+  });
+}
+
+int nxb200_buffer_device_pointer(nxb200_buffer* buf, void** ptr) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf);
+    if (!ptr) fail(NXB_ERR_INVALID_ARGUMENT, "ptr is NULL");
+    *ptr = b->ptr;
+  });
+}
+
+int nxb200_buffer_deallocate(nxb200_buffer* buf) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf, false);
+    bool was = b->deallocated.exchange(true);
+    if (was) fail(NXB_ERR_ALREADY_DEALLOCATED, "buffer was already deallocated");
+    Device& d = nxb::device(b->device);
+    std::lock_guard<std::mutex> g(d.mu);
+    d.alloc.free(b->ptr);
+    b->ptr = nullptr;
+  });
+}
+
+int nxb200_buffer_is_deallocated(nxb200_buffer* buf, int* flag) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf, false);
+    if (flag) *flag = b->deallocated.load() ? 1 : 0;
+  });
+}
+
+int nxb200_buffer_release(nxb200_buffer* buf) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf, false);
+    if (!b->deallocated.exchange(true) && b->ptr) {
+      Device& d = nxb::device(b->device);
+      std::lock_guard<std::mutex> g(d.mu);
+      d.alloc.free(b->ptr);
+    }
+    b->magic = 0;
+    delete b;
+  });
+}
+
+int nxb200_program_build(const uint8_t* bytes, size_t nbytes, nxb200_program** out) {
+  return guarded([&] {
+    if (!bytes || !out) fail(NXB_ERR_INVALID_ARGUMENT, "NULL argument");
+    auto p = std::make_unique<nxb200_program>();
+    p->plan = build_plan(bytes, nbytes);
+    *out = p.release();
+  });
+}
+
+int nxb200_program_io(nxb200_program* prog, int* n_params, int* n_outputs) {
+  return guarded([&] {
+    nxb200_program* p = check_program(prog);
+    if (n_params) *n_params = (int)p->plan->param_slots.size();
+    if (n_outputs) *n_outputs = (int)p->plan->output_slots.size();
+  });
+}
+
+int nxb200_program_output_info(nxb200_program* prog, int i, nxb200_dtype* dtype, int64_t* dims, int* rank) {
+  return guarded([&] {
+    nxb200_program* p = check_program(prog);
+    if (i < 0 || i >= (int)p->plan->output_slots.size()) fail(NXB_ERR_INVALID_ARGUMENT, "output index out of range");
+    const Slot& sl = p->plan->slots[p->plan->output_slots[i]];
+    if (dtype) *dtype = sl.dt;
+    if (rank) *rank = (int)sl.shape.size();
+    if (dims) for (size_t k = 0; k < sl.shape.size(); ++k) dims[k] = sl.shape[k];
+  });
+}
+
+int nxb200_program_run(nxb200_program* prog, int dev, nxb200_buffer* const* args, int n_args, nxb200_buffer** outs, int n_outs) {
+  return guarded([&] { run_program(check_program(prog), dev, args, n_args, outs, n_outs, false); });
+}
+
+int nxb200_program_run_into(nxb200_program* prog, int dev, nxb200_buffer* const* args, int n_args, nxb200_buffer* const* outs,
+                            int n_outs) {
+  return guarded([&] { run_program(check_program(prog), dev, args, n_args, const_cast<nxb200_buffer**>(outs), n_outs, true); });
+}
+
+int nxb200_program_release(nxb200_program* prog) {
+  return guarded([&] {
+    nxb200_program* p = check_program(prog);
+    for (auto& kv : p->loaded) {
+      if (cudaSetDevice(kv.first) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+      Device& d = nxb::device(kv.first);
+      cudaStreamSynchronize(d.stream);
+      for (auto m : kv.second.modules) driver().cuModuleUnload(m);
+      std::lock_guard<std::mutex> g(d.mu);
+      for (auto& l : kv.second.literals) d.alloc.free(l.second);
+    }
+    p->magic = 0;
+    delete p;
+  });
+}
+
+size_t nxb200_program_describe(nxb200_program* prog, char* dst, size_t cap) {
+  if (!prog || prog->magic != 0x4e584250) return 0;
+  std::string s = prog->plan->describe();
+  if (dst && cap) {
+    size_t n = std::min(cap - 1, s.size());
+    memcpy(dst, s.data(), n);
+    dst[n] = 0;
+  }
+  return s.size();
+}
+
+size_t nxb200_program_kernel_source(nxb200_program* prog, int i, char* dst, size_t cap) {
+  if (!prog || prog->magic != 0x4e584250 || i < 0 || i >= (int)prog->plan->kernels.size()) return 0;
+  const std::string& s = prog->plan->kernels[i].source;
+  if (dst && cap) {
+    size_t n = std::min(cap - 1, s.size());
+    memcpy(dst, s.data(), n);
+    dst[n] = 0;
+  }
+  return s.size();
+}
+
+int nxb200_program_launch_count(nxb200_program* prog, int* count) {
+  return guarded([&] {
+    nxb200_program* p = check_program(prog);
+    if (count) *count = (int)p->plan->steps.size();
+  });
+}
+
+int nxb200_device_synchronize(int dev) {
+  return guarded([&] {
+    Device& d = nxb::device(dev);
+    NXB_CUDA(cudaStreamSynchronize(d.stream));
+  });
+}
+
+int nxb200_timer_begin(int dev) {
+  return guarded([&] {
+    Device& d = nxb::device(dev);
+    NXB_CUDA(cudaEventRecord(d.ev0, d.stream));
+  });
+}
+
+int nxb200_timer_end(int dev, float* ms) {
+  return guarded([&] {
+    Device& d = nxb::device(dev);
+    NXB_CUDA(cudaEventRecord(d.ev1, d.stream));
+    NXB_CUDA(cudaEventSynchronize(d.ev1));
+    float t = 0;
+    NXB_CUDA(cudaEventElapsedTime(&t, d.ev0, d.ev1));
+    if (ms) *ms = t;
+  });
+}
+
+int nxb200_device_stream(int dev, void** stream) {
+  return guarded([&] {
+    Device& d = nxb::device(dev);
+    if (stream) *stream = (void*)d.stream;
+  });
+}
+
+int nxb200_memory_stats(int dev, uint64_t* allocated, uint64_t* peak, uint64_t* reserved) {
+  return guarded([&] {
+    Device& d = nxb::device(dev);
+    std::lock_guard<std::mutex> g(d.mu);
+    if (allocated) *allocated = d.alloc.allocated;
+    if (peak) *peak = d.alloc.peak;
+    if (reserved) *reserved = d.alloc.reserved;
+  });
+}
+
+int nxb200_memory_reset_peak(int dev) {
+  return guarded([&] {
+    Device& d = nxb::device(dev);
+    std::lock_guard<std::mutex> g(d.mu);
+    d.alloc.peak = d.alloc.allocated;
+  });
+}
+
+}  // extern "C"

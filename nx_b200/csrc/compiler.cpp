@@ -1,0 +1,1405 @@
+// defn compiler: fusion planner + CUDA source generator.
+//
+// Replaces the Expr -> StableHLO lowering of exla/lib/exla/defn.ex:1090-1706 and
+// XLA's fusion passes for the subset of ops on the hot path.  Strategy:
+//
+//   * values that must live in HBM ("materialised"): parameters, literals,
+//     program outputs, dot operands/results, concatenate results, and reduction
+//     results read by another kernel;
+//   * every other elementwise / view / iota / constant node is generated inline
+//     into each kernel that needs it (index maps of broadcast / transpose /
+//     slice / squeeze compose into the load address, so views cost nothing);
+//   * reductions over trailing axes with the same row shape, everything they
+//     depend on and everything computed from their results are fused into ONE
+//     "row kernel": a CTA (or a warp) owns a row, keeps it in registers, and
+//     runs the dependent phases (max -> exp/sum -> normalise ...) back to back;
+//   * remaining elementwise outputs become flat 128-bit-vectorised kernels.
+//
+// All shapes are compile-time constants of the generated source (programs are
+// specialised per argument signature, as in the reference).
+#include <algorithm>
+#include <functional>
+#include <set>
+#include <sstream>
+
+#include "program.h"
+
+namespace nxb {
+
+namespace {
+
+// ---------------------------------------------------------------------------------
+// op tables
+const std::set<std::string> kUnaryMath = {"exp", "expm1", "log", "log1p", "sigmoid", "cos", "sin", "tan", "cosh",
+                                          "sinh", "tanh", "acos", "asin", "atan", "acosh", "asinh", "atanh", "sqrt",
+                                          "rsqrt", "cbrt", "erf", "erfc", "erf_inv"};
+const std::set<std::string> kUnaryOther = {"abs", "bitwise_not", "ceil", "floor", "negate", "round", "sign",
+                                           "count_leading_zeros", "population_count", "is_nan", "is_infinity",
+                                           "as_type", "copy"};
+const std::set<std::string> kBinary = {"add", "subtract", "multiply", "divide", "pow", "remainder", "atan2", "min",
+                                       "max", "quotient", "bitwise_and", "bitwise_or", "bitwise_xor", "left_shift",
+                                       "right_shift", "equal", "not_equal", "greater", "less", "greater_equal",
+                                       "less_equal", "logical_and", "logical_or", "logical_xor"};
+const std::set<std::string> kCompare = {"equal", "not_equal", "greater", "less", "greater_equal", "less_equal"};
+const std::set<std::string> kLogical = {"logical_and", "logical_or", "logical_xor"};
+const std::set<std::string> kReduce = {"sum", "product", "reduce_max", "reduce_min", "all", "any"};
+const std::set<std::string> kArgReduce = {"argmax", "argmin"};
+const std::set<std::string> kView = {"reshape", "squeeze", "broadcast", "transpose", "slice", "metadata"};
+
+bool is_reduce(const Node& n) { return kReduce.count(n.op) || kArgReduce.count(n.op); }
+bool is_inline(const Node& n) {   // can be generated inside a consumer's kernel
+  return kUnaryMath.count(n.op) || kUnaryOther.count(n.op) || kBinary.count(n.op) || kView.count(n.op) ||
+         n.op == "select" || n.op == "clip" || n.op == "constant" || n.op == "iota";
+}
+
+const char* storage_type(DType t) {
+  static const char* n[] = {"uint8_t", "uint16_t", "uint32_t", "uint64_t", "int8_t", "int16_t", "int32_t", "int64_t",
+                            "f16_t", "bf16_t", "float", "double"};
+  return n[(int)t];
+}
+const char* reg_type(DType t) {
+  if (t == NXB_F16 || t == NXB_BF16) return "float";
+  return storage_type(t);
+}
+const char* unsigned_of(DType t) {
+  static const char* n[] = {"uint8_t", "uint16_t", "uint32_t", "uint64_t", "uint8_t", "uint16_t", "uint32_t", "uint64_t"};
+  return n[(int)t];
+}
+
+std::vector<int64_t> cstrides(const std::vector<int64_t>& s) {
+  std::vector<int64_t> st(s.size(), 1);
+  for (int i = (int)s.size() - 2; i >= 0; --i) st[i] = st[i + 1] * s[i + 1];
+  return st;
+}
+
+std::vector<int64_t> strip_units(const std::vector<int64_t>& s) {
+  std::vector<int64_t> o;
+  for (auto d : s) if (d != 1) o.push_back(d);
+  return o;
+}
+
+struct FusionError : std::exception {
+  std::string msg;
+  explicit FusionError(std::string m) : msg(std::move(m)) {}
+  const char* what() const noexcept override { return msg.c_str(); }
+};
+
+// ---------------------------------------------------------------------------------
+// affine index expressions over the kernel's loop variables
+struct Aff {
+  int64_t c = 0;
+  std::vector<int64_t> k;
+  bool opaque = false;
+  std::string expr;
+  bool is_const() const {
+    if (opaque) return false;
+    for (auto v : k) if (v) return false;
+    return true;
+  }
+};
+
+Aff aff_const(int nv, int64_t c) { Aff a; a.c = c; a.k.assign(nv, 0); return a; }
+Aff aff_var(int nv, int j) { Aff a; a.k.assign(nv, 0); a.k[j] = 1; return a; }
+
+// ---------------------------------------------------------------------------------
+struct Root {
+  int node;
+  bool is_reduce;
+};
+
+// One generated kernel.
+class KernelBuilder {
+ public:
+  enum Mode { EW, ROW };
+  KernelBuilder(Plan& plan, Mode mode, std::vector<int64_t> F, int k, std::vector<int> perm)
+      : plan_(plan), g_(plan.g), mode_(mode), F_(std::move(F)), k_(k), perm_(std::move(perm)) {
+    nv_ = (int)F_.size();
+    if (nv_ == 0) { F_.push_back(1); nv_ = 1; }
+    numel_ = shape_numel(F_);
+    C_ = 1;
+    for (int j = nv_ - k_; j < nv_; ++j) C_ *= F_[j];
+    R_ = C_ ? numel_ / std::max<int64_t>(C_, 1) : 0;
+  }
+
+  std::vector<int> stores;     // nodes written to their slot by this kernel
+  std::vector<int> reduces;    // reductions accumulated by this kernel (ROW)
+  std::set<int> produced;
+
+  KernelSpec build(const std::string& name);
+
+ private:
+  struct Val { std::string v; bool elem; };
+
+  Plan& plan_;
+  Graph& g_;
+  Mode mode_;
+  std::vector<int64_t> F_;
+  int k_;
+  std::vector<int> perm_;    // for a lone reduce over non-trailing axes: F dim j is input dim perm_[j]
+  int nv_ = 0;
+  int64_t numel_ = 0, R_ = 0, C_ = 1;
+  int V_ = 1, T_ = 32, block_ = 256, rpc_ = 1, chunks_ = 1;
+  bool cache_ = false, guard_ = false, big_ = false;
+
+  // code sinks
+  int phase_ = 0, nphases_ = 1;
+  std::vector<std::string> row_sec_, pre_sec_, lane_sec_, post_sec_;
+  std::string decls_;
+  std::map<std::string, std::string> row_memo_;
+  std::vector<std::map<std::string, std::string>> elem_memo_;
+  std::map<std::string, std::pair<std::string, int>> cached_loads_;
+  std::set<int> used_vars_;
+  bool used_flat_ = false;
+  std::vector<int> arg_slots_;
+  std::map<int, int> slot_param_;
+  std::map<int, std::string> red_var_;
+  std::map<int, int> level_memo_;
+  int tmp_ = 0;
+
+  std::string idx_t() const { return big_ ? "long long" : "int"; }
+  std::string newvar(const char* pfx = "t") { return std::string(pfx) + std::to_string(tmp_++); }
+  std::string param(int slot) {
+    auto it = slot_param_.find(slot);
+    if (it != slot_param_.end()) return "p" + std::to_string(it->second);
+    int i = (int)arg_slots_.size();
+    arg_slots_.push_back(slot);
+    slot_param_[slot] = i;
+    return "p" + std::to_string(i);
+  }
+  bool col_dep(const Aff& a) const {
+    if (a.opaque) return true;
+    for (int j = nv_ - (mode_ == ROW ? k_ : nv_); j < nv_; ++j) if (a.k[j]) return true;
+    return false;
+  }
+  bool any_col_dep(const std::vector<Aff>& idx) const {
+    for (auto& a : idx) if (col_dep(a)) return true;
+    return false;
+  }
+  std::string affkey(const Aff& a) const {
+    if (a.opaque) return "o(" + a.expr + ")";
+    std::string s = std::to_string(a.c);
+    for (auto v : a.k) s += "," + std::to_string(v);
+    return s;
+  }
+  std::string idxkey(const std::vector<Aff>& idx) const {
+    std::string s;
+    for (auto& a : idx) s += affkey(a) + ";";
+    return s;
+  }
+  // Text of an affine expression.  base=true substitutes the vector's first lane
+  // for the innermost variable.
+  std::string affstr(const Aff& a, bool base) {
+    if (a.opaque) return a.expr;
+    // shortcut: the address of a same-shape contiguous operand is the flat index
+    if (!a.is_const() && a.c == 0 && a.k == cstrides(F_) && nv_ > 1) {
+      used_flat_ = true;
+      return base ? "flat0" : "flat";
+    }
+    std::string s;
+    auto term = [&](const std::string& t) { s += (s.empty() ? "" : " + ") + t; };
+    for (int j = 0; j < nv_; ++j) {
+      if (!a.k[j] || F_[j] == 1) continue;
+      used_vars_.insert(j);
+      std::string v = (j == nv_ - 1 && base) ? "ib" : "i" + std::to_string(j);
+      term(a.k[j] == 1 ? v : "(" + idx_t() + ")" + std::to_string(a.k[j]) + " * " + v);
+    }
+    if (a.c || s.empty()) term("(" + idx_t() + ")" + std::to_string(a.c));
+    return "(" + s + ")";
+  }
+
+  void stmt(bool elem, const std::string& line) {
+    (elem ? lane_sec_[phase_] : row_sec_[phase_]) += "        " + line + "\n";
+  }
+
+  int level(int n);
+  Val value(int n, const std::vector<Aff>& idx);
+  Val load(int n, const std::vector<Aff>& idx);
+  Val emit_op(int n, const std::vector<Aff>& idx);
+  std::string cvt(const std::string& e, DType from, DType to);
+  std::string literal(double f, int64_t i, bool is_f, DType t);
+  std::vector<Aff> arg_index_binary(const Node& out, const Node& arg, const std::vector<Aff>& idx);
+  std::vector<Aff> full_index() {
+    std::vector<Aff> v;
+    for (int j = 0; j < nv_; ++j) v.push_back(F_[j] == 1 ? aff_const(nv_, 0) : aff_var(nv_, j));
+    return v;
+  }
+  // index of a node whose shape is the kernel's full shape or its row shape
+  std::vector<Aff> index_for_shape(const std::vector<int64_t>& shape, bool* full);
+  void emit_store(int n);
+  void configure();
+};
+
+// ---- helpers -----------------------------------------------------------------------
+
+std::string hexf(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  char b[48];
+  snprintf(b, sizeof b, "__uint_as_float(0x%08xu)", u);
+  return b;
+}
+std::string hexd(double d) {
+  uint64_t u;
+  memcpy(&u, &d, 8);
+  char b[64];
+  snprintf(b, sizeof b, "__longlong_as_double(0x%016llxLL)", (unsigned long long)u);
+  return b;
+}
+float to_bf16_rne(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if (f != f) return f;
+  u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000u;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+std::string KernelBuilder::literal(double f, int64_t i, bool is_f, DType t) {
+  if (dtype_is_float(t)) {
+    double v = is_f ? f : (double)i;
+    if (t == NXB_F64) return hexd(v);
+    float x = (float)v;
+    if (t == NXB_BF16) x = to_bf16_rne(x);
+    if (t == NXB_F16) return "round_f16(" + hexf(x) + ")";
+    return hexf(x);
+  }
+  long long v = is_f ? (long long)f : (long long)i;
+  return std::string("(") + reg_type(t) + ")" + std::to_string(v) + "LL";
+}
+
+std::string KernelBuilder::cvt(const std::string& e, DType from, DType to) {
+  if (from == to) return e;
+  if (dtype_is_float(to)) {
+    if (to == NXB_F64) return "(double)(" + e + ")";
+    std::string f = (from == NXB_F32 || from == NXB_BF16 || from == NXB_F16) ? e : "(float)(" + e + ")";
+    if (to == NXB_BF16) return "round_bf16(" + f + ")";
+    if (to == NXB_F16) return "round_f16(" + f + ")";
+    return f;
+  }
+  if (dtype_is_float(from)) return std::string("f2i<") + reg_type(to) + ">((double)(" + e + "))";
+  return std::string("(") + reg_type(to) + ")(" + e + ")";
+}
+
+std::vector<Aff> KernelBuilder::arg_index_binary(const Node& out, const Node& arg, const std::vector<Aff>& idx) {
+  // NumPy-style right alignment (nx/lib/nx/shape.ex binary_broadcast)
+  int ro = (int)out.shape.size(), ra = (int)arg.shape.size();
+  std::vector<Aff> r;
+  for (int j = 0; j < ra; ++j) {
+    int oj = j + ro - ra;
+    if (arg.shape[j] == 1 || oj < 0) r.push_back(aff_const(nv_, 0));
+    else r.push_back(idx[oj]);
+  }
+  return r;
+}
+
+std::vector<Aff> KernelBuilder::index_for_shape(const std::vector<int64_t>& shape, bool* full) {
+  // Match the non-unit dims of `shape` against the kernel's dims in order: either
+  // all of them (full) or the leading, non-reduced ones (row shaped).
+  std::vector<int> fdims, rdims;
+  for (int j = 0; j < nv_; ++j) if (F_[j] != 1) fdims.push_back(j);
+  for (int j = 0; j < nv_ - k_; ++j) if (F_[j] != 1) rdims.push_back(j);
+  std::vector<int64_t> su = strip_units(shape);
+  auto dims_of = [&](const std::vector<int>& d) { std::vector<int64_t> o; for (int j : d) o.push_back(F_[j]); return o; };
+  const std::vector<int>* use = nullptr;
+  if (su == dims_of(fdims)) { use = &fdims; *full = true; }
+  else if (mode_ == ROW && su == dims_of(rdims)) { use = &rdims; *full = false; }
+  else throw FusionError("shape " + shape_str(shape) + " does not fit kernel space " + shape_str(F_));
+  std::vector<Aff> idx;
+  size_t q = 0;
+  for (auto d : shape) {
+    if (d == 1) idx.push_back(aff_const(nv_, 0));
+    else idx.push_back(aff_var(nv_, (*use)[q++]));
+  }
+  return idx;
+}
+
+int KernelBuilder::level(int n) {
+  auto it = level_memo_.find(n);
+  if (it != level_memo_.end()) return it->second;
+  const Node& nd = g_.nodes[n];
+  int l = 0;
+  bool ext = nd.slot >= 0 && !produced.count(n) && !std::count(reduces.begin(), reduces.end(), n);
+  if (!ext) {
+    if (is_reduce(nd)) {
+      if (!std::count(reduces.begin(), reduces.end(), n)) throw FusionError("reduction outside the kernel is not materialised");
+      l = level(nd.args[0]) + 1;
+    } else {
+      for (int a : nd.args) l = std::max(l, level(a));
+    }
+  }
+  level_memo_[n] = l;
+  return l;
+}
+
+KernelBuilder::Val KernelBuilder::load(int n, const std::vector<Aff>& idx) {
+  const Node& nd = g_.nodes[n];
+  auto st = cstrides(nd.shape);
+  Aff addr = aff_const(nv_, 0);
+  for (size_t j = 0; j < idx.size(); ++j) {
+    if (nd.shape[j] == 1) continue;
+    if (idx[j].opaque || addr.opaque) {
+      std::string e = addr.opaque ? addr.expr : affstr(addr, false);
+      addr.opaque = true;
+      addr.expr = "(" + e + " + (" + idx_t() + ")" + std::to_string(st[j]) + " * " + affstr(idx[j], false) + ")";
+      continue;
+    }
+    addr.c += idx[j].c * st[j];
+    for (int v = 0; v < nv_; ++v) addr.k[v] += idx[j].k[v] * st[j];
+  }
+  const std::string S = storage_type(nd.dt), Rt = reg_type(nd.dt);
+  std::string p = param(nd.slot);
+  std::string key = "L" + std::to_string(nd.slot) + ":" + affkey(addr);
+  bool cdep = col_dep(addr);
+  if (mode_ == ROW && !cdep) {
+    auto it = row_memo_.find(key);
+    if (it != row_memo_.end()) return {it->second, false};
+    std::string v = newvar("lv");
+    stmt(false, "const " + Rt + " " + v + " = ld1<" + S + ">(" + p + " + " + affstr(addr, false) + ");");
+    row_memo_[key] = v;
+    return {v, false};
+  }
+  int64_t kv = addr.opaque ? -1 : addr.k[nv_ - 1];
+  bool aligned = !addr.opaque && addr.c % V_ == 0;
+  if (aligned)
+    for (int j = 0; j < nv_ - 1; ++j) if (F_[j] != 1 && addr.k[j] % V_ != 0) aligned = false;
+  if (V_ > 1 && kv == 1 && aligned) {
+    if (mode_ == ROW && cache_) {
+      auto it = cached_loads_.find(key);
+      if (it == cached_loads_.end()) {
+        std::string v = newvar("lv");
+        decls_ += "      " + Rt + " " + v + "[" + std::to_string(chunks_) + "][" + std::to_string(V_) + "];\n";
+        pre_sec_[phase_] += "          ld_vec<" + S + ", " + std::to_string(V_) + ">(" + p + " + " + affstr(addr, true) + ", " + v + "[ch]);\n";
+        it = cached_loads_.emplace(key, std::make_pair(v, phase_)).first;
+      }
+      return {it->second.first + "[ch][v]", true};
+    }
+    auto& memo = elem_memo_[phase_];
+    auto it = memo.find(key);
+    if (it != memo.end()) return {it->second, true};
+    std::string v = newvar("lv");
+    pre_sec_[phase_] += "          " + Rt + " " + v + "[" + std::to_string(V_) + "]; ld_vec<" + S + ", " + std::to_string(V_) + ">(" + p + " + " +
+                        affstr(addr, true) + ", " + v + ");\n";
+    memo[key] = v + "[v]";
+    return {v + "[v]", true};
+  }
+  auto& memo = elem_memo_[phase_];
+  auto it = memo.find(key);
+  if (it != memo.end()) return {it->second, true};
+  std::string v = newvar("lv");
+  if (V_ == 1 || kv != 0 || addr.opaque) {
+    stmt(true, "const " + Rt + " " + v + " = ld1<" + S + ">(" + p + " + " + affstr(addr, false) + ");");
+  } else {
+    // same address for every lane of the vector: load once per vector
+    pre_sec_[phase_] += "          const " + Rt + " " + v + " = ld1<" + S + ">(" + p + " + " + affstr(addr, true) + ");\n";
+  }
+  memo[key] = v;
+  return {v, true};
+}
+
+KernelBuilder::Val KernelBuilder::value(int n, const std::vector<Aff>& idx) {
+  const Node& nd = g_.nodes[n];
+  bool in_red = std::count(reduces.begin(), reduces.end(), n) > 0;
+  if (nd.slot >= 0 && !produced.count(n) && !in_red) return load(n, idx);
+  if (nd.op == "constant") {
+    bool isf = !nd.flts.empty();
+    return {literal(isf ? nd.flts[0] : 0.0, isf ? 0 : nd.ints[0], isf, nd.dt), false};
+  }
+  std::string key = std::to_string(n) + ":" + idxkey(idx);
+  auto rit = row_memo_.find(key);
+  if (rit != row_memo_.end()) return {rit->second, false};
+  auto eit = elem_memo_[phase_].find(key);
+  if (eit != elem_memo_[phase_].end()) return {eit->second, true};
+  Val v = emit_op(n, idx);
+  if (v.elem) elem_memo_[phase_][key] = v.v;
+  else row_memo_[key] = v.v;
+  return v;
+}
+
+KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
+  const Node& nd = g_.nodes[n];
+  const std::string& op = nd.op;
+  const DType t = nd.dt;
+  auto def = [&](bool elem, DType dt, const std::string& e) -> Val {
+    std::string v = newvar();
+    stmt(elem, std::string("const ") + reg_type(dt) + " " + v + " = " + e + ";");
+    return {v, elem};
+  };
+
+  if (is_reduce(nd)) {
+    // result of a reduction accumulated by this kernel: must be asked for at the current row
+    auto it = red_var_.find(n);
+    if (it == red_var_.end()) throw FusionError("reduction result used before it is complete");
+    const Node& in = g_.nodes[nd.args[0]];
+    // build the expected index: non-reduced dims in order -> row variables, kept dims -> 0
+    std::vector<Aff> want;
+    std::vector<int64_t> inshape = in.shape;
+    if (inshape.empty()) inshape.push_back(1);
+    bool full;
+    std::vector<Aff> w = index_for_shape(nd.shape, &full);
+    if (full && k_ > 0 && C_ != 1) throw FusionError("reduction result has the full shape");
+    for (size_t j = 0; j < idx.size(); ++j)
+      if (affkey(idx[j]) != affkey(w[j])) throw FusionError("reduction result indexed off the current row");
+    return {it->second, false};
+  }
+  if (op == "metadata" || op == "copy") return value(nd.args[0], idx);
+  if (op == "iota") {
+    int ax = (int)nd.ints[0];
+    Aff a;
+    if (ax >= 0) a = idx[ax];
+    else {
+      a = aff_const(nv_, 0);
+      auto st = cstrides(nd.shape);
+      for (size_t j = 0; j < idx.size(); ++j) {
+        if (idx[j].opaque) throw FusionError("iota over an opaque index");
+        a.c += idx[j].c * st[j];
+        for (int v = 0; v < nv_; ++v) a.k[v] += idx[j].k[v] * st[j];
+      }
+    }
+    bool e = col_dep(a);
+    if (a.is_const()) return {literal(0, a.c, false, t), false};
+    return def(e, t, cvt("(long long)" + affstr(a, false), NXB_S64, t));
+  }
+  if (op == "broadcast") {
+    const Node& a = g_.nodes[nd.args[0]];
+    int na = (int)nd.ints[0];
+    std::vector<Aff> ai;
+    for (int j = 0; j < na; ++j) ai.push_back(a.shape[j] == 1 ? aff_const(nv_, 0) : idx[nd.ints[1 + j]]);
+    return value(nd.args[0], ai);
+  }
+  if (op == "squeeze") {
+    const Node& a = g_.nodes[nd.args[0]];
+    std::set<int64_t> ax(nd.ints.begin() + 1, nd.ints.end());
+    std::vector<Aff> ai;
+    size_t q = 0;
+    for (size_t j = 0; j < a.shape.size(); ++j) ai.push_back(ax.count((int64_t)j) ? aff_const(nv_, 0) : idx[q++]);
+    return value(nd.args[0], ai);
+  }
+  if (op == "transpose") {
+    std::vector<Aff> ai(idx.size(), aff_const(nv_, 0));
+    for (size_t j = 0; j < idx.size(); ++j) ai[nd.ints[j]] = idx[j];
+    return value(nd.args[0], ai);
+  }
+  if (op == "slice") {
+    size_t r = idx.size();
+    std::vector<Aff> ai;
+    for (size_t j = 0; j < r; ++j) {
+      Aff a = idx[j];
+      int64_t st = nd.ints[j], sd = nd.ints[2 * r + j];
+      if (a.opaque) a.expr = "((" + idx_t() + ")" + std::to_string(st) + " + (" + idx_t() + ")" + std::to_string(sd) + " * " + a.expr + ")";
+      else { a.c = a.c * sd + st; for (auto& kk : a.k) kk *= sd; }
+      ai.push_back(a);
+    }
+    return value(nd.args[0], ai);
+  }
+  if (op == "reshape") {
+    const Node& a = g_.nodes[nd.args[0]];
+    std::vector<Aff> ai;
+    if (strip_units(a.shape) == strip_units(nd.shape)) {
+      // only unit dims were added or removed
+      std::vector<Aff> nonunit;
+      for (size_t j = 0; j < idx.size(); ++j) if (nd.shape[j] != 1) nonunit.push_back(idx[j]);
+      size_t q = 0;
+      for (auto d : a.shape) ai.push_back(d == 1 ? aff_const(nv_, 0) : nonunit[q++]);
+    } else {
+      // general case: linear offset in the new shape, then div/mod into the old one
+      auto st = cstrides(nd.shape);
+      Aff lin = aff_const(nv_, 0);
+      bool opq = false;
+      std::string e;
+      for (size_t j = 0; j < idx.size(); ++j) {
+        if (idx[j].opaque) opq = true;
+      }
+      if (!opq) {
+        for (size_t j = 0; j < idx.size(); ++j) {
+          lin.c += idx[j].c * st[j];
+          for (int v = 0; v < nv_; ++v) lin.k[v] += idx[j].k[v] * st[j];
+        }
+        e = affstr(lin, false);
+      } else {
+        for (size_t j = 0; j < idx.size(); ++j)
+          e += (j ? " + " : "") + std::string("(") + idx_t() + ")" + std::to_string(st[j]) + " * " + affstr(idx[j], false);
+        e = "(" + e + ")";
+      }
+      auto ast = cstrides(a.shape);
+      for (size_t j = 0; j < a.shape.size(); ++j) {
+        Aff o;
+        o.opaque = true;
+        o.k.assign(nv_, 0);
+        o.expr = "((" + e + " / (" + idx_t() + ")" + std::to_string(ast[j]) + ") % (" + idx_t() + ")" + std::to_string(a.shape[j]) + ")";
+        ai.push_back(a.shape[j] == 1 ? aff_const(nv_, 0) : o);
+      }
+    }
+    return value(nd.args[0], ai);
+  }
+
+  // ---- elementwise ------------------------------------------------------------------
+  if (op == "as_type") {
+    const Node& a = g_.nodes[nd.args[0]];
+    Val x = value(nd.args[0], idx);
+    if (a.dt == t) return x;
+    return def(x.elem, t, cvt(x.v, a.dt, t));
+  }
+  if (kUnaryMath.count(op) || kUnaryOther.count(op)) {
+    const Node& a = g_.nodes[nd.args[0]];
+    Val x = value(nd.args[0], idx);
+    const bool dbl = t == NXB_F64;
+    auto fn = [&](const char* base) { return std::string(base) + (dbl ? "" : "f"); };
+    std::string e;
+    if (op == "is_nan") {
+      e = dtype_is_float(a.dt) ? "(uint8_t)(" + x.v + " != " + x.v + ")" : "(uint8_t)0";
+      return def(x.elem, t, e);
+    }
+    if (op == "is_infinity") {
+      e = dtype_is_float(a.dt) ? "(uint8_t)(" + std::string(a.dt == NXB_F64 ? "fabs" : "fabsf") + "(" + x.v + ") == NXB_INF)" : "(uint8_t)0";
+      return def(x.elem, t, e);
+    }
+    if (op == "population_count" || op == "count_leading_zeros") {
+      e = std::string(op == "population_count" ? "nx_popc<" : "nx_clz<") + reg_type(a.dt) + ">(" + x.v + ")";
+      return def(x.elem, t, cvt(e, a.dt, t));
+    }
+    std::string xv = cvt(x.v, a.dt, t);     // the argument is converted to the output type first
+    if (dtype_is_float(t)) {
+      static const std::map<std::string, const char*> lib = {
+          {"expm1", "expm1"}, {"log1p", "log1p"}, {"cos", "cos"}, {"sin", "sin"}, {"tan", "tan"}, {"cosh", "cosh"},
+          {"sinh", "sinh"}, {"acos", "acos"}, {"asin", "asin"}, {"atan", "atan"}, {"acosh", "acosh"},
+          {"asinh", "asinh"}, {"atanh", "atanh"}, {"sqrt", "sqrt"}, {"cbrt", "cbrt"}, {"erf", "erf"},
+          {"erfc", "erfc"}, {"abs", "fabs"}, {"floor", "floor"}, {"ceil", "ceil"}};
+      static const std::map<std::string, const char*> own = {
+          {"exp", "nx_exp"}, {"log", "nx_log"}, {"sigmoid", "nx_sigmoid"}, {"tanh", "nx_tanh"},
+          {"rsqrt", "nx_rsqrt"}, {"erf_inv", "nx_erf_inv"}, {"round", "nx_round"}, {"sign", "nx_sign"}};
+      if (lib.count(op)) e = fn(lib.at(op)) + "(" + xv + ")";
+      else if (own.count(op)) e = std::string(own.at(op)) + "(" + xv + ")";
+      else if (op == "negate") e = "-" + xv;
+      else fail(NXB_ERR_INVALID_ARGUMENT, "op " + op + " is not defined for " + dtype_name(t));
+      if (t == NXB_BF16) e = "round_bf16(" + e + ")";
+      if (t == NXB_F16) e = "round_f16(" + e + ")";
+    } else {
+      const std::string RT = reg_type(t), UT = unsigned_of(t);
+      if (op == "negate") e = "(" + RT + ")((" + UT + ")0 - (" + UT + ")" + xv + ")";
+      else if (op == "abs") e = dtype_is_signed(t) ? "(" + RT + ")(" + xv + " < 0 ? (" + UT + ")0 - (" + UT + ")" + xv + " : (" + UT + ")" + xv + ")" : xv;
+      else if (op == "sign") e = dtype_is_signed(t) ? "nx_sign_i<" + RT + ">(" + xv + ")" : "(" + RT + ")(" + xv + " != 0)";
+      else if (op == "bitwise_not") e = "(" + RT + ")~" + xv;
+      else if (op == "floor" || op == "ceil" || op == "round") e = xv;
+      else fail(NXB_ERR_INVALID_ARGUMENT, "op " + op + " is not defined for " + dtype_name(t));
+    }
+    return def(x.elem, t, e);
+  }
+  if (kBinary.count(op)) {
+    const Node& a = g_.nodes[nd.args[0]];
+    const Node& b = g_.nodes[nd.args[1]];
+    Val x = value(nd.args[0], arg_index_binary(nd, a, idx));
+    Val y = value(nd.args[1], arg_index_binary(nd, b, idx));
+    bool elem = x.elem || y.elem;
+    if (kLogical.count(op)) {
+      std::string xa = "(" + x.v + " != 0)", yb = "(" + y.v + " != 0)";
+      std::string o = op == "logical_and" ? " && " : op == "logical_or" ? " || " : " != ";
+      return def(elem, t, "(uint8_t)(" + xa + o + yb + ")");
+    }
+    // operands are converted to the merged type first, the result to the node's type after
+    // (exla/lib/exla/defn.ex:2380-2410)
+    DType ct = dtype_merge(a.dt, b.dt);
+    if (!kCompare.count(op)) ct = dtype_merge(ct, t);
+    std::string xv = cvt(x.v, a.dt, ct), yv = cvt(y.v, b.dt, ct);
+    std::string e;
+    if (kCompare.count(op)) {
+      static const std::map<std::string, const char*> sym = {{"equal", "=="}, {"not_equal", "!="}, {"greater", ">"},
+                                                            {"less", "<"}, {"greater_equal", ">="}, {"less_equal", "<="}};
+      return def(elem, t, "(uint8_t)(" + xv + " " + sym.at(op) + " " + yv + ")");
+    }
+    const bool dbl = ct == NXB_F64;
+    if (dtype_is_float(ct)) {
+      if (op == "add") e = xv + " + " + yv;
+      else if (op == "subtract") e = xv + " - " + yv;
+      else if (op == "multiply") e = xv + " * " + yv;
+      else if (op == "divide") e = xv + " / " + yv;
+      else if (op == "max") e = "nx_max(" + xv + ", " + yv + ")";
+      else if (op == "min") e = "nx_min(" + xv + ", " + yv + ")";
+      else if (op == "pow") e = std::string(dbl ? "pow" : "powf") + "(" + xv + ", " + yv + ")";
+      else if (op == "remainder") e = std::string(dbl ? "fmod" : "fmodf") + "(" + xv + ", " + yv + ")";
+      else if (op == "atan2") e = std::string(dbl ? "atan2" : "atan2f") + "(" + xv + ", " + yv + ")";
+      else fail(NXB_ERR_INVALID_ARGUMENT, "op " + op + " is not defined for " + dtype_name(ct));
+      if (ct == NXB_BF16) e = "round_bf16(" + e + ")";
+      if (ct == NXB_F16) e = "round_f16(" + e + ")";
+    } else {
+      const std::string RT = reg_type(ct), UT = unsigned_of(ct);
+      auto wrap = [&](const char* o) { return "(" + RT + ")((" + UT + ")" + xv + " " + o + " (" + UT + ")" + yv + ")"; };
+      if (op == "add") e = wrap("+");
+      else if (op == "subtract") e = wrap("-");
+      else if (op == "multiply") e = wrap("*");
+      else if (op == "bitwise_and") e = wrap("&");
+      else if (op == "bitwise_or") e = wrap("|");
+      else if (op == "bitwise_xor") e = wrap("^");
+      else if (op == "max") e = "nx_max(" + xv + ", " + yv + ")";
+      else if (op == "min") e = "nx_min(" + xv + ", " + yv + ")";
+      else if (op == "quotient" || op == "divide") e = "nx_idiv<" + RT + ">(" + xv + ", " + yv + ")";
+      else if (op == "remainder") e = "nx_irem<" + RT + ">(" + xv + ", " + yv + ")";
+      else if (op == "pow") e = "nx_ipow<" + RT + ">(" + xv + ", " + yv + ")";
+      else if (op == "left_shift") e = "nx_shl<" + RT + ">(" + xv + ", " + yv + ")";
+      else if (op == "right_shift") e = "nx_shr<" + RT + ">(" + xv + ", " + yv + ")";
+      else fail(NXB_ERR_INVALID_ARGUMENT, "op " + op + " is not defined for " + dtype_name(ct));
+    }
+    return def(elem, t, cvt(e, ct, t));
+  }
+  if (op == "select") {
+    const Node& p = g_.nodes[nd.args[0]];
+    const Node& a = g_.nodes[nd.args[1]];
+    const Node& b = g_.nodes[nd.args[2]];
+    Val pv = value(nd.args[0], arg_index_binary(nd, p, idx));
+    Val x = value(nd.args[1], arg_index_binary(nd, a, idx));
+    Val y = value(nd.args[2], arg_index_binary(nd, b, idx));
+    return def(pv.elem || x.elem || y.elem, t, "(" + pv.v + " != 0) ? " + cvt(x.v, a.dt, t) + " : " + cvt(y.v, b.dt, t));
+  }
+  if (op == "clip") {
+    Val x = value(nd.args[0], idx);
+    Val lo = value(nd.args[1], {});
+    Val hi = value(nd.args[2], {});
+    std::string e = "nx_min(nx_max(" + cvt(x.v, g_.nodes[nd.args[0]].dt, t) + ", " + cvt(lo.v, g_.nodes[nd.args[1]].dt, t) + "), " +
+                    cvt(hi.v, g_.nodes[nd.args[2]].dt, t) + ")";
+    return def(x.elem || lo.elem || hi.elem, t, e);
+  }
+  throw FusionError("op " + op + " cannot be generated inline");
+}
+
+void KernelBuilder::emit_store(int n) {
+  const Node& nd = g_.nodes[n];
+  bool full;
+  std::vector<Aff> idx = index_for_shape(nd.shape, &full);
+  Val v = value(n, idx);
+  std::string p = param(nd.slot);
+  const std::string S = storage_type(nd.dt), Rt = reg_type(nd.dt);
+  auto st = cstrides(nd.shape);
+  Aff addr = aff_const(nv_, 0);
+  for (size_t j = 0; j < idx.size(); ++j) {
+    addr.c += idx[j].c * st[j];
+    for (int q = 0; q < nv_; ++q) addr.k[q] += idx[j].k[q] * st[j];
+  }
+  if (mode_ == ROW && !full) {
+    // one value per row: lane 0 of the row writes it
+    row_sec_[phase_] += "        if (tid == 0) st1<" + S + ">(" + p + " + " + affstr(addr, false) + ", " + v.v + ");\n";
+    return;
+  }
+  if (V_ > 1) {
+    std::string sv = newvar("st");
+    pre_sec_[phase_] += "          " + Rt + " " + sv + "[" + std::to_string(V_) + "];\n";
+    lane_sec_[phase_] += "        " + sv + "[v] = " + v.v + ";\n";
+    post_sec_[phase_] += "          st_vec<" + S + ", " + std::to_string(V_) + ">(" + p + " + " + affstr(addr, true) + ", " + sv + ");\n";
+  } else {
+    lane_sec_[phase_] += "        st1<" + S + ">(" + p + " + " + affstr(addr, false) + ", " + v.v + ");\n";
+  }
+}
+
+void KernelBuilder::configure() {
+  // vector width: 16 bytes of the narrowest element touched, limited by divisibility
+  size_t minsz = 8;
+  for (int n : stores) minsz = std::min(minsz, dtype_size(g_.nodes[n].dt));
+  for (int n : reduces) minsz = std::min(minsz, dtype_size(g_.nodes[g_.nodes[n].args[0]].dt));
+  std::function<void(int, std::set<int>&)> scan = [&](int n, std::set<int>& seen) {
+    if (!seen.insert(n).second) return;
+    const Node& nd = g_.nodes[n];
+    if (nd.slot >= 0 && !produced.count(n) && !std::count(reduces.begin(), reduces.end(), n)) {
+      if (strip_units(nd.shape) == strip_units(F_)) minsz = std::min(minsz, dtype_size(nd.dt));
+      return;
+    }
+    for (int a : nd.args) scan(a, seen);
+  };
+  std::set<int> seen;
+  for (int n : stores) scan(n, seen);
+  for (int n : reduces) scan(n, seen);
+  V_ = (int)std::min<size_t>(8, 16 / minsz);
+  if (!perm_.empty()) V_ = 1;
+  while (V_ > 1 && F_[nv_ - 1] % V_ != 0) V_ /= 2;
+  big_ = numel_ >= (int64_t(1) << 31) - 4096;
+  for (int n : seen)
+    if (shape_numel(g_.nodes[n].shape) >= (int64_t(1) << 31) - 4096) big_ = true;
+  if (mode_ == ROW) {
+    int64_t per = std::max<int64_t>(1, C_ / V_);
+    int64_t want = (per + 3) / 4;        // aim for <= 4 vectors per thread
+    T_ = 32;
+    while (T_ < want && T_ < 1024) T_ *= 2;
+    chunks_ = (int)((per + T_ - 1) / T_);
+    guard_ = (per % T_) != 0;
+    if (T_ >= 64) { block_ = T_; rpc_ = 1; } else { block_ = 128; rpc_ = 4; }
+    cache_ = chunks_ * V_ <= 32 && chunks_ <= 16;
+  } else {
+    block_ = 256;
+  }
+}
+
+KernelSpec KernelBuilder::build(const std::string& name) {
+  for (int n : stores) produced.insert(n);
+  configure();
+
+  // phases
+  std::map<int, int> red_phase;
+  nphases_ = 1;
+  if (mode_ == ROW) {
+    for (int r : reduces) {
+      red_phase[r] = level(g_.nodes[r].args[0]);
+      nphases_ = std::max(nphases_, red_phase[r] + 1);
+    }
+    for (int s : stores) nphases_ = std::max(nphases_, level(s) + 1);
+  }
+  row_sec_.assign(nphases_ + 1, "");
+  pre_sec_.assign(nphases_ + 1, "");
+  lane_sec_.assign(nphases_ + 1, "");
+  post_sec_.assign(nphases_ + 1, "");
+  elem_memo_.assign(nphases_ + 1, {});
+  std::vector<std::string> red_init(nphases_ + 1), red_fin(nphases_ + 1);
+
+  std::vector<int> row_stores;
+  for (phase_ = 0; phase_ < nphases_; ++phase_) {
+    for (int r : reduces) {
+      if (red_phase[r] != phase_) continue;
+      const Node& nd = g_.nodes[r];
+      const Node& in = g_.nodes[nd.args[0]];
+      // index of the input element in terms of the kernel's variables
+      std::vector<Aff> idx(in.shape.size(), aff_const(nv_, 0));
+      if (!perm_.empty()) {
+        for (int j = 0; j < nv_; ++j) if (F_[j] != 1) idx[perm_[j]] = aff_var(nv_, j);
+      } else if (in.shape.empty()) {
+        idx.clear();
+      } else {
+        bool full;
+        idx = index_for_shape(in.shape, &full);
+        if (!full && C_ != 1) throw FusionError("reduction input does not span the kernel space");
+      }
+      Val x = value(nd.args[0], idx);
+      std::string acc = newvar("acc"), res = newvar("red");
+      const std::string T = std::to_string(T_);
+      if (kArgReduce.count(nd.op)) {
+        const std::string RT = reg_type(in.dt);
+        bool is_max = nd.op == "argmax", high = nd.ints[0] != 0;
+        std::string tpl = std::string(is_max ? "true" : "false") + ", " + (high ? "true" : "false");
+        red_init[phase_] += "      ArgPair<" + RT + "> " + acc + "; " + acc + ".v = (" + RT + ")0; " + acc + ".i = -1;\n";
+        lane_sec_[phase_] += "        { ArgPair<" + RT + "> c_; c_.v = " + x.v + "; c_.i = (long long)(col0 + v); " + acc + " = arg_combine<" + tpl + ">(" + acc + ", c_); }\n";
+        red_fin[phase_] += "      const " + std::string(reg_type(nd.dt)) + " " + res + " = (" + reg_type(nd.dt) + ")row_arg_reduce<" + tpl + ", " + RT + ", " + T + ">(" + acc +
+                           ", scratch).i;\n";
+      } else {
+        DType ot = nd.dt;
+        const std::string RT = reg_type(ot);
+        std::string init, opn, xv = cvt(x.v, in.dt, ot);
+        if (nd.op == "sum") { init = "(" + RT + ")0"; opn = "OpSum"; }
+        else if (nd.op == "product") { init = "(" + RT + ")1"; opn = "OpProd"; }
+        else if (nd.op == "reduce_max") {
+          opn = "OpMax";
+          init = dtype_is_float(ot) ? (ot == NXB_F64 ? "-(double)NXB_INF" : "-NXB_INF")
+                                    : literal(0, dtype_is_signed(ot) ? -(int64_t)((uint64_t)1 << (dtype_size(ot) * 8 - 1)) : 0, false, ot);
+        } else if (nd.op == "reduce_min") {
+          opn = "OpMin";
+          int bits = (int)dtype_size(ot) * 8;
+          int64_t mx = dtype_is_signed(ot) ? (int64_t)(((uint64_t)1 << (bits - 1)) - 1) : (bits == 64 ? -1 : (int64_t)(((uint64_t)1 << bits) - 1));
+          init = dtype_is_float(ot) ? (ot == NXB_F64 ? "(double)NXB_INF" : "NXB_INF") : literal(0, mx, false, ot);
+        } else if (nd.op == "all") { init = "(uint8_t)1"; opn = "OpAnd"; xv = "(uint8_t)(" + x.v + " != 0)"; }
+        else { init = "(uint8_t)0"; opn = "OpOr"; xv = "(uint8_t)(" + x.v + " != 0)"; }
+        // narrow integer accumulators are widened to 32 bits for the shuffle
+        red_init[phase_] += "      " + RT + " " + acc + " = " + init + ";\n";
+        lane_sec_[phase_] += "        " + acc + " = " + opn + "::apply(" + acc + ", " + xv + ");\n";
+        std::string fin = "row_reduce<" + opn + ", " + RT + ", " + T + ">(" + acc + ", scratch)";
+        if (ot == NXB_BF16) fin = "round_bf16(" + fin + ")";
+        if (ot == NXB_F16) fin = "round_f16(" + fin + ")";
+        red_fin[phase_] += "      const " + RT + " " + res + " = " + fin + ";\n";
+      }
+      red_var_[r] = res;
+    }
+    for (int s : stores) {
+      if (mode_ == ROW) {
+        bool full;
+        index_for_shape(g_.nodes[s].shape, &full);
+        if (!full) { if (phase_ == 0) row_stores.push_back(s); continue; }
+        if (level(s) != phase_) continue;
+      }
+      emit_store(s);
+    }
+  }
+  // results of reductions that are themselves kernel outputs, and other per-row values
+  phase_ = nphases_;
+  for (int r : reduces) {
+    const Node& nd = g_.nodes[r];
+    if (nd.slot < 0) continue;
+    // address of the result: its own shape indexed by the row variables
+    bool full;
+    std::vector<Aff> idx = index_for_shape(nd.shape, &full);
+    auto st = cstrides(nd.shape);
+    Aff addr = aff_const(nv_, 0);
+    for (size_t j = 0; j < idx.size(); ++j) {
+      addr.c += idx[j].c * st[j];
+      for (int q = 0; q < nv_; ++q) addr.k[q] += idx[j].k[q] * st[j];
+    }
+    row_sec_[phase_] += "        if (tid == 0) st1<" + std::string(storage_type(nd.dt)) + ">(" + param(nd.slot) + " + " + affstr(addr, false) + ", " + red_var_[r] + ");\n";
+  }
+  for (int s : row_stores) emit_store(s);
+
+  // ---- assemble the source ------------------------------------------------------------------
+  std::ostringstream o;
+  const std::string I = idx_t();
+  std::vector<const Node*> argn;
+  o << "extern \"C\" __global__ void __launch_bounds__(" << block_ << ") " << name << "(";
+  for (size_t i = 0; i < arg_slots_.size(); ++i) {
+    const Slot& sl = plan_.slots[arg_slots_[i]];
+    bool written = false;
+    for (int s : stores) if (g_.nodes[s].slot == arg_slots_[i]) written = true;
+    for (int r : reduces) if (g_.nodes[r].slot == arg_slots_[i]) written = true;
+    o << (i ? ", " : "") << (written ? "" : "const ") << storage_type(sl.dt) << "* __restrict__ p" << i;
+  }
+  o << ") {\n";
+  auto decomp = [&](int lo, int hi, const std::string& src, bool with_base) {
+    // define index variables i<lo>..i<hi-1> from the linear index `src`
+    std::string rem = src;
+    for (int j = hi - 1; j >= lo; --j) {
+      if (F_[j] == 1) continue;
+      bool last_nonunit = true;
+      for (int q = lo; q < j; ++q) if (F_[q] != 1) last_nonunit = false;
+      std::string nm = (with_base && j == nv_ - 1) ? "ib" : "i" + std::to_string(j);
+      if (used_vars_.count(j)) {
+        o << "        const " << I << " " << nm << " = " << (last_nonunit ? rem : "(" + rem + ") % (" + I + ")" + std::to_string(F_[j])) << ";\n";
+      }
+      if (!last_nonunit) rem = "(" + rem + ") / (" + I + ")" + std::to_string(F_[j]);
+    }
+  };
+  if (mode_ == EW) {
+    int64_t nvec = numel_ / V_;
+    o << "  const " << I << " nvec = (" << I << ")" << nvec << "LL;\n";
+    o << "  for (" << I << " g = (" << I << ")blockIdx.x * " << block_ << " + threadIdx.x; g < nvec; g += (" << I << ")gridDim.x * " << block_ << ") {\n";
+    o << "        const " << I << " flat0 = g * " << V_ << ";\n";
+    decomp(0, nv_, "flat0", true);
+    o << pre_sec_[0];
+    o << "#pragma unroll\n      for (int v = 0; v < " << V_ << "; ++v) {\n";
+    if (used_vars_.count(nv_ - 1)) o << "        const " << I << " i" << nv_ - 1 << " = ib + v;\n";
+    if (used_flat_) o << "        const " << I << " flat = flat0 + v;\n";
+    o << lane_sec_[0] << "      }\n" << post_sec_[0] << "  }\n}\n";
+  } else {
+    o << "  __shared__ long long scratch_all[" << 64 << "];\n";
+    o << "  void* scratch = scratch_all;\n";
+    if (rpc_ > 1) o << "  const int tid = threadIdx.x & 31;\n  const " << I << " row_in_cta = threadIdx.x >> 5;\n";
+    else o << "  const int tid = threadIdx.x;\n  const " << I << " row_in_cta = 0;\n";
+    o << "  for (" << I << " row = (" << I << ")blockIdx.x * " << rpc_ << " + row_in_cta; row < (" << I << ")" << R_ << "LL; row += (" << I << ")gridDim.x * " << rpc_ << ") {\n";
+    o << "        const " << I << " rowbase = row * (" << I << ")" << C_ << "LL;\n";
+    decomp(0, nv_ - k_, "row", false);
+    o << decls_;
+    for (int p = 0; p < nphases_; ++p) {
+      o << row_sec_[p] << red_init[p];
+      bool has_loop = !pre_sec_[p].empty() || !lane_sec_[p].empty() || !post_sec_[p].empty();
+      if (has_loop) {
+        o << (cache_ || chunks_ <= 16 ? "#pragma unroll\n" : "#pragma unroll 2\n");
+        o << "      for (int ch = 0; ch < " << chunks_ << "; ++ch) {\n";
+        o << "        const " << I << " col0 = ((" << I << ")ch * " << T_ << " + tid) * " << V_ << ";\n";
+        if (guard_) o << "        if (col0 < (" << I << ")" << C_ << "LL) {\n";
+        o << "        const " << I << " flat0 = rowbase + col0;\n";
+        // column variables
+        {
+          std::string rem = "col0";
+          for (int j = nv_ - 1; j >= nv_ - k_; --j) {
+            if (F_[j] == 1) continue;
+            bool last_nonunit = true;
+            for (int q = nv_ - k_; q < j; ++q) if (F_[q] != 1) last_nonunit = false;
+            std::string nm = (j == nv_ - 1) ? "ib" : "i" + std::to_string(j);
+            if (used_vars_.count(j))
+              o << "        const " << I << " " << nm << " = " << (last_nonunit ? rem : "(" + rem + ") % (" + I + ")" + std::to_string(F_[j])) << ";\n";
+            if (!last_nonunit) rem = "(" + rem + ") / (" + I + ")" + std::to_string(F_[j]);
+          }
+        }
+        o << pre_sec_[p];
+        o << "#pragma unroll\n        for (int v = 0; v < " << V_ << "; ++v) {\n";
+        if (used_vars_.count(nv_ - 1)) o << "        const " << I << " i" << nv_ - 1 << " = ib + v;\n";
+        if (used_flat_) o << "        const " << I << " flat = flat0 + v;\n";
+        o << lane_sec_[p] << "        }\n" << post_sec_[p];
+        if (guard_) o << "        }\n";
+        o << "      }\n";
+      }
+      o << red_fin[p];
+    }
+    o << row_sec_[nphases_];
+    o << "  }\n}\n";
+  }
+
+  KernelSpec ks;
+  ks.name = name;
+  ks.source = o.str();
+  ks.block = (unsigned)block_;
+  ks.arg_slots = arg_slots_;
+  ks.arg_offsets.assign(arg_slots_.size(), 0);
+  int64_t nblocks;
+  if (mode_ == EW) nblocks = (numel_ / V_ + block_ - 1) / block_;
+  else nblocks = (R_ + rpc_ - 1) / rpc_;
+  ks.grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(nblocks, 0x7fffffff));
+  std::ostringstream d;
+  d << name << (mode_ == EW ? " elementwise" : " row") << " space=" << shape_str(F_);
+  if (mode_ == ROW) d << " rows=" << R_ << " cols=" << C_ << " threads/row=" << T_ << " phases=" << nphases_ << (cache_ ? " row-in-registers" : " streaming");
+  d << " vec=" << V_ << " grid=" << ks.grid << " block=" << ks.block << " stores=[";
+  for (size_t i = 0; i < stores.size(); ++i) d << (i ? "," : "") << g_.nodes[stores[i]].op << "#" << stores[i];
+  d << "] reduces=[";
+  for (size_t i = 0; i < reduces.size(); ++i) d << (i ? "," : "") << g_.nodes[reduces[i]].op << "#" << reduces[i];
+  d << "]";
+  ks.desc = d.str();
+  return ks;
+}
+
+}  // namespace
+
+// =====================================================================================
+// planner
+// =====================================================================================
+
+namespace {
+
+struct Unit {           // one launch-to-be
+  enum Kind { ROW, EW, GEMM } kind = EW;
+  std::vector<int64_t> F;
+  int k = 0;
+  std::vector<int> perm;
+  std::vector<int> reduces, stores;
+  int gemm_node = -1;
+  std::set<int> reads, writes;   // slots
+};
+
+struct Planner {
+  Plan& plan;
+  Graph& g;
+  std::vector<char> mat;            // value must live in a slot
+  explicit Planner(Plan& p) : plan(p), g(p.g) {}
+
+  int new_slot(Slot::Kind kind, int node, int index) {
+    Slot s;
+    s.kind = kind;
+    s.node = node;
+    s.index = index;
+    s.dt = g.nodes[node].dt;
+    s.shape = g.nodes[node].shape;
+    s.nbytes = (size_t)shape_numel(s.shape) * dtype_size(s.dt);
+    plan.slots.push_back(s);
+    return (int)plan.slots.size() - 1;
+  }
+
+  // reductions whose axes are the trailing ones: signature = (input shape, k)
+  bool trailing_reduce(const Node& nd, std::vector<int64_t>* F, int* k, std::vector<int>* perm) {
+    const Node& in = g.nodes[nd.args[0]];
+    int r = (int)in.shape.size();
+    std::vector<int> axes;
+    if (kArgReduce.count(nd.op)) {
+      if (nd.ints[1] < 0) for (int j = 0; j < r; ++j) axes.push_back(j);
+      else axes.push_back((int)nd.ints[1]);
+    } else {
+      for (int j = 0; j < nd.ints[1]; ++j) axes.push_back((int)nd.ints[2 + j]);
+    }
+    std::sort(axes.begin(), axes.end());
+    bool trailing = true;
+    for (size_t j = 0; j < axes.size(); ++j) if (axes[j] != r - (int)axes.size() + (int)j) trailing = false;
+    *k = (int)axes.size();
+    perm->clear();
+    if (trailing) { *F = in.shape; return true; }
+    // move the reduced axes last
+    F->clear();
+    for (int j = 0; j < r; ++j) if (!std::count(axes.begin(), axes.end(), j)) { F->push_back(in.shape[j]); perm->push_back(j); }
+    for (int a : axes) { F->push_back(in.shape[a]); perm->push_back(a); }
+    return false;
+  }
+
+  bool is_leaf(int n) const {
+    const std::string& op = g.nodes[n].op;
+    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate";
+  }
+
+  // Nodes reachable backwards through everything a kernel can generate inline
+  // (elementwise, views, reductions); `leaves` collects the buffers it ends at.
+  void cone(int n, std::set<int>& seen, std::set<int>& leaves, std::set<int>& reds, bool root) {
+    if (is_leaf(n)) { leaves.insert(n); return; }
+    if (!seen.insert(n).second) return;
+    const Node& nd = g.nodes[n];
+    if (is_reduce(nd) && !root) reds.insert(n);
+    for (int a : nd.args) cone(a, seen, leaves, reds, false);
+  }
+};
+
+}  // namespace
+
+std::string Plan::describe() const {
+  std::ostringstream o;
+  for (auto& st : steps) {
+    if (st.kind == Step::KERNEL) o << kernels[st.index].desc << "\n";
+    else o << gemms[st.index].desc << "\n";
+  }
+  return o.str();
+}
+
+// implemented in gemm_plan.cpp
+bool plan_dot(Plan& plan, int node, std::vector<int>& need_materialised, GemmSpec* out);
+void canonicalize_dots(Graph& g);
+
+std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
+  auto plan = std::make_unique<Plan>();
+  plan->g = parse_graph(bytes, nbytes);
+  Graph& g = plan->g;
+  // common-subexpression elimination: the tracer gives every call a fresh node, so
+  // e.g. two reduce_max over the same tensor arrive as two nodes
+  {
+    std::map<std::string, int> seen;
+    std::vector<int> remap(g.nodes.size());
+    for (size_t n = 0; n < g.nodes.size(); ++n) {
+      Node& nd = g.nodes[n];
+      for (int& a : nd.args) a = remap[a];
+      remap[n] = (int)n;
+      if (nd.op == "parameter") continue;
+      std::string key = nd.op + "|" + std::to_string((int)nd.dt) + "|" + shape_str(nd.shape) + "|";
+      for (int a : nd.args) key += std::to_string(a) + ",";
+      key += "|";
+      for (auto v : nd.ints) key += std::to_string(v) + ",";
+      key += "|";
+      for (auto v : nd.flts) { char b[32]; uint64_t u; memcpy(&u, &v, 8); snprintf(b, sizeof b, "%llx,", (unsigned long long)u); key += b; }
+      key += "|" + nd.blob;
+      auto it = seen.find(key);
+      if (it != seen.end()) remap[n] = it->second;
+      else seen.emplace(std::move(key), (int)n);
+    }
+    for (int& o : g.outputs) o = remap[o];
+  }
+  canonicalize_dots(g);
+  Planner P(*plan);
+
+  // outputs that are leaves, aliases of leaves, or repeated get an identity node so that
+  // every result is a fresh buffer (exla/lib/exla/defn.ex:387-393)
+  {
+    std::set<int> seen_out;
+    for (auto& o : g.outputs) {
+      const Node& nd = g.nodes[o];
+      bool leafish = nd.op == "parameter" || nd.op == "tensor" || nd.op == "metadata" || nd.op == "reshape" ||
+                     nd.op == "squeeze" || !seen_out.insert(o).second;
+      if (leafish) {
+        Node c;
+        c.op = "copy";
+        c.dt = nd.dt;
+        c.shape = nd.shape;
+        c.args = {o};
+        g.nodes.push_back(c);
+        o = (int)g.nodes.size() - 1;
+        seen_out.insert(o);
+      }
+    }
+  }
+  const int N = (int)g.nodes.size();
+
+  // liveness + op support
+  {
+    std::vector<int> stack(g.outputs.begin(), g.outputs.end());
+    while (!stack.empty()) {
+      int n = stack.back();
+      stack.pop_back();
+      if (g.nodes[n].live) continue;
+      g.nodes[n].live = true;
+      for (int a : g.nodes[n].args) stack.push_back(a);
+    }
+    for (int n = 0; n < N; ++n) {
+      const Node& nd = g.nodes[n];
+      if (!nd.live) continue;
+      bool ok = is_inline(nd) || is_reduce(nd) || nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate";
+      if (!ok) fail(NXB_ERR_UNSUPPORTED, "Nx op :" + nd.op + " is not implemented by the B200 compiler");
+      if (nd.op == "slice" && nd.args.size() != 1) fail(NXB_ERR_UNSUPPORTED, "slice with dynamic start indices is not implemented");
+    }
+  }
+
+  // slots for leaves
+  plan->param_slots.assign(g.n_params, -1);
+  P.mat.assign(N, 0);
+  for (int n = 0; n < N; ++n) {
+    Node& nd = g.nodes[n];
+    if (!nd.live) continue;
+    if (nd.op == "parameter") {
+      int pi = (int)nd.ints[0];
+      if (plan->param_slots[pi] < 0) plan->param_slots[pi] = P.new_slot(Slot::PARAM, n, pi);
+      nd.slot = plan->param_slots[pi];
+    } else if (nd.op == "tensor") {
+      nd.slot = P.new_slot(Slot::LITERAL, n, n);
+    }
+  }
+  // what must be materialised regardless of fusion
+  for (int o : g.outputs) P.mat[o] = 1;
+  std::vector<int> dots, concats;
+  for (int n = 0; n < N; ++n) {
+    const Node& nd = g.nodes[n];
+    if (!nd.live) continue;
+    if (nd.op == "dot") { P.mat[n] = 1; dots.push_back(n); }
+    if (nd.op == "concatenate") { P.mat[n] = 1; concats.push_back(n); }
+  }
+  // dot operands: decided by the GEMM planner (it may accept a transposed view directly)
+  std::map<int, GemmSpec> gemm_of;
+  for (int n : dots) {
+    std::vector<int> need;
+    GemmSpec gs;
+    plan_dot(*plan, n, need, &gs);
+    for (int m : need) P.mat[m] = 1;
+  }
+  // contiguous reshapes / metadata over materialised values share the buffer
+  auto propagate_alias = [&]() {
+    for (int n = 0; n < N; ++n) {
+      Node& nd = g.nodes[n];
+      if (!nd.live || nd.slot >= 0) continue;
+      if ((nd.op == "metadata" || nd.op == "reshape" || nd.op == "squeeze") && !nd.args.empty()) {
+        const Node& a = g.nodes[nd.args[0]];
+        if (a.slot >= 0 && !P.mat[n]) { nd.slot = a.slot; nd.alias = nd.args[0]; }
+      }
+    }
+  };
+
+  // ---- fusion: decide units ----------------------------------------------------------------
+  // `level 2` = fused row kernels; `level 1` = one kernel per materialised value (always valid)
+  for (int fusion = 2; fusion >= 1; --fusion) {
+    try {
+      // reset planner state that depends on the fusion attempt
+      Plan& pl = *plan;
+      pl.steps.clear();
+      pl.kernels.clear();
+      pl.gemms.clear();
+      pl.slots.resize(0);
+      for (auto& nd : g.nodes) { nd.slot = -1; nd.alias = -1; }
+      pl.param_slots.assign(g.n_params, -1);
+      for (int n = 0; n < N; ++n) {
+        Node& nd = g.nodes[n];
+        if (!nd.live) continue;
+        if (nd.op == "parameter") {
+          int pi = (int)nd.ints[0];
+          if (pl.param_slots[pi] < 0) pl.param_slots[pi] = P.new_slot(Slot::PARAM, n, pi);
+          nd.slot = pl.param_slots[pi];
+        } else if (nd.op == "tensor") {
+          nd.slot = P.new_slot(Slot::LITERAL, n, n);
+        }
+      }
+      // Fixpoint: reductions read from outside their kernel become materialised.
+      std::vector<Unit> units;
+      for (int iter = 0; iter < 64; ++iter) {
+        bool changed = false;
+        units.clear();
+        // (1) reduction groups
+        struct RInfo { int node; std::vector<int64_t> F; int k; std::vector<int> perm; std::set<int> cone, leaves, reds; };
+        std::vector<RInfo> rs;
+        for (int n = 0; n < N; ++n) {
+          const Node& nd = g.nodes[n];
+          if (!nd.live || !is_reduce(nd)) continue;
+          RInfo ri;
+          ri.node = n;
+          P.trailing_reduce(nd, &ri.F, &ri.k, &ri.perm);
+          P.cone(n, ri.cone, ri.leaves, ri.reds, true);
+          rs.push_back(std::move(ri));
+        }
+        std::vector<int> grp(rs.size());
+        for (size_t i = 0; i < rs.size(); ++i) grp[i] = (int)i;
+        std::function<int(int)> find = [&](int x) { return grp[x] == x ? x : grp[x] = find(grp[x]); };
+        std::map<int, int> ridx;
+        for (size_t i = 0; i < rs.size(); ++i) ridx[rs[i].node] = (int)i;
+        if (fusion >= 2) {
+          for (size_t i = 0; i < rs.size(); ++i)
+            for (size_t j = 0; j < i; ++j) {
+              if (!rs[i].perm.empty() || !rs[j].perm.empty()) continue;
+              if (rs[i].F != rs[j].F || rs[i].k != rs[j].k) continue;
+              bool share = rs[i].reds.count(rs[j].node) || rs[j].reds.count(rs[i].node);
+              if (!share)
+                for (int l : rs[i].leaves) if (rs[j].leaves.count(l) && strip_units(g.nodes[l].shape) == strip_units(rs[i].F)) { share = true; break; }
+              if (share) grp[find((int)i)] = find((int)j);
+            }
+        }
+        // a reduction that depends on a reduction of another group reads it from memory
+        for (size_t i = 0; i < rs.size(); ++i)
+          for (int r : rs[i].reds)
+            if (find(ridx[r]) != find((int)i) && !P.mat[r]) { P.mat[r] = 1; changed = true; }
+        if (changed) continue;
+        std::map<int, int> unit_of_group;
+        for (size_t i = 0; i < rs.size(); ++i) {
+          int gi = find((int)i);
+          if (!unit_of_group.count(gi)) {
+            Unit u;
+            u.kind = Unit::ROW;
+            u.F = rs[i].F;
+            u.k = rs[i].k;
+            u.perm = rs[i].perm;
+            unit_of_group[gi] = (int)units.size();
+            units.push_back(u);
+          }
+          units[unit_of_group[gi]].reduces.push_back(rs[i].node);
+        }
+        // (2) store roots
+        std::vector<int> roots;
+        for (int n = 0; n < N; ++n) {
+          const Node& nd = g.nodes[n];
+          if (!nd.live || !P.mat[n]) continue;
+          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || is_reduce(nd)) continue;
+          roots.push_back(n);
+        }
+        for (int n : roots) {
+          std::set<int> seen, leaves, reds;
+          P.cone(n, seen, leaves, reds, true);
+          const Node& nd = g.nodes[n];
+          int target = -1;
+          bool conflict = false;
+          for (int r : reds) {
+            int u = unit_of_group[find(ridx[r])];
+            if (target < 0) target = u;
+            else if (target != u) conflict = true;
+          }
+          auto fits = [&](const Unit& u) {
+            if (!u.perm.empty()) return false;
+            std::vector<int64_t> su = strip_units(nd.shape), fu = strip_units(u.F);
+            std::vector<int64_t> ru(u.F.begin(), u.F.end() - u.k);
+            ru = strip_units(ru);
+            return su == fu || su == ru;
+          };
+          if (target >= 0 && (conflict || fusion < 2 || !fits(units[target]))) {
+            for (int r : reds) if (!P.mat[r]) { P.mat[r] = 1; changed = true; }
+            continue;
+          }
+          if (target < 0 && fusion >= 2) {
+            // no reduction involved: ride along with a row kernel that already reads the same data
+            for (size_t ui = 0; ui < units.size() && target < 0; ++ui) {
+              Unit& u = units[ui];
+              if (u.kind != Unit::ROW || !u.perm.empty() || strip_units(nd.shape) != strip_units(u.F)) continue;
+              std::set<int> uleaves;
+              for (int r : u.reduces) { auto& ri = rs[ridx[r]]; uleaves.insert(ri.leaves.begin(), ri.leaves.end()); }
+              bool sub = !leaves.empty();
+              for (int l : leaves) if (!uleaves.count(l) && g.nodes[l].op != "constant") sub = false;
+              if (sub) target = (int)ui;
+            }
+          }
+          if (target >= 0) units[target].stores.push_back(n);
+          else {
+            // elementwise kernel; merge with an existing one of the same shape that shares an input
+            int merged = -1;
+            for (size_t ui = 0; ui < units.size() && merged < 0 && fusion >= 2; ++ui) {
+              Unit& u = units[ui];
+              if (u.kind != Unit::EW || u.F != nd.shape) continue;
+              for (int s : u.stores) {
+                std::set<int> s2, l2, r2;
+                P.cone(s, s2, l2, r2, true);
+                // merging is only safe if neither root depends on the other
+                if (s2.count(n) || seen.count(s)) { merged = -2; break; }
+                for (int l : leaves) if (l2.count(l)) merged = (int)ui;
+              }
+              if (merged == -2) merged = -1;
+            }
+            if (merged >= 0) units[merged].stores.push_back(n);
+            else {
+              Unit u;
+              u.kind = Unit::EW;
+              u.F = nd.shape;
+              u.stores.push_back(n);
+              units.push_back(u);
+            }
+          }
+        }
+        if (!changed) break;
+      }
+
+      // ---- slots for everything materialised ------------------------------------------------
+      std::map<int, int> out_index;
+      for (size_t i = 0; i < g.outputs.size(); ++i) out_index[g.outputs[i]] = (int)i;
+      pl.output_slots.assign(g.outputs.size(), -1);
+      for (int n = 0; n < N; ++n) {
+        Node& nd = g.nodes[n];
+        if (!nd.live || !P.mat[n] || nd.slot >= 0) continue;
+        if (out_index.count(n)) {
+          nd.slot = P.new_slot(Slot::OUTPUT, n, out_index[n]);
+          pl.output_slots[out_index[n]] = nd.slot;
+        } else {
+          nd.slot = P.new_slot(Slot::TEMP, n, n);
+        }
+      }
+      propagate_alias();
+
+      // gemm + concatenate units
+      for (int n : dots) {
+        Unit u;
+        u.kind = Unit::GEMM;
+        u.gemm_node = n;
+        units.push_back(u);
+      }
+      for (int n : concats) {
+        // one copy kernel per input, each writing its slice of the result
+        const Node& nd = g.nodes[n];
+        (void)nd;
+        fail(NXB_ERR_UNSUPPORTED, "concatenate is not implemented yet");
+      }
+
+      // ---- order units by data dependence ---------------------------------------------------------
+      auto unit_io = [&](Unit& u) {
+        u.reads.clear();
+        u.writes.clear();
+        if (u.kind == Unit::GEMM) {
+          const Node& nd = g.nodes[u.gemm_node];
+          u.writes.insert(nd.slot);
+          std::vector<int> need;
+          GemmSpec gs;
+          plan_dot(pl, u.gemm_node, need, &gs);
+          u.reads.insert(gs.a.slot);
+          u.reads.insert(gs.b.slot);
+          return;
+        }
+        std::set<int> seen, leaves, reds;
+        for (int s : u.stores) { u.writes.insert(g.nodes[s].slot); }
+        for (int r : u.reduces) if (g.nodes[r].slot >= 0) u.writes.insert(g.nodes[r].slot);
+        std::set<int> own(u.stores.begin(), u.stores.end());
+        own.insert(u.reduces.begin(), u.reduces.end());
+        std::function<void(int)> walk = [&](int n) {
+          if (!seen.insert(n).second) return;
+          const Node& nd = g.nodes[n];
+          if (nd.slot >= 0 && !own.count(n)) { u.reads.insert(nd.slot); return; }
+          for (int a : nd.args) walk(a);
+        };
+        for (int s : u.stores) walk(s);
+        for (int r : u.reduces) walk(r);
+      };
+      for (auto& u : units) unit_io(u);
+      std::vector<int> order;
+      {
+        size_t U = units.size();
+        std::vector<char> done(U, 0);
+        std::set<int> ready;   // slots available
+        for (auto& sl : pl.slots) if (sl.kind == Slot::PARAM || sl.kind == Slot::LITERAL) ready.insert((int)(&sl - &pl.slots[0]));
+        for (size_t round = 0; round < U; ++round) {
+          bool progress = false;
+          for (size_t i = 0; i < U; ++i) {
+            if (done[i]) continue;
+            bool ok = true;
+            for (int r : units[i].reads) if (!ready.count(r) && !units[i].writes.count(r)) ok = false;
+            if (!ok) continue;
+            done[i] = 1;
+            order.push_back((int)i);
+            for (int w : units[i].writes) ready.insert(w);
+            progress = true;
+          }
+          if (!progress) break;
+        }
+        if (order.size() != U) throw FusionError("fused kernels depend on each other");
+      }
+
+      // ---- generate -------------------------------------------------------------------------------
+      int kid = 0;
+      for (int ui : order) {
+        Unit& u = units[ui];
+        int step_index = (int)pl.steps.size();
+        if (u.kind == Unit::GEMM) {
+          std::vector<int> need;
+          GemmSpec gs;
+          plan_dot(pl, u.gemm_node, need, &gs);
+          pl.gemms.push_back(gs);
+          pl.steps.push_back({Step::GEMM, (int)pl.gemms.size() - 1});
+        } else {
+          KernelBuilder kb(pl, u.kind == Unit::ROW ? KernelBuilder::ROW : KernelBuilder::EW, u.F, u.kind == Unit::ROW ? u.k : 0, u.perm);
+          kb.stores = u.stores;
+          kb.reduces = u.reduces;
+          // reductions nobody outside reads and that are not outputs need no slot; fine as is
+          KernelSpec ks = kb.build("nxb_k" + std::to_string(kid++) + (u.kind == Unit::ROW ? "_row" : "_ew"));
+          pl.kernels.push_back(std::move(ks));
+          pl.steps.push_back({Step::KERNEL, (int)pl.kernels.size() - 1});
+        }
+        for (int s : u.reads) { Slot& sl = pl.slots[s]; if (sl.first_step < 0) sl.first_step = step_index; sl.last_step = step_index; }
+        for (int s : u.writes) { Slot& sl = pl.slots[s]; if (sl.first_step < 0) sl.first_step = step_index; sl.last_step = step_index; }
+      }
+      break;   // success
+    } catch (const FusionError& e) {
+      if (fusion == 1) fail(NXB_ERR_UNSUPPORTED, std::string("cannot compile this graph: ") + e.what());
+      // retry without cross-reduction fusion
+      for (int n = 0; n < N; ++n) if (g.nodes[n].live && is_reduce(g.nodes[n])) P.mat[n] = 1;
+    }
+  }
+
+  for (auto& ks : plan->kernels) ks.cubin = compile_to_cubin(ks.source, ks.name);
+  return plan;
+}
+
+}  // namespace nxb

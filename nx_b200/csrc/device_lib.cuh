@@ -1,0 +1,266 @@
+// Device-side support library for the fused kernels the planner generates.
+//
+// This text is compiled together with each generated kernel body (NVRTC,
+// sm_100a), so it uses no headers: fixed-width types, bf16/f16 conversions,
+// the math routines, 128-bit vector access and the row reductions are all
+// defined here.  Numerics contract:
+//   * f32 functions are accurate to a few ulp (parity tolerance is rtol 1e-5);
+//   * bf16/f16 values are held widened in a float register and rounded to
+//     nearest-even after every graph node (what a literal reading of the
+//     user's graph asks for);
+//   * integer arithmetic wraps.
+#pragma once
+
+typedef signed char int8_t;
+typedef unsigned char uint8_t;
+typedef short int16_t;
+typedef unsigned short uint16_t;
+typedef int int32_t;
+typedef unsigned int uint32_t;
+typedef long long int64_t;
+typedef unsigned long long uint64_t;
+
+#define NXB_DEV __device__ __forceinline__
+#define NXB_INF __int_as_float(0x7f800000)
+#define NXB_NAN __int_as_float(0x7fc00000)
+
+// ---- storage types for the 16-bit floats -----------------------------------------
+struct bf16_t { uint16_t bits; };
+struct f16_t { uint16_t bits; };
+
+NXB_DEV float bf16_to_f32(bf16_t h) { return __uint_as_float(((uint32_t)h.bits) << 16); }
+NXB_DEV bf16_t f32_to_bf16(float f) {
+  bf16_t r;
+  asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r.bits) : "f"(f));
+  return r;
+}
+// round a float register to the nearest bf16 value, keeping it widened
+NXB_DEV float round_bf16(float f) { return bf16_to_f32(f32_to_bf16(f)); }
+NXB_DEV float f16_to_f32(f16_t h) {
+  float f;
+  asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h.bits));
+  return f;
+}
+NXB_DEV f16_t f32_to_f16(float f) {
+  f16_t r;
+  asm("cvt.rn.f16.f32 %0, %1;" : "=h"(r.bits) : "f"(f));
+  return r;
+}
+NXB_DEV float round_f16(float f) { return f16_to_f32(f32_to_f16(f)); }
+
+// ---- memory <-> register representation -----------------------------------------
+// Storage type S (what sits in HBM) and register type R (what code computes on).
+template <typename S> struct Repr { typedef S R; static NXB_DEV R load(S s) { return s; } static NXB_DEV S store(R r) { return r; } };
+template <> struct Repr<bf16_t> { typedef float R; static NXB_DEV float load(bf16_t s) { return bf16_to_f32(s); } static NXB_DEV bf16_t store(float r) { return f32_to_bf16(r); } };
+template <> struct Repr<f16_t> { typedef float R; static NXB_DEV float load(f16_t s) { return f16_to_f32(s); } static NXB_DEV f16_t store(float r) { return f32_to_f16(r); } };
+
+template <typename S, int V> struct __align__(sizeof(S) * V) Pack { S v[V]; };
+
+// Vector load of V consecutive elements (address must be aligned to sizeof(S)*V).
+template <typename S, int V>
+NXB_DEV void ld_vec(const S* __restrict__ p, typename Repr<S>::R (&dst)[V]) {
+  Pack<S, V> t = *reinterpret_cast<const Pack<S, V>*>(p);
+#pragma unroll
+  for (int i = 0; i < V; ++i) dst[i] = Repr<S>::load(t.v[i]);
+}
+template <typename S, int V>
+NXB_DEV void st_vec(S* __restrict__ p, const typename Repr<S>::R (&src)[V]) {
+  Pack<S, V> t;
+#pragma unroll
+  for (int i = 0; i < V; ++i) t.v[i] = Repr<S>::store(src[i]);
+  *reinterpret_cast<Pack<S, V>*>(p) = t;
+}
+template <typename S> NXB_DEV typename Repr<S>::R ld1(const S* __restrict__ p) { return Repr<S>::load(*p); }
+template <typename S> NXB_DEV void st1(S* __restrict__ p, typename Repr<S>::R v) { *p = Repr<S>::store(v); }
+
+// ---- conversions (as_type) ---------------------------------------------------------
+// float -> integer: truncate; NaN -> 0; out of range (incl. +-inf) saturates.
+template <typename I> NXB_DEV I f2i(double f) {
+  const bool is_signed = ((I)-1) < (I)0;
+  const int bits = sizeof(I) * 8;
+  if (f != f) return (I)0;
+  if (is_signed) {
+    double lo = -__longlong_as_double(0x3ff0000000000000LL + ((long long)(bits - 1) << 52));  // -2^(bits-1)
+    if (f <= lo) return (I)((uint64_t)1 << (bits - 1));
+    if (f >= -lo) return (I)(((uint64_t)1 << (bits - 1)) - 1);
+    return (I)(long long)f;
+  } else {
+    if (f <= 0.0) return (I)0;
+    double hi = __longlong_as_double(0x3ff0000000000000LL + ((long long)bits << 52));          // 2^bits
+    if (f >= hi) return (I)~(I)0;
+    return (I)(unsigned long long)f;
+  }
+}
+
+// ---- f32 math ------------------------------------------------------------------------
+NXB_DEV float fast_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+NXB_DEV float fast_rcp(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+NXB_DEV float fast_lg2(float x) { float y; asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+// The f32 transcendental functions are the CUDA math library's (1-2 ulp), reached
+// through these wrappers so that a tuned replacement only has to be swapped in here.
+NXB_DEV float nx_exp(float x) { return expf(x); }
+NXB_DEV float nx_sigmoid(float x) { return __fdiv_rn(1.f, 1.f + expf(-x)); }
+NXB_DEV float nx_tanh(float x) { return tanhf(x); }
+NXB_DEV float nx_log(float x) { return logf(x); }
+NXB_DEV float nx_rsqrt(float x) { return 1.0f / sqrtf(x); }
+NXB_DEV float nx_erf_inv(float x) { return erfinvf(x); }
+NXB_DEV float nx_round(float x) { return roundf(x); }     // half away from zero
+NXB_DEV double nx_round(double x) { return round(x); }
+NXB_DEV float nx_sign(float x) { return (x > 0.f) ? 1.f : ((x < 0.f) ? -1.f : x); }
+NXB_DEV double nx_sign(double x) { return (x > 0.0) ? 1.0 : ((x < 0.0) ? -1.0 : x); }
+template <typename I> NXB_DEV I nx_sign_i(I x) { return (I)((x > 0) - (x < 0)); }
+
+NXB_DEV double nx_exp(double x) { return exp(x); }
+NXB_DEV double nx_sigmoid(double x) { return 1.0 / (1.0 + exp(-x)); }
+NXB_DEV double nx_tanh(double x) { return tanh(x); }
+NXB_DEV double nx_log(double x) { return log(x); }
+NXB_DEV double nx_rsqrt(double x) { return 1.0 / sqrt(x); }
+NXB_DEV double nx_erf_inv(double x) { return erfinv(x); }
+
+// max/min where NaN wins (nx element_max/element_min)
+NXB_DEV float nx_max(float a, float b) { return (a != a || b != b) ? NXB_NAN : fmaxf(a, b); }
+NXB_DEV float nx_min(float a, float b) { return (a != a || b != b) ? NXB_NAN : fminf(a, b); }
+NXB_DEV double nx_max(double a, double b) { return (a != a || b != b) ? (double)NXB_NAN : fmax(a, b); }
+NXB_DEV double nx_min(double a, double b) { return (a != a || b != b) ? (double)NXB_NAN : fmin(a, b); }
+#define NXB_INT_MINMAX(T) \
+  NXB_DEV T nx_max(T a, T b) { return a > b ? a : b; } \
+  NXB_DEV T nx_min(T a, T b) { return a < b ? a : b; }
+NXB_INT_MINMAX(int8_t) NXB_INT_MINMAX(uint8_t) NXB_INT_MINMAX(int16_t) NXB_INT_MINMAX(uint16_t)
+NXB_INT_MINMAX(int32_t) NXB_INT_MINMAX(uint32_t) NXB_INT_MINMAX(int64_t) NXB_INT_MINMAX(uint64_t)
+
+template <typename I> NXB_DEV I nx_ipow(I base, I e) {
+  I r = 1;
+  const bool is_signed = ((I)-1) < (I)0;
+  if (is_signed && e < 0) return (base == 1) ? (I)1 : ((base == (I)-1) ? ((e & 1) ? (I)-1 : (I)1) : (I)0);
+  while (e) { if (e & 1) r = (I)(r * base); base = (I)(base * base); e = (I)((uint64_t)e >> 1); }
+  return r;
+}
+template <typename I> NXB_DEV I nx_idiv(I a, I b) { return b == 0 ? (I)-1 : (I)(a / b); }
+template <typename I> NXB_DEV I nx_irem(I a, I b) { return b == 0 ? a : (I)(a % b); }
+template <typename I> NXB_DEV I nx_shl(I a, I b) { return ((uint64_t)b >= sizeof(I) * 8) ? (I)0 : (I)(a << b); }
+template <typename I> NXB_DEV I nx_shr(I a, I b) {
+  const bool is_signed = ((I)-1) < (I)0;
+  if ((uint64_t)b >= sizeof(I) * 8) return (is_signed && a < 0) ? (I)-1 : (I)0;
+  return (I)(a >> b);
+}
+template <typename I> NXB_DEV I nx_popc(I a) {
+  return (I)__popcll((unsigned long long)a & (sizeof(I) == 8 ? ~0ULL : ((1ULL << (sizeof(I) * 8 % 64)) - 1)));
+}
+template <typename I> NXB_DEV I nx_clz(I a) {
+  unsigned long long u = (unsigned long long)a & (sizeof(I) == 8 ? ~0ULL : ((1ULL << (sizeof(I) * 8 % 64)) - 1));
+  return (I)(__clzll((long long)u) - (64 - (int)sizeof(I) * 8));
+}
+
+// ---- reductions ------------------------------------------------------------------------
+// Combine operators.  Each has ::apply(a, b) on the register type.
+struct OpSum { template <typename T> static NXB_DEV T apply(T a, T b) { return a + b; } };
+struct OpProd { template <typename T> static NXB_DEV T apply(T a, T b) { return a * b; } };
+struct OpMax { template <typename T> static NXB_DEV T apply(T a, T b) { return nx_max(a, b); } };
+struct OpMin { template <typename T> static NXB_DEV T apply(T a, T b) { return nx_min(a, b); } };
+struct OpAnd { template <typename T> static NXB_DEV T apply(T a, T b) { return (T)(a & b); } };
+struct OpOr { template <typename T> static NXB_DEV T apply(T a, T b) { return (T)(a | b); } };
+
+template <typename T> NXB_DEV T shfl_xor(T v, int m) {
+  if (sizeof(T) == 8) {
+    long long x = *reinterpret_cast<long long*>(&v);
+    x = __shfl_xor_sync(0xffffffffu, x, m);
+    return *reinterpret_cast<T*>(&x);
+  } else if (sizeof(T) == 4) {
+    int x = *reinterpret_cast<int*>(&v);
+    x = __shfl_xor_sync(0xffffffffu, x, m);
+    return *reinterpret_cast<T*>(&x);
+  } else {
+    int x = (int)v;
+    x = __shfl_xor_sync(0xffffffffu, x, m);
+    return (T)x;
+  }
+}
+
+template <typename Op, typename T> NXB_DEV T warp_reduce(T v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = Op::apply(v, shfl_xor(v, m));
+  return v;
+}
+
+// All THREADS threads of the CTA cooperate on one row; every thread gets the result.
+// `scratch` is shared memory with room for 32 elements of 8 bytes.
+template <typename Op, typename T, int THREADS>
+NXB_DEV T row_reduce(T v, void* scratch) {
+  v = warp_reduce<Op>(v);
+  if (THREADS > 32) {
+    T* s = reinterpret_cast<T*>(scratch);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();                    // scratch may still be read from the previous use
+    if (lane == 0) s[warp] = v;
+    __syncthreads();
+    // every warp reduces the per-warp partials itself: one barrier fewer than a broadcast
+    const int NW = THREADS / 32;
+    T w = s[lane < NW ? lane : 0];
+    if (NW < 32) {
+#pragma unroll
+      for (int m = NW / 2; m > 0; m >>= 1) w = Op::apply(w, shfl_xor(w, m));
+    } else {
+      w = warp_reduce<Op>(w);
+    }
+    v = w;
+  }
+  return v;
+}
+
+// (value, index) pair for argmax/argmin.  `better(a, b)` is a strict total
+// order, so the result does not depend on the reduction tree:
+//   * a NaN beats every number; among NaNs the highest index wins (what
+//     Nx.BinaryBackend's left-to-right scan returns);
+//   * otherwise the larger (argmax) / smaller (argmin) value wins;
+//   * equal values: lowest index (tie_break :low) or highest (:high).
+template <typename T> struct ArgPair { T v; long long i; };
+
+template <typename T> NXB_DEV bool is_nan_any(T) { return false; }
+template <> NXB_DEV bool is_nan_any<float>(float x) { return x != x; }
+template <> NXB_DEV bool is_nan_any<double>(double x) { return x != x; }
+
+template <bool IS_MAX, bool TIE_HIGH, typename T>
+NXB_DEV bool arg_better(const ArgPair<T>& a, const ArgPair<T>& b) {
+  if (b.i < 0) return a.i >= 0;
+  if (a.i < 0) return false;
+  const bool an = is_nan_any(a.v), bn = is_nan_any(b.v);
+  if (an || bn) return an && (!bn || a.i > b.i);
+  if (a.v != b.v) return IS_MAX ? (a.v > b.v) : (a.v < b.v);
+  return TIE_HIGH ? (a.i > b.i) : (a.i < b.i);
+}
+
+template <bool IS_MAX, bool TIE_HIGH, typename T>
+NXB_DEV ArgPair<T> arg_combine(ArgPair<T> a, ArgPair<T> b) { return arg_better<IS_MAX, TIE_HIGH>(b, a) ? b : a; }
+
+template <bool IS_MAX, bool TIE_HIGH, typename T, int THREADS>
+NXB_DEV ArgPair<T> row_arg_reduce(ArgPair<T> p, void* scratch) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) {
+    ArgPair<T> o;
+    o.v = shfl_xor(p.v, m);
+    o.i = shfl_xor(p.i, m);
+    p = arg_combine<IS_MAX, TIE_HIGH>(p, o);
+  }
+  if (THREADS > 32) {
+    // scratch: 32 values (8 bytes each) followed by 32 indices
+    long long* sv = reinterpret_cast<long long*>(scratch);
+    long long* si = sv + 32;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) { T* pv = reinterpret_cast<T*>(&sv[warp]); *pv = p.v; si[warp] = p.i; }
+    __syncthreads();
+    const int NW = THREADS / 32;
+    ArgPair<T> w;
+    if (lane < NW) { w.v = *reinterpret_cast<T*>(&sv[lane]); w.i = si[lane]; } else { w.v = p.v; w.i = -1; }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+      ArgPair<T> o;
+      o.v = shfl_xor(w.v, m);
+      o.i = shfl_xor(w.i, m);
+      w = arg_combine<IS_MAX, TIE_HIGH>(w, o);
+    }
+    p = w;
+  }
+  return p;
+}

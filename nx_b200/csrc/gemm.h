@@ -1,0 +1,28 @@
+// Matrix-product launchers shared by the planner and the executor.
+#pragma once
+#include "program.h"
+
+namespace nxb {
+
+// C[b][m][n] = sum_k A[b][m][k] * B[b][k][n], C row-major [batch][m][n].
+// An operand with trans == false has the reduction index k contiguous
+// (A stored [m][k], B stored [n][k]); with trans == true the other index is
+// contiguous (A stored [k][m], B stored [k][n]).  `ld` is the stride of the
+// non-contiguous index, `batch_stride` the distance between matrices.
+struct GemmArgs {
+  const void* a; const void* b; void* c;
+  const void* bias;     // optional, per output column n, in the output type
+  const void* scale;    // optional, f32 per output column n
+  int64_t batch, m, n, k;
+  int64_t lda, ldb, bsa, bsb;
+  bool ta, tb;
+  DType da, db, dc;
+  int epilogue;
+};
+
+enum GemmEpilogue { EPI_NONE = 0 };
+
+// Generic CUDA-core product for every type combination (exact for integers).
+void launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);
+
+}  // namespace nxb

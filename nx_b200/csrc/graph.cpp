@@ -1,0 +1,116 @@
+// Deserialiser for the program wire format (layout in include/nxb200.h) and
+// NVRTC front door.
+#include "program.h"
+
+#include <nvrtc.h>
+
+namespace nxb {
+
+namespace {
+struct Reader {
+  const uint8_t* p;
+  size_t n, pos = 0;
+  void need(size_t k) {
+    if (pos + k > n) fail(NXB_ERR_INVALID_ARGUMENT, "program bytes are truncated");
+  }
+  template <typename T> T get() {
+    need(sizeof(T));
+    T v;
+    memcpy(&v, p + pos, sizeof(T));
+    pos += sizeof(T);
+    return v;
+  }
+  std::string bytes(size_t k) {
+    need(k);
+    std::string s((const char*)p + pos, k);
+    pos += k;
+    return s;
+  }
+};
+}  // namespace
+
+Graph parse_graph(const uint8_t* bytes, size_t nbytes) {
+  Reader r{bytes, nbytes};
+  if (nbytes < 8 || memcmp(bytes, "NXB1", 4) != 0) fail(NXB_ERR_INVALID_ARGUMENT, "not an NXB1 program");
+  r.pos = 4;
+  Graph g;
+  uint32_t n = r.get<uint32_t>();
+  if (n > (1u << 24)) fail(NXB_ERR_INVALID_ARGUMENT, "program has too many nodes");
+  g.nodes.resize(n);
+  for (uint32_t i = 0; i < n; ++i) {
+    Node& nd = g.nodes[i];
+    uint8_t l = r.get<uint8_t>();
+    nd.op = r.bytes(l);
+    uint8_t dt = r.get<uint8_t>();
+    if (dt > NXB_F64) fail(NXB_ERR_INVALID_ARGUMENT, "node " + std::to_string(i) + ": unknown element type code");
+    nd.dt = (DType)dt;
+    uint8_t rank = r.get<uint8_t>();
+    if (rank > NXB_MAX_RANK) fail(NXB_ERR_INVALID_ARGUMENT, "node " + std::to_string(i) + ": rank above " + std::to_string(NXB_MAX_RANK));
+    for (int k = 0; k < rank; ++k) {
+      int64_t d = r.get<int64_t>();
+      if (d < 0) fail(NXB_ERR_INVALID_ARGUMENT, "negative dimension");
+      nd.shape.push_back(d);
+    }
+    uint16_t na = r.get<uint16_t>();
+    for (int k = 0; k < na; ++k) {
+      uint32_t a = r.get<uint32_t>();
+      if (a >= i) fail(NXB_ERR_INVALID_ARGUMENT, "node " + std::to_string(i) + " refers to a later node");
+      nd.args.push_back((int)a);
+    }
+    uint16_t ni = r.get<uint16_t>();
+    for (int k = 0; k < ni; ++k) nd.ints.push_back(r.get<int64_t>());
+    uint16_t nf = r.get<uint16_t>();
+    for (int k = 0; k < nf; ++k) nd.flts.push_back(r.get<double>());
+    uint64_t nb = r.get<uint64_t>();
+    nd.blob = r.bytes((size_t)nb);
+    if (nd.op == "parameter") {
+      if (nd.ints.size() != 1 || nd.ints[0] < 0) fail(NXB_ERR_INVALID_ARGUMENT, "parameter node without an index");
+      g.n_params = std::max(g.n_params, (int)nd.ints[0] + 1);
+    }
+    if (nd.op == "tensor" && nd.blob.size() != (size_t)shape_numel(nd.shape) * dtype_size(nd.dt))
+      fail(NXB_ERR_INVALID_ARGUMENT, "tensor literal has the wrong number of bytes");
+  }
+  uint32_t no = r.get<uint32_t>();
+  for (uint32_t i = 0; i < no; ++i) {
+    uint32_t o = r.get<uint32_t>();
+    if (o >= n) fail(NXB_ERR_INVALID_ARGUMENT, "output index out of range");
+    g.outputs.push_back((int)o);
+  }
+  return g;
+}
+
+const char* device_lib_source() {
+  static const char* src =
+#include "device_lib_embed.inc"
+      ;
+  return src;
+}
+
+std::string compile_to_cubin(const std::string& source, const std::string& name) {
+  nvrtcProgram prog;
+  std::string full = std::string(device_lib_source()) + "\n" + source;
+  if (nvrtcCreateProgram(&prog, full.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS)
+    fail(NXB_ERR_RUNTIME, "nvrtcCreateProgram failed");
+  const char* opts[] = {"-arch=sm_100a", "-std=c++17", "-lineinfo", "--use_fast_math=false", "-default-device"};
+  const char* use[] = {opts[0], opts[1], opts[2]};
+  nvrtcResult r = nvrtcCompileProgram(prog, 3, use);
+  if (r != NVRTC_SUCCESS) {
+    size_t n = 0;
+    nvrtcGetProgramLogSize(prog, &n);
+    std::string log(n, '\0');
+    nvrtcGetProgramLog(prog, &log[0]);
+    nvrtcDestroyProgram(&prog);
+    fail(NXB_ERR_RUNTIME, "kernel " + name + " failed to compile:\n" + log + "\n--- source ---\n" + source);
+  }
+  size_t n = 0;
+  if (nvrtcGetCUBINSize(prog, &n) != NVRTC_SUCCESS || n == 0) {
+    nvrtcDestroyProgram(&prog);
+    fail(NXB_ERR_RUNTIME, "nvrtc produced no cubin for " + name);
+  }
+  std::string cubin(n, '\0');
+  nvrtcGetCUBIN(prog, &cubin[0]);
+  nvrtcDestroyProgram(&prog);
+  return cubin;
+}
+
+}  // namespace nxb

@@ -1,0 +1,103 @@
+// The compiled form of a defn: graph, buffer slots, generated kernels, steps.
+#pragma once
+
+#include "common.h"
+
+namespace nxb {
+
+struct Node {
+  std::string op;
+  DType dt = NXB_F32;
+  std::vector<int64_t> shape;
+  std::vector<int> args;
+  std::vector<int64_t> ints;
+  std::vector<double> flts;
+  std::string blob;
+  // planner state
+  int alias = -1;        // node whose buffer this node shares (metadata, contiguous reshape)
+  int slot = -1;         // buffer slot when the value lives in global memory
+  bool live = false;
+};
+
+struct Graph {
+  std::vector<Node> nodes;
+  std::vector<int> outputs;
+  int n_params = 0;
+};
+
+Graph parse_graph(const uint8_t* bytes, size_t nbytes);
+
+struct Slot {
+  enum Kind { PARAM, OUTPUT, TEMP, LITERAL } kind = TEMP;
+  int index = 0;          // parameter index / output index / literal node
+  DType dt = NXB_F32;
+  std::vector<int64_t> shape;
+  size_t nbytes = 0;
+  int node = -1;
+  int first_step = -1, last_step = -1;
+};
+
+struct KernelSpec {
+  std::string name, source, desc, cubin;
+  unsigned grid = 1, block = 1, smem = 0;
+  std::vector<int> arg_slots;     // one pointer argument per entry
+  std::vector<size_t> arg_offsets;  // byte offset added to the slot's base pointer
+};
+
+// Operand of a matrix product as a strided batch of row-major matrices.
+struct GemmOperand {
+  int slot = -1;
+  int64_t batch_stride = 0;   // elements
+  int64_t ld = 0;             // leading dimension, elements
+  bool trans = false;         // false: the reduction index is contiguous
+  DType dt = NXB_F32;
+};
+
+struct GemmSpec {
+  int64_t batch = 1, m = 0, n = 0, k = 0;
+  GemmOperand a, b;           // a: [m,k] (trans: [k,m]);  b: [k,n] stored as [n,k] when !trans... see gemm.h
+  int out_slot = -1;
+  DType out_dt = NXB_F32;
+  std::string desc;
+  // fused epilogue (see gemm.h)
+  int epilogue = 0;
+  int bias_slot = -1;
+  int scale_slot = -1;
+};
+
+struct Step {
+  enum Kind { KERNEL, GEMM } kind = KERNEL;
+  int index = 0;
+};
+
+struct Plan {
+  Graph g;
+  std::vector<Slot> slots;
+  std::vector<Step> steps;
+  std::vector<KernelSpec> kernels;
+  std::vector<GemmSpec> gemms;
+  std::vector<int> param_slots;   // by parameter index (-1 when unused)
+  std::vector<int> output_slots;  // by output index
+  std::string describe() const;
+};
+
+std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes);
+
+// NVRTC: compile CUDA source to an sm_100a cubin (needs no GPU).
+std::string compile_to_cubin(const std::string& source, const std::string& name);
+const char* device_lib_source();
+
+}  // namespace nxb
+
+struct nxb200_program {
+  uint32_t magic = 0x4e584250;    // "NXBP"
+  std::unique_ptr<nxb::Plan> plan;
+  std::mutex mu;
+  // per device: loaded modules/functions and uploaded literals
+  struct Loaded {
+    std::vector<CUmodule> modules;
+    std::vector<CUfunction> functions;
+    std::map<int, void*> literals;   // slot -> device pointer
+  };
+  std::map<int, Loaded> loaded;
+};

@@ -62,6 +62,19 @@ class Program:
         l.nxb200_program_describe(self.handle, buf, n + 1)
         return buf.value.decode()
 
+    def kernel_sources(self):
+        """Generated CUDA source of each fused kernel (diagnostics)."""
+        l = nif.lib()
+        out, i = [], 0
+        while True:
+            n = l.nxb200_program_kernel_source(self.handle, i, None, 0)
+            if n == 0:
+                return out
+            buf = C.create_string_buffer(n + 1)
+            l.nxb200_program_kernel_source(self.handle, i, buf, n + 1)
+            out.append(buf.value.decode())
+            i += 1
+
     def launch_count(self):
         n = C.c_int()
         nif.check(nif.lib().nxb200_program_launch_count(self.handle, C.byref(n)))
@@ -226,3 +239,4 @@ def build_program(fun, templates):
     oracle, which interprets the same bytes)."""
     outs, ospec = trace(fun, list(templates))
     return E.serialize(outs), ospec
+

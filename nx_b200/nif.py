@@ -88,6 +88,8 @@ def _declare(l):
         f.argtypes = args
     l.nxb200_program_describe.restype = sz
     l.nxb200_program_describe.argtypes = [vp, C.c_char_p, sz]
+    l.nxb200_program_kernel_source.restype = sz
+    l.nxb200_program_kernel_source.argtypes = [vp, i32, C.c_char_p, sz]
 
 
 def last_error():

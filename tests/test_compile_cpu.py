@@ -1,0 +1,53 @@
+"""Host-only checks of the native library: it loads, exports every symbol the
+header declares, and the planner + code generator produce kernels that compile
+for sm_100a (NVRTC needs no GPU) for every golden graph."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from golden.reference_vectors import CASES
+from helpers import host_tensor
+from nx_b200 import defn, nif
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "nxb200.h")).read()
+    names = set(re.findall(r"\b(nxb200_[a-z_0-9]+)\s*\(", header))
+    assert len(names) > 25
+    lib = ctypes.CDLL(nif.lib_path())
+    missing = [n for n in sorted(names) if not hasattr(lib, n)]
+    assert not missing, f"declared but not exported: {missing}"
+
+
+def test_init_without_gpu_reports_zero_or_more_devices():
+    assert nif.device_count() >= 0
+
+
+@pytest.mark.parametrize("c", CASES, ids=[c["name"] for c in CASES])
+def test_golden_graphs_compile(c):
+    args = [host_tensor(v, t) for v, t in c["args"]]
+    blob, _ = defn.build_program(c["fun"], args)
+    prog = defn.Program(blob)
+    assert prog.n_outputs == len(c["expect"])
+    assert prog.launch_count() >= 1
+
+
+def test_bad_program_bytes_are_rejected():
+    with pytest.raises(ValueError):
+        defn.Program(b"nope")
+    with pytest.raises(ValueError):
+        defn.Program(b"NXB1" + b"\x01\x00\x00\x00")
+
+
+def test_unsupported_op_is_reported():
+    import struct
+    name = b"while"
+    blob = b"NXB1" + struct.pack("<I", 1) + struct.pack("<B", len(name)) + name + struct.pack("<BB", 10, 0) \
+        + struct.pack("<H", 0) + struct.pack("<H", 0) + struct.pack("<H", 0) + struct.pack("<Q", 0) \
+        + struct.pack("<I", 1) + struct.pack("<I", 0)
+    with pytest.raises(nif.Unsupported):
+        defn.Program(blob)

@@ -1,0 +1,280 @@
+"""Parity of the CUDA path against the CPU oracle on seeded random inputs.
+
+Tolerances (the ones the north star states): bit-exact for integer and index
+outputs; f32 within rtol 1e-5 (plus atol 1e-6 for values that cancel to ~0);
+bf16 within rtol 2e-2 / atol 1e-2.
+"""
+import numpy as np
+import pytest
+
+import nx_oracle as O
+from helpers import assert_close
+from nx_b200 import backend, defn, nx, types as T
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = dict(rtol=1e-5, atol=1e-6)
+BF16_TOL = dict(rtol=2e-2, atol=1e-2)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    backend.set_default_backend("b200", 0)
+    yield
+    backend.set_default_backend(None)
+
+
+def run_both(fun, arrays, types):
+    """arrays: numpy arrays (f32 for bf16 inputs); returns [(gpu, oracle, type)]."""
+    host = []
+    for a, t in zip(arrays, types):
+        backend.set_default_backend(None)
+        host.append(nx.tensor(a, t))
+        backend.set_default_backend("b200", 0)
+    dev = [backend.backend_transfer(h) for h in host]
+    out = defn.jit(fun)(*dev)
+    outs = list(out) if isinstance(out, (tuple, list)) else [out]
+    blob, _ = defn.build_program(fun, host)
+    ref = O.run_program(blob, [h.data.raw for h in host], "xla_like")
+    assert len(ref) == len(outs)
+    return [(nx.to_numpy(g), r[0], r[1]) for g, r in zip(outs, ref)]
+
+
+def check(results, what=""):
+    for i, (g, r, t) in enumerate(results):
+        assert g.shape == r.shape
+        if t[0] in ("s", "u"):
+            assert np.array_equal(g, r), f"{what} output {i}: integer mismatch"
+        elif t == ("bf", 16):
+            assert_close(g, r, what=f"{what} output {i}", **BF16_TOL)
+        else:
+            assert_close(g, r, what=f"{what} output {i}", **F32_TOL)
+
+
+def fused_rows(x):
+    m = nx.reduce_max(x, axes=[1], keep_axes=True)
+    e = nx.exp(x - m)
+    s = nx.sum(e, axes=[1], keep_axes=True)
+    return (nx.squeeze(m, [1]), e, nx.squeeze(s, [1]), nx.logsumexp(x, axes=[1]), e / s,
+            nx.argmax(x, axis=1), nx.tanh(x * 0.5 + 0.1) * nx.sigmoid(x))
+
+
+@pytest.mark.parametrize("shape", [(1, 1), (3, 5), (7, 127), (4, 128), (5, 129), (16, 1000), (8, 4096),
+                                   (3, 32768), (2, 40000), (64, 10)])
+def test_fused_row_program_f32(shape):
+    """The bandwidth-bound configuration (row max, exp, sum, logsumexp, softmax,
+    argmax, tanh*sigmoid chain) at sizes around every tile and vector boundary."""
+    rng = np.random.default_rng(1)
+    x = rng.normal(0, 2, shape).astype(np.float32)
+    check(run_both(fused_rows, [x], ["f32"]), f"rows {shape}")
+
+
+def test_fused_row_program_is_one_launch():
+    prog = defn.compile(fused_rows, [defn.template((64, 1024), "f32")]).program
+    assert prog.launch_count() == 1, prog.describe()
+
+
+def test_argmax_ties_and_nan_rows():
+    x = np.zeros((6, 300), dtype=np.float32)
+    x[1, 7] = x[1, 200] = 3.0            # tie: lowest index
+    x[2, 5] = np.nan                      # one NaN beats numbers
+    x[3, 5] = x[3, 250] = np.nan          # several NaNs: last one (BinaryBackend scan order)
+    x[4] = -np.inf
+    x[5, 299] = np.inf
+    t = nx.tensor(x)
+    lo = nx.to_numpy(nx.argmax(t, axis=1))
+    hi = nx.to_numpy(nx.argmax(t, axis=1, tie_break="high"))
+    assert lo.tolist() == [0, 7, 5, 250, 0, 299]
+    assert hi.tolist() == [299, 200, 5, 250, 299, 299]
+    assert nx.to_numpy(nx.argmin(t, axis=1)).tolist() == [0, 0, 5, 250, 0, 0]
+
+
+UNARY = ["exp", "expm1", "log", "log1p", "sigmoid", "cos", "sin", "tan", "cosh", "sinh", "tanh", "acos", "asin",
+         "atan", "acosh", "asinh", "atanh", "sqrt", "rsqrt", "cbrt", "erf", "erfc", "erf_inv"]
+
+
+@pytest.mark.parametrize("op", UNARY)
+def test_unary_math_f32(op):
+    rng = np.random.default_rng(7)
+    x = rng.uniform(-3, 3, (33, 77)).astype(np.float32)
+    if op in ("log", "sqrt", "rsqrt", "log1p"):
+        x = np.abs(x) + 0.01
+    if op in ("acos", "asin", "atanh", "erf_inv"):
+        x = np.clip(x / 3.1, -0.99, 0.99)
+    if op == "acosh":
+        x = np.abs(x) + 1.0
+    f = getattr(nx, op)
+    check(run_both(lambda t: f(t), [x], ["f32"]), op)
+
+
+@pytest.mark.parametrize("op", ["exp", "tanh", "sigmoid", "rsqrt", "cos", "sin", "erf", "negate", "abs"])
+def test_unary_bf16(op):
+    rng = np.random.default_rng(8)
+    x = np.abs(rng.normal(0, 1, (17, 256)).astype(np.float32)) + 0.05
+    f = getattr(nx, op)
+    check(run_both(lambda t: f(t), [x], ["bf16"]), op)
+
+
+BINARY = ["add", "subtract", "multiply", "divide", "pow", "remainder", "atan2", "min", "max"]
+
+
+@pytest.mark.parametrize("op", BINARY)
+@pytest.mark.parametrize("types", [("f32", "f32"), ("bf16", "bf16"), ("f32", "bf16"), ("s32", "f32")])
+def test_binary_float(op, types):
+    rng = np.random.default_rng(9)
+    a = rng.uniform(0.5, 3, (9, 1, 64)).astype(np.float32)
+    b = rng.uniform(0.5, 3, (5, 64)).astype(np.float32)
+    if types[0].startswith("s"):
+        a = np.round(a * 3)
+    f = getattr(nx, op)
+    check(run_both(lambda x, y: f(x, y), [a, b], list(types)), f"{op} {types}")
+
+
+INT_BINARY = ["add", "subtract", "multiply", "quotient", "remainder", "min", "max", "bitwise_and", "bitwise_or",
+              "bitwise_xor", "left_shift", "right_shift", "pow"]
+
+
+@pytest.mark.parametrize("op", INT_BINARY)
+@pytest.mark.parametrize("types", [("s32", "s32"), ("s8", "s8"), ("u8", "s8"), ("u8", "u8"), ("s64", "s32"), ("u16", "u32")])
+def test_binary_integer_exact(op, types):
+    rng = np.random.default_rng(10)
+    a = rng.integers(1, 100, (13, 37))
+    b = rng.integers(1, 6, (37,))
+    if op in ("left_shift", "right_shift", "pow"):
+        b = rng.integers(0, 4, (37,))
+    f = getattr(nx, op)
+    check(run_both(lambda x, y: f(x, y), [a, b], list(types)), f"{op} {types}")
+
+
+@pytest.mark.parametrize("op", ["equal", "not_equal", "greater", "less", "greater_equal", "less_equal",
+                                "logical_and", "logical_or", "logical_xor"])
+def test_comparisons(op):
+    rng = np.random.default_rng(11)
+    a = rng.integers(-2, 3, (40, 9)).astype(np.float32)
+    b = rng.integers(-2, 3, (9,))
+    a[0, 0] = np.nan
+    f = getattr(nx, op)
+    check(run_both(lambda x, y: f(x, y), [a, b], ["f32", "s32"]), op)
+
+
+@pytest.mark.parametrize("src,dst", [("f32", "s32"), ("f32", "u8"), ("f32", "bf16"), ("bf16", "f32"), ("s32", "f32"),
+                                     ("s32", "s8"), ("u8", "f32"), ("f32", "f64"), ("f64", "f32"), ("f32", "f16"),
+                                     ("s64", "bf16")])
+def test_as_type(src, dst):
+    rng = np.random.default_rng(12)
+    x = rng.uniform(-200, 200, (1000,)).astype(np.float32)
+    if src[0] in "su":
+        x = np.round(x)
+    if src[0] == "u":
+        x = np.abs(x)
+    check(run_both(lambda t: nx.as_type(t, dst), [x], [src]), f"{src}->{dst}")
+
+
+def test_as_type_non_finite_to_int():
+    x = np.array([np.inf, np.nan, -np.inf, 1e20, -1e20, 3.99, -3.99], dtype=np.float32)
+    t = nx.tensor(x)
+    assert nx.to_numpy(nx.as_type(t, "s16")).tolist() == [32767, 0, -32768, 32767, -32768, 3, -3]
+    assert nx.to_numpy(nx.as_type(t, "u8")).tolist() == [255, 0, 0, 255, 0, 3, 0]
+    assert nx.to_numpy(nx.as_type(t, "s64")).tolist()[:3] == [2**63 - 1, 0, -2**63]
+
+
+@pytest.mark.parametrize("op", ["sum", "product", "reduce_max", "reduce_min"])
+@pytest.mark.parametrize("axes,keep", [([2], False), ([1, 2], True), ([0], False), ([0, 2], True), (None, False), ([1], False)])
+def test_reductions_all_axes(op, axes, keep):
+    rng = np.random.default_rng(13)
+    x = rng.uniform(0.9, 1.1, (6, 10, 36)).astype(np.float32)
+    f = getattr(nx, op)
+    check(run_both(lambda t: f(t, axes=axes, keep_axes=keep), [x], ["f32"]), f"{op} {axes}")
+    xi = rng.integers(-3, 4, (6, 10, 36))
+    if op != "product":
+        check(run_both(lambda t: f(t, axes=axes, keep_axes=keep), [xi], ["s8"]), f"{op} {axes} s8")
+
+
+def test_all_any():
+    rng = np.random.default_rng(14)
+    x = rng.integers(0, 2, (50, 70))
+    check(run_both(lambda t: (nx.all(t, axes=[1]), nx.any(t, axes=[1]), nx.all(t), nx.any(t, axes=[0])), [x], ["u8"]))
+
+
+def test_shape_ops_fuse_into_consumers():
+    rng = np.random.default_rng(15)
+    x = rng.normal(0, 1, (4, 6, 8)).astype(np.float32)
+    b = rng.normal(0, 1, (6,)).astype(np.float32)
+
+    def f(x, b):
+        t = nx.transpose(x, [2, 0, 1])                     # {8,4,6}
+        y = t + nx.broadcast(b, (8, 4, 6), axes=[2])
+        s = nx.slice(y, [1, 0, 2], [6, 4, 3], [2, 1, 1])   # {3,4,3}
+        r = nx.reshape(s, (9, 4))
+        i = nx.iota((9, 4), axis=0)
+        return r * 2.0, nx.select(nx.greater(i, 3), r, 0.0), nx.squeeze(nx.new_axis(r, 0), [0]) - 1
+
+    check(run_both(f, [x, b], ["f32", "f32"]), "shape ops")
+
+
+def test_outputs_that_are_inputs_or_constants():
+    x = np.arange(12, dtype=np.float32).reshape(3, 4)
+
+    def f(t):
+        return t, nx.reshape(t, (4, 3)), nx.broadcast(nx.as_type(2, "f32"), (2, 2)), nx.iota((2, 3), axis=1), t
+
+    check(run_both(f, [x], ["f32"]), "leaf outputs")
+
+
+def test_mlp_small_config():
+    """relu(x.W1+b1).W2+b2 -> softmax -> argmax on {64,784}x{784,128}x{128,10}
+    (the CPU-sized configuration), f32 logits and exact argmax."""
+    rng = np.random.default_rng(0)
+    x = rng.uniform(0, 1, (64, 784)).astype(np.float32)
+    w1 = rng.normal(0, 0.05, (784, 128)).astype(np.float32)
+    b1 = rng.normal(0, 0.05, (128,)).astype(np.float32)
+    w2 = rng.normal(0, 0.05, (128, 10)).astype(np.float32)
+    b2 = rng.normal(0, 0.05, (10,)).astype(np.float32)
+
+    def mlp(x, w1, b1, w2, b2):
+        h = nx.max(nx.dot(x, w1) + b1, 0.0)
+        logits = nx.dot(h, w2) + b2
+        m = nx.reduce_max(logits, axes=[1], keep_axes=True)
+        e = nx.exp(logits - m)
+        p = e / nx.sum(e, axes=[1], keep_axes=True)
+        return logits, p, nx.argmax(p, axis=1)
+
+    res = run_both(mlp, [x, w1, b1, w2, b2], ["f32"] * 5)
+    # dot products of 784 terms: compare with an absolute floor scaled to the logits' size
+    assert_close(res[0][0], res[0][1], rtol=1e-5, atol=2e-6, what="logits")
+    assert_close(res[1][0], res[1][1], rtol=1e-5, atol=1e-6, what="softmax")
+    assert np.array_equal(res[2][0], res[2][1])
+    # and against the BinaryBackend-mode oracle (f64 scalar math), the oracle of this config
+    backend.set_default_backend(None)
+    host = [nx.tensor(a, "f32") for a in (x, w1, b1, w2, b2)]
+    backend.set_default_backend("b200", 0)
+    blob, _ = defn.build_program(mlp, host)
+    bb = O.run_program(blob, [h.data.raw for h in host], "binary_backend")
+    assert_close(res[0][0], bb[0][0], rtol=1e-5, atol=2e-6, what="logits vs binary_backend")
+    assert np.array_equal(res[2][0], bb[2][0])
+
+
+def test_dot_integer_exact_and_wrapping():
+    rng = np.random.default_rng(3)
+    a = rng.integers(-127, 128, (33, 300))
+    b = rng.integers(-127, 128, (300, 17))
+    check(run_both(lambda x, y: nx.dot(nx.as_type(x, "s32"), nx.as_type(y, "s32")), [a, b], ["s8", "s8"]), "s8->s32 dot")
+    check(run_both(lambda x, y: nx.dot(x, y), [a, b], ["s8", "s8"]), "s8 dot wraps to s8")
+    check(run_both(lambda x, y: nx.dot(x, [1], y, [0]), [a, b], ["s32", "s32"]), "s32 dot")
+
+
+def test_dot_layouts():
+    rng = np.random.default_rng(4)
+    a = rng.normal(0, 1, (3, 20, 12)).astype(np.float32)
+    b = rng.normal(0, 1, (3, 12, 7)).astype(np.float32)
+    c = rng.normal(0, 1, (3, 7, 12)).astype(np.float32)
+    tol = dict(rtol=1e-5, atol=1e-5)
+    for fun, arrs in [
+        (lambda x, y: nx.dot(x, [2], [0], y, [1], [0]), [a, b]),
+        (lambda x, y: nx.dot(x, [2], [0], y, [2], [0]), [a, c]),
+        (lambda x, y: nx.dot(x, [1], [0], y, [2], [0]), [np.ascontiguousarray(a.transpose(0, 2, 1)), c]),
+        (lambda x, y: nx.dot(nx.transpose(x, [0, 2, 1]), [2], [0], y, [1], [0]), [a, rng.normal(0, 1, (3, 20, 5)).astype(np.float32)]),
+        (lambda x, y: nx.dot(x, [0, 2], [], y, [0, 1], []), [a, rng.normal(0, 1, (3, 12, 9)).astype(np.float32)]),
+    ]:
+        for g, r, t in run_both(fun, arrs, ["f32", "f32"]):
+            assert_close(g, r, what="dot layout", **tol)
