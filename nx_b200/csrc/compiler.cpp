@@ -1241,10 +1241,14 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
             return su == fu || su == ru;
           };
           if (target >= 0 && (conflict || fusion < 2 || !fits(units[target]))) {
-            for (int r : reds) if (!P.mat[r]) { P.mat[r] = 1; changed = true; }
-            continue;
+            // cannot ride in the reductions' kernel: read their results from memory instead
+            bool marked = false;
+            for (int r : reds) if (!P.mat[r]) { P.mat[r] = 1; marked = true; }
+            if (marked) { changed = true; continue; }
+            target = -1;
+            conflict = true;
           }
-          if (target < 0 && fusion >= 2) {
+          if (target < 0 && fusion >= 2 && !conflict) {
             // no reduction involved: ride along with a row kernel that already reads the same data
             for (size_t ui = 0; ui < units.size() && target < 0; ++ui) {
               Unit& u = units[ui];

@@ -196,7 +196,7 @@ NXB_DEV T row_reduce(T v, void* scratch) {
     __syncthreads();
     // every warp reduces the per-warp partials itself: one barrier fewer than a broadcast
     const int NW = THREADS / 32;
-    T w = s[lane < NW ? lane : 0];
+    T w = s[lane & (NW - 1)];          // every aligned group of NW lanes folds all partials
     if (NW < 32) {
 #pragma unroll
       for (int m = NW / 2; m > 0; m >>= 1) w = Op::apply(w, shfl_xor(w, m));
