@@ -1,0 +1,56 @@
+/* CPU restatement of the bandwidth-bound configuration, for timing and for
+ * parity checks at sizes where the numpy oracle is slow.  TEST INFRASTRUCTURE
+ * ONLY: nothing in the product links or calls this file.
+ *
+ * One pass per output with no fusion across outputs, which is how the
+ * reference's evaluator walks the graph node by node
+ * (nx/lib/nx/defn/evaluator.ex:363-388): reduce_max (nx/lib/nx/binary_backend.ex:1344-1355),
+ * exp(x - max), sum (:1316-1324), Nx.logsumexp (nx/lib/nx.ex:18400-18433), the
+ * softmax division, argmax with the lowest index on ties (:1415-1431) and the
+ * chain tanh(x*0.5+0.1)*sigmoid(x), all in f32 arithmetic (XLA-style numerics;
+ * the f64 BinaryBackend mode lives in nx_oracle.py).  Rows are independent and
+ * are spread over OpenMP threads.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <omp.h>
+
+int rows_oracle_threads(void) { return omp_get_max_threads(); }
+
+void rows_oracle(const float *x, int64_t rows, int64_t cols, float *rowmax, float *e, float *sum,
+                 float *lse, float *softmax, int32_t *argmax, float *chain) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    const float *xr = x + r * cols;
+    float *er = e + r * cols, *sr = softmax + r * cols, *cr = chain + r * cols;
+    /* reduce_max: NaN propagates */
+    float m = -INFINITY;
+    int has_nan = 0;
+    for (int64_t c = 0; c < cols; ++c) {
+      if (xr[c] != xr[c]) has_nan = 1;
+      if (xr[c] > m) m = xr[c];
+    }
+    if (has_nan) m = NAN;
+    rowmax[r] = m;
+    /* exp(x - max) materialised, then its sum */
+    for (int64_t c = 0; c < cols; ++c) er[c] = expf(xr[c] - m);
+    float s = 0.f;
+    for (int64_t c = 0; c < cols; ++c) s += er[c];
+    sum[r] = s;
+    /* logsumexp: the max is replaced by 0 when it is infinite */
+    float m2 = isinf(m) ? 0.f : m;
+    float s2 = 0.f;
+    for (int64_t c = 0; c < cols; ++c) s2 += expf(xr[c] - m2);
+    lse[r] = logf(s2) + m2;
+    for (int64_t c = 0; c < cols; ++c) sr[c] = er[c] / s;
+    /* argmax: a candidate replaces the current one if strictly greater or NaN */
+    int64_t best = 0;
+    float bv = xr[0];
+    for (int64_t c = 1; c < cols; ++c) {
+      float v = xr[c];
+      if (v != v || (!(bv != bv) && v > bv)) { bv = v; best = c; }
+    }
+    argmax[r] = (int32_t)best;
+    for (int64_t c = 0; c < cols; ++c) cr[c] = tanhf(xr[c] * 0.5f + 0.1f) * (1.0f / (1.0f + expf(-xr[c])));
+  }
+}
