@@ -611,7 +611,23 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
       if (op == "add") e = xv + " + " + yv;
       else if (op == "subtract") e = xv + " - " + yv;
       else if (op == "multiply") e = xv + " * " + yv;
-      else if (op == "divide") e = xv + " / " + yv;
+      else if (op == "divide") {
+        if (mode_ == ROW && x.elem && !y.elem && ct != NXB_F64) {
+          // dividing a row by a per-row value: one reciprocal per row, one multiply per element
+          std::string rk = "rcp:" + yv;
+          auto it = row_memo_.find(rk);
+          std::string rv;
+          if (it != row_memo_.end()) rv = it->second;
+          else {
+            rv = newvar("rc");
+            stmt(false, "const float " + rv + " = 1.0f / " + yv + ";");
+            row_memo_[rk] = rv;
+          }
+          e = xv + " * " + rv;
+        } else {
+          e = xv + " / " + yv;
+        }
+      }
       else if (op == "max") e = "nx_max(" + xv + ", " + yv + ")";
       else if (op == "min") e = "nx_min(" + xv + ", " + yv + ")";
       else if (op == "pow") e = std::string(dbl ? "pow" : "powf") + "(" + xv + ", " + yv + ")";
@@ -771,7 +787,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
         bool is_max = nd.op == "argmax", high = nd.ints[0] != 0;
         std::string tpl = std::string(is_max ? "true" : "false") + ", " + (high ? "true" : "false");
         red_init[phase_] += "      ArgPair<" + RT + "> " + acc + "; " + acc + ".v = (" + RT + ")0; " + acc + ".i = -1;\n";
-        lane_sec_[phase_] += "        { ArgPair<" + RT + "> c_; c_.v = " + x.v + "; c_.i = (long long)(col0 + v); " + acc + " = arg_combine<" + tpl + ">(" + acc + ", c_); }\n";
+        lane_sec_[phase_] += "        arg_step<" + tpl + ">(" + acc + ", " + x.v + ", (long long)(col0 + v));\n";
         red_fin[phase_] += "      const " + std::string(reg_type(nd.dt)) + " " + res + " = (" + reg_type(nd.dt) + ")row_arg_reduce<" + tpl + ", " + RT + ", " + T + ">(" + acc +
                            ", scratch).i;\n";
       } else {

@@ -97,11 +97,38 @@ NXB_DEV float fast_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=
 NXB_DEV float fast_rcp(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 NXB_DEV float fast_lg2(float x) { float y; asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
-// The f32 transcendental functions are the CUDA math library's (1-2 ulp), reached
-// through these wrappers so that a tuned replacement only has to be swapped in here.
-NXB_DEV float nx_exp(float x) { return expf(x); }
-NXB_DEV float nx_sigmoid(float x) { return __fdiv_rn(1.f, 1.f + expf(-x)); }
-NXB_DEV float nx_tanh(float x) { return tanhf(x); }
+// exp(x) in ~6 instructions at ~2 ulp.  MUFU.EX2 is accurate to 2^-22 for any
+// argument, so the only error to remove is the one made when x*log2(e) is
+// rounded to f32 (its ulp grows with |x|): the rounding error of the product
+// and the representation error of the constant are recovered with two FMAs and
+// applied as a first-order correction, exp2(t + c) = exp2(t) * (1 + c ln 2).
+NXB_DEV float nx_exp(float x) {
+  const float L2E = 1.44269502162933349609375f;        // f32(log2 e)
+  const float L2E_LO = 1.925963033500665e-08f;          // log2 e - f32(log2 e)
+  float t = x * L2E;
+  float c = fmaf(x, L2E, -t);
+  c = fmaf(x, L2E_LO, c);
+  float p = fast_ex2(t);
+  float r = fmaf(p * c, 0.693147182464599609375f, p);
+  // p is 0 or inf at the ends of the range, where the correction would make a NaN
+  return (p == 0.f || p == NXB_INF) ? p : r;
+}
+// 1 / (1 + exp(-x)); rcp.approx is within 1 ulp
+NXB_DEV float nx_sigmoid(float x) { return fast_rcp(1.f + nx_exp(-x)); }
+// tanh: odd polynomial near 0 (keeps relative accuracy), 1 - 2/(exp(2|x|)+1) elsewhere
+NXB_DEV float nx_tanh(float x) {
+  const float ax = fabsf(x);
+  const float x2 = x * x;
+  float p = 0.021869488f;                 // 62/2835
+  p = fmaf(p, x2, -0.053968254f);         // -17/315
+  p = fmaf(p, x2, 0.133333333f);          // 2/15
+  p = fmaf(p, x2, -0.333333333f);         // -1/3
+  const float small = fmaf(p * x2, x, x);
+  const float e = nx_exp(2.f * ax);
+  float big = fmaf(-2.f, fast_rcp(e + 1.f), 1.f);
+  big = copysignf(big, x);
+  return (ax < 0.12f) ? small : big;
+}
 NXB_DEV float nx_log(float x) { return logf(x); }
 NXB_DEV float nx_rsqrt(float x) { return 1.0f / sqrtf(x); }
 NXB_DEV float nx_erf_inv(float x) { return erfinvf(x); }
@@ -119,8 +146,8 @@ NXB_DEV double nx_rsqrt(double x) { return 1.0 / sqrt(x); }
 NXB_DEV double nx_erf_inv(double x) { return erfinv(x); }
 
 // max/min where NaN wins (nx element_max/element_min)
-NXB_DEV float nx_max(float a, float b) { return (a != a || b != b) ? NXB_NAN : fmaxf(a, b); }
-NXB_DEV float nx_min(float a, float b) { return (a != a || b != b) ? NXB_NAN : fminf(a, b); }
+NXB_DEV float nx_max(float a, float b) { float r; asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
+NXB_DEV float nx_min(float a, float b) { float r; asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b)); return r; }
 NXB_DEV double nx_max(double a, double b) { return (a != a || b != b) ? (double)NXB_NAN : fmax(a, b); }
 NXB_DEV double nx_min(double a, double b) { return (a != a || b != b) ? (double)NXB_NAN : fmin(a, b); }
 #define NXB_INT_MINMAX(T) \
@@ -228,6 +255,19 @@ NXB_DEV bool arg_better(const ArgPair<T>& a, const ArgPair<T>& b) {
   if (an || bn) return an && (!bn || a.i > b.i);
   if (a.v != b.v) return IS_MAX ? (a.v > b.v) : (a.v < b.v);
   return TIE_HIGH ? (a.i > b.i) : (a.i < b.i);
+}
+
+// One step of a thread's own scan.  A thread visits its elements in increasing
+// index order, so "replace when strictly better (or equal, for tie_break :high),
+// or when the candidate is NaN" reproduces the order above without comparing indices.
+template <bool IS_MAX, bool TIE_HIGH, typename T>
+NXB_DEV void arg_step(ArgPair<T>& acc, T v, long long i) {
+  bool take;
+  if (TIE_HIGH) take = IS_MAX ? (v >= acc.v) : (v <= acc.v);
+  else take = IS_MAX ? (v > acc.v) : (v < acc.v);
+  take = (take && !is_nan_any(acc.v)) || is_nan_any(v) || acc.i < 0;
+  acc.v = take ? v : acc.v;
+  acc.i = take ? i : acc.i;
 }
 
 template <bool IS_MAX, bool TIE_HIGH, typename T>

@@ -107,6 +107,18 @@ def test_unary_math_f32(op):
     check(run_both(lambda t: f(t), [x], ["f32"]), op)
 
 
+@pytest.mark.parametrize("op,lo,hi", [("exp", -110.0, 89.5), ("exp", -1e-3, 1e-3), ("tanh", -0.2, 0.2), ("tanh", -1e-4, 1e-4),
+                                      ("tanh", -12.0, 12.0), ("sigmoid", -100.0, 100.0), ("sigmoid", -1e-3, 1e-3)])
+def test_hand_written_math_over_wide_ranges(op, lo, hi):
+    """exp / tanh / sigmoid are this library's own routines: sweep the ends of their ranges."""
+    x = np.linspace(lo, hi, 200001).astype(np.float32)
+    x = np.concatenate([x, np.array([0.0, -0.0, np.inf, -np.inf, np.nan], dtype=np.float32)])
+    f = getattr(nx, op)
+    for g, r, t in run_both(lambda t: f(t), [x], ["f32"]):
+        # results below the smallest normal number are flushed to zero on the device
+        assert_close(g, r, rtol=1e-5, atol=1.2e-38, what=op)
+
+
 @pytest.mark.parametrize("op", ["exp", "tanh", "sigmoid", "rsqrt", "cos", "sin", "erf", "negate", "abs"])
 def test_unary_bf16(op):
     rng = np.random.default_rng(8)
