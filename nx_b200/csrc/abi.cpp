@@ -158,7 +158,27 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         ga.ta = gs.a.trans; ga.tb = gs.b.trans;
         ga.da = gs.a.dt; ga.db = gs.b.dt; ga.dc = gs.out_dt;
         ga.epilogue = gs.epilogue;
-        launch_simt_gemm(ga, d.stream);
+        if (tc_gemm_supported(ga)) {
+          // bring both operands to K-major form, then run on the tensor cores
+          void* ta = nullptr;
+          void* tb = nullptr;
+          const size_t es = dtype_size(ga.da);
+          if (ga.ta) {
+            ta = d.alloc.alloc((size_t)(ga.batch * ga.m * ga.k) * es);
+            launch_transpose(ga.a, ta, ga.batch, ga.k, ga.m, es, d.stream);
+            ga.a = ta; ga.ta = false; ga.lda = ga.k; ga.bsa = ga.m * ga.k;
+          }
+          if (ga.tb) {
+            tb = d.alloc.alloc((size_t)(ga.batch * ga.n * ga.k) * es);
+            launch_transpose(ga.b, tb, ga.batch, ga.k, ga.n, es, d.stream);
+            ga.b = tb; ga.tb = false; ga.ldb = ga.k; ga.bsb = ga.n * ga.k;
+          }
+          launch_tc_gemm(ga, d.status_dev, d.sm_count, d.stream);
+          if (ta) d.alloc.free(ta);
+          if (tb) d.alloc.free(tb);
+        } else {
+          launch_simt_gemm(ga, d.stream);
+        }
       }
       for (size_t s = 0; s < plan.slots.size(); ++s)
         if (plan.slots[s].kind == Slot::TEMP && plan.slots[s].last_step == (int)st && ptr[s]) { d.alloc.free(ptr[s]); ptr[s] = nullptr; }
@@ -238,6 +258,7 @@ int nxb200_buffer_to_host(nxb200_buffer* buf, void* dst, size_t nbytes) {
     Device& d = nxb::device(b->device);
     if (nbytes) NXB_CUDA(cudaMemcpyAsync(dst, b->ptr, nbytes, cudaMemcpyDeviceToHost, d.stream));
     NXB_CUDA(cudaStreamSynchronize(d.stream));
+    check_device_status(d);
   });
 }
 
@@ -417,6 +438,7 @@ int nxb200_device_synchronize(int dev) {
   return guarded([&] {
     Device& d = nxb::device(dev);
     NXB_CUDA(cudaStreamSynchronize(d.stream));
+    check_device_status(d);
   });
 }
 

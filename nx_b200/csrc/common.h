@@ -103,7 +103,11 @@ struct Device {
   Allocator alloc;
   std::mutex mu;             // serialises enqueue + allocator state for this device
   int sm_count = 148;
+  // Word in mapped host memory that a kernel sets when one of its bounded waits gives up.
+  volatile int* status_host = nullptr;
+  int* status_dev = nullptr;
 };
+void check_device_status(Device& d);   // throws NXB_ERR_TIMEOUT if a kernel reported a stalled wait
 
 int device_count();
 Device& device(int id);       // makes the device current on the calling thread

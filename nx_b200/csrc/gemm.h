@@ -25,4 +25,9 @@ enum GemmEpilogue { EPI_NONE = 0 };
 // Generic CUDA-core product for every type combination (exact for integers).
 void launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);
 
+// Tensor-core product (tcgen05 + TMA).  Needs both operands K-major (ta == tb == false).
+bool tc_gemm_supported(const GemmArgs& g);
+void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStream_t stream);
+void launch_transpose(const void* in, void* out, int64_t batch, int64_t rows, int64_t cols, size_t elem_size, cudaStream_t stream);
+
 }  // namespace nxb

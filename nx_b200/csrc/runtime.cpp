@@ -162,10 +162,22 @@ Device& device(int id) {
       int sms = 148;
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, id);
       d.sm_count = sms;
+      int* host = nullptr;
+      NXB_CUDA(cudaHostAlloc((void**)&host, 64, cudaHostAllocMapped));
+      *host = 0;
+      NXB_CUDA(cudaHostGetDevicePointer((void**)&d.status_dev, host, 0));
+      d.status_host = host;
       d.stream = s;
     }
   }
   return d;
+}
+
+void check_device_status(Device& d) {
+  if (d.status_host && *d.status_host) {
+    *d.status_host = 0;
+    fail(NXB_ERR_TIMEOUT, "a kernel gave up waiting on an internal barrier (results of the last run are invalid)");
+  }
 }
 
 }  // namespace nxb

@@ -1,0 +1,108 @@
+"""Tensor-core matrix products (tcgen05 + TMA) against the CPU oracle.
+
+bf16 / f16 products accumulate in f32 on the device; the oracle accumulates the
+same bf16 values exactly and rounds once, so the stated bf16 tolerance
+(rtol 2e-2, atol 1e-2) is far wider than the observed difference.  Integer
+products must be bit-exact.
+"""
+import numpy as np
+import pytest
+
+import nx_oracle as O
+from helpers import assert_close
+from nx_b200 import backend, defn, nx
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    backend.set_default_backend("b200", 0)
+    yield
+    backend.set_default_backend(None)
+
+
+def run_both(fun, arrays, types):
+    host = []
+    for a, t in zip(arrays, types):
+        backend.set_default_backend(None)
+        host.append(nx.tensor(a, t))
+        backend.set_default_backend("b200", 0)
+    dev = [backend.backend_transfer(h) for h in host]
+    jitted = defn.jit(fun)
+    out = jitted(*dev)
+    outs = list(out) if isinstance(out, (tuple, list)) else [out]
+    blob, _ = defn.build_program(fun, host)
+    ref = O.run_program(blob, [h.data.raw for h in host], "xla_like")
+    return [(nx.to_numpy(g), r[0], r[1]) for g, r in zip(outs, ref)]
+
+
+SHAPES = [(128, 256, 64), (1, 8, 8), (130, 260, 72), (257, 513, 136), (64, 1000, 4096), (384, 768, 512),
+          (1024, 1024, 1024)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_bf16_dot(m, n, k):
+    rng = np.random.default_rng(2)
+    a = rng.normal(0, 1 / np.sqrt(k), (m, k)).astype(np.float32)
+    b = rng.normal(0, 1, (k, n)).astype(np.float32)
+    bt = np.ascontiguousarray(b.T)
+    # b given as {k,n} (reduction index strided) and as {n,k} (contiguous)
+    for fun, arrs in [(lambda x, y: nx.dot(x, y), [a, b]), (lambda x, y: nx.dot(x, [1], y, [1]), [a, bt])]:
+        (g, r, t), = run_both(fun, arrs, ["bf16", "bf16"])
+        assert t == ("bf", 16)
+        assert_close(g, r, rtol=2e-2, atol=1e-2, what=f"bf16 dot {m}x{n}x{k}")
+        # much tighter than the stated tolerance: at most one bf16 ulp (2^-8 relative) away
+        assert_close(g, r, rtol=2 ** -7, atol=2 ** -9, what=f"bf16 dot {m}x{n}x{k} (1 ulp)")
+
+
+def test_bf16_dot_uses_tensor_cores():
+    prog = defn.compile(lambda x, y: nx.dot(x, y), [defn.template((256, 512), "bf16"), defn.template((512, 256), "bf16")]).program
+    assert "gemm" in prog.describe()
+
+
+def test_bf16_batched_dot():
+    rng = np.random.default_rng(3)
+    a = rng.normal(0, 0.2, (5, 200, 72)).astype(np.float32)
+    b = rng.normal(0, 1, (5, 72, 300)).astype(np.float32)
+    (g, r, t), = run_both(lambda x, y: nx.dot(x, [2], [0], y, [1], [0]), [a, b], ["bf16", "bf16"])
+    assert g.shape == (5, 200, 300)
+    assert_close(g, r, rtol=2 ** -7, atol=2 ** -9, what="batched bf16 dot")
+
+
+def test_f16_dot():
+    rng = np.random.default_rng(4)
+    a = rng.normal(0, 0.1, (200, 264)).astype(np.float32)
+    b = rng.normal(0, 1, (264, 136)).astype(np.float32)
+    (g, r, t), = run_both(lambda x, y: nx.dot(x, y), [a, b], ["f16", "f16"])
+    assert_close(g, r, rtol=2 ** -10, atol=2 ** -11, what="f16 dot")
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (33, 50, 304), (300, 520, 4096)])
+def test_s8_dot_exact(m, n, k):
+    rng = np.random.default_rng(5)
+    a = rng.integers(-127, 128, (m, k))
+    b = rng.integers(-127, 128, (n, k))
+    res = run_both(lambda x, y: (nx.dot(nx.as_type(x, "s32"), [1], nx.as_type(y, "s32"), [1]), nx.dot(x, [1], y, [1])),
+                   [a, b], ["s8", "s8"])
+    for g, r, t in res:
+        assert np.array_equal(g, r), f"s8 dot {m}x{n}x{k} -> {t}"
+
+
+def test_quantised_linear():
+    """y = x . (as_type(W, f32) * scale)^T with W s8 {N,K}, per-output-channel f32 scales, x bf16 {M,K}."""
+    rng = np.random.default_rng(3)
+    n, k = 704, 512
+    w = rng.integers(-127, 128, (n, k))
+    scale = rng.uniform(1e-3, 2e-2, (n,)).astype(np.float32)
+    for m in (1, 16, 256):
+        x = rng.normal(0, 1, (m, k)).astype(np.float32)
+
+        def linear(x, w, s):
+            wdq = nx.as_type(w, "f32") * nx.reshape(s, (n, 1))
+            return nx.dot(x, [1], wdq, [1])
+
+        (g, r, t), = run_both(linear, [x, w, scale], ["bf16", "s8", "f32"])
+        assert t == ("f", 32) and g.shape == (m, n)
+        # f32 sums of 512 products of size ~1: the absolute floor is 1e-5 of the output's scale
+        assert_close(g, r, rtol=1e-5, atol=1e-5 * float(np.abs(r).max()), what=f"dequant linear M={m}")
