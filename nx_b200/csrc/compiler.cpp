@@ -18,6 +18,8 @@
 // All shapes are compile-time constants of the generated source (programs are
 // specialised per argument signature, as in the reference).
 #include <algorithm>
+#include <cstdio>
+#include <cstdlib>
 #include <functional>
 #include <set>
 #include <sstream>
@@ -683,8 +685,9 @@ void KernelBuilder::emit_store(int n) {
   Val v = value(n, idx);
   std::string p = param(nd.slot);
   const std::string S = storage_type(nd.dt), Rt = reg_type(nd.dt);
-  auto st = cstrides(nd.shape);
-  Aff addr = aff_const(nv_, 0);
+  // a piece of a concatenate writes into its parent's buffer with the parent's strides
+  auto st = nd.out_strides.empty() ? cstrides(nd.shape) : nd.out_strides;
+  Aff addr = aff_const(nv_, nd.out_offset);
   for (size_t j = 0; j < idx.size(); ++j) {
     addr.c += idx[j].c * st[j];
     for (int q = 0; q < nv_; ++q) addr.k[q] += idx[j].k[q] * st[j];
@@ -694,7 +697,9 @@ void KernelBuilder::emit_store(int n) {
     row_sec_[phase_] += "        if (tid == 0) st1<" + S + ">(" + p + " + " + affstr(addr, false) + ", " + v.v + ");\n";
     return;
   }
-  if (V_ > 1) {
+  bool aligned = addr.c % V_ == 0 && addr.k[nv_ - 1] == 1;
+  for (int j = 0; j < nv_ - 1; ++j) if (F_[j] != 1 && addr.k[j] % V_ != 0) aligned = false;
+  if (V_ > 1 && aligned) {
     std::string sv = newvar("st");
     pre_sec_[phase_] += "          " + Rt + " " + sv + "[" + std::to_string(V_) + "];\n";
     lane_sec_[phase_] += "        " + sv + "[v] = " + v.v + ";\n";
@@ -1010,6 +1015,21 @@ struct Planner {
     return false;
   }
 
+  // Number of buffer boundaries (dot, concatenate) on the longest path from the inputs.
+  // Members of one fused kernel must share it: then no path between two members can
+  // leave the kernel through a boundary and come back, i.e. no dependency cycle.
+  std::vector<int> depth_memo;
+  int depth(int n) {
+    if (depth_memo.size() != g.nodes.size()) depth_memo.assign(g.nodes.size(), -1);
+    if (depth_memo[n] >= 0) return depth_memo[n];
+    int d = 0;
+    for (int a : g.nodes[n].args) {
+      const std::string& op = g.nodes[a].op;
+      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate") ? 1 : 0));
+    }
+    return depth_memo[n] = d;
+  }
+
   bool is_leaf(int n) const {
     const std::string& op = g.nodes[n].op;
     return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate";
@@ -1091,6 +1111,32 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       }
     }
   }
+  // concatenate: every input becomes a "piece" node that is written straight into its
+  // slice of the result (inputs converted to the result type, exla/lib/exla/defn.ex:1659-1668)
+  {
+    size_t n0 = g.nodes.size();
+    for (size_t n = 0; n < n0; ++n) {
+      if (g.nodes[n].op != "concatenate") continue;
+      const int axis = (int)g.nodes[n].ints.at(0);
+      const std::vector<int64_t> pst = cstrides(g.nodes[n].shape);
+      int64_t off = 0;
+      std::vector<int> pieces;
+      for (int a : std::vector<int>(g.nodes[n].args)) {
+        Node c;
+        c.op = g.nodes[a].dt == g.nodes[n].dt ? "copy" : "as_type";
+        c.dt = g.nodes[n].dt;
+        c.shape = g.nodes[a].shape;
+        c.args = {a};
+        c.piece_of = (int)n;
+        c.out_strides = pst;
+        c.out_offset = off * pst[axis];
+        off += g.nodes[a].shape[axis];
+        g.nodes.push_back(c);
+        pieces.push_back((int)g.nodes.size() - 1);
+      }
+      g.nodes[n].args = pieces;
+    }
+  }
   const int N = (int)g.nodes.size();
 
   // liveness + op support
@@ -1134,6 +1180,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     if (!nd.live) continue;
     if (nd.op == "dot") { P.mat[n] = 1; dots.push_back(n); }
     if (nd.op == "concatenate") { P.mat[n] = 1; concats.push_back(n); }
+    if (nd.piece_of >= 0) P.mat[n] = 1;
   }
   // dot operands: decided by the GEMM planner (it may accept a transposed view directly)
   std::map<int, GemmSpec> gemm_of;
@@ -1205,6 +1252,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
             for (size_t j = 0; j < i; ++j) {
               if (!rs[i].perm.empty() || !rs[j].perm.empty()) continue;
               if (rs[i].F != rs[j].F || rs[i].k != rs[j].k) continue;
+              if (P.depth(rs[i].node) != P.depth(rs[j].node)) continue;
               bool share = rs[i].reds.count(rs[j].node) || rs[j].reds.count(rs[i].node);
               if (!share)
                 for (int l : rs[i].leaves) if (rs[j].leaves.count(l) && strip_units(g.nodes[l].shape) == strip_units(rs[i].F)) { share = true; break; }
@@ -1251,12 +1299,13 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           }
           auto fits = [&](const Unit& u) {
             if (!u.perm.empty()) return false;
+            if (P.depth(u.reduces[0]) != P.depth(n)) return false;
             std::vector<int64_t> su = strip_units(nd.shape), fu = strip_units(u.F);
             std::vector<int64_t> ru(u.F.begin(), u.F.end() - u.k);
             ru = strip_units(ru);
             return su == fu || su == ru;
           };
-          if (target >= 0 && (conflict || fusion < 2 || !fits(units[target]))) {
+          if (target >= 0 && (conflict || fusion < 2 || nd.piece_of >= 0 || !fits(units[target]))) {
             // cannot ride in the reductions' kernel: read their results from memory instead
             bool marked = false;
             for (int r : reds) if (!P.mat[r]) { P.mat[r] = 1; marked = true; }
@@ -1264,11 +1313,12 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
             target = -1;
             conflict = true;
           }
-          if (target < 0 && fusion >= 2 && !conflict) {
+          if (target < 0 && fusion >= 2 && !conflict && nd.piece_of < 0) {
             // no reduction involved: ride along with a row kernel that already reads the same data
             for (size_t ui = 0; ui < units.size() && target < 0; ++ui) {
               Unit& u = units[ui];
               if (u.kind != Unit::ROW || !u.perm.empty() || strip_units(nd.shape) != strip_units(u.F)) continue;
+              if (P.depth(u.reduces[0]) != P.depth(n)) continue;
               std::set<int> uleaves;
               for (int r : u.reduces) { auto& ri = rs[ridx[r]]; uleaves.insert(ri.leaves.begin(), ri.leaves.end()); }
               bool sub = !leaves.empty();
@@ -1280,9 +1330,10 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           else {
             // elementwise kernel; merge with an existing one of the same shape that shares an input
             int merged = -1;
-            for (size_t ui = 0; ui < units.size() && merged < 0 && fusion >= 2; ++ui) {
+            for (size_t ui = 0; ui < units.size() && merged < 0 && fusion >= 2 && nd.piece_of < 0; ++ui) {
               Unit& u = units[ui];
-              if (u.kind != Unit::EW || u.F != nd.shape) continue;
+              if (u.kind != Unit::EW || u.F != nd.shape || g.nodes[u.stores[0]].piece_of >= 0) continue;
+              if (P.depth(u.stores[0]) != P.depth(n)) continue;
               for (int s : u.stores) {
                 std::set<int> s2, l2, r2;
                 P.cone(s, s2, l2, r2, true);
@@ -1312,6 +1363,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       for (int n = 0; n < N; ++n) {
         Node& nd = g.nodes[n];
         if (!nd.live || !P.mat[n] || nd.slot >= 0) continue;
+        if (nd.piece_of >= 0) { nd.slot = g.nodes[nd.piece_of].slot; continue; }
         if (out_index.count(n)) {
           nd.slot = P.new_slot(Slot::OUTPUT, n, out_index[n]);
           pl.output_slots[out_index[n]] = nd.slot;
@@ -1327,12 +1379,6 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         u.kind = Unit::GEMM;
         u.gemm_node = n;
         units.push_back(u);
-      }
-      for (int n : concats) {
-        // one copy kernel per input, each writing its slice of the result
-        const Node& nd = g.nodes[n];
-        (void)nd;
-        fail(NXB_ERR_UNSUPPORTED, "concatenate is not implemented yet");
       }
 
       // ---- order units by data dependence ---------------------------------------------------------
@@ -1368,7 +1414,9 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       {
         size_t U = units.size();
         std::vector<char> done(U, 0);
-        std::set<int> ready;   // slots available
+        std::set<int> ready;   // slots whose every writer has been scheduled
+        std::map<int, int> writers;
+        for (auto& u : units) for (int w : u.writes) writers[w]++;
         for (auto& sl : pl.slots) if (sl.kind == Slot::PARAM || sl.kind == Slot::LITERAL) ready.insert((int)(&sl - &pl.slots[0]));
         for (size_t round = 0; round < U; ++round) {
           bool progress = false;
@@ -1379,7 +1427,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
             if (!ok) continue;
             done[i] = 1;
             order.push_back((int)i);
-            for (int w : units[i].writes) ready.insert(w);
+            for (int w : units[i].writes) if (--writers[w] == 0) ready.insert(w);
             progress = true;
           }
           if (!progress) break;
@@ -1413,6 +1461,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       break;   // success
     } catch (const FusionError& e) {
       if (fusion == 1) fail(NXB_ERR_UNSUPPORTED, std::string("cannot compile this graph: ") + e.what());
+      if (getenv("NXB200_DEBUG")) fprintf(stderr, "[nxb200] fused plan rejected: %s\n", e.what());
       // retry without cross-reduction fusion
       for (int n = 0; n < N; ++n) if (g.nodes[n].live && is_reduce(g.nodes[n])) P.mat[n] = 1;
     }

@@ -17,6 +17,13 @@ struct Node {
   int alias = -1;        // node whose buffer this node shares (metadata, contiguous reshape)
   int slot = -1;         // buffer slot when the value lives in global memory
   bool live = false;
+  // A piece of a concatenate result: written into the parent's buffer at this element
+  // offset with these strides instead of densely into a buffer of its own.
+  int piece_of = -1;
+  int64_t out_offset = 0;
+  std::vector<int64_t> out_strides;
+  // dot only: node holding a per-output-column f32 factor applied to the product (-1: none)
+  int scale_arg = -1;
 };
 
 struct Graph {

@@ -359,8 +359,8 @@ def as_type(x, type):
 
 def select(pred, on_true, on_false):
     """nx/lib/nx.ex:7782-7830."""
+    type = _binary_type(_num(on_true), _num(on_false))
     pred, on_true, on_false = (_as_operand(_num(v)) for v in (pred, on_true, on_false))
-    type = T.merge(on_true.type, on_false.type)
     shape = binary_broadcast(on_true.shape, on_false.shape) if pred.shape == () else pred.shape
     for v in (on_true, on_false):
         if binary_broadcast(v.shape, shape) != shape:

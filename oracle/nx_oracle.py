@@ -67,18 +67,20 @@ def type_merge(a, b):
 
 def bf16_round_rne(a):
     """f32 -> nearest-even bf16, returned widened to f32 (XLA convert)."""
-    a = np.ascontiguousarray(a, dtype=np.float32)
+    shape = np.shape(a)
+    a = np.ascontiguousarray(a, dtype=np.float32).reshape(-1)
     u = a.view(np.uint32)
     r = (u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) & np.uint32(0xFFFF0000)
     out = r.view(np.float32)
-    return np.where(np.isnan(a), np.float32(np.nan), out).astype(np.float32)
+    return np.where(np.isnan(a), np.float32(np.nan), out).astype(np.float32).reshape(shape)
 
 
 def bf16_truncate(a):
     """f32 -> bf16 by dropping the low 16 bits (nx/lib/nx/floating.ex:60-64)."""
-    a = np.ascontiguousarray(a, dtype=np.float32)
+    shape = np.shape(a)
+    a = np.ascontiguousarray(a, dtype=np.float32).reshape(-1)
     out = (a.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
-    return np.where(np.isnan(a), np.float32(np.nan), out).astype(np.float32)
+    return np.where(np.isnan(a), np.float32(np.nan), out).astype(np.float32).reshape(shape)
 
 
 def decode(raw, t, shape):

@@ -1,0 +1,109 @@
+"""The five configurations on the GPU at reduced sizes, against the CPU oracle,
+plus size-independent properties at larger sizes."""
+import numpy as np
+import pytest
+
+import nx_oracle as O
+from helpers import assert_close
+from nx_b200 import backend, configs, defn, nx
+
+pytestmark = pytest.mark.gpu
+BF16 = dict(rtol=2e-2, atol=1e-2)
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    backend.set_default_backend("b200", 0)
+    yield
+    backend.set_default_backend(None)
+
+
+def run_both(fun, inputs, mode="xla_like"):
+    host = []
+    for a, t in inputs:
+        backend.set_default_backend(None)
+        host.append(nx.tensor(a, t))
+        backend.set_default_backend("b200", 0)
+    dev = [backend.backend_transfer(h) for h in host]
+    out = defn.jit(fun)(*dev)
+    outs = list(out) if isinstance(out, (tuple, list)) else [out]
+    blob, _ = defn.build_program(fun, host)
+    ref = O.run_program(blob, [h.data.raw for h in host], mode)
+    return [(nx.to_numpy(g), r[0], r[1]) for g, r in zip(outs, ref)]
+
+
+def test_concatenate_and_slices():
+    rng = np.random.default_rng(20)
+    a = rng.normal(0, 1, (3, 5, 8)).astype(np.float32)
+    b = rng.normal(0, 1, (3, 2, 8)).astype(np.float32)
+    c = rng.integers(-5, 5, (3, 5, 4))
+
+    def f(a, b, c):
+        return (nx.concatenate([a, b], axis=1), nx.concatenate([a, c, a * 2.0], axis=2),
+                nx.concatenate([nx.negate(nx.slice_along_axis(a, 4, 4, axis=2)), nx.slice_along_axis(a, 0, 4, axis=2)], axis=2) + 1.0)
+
+    for g, r, t in run_both(f, [(a, "f32"), (b, "f32"), (c, "s32")]):
+        assert_close(g, r, rtol=1e-6, atol=0, what="concatenate")
+
+
+def test_rope_tables_and_rotation():
+    rng = np.random.default_rng(21)
+    t = rng.normal(0, 1, (2, 3, 16, 8)).astype(np.float32)
+
+    def f(t):
+        cos, sin = configs.rope_tables(16, 8, 10000.0, "f32")
+        return configs.rope(t, cos, sin), cos, sin
+
+    for g, r, _ in run_both(f, [(t, "f32")]):
+        assert_close(g, r, rtol=1e-5, atol=2e-6, what="rope")
+
+
+def test_rms_norm_bf16():
+    rng = np.random.default_rng(22)
+    x = rng.normal(0, 1, (4, 33, 512)).astype(np.float32)
+    gain = (1 + rng.normal(0, 0.02, (512,))).astype(np.float32)
+    (g, r, t), = run_both(lambda x, g: configs.rms_norm(x, g), [(x, "bf16"), (gain, "bf16")])
+    assert_close(g, r, what="rms_norm", **BF16)
+
+
+@pytest.mark.parametrize("batch,seq,hidden,heads,inter", [(2, 16, 64, 4, 176), (1, 64, 256, 4, 344), (2, 128, 512, 8, 688)])
+def test_decoder_block(batch, seq, hidden, heads, inter):
+    block = configs.make_decoder_block(n_heads=heads)
+    inputs = configs.decoder_inputs(batch=batch, seq=seq, hidden=hidden, inter=inter)
+    (g, r, t), = run_both(block, inputs)
+    assert t == ("bf", 16) and g.shape == (batch, seq, hidden)
+    assert np.isfinite(g).all()
+    assert_close(g, r, what="decoder block", **BF16)
+
+
+def test_dense_bias_gelu_reduced():
+    inputs = configs.dense_inputs(m=384, n=512, k=1024)
+    (g, r, t), = run_both(configs.dense_bias_gelu, inputs)
+    assert_close(g, r, what="dense+bias+gelu", **BF16)
+
+
+def test_batched_dot_reduced():
+    (g, r, t), = run_both(configs.batched_dot, configs.batched_inputs(batch=6, m=256, k=128, n=512))
+    assert_close(g, r, what="batched dot", **BF16)
+
+
+@pytest.mark.parametrize("m", [1, 16, 256])
+def test_quantised_linear_reduced(m):
+    f_in, i_in = configs.quantised_inputs(m=m, n=1024, k=512)
+    (g, r, t), = run_both(configs.quantised_linear, f_in)
+    assert t == ("f", 32)
+    assert_close(g, r, rtol=1e-5, atol=1e-5 * float(np.abs(r).max()), what=f"quantised linear M={m}")
+    (gi, ri, ti), = run_both(configs.integer_linear, i_in)
+    assert ti == ("s", 32) and np.array_equal(gi, ri)
+
+
+def test_softmax_rows_sum_to_one_at_full_width():
+    """Size-independent property at the full row width: softmax rows sum to 1,
+    exp(x-max) has a 1 at the argmax, logsumexp = log(sum) + max."""
+    x = configs.fused_rows_input(rows=64, cols=32768)
+    m, e, s, lse, p, am, chain = [nx.to_numpy(t) for t in defn.jit(configs.fused_rows)(nx.tensor(x))]
+    np.testing.assert_allclose(p.sum(axis=1, dtype=np.float64), 1.0, rtol=1e-5)
+    assert np.array_equal(am, x.argmax(axis=1))
+    assert np.all(e[np.arange(64), am] == 1.0)
+    np.testing.assert_allclose(lse, np.log(s.astype(np.float64)) + m, rtol=1e-6)
+    assert np.array_equal(m, x.max(axis=1))
