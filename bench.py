@@ -1,18 +1,26 @@
-"""Benchmark of the hot path: the bandwidth-bound fused defn.
+"""Benchmark of the hot path.
 
-Workload (the second configuration of BASELINE.json): logits f32 {8192,32768}
-normal(0,2) from seed 1; ONE defn that returns row max, exp(x-max), its sum,
-logsumexp, softmax, argmax per row and the chain tanh(x*0.5+0.1)*sigmoid(x).
-The compiler turns it into a single row kernel, so one step = one launch that
-reads x once (1 GiB) and writes the three full-size outputs (3 GiB) plus four
-per-row vectors.  ``value`` = those algorithmic bytes / device time.
+Headline workload (the second configuration of BASELINE.json, the one the
+metric "fused-op HBM GB/s" is quoted on): logits f32 {8192,32768} normal(0,2)
+from seed 1; ONE defn returning row max, exp(x-max), its sum, logsumexp,
+softmax, argmax per row and the chain tanh(x*0.5+0.1)*sigmoid(x).  The compiler
+turns it into a single row kernel, so one step = one launch that reads x once
+(1 GiB) and writes the three full-size outputs (3 GiB) plus four per-row
+vectors.  ``value`` = those algorithmic bytes / device time, whole job.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--all-configs]
 
-N > 1 runs one replica per GPU (the configuration has no cross-device
-exchange; "replicas only"), launched by torch.distributed.run, and reports the
-aggregate.  ``--impl reference`` times the CPU restatement of the same graph
-(oracle/rows_oracle.c, all host threads) on a bounded sample of rows.
+N > 1 (launched by torch.distributed.run, one rank per GPU): the headline
+configuration has no cross-device exchange, so it runs as independent replicas
+("replicas only", weak scaling) and the aggregate is reported.  The sharded
+configuration (the decoder block) is timed in the same run and reported under
+``"decoder"``: batch data-parallel over N GPUs (no collective) and, for N > 1,
+tensor-parallel linears with an NCCL all-reduce after each row-parallel product.
+
+``--impl reference`` times the CPU restatement of the same graph
+(oracle/rows_oracle.c, all host threads).  ``--all-configs`` adds device-time
+measurements of the other configurations (MLP, dense dot, batched dot,
+quantised linear) under ``"configs"``.
 """
 from __future__ import annotations
 
@@ -34,10 +42,13 @@ sys.path.insert(0, ROOT)
 ROWS, COLS = 8192, 32768
 SEED = 1
 METRIC, UNIT = "fused-op HBM GB/s", "GB/s"
+WORKLOAD = "fused row defn f32 {%d,32768} (max, exp, sum, logsumexp, softmax, argmax, tanh*sigmoid chain)"
 
-# DRAM bytes per launch of the row kernel measured once under ncu
-# (dram__bytes_read.sum + dram__bytes_write.sum; see profiles/).  None until captured.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM bytes per launch of the row kernel from one ncu capture of a 1024-row case
+# (dram__bytes_read.sum + dram__bytes_write.sum = 134.3 MB + 343.8 MB), scaled by the
+# row count; reads match the algorithmic 128 MiB exactly, writes are below the
+# algorithmic 384 MiB because the last ~59 MB were still dirty in L2 when the kernel ended.
+NCU_TRAFFIC_BYTES_PER_1024_ROWS = 134_280_448 + 343_771_136
 
 
 def algorithmic_bytes(rows, cols):
@@ -46,30 +57,12 @@ def algorithmic_bytes(rows, cols):
     return full * 4 + rows * 4 * 4          # x, exp, softmax, chain; max, sum, lse (f32) + argmax (s32)
 
 
-def fused_rows(x):
-    from nx_b200 import nx
-    m = nx.reduce_max(x, axes=[1], keep_axes=True)
-    e = nx.exp(x - m)
-    s = nx.sum(e, axes=[1], keep_axes=True)
-    return (nx.squeeze(m, [1]), e, nx.squeeze(s, [1]), nx.logsumexp(x, axes=[1]), e / s,
-            nx.argmax(x, axis=1), nx.tanh(x * 0.5 + 0.1) * nx.sigmoid(x))
-
-
-def make_input(rows, cols, seed):
-    rng = np.random.default_rng(seed)
-    out = np.empty((rows, cols), dtype=np.float32)
-    step = max(1, (1 << 24) // cols)
-    for r in range(0, rows, step):
-        out[r:r + step] = rng.standard_normal((min(step, rows - r), cols), dtype=np.float32) * 2.0
-    return out
-
-
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return float(d["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+        return d, "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
 class ClockSampler:
@@ -81,7 +74,7 @@ class ClockSampler:
         self.rows, self.proc = [], None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -95,7 +88,7 @@ class ClockSampler:
     def stop(self):
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
@@ -109,6 +102,8 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
+# ---- CPU arm -----------------------------------------------------------------------------
+
 def load_rows_oracle():
     path = os.path.join(ROOT, "oracle", "librows_oracle.so")
     if not os.path.exists(path):
@@ -120,46 +115,158 @@ def load_rows_oracle():
     return lib
 
 
-def cpu_rows(lib, x):
-    rows, cols = x.shape
-    outs = [np.empty(rows, np.float32), np.empty((rows, cols), np.float32), np.empty(rows, np.float32),
-            np.empty(rows, np.float32), np.empty((rows, cols), np.float32), np.empty(rows, np.int32),
-            np.empty((rows, cols), np.float32)]
-    t0 = time.perf_counter()
-    lib.rows_oracle(x.ctypes.data, rows, cols, *[o.ctypes.data for o in outs])
-    return time.perf_counter() - t0, outs
+class CpuRows:
+    """The CPU restatement with its output buffers allocated (and touched) once."""
+
+    def __init__(self, rows, cols):
+        self.lib = load_rows_oracle()
+        self.outs = [np.zeros(rows, np.float32), np.zeros((rows, cols), np.float32), np.zeros(rows, np.float32),
+                     np.zeros(rows, np.float32), np.zeros((rows, cols), np.float32), np.zeros(rows, np.int32),
+                     np.zeros((rows, cols), np.float32)]
+
+    def __call__(self, x):
+        t0 = time.perf_counter()
+        self.lib.rows_oracle(x.ctypes.data, x.shape[0], x.shape[1], *[o.ctypes.data for o in self.outs])
+        return time.perf_counter() - t0
 
 
-def cpu_baseline(x_sample):
-    lib = load_rows_oracle()
-    cpu_rows(lib, x_sample[:8])                      # page in / spin up the thread pool
-    dt, _ = cpu_rows(lib, x_sample)
-    gbs = algorithmic_bytes(*x_sample.shape) / dt / 1e9
-    return {"value": round(gbs, 3), "unit": UNIT, "cores": lib.rows_oracle_threads(), "kind": "port",
-            "sample": f"{x_sample.shape[0]} of {ROWS} rows x {COLS} cols, one pass, {dt:.2f} s"}
+def cpu_baseline(x):
+    """Oracle port on this box's host cores: the full workload, three passes (a few seconds)."""
+    f = CpuRows(*x.shape)
+    f(x[:64])
+    times = [f(x) for _ in range(3)]
+    dt = min(times)
+    return {"value": round(algorithmic_bytes(*x.shape) / dt / 1e9, 3), "unit": UNIT, "cores": f.lib.rows_oracle_threads(),
+            "kind": "port", "sample": f"all {x.shape[0]} rows x {x.shape[1]} cols, best of 3 passes ({sum(times):.1f} s total)"}
 
 
-def run_reference(args, rank, world):
+def run_reference(args, rank):
     if rank != 0:
         return
-    lib = load_rows_oracle()
-    rows = 1024                                        # bounded sample: 0.5 GiB of algorithmic traffic per step
-    x = make_input(rows, COLS, SEED)
+    from nx_b200 import configs
+    rows = ROWS
+    x = configs.fused_rows_input(rows, COLS, SEED)
+    f = CpuRows(rows, COLS)
     for _ in range(max(1, min(args.warmup, 2))):
-        cpu_rows(lib, x[:64])
-    times = [cpu_rows(lib, x)[0] for _ in range(args.steps)]
+        f(x[:256])
+    steps = max(1, min(args.steps, 10))             # each step is the whole workload (under a second per step)
+    times = [f(x) for _ in range(steps)]
     dt = sum(times) / len(times)
     gbs = algorithmic_bytes(rows, COLS) / dt / 1e9
+    cores = f.lib.rows_oracle_threads()
     line = {"impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3 * ROWS / rows, 3),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "fused row defn f32 {8192,32768} (max, exp, sum, logsumexp, softmax, argmax, tanh*sigmoid chain)",
-                       "sample_rows": rows},
-            "cpu_baseline": {"value": round(gbs, 3), "unit": UNIT, "cores": lib.rows_oracle_threads(), "kind": "port",
-                             "sample": f"{rows} of {ROWS} rows per step; ms_per_step is scaled to the full {ROWS} rows"},
+            "steps": steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD % rows, "seed": SEED,
+                       "note": "CPU restatement of the reference's evaluator path (one pass per output), all host threads"},
+            "cpu_baseline": {"value": round(gbs, 3), "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"whole workload per step, {steps} steps"},
             "e2e": {"value": round(gbs, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
+
+
+# ---- device helpers ------------------------------------------------------------------------
+
+class Timer:
+    def __init__(self, lib, device):
+        self.lib, self.device = lib, device
+
+    def time(self, fn, steps, warmup=3):
+        from nx_b200 import nif
+        for _ in range(warmup):
+            fn()
+        nif.check(self.lib.nxb200_device_synchronize(self.device))
+        nif.check(self.lib.nxb200_timer_begin(self.device))
+        for _ in range(steps):
+            fn()
+        ms = C.c_float()
+        nif.check(self.lib.nxb200_timer_end(self.device, C.byref(ms)))
+        return ms.value / steps
+
+
+def device_inputs(inputs):
+    from nx_b200 import nx
+    return [nx.tensor(a, t) for a, t in inputs]
+
+
+def time_program(timer, fun, inputs, device, steps=10):
+    from nx_b200 import defn
+    dev = device_inputs(inputs)
+    prog = defn.compile(fun, [defn.template(a.shape, t) for a, t in inputs], device=device).program
+    outs = prog.run(dev, device)
+    return timer.time(lambda: prog.run_into(dev, outs, device), steps), prog
+
+
+def decoder_section(timer, device, rank, world, dist, torch):
+    """Decoder block tokens/s: single GPU, batch data-parallel and tensor-parallel."""
+    from nx_b200 import backend as B, configs, defn, nx, sharding
+    block = configs.make_decoder_block()
+    batch, seq = 8, 2048
+    inputs = configs.decoder_inputs(batch=batch, seq=seq)
+    out = {"tokens_per_step": batch * seq, "flops_per_token": 438.4e6,
+           "note": "bf16 {8,2048,4096}, 32 heads, SwiGLU 11008; FLOP count uses full (unmasked) attention"}
+
+    def sync_max(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def run_sharded(mesh, shardings, label):
+        def shard(a, sh):
+            for dim, axes in sh.items():
+                n = mesh.shape[axes[0]]
+                c = mesh.coords(rank)[axes[0]]
+                step = a.shape[dim] // n
+                a = np.take(a, range(c * step, (c + 1) * step), axis=dim)
+            return np.ascontiguousarray(a)
+        local = [(shard(a, sh), t) for (a, t), sh in zip(inputs, shardings)]
+        blob, _, _ = sharding.partition(block, mesh, shardings, [defn.template(a.shape, t) for a, t in local], rank)
+        prog = defn.Program(blob)
+        dev = device_inputs(local)
+        outs = prog.run(dev, device)
+        if dist is not None:
+            dist.barrier()
+        ms = sync_max(timer.time(lambda: prog.run_into(dev, outs, device), 5, warmup=2))
+        out[label] = {"ms_per_step": round(ms, 3), "tokens_per_s": round(batch * seq / ms * 1e3),
+                      "tflops": round(438.4e6 * batch * seq / ms / 1e9, 1), "launches_per_step": prog.launch_count()}
+
+    if world == 1:
+        run_sharded(sharding.Mesh("one", (1,)), [{}] * 10, "single")
+    else:
+        run_sharded(sharding.Mesh("dp", (world,)), [{0: [0]}] + [{}] * 9, f"dp{world}")
+        mesh = sharding.Mesh("tp", (world,))
+        ex = sharding.torch_exchange()
+        sharding.init_tensor_parallel_group(mesh, 0, rank, device, ex)
+        tp = [{}, {1: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {}, {}]
+        run_sharded(mesh, tp, f"tp{world}")
+    return out
+
+
+def other_configs(timer, device, pk):
+    from nx_b200 import configs
+    res = {}
+    ms, prog = time_program(timer, configs.mlp, configs.mlp_inputs(), device, steps=50)
+    res["mlp_f32_64x784x128x10"] = {"ms": round(ms, 4), "launches": prog.launch_count()}
+    ms, prog = time_program(timer, configs.dense_bias_gelu, configs.dense_inputs(), device)
+    tf = 2 * 8192 ** 3 / ms / 1e9
+    res["dense_bf16_8192^3_bias_gelu"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / pk["bf16_tflops"], 3),
+                                           "plan": prog.describe().strip().split("\n")}
+    ms, prog = time_program(timer, lambda a, b: configs.nx.dot(a, [1], b, [1]), [configs.dense_inputs()[0], configs.dense_inputs()[0]], device)
+    tf = 2 * 8192 ** 3 / ms / 1e9
+    res["dot_bf16_8192^3_kmajor"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / pk["bf16_tflops"], 3)}
+    ms, prog = time_program(timer, configs.batched_dot, configs.batched_inputs(), device)
+    byt = (2 * 64 * 2048 * 128 + 64 * 2048 * 2048) * 2
+    res["batched_bf16_64x2048x128x2048"] = {"ms": round(ms, 4), "tflops": round(2 * 64 * 2048 * 2048 * 128 / ms / 1e9, 1),
+                                            "gbs": round(byt / ms / 1e6, 1), "frac_of_measured_hbm": round(byt / ms / 1e6 / pk["hbm_gbs"], 3)}
+    for m in (1, 16, 256, 4096):
+        f_in, i_in = configs.quantised_inputs(m=m)
+        ms, prog = time_program(timer, configs.quantised_linear, f_in, device)
+        byt = 11008 * 4096 + 11008 * 4 + m * 4096 * 2 + m * 11008 * 4
+        res[f"quantised_linear_M{m}"] = {"ms": round(ms, 4), "tflops": round(2 * m * 4096 * 11008 / ms / 1e9, 2), "gbs": round(byt / ms / 1e6, 1)}
+    return res
 
 
 def main():
@@ -171,12 +278,14 @@ def main():
     ap.add_argument("--rows", type=int, default=ROWS, help="reduced row count (profiling captures only)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-decoder", action="store_true")
+    ap.add_argument("--all-configs", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
-        return run_reference(args, rank, world)
+        return run_reference(args, rank)
     args.warmup = max(args.warmup, 3)
 
     import torch
@@ -186,14 +295,14 @@ def main():
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
-    from nx_b200 import backend, defn, nif, nx
+    from nx_b200 import backend, configs, defn, nif, nx
     backend.set_default_backend("b200", local)
     lib = nif.lib()
+    timer = Timer(lib, local)
     rows = args.rows
-    x_host = make_input(rows, COLS, SEED)
+    x_host = configs.fused_rows_input(rows, COLS, SEED)
     x = nx.tensor(x_host)
-    step_fn = defn.compile(fused_rows, [defn.template((rows, COLS), "f32")], device=local)
-    prog = step_fn.program
+    prog = defn.compile(configs.fused_rows, [defn.template((rows, COLS), "f32")], device=local).program
     outs = prog.run([x], local)                       # allocates the output buffers once
     nbytes = algorithmic_bytes(rows, COLS)
 
@@ -251,23 +360,39 @@ def main():
             dt = float(t.item())
         e2e = {"value": round(world * nbytes / dt / 1e9, 3), "unit": UNIT, "h2d_bytes_per_step": int(x_host.nbytes),
                "d2h_bytes_per_step": int(sum(out_bytes)), "ms_per_step": round(dt * 1e3, 3), "steps": e2e_steps}
+        del pin_in, pin_out
+
+    launches = args.steps * prog.launch_count()
+    plan = prog.describe().strip().split("\n")
+    # free the 4 GiB of the headline workload before the other sections
+    for t_ in [x] + outs:
+        backend.backend_deallocate(t_)
+
+    decoder = None
+    if not args.no_decoder and rows == ROWS:
+        decoder = decoder_section(timer, local, rank, world, dist, torch)
 
     if rank == 0:
-        peak, which = peaks()
+        pk, which = peaks()
+        peak = float(pk["hbm_gbs"])
         line = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "fused row defn f32 {%d,32768} (max, exp, sum, logsumexp, softmax, argmax, tanh*sigmoid chain)" % rows,
-                           "seed": SEED, "parallelism": "replicas only" if world > 1 else "single GPU",
-                           "l2": "inputs (1 GiB) and outputs (3 GiB) per step are larger than L2 (126 MB); no flush needed"},
+                "config": {"workload": WORKLOAD % rows, "seed": SEED,
+                           "parallelism": "replicas only" if world > 1 else "single GPU",
+                           "l2": "input (1 GiB) and outputs (3 GiB) per step exceed L2 (126 MB); no flush needed"},
                 "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
-                             "frac": round(per_gpu / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                             "frac": round(per_gpu / peak, 4),
+                             "traffic": int(NCU_TRAFFIC_BYTES_PER_1024_ROWS * rows / 1024),
                              "peak_source": f"of {which}", "kernel": "nxb_k0_row",
                              "algorithmic_bytes_per_launch": nbytes},
-                "clocks": clocks, "gpu_launches": args.steps * prog.launch_count(), "e2e": e2e,
-                "plan": prog.describe().strip().split("\n")}
+                "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "plan": plan}
+        if decoder is not None:
+            line["decoder"] = decoder
+        if args.all_configs and world == 1:
+            line["configs"] = other_configs(timer, local, pk)
         if not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(x_host[:min(rows, 1024)])
+            line["cpu_baseline"] = cpu_baseline(x_host)
         print(json.dumps(line))
     if dist is not None:
         dist.barrier()

@@ -7,7 +7,7 @@
 namespace nxb {
 const std::string& last_error();
 void canonicalize_dots(Graph& g);
-int comm_all_reduce_sum(nxb200_buffer* buf);
+void comm_all_reduce(const void* in, void* out, size_t count, DType dt, Device& d);
 }  // namespace nxb
 
 using namespace nxb;
@@ -147,6 +147,9 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         }
         check_cu(drv.cuLaunchKernel(L.functions[step.index], ks.grid, 1, 1, ks.block, 1, 1, ks.smem, (CUstream)d.stream, argp.data(), nullptr),
                  ("launching " + ks.name).c_str());
+      } else if (step.kind == Step::ALLREDUCE) {
+        const CollectiveSpec& cs = plan.collectives[step.index];
+        comm_all_reduce(ptr[cs.in_slot], ptr[cs.out_slot], (size_t)cs.count, cs.dt, d);
       } else {
         const GemmSpec& gs = plan.gemms[step.index];
         GemmArgs ga{};

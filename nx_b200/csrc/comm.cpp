@@ -76,7 +76,10 @@ void comm_init(int dev, int rank, int world, const uint8_t* id) {
   g_rank = rank;
 }
 
-void comm_all_reduce_sum_ptr(void* p, size_t count, DType dt, Device& d) {
+void comm_all_reduce(const void* in, void* out, size_t count, DType dt, Device& d);
+void comm_all_reduce_sum_ptr(void* p, size_t count, DType dt, Device& d) { comm_all_reduce(p, p, count, dt, d); }
+
+void comm_all_reduce(const void* in, void* out, size_t count, DType dt, Device& d) {
   if (!g_comm) fail(NXB_ERR_INVALID_ARGUMENT, "no communicator: call nxb200_comm_init first");
   int t;
   switch (dt) {
@@ -92,7 +95,7 @@ void comm_all_reduce_sum_ptr(void* p, size_t count, DType dt, Device& d) {
     case NXB_F64: t = ncclFloat64; break;
     default: fail(NXB_ERR_UNSUPPORTED, "all-reduce of 16-bit integers");
   }
-  check_nccl(nccl().AllReduce(p, p, count, t, ncclSum, g_comm, d.stream), "ncclAllReduce");
+  check_nccl(nccl().AllReduce(in, out, count, t, ncclSum, g_comm, d.stream), "ncclAllReduce");
 }
 
 void comm_destroy() {

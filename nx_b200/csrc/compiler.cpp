@@ -964,7 +964,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
 namespace {
 
 struct Unit {           // one launch-to-be
-  enum Kind { ROW, EW, GEMM } kind = EW;
+  enum Kind { ROW, EW, GEMM, ALLREDUCE } kind = EW;
   std::vector<int64_t> F;
   int k = 0;
   std::vector<int> perm;
@@ -1025,14 +1025,14 @@ struct Planner {
     int d = 0;
     for (int a : g.nodes[n].args) {
       const std::string& op = g.nodes[a].op;
-      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate") ? 1 : 0));
+      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate" || op == "all_reduce") ? 1 : 0));
     }
     return depth_memo[n] = d;
   }
 
   bool is_leaf(int n) const {
     const std::string& op = g.nodes[n].op;
-    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate";
+    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate" || op == "all_reduce";
   }
 
   // Nodes reachable backwards through everything a kernel can generate inline
@@ -1052,7 +1052,8 @@ std::string Plan::describe() const {
   std::ostringstream o;
   for (auto& st : steps) {
     if (st.kind == Step::KERNEL) o << kernels[st.index].desc << "\n";
-    else o << gemms[st.index].desc << "\n";
+    else if (st.kind == Step::GEMM) o << gemms[st.index].desc << "\n";
+    else o << collectives[st.index].desc << "\n";
   }
   return o.str();
 }
@@ -1152,7 +1153,8 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     for (int n = 0; n < N; ++n) {
       const Node& nd = g.nodes[n];
       if (!nd.live) continue;
-      bool ok = is_inline(nd) || is_reduce(nd) || nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate";
+      bool ok = is_inline(nd) || is_reduce(nd) || nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" ||
+                nd.op == "all_reduce";
       if (!ok) fail(NXB_ERR_UNSUPPORTED, "Nx op :" + nd.op + " is not implemented by the B200 compiler");
       if (nd.op == "slice" && nd.args.size() != 1) fail(NXB_ERR_UNSUPPORTED, "slice with dynamic start indices is not implemented");
     }
@@ -1174,13 +1176,19 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
   }
   // what must be materialised regardless of fusion
   for (int o : g.outputs) P.mat[o] = 1;
-  std::vector<int> dots, concats;
+  std::vector<int> dots, concats, allreduces;
   for (int n = 0; n < N; ++n) {
     const Node& nd = g.nodes[n];
     if (!nd.live) continue;
     if (nd.op == "dot") { P.mat[n] = 1; dots.push_back(n); }
     if (nd.op == "concatenate") { P.mat[n] = 1; concats.push_back(n); }
     if (nd.piece_of >= 0) P.mat[n] = 1;
+    if (nd.op == "all_reduce") {
+      P.mat[n] = 1;
+      allreduces.push_back(n);
+      const std::string& aop = g.nodes[nd.args[0]].op;
+      if (aop != "parameter" && aop != "tensor") P.mat[nd.args[0]] = 1;
+    }
   }
   // dot operands: decided by the GEMM planner (it may accept a transposed view directly)
   std::map<int, GemmSpec> gemm_of;
@@ -1283,7 +1291,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         for (int n = 0; n < N; ++n) {
           const Node& nd = g.nodes[n];
           if (!nd.live || !P.mat[n]) continue;
-          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || is_reduce(nd)) continue;
+          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || nd.op == "all_reduce" || is_reduce(nd)) continue;
           roots.push_back(n);
         }
         for (int n : roots) {
@@ -1381,10 +1389,23 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         units.push_back(u);
       }
 
+      for (int n : allreduces) {
+        Unit u;
+        u.kind = Unit::ALLREDUCE;
+        u.gemm_node = n;
+        units.push_back(u);
+      }
+
       // ---- order units by data dependence ---------------------------------------------------------
       auto unit_io = [&](Unit& u) {
         u.reads.clear();
         u.writes.clear();
+        if (u.kind == Unit::ALLREDUCE) {
+          const Node& nd = g.nodes[u.gemm_node];
+          u.writes.insert(nd.slot);
+          u.reads.insert(g.nodes[nd.args[0]].slot);
+          return;
+        }
         if (u.kind == Unit::GEMM) {
           const Node& nd = g.nodes[u.gemm_node];
           u.writes.insert(nd.slot);
@@ -1440,7 +1461,17 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       for (int ui : order) {
         Unit& u = units[ui];
         int step_index = (int)pl.steps.size();
-        if (u.kind == Unit::GEMM) {
+        if (u.kind == Unit::ALLREDUCE) {
+          const Node& nd = g.nodes[u.gemm_node];
+          CollectiveSpec cs;
+          cs.in_slot = g.nodes[nd.args[0]].slot;
+          cs.out_slot = nd.slot;
+          cs.count = shape_numel(nd.shape);
+          cs.dt = nd.dt;
+          cs.desc = "all_reduce#" + std::to_string(u.gemm_node) + " sum " + dtype_name(nd.dt) + shape_str(nd.shape) + " over the tensor-parallel group (NCCL)";
+          pl.collectives.push_back(cs);
+          pl.steps.push_back({Step::ALLREDUCE, (int)pl.collectives.size() - 1});
+        } else if (u.kind == Unit::GEMM) {
           std::vector<int> need;
           GemmSpec gs;
           plan_dot(pl, u.gemm_node, need, &gs);

@@ -72,8 +72,15 @@ struct GemmSpec {
   int scale_slot = -1;
 };
 
+struct CollectiveSpec {
+  int in_slot = -1, out_slot = -1;
+  int64_t count = 0;
+  DType dt = NXB_F32;
+  std::string desc;
+};
+
 struct Step {
-  enum Kind { KERNEL, GEMM } kind = KERNEL;
+  enum Kind { KERNEL, GEMM, ALLREDUCE } kind = KERNEL;
   int index = 0;
 };
 
@@ -83,6 +90,7 @@ struct Plan {
   std::vector<Step> steps;
   std::vector<KernelSpec> kernels;
   std::vector<GemmSpec> gemms;
+  std::vector<CollectiveSpec> collectives;
   std::vector<int> param_slots;   // by parameter index (-1 when unused)
   std::vector<int> output_slots;  // by output index
   std::string describe() const;

@@ -411,8 +411,10 @@ def _dot(a, ta, c1, b1, b, tb, c2, b2, out_t, mode):
     return r.reshape(bs + m + n)
 
 
-def evaluate(nodes, outs, params, mode="xla_like"):
-    """params: list of oracle arrays (see `decode`). Returns list of arrays."""
+def evaluate(nodes, outs, params, mode="xla_like", all_reduce=None):
+    """params: list of oracle arrays (see `decode`). Returns list of arrays.
+    ``all_reduce(array, mesh_axis)`` supplies the cross-partition sum for the
+    programs of sharded runs (tests pass a gloo all-reduce)."""
     if mode not in ("xla_like", "binary_backend"):
         raise ValueError(mode)
     vals = [None] * len(nodes)
@@ -433,6 +435,10 @@ def evaluate(nodes, outs, params, mode="xla_like"):
             v = decode(nd.blob, t, nd.shape)
         elif op == "metadata":
             v = arg[0]
+        elif op == "all_reduce":
+            if all_reduce is None:
+                raise ValueError("program contains all_reduce but no reducer was given")
+            v = _store(all_reduce(arg[0].astype(np.float64 if is_float(t) else np.int64), nd.ints[0]), t, mode)
         elif op == "iota":
             ax = nd.ints[0]
             if ax < 0:
@@ -526,7 +532,7 @@ def evaluate(nodes, outs, params, mode="xla_like"):
     return [vals[o] for o in outs]
 
 
-def run_program(blob, params_raw, mode="xla_like"):
+def run_program(blob, params_raw, mode="xla_like", all_reduce=None):
     """Evaluate a serialised program.  ``params_raw`` are raw byte strings (one
     per parameter, in parameter order).  Returns a list of
     ``(array, type, raw_bytes)`` per output."""
@@ -538,5 +544,5 @@ def run_program(blob, params_raw, mode="xla_like"):
     params = [None] * (max(ptypes) + 1 if ptypes else 0)
     for i, (t, s) in ptypes.items():
         params[i] = decode(params_raw[i], t, s)
-    res = evaluate(nodes, outs, params, mode)
+    res = evaluate(nodes, outs, params, mode, all_reduce)
     return [(r, nodes[o].type, encode(r, nodes[o].type)) for r, o in zip(res, outs)]

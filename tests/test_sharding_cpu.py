@@ -1,0 +1,131 @@
+"""Host-side logic of sharded execution, without a GPU.
+
+The partitioner's per-partition programs are interpreted by the CPU oracle;
+the all-reduce between tensor-parallel partitions runs over torch.distributed
+(gloo, world_size 2, rendezvous on 127.0.0.1).  The stitched result must equal
+the oracle's evaluation of the unpartitioned program, the way the reference's
+sharding tests compare per-device shards with the global value
+(exla/test/exla/defn/sharding_test.exs:140-191)."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import nx_oracle as O
+from helpers import host_tensor
+from nx_b200 import configs, defn, nx, sharding
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_mesh_coordinates_are_row_major():
+    m = sharding.Mesh("m", (2, 4))
+    assert [m.coords(i) for i in range(8)] == [(0, 0), (0, 1), (0, 2), (0, 3), (1, 0), (1, 1), (1, 2), (1, 3)]
+
+
+def test_sharding_validation_errors():
+    m = sharding.Mesh("m", (2, 2))
+    with pytest.raises(sharding.ShardingError):
+        sharding.validate_shardings(m, [(4, 4)], [])
+    with pytest.raises(sharding.ShardingError):
+        sharding.validate_shardings(m, [(4, 4)], [{2: [0]}])
+    with pytest.raises(sharding.ShardingError):
+        sharding.validate_shardings(m, [(4, 4)], [{0: [0], 1: [0]}])
+    with pytest.raises(sharding.ShardingError):
+        sharding.validate_shardings(m, [(4, 4)], [{0: [5]}])
+    assert sharding.validate_shardings(m, [(4, 4), (3,)], [{0: [1]}, {}]) == [(1, None), (None,)]
+    assert sharding.global_shape((2, 4), (1, None), m) == (4, 4)
+
+
+def test_unsupported_patterns_raise():
+    m = sharding.Mesh("m", (2,))
+    a, b = defn.template((4, 4), "f32"), defn.template((8, 4), "f32")
+    # contraction split on one side only would need an all-gather
+    with pytest.raises(sharding.ShardingError):
+        sharding.partition(lambda x, y: nx.dot(x, y), m, [{1: [0]}, {}], [a, b], 0)
+    with pytest.raises(sharding.ShardingError):
+        sharding.partition(lambda x: nx.reduce_max(x, axes=[0]), m, [{0: [0]}], [a], 0)
+
+
+def _decoder_case():
+    block = configs.make_decoder_block(n_heads=4)
+    inputs = configs.decoder_inputs(batch=2, seq=16, hidden=64, inter=176)
+    return block, inputs
+
+
+def test_batch_data_parallel_needs_no_collective():
+    block, inputs = _decoder_case()
+    mesh = sharding.Mesh("dp", (2,))
+    shardings = [{0: [0]}] + [{}] * 9
+    host = [host_tensor(a, t) for a, t in inputs]
+    blob, _ = defn.build_program(block, host)
+    (full, _, _), = O.run_program(blob, [h.data.raw for h in host], "xla_like")
+    parts = []
+    for p in range(2):
+        local = [host_tensor(inputs[0][0][p:p + 1], "bf16")] + host[1:]
+        pblob, _, out_specs = sharding.partition(block, mesh, shardings, local, p)
+        nodes, _ = O.parse_program(pblob)
+        assert not [n for n in nodes if n.op == "all_reduce"]
+        assert out_specs == [(0, None, None)]
+        (o, _, _), = O.run_program(pblob, [h.data.raw for h in local], "xla_like")
+        parts.append(o)
+    np.testing.assert_array_equal(np.concatenate(parts, axis=0), full)
+
+
+WORKER = r"""
+import os, sys
+import numpy as np
+import torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "oracle")); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+import nx_oracle as O
+from helpers import host_tensor
+from nx_b200 import configs, defn, sharding
+dist.init_process_group("gloo")
+rank = dist.get_rank()
+block = configs.make_decoder_block(n_heads=4)
+inputs = configs.decoder_inputs(batch=2, seq=16, hidden=64, inter=176)
+mesh = sharding.Mesh("tp", (2,))
+# column-parallel Wq Wk Wv Wgate Wup (split output axis), row-parallel Wo Wdown (split input axis)
+shardings = [{}, {1: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {}, {}]
+def shard(a, sh):
+    for dim in sh:
+        n = a.shape[dim] // 2
+        a = np.take(a, range(rank * n, (rank + 1) * n), axis=dim)
+    return np.ascontiguousarray(a)
+local = [host_tensor(shard(a, sh), t) for (a, t), sh in zip(inputs, shardings)]
+blob, _, out_specs = sharding.partition(block, mesh, shardings, local, rank)
+nodes, _ = O.parse_program(blob)
+assert len([n for n in nodes if n.op == "all_reduce"]) == 2, "one all-reduce per row-parallel linear"
+def all_reduce(arr, axis):
+    t = torch.from_numpy(np.ascontiguousarray(arr))
+    dist.all_reduce(t)
+    return t.numpy()
+(out, _, _), = O.run_program(blob, [h.data.raw for h in local], "xla_like", all_reduce=all_reduce)
+assert out_specs == [(None, None, None)]
+np.save(os.path.join(sys.argv[2], f"out{rank}.npy"), out)
+dist.barrier()
+"""
+
+
+def test_tensor_parallel_two_gloo_ranks(tmp_path):
+    block, inputs = _decoder_case()
+    host = [host_tensor(a, t) for a, t in inputs]
+    blob, _ = defn.build_program(block, host)
+    (full, _, _), = O.run_program(blob, [h.data.raw for h in host], "xla_like")
+    script = tmp_path / "worker.py"
+    script.write_text(WORKER)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(script), ROOT, str(tmp_path)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    o0, o1 = np.load(tmp_path / "out0.npy"), np.load(tmp_path / "out1.npy")
+    # both tensor-parallel ranks hold the full (replicated) result
+    np.testing.assert_array_equal(o0, o1)
+    # splitting the contraction changes where bf16 rounding happens: compare within the bf16 tolerance
+    np.testing.assert_allclose(o0, full, rtol=2e-2, atol=1e-2)
