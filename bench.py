@@ -112,6 +112,8 @@ def load_rows_oracle():
     lib.rows_oracle.restype = None
     lib.rows_oracle.argtypes = [C.c_void_p, C.c_int64, C.c_int64] + [C.c_void_p] * 7
     lib.rows_oracle_threads.restype = C.c_int
+    # launchers such as torch.distributed.run export OMP_NUM_THREADS=1: use the cores this process may run on
+    lib.rows_oracle_set_threads(len(os.sched_getaffinity(0)))
     return lib
 
 
@@ -391,7 +393,7 @@ def main():
             line["decoder"] = decoder
         if args.all_configs and world == 1:
             line["configs"] = other_configs(timer, local, pk)
-        if not args.no_cpu:
+        if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(x_host)
         print(json.dumps(line))
     if dist is not None:

@@ -16,6 +16,7 @@
 #include <omp.h>
 
 int rows_oracle_threads(void) { return omp_get_max_threads(); }
+void rows_oracle_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
 
 void rows_oracle(const float *x, int64_t rows, int64_t cols, float *rowmax, float *e, float *sum,
                  float *lse, float *softmax, int32_t *argmax, float *chain) {
