@@ -142,6 +142,27 @@ size_t nxb200_program_kernel_source(nxb200_program *prog, int i, char *dst, size
 /* Number of kernels one run launches. */
 int nxb200_program_launch_count(nxb200_program *prog, int *count);
 
+/* Matrix product that allocates nothing: c {m,n} = a {m,k} . b {k,n}, bf16 operands
+ * and result, f32 accumulation, all three given as raw device pointers on `device`.
+ * No counterpart in the reference, whose runtime always allocates through its client.
+ * It exists for callers that must not trigger a cudaMalloc inside this library: a
+ * process that has handed the device's memory to another allocator up front (an XLA
+ * client with preallocation, say) and would see the allocation fail, or a serving
+ * loop that cannot take the device-wide stall an allocation causes.  The scratch the
+ * product needs (a copy of b with k contiguous) is a fixed 32 MiB array inside the
+ * library, so k*n may be at most 16,777,216 elements; larger operands, k or n not a
+ * multiple of 8, or pointers that are not 16-byte aligned are rejected with
+ * NXB_ERR_INVALID_ARGUMENT.  Every GPU that loads the library holds those 32 MiB
+ * until the process exits.
+ *
+ * The first call on a device looks up the array's device address (set-up that has
+ * to happen outside any stream capture, so make that first call before capturing).
+ * All calls share the one array: calls that overlap on the same GPU (different
+ * streams or threads) race on it.  The call enqueues on `stream` (a cudaStream_t, or
+ * NULL for the default stream) and returns after the result is complete. */
+int nxb200_dot_bf16_static_scratch(int device, const void *a, const void *b, void *c,
+                                   int64_t m, int64_t n, int64_t k, void *stream);
+
 /* ---- device control ---------------------------------------------------------*/
 int nxb200_device_synchronize(int device);
 /* Device-side timing of everything enqueued between the two calls on the

@@ -413,3 +413,82 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
 }
 
 }  // namespace nxb
+
+// ---------------------------------------------------------------------------------------
+// Matrix product that allocates nothing.
+//
+// Some callers cannot let this library call cudaMalloc: an application that has
+// already given (nearly) all device memory to another allocator — e.g. an XLA
+// client started with `preallocate: true`, which takes its memory fraction up
+// front — would see the allocation fail, and a serving loop with a latency
+// budget cannot afford the device-wide synchronisation a cudaMalloc implies.
+// For them the scratch the product needs (the K-major copy of B) lives in a
+// fixed array inside the library image: every GPU that loads the library
+// reserves NOALLOC_SCRATCH_BYTES for as long as the process lives.
+constexpr size_t NOALLOC_SCRATCH_BYTES = size_t(32) << 20;   // 32 MiB: B of up to 16 Mi bf16 elements
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+static __device__ int g_noalloc_status;
+
+namespace {
+struct NoAllocDevice {
+  void* scratch = nullptr;   // device address of g_noalloc_scratch on this device
+  int* status = nullptr;     // device address of g_noalloc_status on this device
+  int sm_count = 0;
+};
+std::mutex g_noalloc_mu;
+std::map<int, NoAllocDevice> g_noalloc_devices;
+}  // namespace
+
+extern "C" int nxb200_dot_bf16_static_scratch(int device, const void* a, const void* b, void* c, int64_t m, int64_t n,
+                                              int64_t k, void* stream_handle) {
+  using namespace nxb;
+  try {
+    cudaStream_t stream = (cudaStream_t)stream_handle;
+    if (!a || !b || !c) fail(NXB_ERR_INVALID_ARGUMENT, "a, b and c must be device pointers");
+    if (m < 1 || n < 1 || k < 1) fail(NXB_ERR_INVALID_ARGUMENT, "m, n and k must be positive");
+    if (k % 8 != 0 || n % 8 != 0)
+      fail(NXB_ERR_INVALID_ARGUMENT, "k and n must be multiples of 8 (rows of both operands must start on 16-byte boundaries)");
+    const size_t need = (size_t)n * (size_t)k * 2;
+    if (need > NOALLOC_SCRATCH_BYTES)
+      fail(NXB_ERR_INVALID_ARGUMENT, "operand b has " + std::to_string(need) + " bytes; the built-in scratch holds at most " +
+                                         std::to_string(NOALLOC_SCRATCH_BYTES) + " (k*n <= " + std::to_string(NOALLOC_SCRATCH_BYTES / 2) + " elements)");
+    NXB_CUDA(cudaSetDevice(device));
+    NoAllocDevice dev;
+    {
+      // One-time set-up per device, with that device current: in host code the array's
+      // name is only a handle, the address a kernel can use comes from the runtime.
+      std::lock_guard<std::mutex> g(g_noalloc_mu);
+      auto it = g_noalloc_devices.find(device);
+      if (it == g_noalloc_devices.end()) {
+        NoAllocDevice d;
+        NXB_CUDA(cudaGetSymbolAddress(&d.scratch, g_noalloc_scratch));
+        NXB_CUDA(cudaGetSymbolAddress((void**)&d.status, g_noalloc_status));
+        NXB_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device));
+        it = g_noalloc_devices.emplace(device, d).first;
+      }
+      dev = it->second;
+    }
+    // the status word must start at zero; the scratch is fully rewritten before it is read
+    NXB_CUDA(cudaMemsetAsync(dev.status, 0, sizeof(int), stream));
+    launch_transpose(b, dev.scratch, 1, k, n, 2, stream);          // B {k,n} -> {n,k}
+    GemmArgs g{};
+    g.a = a; g.b = dev.scratch; g.c = c;
+    g.batch = 1; g.m = m; g.n = n; g.k = k;
+    g.lda = k; g.ldb = k; g.bsa = m * k; g.bsb = n * k;
+    g.ta = g.tb = false;
+    g.da = g.db = g.dc = NXB_BF16;
+    if (!tc_gemm_supported(g)) fail(NXB_ERR_INVALID_ARGUMENT, "operands must be 16-byte aligned");
+    launch_tc_gemm(g, dev.status, dev.sm_count, stream);
+    int status = 0;
+    NXB_CUDA(cudaMemcpyAsync(&status, dev.status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    NXB_CUDA(cudaStreamSynchronize(stream));
+    if (status) fail(NXB_ERR_TIMEOUT, "the product gave up waiting on an internal barrier; c is invalid");
+    return NXB_OK;
+  } catch (const Error& e) {
+    set_last_error(e.msg);
+    return e.status;
+  } catch (const std::exception& e) {
+    set_last_error(e.what());
+    return NXB_ERR_RUNTIME;
+  }
+}

@@ -81,6 +81,7 @@ def _declare(l):
         "nxb200_comm_init": [i32, i32, i32, C.c_char_p],
         "nxb200_comm_all_reduce_sum": [vp],
         "nxb200_comm_destroy": [],
+        "nxb200_dot_bf16_static_scratch": [i32, vp, vp, vp, C.c_int64, C.c_int64, C.c_int64, vp],
     }
     for name, args in sigs.items():
         f = getattr(l, name)
