@@ -161,6 +161,8 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         ga.ta = gs.a.trans; ga.tb = gs.b.trans;
         ga.da = gs.a.dt; ga.db = gs.b.dt; ga.dc = gs.out_dt;
         ga.epilogue = gs.epilogue;
+        if (gs.scale_slot >= 0) ga.scale = ptr[gs.scale_slot];
+        if (ga.scale && !tc_gemm_supported(ga)) fail(NXB_ERR_RUNTIME, "internal: scaled product outside the tensor-core path");
         if (tc_gemm_supported(ga)) {
           // bring both operands to K-major form, then run on the tensor cores
           void* ta = nullptr;

@@ -1061,6 +1061,7 @@ std::string Plan::describe() const {
 // implemented in gemm_plan.cpp
 bool plan_dot(Plan& plan, int node, std::vector<int>& need_materialised, GemmSpec* out);
 void canonicalize_dots(Graph& g);
+void rewrite_quantised_linears(Graph& g);
 
 std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
   auto plan = std::make_unique<Plan>();
@@ -1089,6 +1090,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     }
     for (int& o : g.outputs) o = remap[o];
   }
+  rewrite_quantised_linears(g);
   canonicalize_dots(g);
   Planner P(*plan);
 
@@ -1414,6 +1416,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           plan_dot(pl, u.gemm_node, need, &gs);
           u.reads.insert(gs.a.slot);
           u.reads.insert(gs.b.slot);
+          if (gs.scale_slot >= 0) u.reads.insert(gs.scale_slot);
           return;
         }
         std::set<int> seen, leaves, reds;

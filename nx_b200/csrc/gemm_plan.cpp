@@ -75,6 +75,66 @@ void canonicalize_dots(Graph& g) {
   }
 }
 
+// Weight-only quantised linear: dot(x: bf16, multiply(as_type(W: s8 -> f32), S)) where S has
+// one value per output channel.  The per-channel factor does not depend on the contracted
+// index, so it moves out of the sum:  sum_k x[m,k] * (W[n,k] * S[n]) = S[n] * sum_k x[m,k] * W[n,k].
+// The product then runs on the tensor cores with W converted (exactly) to bf16, f32
+// accumulation, and S applied to the accumulator in the epilogue.
+void rewrite_quantised_linears(Graph& g) {
+  size_t N = g.nodes.size();
+  auto skip_meta = [&](int n) { while (g.nodes[n].op == "metadata") n = g.nodes[n].args[0]; return n; };
+  for (size_t n = 0; n < N; ++n) {
+    if (g.nodes[n].op != "dot" || g.nodes[n].dt != NXB_F32) continue;
+    DotAxes d = dot_axes(g.nodes[n]);
+    if (!d.b1.empty() || d.c1.size() != 1 || d.c2.size() != 1) continue;
+    int x = g.nodes[n].args[0], wq = skip_meta(g.nodes[n].args[1]);
+    if (g.nodes[x].dt != NXB_BF16 || g.nodes[x].shape.size() != 2) continue;
+    const Node& mul = g.nodes[wq];
+    if (mul.op != "multiply" || mul.dt != NXB_F32 || mul.shape.size() != 2) continue;
+    int cvt = -1, sc = -1;
+    for (int side = 0; side < 2; ++side) {
+      int f = skip_meta(mul.args[side]);
+      if (g.nodes[f].op == "as_type" && g.nodes[g.nodes[f].args[0]].dt == NXB_S8 && g.nodes[f].shape == mul.shape) { cvt = f; sc = skip_meta(mul.args[1 - side]); }
+    }
+    if (cvt < 0) continue;
+    const int caxis = d.c2[0], faxis = 1 - caxis;
+    const Node& S = g.nodes[sc];
+    if (S.dt != NXB_F32) continue;
+    // S aligned to the right of {d0,d1}: extent 1 (or absent) along the contracted axis, N along the free one
+    std::vector<int64_t> sh = S.shape;
+    while (sh.size() < 2) sh.insert(sh.begin(), 1);
+    if (sh.size() != 2 || sh[caxis] != 1 || sh[faxis] != mul.shape[faxis]) continue;
+    if (mul.shape[caxis] % 8 != 0) continue;      // the tensor-core path needs 16-byte aligned rows
+    Node wb;
+    wb.op = "as_type";
+    wb.dt = NXB_BF16;
+    wb.shape = mul.shape;
+    wb.args = {g.nodes[cvt].args[0]};
+    g.nodes.push_back(wb);
+    g.nodes[n].args[1] = (int)g.nodes.size() - 1;
+    g.nodes[n].args.push_back(sc);      // third argument: keeps the factor alive and ordered before the product
+    g.nodes[n].scale_arg = sc;
+  }
+  // dot(as_type(a: s8 -> s32), as_type(b: s8 -> s32)) -> the s8 tensor-core product with an s32
+  // accumulator: the same integers, bit for bit (|sum| <= k * 127^2 stays far inside 32 bits for
+  // any k the tensor map can address... guarded below).
+  for (size_t n = 0; n < N; ++n) {
+    Node& nd = g.nodes[n];
+    if (nd.op != "dot" || nd.dt != NXB_S32 || nd.scale_arg >= 0) continue;
+    int a = skip_meta(nd.args[0]), b = skip_meta(nd.args[1]);
+    auto widened_s8 = [&](int x) {
+      return g.nodes[x].op == "as_type" && g.nodes[x].dt == NXB_S32 && g.nodes[g.nodes[x].args[0]].dt == NXB_S8;
+    };
+    if (!widened_s8(a) || !widened_s8(b)) continue;
+    DotAxes d = dot_axes(nd);
+    int64_t k = 1;
+    for (int ax : d.c1) k *= g.nodes[a].shape[ax];
+    if (k % 16 != 0 || k > 130000) continue;       // 16-byte rows; 130000 * 127^2 < 2^31
+    nd.args[0] = g.nodes[a].args[0];
+    nd.args[1] = g.nodes[b].args[0];
+  }
+}
+
 bool plan_dot(Plan& plan, int node, std::vector<int>& need, GemmSpec* out) {
   Graph& g = plan.g;
   const Node& nd = g.nodes[node];
@@ -105,9 +165,14 @@ bool plan_dot(Plan& plan, int node, std::vector<int>& need, GemmSpec* out) {
   gs.out_dt = nd.dt;
   if (a.slot < 0) need.push_back(nd.args[0]);
   if (b.slot < 0) need.push_back(nd.args[1]);
+  if (nd.scale_arg >= 0) {
+    gs.scale_slot = g.nodes[nd.scale_arg].slot;
+    if (gs.scale_slot < 0) need.push_back(nd.scale_arg);
+  }
   gs.desc = "gemm#" + std::to_string(node) + " batch=" + std::to_string(gs.batch) + " m=" + std::to_string(gs.m) + " n=" +
             std::to_string(gs.n) + " k=" + std::to_string(gs.k) + " a=" + dtype_name(a.dt) + (gs.a.trans ? "[k,m]" : "[m,k]") + " b=" +
-            dtype_name(b.dt) + (gs.b.trans ? "[k,n]" : "[n,k]") + " out=" + dtype_name(nd.dt);
+            dtype_name(b.dt) + (gs.b.trans ? "[k,n]" : "[n,k]") + " out=" + dtype_name(nd.dt) +
+            (nd.scale_arg >= 0 ? " epilogue=per-column f32 scale" : "");
   *out = gs;
   return true;
 }

@@ -22,10 +22,14 @@
 namespace nxb {
 namespace {
 
-constexpr int BM = 128, BN = 256, STAGES = 4;
+constexpr int BM = 128;
 constexpr int ROW_BYTES = 128;                        // one swizzle row: 64 bf16 or 128 s8
-constexpr int A_STAGE = BM * ROW_BYTES, B_STAGE = BN * ROW_BYTES;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE + B_STAGE) + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int A_STAGE = BM * ROW_BYTES;
+// The tile width BN is 256 for large products; narrow outputs (few rows, e.g. a linear layer
+// applied to 1..128 tokens) use 128 or 64 so that enough tiles exist to occupy every SM, with a
+// deeper ring since the product is then bound by streaming the weights.
+__host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 4 : bn == 128 ? 6 : 8; }
+__host__ __device__ constexpr int smem_bytes_for(int bn) { return stages_for(bn) * (A_STAGE + bn * ROW_BYTES) + 1024 /*alignment*/ + 256 /*barriers*/; }
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 enum Kind { KIND_BF16 = 0, KIND_F16 = 1, KIND_S8 = 2 };
@@ -139,10 +143,13 @@ __device__ __forceinline__ unsigned short f32_to_f16_bits(float f) {
   return h;
 }
 
-template <int KIND>
+template <int KIND, int BN>
 __global__ void __launch_bounds__(192, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
   extern __shared__ unsigned char smem_raw[];
+  constexpr int STAGES = stages_for(BN);
+  constexpr int B_STAGE = BN * ROW_BYTES;
+  constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;      // two accumulators; a power of two >= 32
   constexpr int BK = (KIND == KIND_S8) ? 128 : 64;          // elements per 128-byte row
   constexpr int UMMA_K_BYTES = 32;                          // one MMA consumes 32 bytes of K per row
 
@@ -163,7 +170,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -305,7 +312,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -389,7 +396,12 @@ bool tc_gemm_supported(const GemmArgs& g) {
 
 void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStream_t stream) {
   CUtensorMap ma = make_map(g.a, g.da, g.k, g.m, g.batch, g.lda, g.bsa, BM);
-  CUtensorMap mb = make_map(g.b, g.db, g.k, g.n, g.batch, g.ldb, g.bsb, BN);
+  // tile width: the widest one that still yields at least one tile per SM
+  const long long mt = (g.m + BM - 1) / BM;
+  int bn = 256;
+  if (mt * ((g.n + 255) / 256) * g.batch < sm_count) bn = 128;
+  if (bn == 128 && mt * ((g.n + 127) / 128) * g.batch < sm_count) bn = 64;
+  CUtensorMap mb = make_map(g.b, g.db, g.k, g.n, g.batch, g.ldb, g.bsb, bn);
   TcParams p{};
   p.c = g.c;
   p.bias = g.bias;
@@ -397,19 +409,26 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
   p.status = status_word;
   p.m = (int)g.m; p.n = (int)g.n; p.k = (int)g.k; p.batch = (int)g.batch;
   p.mtiles = (int)((g.m + BM - 1) / BM);
-  p.ntiles = (int)((g.n + BN - 1) / BN);
+  p.ntiles = (int)((g.n + bn - 1) / bn);
   p.out_dt = g.dc;
   p.epilogue = g.epilogue;
   long long tiles = (long long)p.mtiles * p.ntiles * p.batch;
   unsigned grid = (unsigned)std::min<long long>(tiles, sm_count);
-  auto launch = [&](auto kern) {
-    NXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    kern<<<grid, 192, SMEM_BYTES, stream>>>(ma, mb, p);
+  auto launch = [&](auto kern, int smem) {
+    NXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, 192, smem, stream>>>(ma, mb, p);
     NXB_CUDA(cudaGetLastError());
   };
-  if (g.da == NXB_BF16) launch(tc_gemm_kernel<KIND_BF16>);
-  else if (g.da == NXB_F16) launch(tc_gemm_kernel<KIND_F16>);
-  else launch(tc_gemm_kernel<KIND_S8>);
+#define NXB_LAUNCH_KIND(K)                                                      \
+  do {                                                                          \
+    if (bn == 256) launch(tc_gemm_kernel<K, 256>, smem_bytes_for(256));         \
+    else if (bn == 128) launch(tc_gemm_kernel<K, 128>, smem_bytes_for(128));    \
+    else launch(tc_gemm_kernel<K, 64>, smem_bytes_for(64));                     \
+  } while (0)
+  if (g.da == NXB_BF16) NXB_LAUNCH_KIND(KIND_BF16);
+  else if (g.da == NXB_F16) NXB_LAUNCH_KIND(KIND_F16);
+  else NXB_LAUNCH_KIND(KIND_S8);
+#undef NXB_LAUNCH_KIND
 }
 
 }  // namespace nxb
