@@ -70,6 +70,8 @@ void ensure_loaded(nxb200_program* p, Device& d) {
     check_cu(drv.cuModuleLoadData(&m, ks.cubin.data()), ("loading kernel " + ks.name).c_str());
     CUfunction f;
     check_cu(drv.cuModuleGetFunction(&f, m, ks.name.c_str()), ("resolving kernel " + ks.name).c_str());
+    if (ks.smem > 48 * 1024)
+      check_cu(drv.cuFuncSetAttribute(f, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)ks.smem), ("configuring " + ks.name).c_str());
     L.modules.push_back(m);
     L.functions.push_back(f);
   }
@@ -155,30 +157,52 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         GemmArgs ga{};
         ga.a = ptr[gs.a.slot];
         ga.b = ptr[gs.b.slot];
-        ga.c = ptr[gs.out_slot];
+        ga.c = gs.jit_kernel >= 0 ? nullptr : ptr[gs.out_slot];
         ga.batch = gs.batch; ga.m = gs.m; ga.n = gs.n; ga.k = gs.k;
         ga.lda = gs.a.ld; ga.ldb = gs.b.ld; ga.bsa = gs.a.batch_stride; ga.bsb = gs.b.batch_stride;
         ga.ta = gs.a.trans; ga.tb = gs.b.trans;
         ga.da = gs.a.dt; ga.db = gs.b.dt; ga.dc = gs.out_dt;
         ga.epilogue = gs.epilogue;
         if (gs.scale_slot >= 0) ga.scale = ptr[gs.scale_slot];
-        if (ga.scale && !tc_gemm_supported(ga)) fail(NXB_ERR_RUNTIME, "internal: scaled product outside the tensor-core path");
-        if (tc_gemm_supported(ga)) {
-          // bring both operands to K-major form, then run on the tensor cores
+        // 16-bit operands are consumed with either index contiguous when their rows are 16-byte
+        // aligned; everything else is first copied into K-major form
+        const size_t es = dtype_size(ga.da);
+        const bool mn_a = ga.ta && es == 2 && (ga.m * es) % 16 == 0;
+        const bool mn_b = ga.tb && es == 2 && (ga.n * es) % 16 == 0;
+        GemmArgs fin = ga;
+        if (ga.ta && !mn_a) { fin.ta = false; fin.lda = ga.k; fin.bsa = ga.m * ga.k; }
+        if (ga.tb && !mn_b) { fin.tb = false; fin.ldb = ga.k; fin.bsb = ga.n * ga.k; }
+        const bool on_tensor_cores = tc_gemm_supported(fin);
+        if ((ga.scale || gs.jit_kernel >= 0) && !on_tensor_cores) fail(NXB_ERR_RUNTIME, "internal: fused product outside the tensor-core path");
+        if (on_tensor_cores) {
           void* ta = nullptr;
           void* tb = nullptr;
-          const size_t es = dtype_size(ga.da);
-          if (ga.ta) {
+          if (ga.ta && !mn_a) {
             ta = d.alloc.alloc((size_t)(ga.batch * ga.m * ga.k) * es);
             launch_transpose(ga.a, ta, ga.batch, ga.k, ga.m, es, d.stream);
-            ga.a = ta; ga.ta = false; ga.lda = ga.k; ga.bsa = ga.m * ga.k;
+            fin.a = ta;
           }
-          if (ga.tb) {
+          if (ga.tb && !mn_b) {
             tb = d.alloc.alloc((size_t)(ga.batch * ga.n * ga.k) * es);
             launch_transpose(ga.b, tb, ga.batch, ga.k, ga.n, es, d.stream);
-            ga.b = tb; ga.tb = false; ga.ldb = ga.k; ga.bsb = ga.n * ga.k;
+            fin.b = tb;
           }
-          launch_tc_gemm(ga, d.status_dev, d.sm_count, d.stream);
+          ga = fin;
+          if (gs.jit_kernel >= 0) {
+            const KernelSpec& ks = plan.kernels[gs.jit_kernel];
+            std::vector<void*> ep(ks.arg_slots.size());
+            for (size_t a = 0; a < ks.arg_slots.size(); ++a) {
+              ep[a] = ptr[ks.arg_slots[a]];
+              if (!ep[a]) fail(NXB_ERR_RUNTIME, "internal: epilogue of " + ks.name + " reads a buffer that was never produced");
+            }
+            TcLaunch tl;
+            tc_prepare_launch(ga, gs.bn, ep.data(), (int)ep.size(), d.status_dev, d.sm_count, &tl);
+            void* params[3] = {tl.map_a, tl.map_b, tl.params};
+            check_cu(drv.cuLaunchKernel(L.functions[gs.jit_kernel], tl.grid, 1, 1, 192, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
+                     ("launching " + ks.name).c_str());
+          } else {
+            launch_tc_gemm(ga, d.status_dev, d.sm_count, d.stream);
+          }
           if (ta) d.alloc.free(ta);
           if (tb) d.alloc.free(tb);
         } else {

@@ -112,7 +112,11 @@ struct Root {
 // One generated kernel.
 class KernelBuilder {
  public:
-  enum Mode { EW, ROW };
+  enum Mode { EW, ROW, EPI };   // EPI: body of a matrix-product epilogue (a __device__ function)
+  int acc_node = -1;            // EPI: the dot node whose accumulator the function receives
+  int force_v = 0;              // EPI: vector width to generate (8 or 1)
+  std::vector<int> seed_args;   // EPI: argument order to reuse (so both widths see the same pointers)
+  std::string idx_type() const { return idx_t(); }
   KernelBuilder(Plan& plan, Mode mode, std::vector<int64_t> F, int k, std::vector<int> perm)
       : plan_(plan), g_(plan.g), mode_(mode), F_(std::move(F)), k_(k), perm_(std::move(perm)) {
     nv_ = (int)F_.size();
@@ -140,6 +144,9 @@ class KernelBuilder {
   std::vector<int> perm_;    // for a lone reduce over non-trailing axes: F dim j is input dim perm_[j]
   int nv_ = 0;
   int64_t numel_ = 0, R_ = 0, C_ = 1;
+public:
+  int vec_width() const { return V_; }
+private:
   int V_ = 1, T_ = 32, block_ = 256, rpc_ = 1, chunks_ = 1;
   bool cache_ = false, guard_ = false, big_ = false;
 
@@ -213,6 +220,13 @@ class KernelBuilder {
     (elem ? lane_sec_[phase_] : row_sec_[phase_]) += "        " + line + "\n";
   }
 
+  // a node that merely renames the product's buffer (reshape / squeeze / metadata over it)
+  bool aliases_acc(int n) const {
+    if (acc_node < 0 || n == acc_node) return false;
+    int a = n;
+    while (a >= 0 && g_.nodes[a].alias >= 0) a = g_.nodes[a].alias;
+    return a == acc_node;
+  }
   int level(int n);
   Val value(int n, const std::vector<Aff>& idx);
   Val load(int n, const std::vector<Aff>& idx);
@@ -320,7 +334,7 @@ int KernelBuilder::level(int n) {
   if (it != level_memo_.end()) return it->second;
   const Node& nd = g_.nodes[n];
   int l = 0;
-  bool ext = nd.slot >= 0 && !produced.count(n) && !std::count(reduces.begin(), reduces.end(), n);
+  bool ext = (nd.slot >= 0 && !produced.count(n) && !std::count(reduces.begin(), reduces.end(), n) && !aliases_acc(n)) || n == acc_node;
   if (!ext) {
     if (is_reduce(nd)) {
       if (!std::count(reduces.begin(), reduces.end(), n)) throw FusionError("reduction outside the kernel is not materialised");
@@ -401,7 +415,28 @@ KernelBuilder::Val KernelBuilder::load(int n, const std::vector<Aff>& idx) {
 KernelBuilder::Val KernelBuilder::value(int n, const std::vector<Aff>& idx) {
   const Node& nd = g_.nodes[n];
   bool in_red = std::count(reduces.begin(), reduces.end(), n) > 0;
-  if (nd.slot >= 0 && !produced.count(n) && !in_red) return load(n, idx);
+  if (n == acc_node) {
+    // the product's own element: only legal at the position this thread's accumulator holds
+    auto st = cstrides(nd.shape);
+    Aff addr = aff_const(nv_, 0);
+    for (size_t j = 0; j < idx.size(); ++j) {
+      if (idx[j].opaque) throw FusionError("product read through a reshaped index");
+      addr.c += idx[j].c * st[j];
+      for (int v = 0; v < nv_; ++v) addr.k[v] += idx[j].k[v] * st[j];
+    }
+    auto fs = cstrides(F_);
+    bool same = addr.c == 0;
+    for (int j = 0; j < nv_; ++j) if (F_[j] != 1 && addr.k[j] != fs[j]) same = false;
+    if (!same) throw FusionError("product consumed at a transposed or sliced position");
+    std::string key = "acc";
+    auto it = elem_memo_[phase_].find(key);
+    if (it != elem_memo_[phase_].end()) return {it->second, true};
+    std::string v = newvar();
+    stmt(true, std::string("const ") + reg_type(nd.dt) + " " + v + " = " + cvt("acc[v]", NXB_F32, nd.dt) + ";");
+    elem_memo_[phase_][key] = v;
+    return {v, true};
+  }
+  if (nd.slot >= 0 && !produced.count(n) && !in_red && !aliases_acc(n)) return load(n, idx);
   if (nd.op == "constant") {
     bool isf = !nd.flts.empty();
     return {literal(isf ? nd.flts[0] : 0.0, isf ? 0 : nd.ints[0], isf, nd.dt), false};
@@ -717,7 +752,8 @@ void KernelBuilder::configure() {
   std::function<void(int, std::set<int>&)> scan = [&](int n, std::set<int>& seen) {
     if (!seen.insert(n).second) return;
     const Node& nd = g_.nodes[n];
-    if (nd.slot >= 0 && !produced.count(n) && !std::count(reduces.begin(), reduces.end(), n)) {
+    if (n == acc_node) return;
+    if (nd.slot >= 0 && !produced.count(n) && !std::count(reduces.begin(), reduces.end(), n) && !aliases_acc(n)) {
       if (strip_units(nd.shape) == strip_units(F_)) minsz = std::min(minsz, dtype_size(nd.dt));
       return;
     }
@@ -728,6 +764,7 @@ void KernelBuilder::configure() {
   for (int n : reduces) scan(n, seen);
   V_ = (int)std::min<size_t>(8, 16 / minsz);
   if (!perm_.empty()) V_ = 1;
+  if (mode_ == EPI) V_ = force_v;
   while (V_ > 1 && F_[nv_ - 1] % V_ != 0) V_ /= 2;
   big_ = numel_ >= (int64_t(1) << 31) - 4096;
   for (int n : seen)
@@ -748,6 +785,7 @@ void KernelBuilder::configure() {
 
 KernelSpec KernelBuilder::build(const std::string& name) {
   for (int n : stores) produced.insert(n);
+  for (int sl : seed_args) param(sl);
   configure();
 
   // phases
@@ -854,15 +892,26 @@ KernelSpec KernelBuilder::build(const std::string& name) {
   std::ostringstream o;
   const std::string I = idx_t();
   std::vector<const Node*> argn;
-  o << "extern \"C\" __global__ void __launch_bounds__(" << block_ << ") " << name << "(";
-  for (size_t i = 0; i < arg_slots_.size(); ++i) {
-    const Slot& sl = plan_.slots[arg_slots_[i]];
-    bool written = false;
-    for (int s : stores) if (g_.nodes[s].slot == arg_slots_[i]) written = true;
-    for (int r : reduces) if (g_.nodes[r].slot == arg_slots_[i]) written = true;
-    o << (i ? ", " : "") << (written ? "" : "const ") << storage_type(sl.dt) << "* __restrict__ p" << i;
+  auto is_written = [&](int slot) {
+    for (int s : stores) if (g_.nodes[s].slot == slot) return true;
+    for (int r : reduces) if (g_.nodes[r].slot == slot) return true;
+    return false;
+  };
+  if (mode_ == EPI) {
+    o << "__device__ __forceinline__ void " << name << "(const float* acc, const " << I << " flat0, void* const* ep) {\n";
+    for (size_t i = 0; i < arg_slots_.size(); ++i) {
+      const Slot& sl = plan_.slots[arg_slots_[i]];
+      o << "  " << (is_written(arg_slots_[i]) ? "" : "const ") << storage_type(sl.dt) << "* __restrict__ p" << i << " = (" <<
+          (is_written(arg_slots_[i]) ? "" : "const ") << storage_type(sl.dt) << "*)ep[" << i << "];\n";
+    }
+  } else {
+    o << "extern \"C\" __global__ void __launch_bounds__(" << block_ << ") " << name << "(";
+    for (size_t i = 0; i < arg_slots_.size(); ++i) {
+      const Slot& sl = plan_.slots[arg_slots_[i]];
+      o << (i ? ", " : "") << (is_written(arg_slots_[i]) ? "" : "const ") << storage_type(sl.dt) << "* __restrict__ p" << i;
+    }
+    o << ") {\n";
   }
-  o << ") {\n";
   auto decomp = [&](int lo, int hi, const std::string& src, bool with_base) {
     // define index variables i<lo>..i<hi-1> from the linear index `src`
     std::string rem = src;
@@ -877,7 +926,14 @@ KernelSpec KernelBuilder::build(const std::string& name) {
       if (!last_nonunit) rem = "(" + rem + ") / (" + I + ")" + std::to_string(F_[j]);
     }
   };
-  if (mode_ == EW) {
+  if (mode_ == EPI) {
+    decomp(0, nv_, "flat0", true);
+    o << pre_sec_[0];
+    o << "#pragma unroll\n      for (int v = 0; v < " << V_ << "; ++v) {\n";
+    if (used_vars_.count(nv_ - 1)) o << "        const " << I << " i" << nv_ - 1 << " = ib + v;\n";
+    if (used_flat_) o << "        const " << I << " flat = flat0 + v;\n";
+    o << lane_sec_[0] << "      }\n" << post_sec_[0] << "}\n";
+  } else if (mode_ == EW) {
     int64_t nvec = numel_ / V_;
     o << "  const " << I << " nvec = (" << I << ")" << nvec << "LL;\n";
     o << "  for (" << I << " g = (" << I << ")blockIdx.x * " << block_ << " + threadIdx.x; g < nvec; g += (" << I << ")gridDim.x * " << block_ << ") {\n";
@@ -965,6 +1021,7 @@ namespace {
 
 struct Unit {           // one launch-to-be
   enum Kind { ROW, EW, GEMM, ALLREDUCE } kind = EW;
+  bool fused_epilogue = false;   // GEMM whose epilogue computes `stores`
   std::vector<int64_t> F;
   int k = 0;
   std::vector<int> perm;
@@ -1062,6 +1119,8 @@ std::string Plan::describe() const {
 bool plan_dot(Plan& plan, int node, std::vector<int>& need_materialised, GemmSpec* out);
 void canonicalize_dots(Graph& g);
 void rewrite_quantised_linears(Graph& g);
+int tc_pick_bn(int64_t m, int64_t n, int64_t batch, int sm_count);
+int tc_smem_bytes(int bn);
 
 std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
   auto plan = std::make_unique<Plan>();
@@ -1383,8 +1442,50 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       }
       propagate_alias();
 
+      // ---- a matrix product absorbs the elementwise kernel that consumes it ---------------------
+      std::set<int> fused_dots;
+      if (fusion >= 2) {
+        std::vector<std::vector<int>> consumers(N);
+        for (int n = 0; n < N; ++n)
+          if (g.nodes[n].live) for (int a : g.nodes[n].args) consumers[a].push_back(n);
+        std::set<int> outs(g.outputs.begin(), g.outputs.end());
+        for (auto& u : units) {
+          if (u.kind != Unit::EW || g.nodes[u.stores[0]].piece_of >= 0) continue;
+          std::set<int> seen, leaves, reds;
+          for (int st : u.stores) P.cone(st, seen, leaves, reds, true);
+          if (!reds.empty()) continue;
+          int D = -1, ndots = 0;
+          for (int l : leaves) if (g.nodes[l].op == "dot") { D = l; ++ndots; }
+          if (ndots != 1 || outs.count(D) || fused_dots.count(D)) continue;
+          const Node& dn = g.nodes[D];
+          const DType ta = g.nodes[dn.args[0]].dt, tb = g.nodes[dn.args[1]].dt;
+          if (!(ta == tb && (ta == NXB_BF16 || ta == NXB_F16) && (dn.dt == ta || dn.dt == NXB_F32))) continue;
+          if (shape_numel(dn.shape) != shape_numel(u.F) || shape_numel(u.F) == 0) continue;
+          bool inside = true;
+          for (int c : consumers[D]) if (!seen.count(c)) inside = false;
+          if (!inside) continue;
+          std::vector<int> need;
+          GemmSpec gs;
+          plan_dot(pl, D, need, &gs);
+          if (gs.k % 8 != 0 || gs.batch > 65535) continue;
+          try {
+            KernelBuilder dry(pl, KernelBuilder::EPI, u.F, 0, {});
+            dry.stores = u.stores;
+            dry.acc_node = D;
+            dry.force_v = 1;
+            dry.build("dry");
+          } catch (const FusionError&) {
+            continue;
+          }
+          u.kind = Unit::GEMM;
+          u.fused_epilogue = true;
+          u.gemm_node = D;
+          fused_dots.insert(D);
+        }
+      }
       // gemm + concatenate units
       for (int n : dots) {
+        if (fused_dots.count(n)) continue;
         Unit u;
         u.kind = Unit::GEMM;
         u.gemm_node = n;
@@ -1410,14 +1511,13 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         }
         if (u.kind == Unit::GEMM) {
           const Node& nd = g.nodes[u.gemm_node];
-          u.writes.insert(nd.slot);
           std::vector<int> need;
           GemmSpec gs;
           plan_dot(pl, u.gemm_node, need, &gs);
           u.reads.insert(gs.a.slot);
           u.reads.insert(gs.b.slot);
           if (gs.scale_slot >= 0) u.reads.insert(gs.scale_slot);
-          return;
+          if (!u.fused_epilogue) { u.writes.insert(nd.slot); return; }
         }
         std::set<int> seen, leaves, reds;
         for (int s : u.stores) { u.writes.insert(g.nodes[s].slot); }
@@ -1426,7 +1526,13 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         own.insert(u.reduces.begin(), u.reduces.end());
         std::function<void(int)> walk = [&](int n) {
           if (!seen.insert(n).second) return;
+          if (u.fused_epilogue && n == u.gemm_node) return;
           const Node& nd = g.nodes[n];
+          if (u.fused_epilogue && nd.alias >= 0) {
+            int a = n;
+            while (a >= 0 && g.nodes[a].alias >= 0) a = g.nodes[a].alias;
+            if (a == u.gemm_node) { for (int x : nd.args) walk(x); return; }
+          }
           if (nd.slot >= 0 && !own.count(n)) { u.reads.insert(nd.slot); return; }
           for (int a : nd.args) walk(a);
         };
@@ -1456,7 +1562,19 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           }
           if (!progress) break;
         }
-        if (order.size() != U) throw FusionError("fused kernels depend on each other");
+        if (order.size() != U) {
+          if (getenv("NXB200_DEBUG")) {
+            for (size_t i = 0; i < U; ++i) {
+              if (done[i]) continue;
+              fprintf(stderr, "[nxb200] stuck unit kind=%d gemm=%d stores=", (int)units[i].kind, units[i].gemm_node);
+              for (int st : units[i].stores) fprintf(stderr, "%s#%d ", g.nodes[st].op.c_str(), st);
+              fprintf(stderr, " waits for slots:");
+              for (int r : units[i].reads) if (!ready.count(r) && !units[i].writes.count(r)) fprintf(stderr, " %d(node %d %s)", r, pl.slots[r].node, g.nodes[pl.slots[r].node].op.c_str());
+              fprintf(stderr, "\n");
+            }
+          }
+          throw FusionError("fused kernels depend on each other");
+        }
       }
 
       // ---- generate -------------------------------------------------------------------------------
@@ -1474,6 +1592,55 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           cs.desc = "all_reduce#" + std::to_string(u.gemm_node) + " sum " + dtype_name(nd.dt) + shape_str(nd.shape) + " over the tensor-parallel group (NCCL)";
           pl.collectives.push_back(cs);
           pl.steps.push_back({Step::ALLREDUCE, (int)pl.collectives.size() - 1});
+        } else if (u.kind == Unit::GEMM && u.fused_epilogue) {
+          std::vector<int> need;
+          GemmSpec gs;
+          plan_dot(pl, u.gemm_node, need, &gs);
+          gs.bn = tc_pick_bn(gs.m, gs.n, gs.batch, 148);
+          const std::string kname = "nxb_k" + std::to_string(kid++) + "_gemm";
+          // the epilogue in two widths: whole 16-byte vectors, and single elements for ragged edges
+          KernelBuilder ks1(pl, KernelBuilder::EPI, u.F, 0, {});
+          ks1.stores = u.stores; ks1.acc_node = u.gemm_node; ks1.force_v = 1;
+          KernelSpec f1 = ks1.build(kname + "_epi1");
+          KernelBuilder ksv(pl, KernelBuilder::EPI, u.F, 0, {});
+          ksv.stores = u.stores; ksv.acc_node = u.gemm_node; ksv.force_v = (gs.n % 8 == 0) ? 8 : 1; ksv.seed_args = f1.arg_slots;
+          KernelSpec fv = ksv.build(kname + "_epiv");
+          if (fv.arg_slots.size() != f1.arg_slots.size()) {
+            KernelBuilder again(pl, KernelBuilder::EPI, u.F, 0, {});
+            again.stores = u.stores; again.acc_node = u.gemm_node; again.force_v = 1; again.seed_args = fv.arg_slots;
+            f1 = again.build(kname + "_epi1");
+          }
+          if (fv.arg_slots != f1.arg_slots) throw FusionError("epilogue variants disagree on their arguments");
+          const int V = ksv.vec_width();
+          const std::string I = ksv.idx_type();
+          const DType ta = g.nodes[g.nodes[u.gemm_node].args[0]].dt;
+          std::ostringstream o;
+          o << fv.source << f1.source;
+          o << "struct EpiGen {\n  static __device__ __forceinline__ void store(const nxb_gemm::TcParams& p, float (&f)[32], const uint32_t (&raw)[32], long long b, long long m, long long n0) {\n";
+          o << "    const " << I << " flat0 = (" << I << ")((b * p.m + m) * p.n + n0);\n";
+          o << "    if (n0 + 32 <= p.n) {\n#pragma unroll\n      for (int j = 0; j < 32; j += " << V << ") " << kname << "_epiv(f + j, flat0 + j, p.ep);\n    } else {\n";
+          o << "      for (int j = 0; j < 32 && n0 + j < p.n; ++j) " << kname << "_epi1(f + j, flat0 + j, p.ep);\n    }\n  }\n};\n";
+          o << "extern \"C\" __global__ void __launch_bounds__(192, 1) " << kname
+            << "(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const nxb_gemm::TcParams p) {\n"
+            << "  nxb_gemm::tc_gemm_body<" << (ta == NXB_BF16 ? "nxb_gemm::KIND_BF16" : "nxb_gemm::KIND_F16") << ", " << gs.bn << ", EpiGen>(map_a, map_b, p);\n}\n";
+          KernelSpec ks;
+          ks.name = kname;
+          ks.source = o.str();
+          ks.block = 192;
+          ks.smem = (unsigned)tc_smem_bytes(gs.bn);
+          ks.arg_slots = fv.arg_slots;
+          ks.arg_offsets.assign(ks.arg_slots.size(), 0);
+          ks.tensor_core = true;
+          std::ostringstream d;
+          d << gs.desc << " tile=128x" << gs.bn << " fused epilogue -> stores=[";
+          for (size_t i = 0; i < u.stores.size(); ++i) d << (i ? "," : "") << g.nodes[u.stores[i]].op << "#" << u.stores[i];
+          d << "] (" << kname << ")";
+          ks.desc = d.str();
+          gs.desc = ks.desc;
+          pl.kernels.push_back(std::move(ks));
+          gs.jit_kernel = (int)pl.kernels.size() - 1;
+          pl.gemms.push_back(gs);
+          pl.steps.push_back({Step::GEMM, (int)pl.gemms.size() - 1});
         } else if (u.kind == Unit::GEMM) {
           std::vector<int> need;
           GemmSpec gs;
@@ -1501,7 +1668,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     }
   }
 
-  for (auto& ks : plan->kernels) ks.cubin = compile_to_cubin(ks.source, ks.name);
+  for (auto& ks : plan->kernels) ks.cubin = compile_to_cubin(ks.source, ks.name, ks.tensor_core);
   return plan;
 }
 

@@ -28,6 +28,19 @@ void launch_simt_gemm(const GemmArgs& g, cudaStream_t stream);
 // Tensor-core product (tcgen05 + TMA).  Needs both operands K-major (ta == tb == false).
 bool tc_gemm_supported(const GemmArgs& g);
 void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStream_t stream);
+// Everything a generated tensor-core kernel needs at launch: the two tensor maps and the
+// parameter block, laid out as the device code expects.
+struct TcLaunch {
+  alignas(64) unsigned char map_a[128];
+  alignas(64) unsigned char map_b[128];
+  alignas(16) unsigned char params[256];
+  unsigned grid = 1;
+  int smem = 0;
+};
+int tc_pick_bn(int64_t m, int64_t n, int64_t batch, int sm_count);
+int tc_smem_bytes(int bn);
+void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int* status_word, int sm_count, TcLaunch* out);
+const char* gemm_device_source();
 void launch_transpose(const void* in, void* out, int64_t batch, int64_t rows, int64_t cols, size_t elem_size, cudaStream_t stream);
 
 }  // namespace nxb

@@ -86,9 +86,11 @@ const char* device_lib_source() {
   return src;
 }
 
-std::string compile_to_cubin(const std::string& source, const std::string& name) {
+const char* gemm_device_source();
+
+std::string compile_to_cubin(const std::string& source, const std::string& name, bool tensor_core) {
   nvrtcProgram prog;
-  std::string full = std::string(device_lib_source()) + "\n" + source;
+  std::string full = std::string(device_lib_source()) + "\n" + (tensor_core ? std::string(gemm_device_source()) + "\n" : std::string()) + source;
   if (nvrtcCreateProgram(&prog, full.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS)
     fail(NXB_ERR_RUNTIME, "nvrtcCreateProgram failed");
   const char* opts[] = {"-arch=sm_100a", "-std=c++17", "-lineinfo", "--use_fast_math=false", "-default-device"};

@@ -49,6 +49,7 @@ struct KernelSpec {
   unsigned grid = 1, block = 1, smem = 0;
   std::vector<int> arg_slots;     // one pointer argument per entry
   std::vector<size_t> arg_offsets;  // byte offset added to the slot's base pointer
+  bool tensor_core = false;       // a generated matrix-product kernel (needs the GEMM device source)
 };
 
 // Operand of a matrix product as a strided batch of row-major matrices.
@@ -70,6 +71,10 @@ struct GemmSpec {
   int epilogue = 0;
   int bias_slot = -1;
   int scale_slot = -1;
+  // >= 0: index of a generated kernel (plan.kernels) whose epilogue computes and stores the
+  // consumers of this product; the product itself is then never written to memory
+  int jit_kernel = -1;
+  int bn = 256;
 };
 
 struct CollectiveSpec {
@@ -99,7 +104,7 @@ struct Plan {
 std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes);
 
 // NVRTC: compile CUDA source to an sm_100a cubin (needs no GPU).
-std::string compile_to_cubin(const std::string& source, const std::string& name);
+std::string compile_to_cubin(const std::string& source, const std::string& name, bool tensor_core = false);
 const char* device_lib_source();
 
 }  // namespace nxb
