@@ -282,6 +282,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decoder", action="store_true")
     ap.add_argument("--all-configs", action="store_true")
+    ap.add_argument("--profile-gemm", type=int, default=0, metavar="N",
+                    help="run only an N^3 bf16 dense product with the fused bias+gelu epilogue (ncu captures of the tensor-core kernel)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -301,6 +303,12 @@ def main():
     backend.set_default_backend("b200", local)
     lib = nif.lib()
     timer = Timer(lib, local)
+    if args.profile_gemm:
+        n = args.profile_gemm
+        ms_, prog_ = time_program(timer, configs.dense_bias_gelu, configs.dense_inputs(m=n, n=n, k=n), local, steps=args.steps)
+        print(json.dumps({"workload": f"dense bf16 {n}^3 + bias + gelu", "ms": round(ms_, 4), "tflops": round(2 * n ** 3 / ms_ / 1e9, 1),
+                          "plan": prog_.describe().strip().split("\n")}))
+        return
     rows = args.rows
     x_host = configs.fused_rows_input(rows, COLS, SEED)
     x = nx.tensor(x_host)

@@ -149,6 +149,13 @@ public:
 private:
   int V_ = 1, T_ = 32, block_ = 256, rpc_ = 1, chunks_ = 1;
   bool cache_ = false, guard_ = false, big_ = false;
+  // Row staging: full-row inputs of a one-CTA-per-row kernel are brought into shared memory by a
+  // bulk copy issued one row ahead, so the load of row r+1 overlaps the arithmetic of row r.
+  bool stage_ = false;
+  struct Staged { std::string param, stype; int64_t bytes, offset; };
+  std::vector<Staged> staged_;
+  std::string stage_load_sec_;
+  int64_t stage_bytes_ = 0;
 
   // code sinks
   int phase_ = 0, nphases_ = 1;
@@ -384,7 +391,19 @@ KernelBuilder::Val KernelBuilder::load(int n, const std::vector<Aff>& idx) {
       if (it == cached_loads_.end()) {
         std::string v = newvar("lv");
         decls_ += "      " + Rt + " " + v + "[" + std::to_string(chunks_) + "][" + std::to_string(V_) + "];\n";
-        pre_sec_[phase_] += "          ld_vec<" + S + ", " + std::to_string(V_) + ">(" + p + " + " + affstr(addr, true) + ", " + v + "[ch]);\n";
+        const int64_t row_bytes = C_ * (int64_t)dtype_size(nd.dt);
+        const bool flat_row = addr.c == 0 && addr.k == cstrides(F_) && nv_ > 1;
+        if (stage_ && phase_ == 0 && flat_row && row_bytes % 16 == 0 && stage_bytes_ + row_bytes <= 200 * 1024) {
+          Staged sg{p, S, row_bytes, stage_bytes_};
+          stage_bytes_ += (row_bytes + 127) / 128 * 128;
+          staged_.push_back(sg);
+          // loaded by a loop of its own ahead of phase 0, so the buffer is free again at once
+          stage_load_sec_ += "          if (use_stage) ld_vec<" + S + ", " + std::to_string(V_) + ">(reinterpret_cast<const " + S + "*>(stage_buf + " +
+                             std::to_string(sg.offset) + ") + col0, " + v + "[ch]);\n          else ld_vec<" + S + ", " + std::to_string(V_) + ">(" + p +
+                             " + rowbase + col0, " + v + "[ch]);\n";
+        } else {
+          pre_sec_[phase_] += "          ld_vec<" + S + ", " + std::to_string(V_) + ">(" + p + " + " + affstr(addr, true) + ", " + v + "[ch]);\n";
+        }
         it = cached_loads_.emplace(key, std::make_pair(v, phase_)).first;
       }
       return {it->second.first + "[ch][v]", true};
@@ -778,6 +797,8 @@ void KernelBuilder::configure() {
     guard_ = (per % T_) != 0;
     if (T_ >= 64) { block_ = T_; rpc_ = 1; } else { block_ = 128; rpc_ = 4; }
     cache_ = chunks_ * V_ <= 32 && chunks_ <= 16;
+    // worth it when a CTA is so large that only one fits per SM (nothing else hides the load)
+    stage_ = cache_ && rpc_ == 1 && !guard_ && block_ >= 512 && perm_.empty() && R_ > 148;
   } else {
     block_ = 256;
   }
@@ -804,6 +825,9 @@ KernelSpec KernelBuilder::build(const std::string& name) {
   post_sec_.assign(nphases_ + 1, "");
   elem_memo_.assign(nphases_ + 1, {});
   std::vector<std::string> red_init(nphases_ + 1), red_fin(nphases_ + 1);
+  struct Fin { bool arg; std::string acc, res, op, rt, out_rt, round; };
+  std::vector<std::vector<Fin>> fins(nphases_ + 1);
+  int scratch_slots = 2;
 
   std::vector<int> row_stores;
   for (phase_ = 0; phase_ < nphases_; ++phase_) {
@@ -831,8 +855,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
         std::string tpl = std::string(is_max ? "true" : "false") + ", " + (high ? "true" : "false");
         red_init[phase_] += "      ArgPair<" + RT + "> " + acc + "; " + acc + ".v = (" + RT + ")0; " + acc + ".i = -1;\n";
         lane_sec_[phase_] += "        arg_step<" + tpl + ">(" + acc + ", " + x.v + ", (long long)(col0 + v));\n";
-        red_fin[phase_] += "      const " + std::string(reg_type(nd.dt)) + " " + res + " = (" + reg_type(nd.dt) + ")row_arg_reduce<" + tpl + ", " + RT + ", " + T + ">(" + acc +
-                           ", scratch).i;\n";
+        fins[phase_].push_back({true, acc, res, tpl, RT, reg_type(nd.dt), ""});
       } else {
         DType ot = nd.dt;
         const std::string RT = reg_type(ot);
@@ -853,10 +876,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
         // narrow integer accumulators are widened to 32 bits for the shuffle
         red_init[phase_] += "      " + RT + " " + acc + " = " + init + ";\n";
         lane_sec_[phase_] += "        " + acc + " = " + opn + "::apply(" + acc + ", " + xv + ");\n";
-        std::string fin = "row_reduce<" + opn + ", " + RT + ", " + T + ">(" + acc + ", scratch)";
-        if (ot == NXB_BF16) fin = "round_bf16(" + fin + ")";
-        if (ot == NXB_F16) fin = "round_f16(" + fin + ")";
-        red_fin[phase_] += "      const " + RT + " " + res + " = " + fin + ";\n";
+        fins[phase_].push_back({false, acc, res, opn, RT, RT, ot == NXB_BF16 ? "round_bf16" : ot == NXB_F16 ? "round_f16" : ""});
       }
       red_var_[r] = res;
     }
@@ -868,6 +888,38 @@ KernelSpec KernelBuilder::build(const std::string& name) {
         if (level(s) != phase_) continue;
       }
       emit_store(s);
+    }
+  }
+  // finish the reductions of each phase together: one pair of barriers per phase
+  for (int p = 0; p < nphases_; ++p) {
+    if (fins[p].empty()) continue;
+    const std::string T = std::to_string(T_);
+    std::string& o = red_fin[p];
+    int slot = 0;
+    std::vector<int> slots;
+    for (auto& f : fins[p]) {
+      if (f.arg) o += "      ArgPair<" + f.rt + "> w_" + f.res + " = warp_arg_reduce<" + f.op + ">(" + f.acc + ");\n";
+      else o += "      " + f.rt + " w_" + f.res + " = warp_reduce<" + f.op + ">(" + f.acc + ");\n";
+      slots.push_back(slot);
+      slot += f.arg ? 2 : 1;
+    }
+    scratch_slots = std::max(scratch_slots, slot);
+    if (T_ > 32) {
+      o += "      __syncthreads();\n      if ((threadIdx.x & 31) == 0) {\n";
+      for (size_t i = 0; i < fins[p].size(); ++i) {
+        auto& f = fins[p][i];
+        o += std::string("        ") + (f.arg ? "park_arg_partial<" : "park_partial<") + f.rt + ">(scratch, " + std::to_string(slots[i]) + ", w_" + f.res + ");\n";
+      }
+      o += "      }\n      __syncthreads();\n";
+      for (size_t i = 0; i < fins[p].size(); ++i) {
+        auto& f = fins[p][i];
+        if (f.arg) o += "      w_" + f.res + " = fold_arg_partials<" + f.op + ", " + f.rt + ", " + T + ">(scratch, " + std::to_string(slots[i]) + ");\n";
+        else o += "      w_" + f.res + " = fold_partials<" + f.op + ", " + f.rt + ", " + T + ">(scratch, " + std::to_string(slots[i]) + ");\n";
+      }
+    }
+    for (auto& f : fins[p]) {
+      if (f.arg) o += "      const " + f.out_rt + " " + f.res + " = (" + f.out_rt + ")w_" + f.res + ".i;\n";
+      else o += "      const " + f.out_rt + " " + f.res + " = " + (f.round.empty() ? "w_" + f.res : f.round + "(w_" + f.res + ")") + ";\n";
     }
   }
   // results of reductions that are themselves kernel outputs, and other per-row values
@@ -945,14 +997,44 @@ KernelSpec KernelBuilder::build(const std::string& name) {
     if (used_flat_) o << "        const " << I << " flat = flat0 + v;\n";
     o << lane_sec_[0] << "      }\n" << post_sec_[0] << "  }\n}\n";
   } else {
-    o << "  __shared__ long long scratch_all[" << 64 << "];\n";
+    o << "  __shared__ long long scratch_all[" << 32 * scratch_slots << "];\n";
     o << "  void* scratch = scratch_all;\n";
     if (rpc_ > 1) o << "  const int tid = threadIdx.x & 31;\n  const " << I << " row_in_cta = threadIdx.x >> 5;\n";
     else o << "  const int tid = threadIdx.x;\n  const " << I << " row_in_cta = 0;\n";
+    const bool staging = !staged_.empty();
+    std::string issue_copies;      // lane 0 posts the byte count and one bulk copy per staged input
+    if (staging) {
+      int64_t total = 0;
+      for (auto& sg : staged_) total += sg.bytes;
+      issue_copies = "stg_expect(&stage_bar, " + std::to_string(total) + "u);";
+      for (auto& sg : staged_)
+        issue_copies += " stg_copy(stage_buf + " + std::to_string(sg.offset) + ", " + sg.param + " + NEXT_ROW * (" + I + ")" + std::to_string(C_) + "LL, " +
+                        std::to_string(sg.bytes) + "u, &stage_bar);";
+      o << "  extern __shared__ __align__(1024) unsigned char stage_buf[];\n";
+      o << "  __shared__ unsigned long long stage_bar;\n  __shared__ int stage_off;\n";
+      o << "  if (threadIdx.x == 0) { stg_bar_init(&stage_bar); stage_off = 0; }\n  __syncthreads();\n";
+      o << "  unsigned stage_parity = 0;\n";
+      std::string first = issue_copies;
+      for (size_t pos; (pos = first.find("NEXT_ROW")) != std::string::npos;) first.replace(pos, 8, "((" + I + ")blockIdx.x)");
+      o << "  if (threadIdx.x == 0 && (" << I << ")blockIdx.x < (" << I << ")" << R_ << "LL) { " << first << " }\n";
+    }
     o << "  for (" << I << " row = (" << I << ")blockIdx.x * " << rpc_ << " + row_in_cta; row < (" << I << ")" << R_ << "LL; row += (" << I << ")gridDim.x * " << rpc_ << ") {\n";
     o << "        const " << I << " rowbase = row * (" << I << ")" << C_ << "LL;\n";
+    if (staging) {
+      o << "        bool use_stage = stage_off == 0;\n";
+      o << "        if (use_stage) { if (!stg_wait(&stage_bar, stage_parity)) { stage_off = 1; use_stage = false; } stage_parity ^= 1u; }\n";
+    }
     decomp(0, nv_ - k_, "row", false);
     o << decls_;
+    if (staging) {
+      std::string next = issue_copies;
+      for (size_t pos; (pos = next.find("NEXT_ROW")) != std::string::npos;) next.replace(pos, 8, "(row + (" + I + ")gridDim.x)");
+      o << "#pragma unroll\n      for (int ch = 0; ch < " << chunks_ << "; ++ch) {\n";
+      o << "        const " << I << " col0 = ((" << I << ")ch * " << T_ << " + tid) * " << V_ << ";\n" << stage_load_sec_ << "      }\n";
+      // every thread has its part of the row in registers: the buffer can take the next row
+      o << "      __syncthreads();\n";
+      o << "      if (threadIdx.x == 0 && stage_off == 0 && row + (" << I << ")gridDim.x < (" << I << ")" << R_ << "LL) { " << next << " }\n";
+    }
     for (int p = 0; p < nphases_; ++p) {
       o << row_sec_[p] << red_init[p];
       bool has_loop = !pre_sec_[p].empty() || !lane_sec_[p].empty() || !post_sec_[p].empty();
@@ -998,10 +1080,15 @@ KernelSpec KernelBuilder::build(const std::string& name) {
   int64_t nblocks;
   if (mode_ == EW) nblocks = (numel_ / V_ + block_ - 1) / block_;
   else nblocks = (R_ + rpc_ - 1) / rpc_;
+  if (!staged_.empty()) {
+    nblocks = std::min<int64_t>(nblocks, 148);      // persistent: one CTA per SM walks the rows
+    ks.smem = (unsigned)stage_bytes_;
+  }
   ks.grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(nblocks, 0x7fffffff));
   std::ostringstream d;
   d << name << (mode_ == EW ? " elementwise" : " row") << " space=" << shape_str(F_);
-  if (mode_ == ROW) d << " rows=" << R_ << " cols=" << C_ << " threads/row=" << T_ << " phases=" << nphases_ << (cache_ ? " row-in-registers" : " streaming");
+  if (mode_ == ROW) d << " rows=" << R_ << " cols=" << C_ << " threads/row=" << T_ << " phases=" << nphases_ << (cache_ ? " row-in-registers" : " streaming")
+                      << (staged_.empty() ? "" : " next-row-staged-in-smem");
   d << " vec=" << V_ << " grid=" << ks.grid << " block=" << ks.block << " stores=[";
   for (size_t i = 0; i < stores.size(); ++i) d << (i ? "," : "") << g_.nodes[stores[i]].op << "#" << stores[i];
   d << "] reduces=[";

@@ -110,7 +110,7 @@ NXB_DEV float nx_exp(float x) {
   c = fmaf(x, L2E_LO, c);
   float p = fast_ex2(t);
   float r = fmaf(p * c, 0.693147182464599609375f, p);
-  // p is 0 or inf at the ends of the range, where the correction would make a NaN
+  // p is 0 or inf at the ends of the range (and for infinite x, where c is NaN): return it as is
   return (p == 0.f || p == NXB_INF) ? p : r;
 }
 // 1 / (1 + exp(-x)); rcp.approx is within 1 ulp
@@ -179,6 +179,39 @@ template <typename I> NXB_DEV I nx_clz(I a) {
   return (I)(__clzll((long long)u) - (64 - (int)sizeof(I) * 8));
 }
 
+// ---- row staging: bulk copy of the next row into shared memory while this one is computed ----
+NXB_DEV uint32_t stg_smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+NXB_DEV void stg_bar_init(void* bar) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(stg_smem_addr(bar)) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+NXB_DEV void stg_expect(void* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(stg_smem_addr(bar)), "r"(bytes) : "memory");
+}
+// 1-D bulk copy global -> shared (both 16-byte aligned, size a multiple of 16), completion on `bar`
+NXB_DEV void stg_copy(void* dst, const void* src, uint32_t bytes, void* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(stg_smem_addr(dst)), "l"(src), "r"(bytes), "r"(stg_smem_addr(bar)) : "memory");
+}
+NXB_DEV bool stg_try_wait(void* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(stg_smem_addr(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait (about one second).  On expiry the caller stops using the staging buffer and
+// reads the row from global memory instead, so a lost copy costs speed, never correctness.
+NXB_DEV bool stg_wait(void* bar, uint32_t parity) {
+  if (stg_try_wait(bar, parity)) return true;
+  unsigned long long t0, t1;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  for (;;) {
+    for (int i = 0; i < 32; ++i) if (stg_try_wait(bar, parity)) return true;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t1));
+    if (t1 - t0 > 1000000000ull) return false;
+  }
+}
+
 // ---- reductions ------------------------------------------------------------------------
 // Combine operators.  Each has ::apply(a, b) on the register type.
 struct OpSum { template <typename T> static NXB_DEV T apply(T a, T b) { return a + b; } };
@@ -233,6 +266,20 @@ NXB_DEV T row_reduce(T v, void* scratch) {
     v = w;
   }
   return v;
+}
+
+// Several reductions of one phase share a single pair of barriers: every warp reduces its own
+// values with shuffles, lane 0 of each warp parks them in shared memory (one 32-entry, 8-byte
+// slot array per reduction), and after the barrier every warp folds the per-warp partials.
+template <typename T> NXB_DEV void park_partial(void* scratch, int slot, T v) {
+  reinterpret_cast<T*>(reinterpret_cast<long long*>(scratch) + slot * 32)[threadIdx.x >> 5] = v;
+}
+template <typename Op, typename T, int THREADS> NXB_DEV T fold_partials(const void* scratch, int slot) {
+  const int NW = THREADS / 32, lane = threadIdx.x & 31;
+  T w = reinterpret_cast<const T*>(reinterpret_cast<const long long*>(scratch) + slot * 32)[lane & (NW - 1)];
+#pragma unroll
+  for (int m = NW / 2; m > 0; m >>= 1) w = Op::apply(w, shfl_xor(w, m));
+  return w;
 }
 
 // (value, index) pair for argmax/argmin.  `better(a, b)` is a strict total
@@ -303,4 +350,36 @@ NXB_DEV ArgPair<T> row_arg_reduce(ArgPair<T> p, void* scratch) {
     p = w;
   }
   return p;
+}
+
+template <bool IS_MAX, bool TIE_HIGH, typename T> NXB_DEV ArgPair<T> warp_arg_reduce(ArgPair<T> p) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) {
+    ArgPair<T> o;
+    o.v = shfl_xor(p.v, m);
+    o.i = shfl_xor(p.i, m);
+    p = arg_combine<IS_MAX, TIE_HIGH>(p, o);
+  }
+  return p;
+}
+// an arg-reduction uses two slots: values in `slot`, indices in `slot + 1`
+template <typename T> NXB_DEV void park_arg_partial(void* scratch, int slot, const ArgPair<T>& p) {
+  park_partial<T>(scratch, slot, p.v);
+  park_partial<long long>(scratch, slot + 1, p.i);
+}
+template <bool IS_MAX, bool TIE_HIGH, typename T, int THREADS>
+NXB_DEV ArgPair<T> fold_arg_partials(const void* scratch, int slot) {
+  const int NW = THREADS / 32, lane = threadIdx.x & 31;
+  const long long* base = reinterpret_cast<const long long*>(scratch);
+  ArgPair<T> w;
+  w.v = reinterpret_cast<const T*>(base + slot * 32)[lane & (NW - 1)];
+  w.i = (base + (slot + 1) * 32)[lane & (NW - 1)];
+#pragma unroll
+  for (int m = NW / 2; m > 0; m >>= 1) {
+    ArgPair<T> o;
+    o.v = shfl_xor(w.v, m);
+    o.i = shfl_xor(w.i, m);
+    w = arg_combine<IS_MAX, TIE_HIGH>(w, o);
+  }
+  return w;
 }
