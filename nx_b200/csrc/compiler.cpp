@@ -165,6 +165,22 @@ private:
   std::vector<std::map<std::string, std::string>> elem_memo_;
   std::map<std::string, std::pair<std::string, int>> cached_loads_;
   std::set<int> used_vars_;
+  // 16-bit float values that are still held at f32 precision ("excess precision", what XLA does
+  // inside a fusion by default): arithmetic consumes them as they are; comparisons, index
+  // reductions, integer conversions and rounding ops first round them to their declared type.
+  std::set<std::string> raw_;
+  bool excess_ = getenv("NXB200_STRICT_ROUNDING") == nullptr;
+  std::string exact(const Val& x, DType dt) {
+    if (!raw_.count(x.v)) return x.v;
+    std::string key = "exact:" + x.v;
+    auto& memo = x.elem ? elem_memo_[phase_] : row_memo_;
+    auto it = memo.find(key);
+    if (it != memo.end()) return it->second;
+    std::string v = newvar("rx");
+    stmt(x.elem, "const float " + v + " = " + (dt == NXB_BF16 ? "round_bf16(" : "round_f16(") + x.v + ");");
+    memo[key] = v;
+    return v;
+  }
   bool used_flat_ = false;
   std::vector<int> arg_slots_;
   std::map<int, int> slot_param_;
@@ -451,7 +467,9 @@ KernelBuilder::Val KernelBuilder::value(int n, const std::vector<Aff>& idx) {
     auto it = elem_memo_[phase_].find(key);
     if (it != elem_memo_[phase_].end()) return {it->second, true};
     std::string v = newvar();
-    stmt(true, std::string("const ") + reg_type(nd.dt) + " " + v + " = " + cvt("acc[v]", NXB_F32, nd.dt) + ";");
+    const bool keep_f32 = excess_ && (nd.dt == NXB_BF16 || nd.dt == NXB_F16);
+    stmt(true, std::string("const ") + reg_type(nd.dt) + " " + v + " = " + (keep_f32 ? std::string("acc[v]") : cvt("acc[v]", NXB_F32, nd.dt)) + ";");
+    if (keep_f32) raw_.insert(v);
     elem_memo_[phase_][key] = v;
     return {v, true};
   }
@@ -593,7 +611,7 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
     const Node& a = g_.nodes[nd.args[0]];
     Val x = value(nd.args[0], idx);
     if (a.dt == t) return x;
-    return def(x.elem, t, cvt(x.v, a.dt, t));
+    return def(x.elem, t, cvt(dtype_is_float(t) ? x.v : exact(x, a.dt), a.dt, t));
   }
   if (kUnaryMath.count(op) || kUnaryOther.count(op)) {
     const Node& a = g_.nodes[nd.args[0]];
@@ -613,7 +631,8 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
       e = std::string(op == "population_count" ? "nx_popc<" : "nx_clz<") + reg_type(a.dt) + ">(" + x.v + ")";
       return def(x.elem, t, cvt(e, a.dt, t));
     }
-    std::string xv = cvt(x.v, a.dt, t);     // the argument is converted to the output type first
+    const bool exact_in = op == "floor" || op == "ceil" || op == "round" || op == "sign";
+    std::string xv = cvt(exact_in ? exact(x, a.dt) : x.v, a.dt, t);     // the argument is converted to the output type first
     if (dtype_is_float(t)) {
       static const std::map<std::string, const char*> lib = {
           {"expm1", "expm1"}, {"log1p", "log1p"}, {"cos", "cos"}, {"sin", "sin"}, {"tan", "tan"}, {"cosh", "cosh"},
@@ -627,6 +646,11 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
       else if (own.count(op)) e = std::string(own.at(op)) + "(" + xv + ")";
       else if (op == "negate") e = "-" + xv;
       else fail(NXB_ERR_INVALID_ARGUMENT, "op " + op + " is not defined for " + dtype_name(t));
+      if ((t == NXB_BF16 || t == NXB_F16) && excess_ && !exact_in) {
+        Val r = def(x.elem, t, e);
+        raw_.insert(r.v);
+        return r;
+      }
       if (t == NXB_BF16) e = "round_bf16(" + e + ")";
       if (t == NXB_F16) e = "round_f16(" + e + ")";
     } else {
@@ -647,7 +671,7 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
     Val y = value(nd.args[1], arg_index_binary(nd, b, idx));
     bool elem = x.elem || y.elem;
     if (kLogical.count(op)) {
-      std::string xa = "(" + x.v + " != 0)", yb = "(" + y.v + " != 0)";
+      std::string xa = "(" + exact(x, a.dt) + " != 0)", yb = "(" + exact(y, b.dt) + " != 0)";
       std::string o = op == "logical_and" ? " && " : op == "logical_or" ? " || " : " != ";
       return def(elem, t, "(uint8_t)(" + xa + o + yb + ")");
     }
@@ -655,7 +679,8 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
     // (exla/lib/exla/defn.ex:2380-2410)
     DType ct = dtype_merge(a.dt, b.dt);
     if (!kCompare.count(op)) ct = dtype_merge(ct, t);
-    std::string xv = cvt(x.v, a.dt, ct), yv = cvt(y.v, b.dt, ct);
+    const bool cmp = kCompare.count(op) > 0;
+    std::string xv = cvt(cmp ? exact(x, a.dt) : x.v, a.dt, ct), yv = cvt(cmp ? exact(y, b.dt) : y.v, b.dt, ct);
     std::string e;
     if (kCompare.count(op)) {
       static const std::map<std::string, const char*> sym = {{"equal", "=="}, {"not_equal", "!="}, {"greater", ">"},
@@ -690,6 +715,12 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
       else if (op == "remainder") e = std::string(dbl ? "fmod" : "fmodf") + "(" + xv + ", " + yv + ")";
       else if (op == "atan2") e = std::string(dbl ? "atan2" : "atan2f") + "(" + xv + ", " + yv + ")";
       else fail(NXB_ERR_INVALID_ARGUMENT, "op " + op + " is not defined for " + dtype_name(ct));
+      const bool keeps = op == "add" || op == "subtract" || op == "multiply" || op == "divide" || op == "max" || op == "min";
+      if ((ct == NXB_BF16 || ct == NXB_F16) && ct == t && excess_ && keeps) {
+        Val r = def(elem, t, e);
+        raw_.insert(r.v);
+        return r;
+      }
       if (ct == NXB_BF16) e = "round_bf16(" + e + ")";
       if (ct == NXB_F16) e = "round_f16(" + e + ")";
     } else {
@@ -719,7 +750,9 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
     Val pv = value(nd.args[0], arg_index_binary(nd, p, idx));
     Val x = value(nd.args[1], arg_index_binary(nd, a, idx));
     Val y = value(nd.args[2], arg_index_binary(nd, b, idx));
-    return def(pv.elem || x.elem || y.elem, t, "(" + pv.v + " != 0) ? " + cvt(x.v, a.dt, t) + " : " + cvt(y.v, b.dt, t));
+    Val r = def(pv.elem || x.elem || y.elem, t, "(" + pv.v + " != 0) ? " + cvt(x.v, a.dt, t) + " : " + cvt(y.v, b.dt, t));
+    if ((t == NXB_BF16 || t == NXB_F16) && (raw_.count(x.v) || raw_.count(y.v))) raw_.insert(r.v);
+    return r;
   }
   if (op == "clip") {
     Val x = value(nd.args[0], idx);
@@ -727,7 +760,9 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
     Val hi = value(nd.args[2], {});
     std::string e = "nx_min(nx_max(" + cvt(x.v, g_.nodes[nd.args[0]].dt, t) + ", " + cvt(lo.v, g_.nodes[nd.args[1]].dt, t) + "), " +
                     cvt(hi.v, g_.nodes[nd.args[2]].dt, t) + ")";
-    return def(x.elem || lo.elem || hi.elem, t, e);
+    Val r = def(x.elem || lo.elem || hi.elem, t, e);
+    if ((t == NXB_BF16 || t == NXB_F16) && raw_.count(x.v)) raw_.insert(r.v);
+    return r;
   }
   throw FusionError("op " + op + " cannot be generated inline");
 }
@@ -854,7 +889,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
         bool is_max = nd.op == "argmax", high = nd.ints[0] != 0;
         std::string tpl = std::string(is_max ? "true" : "false") + ", " + (high ? "true" : "false");
         red_init[phase_] += "      ArgPair<" + RT + "> " + acc + "; " + acc + ".v = (" + RT + ")0; " + acc + ".i = -1;\n";
-        lane_sec_[phase_] += "        arg_step<" + tpl + ">(" + acc + ", " + x.v + ", (long long)(col0 + v));\n";
+        lane_sec_[phase_] += "        arg_step<" + tpl + ">(" + acc + ", " + exact(x, in.dt) + ", (long long)(col0 + v));\n";
         fins[phase_].push_back({true, acc, res, tpl, RT, reg_type(nd.dt), ""});
       } else {
         DType ot = nd.dt;
@@ -871,8 +906,8 @@ KernelSpec KernelBuilder::build(const std::string& name) {
           int bits = (int)dtype_size(ot) * 8;
           int64_t mx = dtype_is_signed(ot) ? (int64_t)(((uint64_t)1 << (bits - 1)) - 1) : (bits == 64 ? -1 : (int64_t)(((uint64_t)1 << bits) - 1));
           init = dtype_is_float(ot) ? (ot == NXB_F64 ? "(double)NXB_INF" : "NXB_INF") : literal(0, mx, false, ot);
-        } else if (nd.op == "all") { init = "(uint8_t)1"; opn = "OpAnd"; xv = "(uint8_t)(" + x.v + " != 0)"; }
-        else { init = "(uint8_t)0"; opn = "OpOr"; xv = "(uint8_t)(" + x.v + " != 0)"; }
+        } else if (nd.op == "all") { init = "(uint8_t)1"; opn = "OpAnd"; xv = "(uint8_t)(" + exact(x, in.dt) + " != 0)"; }
+        else { init = "(uint8_t)0"; opn = "OpOr"; xv = "(uint8_t)(" + exact(x, in.dt) + " != 0)"; }
         // narrow integer accumulators are widened to 32 bits for the shuffle
         red_init[phase_] += "      " + RT + " " + acc + " = " + init + ";\n";
         lane_sec_[phase_] += "        " + acc + " = " + opn + "::apply(" + acc + ", " + xv + ");\n";
