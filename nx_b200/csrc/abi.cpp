@@ -197,7 +197,7 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
             }
             TcLaunch tl;
             tc_prepare_launch(ga, gs.bn, ep.data(), (int)ep.size(), d.status_dev, d.sm_count, &tl);
-            void* params[3] = {tl.map_a, tl.map_b, tl.params};
+            void* params[4] = {tl.map_a, tl.map_b, tl.map_c, tl.params};
             check_cu(drv.cuLaunchKernel(L.functions[gs.jit_kernel], tl.grid, 1, 1, 192, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
                      ("launching " + ks.name).c_str());
           } else {

@@ -1738,13 +1738,13 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           const DType ta = g.nodes[g.nodes[u.gemm_node].args[0]].dt;
           std::ostringstream o;
           o << fv.source << f1.source;
-          o << "struct EpiGen {\n  static __device__ __forceinline__ void store(const nxb_gemm::TcParams& p, float (&f)[32], const uint32_t (&raw)[32], long long b, long long m, long long n0) {\n";
+          o << "struct EpiGen {\n  static constexpr bool kStaged = false;\n  static __device__ __forceinline__ void store(const nxb_gemm::TcParams& p, float (&f)[32], const uint32_t (&raw)[32], long long b, long long m, long long n0) {\n";
           o << "    const " << I << " flat0 = (" << I << ")((b * p.m + m) * p.n + n0);\n";
           o << "    if (n0 + 32 <= p.n) {\n#pragma unroll\n      for (int j = 0; j < 32; j += " << V << ") " << kname << "_epiv(f + j, flat0 + j, p.ep);\n    } else {\n";
           o << "      for (int j = 0; j < 32 && n0 + j < p.n; ++j) " << kname << "_epi1(f + j, flat0 + j, p.ep);\n    }\n  }\n};\n";
           o << "extern \"C\" __global__ void __launch_bounds__(192, 1) " << kname
-            << "(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const nxb_gemm::TcParams p) {\n"
-            << "  nxb_gemm::tc_gemm_body<" << (ta == NXB_BF16 ? "nxb_gemm::KIND_BF16" : "nxb_gemm::KIND_F16") << ", " << gs.bn << ", EpiGen>(map_a, map_b, p);\n}\n";
+            << "(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const nxb_gemm::TcParams p) {\n"
+            << "  nxb_gemm::tc_gemm_body<" << (ta == NXB_BF16 ? "nxb_gemm::KIND_BF16" : "nxb_gemm::KIND_F16") << ", " << gs.bn << ", EpiGen>(map_a, map_b, map_c, p);\n}\n";
           KernelSpec ks;
           ks.name = kname;
           ks.source = o.str();

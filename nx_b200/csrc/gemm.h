@@ -33,6 +33,7 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
 struct TcLaunch {
   alignas(64) unsigned char map_a[128];
   alignas(64) unsigned char map_b[128];
+  alignas(64) unsigned char map_c[128];
   alignas(16) unsigned char params[256];
   unsigned grid = 1;
   int smem = 0;

@@ -27,8 +27,9 @@ using namespace nxb_gemm;
 
 template <int KIND, int BN>
 __global__ void __launch_bounds__(192, 1)
-tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcParams p) {
-  tc_gemm_body<KIND, BN, EpiStore>(map_a, map_b, p);
+tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const __grid_constant__ CUtensorMap map_c, TcParams p) {
+  tc_gemm_body<KIND, BN, EpiStore>(map_a, map_b, map_c, p);
 }
 
 CUtensorMapDataType tm_type(DType t) {
@@ -73,6 +74,29 @@ CUtensorMap make_map_mn(const void* ptr, DType dt, int64_t k, int64_t rows, int6
                                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
            "cuTensorMapEncodeTiled");
   return m;
+}
+
+// Result C [batch][m][n] for the staged store: boxes of 32 x 32 elements, swizzled like the
+// staging tiles (64-byte rows for 2-byte elements, 128-byte rows for 4-byte ones).  When C cannot
+// be described (rows not 16-byte aligned) a map over a dummy is returned and *ok is false.
+CUtensorMap make_map_c(void* ptr, DType dt, int64_t m, int64_t n, int64_t batch, bool* ok) {
+  const DriverApi& drv = driver();
+  CUtensorMap t;
+  memset(&t, 0, sizeof t);
+  const size_t es = dtype_size(dt);
+  *ok = ptr && (es == 2 || es == 4) && (n * es) % 16 == 0 && ((uintptr_t)ptr) % 16 == 0 && dt != NXB_U16 && dt != NXB_S16;
+  if (!*ok) return t;
+  CUtensorMapDataType ty = dt == NXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : dt == NXB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                           : dt == NXB_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_INT32;
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)(n * es), (cuuint64_t)(m * n * es)};
+  cuuint32_t box[3] = {32, 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  check_cu(drv.cuTensorMapEncodeTiled(&t, ty, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                      es == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+           "cuTensorMapEncodeTiled (result)");
+  return t;
 }
 
 // out[b][c][r] = in[b][r][c] for 1- and 2-byte elements (operands whose reduction index is
@@ -163,8 +187,12 @@ void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int
   TcParams p = make_params(g, bn, status_word);
   if (n_ep > (int)(sizeof(p.ep) / sizeof(p.ep[0]))) fail(NXB_ERR_UNSUPPORTED, "fused epilogue reads too many buffers");
   for (int i = 0; i < n_ep; ++i) p.ep[i] = ep[i];
+  bool c_ok = false;
+  CUtensorMap mc = make_map_c(nullptr, g.dc, g.m, g.n, g.batch, &c_ok);    // generated epilogues store by themselves
+  p.tma_store = 0;
   memcpy(out->map_a, &ma, 128);
   memcpy(out->map_b, &mb, 128);
+  memcpy(out->map_c, &mc, 128);
   memcpy(out->params, &p, sizeof p);
   long long tiles = (long long)p.mtiles * p.ntiles * p.batch;
   out->grid = (unsigned)std::min<long long>(tiles, sm_count);
@@ -176,11 +204,14 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
   CUtensorMap ma = g.ta ? make_map_mn(g.a, g.da, g.k, g.m, g.batch, g.lda, g.bsa) : make_map(g.a, g.da, g.k, g.m, g.batch, g.lda, g.bsa, BM);
   CUtensorMap mb = g.tb ? make_map_mn(g.b, g.db, g.k, g.n, g.batch, g.ldb, g.bsb) : make_map(g.b, g.db, g.k, g.n, g.batch, g.ldb, g.bsb, bn);
   TcParams p = make_params(g, bn, status_word);
+  bool c_ok = false;
+  CUtensorMap mc = make_map_c(g.c, g.dc, g.m, g.n, g.batch, &c_ok);
+  p.tma_store = c_ok ? 1 : 0;
   long long tiles = (long long)p.mtiles * p.ntiles * p.batch;
   unsigned grid = (unsigned)std::min<long long>(tiles, sm_count);
   auto launch = [&](auto kern, int smem) {
     NXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, 192, smem, stream>>>(ma, mb, p);
+    kern<<<grid, 192, smem, stream>>>(ma, mb, mc, p);
     NXB_CUDA(cudaGetLastError());
   };
 #define NXB_LAUNCH_KIND(K)                                                      \

@@ -20,7 +20,10 @@ constexpr int A_STAGE = BM * ROW_BYTES;
 // applied to 1..128 tokens) use 128 or 64 so that enough tiles exist to occupy every SM, with a
 // deeper ring since the product is then bound by streaming the weights.
 __host__ __device__ constexpr int stages_for(int bn) { return bn == 256 ? 4 : bn == 128 ? 6 : 8; }
-__host__ __device__ constexpr int smem_bytes_for(int bn) { return stages_for(bn) * (A_STAGE + bn * ROW_BYTES) + 1024 /*alignment*/ + 256 /*barriers*/; }
+constexpr int STORE_STAGE = 4 * 2 * 4096;   // per epilogue warp: two 32x32 staging tiles of up to 4 bytes per element
+__host__ __device__ constexpr int smem_bytes_for(int bn) {
+  return stages_for(bn) * (A_STAGE + bn * ROW_BYTES) + STORE_STAGE + 1024 /*alignment*/ + 256 /*barriers*/;
+}
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 enum Kind { KIND_BF16 = 0, KIND_F16 = 1, KIND_S8 = 2 };
@@ -35,6 +38,7 @@ struct TcParams {
   int out_dt;        // nxb200_dtype of C
   int epilogue;
   int a_mn, b_mn;    // operand stored with its free index contiguous ([k][m] / [k][n]) instead of k
+  int tma_store;     // results leave through shared memory and a TMA store (rows of C 16-byte aligned)
   void* ep[14];      // buffers of a generated epilogue, in its argument order
 };
 
@@ -143,9 +147,16 @@ __device__ __forceinline__ unsigned short f32_to_f16_bits(float f) {
   return h;
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"((unsigned long long)map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 // Default epilogue: convert the 32 accumulator values of one row segment to the output type
 // and store them (128-bit stores when the segment is complete and rows are 16-byte aligned).
 struct EpiStore {
+  static constexpr bool kStaged = true;     // may leave through the shared-memory staged TMA store
   static __device__ __forceinline__ void store(const TcParams& p, float (&f)[32], const uint32_t (&v)[32], long long b, long long m, long long n0) {
     const long long rowoff = (b * p.m + m) * p.n;
     const bool vec_ok = (p.n % 8) == 0;
@@ -185,7 +196,7 @@ struct EpiStore {
 };
 
 template <int KIND, int BN, class Epi>
-__device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUtensorMap& map_b, const TcParams& p) {
+__device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const TcParams& p) {
   extern __shared__ unsigned char smem_raw[];
   constexpr int STAGES = stages_for(BN);
   constexpr int B_STAGE = BN * ROW_BYTES;
@@ -195,7 +206,8 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
 
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA = base, sB = base + STAGES * A_STAGE;
-  const uint32_t bars = sB + STAGES * B_STAGE;
+  const uint32_t sStore = sB + STAGES * B_STAGE;          // 1024-byte aligned: stage sizes are multiples of 8 KB
+  const uint32_t bars = sStore + STORE_STAGE;
   const uint32_t full0 = bars, empty0 = bars + 8 * STAGES, tfull0 = bars + 16 * STAGES, tempty0 = tfull0 + 16;
   const uint32_t tmem_slot = tempty0 + 16;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -287,6 +299,7 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
   } else {
     // epilogue warps 2..5; a warp may only read the TMEM lanes of its quarter (warp id mod 4)
     const int q = warp & 3;
+    uint32_t store_iter = 0;
     int a = 0;
     uint32_t aph = 0;
     bool ok = true;
@@ -297,11 +310,60 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       if (!mbar_wait(tfull0 + 8 * a, aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const long long m = (long long)mt * BM + q * 32 + lane;
+      const bool staged = Epi::kStaged && p.tma_store != 0;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c * 32), v);
         const long long n0 = (long long)nt * BN + c * 32;
+        if (staged) {
+          // 32 rows x 32 columns of this warp go to a swizzled staging tile; one lane hands the
+          // tile to the TMA unit, which writes full lines and clips at the matrix edges.
+          if ((long long)mt * BM + q * 32 >= p.m || n0 >= p.n) continue;      // warp-uniform
+          // each warp owns 8 KB of staging: four 2 KB tiles for 2-byte results, two 4 KB tiles otherwise
+          const bool two_byte = p.out_dt == NXB_BF16 || p.out_dt == NXB_F16;
+          const uint32_t buf = sStore + (uint32_t)(warp - 2) * 8192u + (two_byte ? (store_iter & 3) * 2048u : (store_iter & 1) * 4096u);
+          if (lane == 0) {   // the tile about to be overwritten must have been read by the TMA unit
+            if (two_byte) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          }
+          __syncwarp();
+          float f[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) f[j] = (KIND == KIND_S8) ? (float)(int)v[j] : __uint_as_float(v[j]);
+          if (p.scale) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) if (n0 + j < p.n) f[j] *= p.scale[n0 + j];
+          }
+          if (p.out_dt == NXB_BF16 || p.out_dt == NXB_F16) {
+            // rows of 64 bytes, 64-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              unsigned short h[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) h[e] = p.out_dt == NXB_BF16 ? f32_to_bf16_bits(f[j * 8 + e]) : f32_to_f16_bits(f[j * 8 + e]);
+              const uint32_t dst = buf + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) * 16);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(h[0] | ((uint32_t)h[1] << 16)), "r"(h[2] | ((uint32_t)h[3] << 16)),
+                           "r"(h[4] | ((uint32_t)h[5] << 16)), "r"(h[6] | ((uint32_t)h[7] << 16)) : "memory");
+            }
+          } else {
+            // 4-byte results: rows of 128 bytes, 128-byte swizzle: chunk j of row r sits at chunk j ^ (r & 7)
+            const bool as_int = p.out_dt == NXB_S32 || p.out_dt == NXB_U32;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint32_t w[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) w[e] = as_int ? v[j * 4 + e] : __float_as_uint(f[j * 4 + e]);
+              const uint32_t dst = buf + (uint32_t)lane * 128u + (uint32_t)((j ^ (lane & 7)) * 16);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+            }
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) tma_store_3d(&map_c, buf, (int)n0, mt * BM + q * 32, b);
+          ++store_iter;
+          continue;
+        }
         if (m < p.m && n0 < p.n) {
           float f[32];
 #pragma unroll
@@ -318,6 +380,8 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       if (lane == 0) mbar_arrive(tempty0 + 8 * a);
       if (++a == 2) { a = 0; aph ^= 1; }
     }
+    // the staging tiles must stay valid until the TMA unit has read them
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   // teardown: everyone meets, copies in flight are given time to land if a wait gave up
