@@ -149,6 +149,17 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         }
         check_cu(drv.cuLaunchKernel(L.functions[step.index], ks.grid, 1, 1, ks.block, 1, 1, ks.smem, (CUstream)d.stream, argp.data(), nullptr),
                  ("launching " + ks.name).c_str());
+      } else if (step.kind == Step::ATTENTION) {
+        const AttentionSpec& as = plan.attentions[step.index];
+        const KernelSpec& ks = plan.kernels[as.jit_kernel];
+        std::vector<void*> ep(ks.arg_slots.size());
+        for (size_t a = 0; a < ks.arg_slots.size(); ++a) ep[a] = ptr[ks.arg_slots[a]];
+        TcLaunch tl;
+        attn_prepare_launch(ptr[as.q_slot], ptr[as.k_slot], ptr[as.v_slot], ptr[as.out_slot], as.batch_heads, as.sq, as.sk, as.causal, ep.data(),
+                            (int)ep.size(), d.status_dev, &tl);
+        void* params[4] = {tl.map_a, tl.map_b, tl.map_c, tl.params};
+        check_cu(drv.cuLaunchKernel(L.functions[as.jit_kernel], tl.grid, 1, 1, 192, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
+                 ("launching " + ks.name).c_str());
       } else if (step.kind == Step::ALLREDUCE) {
         const CollectiveSpec& cs = plan.collectives[step.index];
         comm_all_reduce(ptr[cs.in_slot], ptr[cs.out_slot], (size_t)cs.count, cs.dt, d);

@@ -1,0 +1,275 @@
+// Fused attention for sm_100a:  O = softmax(f(Q K^T)) V  without writing the scores to memory.
+//
+// The planner recognises  dot(q,k) -> elementwise f (scale, mask ...) -> softmax over the key
+// axis -> dot(p,v)  in a defn graph and generates this kernel with `f` compiled in as
+// AttnXform::apply.  One CTA owns 128 query rows of one (batch, head) pair and walks the key
+// blocks of 128:
+//   warp 0      TMA producer: Q once, then K_j / V_j into a two-stage ring
+//   warp 1      MMA issuer:   S_j = Q K_j^T into one of two TMEM accumulators (so the next
+//               block's scores are computed while this block's softmax runs), then
+//               PV_j = P_j V_j into a third accumulator (P from shared memory, V with its
+//               head-dim index contiguous, i.e. an MN-major B operand)
+//   warps 2..5  softmax, one thread per query row (a row lives in one TMEM lane, so the
+//               row maximum and sum need no cross-thread step): running maximum m, running
+//               sum l, and the output row O (128 f32 registers) rescaled by exp(m_old - m_new)
+// Keys beyond a causal diagonal are skipped block-wise when the planner proved the mask is
+// causal.  Every mbarrier wait is bounded; on expiry the CTA raises an abort flag, all roles
+// leave their loops, tensor memory is released and the host reports NXB_ERR_TIMEOUT.
+//
+// Compiled only through NVRTC, after device_lib.cuh and gemm_sm100_device.cuh (whose PTX
+// wrappers it reuses).
+#pragma once
+
+namespace nxb_attn {
+using namespace nxb_gemm;
+
+struct AttnParams {
+  void* out;           // [bh][sq][128] by default; strides below in elements
+  long long out_bh_hi, out_bh_lo, out_row;   // address = (bh / heads) * hi + (bh % heads) * lo + row * out_row + d
+  int* status;
+  int heads, batch_heads, sq, sk;
+  int causal;          // 1: keys j > query i contribute nothing (proved by the planner)
+  void* ep[14];        // buffers read by the generated score transform
+};
+
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int TILE = 128 * 128 * 2;                 // one 128 x 128 bf16 tile = two 16 KB halves
+constexpr int ATTN_SMEM = TILE /*Q*/ + 2 * 2 * TILE /*K,V x 2 stages*/ + TILE /*P*/ + 1024 + 256;
+
+template <class Xform>
+__device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const AttnParams& p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sKV = base + TILE, sP = sKV + 4 * TILE;
+  const uint32_t bars = sP + TILE;
+  // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_full
+  const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = bars + 24, s_full0 = bars + 40, s_empty0 = bars + 56,
+                 p_full = bars + 72, pv_full = bars + 80, tmem_slot = bars + 88;
+  unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + (tmem_slot - base));
+  volatile int* abort_flag = (volatile int*)(gen_base + (tmem_slot - base) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heavy (late) query blocks first: with a causal mask block i needs i+1 key blocks
+  const int nqb = (p.sq + BQ - 1) / BQ;
+  const int qb = nqb - 1 - (int)(blockIdx.x % nqb);
+  const int bh = (int)(blockIdx.x / nqb);
+  const int q0 = qb * BQ;
+  int nkv = (p.sk + BKV - 1) / BKV;
+  if (p.causal) { int lim = (q0 + BQ - 1) / BKV + 1; if (lim < nkv) nkv = lim; }
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 4); }
+    mbar_init(p_full, 4);
+    mbar_init(pv_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  const uint32_t tS0 = tmem_base, tPV = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, TILE);
+      tma_load_3d(sQ, &map_q, q_full, 0, q0, bh);
+      tma_load_3d(sQ + TILE / 2, &map_q, q_full, 64, q0, bh);
+      uint32_t ph = 0;
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(kv_empty0 + 8 * s, ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(kv_full0 + 8 * s, 2 * TILE);
+        const uint32_t k = sKV + s * 2 * TILE, v = k + TILE;
+        tma_load_3d(k, &map_k, kv_full0 + 8 * s, 0, j * BKV, bh);
+        tma_load_3d(k + TILE / 2, &map_k, kv_full0 + 8 * s, 64, j * BKV, bh);
+        // V_j: rows are keys, 64 head-dim elements per 128-byte row, one box per head-dim half
+        tma_load_3d(v, &map_v, kv_full0 + 8 * s, 0, j * BKV, bh);
+        tma_load_3d(v + TILE / 2, &map_v, kv_full0 + 8 * s, 64, j * BKV, bh);
+        if (s == 1) ph ^= 1;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // S = Q K^T: both K-major.  PV = P V: A K-major, B with N (head dim) contiguous.
+      const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      const uint32_t idesc_pv = idesc_s | (1u << 16);
+      auto issue_s = [&](int j) {
+        const uint32_t k = sKV + (j & 1) * 2 * TILE;
+        const uint32_t d = tS0 + (uint32_t)((j & 1) * 128);
+#pragma unroll
+        for (int k8 = 0; k8 < 8; ++k8) {
+          const uint32_t half = (k8 >> 2) * (TILE / 2), off = (k8 & 3) * 2;      // 32 bytes per step inside a 64-wide half
+          tc_mma(d, make_desc(sQ + half) + off, make_desc(k + half) + off, idesc_s, k8 > 0 ? 1u : 0u, false);
+        }
+        tc_commit(s_full0 + 8 * (j & 1));
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag) && mbar_wait(kv_full0, 0, abort_flag);
+      if (ok) { tc_fence_after(); issue_s(0); }
+      uint32_t kvph[2] = {0, 0}, seph[2] = {0, 0};
+      kvph[0] = 1;             // stage 0 was consumed once above
+      for (int j = 0; j < nkv && ok; ++j) {
+        if (j + 1 < nkv) {
+          const int s = (j + 1) & 1;
+          if (!mbar_wait(kv_full0 + 8 * s, kvph[s], abort_flag)) { ok = false; break; }
+          kvph[s] ^= 1;
+          if (j + 1 >= 2) {     // the S buffer was used by block j-1: wait until the softmax has read it
+            if (!mbar_wait(s_empty0 + 8 * s, seph[s], abort_flag)) { ok = false; break; }
+            seph[s] ^= 1;
+          }
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        if (!mbar_wait(p_full, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t v = sKV + (j & 1) * 2 * TILE + TILE;
+#pragma unroll
+        for (int k8 = 0; k8 < 8; ++k8) {
+          // A = P: two 64-key halves, 32 bytes per step.  B = V: 8-key groups are 1024 bytes apart
+          // inside a head-dim half (16 KB), the two halves 16 KB apart (leading offset).
+          const uint64_t adesc = make_desc(sP + (k8 >> 2) * (TILE / 2)) + (uint64_t)((k8 & 3) * 2);
+          const uint64_t bdesc = ((uint64_t)(((v + k8 * 2048) & 0x3FFFF) >> 4)) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+                                 ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+          tc_mma(tPV, adesc, bdesc, idesc_pv, k8 > 0 ? 1u : 0u, false);
+        }
+        tc_commit(pv_full);
+        tc_commit(kv_empty0 + 8 * (j & 1));
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;                 // query row inside the block == TMEM lane
+    const long long qi = (long long)q0 + row;
+    const long long b_idx = bh / p.heads, h_idx = bh % p.heads;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    float o[HD];
+#pragma unroll
+    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    float m = -NXB_INF, l = 0.f;
+    uint32_t sfph[2] = {0, 0};
+    bool ok = true;
+    for (int j = 0; j < nkv && ok; ++j) {
+      const int s = j & 1;
+      // warp-uniform outcome: the tensor-memory loads below need the whole warp
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * s, sfph[s], abort_flag))) { ok = false; break; }
+      sfph[s] ^= 1;
+      tc_fence_after();
+      const uint32_t tS = tS0 + (uint32_t)(s * 128) + lane_addr;
+      // pass 1: row maximum of the transformed scores of this block
+      float mx = -NXB_INF;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + c * 32, v);
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+          const long long kj = (long long)j * BKV + c * 32 + t;
+          float x = Xform::apply(__uint_as_float(v[t]), (long long)bh, qi, kj, p.ep);
+          x = (kj < p.sk) ? x : -NXB_INF;
+          mx = nx_max(mx, x);
+        }
+      }
+      const float m_new = nx_max(m, mx);
+      const float alpha = (m_new == -NXB_INF) ? 1.f : nx_exp(m - m_new);
+      if (j > 0) {
+        // PV of the previous block is complete (and P's buffer is free): add it in, still in the old scale
+        if (!__all_sync(0xffffffffu, mbar_wait(pv_full, (uint32_t)((j - 1) & 1), abort_flag))) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tPV + lane_addr + c * 32, v);
+#pragma unroll
+          for (int t = 0; t < 32; ++t) o[c * 32 + t] += __uint_as_float(v[t]);
+        }
+      }
+#pragma unroll
+      for (int d = 0; d < HD; ++d) o[d] *= alpha;
+      l *= alpha;
+      m = m_new;
+      // pass 2: probabilities, their sum, and P (bf16) into shared memory as the next MMA's A operand
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS + c * 32, v);
+        uint32_t pk[16];
+#pragma unroll
+        for (int t = 0; t < 32; t += 2) {
+          float e2[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const long long kj = (long long)j * BKV + c * 32 + t + u;
+            float x = Xform::apply(__uint_as_float(v[t + u]), (long long)bh, qi, kj, p.ep);
+            x = (kj < p.sk) ? x : -NXB_INF;
+            const float e = (m_new == -NXB_INF) ? 0.f : nx_exp(x - m_new);
+            e2[u] = e;
+          }
+          const unsigned short h0 = f32_to_bf16_bits(e2[0]), h1 = f32_to_bf16_bits(e2[1]);
+          // the sum uses the same rounded values the product consumes
+          l += __uint_as_float(((uint32_t)h0) << 16) + __uint_as_float(((uint32_t)h1) << 16);
+          pk[t >> 1] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+        }
+        // chunk c covers keys c*32 .. c*32+31: half (c >> 1), 16-byte chunks (c & 1) * 4 .. +3 of this row
+        const uint32_t rowbase = sP + (uint32_t)(c >> 1) * (TILE / 2) + (uint32_t)row * 128u;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t chunk = (uint32_t)((c & 1) * 4 + g);
+          const uint32_t dst = rowbase + ((chunk ^ (uint32_t)(row & 7)) * 16u);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[g * 4]), "r"(pk[g * 4 + 1]), "r"(pk[g * 4 + 2]), "r"(pk[g * 4 + 3]) : "memory");
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(s_empty0 + 8 * s); mbar_arrive(p_full); }
+    }
+    if (ok && nkv > 0) {
+      if (__all_sync(0xffffffffu, mbar_wait(pv_full, (uint32_t)((nkv - 1) & 1), abort_flag))) {
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(tPV + lane_addr + c * 32, v);
+#pragma unroll
+          for (int t = 0; t < 32; ++t) o[c * 32 + t] += __uint_as_float(v[t]);
+        }
+        if (qi < p.sq) {
+          const float inv = 1.f / l;
+          unsigned short* out = (unsigned short*)p.out + b_idx * p.out_bh_hi + h_idx * p.out_bh_lo + qi * p.out_row;
+#pragma unroll
+          for (int d = 0; d < HD; d += 8) {
+            uint4 w;
+            w.x = f32_to_bf16_bits(o[d] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 1] * inv) << 16);
+            w.y = f32_to_bf16_bits(o[d + 2] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 3] * inv) << 16);
+            w.z = f32_to_bf16_bits(o[d + 4] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 5] * inv) << 16);
+            w.w = f32_to_bf16_bits(o[d + 6] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 7] * inv) << 16);
+            *reinterpret_cast<uint4*>(out + d) = w;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) *(volatile int*)p.status = 1;
+    const unsigned long long t0 = now_ns();
+    while (now_ns() - t0 < 200000ull) { }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+}  // namespace nxb_attn

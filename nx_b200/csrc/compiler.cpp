@@ -116,6 +116,8 @@ class KernelBuilder {
   int acc_node = -1;            // EPI: the dot node whose accumulator the function receives
   int force_v = 0;              // EPI: vector width to generate (8 or 1)
   std::vector<int> seed_args;   // EPI: argument order to reuse (so both widths see the same pointers)
+  int ret_node = -1;            // EPI: generate `float f(acc, batch, row, col, ep)` returning this node's value
+                                // at index (batch..., row, col) instead of a storing epilogue
   std::string idx_type() const { return idx_t(); }
   KernelBuilder(Plan& plan, Mode mode, std::vector<int64_t> F, int k, std::vector<int> perm)
       : plan_(plan), g_(plan.g), mode_(mode), F_(std::move(F)), k_(k), perm_(std::move(perm)) {
@@ -223,7 +225,7 @@ private:
   std::string affstr(const Aff& a, bool base) {
     if (a.opaque) return a.expr;
     // shortcut: the address of a same-shape contiguous operand is the flat index
-    if (!a.is_const() && a.c == 0 && a.k == cstrides(F_) && nv_ > 1) {
+    if (ret_node < 0 && !a.is_const() && a.c == 0 && a.k == cstrides(F_) && nv_ > 1) {
       used_flat_ = true;
       return base ? "flat0" : "flat";
     }
@@ -924,6 +926,10 @@ KernelSpec KernelBuilder::build(const std::string& name) {
       }
       emit_store(s);
     }
+    if (ret_node >= 0) {
+      Val r = value(ret_node, full_index());
+      lane_sec_[0] += "        result = " + cvt(r.v, g_.nodes[ret_node].dt, NXB_F32) + ";\n";
+    }
   }
   // finish the reductions of each phase together: one pair of barriers per phase
   for (int p = 0; p < nphases_; ++p) {
@@ -984,7 +990,14 @@ KernelSpec KernelBuilder::build(const std::string& name) {
     for (int r : reduces) if (g_.nodes[r].slot == slot) return true;
     return false;
   };
-  if (mode_ == EPI) {
+  if (mode_ == EPI && ret_node >= 0) {
+    o << "__device__ __forceinline__ float " << name << "(const float accv, const long long bh, const long long qrow, const long long kcol, void* const* ep) {\n";
+    o << "  const float* acc = &accv;\n  float result = 0.f;\n";
+    for (size_t i = 0; i < arg_slots_.size(); ++i) {
+      const Slot& sl = plan_.slots[arg_slots_[i]];
+      o << "  const " << storage_type(sl.dt) << "* __restrict__ p" << i << " = (const " << storage_type(sl.dt) << "*)ep[" << i << "];\n";
+    }
+  } else if (mode_ == EPI) {
     o << "__device__ __forceinline__ void " << name << "(const float* acc, const " << I << " flat0, void* const* ep) {\n";
     for (size_t i = 0; i < arg_slots_.size(); ++i) {
       const Slot& sl = plan_.slots[arg_slots_[i]];
@@ -1013,7 +1026,16 @@ KernelSpec KernelBuilder::build(const std::string& name) {
       if (!last_nonunit) rem = "(" + rem + ") / (" + I + ")" + std::to_string(F_[j]);
     }
   };
-  if (mode_ == EPI) {
+  if (mode_ == EPI && ret_node >= 0) {
+    // index variables: the batch dims from `bh`, then the query row and the key column
+    if (nv_ > 2) decomp(0, nv_ - 2, "(" + I + ")bh", false);
+    if (nv_ >= 2 && used_vars_.count(nv_ - 2)) o << "        const " << I << " i" << nv_ - 2 << " = (" << I << ")qrow;\n";
+    o << "        const " << I << " ib = (" << I << ")kcol;\n";
+    o << pre_sec_[0];
+    o << "      { const int v = 0;\n";
+    if (used_vars_.count(nv_ - 1)) o << "        const " << I << " i" << nv_ - 1 << " = ib;\n";
+    o << lane_sec_[0] << "      }\n  return result;\n}\n";
+  } else if (mode_ == EPI) {
     decomp(0, nv_, "flat0", true);
     o << pre_sec_[0];
     o << "#pragma unroll\n      for (int v = 0; v < " << V_ << "; ++v) {\n";
@@ -1142,7 +1164,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
 namespace {
 
 struct Unit {           // one launch-to-be
-  enum Kind { ROW, EW, GEMM, ALLREDUCE } kind = EW;
+  enum Kind { ROW, EW, GEMM, ALLREDUCE, ATTN } kind = EW;
   bool fused_epilogue = false;   // GEMM whose epilogue computes `stores`
   std::vector<int64_t> F;
   int k = 0;
@@ -1204,14 +1226,14 @@ struct Planner {
     int d = 0;
     for (int a : g.nodes[n].args) {
       const std::string& op = g.nodes[a].op;
-      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate" || op == "all_reduce") ? 1 : 0));
+      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention") ? 1 : 0));
     }
     return depth_memo[n] = d;
   }
 
   bool is_leaf(int n) const {
     const std::string& op = g.nodes[n].op;
-    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate" || op == "all_reduce";
+    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention";
   }
 
   // Nodes reachable backwards through everything a kernel can generate inline
@@ -1232,6 +1254,7 @@ std::string Plan::describe() const {
   for (auto& st : steps) {
     if (st.kind == Step::KERNEL) o << kernels[st.index].desc << "\n";
     else if (st.kind == Step::GEMM) o << gemms[st.index].desc << "\n";
+    else if (st.kind == Step::ATTENTION) o << attentions[st.index].desc << "\n";
     else o << collectives[st.index].desc << "\n";
   }
   return o.str();
@@ -1241,6 +1264,8 @@ std::string Plan::describe() const {
 bool plan_dot(Plan& plan, int node, std::vector<int>& need_materialised, GemmSpec* out);
 void canonicalize_dots(Graph& g);
 void rewrite_quantised_linears(Graph& g);
+void rewrite_attention(Graph& g);
+int attn_smem_bytes();
 int tc_pick_bn(int64_t m, int64_t n, int64_t batch, int sm_count);
 int tc_smem_bytes(int bn);
 
@@ -1272,6 +1297,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     for (int& o : g.outputs) o = remap[o];
   }
   rewrite_quantised_linears(g);
+  rewrite_attention(g);
   canonicalize_dots(g);
   Planner P(*plan);
 
@@ -1337,7 +1363,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       const Node& nd = g.nodes[n];
       if (!nd.live) continue;
       bool ok = is_inline(nd) || is_reduce(nd) || nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" ||
-                nd.op == "all_reduce";
+                nd.op == "all_reduce" || nd.op == "attention";
       if (!ok) fail(NXB_ERR_UNSUPPORTED, "Nx op :" + nd.op + " is not implemented by the B200 compiler");
       if (nd.op == "slice" && nd.args.size() != 1) fail(NXB_ERR_UNSUPPORTED, "slice with dynamic start indices is not implemented");
     }
@@ -1359,13 +1385,21 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
   }
   // what must be materialised regardless of fusion
   for (int o : g.outputs) P.mat[o] = 1;
-  std::vector<int> dots, concats, allreduces;
+  std::vector<int> dots, concats, allreduces, attns;
   for (int n = 0; n < N; ++n) {
     const Node& nd = g.nodes[n];
     if (!nd.live) continue;
     if (nd.op == "dot") { P.mat[n] = 1; dots.push_back(n); }
     if (nd.op == "concatenate") { P.mat[n] = 1; concats.push_back(n); }
     if (nd.piece_of >= 0) P.mat[n] = 1;
+    if (nd.op == "attention") {
+      P.mat[n] = 1;
+      attns.push_back(n);
+      for (int k = 0; k < 3; ++k) {
+        const std::string& aop = g.nodes[nd.args[k]].op;
+        if (aop != "parameter" && aop != "tensor") P.mat[nd.args[k]] = 1;
+      }
+    }
     if (nd.op == "all_reduce") {
       P.mat[n] = 1;
       allreduces.push_back(n);
@@ -1474,7 +1508,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         for (int n = 0; n < N; ++n) {
           const Node& nd = g.nodes[n];
           if (!nd.live || !P.mat[n]) continue;
-          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || nd.op == "all_reduce" || is_reduce(nd)) continue;
+          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || nd.op == "all_reduce" || nd.op == "attention" || is_reduce(nd)) continue;
           roots.push_back(n);
         }
         for (int n : roots) {
@@ -1614,6 +1648,12 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         units.push_back(u);
       }
 
+      for (int n : attns) {
+        Unit u;
+        u.kind = Unit::ATTN;
+        u.gemm_node = n;
+        units.push_back(u);
+      }
       for (int n : allreduces) {
         Unit u;
         u.kind = Unit::ALLREDUCE;
@@ -1629,6 +1669,12 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           const Node& nd = g.nodes[u.gemm_node];
           u.writes.insert(nd.slot);
           u.reads.insert(g.nodes[nd.args[0]].slot);
+          return;
+        }
+        if (u.kind == Unit::ATTN) {
+          const Node& nd = g.nodes[u.gemm_node];
+          u.writes.insert(nd.slot);
+          for (int a : nd.args) u.reads.insert(g.nodes[a].slot);
           return;
         }
         if (u.kind == Unit::GEMM) {
@@ -1704,7 +1750,51 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       for (int ui : order) {
         Unit& u = units[ui];
         int step_index = (int)pl.steps.size();
-        if (u.kind == Unit::ALLREDUCE) {
+        if (u.kind == Unit::ATTN) {
+          const Node& nd = g.nodes[u.gemm_node];
+          const int xnode = (int)nd.ints[0], d1 = (int)nd.ints[1];
+          const std::string kname = "nxb_k" + std::to_string(kid++) + "_attn";
+          // the score transform: value of X at (batch..., query row, key column) given the raw score
+          KernelBuilder kx(pl, KernelBuilder::EPI, g.nodes[d1].shape, 0, {});
+          kx.acc_node = d1;
+          kx.force_v = 1;
+          kx.ret_node = xnode;
+          KernelSpec fx = kx.build(kname + "_xform");
+          std::ostringstream o;
+          o << fx.source;
+          o << "struct AttnXform {\n  static __device__ __forceinline__ float apply(float s, long long bh, long long qi, long long kj, void* const* ep) { return "
+            << kname << "_xform(s, bh, qi, kj, ep); }\n};\n";
+          o << "extern \"C\" __global__ void __launch_bounds__(192, 1) " << kname
+            << "(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const nxb_attn::AttnParams p) {\n"
+            << "  nxb_attn::attn_body<AttnXform>(map_q, map_k, map_v, p);\n}\n";
+          KernelSpec ks;
+          ks.name = kname;
+          ks.source = o.str();
+          ks.block = 192;
+          ks.smem = (unsigned)attn_smem_bytes();
+          ks.arg_slots = fx.arg_slots;
+          ks.arg_offsets.assign(ks.arg_slots.size(), 0);
+          ks.tensor_core = true;
+          ks.attention = true;
+          AttentionSpec as;
+          as.q_slot = g.nodes[nd.args[0]].slot;
+          as.k_slot = g.nodes[nd.args[1]].slot;
+          as.v_slot = g.nodes[nd.args[2]].slot;
+          as.out_slot = nd.slot;
+          as.sq = nd.ints[3];
+          as.sk = nd.ints[4];
+          as.causal = (int)nd.ints[2];
+          as.batch_heads = shape_numel(nd.shape) / (as.sq * 128);
+          std::ostringstream d;
+          d << "attention#" << u.gemm_node << " fused QK^T -> transform(" << g.nodes[xnode].op << "#" << xnode << ") -> softmax -> PV, batch*heads=" << as.batch_heads
+            << " Sq=" << as.sq << " Sk=" << as.sk << " head_dim=128 bf16" << (as.causal ? " causal (key blocks above the diagonal skipped)" : "") << " (" << kname << ")";
+          as.desc = d.str();
+          ks.desc = as.desc;
+          pl.kernels.push_back(std::move(ks));
+          as.jit_kernel = (int)pl.kernels.size() - 1;
+          pl.attentions.push_back(as);
+          pl.steps.push_back({Step::ATTENTION, (int)pl.attentions.size() - 1});
+        } else if (u.kind == Unit::ALLREDUCE) {
           const Node& nd = g.nodes[u.gemm_node];
           CollectiveSpec cs;
           cs.in_slot = g.nodes[nd.args[0]].slot;
@@ -1790,7 +1880,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     }
   }
 
-  for (auto& ks : plan->kernels) ks.cubin = compile_to_cubin(ks.source, ks.name, ks.tensor_core);
+  for (auto& ks : plan->kernels) ks.cubin = compile_to_cubin(ks.source, ks.name, ks.tensor_core, ks.attention);
   return plan;
 }
 

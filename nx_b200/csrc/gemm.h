@@ -42,6 +42,12 @@ int tc_pick_bn(int64_t m, int64_t n, int64_t batch, int sm_count);
 int tc_smem_bytes(int bn);
 void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int* status_word, int sm_count, TcLaunch* out);
 const char* gemm_device_source();
+const char* attention_device_source();
+int attn_smem_bytes();
+// Launch block of a generated attention kernel: tensor maps of q, k, v ([batch*heads][S][128] bf16)
+// and its parameter block.
+void attn_prepare_launch(const void* q, const void* k, const void* v, void* out, int64_t batch_heads, int64_t sq, int64_t sk, int causal,
+                         void* const* ep, int n_ep, int* status_word, TcLaunch* outl);
 void launch_transpose(const void* in, void* out, int64_t batch, int64_t rows, int64_t cols, size_t elem_size, cudaStream_t stream);
 
 }  // namespace nxb

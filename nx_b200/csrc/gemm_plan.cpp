@@ -1,6 +1,8 @@
 // Lowering of Nx `dot` nodes (nx/lib/nx.ex:13123-13161; EXLA: exla/lib/exla/defn.ex:1175-1197)
 // to strided-batched matrix products.
 #include <algorithm>
+#include <cstdlib>
+#include <set>
 
 #include "gemm.h"
 
@@ -132,6 +134,108 @@ void rewrite_quantised_linears(Graph& g) {
     if (k % 16 != 0 || k > 130000) continue;       // 16-byte rows; 130000 * 127^2 < 2^31
     nd.args[0] = g.nodes[a].args[0];
     nd.args[1] = g.nodes[b].args[0];
+  }
+}
+
+// Attention:  dot(q,k) -> X = elementwise(scores, indices ...) -> softmax over the key axis ->
+// dot(p,v), with every intermediate private to the chain, becomes ONE node that the fused
+// kernel of attn_sm100_device.cuh executes (the scores never reach memory).  `X`'s subgraph is
+// kept and compiled into the kernel as the score transform.
+// attention node: args = {q, k, v, extra buffers of the transform...};
+//                 ints = {X node, scores dot node, causal, Sq, Sk}.
+void rewrite_attention(Graph& g) {
+  if (getenv("NXB200_NO_FUSED_ATTENTION")) return;
+  const size_t N = g.nodes.size();
+  std::vector<int> uses(N, 0);
+  for (size_t n = 0; n < N; ++n) for (int a : g.nodes[n].args) uses[a]++;
+  for (int o : g.outputs) uses[o]++;
+  auto is_last_axis_keep = [&](const Node& nd, size_t rank) {
+    return nd.ints.size() == 3 && nd.ints[0] == 1 && nd.ints[1] == 1 && nd.ints[2] == (int64_t)rank - 1;
+  };
+  for (size_t n = 0; n < N; ++n) {
+    if (g.nodes[n].op != "dot" || g.nodes[n].dt != NXB_BF16) continue;
+    const Node& D2 = g.nodes[n];
+    DotAxes d2 = dot_axes(D2);
+    const int p = D2.args[0], v = D2.args[1];
+    const Node& P = g.nodes[p];
+    const size_t r = P.shape.size();
+    if (r < 2 || g.nodes[v].shape.size() != r || P.op != "divide" || uses[p] != 1) continue;
+    std::vector<int> lead;
+    for (size_t i = 0; i + 2 < r; ++i) lead.push_back((int)i);
+    if (d2.c1 != std::vector<int>{(int)r - 1} || d2.c2 != std::vector<int>{(int)r - 2} || d2.b1 != lead || d2.b2 != lead) continue;
+    const int e = P.args[0], sm = P.args[1];
+    const Node& S = g.nodes[sm];
+    const Node& E = g.nodes[e];
+    if (S.op != "sum" || !is_last_axis_keep(S, r) || S.args[0] != e || uses[sm] != 1) continue;
+    if (E.op != "exp" || uses[e] != 2) continue;
+    const Node& SUB = g.nodes[E.args[0]];
+    if (SUB.op != "subtract" || uses[E.args[0]] != 1) continue;
+    const int x = SUB.args[0], mx = SUB.args[1];
+    const Node& M = g.nodes[mx];
+    if (M.op != "reduce_max" || !is_last_axis_keep(M, r) || M.args[0] != x || uses[mx] != 1 || uses[x] != 2) continue;
+    const Node& X = g.nodes[x];
+    if (X.shape != P.shape || X.dt != NXB_BF16 || E.dt != NXB_BF16 || P.dt != NXB_BF16) continue;
+    // the transform's subgraph: exactly one product, no reductions, private intermediates
+    std::vector<int> stack{x}, cone_nodes, extras;
+    std::set<int> seen;
+    int d1 = -1;
+    bool ok = true;
+    std::map<int, int> refs;
+    while (!stack.empty() && ok) {
+      int c = stack.back();
+      stack.pop_back();
+      if (!seen.insert(c).second) continue;
+      const Node& cn = g.nodes[c];
+      if (cn.op == "dot") { if (d1 >= 0 && d1 != c) ok = false; d1 = c; continue; }
+      if (cn.op == "parameter" || cn.op == "tensor" || cn.op == "concatenate" || cn.op == "all_reduce" || cn.op == "attention") { extras.push_back(c); continue; }
+      if (cn.op == "sum" || cn.op == "product" || cn.op == "reduce_max" || cn.op == "reduce_min" || cn.op == "all" || cn.op == "any" ||
+          cn.op == "argmax" || cn.op == "argmin") { ok = false; break; }
+      cone_nodes.push_back(c);
+      for (int a : cn.args) { refs[a]++; stack.push_back(a); }
+    }
+    if (!ok || d1 < 0 || uses[d1] != refs[d1] || extras.size() > 10) continue;
+    const Node& D1 = g.nodes[d1];
+    DotAxes a1 = dot_axes(D1);
+    const int q = D1.args[0], k = D1.args[1];
+    if (g.nodes[q].shape.size() != r || g.nodes[k].shape.size() != r || D1.shape != X.shape || D1.dt != NXB_BF16) continue;
+    if (a1.c1 != std::vector<int>{(int)r - 1} || a1.c2 != std::vector<int>{(int)r - 1} || a1.b1 != lead || a1.b2 != lead) continue;
+    if (g.nodes[q].dt != NXB_BF16 || g.nodes[k].dt != NXB_BF16 || g.nodes[v].dt != NXB_BF16) continue;
+    const int64_t D = g.nodes[q].shape[r - 1], Sq = g.nodes[q].shape[r - 2], Sk = g.nodes[k].shape[r - 2];
+    if (D != 128 || g.nodes[v].shape[r - 1] != 128 || g.nodes[v].shape[r - 2] != Sk) continue;
+    int64_t bh = 1;
+    for (size_t i = 0; i + 2 < r; ++i) bh *= g.nodes[q].shape[i];
+    if (bh < 1 || bh > 65535 * 8 || Sq < 1 || Sk < 1) continue;
+    // causal: X = select(broadcast(iota(rows) >= iota(cols)), ., -inf)
+    int causal = 0;
+    if (X.op == "select" && Sq == Sk) {
+      int mk = X.args[0];
+      while (g.nodes[mk].op == "broadcast" || g.nodes[mk].op == "metadata") {
+        const Node& b = g.nodes[mk];
+        if (b.op == "broadcast") {
+          // must map the mask's two axes onto the last two axes of the scores
+          if (b.ints.size() != 3 || b.ints[1] != (int64_t)r - 2 || b.ints[2] != (int64_t)r - 1) break;
+        }
+        mk = b.args[0];
+      }
+      const Node& ge = g.nodes[mk];
+      const Node& neg = g.nodes[X.args[2]];
+      const bool neg_inf = neg.op == "constant" && !neg.flts.empty() && neg.flts[0] < -1e300;
+      if (ge.op == "greater_equal" && ge.shape == std::vector<int64_t>{Sq, Sk} && neg_inf) {
+        const Node& i0 = g.nodes[ge.args[0]];
+        const Node& i1 = g.nodes[ge.args[1]];
+        if (i0.op == "iota" && i1.op == "iota" && i0.ints[0] == 0 && i1.ints[0] == 1 && i0.shape == ge.shape && i1.shape == ge.shape) causal = 1;
+      }
+    }
+    Node A;
+    A.op = "attention";
+    A.dt = NXB_BF16;
+    A.shape = D2.shape;
+    A.args = {q, k, v};
+    for (int ex : extras) A.args.push_back(ex);
+    A.ints = {x, d1, causal, Sq, Sk};
+    g.nodes[n] = A;
+    // the product that computed the scores is no longer part of the program
+    for (int a : g.nodes[d1].args) uses[a]--;
   }
 }
 

@@ -226,6 +226,52 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
 #undef NXB_LAUNCH_KIND
 }
 
+const char* attention_device_source() {
+  static const char* src =
+#include "attn_device_embed.inc"
+      ;
+  return src;
+}
+
+// host mirror of nxb_attn::AttnParams (attn_sm100_device.cuh); the layouts must match
+struct AttnParamsHost {
+  void* out;
+  long long out_bh_hi, out_bh_lo, out_row;
+  int* status;
+  int heads, batch_heads, sq, sk;
+  int causal;
+  void* ep[14];
+};
+
+int attn_smem_bytes() { return 128 * 128 * 2 * 6 + 1024 + 256; }
+
+void attn_prepare_launch(const void* q, const void* k, const void* v, void* out, int64_t batch_heads, int64_t sq, int64_t sk, int causal,
+                         void* const* ep, int n_ep, int* status_word, TcLaunch* outl) {
+  static_assert(sizeof(AttnParamsHost) <= sizeof(outl->params), "launch block too small");
+  CUtensorMap mq = make_map(q, NXB_BF16, 128, sq, batch_heads, 128, sq * 128, 128);
+  CUtensorMap mk = make_map(k, NXB_BF16, 128, sk, batch_heads, 128, sk * 128, 128);
+  CUtensorMap mv = make_map(v, NXB_BF16, 128, sk, batch_heads, 128, sk * 128, 128);
+  AttnParamsHost p{};
+  p.out = out;
+  p.heads = 1;
+  p.out_bh_hi = sq * 128;
+  p.out_bh_lo = 0;
+  p.out_row = 128;
+  p.status = status_word;
+  p.batch_heads = (int)batch_heads;
+  p.sq = (int)sq;
+  p.sk = (int)sk;
+  p.causal = causal;
+  if (n_ep > 14) fail(NXB_ERR_UNSUPPORTED, "attention score transform reads too many buffers");
+  for (int i = 0; i < n_ep; ++i) p.ep[i] = ep[i];
+  memcpy(outl->map_a, &mq, 128);
+  memcpy(outl->map_b, &mk, 128);
+  memcpy(outl->map_c, &mv, 128);
+  memcpy(outl->params, &p, sizeof p);
+  outl->grid = (unsigned)(batch_heads * ((sq + 127) / 128));
+  outl->smem = attn_smem_bytes();
+}
+
 const char* gemm_device_source() {
   static const char* src =
 #include "gemm_device_embed.inc"

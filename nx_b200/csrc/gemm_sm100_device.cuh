@@ -307,7 +307,8 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       const int b = (int)(t / tiles_per_batch);
       const int r = (int)(t % tiles_per_batch);
       const int nt = r / p.mtiles, mt = r % p.mtiles;
-      if (!mbar_wait(tfull0 + 8 * a, aph, abort_flag)) { ok = false; break; }
+      // warp-uniform outcome: the tensor-memory loads below need the whole warp
+      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * a, aph, abort_flag))) { ok = false; break; }
       tc_fence_after();
       const long long m = (long long)mt * BM + q * 32 + lane;
       const bool staged = Epi::kStaged && p.tma_store != 0;

@@ -50,6 +50,7 @@ struct KernelSpec {
   std::vector<int> arg_slots;     // one pointer argument per entry
   std::vector<size_t> arg_offsets;  // byte offset added to the slot's base pointer
   bool tensor_core = false;       // a generated matrix-product kernel (needs the GEMM device source)
+  bool attention = false;         // ... and the attention device source
 };
 
 // Operand of a matrix product as a strided batch of row-major matrices.
@@ -77,6 +78,14 @@ struct GemmSpec {
   int bn = 256;
 };
 
+struct AttentionSpec {
+  int q_slot = -1, k_slot = -1, v_slot = -1, out_slot = -1;
+  int64_t batch_heads = 1, sq = 0, sk = 0;
+  int causal = 0;
+  int jit_kernel = -1;
+  std::string desc;
+};
+
 struct CollectiveSpec {
   int in_slot = -1, out_slot = -1;
   int64_t count = 0;
@@ -85,7 +94,7 @@ struct CollectiveSpec {
 };
 
 struct Step {
-  enum Kind { KERNEL, GEMM, ALLREDUCE } kind = KERNEL;
+  enum Kind { KERNEL, GEMM, ALLREDUCE, ATTENTION } kind = KERNEL;
   int index = 0;
 };
 
@@ -96,6 +105,7 @@ struct Plan {
   std::vector<KernelSpec> kernels;
   std::vector<GemmSpec> gemms;
   std::vector<CollectiveSpec> collectives;
+  std::vector<AttentionSpec> attentions;
   std::vector<int> param_slots;   // by parameter index (-1 when unused)
   std::vector<int> output_slots;  // by output index
   std::string describe() const;
@@ -104,7 +114,7 @@ struct Plan {
 std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes);
 
 // NVRTC: compile CUDA source to an sm_100a cubin (needs no GPU).
-std::string compile_to_cubin(const std::string& source, const std::string& name, bool tensor_core = false);
+std::string compile_to_cubin(const std::string& source, const std::string& name, bool tensor_core = false, bool attention = false);
 const char* device_lib_source();
 
 }  // namespace nxb

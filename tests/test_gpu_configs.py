@@ -66,7 +66,8 @@ def test_rms_norm_bf16():
     assert_close(g, r, what="rms_norm", **BF16)
 
 
-@pytest.mark.parametrize("batch,seq,hidden,heads,inter", [(2, 16, 64, 4, 176), (1, 64, 256, 4, 344), (2, 128, 512, 8, 688)])
+@pytest.mark.parametrize("batch,seq,hidden,heads,inter", [(2, 16, 64, 4, 176), (1, 64, 256, 4, 344), (2, 128, 512, 8, 688),
+                                                          (1, 256, 512, 4, 688), (2, 200, 256, 2, 344), (1, 640, 384, 3, 344)])
 def test_decoder_block(batch, seq, hidden, heads, inter):
     block = configs.make_decoder_block(n_heads=heads)
     inputs = configs.decoder_inputs(batch=batch, seq=seq, hidden=hidden, inter=inter)
@@ -74,6 +75,35 @@ def test_decoder_block(batch, seq, hidden, heads, inter):
     assert t == ("bf", 16) and g.shape == (batch, seq, hidden)
     assert np.isfinite(g).all()
     assert_close(g, r, what="decoder block", **BF16)
+
+
+def _attention(q, k, v, causal=True, scale=0.0884):
+    s = nx.dot(q, [3], [0, 1], k, [3], [0, 1]) * scale
+    if causal:
+        sq, sk = s.shape[2], s.shape[3]
+        mask = nx.greater_equal(nx.iota((sq, sk), axis=0), nx.iota((sq, sk), axis=1))
+        s = nx.select(nx.broadcast(mask, s.shape), s, float("-inf"))
+    m = nx.reduce_max(s, axes=[-1], keep_axes=True)
+    e = nx.exp(s - m)
+    p = e / nx.sum(e, axes=[-1], keep_axes=True)
+    return nx.dot(p, [3], [0, 1], v, [2], [0, 1])
+
+
+@pytest.mark.parametrize("b,h,sq,sk,causal", [(1, 2, 128, 128, True), (2, 3, 384, 384, True), (1, 2, 200, 200, True),
+                                               (1, 2, 130, 260, False), (2, 1, 512, 64, False)])
+def test_fused_attention(b, h, sq, sk, causal):
+    """head_dim 128 attention is lowered to the fused tensor-core kernel; compare with the oracle
+    (which evaluates the graph node by node) and with the unfused plan."""
+    rng = np.random.default_rng(30)
+    q = rng.normal(0, 1, (b, h, sq, 128)).astype(np.float32)
+    k = rng.normal(0, 1, (b, h, sk, 128)).astype(np.float32)
+    v = rng.normal(0, 1, (b, h, sk, 128)).astype(np.float32)
+    fun = lambda q, k, v: _attention(q, k, v, causal)
+    prog = defn.compile(fun, [defn.template(a.shape, "bf16") for a in (q, k, v)]).program
+    assert "attention" in prog.describe(), prog.describe()
+    (g, r, t), = run_both(fun, [(q, "bf16"), (k, "bf16"), (v, "bf16")])
+    assert g.shape == (b, h, sq, 128)
+    assert_close(g, r, what="fused attention", **BF16)
 
 
 def test_dense_bias_gelu_reduced():
