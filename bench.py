@@ -284,6 +284,8 @@ def main():
     ap.add_argument("--all-configs", action="store_true")
     ap.add_argument("--profile-gemm", type=int, default=0, metavar="N",
                     help="run only an N^3 bf16 dense product with the fused bias+gelu epilogue (ncu captures of the tensor-core kernel)")
+    ap.add_argument("--profile-decoder", type=int, default=0, metavar="B",
+                    help="run only the decoder block on a batch of B sequences (ncu launch lists)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -303,6 +305,11 @@ def main():
     backend.set_default_backend("b200", local)
     lib = nif.lib()
     timer = Timer(lib, local)
+    if args.profile_decoder:
+        ms_, prog_ = time_program(timer, configs.make_decoder_block(), configs.decoder_inputs(batch=args.profile_decoder), local, steps=args.steps)
+        print(json.dumps({"workload": f"decoder block bf16 {{{args.profile_decoder},2048,4096}}", "ms": round(ms_, 4),
+                          "tokens_per_s": round(args.profile_decoder * 2048 / ms_ * 1e3), "plan": prog_.describe().strip().split("\n")}))
+        return
     if args.profile_gemm:
         n = args.profile_gemm
         ms_, prog_ = time_program(timer, configs.dense_bias_gelu, configs.dense_inputs(m=n, n=n, k=n), local, steps=args.steps)

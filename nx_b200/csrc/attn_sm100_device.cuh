@@ -9,9 +9,10 @@
 //               block's scores are computed while this block's softmax runs), then
 //               PV_j = P_j V_j into a third accumulator (P from shared memory, V with its
 //               head-dim index contiguous, i.e. an MN-major B operand)
-//   warps 2..5  softmax, one thread per query row (a row lives in one TMEM lane, so the
-//               row maximum and sum need no cross-thread step): running maximum m, running
-//               sum l, and the output row O (128 f32 registers) rescaled by exp(m_old - m_new)
+//   warps 2..9  softmax, two threads per query row (a row lives in one TMEM lane; each thread
+//               owns 64 key columns and 64 head dims, the halves exchange maxima through shared
+//               memory): running maximum m, running sum l, and the output half-row O (64 f32
+//               registers) rescaled by exp(m_old - m_new)
 // Keys beyond a causal diagonal are skipped block-wise when the planner proved the mask is
 // causal.  Every mbarrier wait is bounded; on expiry the CTA raises an abort flag, all roles
 // leave their loops, tensor memory is released and the host reports NXB_ERR_TIMEOUT.
@@ -34,7 +35,7 @@ struct AttnParams {
 
 constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int TILE = 128 * 128 * 2;                 // one 128 x 128 bf16 tile = two 16 KB halves
-constexpr int ATTN_SMEM = TILE /*Q*/ + 2 * 2 * TILE /*K,V x 2 stages*/ + TILE /*P*/ + 1024 + 256;
+constexpr int ATTN_SMEM = TILE /*Q*/ + 2 * 2 * TILE /*K,V x 2 stages*/ + TILE /*P*/ + 1024 + 256 + 3072 /*exchange*/;
 
 template <class Xform>
 __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const AttnParams& p) {
@@ -44,10 +45,13 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
   const uint32_t bars = sP + TILE;
   // barriers: q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, pv_full
   const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = bars + 24, s_full0 = bars + 40, s_empty0 = bars + 56,
-                 p_full = bars + 72, pv_full = bars + 80, tmem_slot = bars + 88;
+                 p_full = bars + 72, pv_full = bars + 80, xchg_bar = bars + 88, tmem_slot = bars + 96;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + (tmem_slot - base));
   volatile int* abort_flag = (volatile int*)(gen_base + (tmem_slot - base) + 8);
+  // exchange areas of the softmax half-rows: maxima [parity][half][row], sums [half][row]
+  volatile float* xmax = (volatile float*)(gen_base + (bars - base) + 256);
+  volatile float* xsum = xmax + 2 * 2 * 128;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heavy (late) query blocks first: with a causal mask block i needs i+1 key blocks
@@ -60,9 +64,10 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 4); }
-    mbar_init(p_full, 4);
+    for (int s = 0; s < 2; ++s) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1); mbar_init(s_empty0 + 8 * s, 8); }
+    mbar_init(p_full, 8);
     mbar_init(pv_full, 1);
+    mbar_init(xchg_bar, 8);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -143,14 +148,18 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
       }
     }
   } else {
+    // softmax: 8 warps, two threads per query row.  Warps 2..5 take key columns / head dims 0..63
+    // of their TMEM lane quarter, warps 6..9 take 64..127; the two halves of a row exchange their
+    // maxima (and, at the end, their sums) through shared memory.
     const int q = warp & 3;
+    const int hf = (warp - 2) >> 2;
     const int row = q * 32 + lane;                 // query row inside the block == TMEM lane
     const long long qi = (long long)q0 + row;
     const long long b_idx = bh / p.heads, h_idx = bh % p.heads;
-    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    float o[HD];
+    const uint32_t lane_addr = ((uint32_t)(q * 32) << 16) + (uint32_t)(hf * 64);
+    float o[64];
 #pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.f;
+    for (int d = 0; d < 64; ++d) o[d] = 0.f;
     float m = -NXB_INF, l = 0.f;
     uint32_t sfph[2] = {0, 0};
     bool ok = true;
@@ -161,68 +170,57 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
       sfph[s] ^= 1;
       tc_fence_after();
       const uint32_t tS = tS0 + (uint32_t)(s * 128) + lane_addr;
-      // pass 1: row maximum of the transformed scores of this block
+      uint32_t sv[64];
+      tmem_ld32x2(tS, sv);
+      float x[64];
       float mx = -NXB_INF;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          const long long kj = (long long)j * BKV + c * 32 + t;
-          float x = Xform::apply(__uint_as_float(v[t]), (long long)bh, qi, kj, p.ep);
-          x = (kj < p.sk) ? x : -NXB_INF;
-          mx = nx_max(mx, x);
-        }
+      for (int t = 0; t < 64; ++t) {
+        const long long kj = (long long)j * BKV + hf * 64 + t;
+        float xv = Xform::apply(__uint_as_float(sv[t]), (long long)bh, qi, kj, p.ep);
+        xv = (kj < p.sk) ? xv : -NXB_INF;
+        x[t] = xv;
+        mx = nx_max(mx, xv);
       }
-      const float m_new = nx_max(m, mx);
+      // exchange the half-row maxima (double buffered by block parity: one bounded wait per block)
+      xmax[(s * 2 + hf) * 128 + row] = mx;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(xchg_bar);
+      if (!__all_sync(0xffffffffu, mbar_wait(xchg_bar, (uint32_t)(j & 1), abort_flag))) { ok = false; break; }
+      const float m_new = nx_max(m, nx_max(mx, xmax[(s * 2 + (hf ^ 1)) * 128 + row]));
       const float alpha = (m_new == -NXB_INF) ? 1.f : nx_exp(m - m_new);
       if (j > 0) {
         // PV of the previous block is complete (and P's buffer is free): add it in, still in the old scale
         if (!__all_sync(0xffffffffu, mbar_wait(pv_full, (uint32_t)((j - 1) & 1), abort_flag))) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tPV + lane_addr + c * 32, v);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pv[32];
+          tmem_ld32(tPV + lane_addr + (uint32_t)(c * 32), pv);
 #pragma unroll
-          for (int t = 0; t < 32; ++t) o[c * 32 + t] += __uint_as_float(v[t]);
+          for (int t = 0; t < 32; ++t) o[c * 32 + t] += __uint_as_float(pv[t]);
         }
       }
 #pragma unroll
-      for (int d = 0; d < HD; ++d) o[d] *= alpha;
+      for (int d = 0; d < 64; ++d) o[d] *= alpha;
       l *= alpha;
       m = m_new;
-      // pass 2: probabilities, their sum, and P (bf16) into shared memory as the next MMA's A operand
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS + c * 32, v);
-        uint32_t pk[16];
+      // probabilities of my 64 keys, their sum, and P (bf16): exactly one 64-key half of the A operand
+      const uint32_t rowbase = sP + (uint32_t)hf * (TILE / 2) + (uint32_t)row * 128u;
 #pragma unroll
-        for (int t = 0; t < 32; t += 2) {
-          float e2[2];
+      for (int g = 0; g < 8; ++g) {
+        uint32_t pk[4];
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const long long kj = (long long)j * BKV + c * 32 + t + u;
-            float x = Xform::apply(__uint_as_float(v[t + u]), (long long)bh, qi, kj, p.ep);
-            x = (kj < p.sk) ? x : -NXB_INF;
-            const float e = (m_new == -NXB_INF) ? 0.f : nx_exp(x - m_new);
-            e2[u] = e;
-          }
-          const unsigned short h0 = f32_to_bf16_bits(e2[0]), h1 = f32_to_bf16_bits(e2[1]);
+        for (int u = 0; u < 4; ++u) {
+          const float e0 = (m_new == -NXB_INF) ? 0.f : nx_exp(x[g * 8 + u * 2] - m_new);
+          const float e1 = (m_new == -NXB_INF) ? 0.f : nx_exp(x[g * 8 + u * 2 + 1] - m_new);
+          const unsigned short h0 = f32_to_bf16_bits(e0), h1 = f32_to_bf16_bits(e1);
           // the sum uses the same rounded values the product consumes
           l += __uint_as_float(((uint32_t)h0) << 16) + __uint_as_float(((uint32_t)h1) << 16);
-          pk[t >> 1] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+          pk[u] = (uint32_t)h0 | ((uint32_t)h1 << 16);
         }
-        // chunk c covers keys c*32 .. c*32+31: half (c >> 1), 16-byte chunks (c & 1) * 4 .. +3 of this row
-        const uint32_t rowbase = sP + (uint32_t)(c >> 1) * (TILE / 2) + (uint32_t)row * 128u;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const uint32_t chunk = (uint32_t)((c & 1) * 4 + g);
-          const uint32_t dst = rowbase + ((chunk ^ (uint32_t)(row & 7)) * 16u);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[g * 4]), "r"(pk[g * 4 + 1]), "r"(pk[g * 4 + 2]), "r"(pk[g * 4 + 3]) : "memory");
-        }
+        const uint32_t dst = rowbase + (((uint32_t)g ^ (uint32_t)(row & 7)) * 16u);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
@@ -233,17 +231,21 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
       if (__all_sync(0xffffffffu, mbar_wait(pv_full, (uint32_t)((nkv - 1) & 1), abort_flag))) {
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld32(tPV + lane_addr + c * 32, v);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pv[32];
+          tmem_ld32(tPV + lane_addr + (uint32_t)(c * 32), pv);
 #pragma unroll
-          for (int t = 0; t < 32; ++t) o[c * 32 + t] += __uint_as_float(v[t]);
+          for (int t = 0; t < 32; ++t) o[c * 32 + t] += __uint_as_float(pv[t]);
         }
-        if (qi < p.sq) {
-          const float inv = 1.f / l;
-          unsigned short* out = (unsigned short*)p.out + b_idx * p.out_bh_hi + h_idx * p.out_bh_lo + qi * p.out_row;
+        // total of the two half-row sums
+        xsum[hf * 128 + row] = l;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(xchg_bar);
+        if (__all_sync(0xffffffffu, mbar_wait(xchg_bar, (uint32_t)(nkv & 1), abort_flag)) && qi < p.sq) {
+          const float inv = 1.f / (l + xsum[(hf ^ 1) * 128 + row]);
+          unsigned short* out = (unsigned short*)p.out + b_idx * p.out_bh_hi + h_idx * p.out_bh_lo + qi * p.out_row + hf * 64;
 #pragma unroll
-          for (int d = 0; d < HD; d += 8) {
+          for (int d = 0; d < 64; d += 8) {
             uint4 w;
             w.x = f32_to_bf16_bits(o[d] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 1] * inv) << 16);
             w.y = f32_to_bf16_bits(o[d + 2] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 3] * inv) << 16);

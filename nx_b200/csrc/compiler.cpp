@@ -1764,13 +1764,13 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           o << fx.source;
           o << "struct AttnXform {\n  static __device__ __forceinline__ float apply(float s, long long bh, long long qi, long long kj, void* const* ep) { return "
             << kname << "_xform(s, bh, qi, kj, ep); }\n};\n";
-          o << "extern \"C\" __global__ void __launch_bounds__(192, 1) " << kname
+          o << "extern \"C\" __global__ void __launch_bounds__(320, 1) " << kname
             << "(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const nxb_attn::AttnParams p) {\n"
             << "  nxb_attn::attn_body<AttnXform>(map_q, map_k, map_v, p);\n}\n";
           KernelSpec ks;
           ks.name = kname;
           ks.source = o.str();
-          ks.block = 192;
+          ks.block = 320;
           ks.smem = (unsigned)attn_smem_bytes();
           ks.arg_slots = fx.arg_slots;
           ks.arg_offsets.assign(ks.arg_slots.size(), 0);

@@ -243,7 +243,7 @@ struct AttnParamsHost {
   void* ep[14];
 };
 
-int attn_smem_bytes() { return 128 * 128 * 2 * 6 + 1024 + 256; }
+int attn_smem_bytes() { return 128 * 128 * 2 * 6 + 1024 + 256 + 3072; }
 
 void attn_prepare_launch(const void* q, const void* k, const void* v, void* out, int64_t batch_heads, int64_t sq, int64_t sk, int causal,
                          void* const* ep, int n_ep, int* status_word, TcLaunch* outl) {
