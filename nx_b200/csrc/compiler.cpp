@@ -1610,9 +1610,22 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           std::set<int> seen, leaves, reds;
           for (int st : u.stores) P.cone(st, seen, leaves, reds, true);
           if (!reds.empty()) continue;
-          int D = -1, ndots = 0;
-          for (int l : leaves) if (g.nodes[l].op == "dot") { D = l; ++ndots; }
-          if (ndots != 1 || outs.count(D) || fused_dots.count(D)) continue;
+          // the product that runs last takes the epilogue; earlier products in the cone are
+          // ordinary buffers the epilogue reads
+          int D = -1, ties = 0;
+          for (int l : leaves) {
+            if (g.nodes[l].op != "dot") continue;
+            if (D < 0 || P.depth(l) > P.depth(D)) { D = l; ties = 1; }
+            else if (P.depth(l) == P.depth(D)) ++ties;
+          }
+          if (D < 0 || ties != 1 || outs.count(D) || fused_dots.count(D)) continue;
+          // a buffer produced after D (it may depend on D) cannot be read by D's epilogue
+          bool later = false;
+          for (int l : leaves) {
+            const std::string& lop = g.nodes[l].op;
+            if (l != D && (lop == "concatenate" || lop == "all_reduce" || lop == "attention") && P.depth(l) > P.depth(D)) later = true;
+          }
+          if (later) continue;
           const Node& dn = g.nodes[D];
           const DType ta = g.nodes[dn.args[0]].dt, tb = g.nodes[dn.args[1]].dt;
           if (!(ta == tb && (ta == NXB_BF16 || ta == NXB_F16) && (dn.dt == ta || dn.dt == NXB_F32))) continue;
