@@ -183,6 +183,12 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         GemmArgs fin = ga;
         if (ga.ta && !mn_a) { fin.ta = false; fin.lda = ga.k; fin.bsa = ga.m * ga.k; }
         if (ga.tb && !mn_b) { fin.tb = false; fin.ldb = ga.k; fin.bsb = ga.n * ga.k; }
+        if (ga.scale && ga.db == NXB_S8 && ga.da == NXB_BF16) {
+          // s8 weights converted inside the product kernel (few rows of x)
+          if (!wq_linear_supported(ga)) fail(NXB_ERR_RUNTIME, "internal: quantised linear outside the in-kernel conversion path");
+          launch_wq_linear(ga, d.status_dev, d.stream);
+          goto step_done;
+        }
         const bool on_tensor_cores = tc_gemm_supported(fin);
         if ((ga.scale || gs.jit_kernel >= 0) && !on_tensor_cores) fail(NXB_ERR_RUNTIME, "internal: fused product outside the tensor-core path");
         if (on_tensor_cores) {
@@ -220,6 +226,7 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
           launch_simt_gemm(ga, d.stream);
         }
       }
+    step_done:
       for (size_t s = 0; s < plan.slots.size(); ++s)
         if (plan.slots[s].kind == Slot::TEMP && plan.slots[s].last_step == (int)st && ptr[s]) { d.alloc.free(ptr[s]); ptr[s] = nullptr; }
     }

@@ -264,8 +264,8 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
   __syncthreads();
   if (*abort_flag) {
     if (threadIdx.x == 0) *(volatile int*)p.status = 1;
-    const unsigned long long t0 = now_ns();
-    while (now_ns() - t0 < 200000ull) { }
+    const long long t0 = now_cycles();
+    while (now_cycles() - t0 < 400000ll) { }
     __syncthreads();
   }
   if (warp == 1) {

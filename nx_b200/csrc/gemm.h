@@ -48,6 +48,12 @@ int attn_smem_bytes();
 // and its parameter block.
 void attn_prepare_launch(const void* q, const void* k, const void* v, void* out, int64_t batch_heads, int64_t sq, int64_t sk, int causal,
                          void* const* ep, int n_ep, int* status_word, TcLaunch* outl);
+// Weight-only quantised linear with the s8 -> bf16 conversion inside the kernel (x bf16 {m,k},
+// W s8 {n,k}, f32 scale per n): for batches of at most WQ_LINEAR_MAX_ROWS rows, where the layer
+// is a single stream over W.
+constexpr int64_t WQ_LINEAR_MAX_ROWS = 512;
+bool wq_linear_supported(const GemmArgs& g);
+void launch_wq_linear(const GemmArgs& g, int* status_word, cudaStream_t stream);
 void launch_transpose(const void* in, void* out, int64_t batch, int64_t rows, int64_t cols, size_t elem_size, cudaStream_t stream);
 
 }  // namespace nxb

@@ -107,13 +107,21 @@ void rewrite_quantised_linears(Graph& g) {
     while (sh.size() < 2) sh.insert(sh.begin(), 1);
     if (sh.size() != 2 || sh[caxis] != 1 || sh[faxis] != mul.shape[faxis]) continue;
     if (mul.shape[caxis] % 8 != 0) continue;      // the tensor-core path needs 16-byte aligned rows
-    Node wb;
-    wb.op = "as_type";
-    wb.dt = NXB_BF16;
-    wb.shape = mul.shape;
-    wb.args = {g.nodes[cvt].args[0]};
-    g.nodes.push_back(wb);
-    g.nodes[n].args[1] = (int)g.nodes.size() - 1;
+    // Few rows of x and W stored {N,K}: the product kernel converts W itself, so the layer reads
+    // the s8 weights once and no 16-bit copy of them is ever written.
+    const bool in_kernel = !getenv("NXB200_NO_INLINE_DEQUANT") && caxis == 1 && d.c1[0] == 1 && g.nodes[x].shape[0] >= 1 &&
+                           g.nodes[x].shape[0] <= WQ_LINEAR_MAX_ROWS && mul.shape[caxis] % 16 == 0;
+    if (in_kernel) {
+      g.nodes[n].args[1] = g.nodes[cvt].args[0];
+    } else {
+      Node wb;
+      wb.op = "as_type";
+      wb.dt = NXB_BF16;
+      wb.shape = mul.shape;
+      wb.args = {g.nodes[cvt].args[0]};
+      g.nodes.push_back(wb);
+      g.nodes[n].args[1] = (int)g.nodes.size() - 1;
+    }
     g.nodes[n].args.push_back(sc);      // third argument: keeps the factor alive and ordered before the product
     g.nodes[n].scale_arg = sc;
   }

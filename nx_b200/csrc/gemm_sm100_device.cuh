@@ -24,7 +24,7 @@ constexpr int STORE_STAGE = 4 * 2 * 4096;   // per epilogue warp: two 32x32 stag
 __host__ __device__ constexpr int smem_bytes_for(int bn) {
   return stages_for(bn) * (A_STAGE + bn * ROW_BYTES) + STORE_STAGE + 1024 /*alignment*/ + 256 /*barriers*/;
 }
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about two seconds of SM clock
 
 enum Kind { KIND_BF16 = 0, KIND_F16 = 1, KIND_S8 = 2 };
 
@@ -43,11 +43,9 @@ struct TcParams {
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
+// SM cycle counter: cheap to read (the global nanosecond timer costs a long round trip, which a
+// wait that misses its first poll would pay on the critical path)
+__device__ __forceinline__ long long now_cycles() { return clock64(); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -71,12 +69,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false (and raises *abort) when the limit passes or another role gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = now_ns();
+  const long long t0 = now_cycles();
   for (;;) {
     for (int i = 0; i < 64; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (now_ns() - t0 > WAIT_LIMIT_NS) {
+    if (now_cycles() - t0 > WAIT_LIMIT_CYCLES) {
       *abort_flag = 1;
       return false;
     }
@@ -411,8 +409,8 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
   __syncthreads();
   if (*abort_flag) {
     if (threadIdx.x == 0) *(volatile int*)p.status = 1;
-    const unsigned long long t0 = now_ns();
-    while (now_ns() - t0 < 200000ull) { }
+    const long long t0 = now_cycles();
+    while (now_cycles() - t0 < 400000ll) { }
     __syncthreads();
   }
   if (warp == 1) {

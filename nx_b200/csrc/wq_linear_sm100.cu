@@ -1,0 +1,327 @@
+// Weight-only quantised linear for small batches on sm_100a:
+//
+//   y[m][n] = S[n] * sum_k x[m][k] * W[n][k]       x bf16 {M,K}, W s8 {N,K}, S f32 {N}, M <= 512
+//
+// With few rows of x the layer is a stream over W (N*K bytes), so W must cross HBM exactly once
+// and never exist as 16-bit values in memory.  The product is computed transposed: a CTA owns
+// 128 output channels n (the M side of the tensor-core tile, one TMEM lane each) and up to 256
+// rows of x (the N side), so every weight is converted once.
+//   warp 0      TMA producer: per 64-wide k block the raw s8 tile of W (128 rows x 64 bytes,
+//               64-byte swizzle) and the bf16 tile of x (128-byte swizzle; rows beyond M arrive
+//               as zeros) into a deep ring (up to 16 stages: the stream is latency bound, a CTA
+//               needs ~100 KB in flight to draw its share of the memory bandwidth)
+//   12 warps    converters (every warp outside scheduler partition 0): s8 -> bf16 (exact), written as the 128-byte-swizzled K-major A tile
+//               into a second ring.  Three groups of four warps take the k blocks round-robin,
+//               so each group has three k-block periods for its wait -> convert -> fence ->
+//               arrive sequence: the latency of that sequence, not its instruction count, is
+//               what paces a pipeline whose MMAs are a few cycles each.  Afterwards the same
+//               warps are the epilogue (tcgen05.ld, scale per lane, store)
+//   warp 4      MMA issuer (scheduler partition 0, like the producer; warps 8 and 12 idle until the epilogue): tcgen05.mma M=128, N=padded batch, K=16, f32 accumulator in TMEM
+// (The weights cannot be handed over as f16, which would convert in half the instructions: an
+// instruction descriptor with A in f16 and B in bf16 is rejected as an illegal instruction.)
+// Every mbarrier wait is bounded; a stalled wait raises the abort flag, all roles leave their
+// loops, tensor memory is released and the host reports NXB_ERR_TIMEOUT.
+#include <cuda.h>
+
+#include "gemm.h"
+#include "gemm_sm100_device.cuh"
+
+namespace nxb {
+namespace {
+
+using namespace nxb_gemm;
+
+struct WqParams {
+  void* out;
+  const float* scale;
+  int* status;
+  int m, n, k;
+  int mb;        // rows of x per CTA: a multiple of 16, at most 256
+  int out_dt;
+  int stages;    // depth of the {raw W, x} ring
+  int conv_stages;   // depth of the converted-tile ring
+  int tmem_cols;
+  int nacc;      // accumulators used round-robin by consecutive MMAs (summed in the epilogue)
+};
+
+constexpr int WQ_RAW = 128 * 64;      // s8 tile of W, 64 bytes per row
+constexpr int WQ_WB = 128 * 128;      // the same tile as bf16, 128 bytes per row
+constexpr int WQ_MAX_STAGES = 16;
+constexpr int WQ_MAX_CONV_STAGES = 8;  // converted tiles between the converters and the MMA issuer
+constexpr int WQ_SMEM_LIMIT = 232448 - 1024 - 512;
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// four signed bytes -> four bf16 (exact).  Each byte, biased by 128, becomes the low mantissa
+// byte of 2^23; subtracting 2^23 + 128 leaves the integer as an f32.
+__device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t x = w ^ 0x80808080u;
+  const float f0 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7540)) - 8388736.f;
+  const float f1 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7541)) - 8388736.f;
+  const float f2 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7542)) - 8388736.f;
+  const float f3 = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7543)) - 8388736.f;
+  // exact in bf16: the upper halves of the f32 words are the result (a byte permute, not a
+  // quarter-rate convert)
+  lo = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+  hi = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+}
+
+constexpr int WQ_THREADS = 512;
+constexpr int WQ_MMA_WARP = 4;      // same scheduler partition as the producer (warp 0): none of the busy converter warps run there
+
+// Bounded wait that sleeps between polls: for roles with slack, so that their polling does not
+// compete with the producer and MMA threads for issue slots and the barrier unit.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = now_cycles();
+  for (;;) {
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(40);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag) return false;
+    if (now_cycles() - t0 > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(WQ_THREADS, 1)
+wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, WqParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t x_bytes = (uint32_t)p.mb * 128u;
+  const uint32_t stage_bytes = WQ_RAW + x_bytes;
+  const uint32_t wb0 = base + (uint32_t)p.stages * stage_bytes;
+  const uint32_t bars = wb0 + (uint32_t)p.conv_stages * WQ_WB;
+  const uint32_t full0 = bars, empty0 = bars + 128, conv0 = bars + 256, wbe0 = bars + 320, acc_full = bars + 384, tmem_slot = bars + 392;
+  unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + (tmem_slot - base));
+  volatile int* abort_flag = (volatile int*)(gen_base + (tmem_slot - base) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = (int)blockIdx.x * 128, m0 = (int)blockIdx.y * p.mb;
+  const int kblocks = (p.k + 63) / 64;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int c = 0; c < p.conv_stages; ++c) { mbar_init(conv0 + 8 * c, 4); mbar_init(wbe0 + 8 * c, 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == WQ_MMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(p.tmem_cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) break;
+        const uint32_t st = base + (uint32_t)s * stage_bytes;
+        mbar_expect_tx(full0 + 8 * s, WQ_RAW + x_bytes);
+        tma_load_3d(st, &map_w, full0 + 8 * s, kb * 64, n0, 0);
+        tma_load_3d(st + WQ_RAW, &map_x, full0 + 8 * s, kb * 64, m0, 0);
+        if (++s == p.stages) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == WQ_MMA_WARP) {
+    if (lane == 0) {
+      // bf16 x bf16 -> f32, both operands K-major, M = 128 channels, N = padded batch
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mb >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+      // This single thread is the critical path when N is narrow (an MMA is a few cycles of
+      // work), so its loop carries running descriptors, barrier addresses and accumulator
+      // offsets instead of recomputing them.
+      const uint64_t adesc0 = make_desc(wb0), bdesc0 = make_desc(base + WQ_RAW);
+      const uint64_t astep = (uint64_t)(WQ_WB >> 4), bstep = (uint64_t)(stage_bytes >> 4);
+      uint64_t adesc = adesc0, bdesc = bdesc0;
+      uint32_t conv_bar = conv0, wbe_bar = wbe0, empty_bar = empty0;
+      uint32_t acc = tmem_base;
+      const uint32_t acc_end = tmem_base + (uint32_t)(p.nacc * p.mb);
+      int s = 0, c = 0, fresh = p.nacc;       // `fresh` accumulators have not been written yet
+      uint32_t cph = 0;
+      bool ok = true;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        // the converters arrive on conv only after the stage's TMA data (x included) has landed
+        if (!mbar_wait(conv_bar, cph, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        // consecutive MMAs go to different accumulators: accumulating into the columns the
+        // previous one is still writing would serialise them on the pipeline's latency
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4) {
+          tc_mma(acc, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, fresh > 0 ? 0u : 1u, false);
+          if (fresh > 0) --fresh;
+          acc += (uint32_t)p.mb;
+          if (acc == acc_end) acc = tmem_base;
+        }
+        tc_commit(empty_bar);
+        tc_commit(wbe_bar);
+        adesc += astep; bdesc += bstep; conv_bar += 8; wbe_bar += 8; empty_bar += 8;
+        if (++s == p.stages) { s = 0; bdesc = bdesc0; empty_bar = empty0; }
+        if (++c == p.conv_stages) { c = 0; cph ^= 1; adesc = adesc0; conv_bar = conv0; wbe_bar = wbe0; }
+      }
+      if (ok) tc_commit(acc_full);
+    }
+  } else {
+    // The converter warps are the twelve outside scheduler partition 0 (where the producer and
+    // the MMA issuer live: a single thread issuing MMAs loses most of its issue slots to busy
+    // warps on the same scheduler).  Three groups of four warps take the k blocks round-robin,
+    // one thread per row of W, so a group has three k-block periods for its wait -> convert ->
+    // fence -> arrive sequence.
+    const bool converter = (warp & 3) != 0;
+    const int ci = (warp >> 2) * 3 + (warp & 3) - 1;
+    const int grp = ci >> 2;
+    const int r = (ci & 3) * 32 + lane;
+    int s = grp % p.stages, cs = grp % p.conv_stages;
+    uint32_t ph = (uint32_t)((grp / p.stages) & 1), cph = (uint32_t)((grp / p.conv_stages) & 1);
+    bool ok = true;
+    for (int kb = grp; converter && kb < kblocks && ok; kb += 3) {
+      // one lane per warp polls the barriers
+      int okw = 1;
+      if (lane == 0) okw = mbar_wait_relaxed(full0 + 8 * s, ph, abort_flag) && mbar_wait_relaxed(wbe0 + 8 * cs, cph ^ 1, abort_flag);
+      okw = __shfl_sync(0xffffffffu, okw, 0);
+      __syncwarp();
+      if (!okw) { ok = false; break; }
+      const uint32_t st = base + (uint32_t)s * stage_bytes;
+      const uint32_t row = wb0 + (uint32_t)cs * WQ_WB + (uint32_t)r * 128u;
+      uint32_t w[16];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {                     // 16-byte chunks of the 64-byte s8 row
+        const uint32_t src = st + (uint32_t)r * 64u + (uint32_t)((c ^ ((r >> 1) & 3)) * 16);
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4 * c]), "=r"(w[4 * c + 1]), "=r"(w[4 * c + 2]), "=r"(w[4 * c + 3]) : "r"(src));
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[8];
+        s8x4_to_bf16x4(w[4 * c], o[0], o[1]);
+        s8x4_to_bf16x4(w[4 * c + 1], o[2], o[3]);
+        s8x4_to_bf16x4(w[4 * c + 2], o[4], o[5]);
+        s8x4_to_bf16x4(w[4 * c + 3], o[6], o[7]);
+        const uint32_t d0 = row + (uint32_t)(((2 * c) ^ (r & 7)) * 16), d1 = row + (uint32_t)(((2 * c + 1) ^ (r & 7)) * 16);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(conv0 + 8 * cs);
+      s += 3;
+      while (s >= p.stages) { s -= p.stages; ph ^= 1; }
+      cs += 3;
+      while (cs >= p.conv_stages) { cs -= p.conv_stages; cph ^= 1; }
+    }
+    // epilogue: lane = output channel, columns = rows of x
+    int acc_ok = 1;
+    if (lane == 0) acc_ok = ok && mbar_wait_relaxed(acc_full, 0, abort_flag);
+    acc_ok = __shfl_sync(0xffffffffu, acc_ok, 0);
+    __syncwarp();
+    if (acc_ok) {
+      tc_fence_after();
+      const int q = warp & 3;
+      const long long n = (long long)n0 + q * 32 + lane;
+      const float sc = n < p.n ? p.scale[n] : 0.f;
+      // TMEM quarter 0 is served by the two idle warps of partition 0 (8 and 12), the others by four warps each
+      const int nshare = q == 0 ? 2 : 4, share = q == 0 ? (warp >> 2) - 2 : (warp >> 2);
+      for (int c16 = share; c16 < p.mb / 16; c16 += nshare) {
+        if (m0 + c16 * 16 >= p.m) break;                 // warp-uniform
+        uint32_t v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(c16 * 16), v);
+        for (int a = 1; a < p.nacc; ++a) {
+          uint32_t u[16];
+          tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * p.mb + c16 * 16), u);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+        }
+        if (n < p.n) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const long long m = (long long)m0 + c16 * 16 + j;
+            if (m >= p.m) break;
+            const float y = __uint_as_float(v[j]) * sc;
+            if (p.out_dt == NXB_F32) ((float*)p.out)[m * p.n + n] = y;
+            else ((unsigned short*)p.out)[m * p.n + n] = f32_to_bf16_bits(y);
+          }
+        }
+      }
+      tc_fence_before();
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) *(volatile int*)p.status = 1;
+    const long long t0 = now_cycles();
+    while (now_cycles() - t0 < 400000ll) { }
+    __syncthreads();
+  }
+  if (warp == WQ_MMA_WARP) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols) : "memory");
+  }
+}
+
+CUtensorMap wq_map(const void* ptr, CUtensorMapDataType type, size_t es, int64_t k, int64_t rows, int64_t ld, int box_rows, CUtensorMapSwizzle sw) {
+  const DriverApi& drv = driver();
+  if (!drv.cuTensorMapEncodeTiled) fail(NXB_ERR_RUNTIME, "cuTensorMapEncodeTiled is unavailable");
+  CUtensorMap m;
+  cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, 1};
+  cuuint64_t strides[2] = {(cuuint64_t)(ld * es), (cuuint64_t)(ld * es) * (cuuint64_t)rows};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  check_cu(drv.cuTensorMapEncodeTiled(&m, type, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+           "cuTensorMapEncodeTiled");
+  return m;
+}
+
+}  // namespace
+
+bool wq_linear_supported(const GemmArgs& g) {
+  return g.da == NXB_BF16 && g.db == NXB_S8 && g.scale && !g.ta && !g.tb && g.batch == 1 && g.m >= 1 && g.m <= WQ_LINEAR_MAX_ROWS &&
+         g.k % 16 == 0 && (g.lda * 2) % 16 == 0 && g.ldb % 16 == 0 && (g.dc == NXB_F32 || g.dc == NXB_BF16) &&
+         ((uintptr_t)g.a % 16) == 0 && ((uintptr_t)g.b % 16) == 0;
+}
+
+void launch_wq_linear(const GemmArgs& g, int* status_word, cudaStream_t stream) {
+  WqParams p{};
+  p.out = g.c;
+  p.scale = (const float*)g.scale;
+  p.status = status_word;
+  p.m = (int)g.m; p.n = (int)g.n; p.k = (int)g.k;
+  p.mb = (int)std::min<int64_t>(256, (g.m + 15) / 16 * 16);
+  p.out_dt = (int)g.dc;
+  const int stage = WQ_RAW + p.mb * 128;
+  const char* cs_env = getenv("NXB200_WQ_CONV_STAGES");
+  p.conv_stages = cs_env ? std::max(2, std::min(WQ_MAX_CONV_STAGES, atoi(cs_env))) : (p.mb <= 64 ? 8 : 4);
+  p.stages = std::min(WQ_MAX_STAGES, (WQ_SMEM_LIMIT - p.conv_stages * WQ_WB) / stage);
+  const int kblocks = (p.k + 63) / 64;
+  p.nacc = std::max(1, std::min(std::min(8, 512 / p.mb), kblocks * 4));
+  p.tmem_cols = 32;
+  while (p.tmem_cols < p.nacc * p.mb) p.tmem_cols *= 2;
+  CUtensorMap mw = wq_map(g.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.k, g.n, g.ldb, 128, CU_TENSOR_MAP_SWIZZLE_64B);
+  CUtensorMap mx = wq_map(g.a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g.k, g.m, g.lda, p.mb, CU_TENSOR_MAP_SWIZZLE_128B);
+  const int smem = p.stages * stage + p.conv_stages * WQ_WB + 1024 + 512;
+  NXB_CUDA(cudaFuncSetAttribute(wq_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid((unsigned)((g.n + 127) / 128), (unsigned)((g.m + p.mb - 1) / p.mb));
+  wq_linear_kernel<<<grid, WQ_THREADS, smem, stream>>>(mw, mx, p);
+  NXB_CUDA(cudaGetLastError());
+}
+
+}  // namespace nxb

@@ -127,6 +127,16 @@ def test_quantised_linear_reduced(m):
     assert ti == ("s", 32) and np.array_equal(gi, ri)
 
 
+@pytest.mark.parametrize("m,n,k", [(5, 1000, 528), (48, 136, 4096), (300, 392, 80), (512, 128, 64), (513, 256, 128)])
+def test_quantised_linear_ragged(m, n, k):
+    """Edges of the in-kernel conversion path: rows that do not fill a batch tile, a second batch
+    tile, channels and k that end inside a tile, and (513 rows) the hand-over to the general path."""
+    f_in, _ = configs.quantised_inputs(m=m, n=n, k=k)
+    (g, r, t), = run_both(configs.quantised_linear, f_in)
+    assert t == ("f", 32) and g.shape == (m, n)
+    assert_close(g, r, rtol=1e-5, atol=1e-5 * float(np.abs(r).max()), what=f"quantised linear {m}x{n}x{k}")
+
+
 def test_softmax_rows_sum_to_one_at_full_width():
     """Size-independent property at the full row width: softmax rows sum to 1,
     exp(x-max) has a 1 at the argmax, logsumexp = log(sum) + max."""
