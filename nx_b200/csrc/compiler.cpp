@@ -1612,13 +1612,13 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           if (!reds.empty()) continue;
           // the product that runs last takes the epilogue; earlier products in the cone are
           // ordinary buffers the epilogue reads
-          int D = -1, ties = 0;
+          // (products of equal depth cannot depend on one another: the later node takes it)
+          int D = -1;
           for (int l : leaves) {
             if (g.nodes[l].op != "dot") continue;
-            if (D < 0 || P.depth(l) > P.depth(D)) { D = l; ties = 1; }
-            else if (P.depth(l) == P.depth(D)) ++ties;
+            if (D < 0 || P.depth(l) > P.depth(D) || (P.depth(l) == P.depth(D) && l > D)) D = l;
           }
-          if (D < 0 || ties != 1 || outs.count(D) || fused_dots.count(D)) continue;
+          if (D < 0 || outs.count(D) || fused_dots.count(D)) continue;
           // a buffer produced after D (it may depend on D) cannot be read by D's epilogue
           bool later = false;
           for (int l : leaves) {

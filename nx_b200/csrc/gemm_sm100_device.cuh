@@ -80,6 +80,32 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
   }
 }
+// Bounded wait that sleeps between polls: for roles with slack (an epilogue waiting out a whole
+// main loop), so that their polling does not take issue slots and barrier-unit bandwidth from
+// the single threads that feed the tensor cores on the same scheduler.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = now_cycles();
+  for (;;) {
+    for (int i = 0; i < 64; ++i) {
+      __nanosleep(40);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (*abort_flag) return false;
+    if (now_cycles() - t0 > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+// The same wait done by lane 0 on behalf of its warp (all 32 lanes must call).
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait_relaxed(bar, parity, abort_flag);
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();
+  return ok != 0;
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
   asm volatile(
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
@@ -326,7 +352,7 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       const int r = (int)(t % tiles_per_batch);
       const int nt = r / p.mtiles, mt = r % p.mtiles;
       // warp-uniform outcome: the tensor-memory loads below need the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(tfull0 + 8 * a, aph, abort_flag))) { ok = false; break; }
+      if (!mbar_wait_warp(tfull0 + 8 * a, aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const long long m = (long long)mt * BM + q * 32 + lane;
       const bool staged = Epi::kStaged && p.tma_store != 0;

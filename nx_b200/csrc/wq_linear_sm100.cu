@@ -77,24 +77,6 @@ __device__ __forceinline__ void s8x4_to_bf16x4(uint32_t w, uint32_t& lo, uint32_
 constexpr int WQ_THREADS = 512;
 constexpr int WQ_MMA_WARP = 4;      // same scheduler partition as the producer (warp 0): none of the busy converter warps run there
 
-// Bounded wait that sleeps between polls: for roles with slack, so that their polling does not
-// compete with the producer and MMA threads for issue slots and the barrier unit.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = now_cycles();
-  for (;;) {
-    for (int i = 0; i < 64; ++i) {
-      __nanosleep(40);
-      if (mbar_try_wait(bar, parity)) return true;
-    }
-    if (*abort_flag) return false;
-    if (now_cycles() - t0 > WAIT_LIMIT_CYCLES) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
-
 __global__ void __launch_bounds__(WQ_THREADS, 1)
 wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, WqParams p) {
   extern __shared__ unsigned char smem_raw[];
