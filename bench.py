@@ -228,6 +228,8 @@ def decoder_section(timer, device, rank, world, dist, torch):
         blob, _, _ = sharding.partition(block, mesh, shardings, [defn.template(a.shape, t) for a, t in local], rank)
         prog = defn.Program(blob)
         dev = device_inputs(local)
+        if dist is not None:
+            dist.barrier()          # every rank has built its program: kernels that wait on peers are bounded
         outs = prog.run(dev, device)
         if dist is not None:
             dist.barrier()
@@ -241,9 +243,17 @@ def decoder_section(timer, device, rank, world, dist, torch):
         run_sharded(sharding.Mesh("dp", (world,)), [{0: [0]}] + [{}] * 9, f"dp{world}")
         mesh = sharding.Mesh("tp", (world,))
         ex = sharding.torch_exchange()
-        sharding.init_tensor_parallel_group(mesh, 0, rank, device, ex)
+        peer = sharding.init_tensor_parallel_group(mesh, 0, rank, device, ex, gather=sharding.torch_gather(),
+                                                   peer_elems=batch * seq * 4096)
         tp = [{}, {1: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {}, {}]
+        # the two all-reduces as NCCL calls after their products, then fused into the products over peer memory
+        os.environ["NXB200_NO_FUSED_ALLREDUCE"] = "1"
+        run_sharded(mesh, tp, f"tp{world}_nccl")
+        del os.environ["NXB200_NO_FUSED_ALLREDUCE"]
+        before = sharding.fused_all_reduce_launches()
         run_sharded(mesh, tp, f"tp{world}")
+        out[f"tp{world}"]["all_reduce"] = ("fused into the products over peer memory"
+                                           if peer and sharding.fused_all_reduce_launches() > before else "NCCL")
     return out
 
 

@@ -187,6 +187,17 @@ int nxb200_memory_reset_peak(int device);
 int nxb200_comm_id(uint8_t id[NXB_COMM_ID_BYTES]);
 int nxb200_comm_init(int device, int rank, int world, const uint8_t id[NXB_COMM_ID_BYTES]);
 int nxb200_comm_all_reduce_sum(nxb200_buffer *buf);
+/* Peer memory for the product fused with the sum over ranks (XLA would emit the all-reduce
+ * as its own NCCL call after the dot, exla/lib/exla/defn.ex:40-72; here one kernel does both
+ * when this is set up).  peer_alloc reserves this rank's region for matrices of up to `elems`
+ * 16-bit elements and returns a blob (CUDA IPC handle + device UUID); the host gathers the
+ * blobs of all ranks in rank order and passes them to peer_open, which sets *enabled to 0 and
+ * keeps the group on NCCL when two ranks share a GPU or a region cannot be mapped. */
+#define NXB_COMM_PEER_BLOB_BYTES 80
+int nxb200_comm_peer_alloc(int device, uint64_t elems, uint8_t blob[NXB_COMM_PEER_BLOB_BYTES]);
+int nxb200_comm_peer_open(const uint8_t *blobs, int *enabled);
+/* Number of products this process has run fused with their all-reduce (diagnostics). */
+int nxb200_comm_fused_launches(uint64_t *count);
 int nxb200_comm_destroy(void);
 
 #ifdef __cplusplus

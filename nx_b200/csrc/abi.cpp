@@ -133,11 +133,14 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
       }
     }
     const DriverApi& drv = driver();
+    bool skip_step = false;      // the previous product already did this step's all-reduce
     for (size_t st = 0; st < plan.steps.size(); ++st) {
       for (size_t s = 0; s < plan.slots.size(); ++s)
         if (plan.slots[s].kind == Slot::TEMP && plan.slots[s].first_step == (int)st && !ptr[s]) ptr[s] = d.alloc.alloc(plan.slots[s].nbytes);
       const Step& step = plan.steps[st];
-      if (step.kind == Step::KERNEL) {
+      if (skip_step) {
+        skip_step = false;
+      } else if (step.kind == Step::KERNEL) {
         const KernelSpec& ks = plan.kernels[step.index];
         std::vector<void*> argv(ks.arg_slots.size());
         std::vector<void*> argp(ks.arg_slots.size());
@@ -218,7 +221,19 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
             check_cu(drv.cuLaunchKernel(L.functions[gs.jit_kernel], tl.grid, 1, 1, 192, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
                      ("launching " + ks.name).c_str());
           } else {
-            launch_tc_gemm(ga, d.status_dev, d.sm_count, d.stream);
+            // a row-parallel product whose only reader is the sum over ranks: one kernel does
+            // both over peer memory when the group has it (otherwise NCCL follows as its own step)
+            bool fused = false;
+            if (st + 1 < plan.steps.size() && plan.steps[st + 1].kind == Step::ALLREDUCE) {
+              const CollectiveSpec& cs = plan.collectives[plan.steps[st + 1].index];
+              const Slot& prod = plan.slots[gs.out_slot];
+              if (cs.in_slot == gs.out_slot && prod.kind == Slot::TEMP && prod.last_step == (int)st + 1 && cs.dt == ga.dc) {
+                if (!ptr[cs.out_slot]) ptr[cs.out_slot] = d.alloc.alloc(plan.slots[cs.out_slot].nbytes);
+                fused = launch_tc_gemm_allreduce(ga, ptr[cs.out_slot], d.status_dev, d.sm_count, d.stream);
+              }
+            }
+            if (fused) skip_step = true;
+            else launch_tc_gemm(ga, d.status_dev, d.sm_count, d.stream);
           }
           if (ta) d.alloc.free(ta);
           if (tb) d.alloc.free(tb);

@@ -3,7 +3,7 @@
 // without NCCL) never load it.
 #include <dlfcn.h>
 
-#include "common.h"
+#include "gemm.h"
 
 namespace nxb {
 namespace {
@@ -52,6 +52,17 @@ void check_nccl(ncclResult_t r, const char* what) {
 ncclComm_t g_comm = nullptr;
 int g_comm_device = -1, g_world = 1, g_rank = 0;
 
+// Peer memory of the group: see PeerView (gemm.h).
+struct PeerState {
+  bool enabled = false;
+  void* local = nullptr;
+  void* peers[8] = {};
+  size_t bytes = 0;
+  PeerView view;
+} g_peer;
+
+size_t align256(size_t x) { return (x + 255) / 256 * 256; }
+
 }  // namespace
 
 int comm_world() { return g_world; }
@@ -98,7 +109,80 @@ void comm_all_reduce(const void* in, void* out, size_t count, DType dt, Device& 
   check_nccl(nccl().AllReduce(in, out, count, t, ncclSum, g_comm, d.stream), "ncclAllReduce");
 }
 
+// Allocates this rank's region for matrices of up to `elems` 16-bit elements and writes the
+// blob the other ranks need: the 64-byte IPC handle followed by the device's 16-byte UUID.
+void comm_peer_alloc(int dev, size_t elems, uint8_t* blob) {
+  if (!g_comm) fail(NXB_ERR_INVALID_ARGUMENT, "no communicator: call nxb200_comm_init first");
+  if (g_world > 8) fail(NXB_ERR_UNSUPPORTED, "peer memory for more than 8 ranks");
+  if (g_peer.local) fail(NXB_ERR_INVALID_ARGUMENT, "peer memory already allocated in this process");
+  Device& d = device(dev);
+  (void)d;
+  PeerView& v = g_peer.view;
+  v = PeerView();
+  v.rank = g_rank;
+  v.world = g_world;
+  v.elems = elems;
+  v.flag_words = 4 * (elems / (128 * 64) + 64);     // 4 words per output tile of at least 128 x 64
+  v.partial_off = 0;
+  v.result_off = align256(elems * 2);
+  v.ready_off = v.result_off + align256(elems * 2);
+  v.reduced_off = v.ready_off + align256(v.flag_words * 4);
+  g_peer.bytes = v.reduced_off + align256(v.flag_words * 4);
+  NXB_CUDA(cudaMalloc(&g_peer.local, g_peer.bytes));
+  NXB_CUDA(cudaMemset(g_peer.local, 0, g_peer.bytes));
+  NXB_CUDA(cudaDeviceSynchronize());
+  cudaIpcMemHandle_t h;
+  NXB_CUDA(cudaIpcGetMemHandle(&h, g_peer.local));
+  static_assert(sizeof(h) == 64, "IPC handle size");
+  memcpy(blob, &h, 64);
+  cudaDeviceProp prop;
+  NXB_CUDA(cudaGetDeviceProperties(&prop, dev));
+  memcpy(blob + 64, &prop.uuid, 16);
+}
+
+// Maps the other ranks' regions.  `blobs` holds world x NXB_COMM_PEER_BLOB_BYTES bytes in rank
+// order.  Returns false (and leaves the group on NCCL) when two ranks share a GPU - kernels that
+// wait on one another must never share one - or a region cannot be mapped.
+bool comm_peer_open(const uint8_t* blobs) {
+  if (!g_peer.local) fail(NXB_ERR_INVALID_ARGUMENT, "peer memory was not allocated");
+  for (int a = 0; a < g_world; ++a)
+    for (int b = a + 1; b < g_world; ++b)
+      if (memcmp(blobs + a * 80 + 64, blobs + b * 80 + 64, 16) == 0) return false;
+  for (int r = 0; r < g_world; ++r) {
+    if (r == g_rank) { g_peer.peers[r] = g_peer.local; continue; }
+    cudaIpcMemHandle_t h;
+    memcpy(&h, blobs + r * 80, 64);
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+      cudaGetLastError();
+      for (int q = 0; q < r; ++q)
+        if (q != g_rank && g_peer.peers[q]) { cudaIpcCloseMemHandle(g_peer.peers[q]); g_peer.peers[q] = nullptr; }
+      return false;
+    }
+    g_peer.peers[r] = p;
+  }
+  for (int r = 0; r < g_world; ++r) g_peer.view.base[r] = g_peer.peers[r];
+  g_peer.enabled = true;
+  return true;
+}
+
+bool comm_peer_view(int64_t m, int64_t n, int64_t mtiles, int64_t ntiles, PeerView* v) {
+  if (!g_peer.enabled) return false;
+  if ((size_t)(m * n) > g_peer.view.elems || (size_t)(mtiles * ntiles * 4) > g_peer.view.flag_words) return false;
+  if (mtiles % g_world != 0) return false;
+  g_peer.view.epoch += 1;
+  *v = g_peer.view;
+  return true;
+}
+
 void comm_destroy() {
+  if (g_peer.local) {
+    cudaDeviceSynchronize();
+    for (int r = 0; r < g_world; ++r)
+      if (r != g_rank && g_peer.peers[r]) cudaIpcCloseMemHandle(g_peer.peers[r]);
+    cudaFree(g_peer.local);
+    g_peer = PeerState();
+  }
   if (g_comm) {
     nccl().CommDestroy(g_comm);
     g_comm = nullptr;
@@ -142,6 +226,20 @@ int nxb200_comm_all_reduce_sum(nxb200_buffer* buf) {
     Device& d = device(b->device);
     comm_all_reduce_sum_ptr(b->ptr, (size_t)shape_numel(b->dims), b->dtype, d);
   }, buf);
+}
+
+int nxb200_comm_peer_alloc(int dev, uint64_t elems, uint8_t blob[NXB_COMM_PEER_BLOB_BYTES]) {
+  struct A { int d; uint64_t e; uint8_t* b; } a{dev, elems, blob};
+  return guarded_comm([](void* p) { A* a = (A*)p; comm_peer_alloc(a->d, (size_t)a->e, a->b); }, &a);
+}
+
+int nxb200_comm_peer_open(const uint8_t* blobs, int* enabled) {
+  struct A { const uint8_t* b; int* e; } a{blobs, enabled};
+  return guarded_comm([](void* p) { A* a = (A*)p; *a->e = comm_peer_open(a->b) ? 1 : 0; }, &a);
+}
+
+int nxb200_comm_fused_launches(uint64_t* count) {
+  return guarded_comm([](void* p) { *(uint64_t*)p = g_peer.enabled ? g_peer.view.epoch : 0; }, count);
 }
 
 int nxb200_comm_destroy(void) {

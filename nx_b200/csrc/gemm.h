@@ -48,6 +48,22 @@ int attn_smem_bytes();
 // and its parameter block.
 void attn_prepare_launch(const void* q, const void* k, const void* v, void* out, int64_t batch_heads, int64_t sq, int64_t sk, int causal,
                          void* const* ep, int n_ep, int* status_word, TcLaunch* outl);
+// Peer memory of the tensor-parallel group (comm.cpp): one region per rank, mapped into every
+// process, holding [partial product][reduced tiles][ready flags][reduced flags].
+struct PeerView {
+  int rank = 0, world = 1;
+  uint32_t epoch = 0;              // launch number, the same on every rank
+  void* base[8] = {};              // region of each rank ([rank] is the local one)
+  size_t partial_off = 0, result_off = 0, ready_off = 0, reduced_off = 0;
+  size_t elems = 0, flag_words = 0;
+};
+// Fills `v` and advances the epoch when peer memory is set up, a matrix of m x n 16-bit elements
+// with mtiles x ntiles output tiles fits and the ranks can share the row tiles evenly; false
+// otherwise (the caller uses NCCL instead).
+bool comm_peer_view(int64_t m, int64_t n, int64_t mtiles, int64_t ntiles, PeerView* v);
+// Product of a row-parallel linear fused with the sum over ranks (one kernel over peer memory).
+// Returns false, launching nothing, when the shape or the communicator does not allow it.
+bool launch_tc_gemm_allreduce(const GemmArgs& g, void* out, int* status_word, int sm_count, cudaStream_t stream);
 // Weight-only quantised linear with the s8 -> bf16 conversion inside the kernel (x bf16 {m,k},
 // W s8 {n,k}, f32 scale per n): for batches of at most WQ_LINEAR_MAX_ROWS rows, where the layer
 // is a single stream over W.

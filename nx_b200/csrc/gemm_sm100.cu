@@ -32,6 +32,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   tc_gemm_body<KIND, BN, EpiStore>(map_a, map_b, map_c, p);
 }
 
+template <int KIND, int BN>
+__global__ void __launch_bounds__(320, 1)
+tc_gemm_allreduce_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const __grid_constant__ CUtensorMap map_c, TcParams p, const __grid_constant__ CommArgs cm) {
+  tc_gemm_body<KIND, BN, EpiStore, true>(map_a, map_b, map_c, p, &cm);
+}
+
 CUtensorMapDataType tm_type(DType t) {
   switch (t) {
     case NXB_BF16: return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -224,6 +231,49 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
   else if (g.da == NXB_F16) NXB_LAUNCH_KIND(KIND_F16);
   else NXB_LAUNCH_KIND(KIND_S8);
 #undef NXB_LAUNCH_KIND
+}
+
+bool launch_tc_gemm_allreduce(const GemmArgs& g, void* out, int* status_word, int sm_count, cudaStream_t stream) {
+  if (getenv("NXB200_NO_FUSED_ALLREDUCE")) return false;
+  if (!tc_gemm_supported(g) || g.batch != 1 || g.scale || g.bias || g.dc != g.da || (g.da != NXB_BF16 && g.da != NXB_F16) || g.n % 8 != 0) return false;
+  const int bn = tc_pick_bn(g.m, g.n, g.batch, sm_count);
+  TcParams p = make_params(g, bn, status_word);
+  PeerView pv;
+  // (comm_peer_view also checks that every rank owns the same number of row tiles)
+  if (!comm_peer_view(g.m, g.n, p.mtiles, p.ntiles, &pv)) return false;
+  CommArgs cm{};
+  cm.rank = pv.rank; cm.world = pv.world; cm.epoch = pv.epoch;
+  for (int r = 0; r < pv.world; ++r) {
+    char* b = (char*)pv.base[r];
+    cm.partial[r] = (const unsigned short*)(b + pv.partial_off);
+    cm.result[r] = (unsigned short*)(b + pv.result_off);
+    cm.ready[r] = (uint32_t*)(b + pv.ready_off);
+    cm.reduced[r] = (uint32_t*)(b + pv.reduced_off);
+  }
+  cm.out = (unsigned short*)out;
+  p.c = (void*)cm.partial[pv.rank];
+  p.tma_store = 0;
+  CUtensorMap ma = g.ta ? make_map_mn(g.a, g.da, g.k, g.m, g.batch, g.lda, g.bsa) : make_map(g.a, g.da, g.k, g.m, g.batch, g.lda, g.bsa, BM);
+  CUtensorMap mb = g.tb ? make_map_mn(g.b, g.db, g.k, g.n, g.batch, g.ldb, g.bsb) : make_map(g.b, g.db, g.k, g.n, g.batch, g.ldb, g.bsb, bn);
+  CUtensorMap mc;
+  memset(&mc, 0, sizeof mc);
+  long long tiles = (long long)p.mtiles * p.ntiles;
+  unsigned grid = (unsigned)std::min<long long>(tiles, sm_count);
+  auto launch = [&](auto kern, int smem) {
+    NXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    kern<<<grid, 320, smem, stream>>>(ma, mb, mc, p, cm);
+    NXB_CUDA(cudaGetLastError());
+  };
+#define NXB_LAUNCH_AR(K)                                                                 \
+  do {                                                                                   \
+    if (bn == 256) launch(tc_gemm_allreduce_kernel<K, 256>, smem_bytes_for(256));        \
+    else if (bn == 128) launch(tc_gemm_allreduce_kernel<K, 128>, smem_bytes_for(128));   \
+    else launch(tc_gemm_allreduce_kernel<K, 64>, smem_bytes_for(64));                    \
+  } while (0)
+  if (g.da == NXB_BF16) NXB_LAUNCH_AR(KIND_BF16);
+  else NXB_LAUNCH_AR(KIND_F16);
+#undef NXB_LAUNCH_AR
+  return true;
 }
 
 const char* attention_device_source() {

@@ -42,6 +42,22 @@ struct TcParams {
   void* ep[14];      // buffers of a generated epilogue, in its argument order
 };
 
+// Product fused with a sum over ranks (tensor parallelism), over peer memory.  Every rank owns the
+// row tiles mt with mt % world == rank.  Buffers are per rank and mapped into every process
+// (`[rank]` is the local one): `partial` holds this rank's product tiles, `result` the reduced
+// tiles it owns; `ready` / `reduced` hold one word per (tile, 32-row quarter) carrying the epoch
+// (launch number) of the last complete write.  All waits are reads: nothing is pushed to a peer.
+struct CommArgs {
+  int rank, world;
+  uint32_t epoch;
+  int pad;
+  const unsigned short* partial[8];
+  unsigned short* result[8];
+  uint32_t* ready[8];
+  uint32_t* reduced[8];
+  unsigned short* out;       // this rank's copy of the reduced matrix [m][n] (bf16 or f16 bits)
+};
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 // SM cycle counter: cheap to read (the global nanosecond timer costs a long round trip, which a
 // wait that misses its first poll would pay on the critical path)
@@ -105,6 +121,35 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   ok = __shfl_sync(0xffffffffu, ok, 0);
   __syncwarp();
   return ok != 0;
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until a flag (possibly in a peer's memory) has reached `epoch`.
+__device__ __forceinline__ bool flag_wait(const uint32_t* f, uint32_t epoch, volatile int* abort_flag) {
+  const long long t0 = now_cycles();
+  for (;;) {
+    for (int i = 0; i < 16; ++i) {
+      if ((int)(ld_acquire_sys(f) - epoch) >= 0) return true;
+      __nanosleep(200);
+    }
+    if (*abort_flag) return false;
+    // ranks may reach the kernel seconds apart (host-side skew): about half a minute
+    if (now_cycles() - t0 > 15 * WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
 }
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
   asm volatile(
@@ -239,8 +284,110 @@ struct EpiStore {
   }
 };
 
-template <int KIND, int BN, class Epi>
-__device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const TcParams& p) {
+// Tile t of this CTA's walk.  Plain products: consecutive CTAs share a column panel of B and walk
+// down M.  Fused with the sum over ranks: the tiles owned by the next rank come first and this
+// rank's own tiles last, so every owner finds its peers' contributions early.
+template <bool COMM>
+__device__ __forceinline__ void tile_coords(long long t, const TcParams& p, const CommArgs* cm, int& b, int& mt, int& nt) {
+  if (!COMM) {
+    const long long tiles_per_batch = (long long)p.mtiles * p.ntiles;
+    b = (int)(t / tiles_per_batch);
+    const int r = (int)(t % tiles_per_batch);
+    nt = r / p.mtiles;
+    mt = r % p.mtiles;
+  } else {
+    const int mpo = p.mtiles / cm->world;
+    const long long per_owner = (long long)mpo * p.ntiles;
+    const int k = (int)(t / per_owner), j = (int)(t % per_owner);
+    const int owner = (cm->rank + 1 + k) % cm->world;
+    b = 0;
+    nt = j / mpo;
+    mt = (j % mpo) * cm->world + owner;
+  }
+}
+
+// The role of warps 6..9 of the fused kernel: reduce the tiles this rank owns (reading every
+// rank's partial tile), then fetch the tiles the other ranks reduced.  `cw` = 32-row quarter.
+template <int BN>
+__device__ __forceinline__ void comm_role(const TcParams& p, const CommArgs& cm, volatile int* abort_flag) {
+  const int cw = (threadIdx.x >> 5) - 6, lane = threadIdx.x & 31;
+  const int mpo = p.mtiles / cm.world;
+  const int per_owner = mpo * p.ntiles;
+  constexpr int VPR = BN / 8;                 // 16-byte vectors per tile row
+  bool ok = true;
+  // ---- reduce the tiles this rank owns ----
+  for (int j = blockIdx.x; j < per_owner && ok; j += gridDim.x) {
+    const int nt = j / mpo, mt = (j % mpo) * cm.world + cm.rank;
+    const long long fi = ((long long)nt * p.mtiles + mt) * 4 + cw;
+    int got = 1;
+    if (lane < cm.world) got = flag_wait(cm.ready[lane] + fi, cm.epoch, abort_flag);
+    if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+    __syncwarp();
+#pragma unroll 2
+    for (int idx = lane; idx < 32 * VPR; idx += 32) {
+      const long long gm = (long long)mt * BM + cw * 32 + idx / VPR, gn = (long long)nt * BN + (idx % VPR) * 8;
+      if (gm >= p.m || gn >= p.n) continue;
+      const long long off = gm * p.n + gn;
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int r = 0; r < cm.world; ++r) {
+        const uint4 v = ld_sys_v4(cm.partial[r] + off);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (p.out_dt == NXB_BF16) {
+            acc[2 * e] += __uint_as_float(w[e] << 16);
+            acc[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+          } else {
+            float lo, hi;
+            asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}" : "=f"(lo), "=f"(hi) : "r"(w[e]));
+            acc[2 * e] += lo;
+            acc[2 * e + 1] += hi;
+          }
+        }
+      }
+      uint4 o;
+      uint32_t* ow = &o.x;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const unsigned short l = p.out_dt == NXB_BF16 ? f32_to_bf16_bits(acc[2 * e]) : f32_to_f16_bits(acc[2 * e]);
+        const unsigned short h = p.out_dt == NXB_BF16 ? f32_to_bf16_bits(acc[2 * e + 1]) : f32_to_f16_bits(acc[2 * e + 1]);
+        ow[e] = (uint32_t)l | ((uint32_t)h << 16);
+      }
+      *reinterpret_cast<uint4*>(cm.result[cm.rank] + off) = o;
+      *reinterpret_cast<uint4*>(cm.out + off) = o;
+    }
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_system();
+      st_release_sys(cm.reduced[cm.rank] + fi, cm.epoch);
+    }
+  }
+  // ---- fetch the tiles the other ranks own ----
+  for (int k = 1; k < cm.world && ok; ++k) {
+    const int owner = (cm.rank + k) % cm.world;
+    for (int j = blockIdx.x; j < per_owner && ok; j += gridDim.x) {
+      const int nt = j / mpo, mt = (j % mpo) * cm.world + owner;
+      const long long fi = ((long long)nt * p.mtiles + mt) * 4 + cw;
+      int got = 1;
+      if (lane == 0) got = flag_wait(cm.reduced[owner] + fi, cm.epoch, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      __syncwarp();
+#pragma unroll 4
+      for (int idx = lane; idx < 32 * VPR; idx += 32) {
+        const long long gm = (long long)mt * BM + cw * 32 + idx / VPR, gn = (long long)nt * BN + (idx % VPR) * 8;
+        if (gm >= p.m || gn >= p.n) continue;
+        const long long off = gm * p.n + gn;
+        *reinterpret_cast<uint4*>(cm.out + off) = ld_sys_v4(cm.result[owner] + off);
+      }
+    }
+  }
+}
+
+template <int KIND, int BN, class Epi, bool COMM = false>
+__device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUtensorMap& map_b, const CUtensorMap& map_c, const TcParams& p,
+                                             const CommArgs* cm = nullptr) {
   extern __shared__ unsigned char smem_raw[];
   constexpr int STAGES = stages_for(BN);
   constexpr int B_STAGE = BN * ROW_BYTES;
@@ -284,10 +431,8 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       uint32_t ph = 0;
       bool ok = true;
       for (long long t = blockIdx.x; t < ntiles_total && ok; t += gridDim.x) {
-        const int b = (int)(t / tiles_per_batch);
-        const int r = (int)(t % tiles_per_batch);
-        // consecutive CTAs share the same 256-wide column panel of B and walk down M
-        const int nt = r / p.mtiles, mt = r % p.mtiles;
+        int b, mt, nt;
+        tile_coords<COMM>(t, p, cm, b, mt, nt);
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(full0 + 8 * s, A_STAGE + B_STAGE);
@@ -340,6 +485,8 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
         if (++a == 2) { a = 0; aph ^= 1; }
       }
     }
+  } else if (COMM && warp >= 6) {
+    comm_role<BN>(p, *cm, abort_flag);
   } else {
     // epilogue warps 2..5; a warp may only read the TMEM lanes of its quarter (warp id mod 4)
     const int q = warp & 3;
@@ -348,9 +495,8 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
     uint32_t aph = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < ntiles_total && ok; t += gridDim.x) {
-      const int b = (int)(t / tiles_per_batch);
-      const int r = (int)(t % tiles_per_batch);
-      const int nt = r / p.mtiles, mt = r % p.mtiles;
+      int b, mt, nt;
+      tile_coords<COMM>(t, p, cm, b, mt, nt);
       // warp-uniform outcome: the tensor-memory loads below need the whole warp
       if (!mbar_wait_warp(tfull0 + 8 * a, aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -423,6 +569,11 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * a);
+      if (COMM && lane == 0) {
+        // this warp's 32 rows of the tile are in memory: publish them to every rank
+        __threadfence_system();
+        st_release_sys(cm->ready[cm->rank] + ((long long)nt * p.mtiles + mt) * 4 + q, cm->epoch);
+      }
       if (++a == 2) { a = 0; aph ^= 1; }
     }
     // the staging tiles must stay valid until the TMA unit has read them

@@ -14,6 +14,7 @@ _LIB = None
 LIB_NAME = "libnxb200.so"
 MAX_RANK = 8
 COMM_ID_BYTES = 128
+COMM_PEER_BLOB_BYTES = 80
 
 OK, ERR_INVALID, ERR_RUNTIME, ERR_DEALLOCATED, ERR_OOM, ERR_UNSUPPORTED, ERR_NO_DEVICE, ERR_TIMEOUT = \
     0, -1, -2, -3, -4, -5, -6, -7
@@ -80,6 +81,9 @@ def _declare(l):
         "nxb200_comm_id": [C.c_char_p],
         "nxb200_comm_init": [i32, i32, i32, C.c_char_p],
         "nxb200_comm_all_reduce_sum": [vp],
+        "nxb200_comm_peer_alloc": [i32, C.c_uint64, C.c_char_p],
+        "nxb200_comm_peer_open": [C.c_char_p, C.POINTER(C.c_int)],
+        "nxb200_comm_fused_launches": [C.POINTER(C.c_uint64)],
         "nxb200_comm_destroy": [],
         "nxb200_dot_bf16_static_scratch": [i32, vp, vp, vp, C.c_int64, C.c_int64, C.c_int64, vp],
     }

@@ -320,6 +320,15 @@ def partition(fun, mesh, input_shardings, local_templates, partition_index):
     return E.serialize(local_outs), ospec, out_specs
 
 
+def fused_all_reduce_launches():
+    """How many products this process ran as one kernel with their all-reduce."""
+    import ctypes as C
+    from . import nif
+    n = C.c_uint64(0)
+    nif.check(nif.lib().nxb200_comm_fused_launches(C.byref(n)))
+    return n.value
+
+
 def tensor_parallel_axes(blob_nodes):
     """Mesh axes a program all-reduces over (from its all_reduce nodes)."""
     return sorted({n.ints[0] for n in blob_nodes if n.op == "all_reduce"})
@@ -334,19 +343,25 @@ def shard_jit(fun, mesh, input_shardings, partition_index, device=None, **opts):
     from . import defn
     cache = {}
 
-    def run(*local_args):
+    def prepare(*local_args):
+        """Partition and build for these arguments without running (so that the ranks can meet
+        at a host barrier before the first run: kernels that wait on peers are bounded)."""
         flat, _ = defn._templates(local_args)
         key = tuple((t.type, t.shape) for t in flat)
         if key not in cache:
             blob, ospec, out_specs = partition(fun, mesh, input_shardings, list(local_args), partition_index)
             cache[key] = (defn.Program(blob), ospec, out_specs)
-        prog, ospec, _ = cache[key]
+        return flat, cache[key]
+
+    def run(*local_args):
+        flat, (prog, ospec, _) = prepare(*local_args)
         dev = B._device_of(device)
         args = [B.backend_transfer(a, dev) for a in flat]
         outs = prog.run(args, dev)
         return defn._unflatten(ospec, iter(outs))
 
     run.cache = cache
+    run.prepare = prepare
     return run
 
 
@@ -367,11 +382,32 @@ def torch_exchange():
     return exchange
 
 
-def init_tensor_parallel_group(mesh, axis, partition_index, device, exchange):
+def torch_gather():
+    """A ``gather`` for `init_tensor_parallel_group` on top of torch.distributed:
+    every rank contributes ``(group_key, rank_in_group, payload)`` and receives
+    its group's payloads in rank order."""
+    import torch.distributed as dist
+
+    def gather(key, rank_in_group, payload):
+        objs = [None] * dist.get_world_size()
+        dist.all_gather_object(objs, (key, rank_in_group, payload))
+        mine = sorted((r, p) for k, r, p in objs if k == key)
+        return [p for _, p in mine]
+    return gather
+
+
+def init_tensor_parallel_group(mesh, axis, partition_index, device, exchange, gather=None, peer_elems=0):
     """Create the NCCL communicator of the partitions that differ only in their
     coordinate along ``axis``.  ``exchange(group_key, payload_or_None)`` is the
     host's way to hand the 128-byte id from the group's first member to the
-    others (e.g. a torch.distributed broadcast or a key-value store)."""
+    others (e.g. a torch.distributed broadcast or a key-value store).
+
+    With ``gather(group_key, rank_in_group, payload) -> [payloads in rank order]``
+    and ``peer_elems`` > 0 the group also maps a region of every member's GPU
+    memory into every process (CUDA IPC), sized for matrices of ``peer_elems``
+    16-bit elements; a row-parallel product followed by the sum over ranks then
+    runs as one kernel over that memory instead of a product plus an NCCL call.
+    Returns True when that path is enabled."""
     import ctypes as C
     from . import nif
     lib = nif.lib()
@@ -380,7 +416,7 @@ def init_tensor_parallel_group(mesh, axis, partition_index, device, exchange):
     key = tuple(c for i, c in enumerate(coords) if i != axis)
     rank_in_group = coords[axis]
     if n == 1:
-        return
+        return False
     if rank_in_group == 0:
         buf = C.create_string_buffer(nif.COMM_ID_BYTES)
         nif.check(lib.nxb200_comm_id(buf))
@@ -388,3 +424,17 @@ def init_tensor_parallel_group(mesh, axis, partition_index, device, exchange):
     else:
         ident = exchange(key, None)
     nif.check(lib.nxb200_comm_init(device, rank_in_group, n, ident))
+    if gather is None or peer_elems <= 0 or n > 8:
+        return False
+    blob = C.create_string_buffer(nif.COMM_PEER_BLOB_BYTES)
+    nif.check(lib.nxb200_comm_peer_alloc(device, int(peer_elems), blob))
+    blobs = gather(key, rank_in_group, blob.raw)
+    if len(blobs) != n:
+        raise RuntimeError(f"peer memory set-up gathered {len(blobs)} blobs for a group of {n}")
+    enabled = C.c_int(0)
+    nif.check(lib.nxb200_comm_peer_open(b"".join(blobs), C.byref(enabled)))
+    # the members must agree, or some would wait in the fused kernel for the others' NCCL call
+    votes = gather(key, rank_in_group, bool(enabled.value))
+    if any(votes) and not all(votes):
+        raise RuntimeError("peer memory was mapped on some ranks of the group only")
+    return bool(enabled.value)

@@ -1,6 +1,7 @@
-"""Sharded decoder block on two GPUs (one process per GPU, NCCL all-reduce for the
-tensor-parallel linears).  Skipped on a single-GPU machine; the same logic runs on
-CPU over gloo in test_sharding_cpu.py."""
+"""Sharded decoder block on two GPUs, one process per GPU: batch data-parallel, and
+tensor-parallel linears with the sum over ranks done both ways - as an NCCL call after the
+product and fused into the product kernel over peer memory.  Skipped on a single-GPU
+machine; the partitioning logic also runs on CPU over gloo in test_sharding_cpu.py."""
 import os
 import socket
 import subprocess
@@ -53,14 +54,33 @@ assert close(out, full[rank:rank + 1]), "data-parallel shard differs from the or
 
 # tensor-parallel linears: one all-reduce after Wo and one after Wdown
 mesh = sharding.Mesh("tp", (2,))
-sharding.init_tensor_parallel_group(mesh, 0, rank, local, sharding.torch_exchange())
+peer = sharding.init_tensor_parallel_group(mesh, 0, rank, local, sharding.torch_exchange(),
+                                           gather=sharding.torch_gather(), peer_elems=2 * 128 * 512)
+assert peer, "two distinct GPUs of one machine must be able to map each other's memory"
 sh = [{}, {1: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {}, {}]
 f = sharding.shard_jit(block, mesh, sh, rank, device=local)
-out = nx.to_numpy(f(*[nx.tensor(shard(a, s, mesh), t) for (a, t), s in zip(inputs, sh)]))
+args = [nx.tensor(shard(a, s, mesh), t) for (a, t), s in zip(inputs, sh)]
+f.prepare(*args)
+dist.barrier()
+# the NCCL form first (product, then ncclAllReduce), then the product fused with the sum over peer memory
+os.environ["NXB200_NO_FUSED_ALLREDUCE"] = "1"
+out_nccl = nx.to_numpy(f(*args))
+assert sharding.fused_all_reduce_launches() == 0
+del os.environ["NXB200_NO_FUSED_ALLREDUCE"]
+dist.barrier()
+outs = [nx.to_numpy(f(*args)) for _ in range(3)]
+assert sharding.fused_all_reduce_launches() == 6, sharding.fused_all_reduce_launches()
 prog = list(f.cache.values())[0][0]
 assert prog.describe().count("all_reduce") == 2
-assert out.shape == (2, 128, 512)
-assert close(out, full), "tensor-parallel result differs from the oracle"
+for out in [out_nccl] + outs:
+    assert out.shape == (2, 128, 512)
+    assert close(out, full), "tensor-parallel result differs from the oracle"
+# repeated fused runs are bit-identical, and both ranks hold the same bits
+assert all(np.array_equal(outs[0], o) for o in outs[1:])
+t = torch.from_numpy(outs[0].astype(np.float32)).cuda()
+peer_t = [torch.empty_like(t) for _ in range(2)]
+dist.all_gather(peer_t, t)
+assert torch.equal(peer_t[0], peer_t[1]), "ranks disagree on the reduced values"
 dist.barrier()
 print("rank", rank, "ok")
 dist.destroy_process_group()
