@@ -60,6 +60,7 @@ struct PeerView {
 // Fills `v` and advances the epoch when peer memory is set up, a matrix of m x n 16-bit elements
 // with mtiles x ntiles output tiles fits and the ranks can share the row tiles evenly; false
 // otherwise (the caller uses NCCL instead).
+int comm_world();
 bool comm_peer_view(int64_t m, int64_t n, int64_t mtiles, int64_t ntiles, PeerView* v);
 // Product of a row-parallel linear fused with the sum over ranks (one kernel over peer memory).
 // Returns false, launching nothing, when the shape or the communicator does not allow it.

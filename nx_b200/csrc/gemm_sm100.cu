@@ -234,7 +234,15 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
 }
 
 bool launch_tc_gemm_allreduce(const GemmArgs& g, void* out, int* status_word, int sm_count, cudaStream_t stream) {
-  if (getenv("NXB200_NO_FUSED_ALLREDUCE")) return false;
+  // NXB200_FUSED_ALLREDUCE = never | always | auto (default).  The fused kernel hides the exchange
+  // behind the product; NCCL (with in-switch reduction on NVSwitch) moves the bytes faster.  Measured
+  // on two B200: fused wins once the product is longer than the exchange, i.e. for a contracted
+  // extent per rank of a few thousand; below that, and for wider groups whose exchange dwarfs the
+  // product, NCCL after the product is faster.
+  const char* mode = getenv("NXB200_FUSED_ALLREDUCE");
+  if (getenv("NXB200_NO_FUSED_ALLREDUCE") || (mode && !strcmp(mode, "never"))) return false;
+  const bool always = mode && !strcmp(mode, "always");
+  if (!always && g.k * comm_world() < 8192LL * (comm_world() - 1)) return false;
   if (!tc_gemm_supported(g) || g.batch != 1 || g.scale || g.bias || g.dc != g.da || (g.da != NXB_BF16 && g.da != NXB_F16) || g.n % 8 != 0) return false;
   const int bn = tc_pick_bn(g.m, g.n, g.batch, sm_count);
   TcParams p = make_params(g, bn, status_word);

@@ -323,40 +323,63 @@ __device__ __forceinline__ void comm_role(const TcParams& p, const CommArgs& cm,
     if (lane < cm.world) got = flag_wait(cm.ready[lane] + fi, cm.epoch, abort_flag);
     if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
     __syncwarp();
-#pragma unroll 2
-    for (int idx = lane; idx < 32 * VPR; idx += 32) {
-      const long long gm = (long long)mt * BM + cw * 32 + idx / VPR, gn = (long long)nt * BN + (idx % VPR) * 8;
-      if (gm >= p.m || gn >= p.n) continue;
-      const long long off = gm * p.n + gn;
-      float acc[8];
+    // A warp pass covers 32 vectors of 16 bytes; eight passes are loaded together per rank so that
+    // enough requests are in flight to cover the NVLink round trip.
+    constexpr int RB = 8;
+    for (int pb = 0; pb < VPR; pb += RB) {
+      long long off[RB];
+      float acc[RB][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-      for (int r = 0; r < cm.world; ++r) {
-        const uint4 v = ld_sys_v4(cm.partial[r] + off);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      for (int u = 0; u < RB; ++u) {
+        const int idx = (pb + u) * 32 + lane;
+        const long long gm = (long long)mt * BM + cw * 32 + idx / VPR, gn = (long long)nt * BN + (idx % VPR) * 8;
+        off[u] = (gm < p.m && gn < p.n) ? gm * p.n + gn : -1;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          if (p.out_dt == NXB_BF16) {
-            acc[2 * e] += __uint_as_float(w[e] << 16);
-            acc[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
-          } else {
-            float lo, hi;
-            asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}" : "=f"(lo), "=f"(hi) : "r"(w[e]));
-            acc[2 * e] += lo;
-            acc[2 * e + 1] += hi;
+        for (int e = 0; e < 8; ++e) acc[u][e] = 0.f;
+      }
+      // two ranks' tiles are requested together: 16 loads in flight per lane
+      for (int r = 0; r < cm.world; r += 2) {
+        uint4 v[2][RB];
+        const bool two = r + 1 < cm.world;
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+          v[0][u] = off[u] >= 0 ? ld_sys_v4(cm.partial[r] + off[u]) : make_uint4(0, 0, 0, 0);
+          v[1][u] = (two && off[u] >= 0) ? ld_sys_v4(cm.partial[r + 1] + off[u]) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+          for (int u = 0; u < RB; ++u) {
+            const uint32_t w[4] = {v[h][u].x, v[h][u].y, v[h][u].z, v[h][u].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (p.out_dt == NXB_BF16) {
+                acc[u][2 * e] += __uint_as_float(w[e] << 16);
+                acc[u][2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+              } else {
+                float lo, hi;
+                asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %2;\n\tcvt.f32.f16 %0, l;\n\tcvt.f32.f16 %1, h;\n\t}" : "=f"(lo), "=f"(hi) : "r"(w[e]));
+                acc[u][2 * e] += lo;
+                acc[u][2 * e + 1] += hi;
+              }
+            }
           }
         }
       }
-      uint4 o;
-      uint32_t* ow = &o.x;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const unsigned short l = p.out_dt == NXB_BF16 ? f32_to_bf16_bits(acc[2 * e]) : f32_to_f16_bits(acc[2 * e]);
-        const unsigned short h = p.out_dt == NXB_BF16 ? f32_to_bf16_bits(acc[2 * e + 1]) : f32_to_f16_bits(acc[2 * e + 1]);
-        ow[e] = (uint32_t)l | ((uint32_t)h << 16);
+      for (int u = 0; u < RB; ++u) {
+        if (off[u] < 0) continue;
+        uint4 o;
+        uint32_t* ow = &o.x;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const unsigned short l = p.out_dt == NXB_BF16 ? f32_to_bf16_bits(acc[u][2 * e]) : f32_to_f16_bits(acc[u][2 * e]);
+          const unsigned short h = p.out_dt == NXB_BF16 ? f32_to_bf16_bits(acc[u][2 * e + 1]) : f32_to_f16_bits(acc[u][2 * e + 1]);
+          ow[e] = (uint32_t)l | ((uint32_t)h << 16);
+        }
+        *reinterpret_cast<uint4*>(cm.result[cm.rank] + off[u]) = o;
+        *reinterpret_cast<uint4*>(cm.out + off[u]) = o;
       }
-      *reinterpret_cast<uint4*>(cm.result[cm.rank] + off) = o;
-      *reinterpret_cast<uint4*>(cm.out + off) = o;
     }
     __syncwarp();
     if (lane == 0) {
@@ -374,12 +397,20 @@ __device__ __forceinline__ void comm_role(const TcParams& p, const CommArgs& cm,
       if (lane == 0) got = flag_wait(cm.reduced[owner] + fi, cm.epoch, abort_flag);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       __syncwarp();
-#pragma unroll 4
-      for (int idx = lane; idx < 32 * VPR; idx += 32) {
-        const long long gm = (long long)mt * BM + cw * 32 + idx / VPR, gn = (long long)nt * BN + (idx % VPR) * 8;
-        if (gm >= p.m || gn >= p.n) continue;
-        const long long off = gm * p.n + gn;
-        *reinterpret_cast<uint4*>(cm.out + off) = ld_sys_v4(cm.result[owner] + off);
+      constexpr int CB = VPR < 16 ? VPR : 16;
+      for (int pb = 0; pb < VPR; pb += CB) {
+        long long off[CB];
+        uint4 v[CB];
+#pragma unroll
+        for (int u = 0; u < CB; ++u) {
+          const int idx = (pb + u) * 32 + lane;
+          const long long gm = (long long)mt * BM + cw * 32 + idx / VPR, gn = (long long)nt * BN + (idx % VPR) * 8;
+          off[u] = (gm < p.m && gn < p.n) ? gm * p.n + gn : -1;
+          if (off[u] >= 0) v[u] = ld_sys_v4(cm.result[owner] + off[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < CB; ++u)
+          if (off[u] >= 0) *reinterpret_cast<uint4*>(cm.out + off[u]) = v[u];
       }
     }
   }
