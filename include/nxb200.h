@@ -112,8 +112,11 @@ int nxb200_buffer_release(nxb200_buffer *buf);
  * flts=[v]; iota [axis|-1]; sum/product/reduce_max/reduce_min/all/any
  * [keep_axes, n, axes…]; argmax/argmin [tie_break_high, axis|-1, keep_axis];
  * dot [nc1,c1…, nb1,b1…, nc2,c2…, nb2,b2…]; squeeze [n, axes…]; broadcast
- * [n, axes…]; transpose [perm…]; slice [starts…, lengths…, strides…];
- * concatenate [axis]; everything else none.
+ * [n, axes…]; transpose [perm…]; slice [starts…, lengths…, strides…] (with
+ * dynamic starts the node has 1 + rank arguments: the tensor, then one scalar
+ * integer start per axis, and the starts attribute is ignored); gather [axes…]
+ * (arguments: tensor, indices); put_slice none (arguments: tensor, slice, one
+ * scalar integer start per axis); concatenate [axis]; everything else none.
  *
  * Building needs no GPU (kernels are generated and compiled for sm_100a on
  * the host); the first run on a device loads them. */

@@ -51,7 +51,7 @@ const std::set<std::string> kView = {"reshape", "squeeze", "broadcast", "transpo
 bool is_reduce(const Node& n) { return kReduce.count(n.op) || kArgReduce.count(n.op); }
 bool is_inline(const Node& n) {   // can be generated inside a consumer's kernel
   return kUnaryMath.count(n.op) || kUnaryOther.count(n.op) || kBinary.count(n.op) || kView.count(n.op) ||
-         n.op == "select" || n.op == "clip" || n.op == "constant" || n.op == "iota";
+         n.op == "select" || n.op == "clip" || n.op == "constant" || n.op == "iota" || n.op == "gather" || n.op == "put_slice";
 }
 
 const char* storage_type(DType t) {
@@ -554,6 +554,72 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
     std::vector<Aff> ai(idx.size(), aff_const(nv_, 0));
     for (size_t j = 0; j < idx.size(); ++j) ai[nd.ints[j]] = idx[j];
     return value(nd.args[0], ai);
+  }
+  if (op == "slice" && nd.args.size() > 1) {
+    // dynamic starts (Nx.slice with tensor indices): a start is clamped so that the slice fits
+    const Node& a = g_.nodes[nd.args[0]];
+    size_t r = idx.size();
+    std::vector<Aff> ai;
+    for (size_t j = 0; j < r; ++j) {
+      const int64_t span = nd.ints[r + j], sd = nd.ints[2 * r + j];     // window length before striding, stride
+      Val sv = value(nd.args[1 + j], {});
+      Val s = def(true, NXB_S64, "nx_clamp_index(" + sv.v + ", (long long)" + std::to_string(a.shape[j] - span + 1) + ")");
+      Aff o;
+      o.opaque = true;
+      o.k.assign(nv_, 0);
+      o.expr = "((" + idx_t() + ")" + s.v + " + (" + idx_t() + ")" + std::to_string(sd) + " * " + affstr(idx[j], false) + ")";
+      ai.push_back(o);
+    }
+    return value(nd.args[0], ai);
+  }
+  if (op == "gather") {
+    // out dims = batch dims of `indices` ++ dims of `tensor` that are not indexed; an index is
+    // clamped into its axis (XLA's gather semantics, exla/lib/exla/defn.ex gather lowering)
+    const Node& T = g_.nodes[nd.args[0]];
+    const Node& I = g_.nodes[nd.args[1]];
+    const size_t nb = I.shape.size() - 1;
+    std::vector<Aff> tidx(T.shape.size(), aff_const(nv_, 0));
+    std::set<int64_t> indexed(nd.ints.begin(), nd.ints.end());
+    size_t q = nb;
+    for (size_t j = 0; j < T.shape.size(); ++j)
+      if (!indexed.count((int64_t)j)) tidx[j] = idx[q++];
+    for (size_t i = 0; i < nd.ints.size(); ++i) {
+      std::vector<Aff> ii(idx.begin(), idx.begin() + nb);
+      ii.push_back(aff_const(nv_, (int64_t)i));
+      Val iv = value(nd.args[1], ii);
+      Aff o;
+      o.opaque = true;
+      o.k.assign(nv_, 0);
+      o.expr = "(" + idx_t() + ")nx_clamp_index(" + iv.v + ", (long long)" + std::to_string(T.shape[nd.ints[i]]) + ")";
+      tidx[nd.ints[i]] = o;
+    }
+    return value(nd.args[0], tidx);
+  }
+  if (op == "put_slice") {
+    // args: tensor, slice, one scalar start per axis (clamped so that the slice fits)
+    const Node& T = g_.nodes[nd.args[0]];
+    const Node& S = g_.nodes[nd.args[1]];
+    const size_t r = idx.size();
+    std::vector<Aff> sidx;
+    std::string inside;
+    bool elem = false;
+    for (size_t j = 0; j < r; ++j) {
+      if (S.shape[j] == T.shape[j]) { sidx.push_back(idx[j]); continue; }     // the slice spans the axis: start is 0
+      Val sv = value(nd.args[2 + j], {});
+      Val s = def(true, NXB_S64, "nx_clamp_index(" + sv.v + ", (long long)" + std::to_string(T.shape[j] - S.shape[j] + 1) + ")");
+      const std::string c = "((long long)(" + affstr(idx[j], false) + ") - " + s.v + ")";
+      inside += (inside.empty() ? "" : " && ") + std::string("(") + c + " >= 0 && " + c + " < " + std::to_string(S.shape[j]) + ")";
+      Aff o;
+      o.opaque = true;
+      o.k.assign(nv_, 0);
+      o.expr = "(" + idx_t() + ")nx_clamp_index(" + c + ", (long long)" + std::to_string(S.shape[j]) + ")";
+      sidx.push_back(o);
+      elem = true;
+    }
+    Val x = value(nd.args[1], sidx);
+    if (inside.empty()) return def(x.elem, t, cvt(x.v, S.dt, t));           // the slice replaces everything
+    Val y = value(nd.args[0], idx);
+    return def(true, t, "(" + inside + ") ? " + cvt(x.v, S.dt, t) + " : " + cvt(y.v, T.dt, t));
   }
   if (op == "slice") {
     size_t r = idx.size();
@@ -1365,7 +1431,16 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       bool ok = is_inline(nd) || is_reduce(nd) || nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" ||
                 nd.op == "all_reduce" || nd.op == "attention";
       if (!ok) fail(NXB_ERR_UNSUPPORTED, "Nx op :" + nd.op + " is not implemented by the B200 compiler");
-      if (nd.op == "slice" && nd.args.size() != 1) fail(NXB_ERR_UNSUPPORTED, "slice with dynamic start indices is not implemented");
+      if (nd.op == "slice" && nd.args.size() != 1 && nd.args.size() != 1 + nd.shape.size())
+        fail(NXB_ERR_INVALID_ARGUMENT, "slice with dynamic start indices takes one start per axis");
+      if (nd.op == "gather") {
+        if (nd.args.size() != 2 || nd.ints.empty()) fail(NXB_ERR_INVALID_ARGUMENT, "gather takes (tensor, indices) and its indexed axes");
+        const Node& ix = g.nodes[nd.args[1]];
+        if (dtype_is_float(ix.dt) || ix.shape.empty() || ix.shape.back() != (int64_t)nd.ints.size())
+          fail(NXB_ERR_INVALID_ARGUMENT, "gather indices must be integers with one column per indexed axis");
+      }
+      if (nd.op == "put_slice" && nd.args.size() != 2 + nd.shape.size())
+        fail(NXB_ERR_INVALID_ARGUMENT, "put_slice takes (tensor, slice, one start per axis)");
     }
   }
 
@@ -1399,6 +1474,11 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         const std::string& aop = g.nodes[nd.args[k]].op;
         if (aop != "parameter" && aop != "tensor") P.mat[nd.args[k]] = 1;
       }
+    }
+    if (nd.op == "gather") {
+      // rows are fetched by computed addresses: the table has to be a buffer
+      const std::string& aop = g.nodes[nd.args[0]].op;
+      if (aop != "parameter" && aop != "tensor") P.mat[nd.args[0]] = 1;
     }
     if (nd.op == "all_reduce") {
       P.mat[n] = 1;

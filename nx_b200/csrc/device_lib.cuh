@@ -211,6 +211,14 @@ NXB_DEV bool stg_wait(void* bar, uint32_t parity) {
   }
 }
 
+// An index or a slice start clamped into [0, n - 1] (gather, dynamic slice, put_slice); works for
+// every integer type an index tensor may have, unsigned 64-bit included.
+template <typename T> NXB_DEV long long nx_clamp_index(T v, long long n) {
+  if (v < (T)0) return 0;
+  if ((unsigned long long)v > (unsigned long long)(n - 1)) return n - 1;
+  return (long long)v;
+}
+
 // ---- reductions ------------------------------------------------------------------------
 // Combine operators.  Each has ::apply(a, b) on the register type.
 struct OpSum { template <typename T> static NXB_DEV T apply(T a, T b) { return a + b; } };

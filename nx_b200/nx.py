@@ -467,24 +467,91 @@ def transpose(x, axes=None):
     return _dispatch(lambda a: E.node(out, "transpose", [a], ints=axes), [x])
 
 
+def _index_scalar(v):
+    """A start index given as a tensor: must be an integer scalar."""
+    v = _as_operand(v)
+    if v.shape != () or not T.is_integer(v.type):
+        raise ValueError(f"index must be an integer scalar tensor, got {v.type} {v.shape}")
+    return v
+
+
 def slice(x, starts, lengths, strides=None):
-    """``Nx.slice/4`` with static start indices (nx/lib/nx.ex slice; dynamic
-    starts are outside the five configurations)."""
+    """``Nx.slice/4`` (nx/lib/nx.ex slice).  Start indices may be integers or
+    scalar integer tensors; either way a start is clamped so that the slice
+    fits (``Nx.Shape.slice`` for static starts, the backend for dynamic ones)."""
     x = _as_operand(x)
     strides = [1] * x.rank if strides is None else ([strides] * x.rank if isinstance(strides, int) else list(strides))
     starts, lengths = list(starts), list(lengths)
     if not (len(starts) == len(lengths) == len(strides) == x.rank):
         raise ValueError("slice arguments must have one entry per axis")
     shape = []
-    for d, s, l, st in zip(x.shape, starts, lengths, strides):
+    for d, l, st in zip(x.shape, lengths, strides):
         if l < 1 or l > d or st < 1:
             raise ValueError(f"length at axis must be in 1..{d} and strides positive, got length {l} stride {st}")
         shape.append(-(-l // st))
+    if _b.any(isinstance(s, Tensor) for s in starts):
+        dyn = [_index_scalar(s if isinstance(s, Tensor) else tensor(s, "s64")) for s in starts]
+        out = _out(x.type, shape)
+        return _dispatch(lambda a, *ss: E.node(out, "slice", [a, *ss], ints=[0] * x.rank + lengths + strides), [x] + dyn)
     starts = [_b.min(_b.max(s, 0), d - l) for s, d, l in zip(starts, x.shape, lengths)]
     if tuple(shape) == x.shape:
         return x
     out = _out(x.type, shape)
     return _dispatch(lambda a: E.node(out, "slice", [a], ints=starts + lengths + strides), [x])
+
+
+def put_slice(x, start_indices, piece):
+    """``Nx.put_slice/3`` (nx/lib/nx.ex put_slice; backend.ex put_slice): `x` with
+    `piece` written at `start_indices` (integers or scalar integer tensors), each start
+    clamped so that the piece fits.  The result type merges both types."""
+    x, piece = _as_operand(x), _as_operand(piece)
+    starts = list(start_indices)
+    if len(starts) != x.rank or piece.rank != x.rank:
+        raise ValueError("put_slice needs one start index per axis and a slice of the same rank")
+    for d, l in zip(x.shape, piece.shape):
+        if l > d:
+            raise ValueError(f"slice shape {piece.shape} must be less than or equal to tensor shape {x.shape}")
+    dyn = [_index_scalar(s if isinstance(s, Tensor) else tensor(s, "s64")) for s in starts]
+    out = _out(T.merge(x.type, piece.type), x.shape)
+    return _dispatch(lambda a, p, *ss: E.node(out, "put_slice", [a, p, *ss]), [x, piece] + dyn)
+
+
+def gather(x, indices, axes=None):
+    """``Nx.gather/3`` (nx/lib/nx.ex:15160-15203, shape rule nx/lib/nx/shape.ex:1643-1661):
+    the last axis of `indices` holds one coordinate per indexed axis (default: the
+    leading ones); the result has the batch shape of `indices` followed by the axes of
+    `x` that are not indexed.  Out-of-range coordinates are clamped, as the compiled
+    (XLA) path does."""
+    x, indices = _as_operand(x), _as_operand(indices)
+    if indices.rank < 1:
+        raise ValueError("expected indices rank to be at least 1, got: 0")
+    if not T.is_integer(indices.type):
+        raise ValueError(f"indices must be an integer tensor, got {indices.type}")
+    depth = indices.shape[-1]
+    if depth > x.rank:
+        raise ValueError(f"expected the last indices dimension size ({depth}) to be less than or equal to the tensor rank ({x.rank})")
+    axes = list(range(depth)) if axes is None else _norm_axes(x.rank, axes)
+    if len(axes) != depth or sorted(set(axes)) != sorted(axes):
+        raise ValueError(f"expected {depth} distinct axes, got {axes}")
+    if axes != sorted(axes):
+        raise ValueError(":axes must be an ordered list")
+    shape = tuple(indices.shape[:-1]) + tuple(d for i, d in enumerate(x.shape) if i not in axes)
+    out = _out(x.type, shape)
+    return _dispatch(lambda a, i: E.node(out, "gather", [a, i], ints=list(axes)), [x, indices])
+
+
+def take(x, indices, axis=0):
+    """``Nx.take/3`` (nx/lib/nx.ex:14731-14816): gather along one axis; the axes of
+    `indices` replace `axis` in the result."""
+    x, indices = _as_operand(x), _as_operand(indices)
+    if not T.is_integer(indices.type):
+        raise ValueError(f"indices must be an integer tensor, got {indices.type}")
+    a = _norm_axis(x.rank, axis)
+    g = gather(x, reshape(indices, indices.shape + (1,)), axes=[a])       # indices axes ++ remaining axes of x
+    k = indices.rank
+    lead = list(range(k, k + a))
+    perm = lead + list(range(k)) + list(range(k + a, g.rank))
+    return transpose(g, perm)
 
 
 def slice_along_axis(x, start, length, axis=0, strides=1):

@@ -520,7 +520,23 @@ def evaluate(nodes, outs, params, mode="xla_like", all_reduce=None):
         elif op == "slice":
             r = arg[0].ndim
             st, ln, sd = nd.ints[:r], nd.ints[r:2 * r], nd.ints[2 * r:3 * r]
+            if len(arg) > 1:      # dynamic starts, clamped so that the window fits
+                st = [min(max(int(s), 0), d - l) for s, d, l in zip(arg[1:], arg[0].shape, ln)]
             v = arg[0][tuple(slice(s, s + l, d) for s, l, d in zip(st, ln, sd))]
+        elif op == "gather":
+            # nx/lib/nx/binary_backend.ex:1903-1940 (indexed axes first, then a contiguous
+            # copy per index row); coordinates clamped as XLA's gather does
+            axes = list(nd.ints)
+            rest = [j for j in range(arg[0].ndim) if j not in axes]
+            tt = np.transpose(arg[0], axes + rest)
+            idx = arg[1].astype(np.int64) if arg[1].dtype != np.uint64 else np.minimum(arg[1], np.uint64(2 ** 62)).astype(np.int64)
+            coords = tuple(np.clip(idx[..., i], 0, tt.shape[i] - 1) for i in range(len(axes)))
+            v = tt[coords]
+        elif op == "put_slice":
+            base, piece = convert(arg[0], at[0], t, mode), convert(arg[1], at[1], t, mode)
+            st = [min(max(int(s), 0), d - l) for s, d, l in zip(arg[2:], base.shape, piece.shape)]
+            v = np.array(base, copy=True)
+            v[tuple(slice(s, s + l) for s, l in zip(st, piece.shape))] = piece
         elif op == "concatenate":
             v = np.concatenate([convert(a, ta, t, mode) for a, ta in zip(arg, at)], axis=nd.ints[0])
         else:

@@ -172,3 +172,49 @@ case("logsumexp doc axes x,z keep", "nx/lib/nx.ex:18368-18379", lambda t: nx.log
 case("logsumexp scaling factor", "nx/lib/nx.ex:18333-18339",
      lambda t, a: nx.logsumexp(t, exp_scaling_factor=a),
      [([1, 2, 3, 4, 5, 6], "s32"), ([-1, -1, -1, 1, 1, 1], "s32")], [(6.356537, "f32")], exact=False)
+
+# ---- gather / take: exla/test/exla/defn/expr_test.exs:3398-3496, nx/lib/nx.ex:14554-14640,15036-15111 ----
+T2 = [[1, 2], [3, 4]]
+T222 = [[[1, 2], [11, 12]], [[101, 102], [111, 112]]]
+case("gather 1d result", "exla/test/exla/defn/expr_test.exs:3464-3467", lambda t, i: nx.gather(t, i),
+     [(T2, "s32"), ([[1, 1], [0, 1], [1, 0]], "s32")], [([4, 2, 3], "s32")])
+case("gather rank 3", "exla/test/exla/defn/expr_test.exs:3469-3475", lambda t, i: nx.gather(t, i),
+     [(T222, "s32"), ([[0, 0, 0], [0, 1, 1], [1, 1, 1]], "s32")], [([1, 12, 112], "s32")])
+case("gather clamps out-of-range indices", "exla/test/exla/defn/expr_test.exs:3477-3480", lambda t, i: nx.gather(t, i),
+     [(T2, "s32"), ([[-1, -1], [10, 11], [-1, 10]], "s32")], [([1, 4, 2], "s32")], modes=("xla_like",))
+case("gather 2d result", "exla/test/exla/defn/expr_test.exs:3483-3488", lambda t, i: nx.gather(t, i),
+     [(T2, "s32"), ([[[1, 1], [0, 0]], [[1, 0], [0, 1]]], "s32")], [([[4, 1], [3, 2]], "s32")])
+case("gather subsets", "nx/lib/nx.ex:15061-15069", lambda t, i: nx.gather(t, i),
+     [([[1, 2, 3], [3, 4, 5]], "s32"), ([[1], [0]], "s32")], [([[3, 4, 5], [1, 2, 3]], "s32")])
+case("gather axes: [1]", "nx/lib/nx.ex:15075-15085", lambda t, i: nx.gather(t, i, axes=[1]),
+     [([[1, 2, 3], [4, 5, 6]], "s32"), ([[1], [0], [2], [1]], "s32")], [([[2, 5], [1, 4], [3, 6], [2, 5]], "s32")])
+case("gather axes: [2] of iota {2,1,3}", "nx/lib/nx.ex:15091-15111", lambda t, i: nx.gather(t, i, axes=[2]),
+     [([[[0, 1, 2]], [[3, 4, 5]]], "s32"), ([[[1], [0], [2]]], "s32")], [([[[[1], [4]], [[0], [3]], [[2], [5]]]], "s32")])
+case("take axis 0", "exla/test/exla/defn/expr_test.exs:3403-3406", lambda t, i: nx.take(t, i),
+     [(T2, "s32"), ([1, 0, 1], "s32")], [([[3, 4], [1, 2], [3, 4]], "s32")])
+case("take axis 1", "exla/test/exla/defn/expr_test.exs:3408-3411", lambda t, i: nx.take(t, i, axis=1),
+     [(T2, "s32"), ([1, 0, 1], "s32")], [([[2, 1, 2], [4, 3, 4]], "s32")])
+case("take rank 3 axis 1", "nx/lib/nx.ex:14585-14601", lambda t, i: nx.take(t, i, axis=1),
+     [(T222, "s32"), ([1, 0, 1], "s32")], [([[[11, 12], [1, 2], [11, 12]], [[111, 112], [101, 102], [111, 112]]], "s32")])
+case("take 2d indices", "exla/test/exla/defn/expr_test.exs:3414-3456", lambda t, i: nx.take(t, i, axis=1),
+     [(T222, "s32"), ([[0, 0, 0], [1, 1, 1], [0, 0, 0]], "s32")],
+     [([[[[1, 2]] * 3, [[11, 12]] * 3, [[1, 2]] * 3], [[[101, 102]] * 3, [[111, 112]] * 3, [[101, 102]] * 3]], "s32")])
+
+# ---- put_slice and slice with dynamic starts: nx/lib/nx.ex:14421-14464, 14080-14103 ---------------------
+case("put_slice 1d", "nx/lib/nx.ex:14424-14429", lambda t, s: nx.put_slice(t, [2], s),
+     [([0, 1, 2, 3, 4], "s32"), ([5, 6], "s32")], [([0, 1, 5, 6, 4], "s32")])
+case("put_slice 2d", "nx/lib/nx.ex:14431-14439", lambda t, s: nx.put_slice(t, [0, 1], s),
+     [([[1, 2, 3], [4, 5, 6]], "s32"), ([[7, 8], [9, 10]], "s32")], [([[1, 7, 8], [4, 9, 10]], "s32")])
+case("put_slice dynamic starts, merged type", "nx/lib/nx.ex:14443-14451",
+     lambda t, a, b, s: nx.put_slice(t, [a, b], s),
+     [([[1, 2, 3], [4, 5, 6]], "s32"), (0, "s32"), (1, "s32"), ([[10.0, 11.0]], "f32")],
+     [([[1.0, 10.0, 11.0], [4.0, 5.0, 6.0]], "f32")])
+case("put_slice clips the start", "nx/lib/nx.ex:14456-14464", lambda t, a, s: nx.put_slice(t, [a, 1], s),
+     [([[1, 2, 3], [4, 5, 6]], "s32"), (1, "s32"), ([[7, 8], [9, 10]], "s32")], [([[1, 7, 8], [4, 9, 10]], "s32")])
+case("slice dynamic starts with strides", "nx/lib/nx.ex:14080-14103",
+     lambda t, a, b: nx.slice(t, [a, b], [6, 7], strides=[5, 3]),
+     [([[0.0] * 7] * 2 + [[1.0] * 7] * 4, "f32"), (0, "s32"), (0, "s32")], [([[0.0] * 3, [1.0] * 3], "f32")])
+case("slice dynamic starts", "nx/lib/nx.ex:14077-14084", lambda t, a, b: nx.slice(t, [a, b], [1, 1]),
+     [([[1, 2, 3], [4, 5, 6]], "s32"), (1, "s32"), (2, "s32")], [([[6]], "s32")])
+case("slice dynamic start is clipped", "nx/lib/nx.ex:14105-14125", lambda t, a: nx.slice(t, [a, 0], [2, 2]),
+     [([[1, 2], [3, 4], [5, 6]], "s32"), (2, "s32")], [([[3, 4], [5, 6]], "s32")])

@@ -290,3 +290,57 @@ def test_dot_layouts():
     ]:
         for g, r, t in run_both(fun, arrs, ["f32", "f32"]):
             assert_close(g, r, what="dot layout", **tol)
+
+
+# ---- indexed reads and writes: gather / take / put_slice / slice with tensor starts ---------------
+def test_embedding_lookup_feeds_a_fused_row_kernel():
+    """Nx.take on a bf16 table by token ids (an embedding lookup), alone and with an RMS norm
+    computed from the looked-up rows in the same kernel."""
+    rng = np.random.default_rng(11)
+    table = rng.normal(0, 1, (1000, 256)).astype(np.float32)
+    ids = rng.integers(0, 1000, (4, 37))
+    ids[0, :3] = [-5, 1000, 999]                      # out of range: clamped like XLA's gather
+
+    def rms(t):
+        return t * nx.rsqrt(nx.mean(t * t, axes=[-1], keep_axes=True) + 1e-5)
+
+    res = run_both(lambda w, i: (nx.take(w, i), rms(nx.take(w, i))), [table, ids], ["bf16", "s64"])
+    assert res[0][0].shape == (4, 37, 256)
+    assert np.array_equal(res[0][0], res[0][1]), "a lookup copies values"
+    check(res[1:], "rms norm of embeddings")
+    for it in ("s32", "u8", "u32"):
+        small = rng.integers(0, 200, (9,))
+        r = run_both(lambda w, i: nx.take(w, i, axis=1), [table[:50], small], ["f32", it])
+        assert np.array_equal(r[0][0], r[0][1]), it
+
+
+def test_gather_general_axes():
+    rng = np.random.default_rng(12)
+    t = rng.normal(0, 1, (5, 6, 7, 8)).astype(np.float32)
+    idx = np.stack([rng.integers(-1, 7, (3, 4)), rng.integers(0, 9, (3, 4))], axis=-1)      # axes 1 and 3
+    for g, r, _ in run_both(lambda a, i: nx.gather(a, i, axes=[1, 3]), [t, idx], ["f32", "s32"]):
+        assert g.shape == (3, 4, 5, 7) and np.array_equal(g, r)
+    full = np.stack([rng.integers(0, d, (11,)) for d in t.shape], axis=-1)
+    for g, r, _ in run_both(lambda a, i: nx.gather(a * 2.0, i), [t, full], ["f32", "s64"]):          # table computed in the program
+        assert g.shape == (11,) and np.array_equal(g, r)
+
+
+@pytest.mark.parametrize("pos", [0, 5, 60, 63, 200])
+def test_kv_cache_update_and_window_read(pos):
+    """put_slice of one position into a {B,H,S,D} cache at a position held in a tensor, then a
+    dynamic slice reading a window back; positions beyond the end are clamped."""
+    rng = np.random.default_rng(13)
+    cache = rng.normal(0, 1, (2, 3, 64, 16)).astype(np.float32)
+    new = rng.normal(0, 1, (2, 3, 1, 16)).astype(np.float32)
+
+    def f(c, n, p):
+        c2 = nx.put_slice(c, [0, 0, p, 0], n)
+        return c2, nx.slice(c2, [0, 0, p, 0], [2, 3, 4, 16]) * 2.0
+
+    res = run_both(f, [cache, new, np.array(pos)], ["bf16", "bf16", "s32"])
+    assert np.array_equal(res[0][0], res[0][1])
+    p = min(pos, 63)
+    assert np.array_equal(res[0][0][:, :, p], res[0][1][:, :, p])
+    check(res[1:], "window")
+    mixed = run_both(lambda c, n, p: nx.put_slice(c, [0, 0, p, 0], n), [cache, new, np.array(pos)], ["f32", "bf16", "s64"])
+    assert mixed[0][2] == ("f", 32) and np.array_equal(mixed[0][0], mixed[0][1])
