@@ -121,11 +121,111 @@ __global__ void __launch_bounds__(256) simt_gemm_kernel(GemmArgs g) {
     }
 }
 
+// f32 x f32 -> f32: typed loads, the next k chunk fetched into registers while the current one
+// is multiplied, one barrier per chunk (two shared-memory buffers).  TM x TN outputs per CTA of
+// 256 threads, RM x RN per thread; the small tile spreads small products (the MLP configuration)
+// over more SMs.
+template <int TM, int TN, int RM, int RN, int TK>
+__global__ void __launch_bounds__(256) sgemm_kernel(GemmArgs g) {
+  constexpr int LA = TM * TK / 256, LB = TN * TK / 256;      // elements each thread stages per chunk
+  static_assert((TM / RM) * (TN / RN) == 256, "256 threads per tile");
+  __shared__ float As[2][TK][TM + 4];
+  __shared__ float Bs[2][TK][TN + 4];
+  const long long b = blockIdx.z;
+  const long long m0 = (long long)blockIdx.y * TM, n0 = (long long)blockIdx.x * TN;
+  const int tx = threadIdx.x % (TN / RN), ty = threadIdx.x / (TN / RN);
+  const long long sam = g.ta ? 1 : g.lda, sak = g.ta ? g.lda : 1;
+  const long long sbn = g.tb ? 1 : g.ldb, sbk = g.tb ? g.ldb : 1;
+  const float* A = (const float*)g.a + b * g.bsa;
+  const float* B = (const float*)g.b + b * g.bsb;
+  float ra[LA], rb[LB];
+  auto fetch = [&](long long k0) {
+#pragma unroll
+    for (int i = 0; i < LA; ++i) {
+      const int e = threadIdx.x + i * 256;
+      // consecutive threads walk the contiguous index of the operand
+      const int kk = g.ta ? e / TM : e % TK, mm = g.ta ? e % TM : e / TK;
+      const long long m = m0 + mm, k = k0 + kk;
+      ra[i] = (m < g.m && k < g.k) ? A[m * sam + k * sak] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < LB; ++i) {
+      const int e = threadIdx.x + i * 256;
+      const int kk = g.tb ? e / TN : e % TK, nn = g.tb ? e % TN : e / TK;
+      const long long n = n0 + nn, k = k0 + kk;
+      rb[i] = (n < g.n && k < g.k) ? B[n * sbn + k * sbk] : 0.f;
+    }
+  };
+  auto stage = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < LA; ++i) {
+      const int e = threadIdx.x + i * 256;
+      const int kk = g.ta ? e / TM : e % TK, mm = g.ta ? e % TM : e / TK;
+      As[buf][kk][mm] = ra[i];
+    }
+#pragma unroll
+    for (int i = 0; i < LB; ++i) {
+      const int e = threadIdx.x + i * 256;
+      const int kk = g.tb ? e / TN : e % TK, nn = g.tb ? e % TN : e / TK;
+      Bs[buf][kk][nn] = rb[i];
+    }
+  };
+  float acc[RM][RN];
+#pragma unroll
+  for (int i = 0; i < RM; ++i)
+#pragma unroll
+    for (int j = 0; j < RN; ++j) acc[i][j] = 0.f;
+  fetch(0);
+  stage(0);
+  __syncthreads();
+  int buf = 0;
+  for (long long k0 = 0; k0 < g.k; k0 += TK) {
+    const bool more = k0 + TK < g.k;
+    if (more) fetch(k0 + TK);
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      float av[RM], bv[RN];
+#pragma unroll
+      for (int i = 0; i < RM; ++i) av[i] = As[buf][kk][ty * RM + i];
+#pragma unroll
+      for (int j = 0; j < RN; ++j) bv[j] = Bs[buf][kk][tx * RN + j];
+#pragma unroll
+      for (int i = 0; i < RM; ++i)
+#pragma unroll
+        for (int j = 0; j < RN; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    if (more) stage(buf ^ 1);        // the other buffer was last read before the previous barrier
+    __syncthreads();
+    buf ^= 1;
+  }
+  float* C = (float*)g.c + b * g.m * g.n;
+#pragma unroll
+  for (int i = 0; i < RM; ++i)
+#pragma unroll
+    for (int j = 0; j < RN; ++j) {
+      const long long m = m0 + ty * RM + i, n = n0 + tx * RN + j;
+      if (m < g.m && n < g.n) C[m * g.n + n] = acc[i][j];
+    }
+}
+
 }  // namespace
 
 void launch_simt_gemm(const GemmArgs& g, cudaStream_t stream) {
   if (g.batch == 0 || g.m == 0 || g.n == 0) return;
   if (g.batch > 65535) fail(NXB_ERR_UNSUPPORTED, "dot with more than 65535 batch entries on the CUDA-core path");
+  if (g.da == NXB_F32 && g.db == NXB_F32 && g.dc == NXB_F32 && !g.bias && !g.scale) {
+    // small tiles until the grid fills the machine a few times over
+    const long long big = ((g.m + 63) / 64) * ((g.n + 63) / 64) * g.batch;
+    if (big >= 296) {
+      dim3 grid((unsigned)((g.n + 63) / 64), (unsigned)((g.m + 63) / 64), (unsigned)g.batch);
+      sgemm_kernel<64, 64, 4, 4, 16><<<grid, 256, 0, stream>>>(g);
+    } else {
+      dim3 grid((unsigned)((g.n + 31) / 32), (unsigned)((g.m + 15) / 16), (unsigned)g.batch);
+      sgemm_kernel<16, 32, 1, 2, 32><<<grid, 256, 0, stream>>>(g);
+    }
+    NXB_CUDA(cudaGetLastError());
+    return;
+  }
   dim3 grid((unsigned)((g.n + TN - 1) / TN), (unsigned)((g.m + TM - 1) / TM), (unsigned)g.batch);
   switch (g.dc) {
     case NXB_F64: simt_gemm_kernel<double><<<grid, 256, 0, stream>>>(g); break;
