@@ -11,8 +11,9 @@
 //               head-dim index contiguous, i.e. an MN-major B operand)
 //   warps 2..9  softmax, two threads per query row (a row lives in one TMEM lane; each thread
 //               owns 64 key columns and 64 head dims, the halves exchange maxima through shared
-//               memory): running maximum m, running sum l, and the output half-row O (64 f32
-//               registers) rescaled by exp(m_old - m_new)
+//               memory): running maximum m and running sum l; the output row O accumulates in
+//               TMEM across key blocks and is read back and rescaled only when the maximum
+//               moves by more than a threshold (rare after the first blocks)
 // Keys beyond a causal diagonal are skipped block-wise when the planner proved the mask is
 // causal.  Every mbarrier wait is bounded; on expiry the CTA raises an abort flag, all roles
 // leave their loops, tensor memory is released and the host reports NXB_ERR_TIMEOUT.
@@ -141,7 +142,7 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
           const uint64_t adesc = make_desc(sP + (k8 >> 2) * (TILE / 2)) + (uint64_t)((k8 & 3) * 2);
           const uint64_t bdesc = ((uint64_t)(((v + k8 * 2048) & 0x3FFFF) >> 4)) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
                                  ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-          tc_mma(tPV, adesc, bdesc, idesc_pv, k8 > 0 ? 1u : 0u, false);
+          tc_mma(tPV, adesc, bdesc, idesc_pv, (j > 0 || k8 > 0) ? 1u : 0u, false);
         }
         tc_commit(pv_full);
         tc_commit(kv_empty0 + 8 * (j & 1));
@@ -157,16 +158,18 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
     const long long qi = (long long)q0 + row;
     const long long b_idx = bh / p.heads, h_idx = bh % p.heads;
     const uint32_t lane_addr = ((uint32_t)(q * 32) << 16) + (uint32_t)(hf * 64);
-    float o[64];
-#pragma unroll
-    for (int d = 0; d < 64; ++d) o[d] = 0.f;
+    // The output row stays in its TMEM accumulator: PV products accumulate there, and it is only
+    // read back and rescaled when the running maximum moves by more than RESCALE_STEP (until then
+    // the old maximum keeps being used, so probabilities may reach e^RESCALE_STEP = 256, far inside
+    // bf16's range; the final division by the sum makes the result independent of that choice).
+    constexpr float LOG2E = 1.4426950408889634f, RESCALE_STEP = 5.545177444f;
     float m = -NXB_INF, l = 0.f;
     uint32_t sfph[2] = {0, 0};
     bool ok = true;
     for (int j = 0; j < nkv && ok; ++j) {
       const int s = j & 1;
-      // warp-uniform outcome: the tensor-memory loads below need the whole warp
-      if (!__all_sync(0xffffffffu, mbar_wait(s_full0 + 8 * s, sfph[s], abort_flag))) { ok = false; break; }
+      // one lane polls on behalf of its warp; the tensor-memory loads below need the whole warp
+      if (!mbar_wait_warp_tight(s_full0 + 8 * s, sfph[s], abort_flag)) { ok = false; break; }
       sfph[s] ^= 1;
       tc_fence_after();
       const uint32_t tS = tS0 + (uint32_t)(s * 128) + lane_addr;
@@ -174,50 +177,63 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
       tmem_ld32x2(tS, sv);
       float x[64];
       float mx = -NXB_INF;
+      const long long kj0 = (long long)j * BKV + hf * 64;
+      if (kj0 + 64 <= p.sk) {
 #pragma unroll
-      for (int t = 0; t < 64; ++t) {
-        const long long kj = (long long)j * BKV + hf * 64 + t;
-        float xv = Xform::apply(__uint_as_float(sv[t]), (long long)bh, qi, kj, p.ep);
-        xv = (kj < p.sk) ? xv : -NXB_INF;
-        x[t] = xv;
-        mx = nx_max(mx, xv);
+        for (int t = 0; t < 64; ++t) {
+          x[t] = Xform::apply(__uint_as_float(sv[t]), (long long)bh, qi, kj0 + t, p.ep);
+          mx = nx_max(mx, x[t]);
+        }
+      } else {
+        // the last key block: columns beyond the keys contribute nothing
+#pragma unroll
+        for (int t = 0; t < 64; ++t) {
+          const float xv = Xform::apply(__uint_as_float(sv[t]), (long long)bh, qi, kj0 + t, p.ep);
+          x[t] = (kj0 + t < p.sk) ? xv : -NXB_INF;
+          mx = nx_max(mx, x[t]);
+        }
       }
       // exchange the half-row maxima (double buffered by block parity: one bounded wait per block)
       xmax[(s * 2 + hf) * 128 + row] = mx;
       __syncwarp();
       if (lane == 0) mbar_arrive(xchg_bar);
-      if (!__all_sync(0xffffffffu, mbar_wait(xchg_bar, (uint32_t)(j & 1), abort_flag))) { ok = false; break; }
-      const float m_new = nx_max(m, nx_max(mx, xmax[(s * 2 + (hf ^ 1)) * 128 + row]));
-      const float alpha = (m_new == -NXB_INF) ? 1.f : nx_exp(m - m_new);
+      if (!mbar_wait_warp_tight(xchg_bar, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+      const float m_seen = nx_max(m, nx_max(mx, xmax[(s * 2 + (hf ^ 1)) * 128 + row]));
+      // both threads of a row take the same decision: they see the same three numbers
+      const bool move = m_seen > m + RESCALE_STEP || m == -NXB_INF;
+      const float m_use = move ? m_seen : m;
       if (j > 0) {
-        // PV of the previous block is complete (and P's buffer is free): add it in, still in the old scale
-        if (!__all_sync(0xffffffffu, mbar_wait(pv_full, (uint32_t)((j - 1) & 1), abort_flag))) { ok = false; break; }
+        // PV of the previous block is complete: P's buffer is free, and O may be touched
+        if (!mbar_wait_warp_tight(pv_full, (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; break; }
         tc_fence_after();
+        if (__any_sync(0xffffffffu, move && m != -NXB_INF)) {
+          const float alpha = (move && m != -NXB_INF) ? nx_exp2(m * LOG2E - m_use * LOG2E) : 1.f;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t pv[32];
-          tmem_ld32(tPV + lane_addr + (uint32_t)(c * 32), pv);
+          for (int c = 0; c < 2; ++c) {
+            uint32_t ov[32];
+            tmem_ld32(tPV + lane_addr + (uint32_t)(c * 32), ov);
 #pragma unroll
-          for (int t = 0; t < 32; ++t) o[c * 32 + t] += __uint_as_float(pv[t]);
+            for (int t = 0; t < 32; ++t) ov[t] = __float_as_uint(__uint_as_float(ov[t]) * alpha);
+            tmem_st32(tPV + lane_addr + (uint32_t)(c * 32), ov);
+          }
+          l *= alpha;
         }
       }
-#pragma unroll
-      for (int d = 0; d < 64; ++d) o[d] *= alpha;
-      l *= alpha;
-      m = m_new;
-      // probabilities of my 64 keys, their sum, and P (bf16): exactly one 64-key half of the A operand
+      m = m_use;
+      // probabilities of my 64 keys (one FMA and one ex2 each), their sum, and P in bf16: exactly
+      // one 64-key half of the A operand.  A fully masked row has m = -inf: every x is -inf too,
+      // and with a zero offset ex2(-inf) = 0 without a NaN.
+      const float off = (m == -NXB_INF) ? 0.f : -m * LOG2E;
       const uint32_t rowbase = sP + (uint32_t)hf * (TILE / 2) + (uint32_t)row * 128u;
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
         uint32_t pk[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const float e0 = (m_new == -NXB_INF) ? 0.f : nx_exp(x[g * 8 + u * 2] - m_new);
-          const float e1 = (m_new == -NXB_INF) ? 0.f : nx_exp(x[g * 8 + u * 2 + 1] - m_new);
-          const unsigned short h0 = f32_to_bf16_bits(e0), h1 = f32_to_bf16_bits(e1);
-          // the sum uses the same rounded values the product consumes
-          l += __uint_as_float(((uint32_t)h0) << 16) + __uint_as_float(((uint32_t)h1) << 16);
-          pk[u] = (uint32_t)h0 | ((uint32_t)h1 << 16);
+          const float e0 = nx_exp2(fmaf(x[g * 8 + u * 2], LOG2E, off));
+          const float e1 = nx_exp2(fmaf(x[g * 8 + u * 2 + 1], LOG2E, off));
+          l += e0 + e1;
+          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[u]) : "f"(e1), "f"(e0));
         }
         const uint32_t dst = rowbase + (((uint32_t)g ^ (uint32_t)(row & 7)) * 16u);
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
@@ -228,30 +244,30 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
       if (lane == 0) { mbar_arrive(s_empty0 + 8 * s); mbar_arrive(p_full); }
     }
     if (ok && nkv > 0) {
-      if (__all_sync(0xffffffffu, mbar_wait(pv_full, (uint32_t)((nkv - 1) & 1), abort_flag))) {
+      if (mbar_wait_warp_tight(pv_full, (uint32_t)((nkv - 1) & 1), abort_flag)) {
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t pv[32];
-          tmem_ld32(tPV + lane_addr + (uint32_t)(c * 32), pv);
-#pragma unroll
-          for (int t = 0; t < 32; ++t) o[c * 32 + t] += __uint_as_float(pv[t]);
-        }
         // total of the two half-row sums
         xsum[hf * 128 + row] = l;
         __syncwarp();
         if (lane == 0) mbar_arrive(xchg_bar);
-        if (__all_sync(0xffffffffu, mbar_wait(xchg_bar, (uint32_t)(nkv & 1), abort_flag)) && qi < p.sq) {
+        if (mbar_wait_warp_tight(xchg_bar, (uint32_t)(nkv & 1), abort_flag)) {
           const float inv = 1.f / (l + xsum[(hf ^ 1) * 128 + row]);
           unsigned short* out = (unsigned short*)p.out + b_idx * p.out_bh_hi + h_idx * p.out_bh_lo + qi * p.out_row + hf * 64;
 #pragma unroll
-          for (int d = 0; d < 64; d += 8) {
-            uint4 w;
-            w.x = f32_to_bf16_bits(o[d] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 1] * inv) << 16);
-            w.y = f32_to_bf16_bits(o[d + 2] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 3] * inv) << 16);
-            w.z = f32_to_bf16_bits(o[d + 4] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 5] * inv) << 16);
-            w.w = f32_to_bf16_bits(o[d + 6] * inv) | ((uint32_t)f32_to_bf16_bits(o[d + 7] * inv) << 16);
-            *reinterpret_cast<uint4*>(out + d) = w;
+          for (int c = 0; c < 2; ++c) {
+            uint32_t ov[32];
+            tmem_ld32(tPV + lane_addr + (uint32_t)(c * 32), ov);
+            if (qi < p.sq) {
+#pragma unroll
+              for (int d = 0; d < 32; d += 8) {
+                uint4 w;
+                uint32_t* ww = &w.x;
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(ww[e]) : "f"(__uint_as_float(ov[d + 2 * e + 1]) * inv), "f"(__uint_as_float(ov[d + 2 * e]) * inv));
+                *reinterpret_cast<uint4*>(out + c * 32 + d) = w;
+              }
+            }
           }
         }
       }
