@@ -147,6 +147,7 @@ def trace(fun, templates):
         outs = []
         ospec = _flatten(result, outs)
         outs = [B.to_expr(o) for o in outs]
+    trace.params = params          # of the latest trace (the serialiser keeps unused ones)
     return outs, ospec
 
 
@@ -164,7 +165,7 @@ def __compile__(key, templates, fun, opts):
         outs, ospec = trace(fun, templates)
         # outputs that are parameters or constants still need a buffer of
         # their own: results are always fresh tensors (exla/lib/exla/defn.ex:387-393)
-        blob = E.serialize(outs)
+        blob = E.serialize(outs, trace.params)
         entry = (Program(blob), ospec)
         with _cache_lock:
             _cache.setdefault(ck, entry)
@@ -238,5 +239,83 @@ def build_program(fun, templates):
     touching the native library (used by tests of the front-end and by the
     oracle, which interprets the same bytes)."""
     outs, ospec = trace(fun, list(templates))
-    return E.serialize(outs), ospec
+    return E.serialize(outs, trace.params), ospec
 
+
+
+# ---- control flow (nx/lib/nx/defn/kernel.ex while/cond; Expr :while / :cond) --------------------
+# Host-orchestrated: the condition and the body are compiled programs and the loop runs on the
+# host, reading the one-byte predicate back each iteration (what Nx.Defn.Evaluator does with a
+# device backend).  This covers loops at the top of a computation - an autoregressive decode
+# loop over a KV cache - where each iteration is a whole program anyway.
+
+def _traced(values):
+    flat = []
+    for v in values:
+        _flatten(v, flat)
+    return any(isinstance(t, Tensor) and isinstance(getattr(t, "data", None), E.Expr) and t.data.op != "constant" for t in flat)
+
+
+def _signature(state):
+    flat = []
+    _flatten(state, flat)
+    return [(t.type, t.shape) for t in flat]
+
+
+def while_loop(cond_fun, body_fun, init, max_iterations=None, **opts):
+    """``while state = init, cond_fun.(state) do body_fun.(state) end``.
+
+    `init` is a tuple of tensors (containers allowed); both functions take the state's
+    elements as positional arguments.  As in the reference (nx/lib/nx/defn/expr.ex while/4)
+    the body must return the state's exact types and shapes and the condition a scalar.
+    Returns the final state."""
+    from . import nx
+    state = tuple(init)
+    if _traced(state):
+        raise NotImplementedError("while inside a traced defn is not compiled yet: run the loop at the top level")
+    state = tuple(_map_tensors(nx.tensor, s) for s in state)
+    want = _signature(state)
+    cond_c, body_c = jit(cond_fun, **opts), jit(body_fun, **opts)
+    n = 0
+    while True:
+        pred = cond_c(*state)
+        if not isinstance(pred, Tensor) or pred.shape != ():
+            raise ValueError(f"condition must be a scalar tensor, got {getattr(pred, 'shape', type(pred))}")
+        if not nx.to_number(pred):
+            return state
+        if max_iterations is not None and n >= max_iterations:
+            raise RuntimeError(f"while_loop did not finish within {max_iterations} iterations")
+        new = body_c(*state)
+        new = tuple(new) if isinstance(new, (tuple, list)) else (new,)
+        got = _signature(new)
+        if got != want:
+            raise ValueError(f"the do-block in while must return tensors with the same shape, type, and names as the initial arguments: {got} vs {want}")
+        state = new
+        n += 1
+
+
+def cond(pred, then_fun, else_fun, *operands):
+    """``cond do pred -> then_fun.(operands) ; true -> else_fun.(operands) end`` with a scalar
+    predicate.  At the top level the predicate is read back and one branch runs; inside a traced
+    defn both branches become part of the graph and ``select`` picks (identical results for
+    these side-effect-free functions; the reference's single-branch execution only saves work)."""
+    from . import nx
+    p = pred if isinstance(pred, Tensor) else nx.tensor(pred)
+    if p.shape != ():
+        raise ValueError(f"condition must be a scalar tensor, got shape {p.shape}")
+    if not _traced((p,) + tuple(operands)):
+        return then_fun(*operands) if nx.to_number(p) else else_fun(*operands)
+    a, b = then_fun(*operands), else_fun(*operands)
+    fa, fb = [], []
+    spec_a, spec_b = _flatten(a, fa), _flatten(b, fb)
+    if [(t.type, t.shape) for t in fa] != [(t.type, t.shape) for t in fb] or repr(spec_a) != repr(spec_b):
+        raise ValueError("cond expects all branches to return compatible tensor types and shapes")
+    return _unflatten(spec_a, iter([nx.select(p, x, y) for x, y in zip(fa, fb)]))
+
+
+def _map_tensors(fun, c):
+    if isinstance(c, (tuple, list)):
+        return type(c)(_map_tensors(fun, x) for x in c)
+    if isinstance(c, dict):
+        return {k: _map_tensors(fun, v) for k, v in c.items()}
+    return fun(c)

@@ -271,10 +271,17 @@ def topo_order(outputs):
     return order, seen
 
 
-def serialize(outputs):
+def serialize(outputs, params=None):
     """Flatten the DAG reachable from ``outputs`` (a list of tensors whose data
-    are Expr nodes) into the program wire format."""
+    are Expr nodes) into the program wire format.  ``params`` (the function's
+    parameter nodes) are written even when no output depends on them, so that
+    the program keeps the function's arity (EXLA likewise accepts arguments it
+    does not use, exla/lib/exla/defn.ex used-inputs handling)."""
     order, index = topo_order(outputs)
+    for p in params or []:
+        if p.data.id not in index:
+            index[p.data.id] = len(order)
+            order.append(p)
     buf = bytearray(MAGIC)
     buf += struct.pack("<I", len(order))
     for t in order:
