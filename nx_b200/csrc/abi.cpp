@@ -133,6 +133,11 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
       }
     }
     const DriverApi& drv = driver();
+    // Runs the plan's steps on the device's stream.  With `held` the temporaries are kept (their
+    // addresses are baked into a graph being captured) and anything that needs scratch memory of
+    // its own makes the program unfit for replay.
+    struct NotReplayable {};
+    auto run_steps = [&](std::vector<void*>* held) {
     bool skip_step = false;      // the previous product already did this step's all-reduce
     for (size_t st = 0; st < plan.steps.size(); ++st) {
       for (size_t s = 0; s < plan.slots.size(); ++s)
@@ -164,6 +169,7 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         check_cu(drv.cuLaunchKernel(L.functions[as.jit_kernel], tl.grid, 1, 1, 320, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
                  ("launching " + ks.name).c_str());
       } else if (step.kind == Step::ALLREDUCE) {
+        if (held) throw NotReplayable();
         const CollectiveSpec& cs = plan.collectives[step.index];
         comm_all_reduce(ptr[cs.in_slot], ptr[cs.out_slot], (size_t)cs.count, cs.dt, d);
       } else {
@@ -197,6 +203,7 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         if (on_tensor_cores) {
           void* ta = nullptr;
           void* tb = nullptr;
+          if (held && ((ga.ta && !mn_a) || (ga.tb && !mn_b))) throw NotReplayable();
           if (ga.ta && !mn_a) {
             ta = d.alloc.alloc((size_t)(ga.batch * ga.m * ga.k) * es);
             launch_transpose(ga.a, ta, ga.batch, ga.k, ga.m, es, d.stream);
@@ -243,8 +250,79 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
       }
     step_done:
       for (size_t s = 0; s < plan.slots.size(); ++s)
-        if (plan.slots[s].kind == Slot::TEMP && plan.slots[s].last_step == (int)st && ptr[s]) { d.alloc.free(ptr[s]); ptr[s] = nullptr; }
+        if (plan.slots[s].kind == Slot::TEMP && plan.slots[s].last_step == (int)st && ptr[s]) {
+          if (held) held->push_back(ptr[s]);
+          else d.alloc.free(ptr[s]);
+          ptr[s] = nullptr;
+        }
     }
+    };
+
+    // ---- replay of small programs as CUDA graphs ----
+    static const bool graphs_off = getenv("NXB200_NO_GRAPHS") != nullptr;
+    size_t temp_bytes = 0;
+    for (auto& sl : plan.slots) if (sl.kind == Slot::TEMP) temp_bytes += sl.nbytes;
+    const bool small = plan.steps.size() <= 64 && temp_bytes <= (64u << 20) && plan.collectives.empty();
+    bool done = false;
+    if (!graphs_off && small && L.graphable) {
+      std::vector<void*> key;
+      for (int i = 0; i < n_args; ++i) key.push_back(args[i]->ptr);
+      for (int i = 0; i < n_outs; ++i) key.push_back(ptr[plan.output_slots[i]]);
+      ++L.tick;
+      for (auto& r : L.replays)
+        if (r.key == key) {
+          NXB_CUDA(cudaGraphLaunch(r.exec, d.stream));
+          r.last_use = L.tick;
+          done = true;
+          break;
+        }
+      if (!done) {
+        auto it = std::find(L.seen.begin(), L.seen.end(), key);
+        if (it == L.seen.end()) {
+          if (L.seen.size() >= 16) L.seen.erase(L.seen.begin());
+          L.seen.push_back(key);
+        } else {
+          L.seen.erase(it);
+          nxb200_program::Loaded::Replay r;
+          r.key = key;
+          cudaGraph_t graph = nullptr;
+          bool captured = false;
+          if (cudaStreamBeginCapture(d.stream, cudaStreamCaptureModeRelaxed) == cudaSuccess) {
+            try {
+              run_steps(&r.held);
+              captured = cudaStreamEndCapture(d.stream, &graph) == cudaSuccess && graph != nullptr;
+            } catch (const NotReplayable&) {
+              cudaStreamEndCapture(d.stream, &graph);
+            } catch (...) {
+              // whatever failed under capture is retried below as plain launches, which report it properly
+              cudaStreamEndCapture(d.stream, &graph);
+            }
+          }
+          if (captured && cudaGraphInstantiate(&r.exec, graph, 0) == cudaSuccess) {
+            cudaGraphDestroy(graph);
+            NXB_CUDA(cudaGraphLaunch(r.exec, d.stream));
+            r.last_use = L.tick;
+            if (L.replays.size() >= 8) {      // evict the least recently used (its work is ordered before ours on the stream)
+              auto lru = std::min_element(L.replays.begin(), L.replays.end(), [](auto& x, auto& y) { return x.last_use < y.last_use; });
+              cudaGraphExecDestroy(lru->exec);
+              for (void* h : lru->held) d.alloc.free(h);
+              L.replays.erase(lru);
+            }
+            L.replays.push_back(std::move(r));
+            done = true;
+          } else {
+            // not fit for replay (scratch memory, a collective, or the capture failed): plain launches from now on
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            for (void* h : r.held) d.alloc.free(h);
+            for (size_t s2 = 0; s2 < plan.slots.size(); ++s2)
+              if (plan.slots[s2].kind == Slot::TEMP && ptr[s2]) { d.alloc.free(ptr[s2]); ptr[s2] = nullptr; }
+            L.graphable = false;
+          }
+        }
+      }
+    }
+    if (!done) run_steps(nullptr);
   } catch (...) {
     for (auto* b : made) { d.alloc.free(b->ptr); delete b; }
     for (size_t s = 0; s < plan.slots.size(); ++s)
@@ -461,6 +539,10 @@ int nxb200_program_release(nxb200_program* prog) {
       for (auto m : kv.second.modules) driver().cuModuleUnload(m);
       std::lock_guard<std::mutex> g(d.mu);
       for (auto& l : kv.second.literals) d.alloc.free(l.second);
+      for (auto& r : kv.second.replays) {
+        cudaGraphExecDestroy(r.exec);
+        for (void* h : r.held) d.alloc.free(h);
+      }
     }
     p->magic = 0;
     delete p;

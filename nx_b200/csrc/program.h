@@ -128,6 +128,19 @@ struct nxb200_program {
     std::vector<CUmodule> modules;
     std::vector<CUfunction> functions;
     std::map<int, void*> literals;   // slot -> device pointer
+    // Replay of small programs as CUDA graphs: a program whose argument and result
+    // addresses were seen before is captured once (its temporaries stay reserved for
+    // the graph) and afterwards costs one graph launch instead of one launch per step.
+    struct Replay {
+      std::vector<void*> key;          // argument pointers, then result pointers
+      cudaGraphExec_t exec = nullptr;
+      std::vector<void*> held;         // temporaries the captured kernels write
+      uint64_t last_use = 0;
+    };
+    std::vector<Replay> replays;
+    std::vector<std::vector<void*>> seen;   // keys met once (capture on the second meeting)
+    bool graphable = true;
+    uint64_t tick = 0;
   };
   std::map<int, Loaded> loaded;
 };

@@ -344,3 +344,22 @@ def test_kv_cache_update_and_window_read(pos):
     check(res[1:], "window")
     mixed = run_both(lambda c, n, p: nx.put_slice(c, [0, 0, p, 0], n), [cache, new, np.array(pos)], ["f32", "bf16", "s64"])
     assert mixed[0][2] == ("f", 32) and np.array_equal(mixed[0][0], mixed[0][1])
+
+
+def test_repeated_runs_replay_a_graph_and_still_read_current_data():
+    """From its third run on the same buffers a small program is replayed as a captured CUDA graph
+    (the first run executes step by step, the second captures): the replay must read what the
+    buffers hold now.  A second program refills the replayed program's input between runs."""
+    rng = np.random.default_rng(21)
+    w = nx.tensor(rng.normal(0, 1, (64, 32)).astype(np.float32))
+    fill = defn.compile(lambda t: t * 1.0 + 0.0 * nx.sum(t), [defn.template((16, 64), "f32")]).program
+    mlp = defn.compile(lambda t, m: nx.tanh(nx.dot(t, m)) + nx.sum(t, axes=[1], keep_axes=True),
+                       [defn.template((16, 64), "f32"), defn.template((64, 32), "f32")]).program
+    x_dev = fill.run([nx.tensor(np.zeros((16, 64), np.float32))], 0)       # the buffer both programs share
+    outs = None
+    for i in range(6):
+        x = rng.normal(0, 1, (16, 64)).astype(np.float32)
+        fill.run_into([nx.tensor(x)], x_dev, 0)
+        outs = mlp.run([x_dev[0], w], 0) if outs is None else mlp.run_into([x_dev[0], w], outs, 0)
+        want = np.tanh(x.astype(np.float64) @ nx.to_numpy(w).astype(np.float64)) + x.sum(axis=1, keepdims=True)
+        assert_close(nx.to_numpy(outs[0]), want, rtol=1e-5, atol=1e-5, what=f"run {i}")
