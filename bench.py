@@ -365,28 +365,40 @@ def main():
         pin_in = torch.empty(x_host.nbytes, dtype=torch.uint8, pin_memory=True)
         pin_in.numpy()[:] = x_host.reshape(-1).view(np.uint8)
         out_bytes = [o.size * 4 for o in outs]
-        pin_out = [torch.empty(n, dtype=torch.uint8, pin_memory=True) for n in out_bytes]
-        e2e_steps = max(2, min(args.steps, 5))
+        # two sets of pinned result buffers: the host could consume one while the other fills
+        pin_out = [[torch.empty(n, dtype=torch.uint8, pin_memory=True) for n in out_bytes] for _ in range(2)]
+        e2e_steps = max(2, min(args.steps, 6))
 
-        def one():
+        def one(i):
+            # upload on the upload stream (overlaps the previous step's downloads: the link is full
+            # duplex), the program after it, the downloads after the program; the library orders the
+            # next step's program after these downloads, so the device results are never overwritten early
             nif.check(lib.nxb200_buffer_write_async(x.data.handle, pin_in.data_ptr(), x_host.nbytes))
             prog.run_into([x], outs, local)
-            for o, p, n in zip(outs, pin_out, out_bytes):
+            for o, p, n in zip(outs, pin_out[i % 2], out_bytes):
                 nif.check(lib.nxb200_buffer_read_async(o.data.handle, p.data_ptr(), n))
-            nif.check(lib.nxb200_device_synchronize(local))
 
-        one()
+        one(0)
+        nif.check(lib.nxb200_device_synchronize(local))
         barrier()
         t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            one()
+        for i in range(e2e_steps):
+            one(i)
+        nif.check(lib.nxb200_device_synchronize(local))     # every step's results are in host memory
         dt = (time.perf_counter() - t0) / e2e_steps
         if dist is not None:
             t = torch.tensor([dt], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dt = float(t.item())
         e2e = {"value": round(world * nbytes / dt / 1e9, 3), "unit": UNIT, "h2d_bytes_per_step": int(x_host.nbytes),
-               "d2h_bytes_per_step": int(sum(out_bytes)), "ms_per_step": round(dt * 1e3, 3), "steps": e2e_steps}
+               "d2h_bytes_per_step": int(sum(out_bytes)), "ms_per_step": round(dt * 1e3, 3), "steps": e2e_steps,
+               "overlap": "upload of step i+1 runs while step i's results download (separate copy streams)"}
+        # what reached host memory in both result sets is what the device holds
+        for k, o in enumerate(outs):
+            dev_bytes = nx.to_numpy(o).reshape(-1).view(np.uint8)
+            for s in range(2):
+                if not np.array_equal(pin_out[s][k].numpy()[:: 4099], dev_bytes[:: 4099]):
+                    raise SystemExit(f"end-to-end run: result {k} in host buffer set {s} differs from the device tensor")
         del pin_in, pin_out
 
     launches = args.steps * prog.launch_count()

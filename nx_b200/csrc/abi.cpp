@@ -59,6 +59,13 @@ nxb200_buffer* make_buffer(Device& d, DType dt, const int64_t* dims, int rank) {
   return b.release();
 }
 
+// Compute work queued from here on starts after the downloads in flight (caller holds d.mu).
+void order_after_downloads(Device& d) {
+  if (d.pending_reads.empty()) return;
+  NXB_CUDA(cudaStreamWaitEvent(d.stream, d.ev_d2h, 0));
+  d.pending_reads.clear();
+}
+
 void ensure_loaded(nxb200_program* p, Device& d) {
   auto it = p->loaded.find(d.id);
   if (it != p->loaded.end()) return;
@@ -110,6 +117,7 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
   std::lock_guard<std::mutex> pg(p->mu);
   std::lock_guard<std::mutex> dg(d.mu);
   ensure_loaded(p, d);
+  order_after_downloads(d);
   auto& L = p->loaded[device];
   for (auto& kv : L.literals) ptr[kv.first] = kv.second;
   std::vector<nxb200_buffer*> made;
@@ -407,7 +415,16 @@ int nxb200_buffer_write_async(nxb200_buffer* buf, const void* src, size_t nbytes
     nxb200_buffer* b = check_buffer(buf);
     if (nbytes > b->nbytes) fail(NXB_ERR_INVALID_ARGUMENT, "more bytes than the tensor holds");
     Device& d = nxb::device(b->device);
-    NXB_CUDA(cudaMemcpyAsync(b->ptr, src, nbytes, cudaMemcpyHostToDevice, d.stream));
+    std::lock_guard<std::mutex> g(d.mu);
+    // after the kernels already queued (they may still read the buffer), before the ones to come;
+    // concurrent with downloads in flight unless one of them reads this very buffer
+    NXB_CUDA(cudaEventRecord(d.ev_compute, d.stream));
+    NXB_CUDA(cudaStreamWaitEvent(d.h2d, d.ev_compute, 0));
+    if (std::find(d.pending_reads.begin(), d.pending_reads.end(), (const void*)b->ptr) != d.pending_reads.end())
+      NXB_CUDA(cudaStreamWaitEvent(d.h2d, d.ev_d2h, 0));
+    NXB_CUDA(cudaMemcpyAsync(b->ptr, src, nbytes, cudaMemcpyHostToDevice, d.h2d));
+    NXB_CUDA(cudaEventRecord(d.ev_h2d, d.h2d));
+    NXB_CUDA(cudaStreamWaitEvent(d.stream, d.ev_h2d, 0));
   });
 }
 
@@ -416,7 +433,14 @@ int nxb200_buffer_read_async(nxb200_buffer* buf, void* dst, size_t nbytes) {
     nxb200_buffer* b = check_buffer(buf);
     if (nbytes > b->nbytes) fail(NXB_ERR_INVALID_ARGUMENT, "more bytes than the tensor holds");
     Device& d = nxb::device(b->device);
-    NXB_CUDA(cudaMemcpyAsync(dst, b->ptr, nbytes, cudaMemcpyDeviceToHost, d.stream));
+    std::lock_guard<std::mutex> g(d.mu);
+    // after the kernels already queued (they produce the data); the next program waits for it
+    // (order_after_downloads), so the buffer is not overwritten while it is being read
+    NXB_CUDA(cudaEventRecord(d.ev_compute, d.stream));
+    NXB_CUDA(cudaStreamWaitEvent(d.d2h, d.ev_compute, 0));
+    NXB_CUDA(cudaMemcpyAsync(dst, b->ptr, nbytes, cudaMemcpyDeviceToHost, d.d2h));
+    NXB_CUDA(cudaEventRecord(d.ev_d2h, d.d2h));
+    d.pending_reads.push_back(b->ptr);
   });
 }
 
@@ -467,6 +491,7 @@ int nxb200_buffer_deallocate(nxb200_buffer* buf) {
     if (was) fail(NXB_ERR_ALREADY_DEALLOCATED, "buffer was already deallocated");
     Device& d = nxb::device(b->device);
     std::lock_guard<std::mutex> g(d.mu);
+    order_after_downloads(d);      // whoever gets this memory next writes it on the compute stream
     d.alloc.free(b->ptr);
     b->ptr = nullptr;
   });
@@ -582,6 +607,12 @@ int nxb200_device_synchronize(int dev) {
   return guarded([&] {
     Device& d = nxb::device(dev);
     NXB_CUDA(cudaStreamSynchronize(d.stream));
+    NXB_CUDA(cudaStreamSynchronize(d.h2d));
+    NXB_CUDA(cudaStreamSynchronize(d.d2h));
+    {
+      std::lock_guard<std::mutex> g(d.mu);
+      d.pending_reads.clear();
+    }
     check_device_status(d);
   });
 }

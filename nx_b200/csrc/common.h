@@ -100,6 +100,12 @@ struct Device {
   int id = 0;
   cudaStream_t stream = nullptr;
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  // Asynchronous transfers run on streams of their own, so that an upload can overlap a
+  // download (the link is full duplex) and both can overlap kernels.  Ordering against the
+  // compute stream is by events; `pending_reads` are device addresses a download may still read.
+  cudaStream_t h2d = nullptr, d2h = nullptr;
+  cudaEvent_t ev_compute = nullptr, ev_h2d = nullptr, ev_d2h = nullptr;
+  std::vector<const void*> pending_reads;
   Allocator alloc;
   std::mutex mu;             // serialises enqueue + allocator state for this device
   int sm_count = 148;

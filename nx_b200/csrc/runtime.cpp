@@ -159,6 +159,11 @@ Device& device(int id) {
       NXB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
       NXB_CUDA(cudaEventCreate(&d.ev0));
       NXB_CUDA(cudaEventCreate(&d.ev1));
+      NXB_CUDA(cudaStreamCreateWithFlags(&d.h2d, cudaStreamNonBlocking));
+      NXB_CUDA(cudaStreamCreateWithFlags(&d.d2h, cudaStreamNonBlocking));
+      NXB_CUDA(cudaEventCreateWithFlags(&d.ev_compute, cudaEventDisableTiming));
+      NXB_CUDA(cudaEventCreateWithFlags(&d.ev_h2d, cudaEventDisableTiming));
+      NXB_CUDA(cudaEventCreateWithFlags(&d.ev_d2h, cudaEventDisableTiming));
       int sms = 148;
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, id);
       d.sm_count = sms;
