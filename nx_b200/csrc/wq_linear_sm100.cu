@@ -16,7 +16,9 @@
 //               arrive sequence: the latency of that sequence, not its instruction count, is
 //               what paces a pipeline whose MMAs are a few cycles each.  Afterwards the same
 //               warps are the epilogue (tcgen05.ld, scale per lane, store)
-//   warp 4      MMA issuer (scheduler partition 0, like the producer; warps 8 and 12 idle until the epilogue): tcgen05.mma M=128, N=padded batch, K=16, f32 accumulator in TMEM
+//   warps 4,8,12 MMA issuers (scheduler partition 0, like the producer): one thread each (three
+//               for narrow batches, else one), k blocks round-robin, own accumulators; tcgen05.mma
+//               M=128, N=padded batch, K=16, f32 accumulators in TMEM summed by the epilogue
 // (The weights cannot be handed over as f16, which would convert in half the instructions: an
 // instruction descriptor with A in f16 and B in bf16 is rejected as an illegal instruction.)
 // Every mbarrier wait is bounded; a stalled wait raises the abort flag, all roles leave their
@@ -41,6 +43,7 @@ struct WqParams {
   int stages;    // depth of the {raw W, x} ring
   int conv_stages;   // depth of the converted-tile ring
   int tmem_cols;
+  int issuers;   // threads issuing MMAs (1 or 2, alternate k blocks)
   int nacc;      // accumulators used round-robin by consecutive MMAs (summed in the epilogue)
 };
 
@@ -97,7 +100,7 @@ wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     for (int c = 0; c < p.conv_stages; ++c) { mbar_init(conv0 + 8 * c, 4); mbar_init(wbe0 + 8 * c, 1); }
-    mbar_init(acc_full, 1);
+    mbar_init(acc_full, p.issuers);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -109,6 +112,45 @@ wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+
+  // MMA issue by one thread each of up to three warps (4, 8, 12) that take the k blocks round-robin.
+  // With a narrow N an MMA is a few cycles of tensor work, so the rate at which a single thread can
+  // issue them (and commit the stages back) paces the kernel; more issuers, each with its own
+  // accumulators, raise it.
+  auto issue_mmas = [&](int which) {
+    // bf16 x bf16 -> f32, both operands K-major, M = 128 channels, N = padded batch
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mb >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+    const int step = p.issuers;
+    const int my_acc = p.nacc / p.issuers;
+    const uint32_t acc0 = tmem_base + (uint32_t)(which * my_acc * p.mb), acc_end = acc0 + (uint32_t)(my_acc * p.mb);
+    uint32_t acc = acc0;
+    int fresh = my_acc;                       // accumulators not written yet
+    int s = which % p.stages, c = which % p.conv_stages;
+    uint32_t cph = (uint32_t)((which / p.conv_stages) & 1);
+    bool ok = true;
+    for (int kb = which; kb < kblocks; kb += step) {
+      // the converters arrive on conv only after the stage's TMA data (x included) has landed
+      if (!mbar_wait(conv0 + 8 * c, cph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint64_t adesc = make_desc(wb0 + (uint32_t)c * WQ_WB), bdesc = make_desc(base + (uint32_t)s * stage_bytes + WQ_RAW);
+      // consecutive MMAs go to different accumulators: accumulating into the columns the
+      // previous one is still writing would serialise them on the pipeline's latency
+#pragma unroll
+      for (int k4 = 0; k4 < 4; ++k4) {
+        tc_mma(acc, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, fresh > 0 ? 0u : 1u, false);
+        if (fresh > 0) --fresh;
+        acc += (uint32_t)p.mb;
+        if (acc == acc_end) acc = acc0;
+      }
+      tc_commit(empty0 + 8 * s);
+      tc_commit(wbe0 + 8 * c);
+      s += step;
+      while (s >= p.stages) s -= p.stages;
+      c += step;
+      while (c >= p.conv_stages) { c -= p.conv_stages; cph ^= 1; }
+    }
+    if (ok) tc_commit(acc_full);
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -124,43 +166,11 @@ wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       }
     }
   } else if (warp == WQ_MMA_WARP) {
-    if (lane == 0) {
-      // bf16 x bf16 -> f32, both operands K-major, M = 128 channels, N = padded batch
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.mb >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-      // This single thread is the critical path when N is narrow (an MMA is a few cycles of
-      // work), so its loop carries running descriptors, barrier addresses and accumulator
-      // offsets instead of recomputing them.
-      const uint64_t adesc0 = make_desc(wb0), bdesc0 = make_desc(base + WQ_RAW);
-      const uint64_t astep = (uint64_t)(WQ_WB >> 4), bstep = (uint64_t)(stage_bytes >> 4);
-      uint64_t adesc = adesc0, bdesc = bdesc0;
-      uint32_t conv_bar = conv0, wbe_bar = wbe0, empty_bar = empty0;
-      uint32_t acc = tmem_base;
-      const uint32_t acc_end = tmem_base + (uint32_t)(p.nacc * p.mb);
-      int s = 0, c = 0, fresh = p.nacc;       // `fresh` accumulators have not been written yet
-      uint32_t cph = 0;
-      bool ok = true;
-      for (int kb = 0; kb < kblocks; ++kb) {
-        // the converters arrive on conv only after the stage's TMA data (x included) has landed
-        if (!mbar_wait(conv_bar, cph, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        // consecutive MMAs go to different accumulators: accumulating into the columns the
-        // previous one is still writing would serialise them on the pipeline's latency
-#pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4) {
-          tc_mma(acc, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, fresh > 0 ? 0u : 1u, false);
-          if (fresh > 0) --fresh;
-          acc += (uint32_t)p.mb;
-          if (acc == acc_end) acc = tmem_base;
-        }
-        tc_commit(empty_bar);
-        tc_commit(wbe_bar);
-        adesc += astep; bdesc += bstep; conv_bar += 8; wbe_bar += 8; empty_bar += 8;
-        if (++s == p.stages) { s = 0; bdesc = bdesc0; empty_bar = empty0; }
-        if (++c == p.conv_stages) { c = 0; cph ^= 1; adesc = adesc0; conv_bar = conv0; wbe_bar = wbe0; }
-      }
-      if (ok) tc_commit(acc_full);
-    }
+    if (lane == 0) issue_mmas(0);
   } else {
+    // warps 8 and 12 are the second and third issuer when the launch asks for them
+    if ((warp & 3) == 0 && (warp >> 2) - 1 < p.issuers && lane == 0) issue_mmas((warp >> 2) - 1);
+    __syncwarp();
     // The converter warps are the twelve outside scheduler partition 0 (where the producer and
     // the MMA issuer live: a single thread issuing MMAs loses most of its issue slots to busy
     // warps on the same scheduler).  Three groups of four warps take the k blocks round-robin,
@@ -294,7 +304,13 @@ void launch_wq_linear(const GemmArgs& g, int* status_word, cudaStream_t stream) 
   p.conv_stages = cs_env ? std::max(2, std::min(WQ_MAX_CONV_STAGES, atoi(cs_env))) : (p.mb <= 64 ? 8 : 4);
   p.stages = std::min(WQ_MAX_STAGES, (WQ_SMEM_LIMIT - p.conv_stages * WQ_WB) / stage);
   const int kblocks = (p.k + 63) / 64;
-  p.nacc = std::max(1, std::min(std::min(8, 512 / p.mb), kblocks * 4));
+  // narrow batches are bound by the rate at which MMAs can be issued: up to three issuing threads
+  const char* iss_env = getenv("NXB200_WQ_ISSUERS");
+  p.issuers = iss_env ? std::max(1, std::min(3, atoi(iss_env))) : (p.mb <= 64 ? 3 : 1);
+  p.issuers = std::min(p.issuers, std::max(1, kblocks));
+  p.issuers = std::min(p.issuers, 512 / p.mb);          // one accumulator each must fit the 512 TMEM columns
+  const int per_issuer = std::max(1, std::min(std::min(8, 512 / p.mb) / p.issuers, 4));
+  p.nacc = per_issuer * p.issuers;
   p.tmem_cols = 32;
   while (p.tmem_cols < p.nacc * p.mb) p.tmem_cols *= 2;
   CUtensorMap mw = wq_map(g.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.k, g.n, g.ldb, 128, CU_TENSOR_MAP_SWIZZLE_64B);
