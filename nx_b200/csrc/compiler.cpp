@@ -167,6 +167,29 @@ private:
   std::vector<std::map<std::string, std::string>> elem_memo_;
   std::map<std::string, std::pair<std::string, int>> cached_loads_;
   std::set<int> used_vars_;
+  // Register reuse across phases of a row kernel.  A transcendental value needed again in a later
+  // phase (exp(x - max) for the softmax division) would be recomputed there, because the row's 32
+  // registers per thread hold x.  When x itself is not needed after the producing phase, the value
+  // is written over x at the end of that phase and read from there later.  A planning pass (a
+  // throw-away copy of the builder) records where every cached row load is referenced and under
+  // which candidate values; the real pass then follows the plan.
+  bool planning_ = false;
+  struct Stash { std::string array; int phase; };
+  std::map<std::string, Stash> stash_plan_;                       // value key -> where it is kept
+  std::vector<std::string> ctx_;                                  // candidate values being generated
+  std::vector<std::set<std::string>> dep_stack_;                  // cached loads each open value depends on
+  std::map<std::string, std::set<std::string>> deps_;             // per phase-qualified memo key
+  struct LoadRef { int phase; std::set<std::string> ctx; };
+  std::map<std::string, std::vector<LoadRef>> load_refs_;         // cached load key -> references
+  std::map<std::string, std::set<int>> emitted_in_;               // candidate key -> phases that computed it
+  std::map<std::string, std::string> load_array_;                 // cached load key -> register array name
+  std::map<std::string, DType> load_type_;
+  void note_load(const std::string& key) {
+    if (!planning_) return;
+    LoadRef r{phase_, std::set<std::string>(ctx_.begin(), ctx_.end())};
+    load_refs_[key].push_back(r);
+    for (auto& d : dep_stack_) d.insert(key);
+  }
   // 16-bit float values that are still held at f32 precision ("excess precision", what XLA does
   // inside a fusion by default): arithmetic consumes them as they are; comparisons, index
   // reductions, integer conversions and rounding ops first round them to their declared type.
@@ -423,7 +446,10 @@ KernelBuilder::Val KernelBuilder::load(int n, const std::vector<Aff>& idx) {
           pre_sec_[phase_] += "          ld_vec<" + S + ", " + std::to_string(V_) + ">(" + p + " + " + affstr(addr, true) + ", " + v + "[ch]);\n";
         }
         it = cached_loads_.emplace(key, std::make_pair(v, phase_)).first;
+        load_array_[key] = v;
+        load_type_[key] = nd.dt;
       }
+      note_load(key);
       return {it->second.first + "[ch][v]", true};
     }
     auto& memo = elem_memo_[phase_];
@@ -484,8 +510,28 @@ KernelBuilder::Val KernelBuilder::value(int n, const std::vector<Aff>& idx) {
   auto rit = row_memo_.find(key);
   if (rit != row_memo_.end()) return {rit->second, false};
   auto eit = elem_memo_[phase_].find(key);
-  if (eit != elem_memo_[phase_].end()) return {eit->second, true};
+  if (eit != elem_memo_[phase_].end()) {
+    if (planning_) {
+      // a second consumer of a memoised value: its row loads are referenced again, in this context
+      for (auto& l : deps_[std::to_string(phase_) + "/" + key]) note_load(l);
+    }
+    return {eit->second, true};
+  }
+  {
+    auto sp = stash_plan_.find(key);
+    if (sp != stash_plan_.end() && phase_ > sp->second.phase) return {sp->second.array + "[ch][v]", true};
+  }
+  const bool candidate = mode_ == ROW && cache_ && nd.dt == NXB_F32 && kUnaryMath.count(nd.op) && idxkey(idx) == idxkey(full_index());
+  if (planning_) {
+    dep_stack_.emplace_back();
+    if (candidate) ctx_.push_back(key);
+  }
   Val v = emit_op(n, idx);
+  if (planning_) {
+    if (candidate) { ctx_.pop_back(); if (v.elem) emitted_in_[key].insert(phase_); }
+    deps_[std::to_string(phase_) + "/" + key] = dep_stack_.back();
+    dep_stack_.pop_back();
+  }
   if (v.elem) elem_memo_[phase_][key] = v.v;
   else row_memo_[key] = v.v;
   return v;
@@ -908,6 +954,32 @@ void KernelBuilder::configure() {
 }
 
 KernelSpec KernelBuilder::build(const std::string& name) {
+  if (!planning_ && mode_ == ROW && !getenv("NXB200_NO_REGISTER_REUSE")) {
+    KernelBuilder probe(*this);
+    probe.planning_ = true;
+    probe.build(name);
+    // a value computed in phase p and again later, and a row-register array of the same type that
+    // nothing else reads after p: keep the value there
+    std::set<std::string> taken;
+    for (auto& e : probe.emitted_in_) {
+      if (e.second.size() < 2) continue;
+      const int p = *e.second.begin();
+      for (auto& lr : probe.load_refs_) {
+        const std::string& lk = lr.first;
+        if (taken.count(lk) || probe.load_type_[lk] != NXB_F32) continue;
+        bool ok = false, clean = true;
+        for (auto& r : lr.second) {
+          if (r.phase <= p) { if (r.phase == p && r.ctx.count(e.first)) ok = true; continue; }
+          if (!r.ctx.count(e.first)) clean = false;       // someone else still needs the row value later
+        }
+        if (ok && clean) {
+          stash_plan_[e.first] = Stash{probe.load_array_[lk], p};
+          taken.insert(lk);
+          break;
+        }
+      }
+    }
+  }
   for (int n : stores) produced.insert(n);
   for (int sl : seed_args) param(sl);
   configure();
@@ -995,6 +1067,13 @@ KernelSpec KernelBuilder::build(const std::string& name) {
     if (ret_node >= 0) {
       Val r = value(ret_node, full_index());
       lane_sec_[0] += "        result = " + cvt(r.v, g_.nodes[ret_node].dt, NXB_F32) + ";\n";
+    }
+    // values kept for later phases overwrite the row registers they outlive (last statement of the phase)
+    for (auto& sp : stash_plan_) {
+      if (sp.second.phase != phase_) continue;
+      auto it = elem_memo_[phase_].find(sp.first);
+      if (it == elem_memo_[phase_].end()) throw FusionError("internal: planned value was not generated in its phase");
+      lane_sec_[phase_] += "        " + sp.second.array + "[ch][v] = " + it->second + ";\n";
     }
   }
   // finish the reductions of each phase together: one pair of barriers per phase

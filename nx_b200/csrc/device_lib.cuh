@@ -113,8 +113,10 @@ NXB_DEV float nx_exp(float x) {
   // p is 0 or inf at the ends of the range (and for infinite x, where c is NaN): return it as is
   return (p == 0.f || p == NXB_INF) ? p : r;
 }
-// 1 / (1 + exp(-x)); rcp.approx is within 1 ulp
-NXB_DEV float nx_sigmoid(float x) { return fast_rcp(1.f + nx_exp(-x)); }
+// 1 / (1 + exp(-x)); rcp.approx is within 1 ulp.  The exponential here needs no compensated
+// product: its relative error (|x| log2(e) 2^-24 + 2 ulp of ex2, < 8e-6 over the finite range) only
+// matters where it dominates the sum, and ex2's own 0 / inf ends give the right limits.
+NXB_DEV float nx_sigmoid(float x) { return fast_rcp(1.f + fast_ex2(x * -1.44269502162933349609375f)); }
 // tanh: odd polynomial near 0 (keeps relative accuracy), 1 - 2/(exp(2|x|)+1) elsewhere
 NXB_DEV float nx_tanh(float x) {
   const float ax = fabsf(x);
@@ -124,7 +126,7 @@ NXB_DEV float nx_tanh(float x) {
   p = fmaf(p, x2, 0.133333333f);          // 2/15
   p = fmaf(p, x2, -0.333333333f);         // -1/3
   const float small = fmaf(p * x2, x, x);
-  const float e = nx_exp(2.f * ax);
+  const float e = fast_ex2(ax * 2.8853900432586669921875f);     // exp(2|x|): an error of 1e-5 in e moves the result by < 5e-6 of it
   float big = fmaf(-2.f, fast_rcp(e + 1.f), 1.f);
   big = copysignf(big, x);
   return (ax < 0.12f) ? small : big;

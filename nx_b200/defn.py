@@ -137,6 +137,12 @@ def trace(fun, templates):
     """Run ``fun`` with parameter nodes in place of its tensor arguments
     (nx/lib/nx/defn/compiler.ex:184-205, :890-917) and return
     ``(flat_outputs, output_spec)``."""
+    outs, ospec, _ = _trace(fun, templates)
+    return outs, ospec
+
+
+def _trace(fun, templates):
+    """`trace` plus the parameter nodes (the serialiser keeps the unused ones)."""
     flat = []
     spec = [_flatten(t, flat) for t in templates]
     params = [E.parameter(t.type, t.shape, i) for i, t in enumerate(flat)]
@@ -147,8 +153,7 @@ def trace(fun, templates):
         outs = []
         ospec = _flatten(result, outs)
         outs = [B.to_expr(o) for o in outs]
-    trace.params = params          # of the latest trace (the serialiser keeps unused ones)
-    return outs, ospec
+    return outs, ospec, params
 
 
 def __compile__(key, templates, fun, opts):
@@ -162,10 +167,10 @@ def __compile__(key, templates, fun, opts):
     with _cache_lock:
         entry = _cache.get(ck)
     if entry is None:
-        outs, ospec = trace(fun, templates)
+        outs, ospec, params = _trace(fun, templates)
         # outputs that are parameters or constants still need a buffer of
         # their own: results are always fresh tensors (exla/lib/exla/defn.ex:387-393)
-        blob = E.serialize(outs, trace.params)
+        blob = E.serialize(outs, params)
         entry = (Program(blob), ospec)
         with _cache_lock:
             _cache.setdefault(ck, entry)
@@ -238,8 +243,8 @@ def build_program(fun, templates):
     """Trace ``fun`` and return ``(serialised_graph, output_spec)`` without
     touching the native library (used by tests of the front-end and by the
     oracle, which interprets the same bytes)."""
-    outs, ospec = trace(fun, list(templates))
-    return E.serialize(outs, trace.params), ospec
+    outs, ospec, params = _trace(fun, list(templates))
+    return E.serialize(outs, params), ospec
 
 
 
