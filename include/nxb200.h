@@ -107,6 +107,10 @@ int nxb200_buffer_release(nxb200_buffer *buf);
  *           u16 nflts,  f64 flts[nflts]
  *           u64 bloblen, blob[bloblen]                   (literal data of a :tensor node)
  *   u32 n_outputs, u32 output[n_outputs]
+ *   optional: u32 n_donated, (u32 parameter, u32 output)[n_donated]   buffer donation
+ *             (Nx.donatable, exla/lib/exla/defn.ex:598-645): nxb200_program_run hands the
+ *             argument's memory to that result (or releases it) and the argument handle
+ *             becomes deallocated; nxb200_program_run_into consumes nothing
  *
  * Attributes: parameter [index]; constant ints=[v] (integer types) or
  * flts=[v]; iota [axis|-1]; sum/product/reduce_max/reduce_min/all/any

@@ -135,10 +135,21 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         b->dtype = sl.dt;
         b->dims = sl.shape;
         b->nbytes = sl.nbytes;
-        b->ptr = d.alloc.alloc(sl.nbytes);
+        // a result that takes over a donated argument's buffer is written straight into it
+        void* taken = nullptr;
+        for (auto& al : plan.aliases)
+          if (al.output == i && al.in_place && !args[al.param]->deallocated.load()) taken = args[al.param]->ptr;
+        b->ptr = taken ? taken : d.alloc.alloc(sl.nbytes);
         ptr[plan.output_slots[i]] = b->ptr;
         made.push_back(b.release());
       }
+    }
+    // a window update whose result does not share the argument's memory starts from a copy of it
+    for (auto& al : plan.aliases) {
+      if (!al.window) continue;
+      void* dst = ptr[plan.output_slots[al.output]];
+      if (dst != args[al.param]->ptr)
+        NXB_CUDA(cudaMemcpyAsync(dst, args[al.param]->ptr, plan.slots[plan.output_slots[al.output]].nbytes, cudaMemcpyDeviceToDevice, d.stream));
     }
     const DriverApi& drv = driver();
     // Runs the plan's steps on the device's stream.  With `held` the temporaries are kept (their
@@ -332,13 +343,27 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
     }
     if (!done) run_steps(nullptr);
   } catch (...) {
-    for (auto* b : made) { d.alloc.free(b->ptr); delete b; }
+    for (auto* b : made) {
+      bool taken = false;
+      for (int i = 0; i < n_args; ++i) if (args[i]->ptr == b->ptr) taken = true;
+      if (!taken) d.alloc.free(b->ptr);
+      delete b;
+    }
     for (size_t s = 0; s < plan.slots.size(); ++s)
       if (plan.slots[s].kind == Slot::TEMP && ptr[s]) d.alloc.free(ptr[s]);
     throw;
   }
-  if (!outs_provided)
+  if (!outs_provided) {
     for (int i = 0; i < n_outs; ++i) outs[i] = made[i];
+    // donated arguments are consumed: their memory now belongs to a result, or goes back to the
+    // pool (the stream orders any reuse after this program's kernels)
+    for (auto& al : plan.aliases) {
+      nxb200_buffer* a = args[al.param];
+      if (a->deallocated.exchange(true)) continue;
+      if (!(al.in_place && made[al.output]->ptr == a->ptr)) d.alloc.free(a->ptr);
+      a->ptr = nullptr;
+    }
+  }
 }
 
 }  // namespace

@@ -173,6 +173,8 @@ private:
   // is written over x at the end of that phase and read from there later.  A planning pass (a
   // throw-away copy of the builder) records where every cached row load is referenced and under
   // which candidate values; the real pass then follows the plan.
+  std::map<int, bool> ident_loads_;      // read slot -> all loads so far were at the thread's own position
+  std::set<int> ident_stores_;           // written slots stored at the thread's own position
   bool planning_ = false;
   struct Stash { std::string array; int phase; };
   std::map<std::string, Stash> stash_plan_;                       // value key -> where it is kept
@@ -412,6 +414,14 @@ KernelBuilder::Val KernelBuilder::load(int n, const std::vector<Aff>& idx) {
   }
   const std::string S = storage_type(nd.dt), Rt = reg_type(nd.dt);
   std::string p = param(nd.slot);
+  {
+    // donation: a slot may be overwritten in place only if every load of it is at the position
+    // the loading thread itself stores to (the flat index of the kernel's space)
+    const bool ident = !addr.opaque && addr.c == 0 && addr.k == cstrides(F_) && shape_numel(nd.shape) == numel_;
+    auto it = ident_loads_.find(nd.slot);
+    if (it == ident_loads_.end()) ident_loads_[nd.slot] = ident;
+    else it->second = it->second && ident;
+  }
   std::string key = "L" + std::to_string(nd.slot) + ":" + affkey(addr);
   bool cdep = col_dep(addr);
   if (mode_ == ROW && !cdep) {
@@ -895,20 +905,32 @@ void KernelBuilder::emit_store(int n) {
     addr.c += idx[j].c * st[j];
     for (int q = 0; q < nv_; ++q) addr.k[q] += idx[j].k[q] * st[j];
   }
+  if (full && addr.c == 0 && addr.k == cstrides(F_) && shape_numel(nd.shape) == numel_ && nd.window_axes.empty()) ident_stores_.insert(nd.slot);
+  std::string dyn;       // offset of a window whose position is held in scalar tensors
+  bool dyn_aligned = true;
+  for (size_t i = 0; i < nd.window_axes.size(); ++i) {
+    Val sv = value(nd.args[1 + i], {});
+    // (per element, with scalar stores: a window is small next to the tensor it lands in)
+    std::string o = newvar("wo");
+    stmt(true, "const " + idx_t() + " " + o + " = (" + idx_t() + ")nx_clamp_index(" + sv.v + ", (long long)" + std::to_string(nd.window_limit[i]) + ") * (" +
+                   idx_t() + ")" + std::to_string(st[nd.window_axes[i]]) + ";");
+    dyn += " + " + o;
+    dyn_aligned = false;
+  }
   if (mode_ == ROW && !full) {
     // one value per row: lane 0 of the row writes it
     row_sec_[phase_] += "        if (tid == 0) st1<" + S + ">(" + p + " + " + affstr(addr, false) + ", " + v.v + ");\n";
     return;
   }
-  bool aligned = addr.c % V_ == 0 && addr.k[nv_ - 1] == 1;
+  bool aligned = addr.c % V_ == 0 && addr.k[nv_ - 1] == 1 && dyn_aligned;
   for (int j = 0; j < nv_ - 1; ++j) if (F_[j] != 1 && addr.k[j] % V_ != 0) aligned = false;
   if (V_ > 1 && aligned) {
     std::string sv = newvar("st");
     pre_sec_[phase_] += "          " + Rt + " " + sv + "[" + std::to_string(V_) + "];\n";
     lane_sec_[phase_] += "        " + sv + "[v] = " + v.v + ";\n";
-    post_sec_[phase_] += "          st_vec<" + S + ", " + std::to_string(V_) + ">(" + p + " + " + affstr(addr, true) + ", " + sv + ");\n";
+    post_sec_[phase_] += "          st_vec<" + S + ", " + std::to_string(V_) + ">(" + p + " + " + affstr(addr, true) + dyn + ", " + sv + ");\n";
   } else {
-    lane_sec_[phase_] += "        st1<" + S + ">(" + p + " + " + affstr(addr, false) + ", " + v.v + ");\n";
+    lane_sec_[phase_] += "        st1<" + S + ">(" + p + " + " + affstr(addr, false) + dyn + ", " + v.v + ");\n";
   }
 }
 
@@ -1279,6 +1301,12 @@ KernelSpec KernelBuilder::build(const std::string& name) {
   ks.block = (unsigned)block_;
   ks.arg_slots = arg_slots_;
   ks.arg_offsets.assign(arg_slots_.size(), 0);
+  for (int sl : arg_slots_) if (is_written(sl)) ks.written_slots.push_back(sl);
+  if (mode_ == EW || (mode_ == ROW && cache_)) {
+    // (a row kernel that re-reads its input in later phases would see its own results)
+    for (auto& kv : ident_loads_) if (kv.second) ks.inplace_ok.push_back(kv.first);
+    for (int sl : ident_stores_) ks.inplace_ok.push_back(-1 - sl);      // negative: written at the thread's own position
+  }
   int64_t nblocks;
   if (mode_ == EW) nblocks = (numel_ / V_ + block_ - 1) / block_;
   else nblocks = (R_ + rpc_ - 1) / rpc_;
@@ -1402,6 +1430,8 @@ std::string Plan::describe() const {
     else if (st.kind == Step::ATTENTION) o << attentions[st.index].desc << "\n";
     else o << collectives[st.index].desc << "\n";
   }
+  for (auto& a : aliases)
+    o << "donation: argument " << a.param << " -> result " << a.output << (a.in_place ? " (written in place)" : " (own buffer; the argument is released after the run)") << "\n";
   return o.str();
 }
 
@@ -1466,12 +1496,49 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       }
     }
   }
+  // put_slice into a donated argument that nothing else reads: only the window is written, the
+  // rest of the result is the argument's own memory (an update of a KV cache costs O(slice))
+  std::set<int> window_outputs;
+  if (!getenv("NXB200_NO_WINDOW_UPDATE")) {
+    std::vector<int> uses(g.nodes.size(), 0);
+    for (auto& nd : g.nodes) for (int a : nd.args) uses[a]++;
+    for (int o : g.outputs) uses[o]++;
+    for (auto& al : g.aliases) {
+      const int o = g.outputs[al.second];
+      Node& nd = g.nodes[o];
+      if (nd.op != "put_slice" || uses[o] != 1) continue;
+      const int p = nd.args[0];
+      if (g.nodes[p].op != "parameter" || g.nodes[p].ints.at(0) != al.first || uses[p] != 1 || g.nodes[p].dt != nd.dt) continue;
+      const int piece = nd.args[1];
+      Node w;
+      w.op = g.nodes[piece].dt == nd.dt ? "copy" : "as_type";
+      w.dt = nd.dt;
+      w.shape = g.nodes[piece].shape;
+      w.args = {piece};
+      w.piece_of = o;
+      w.out_strides = cstrides(nd.shape);
+      w.out_offset = 0;
+      for (size_t j = 0; j < nd.shape.size(); ++j) {
+        if (w.shape[j] == nd.shape[j]) continue;           // the piece spans the axis: start is 0
+        w.window_axes.push_back((int)j);
+        w.window_limit.push_back(nd.shape[j] - w.shape[j] + 1);
+        w.args.push_back(nd.args[2 + j]);
+      }
+      g.nodes.push_back(w);
+      Node& out = g.nodes[o];
+      out.op = "concatenate";
+      out.ints = {0};
+      out.args = {(int)g.nodes.size() - 1};
+      window_outputs.insert(al.second);
+    }
+  }
   // concatenate: every input becomes a "piece" node that is written straight into its
   // slice of the result (inputs converted to the result type, exla/lib/exla/defn.ex:1659-1668)
   {
     size_t n0 = g.nodes.size();
     for (size_t n = 0; n < n0; ++n) {
       if (g.nodes[n].op != "concatenate") continue;
+      if (g.nodes[n].args.size() == 1 && g.nodes[g.nodes[n].args[0]].piece_of == (int)n) continue;    // a window update (above)
       const int axis = (int)g.nodes[n].ints.at(0);
       const std::vector<int64_t> pst = cstrides(g.nodes[n].shape);
       int64_t off = 0;
@@ -2050,6 +2117,55 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       // retry without cross-reduction fusion
       for (int n = 0; n < N; ++n) if (g.nodes[n].live && is_reduce(g.nodes[n])) P.mat[n] = 1;
     }
+  }
+
+  // ---- buffer donation: which results may be written straight into their donated argument ----
+  Plan& pl = *plan;
+  for (auto& al : pl.g.aliases) {
+    Plan::Alias a{al.first, al.second, false};
+    if (window_outputs.count(al.second)) {
+      a.in_place = a.window = true;
+      pl.aliases.push_back(a);
+      continue;
+    }
+    const int sp = pl.param_slots[a.param], so = pl.output_slots[a.output];
+    if (sp >= 0 && so >= 0 && sp != so && pl.slots[so].kind == Slot::OUTPUT) {
+      // every reader of the argument, and the writer of the result
+      int readers = 0, writer = -1;
+      bool other = false;
+      for (size_t st = 0; st < pl.steps.size(); ++st) {
+        const Step& step = pl.steps[st];
+        if (step.kind == Step::KERNEL) {
+          const KernelSpec& ks = pl.kernels[step.index];
+          const bool reads = std::count(ks.arg_slots.begin(), ks.arg_slots.end(), sp) > 0;
+          const bool writes = std::count(ks.written_slots.begin(), ks.written_slots.end(), so) > 0;
+          if (reads) ++readers;
+          if (writes) writer = (int)st;
+          if (reads && !writes) other = true;
+        } else if (step.kind == Step::GEMM) {
+          const GemmSpec& gs = pl.gemms[step.index];
+          if (gs.a.slot == sp || gs.b.slot == sp || gs.scale_slot == sp || gs.out_slot == so) other = true;
+          if (gs.jit_kernel >= 0) {
+            const KernelSpec& ks = pl.kernels[gs.jit_kernel];
+            if (std::count(ks.arg_slots.begin(), ks.arg_slots.end(), sp) || std::count(ks.arg_slots.begin(), ks.arg_slots.end(), so)) other = true;
+          }
+        } else if (step.kind == Step::ATTENTION) {
+          const AttentionSpec& as = pl.attentions[step.index];
+          const KernelSpec& ks = pl.kernels[as.jit_kernel];
+          if (as.q_slot == sp || as.k_slot == sp || as.v_slot == sp || as.out_slot == so || std::count(ks.arg_slots.begin(), ks.arg_slots.end(), sp)) other = true;
+        } else {
+          const CollectiveSpec& cs = pl.collectives[step.index];
+          if (cs.in_slot == sp || cs.out_slot == so) other = true;
+        }
+      }
+      if (!other && readers == 1 && writer >= 0) {
+        const KernelSpec& ks = pl.kernels[pl.steps[writer].index];
+        const bool rd = std::count(ks.inplace_ok.begin(), ks.inplace_ok.end(), sp) > 0;
+        const bool wr = std::count(ks.inplace_ok.begin(), ks.inplace_ok.end(), -1 - so) > 0;
+        a.in_place = rd && wr && pl.slots[sp].nbytes == pl.slots[so].nbytes;
+      }
+    }
+    pl.aliases.push_back(a);
   }
 
   for (auto& ks : plan->kernels) ks.cubin = compile_to_cubin(ks.source, ks.name, ks.tensor_core, ks.attention);

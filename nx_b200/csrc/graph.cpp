@@ -76,6 +76,15 @@ Graph parse_graph(const uint8_t* bytes, size_t nbytes) {
     if (o >= n) fail(NXB_ERR_INVALID_ARGUMENT, "output index out of range");
     g.outputs.push_back((int)o);
   }
+  // optional: buffer donation, (parameter index, output index) pairs
+  if (r.pos < nbytes) {
+    uint32_t na = r.get<uint32_t>();
+    for (uint32_t i = 0; i < na; ++i) {
+      uint32_t p = r.get<uint32_t>(), o = r.get<uint32_t>();
+      if ((int)p >= g.n_params || o >= no) fail(NXB_ERR_INVALID_ARGUMENT, "donation pair out of range");
+      g.aliases.push_back({(int)p, (int)o});
+    }
+  }
   return g;
 }
 

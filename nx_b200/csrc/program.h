@@ -22,6 +22,10 @@ struct Node {
   int piece_of = -1;
   int64_t out_offset = 0;
   std::vector<int64_t> out_strides;
+  // a piece written at a position given by scalar tensors (put_slice into a donated buffer):
+  // window_axes[i] is the axis whose start is args[1 + i], clamped into [0, window_limit[i] - 1]
+  std::vector<int> window_axes;
+  std::vector<int64_t> window_limit;
   // dot only: node holding a per-output-column f32 factor applied to the product (-1: none)
   int scale_arg = -1;
 };
@@ -30,6 +34,7 @@ struct Graph {
   std::vector<Node> nodes;
   std::vector<int> outputs;
   int n_params = 0;
+  std::vector<std::pair<int, int>> aliases;   // donated (parameter index, output index) pairs
 };
 
 Graph parse_graph(const uint8_t* bytes, size_t nbytes);
@@ -49,6 +54,9 @@ struct KernelSpec {
   unsigned grid = 1, block = 1, smem = 0;
   std::vector<int> arg_slots;     // one pointer argument per entry
   std::vector<size_t> arg_offsets;  // byte offset added to the slot's base pointer
+  std::vector<int> written_slots;   // slots this kernel stores to
+  std::vector<int> inplace_ok;      // read slots whose every load is at the loading thread's own position
+                                    // (s >= 0), and written slots stored there (encoded -1 - s)
   bool tensor_core = false;       // a generated matrix-product kernel (needs the GEMM device source)
   bool attention = false;         // ... and the attention device source
 };
@@ -108,6 +116,14 @@ struct Plan {
   std::vector<AttentionSpec> attentions;
   std::vector<int> param_slots;   // by parameter index (-1 when unused)
   std::vector<int> output_slots;  // by output index
+  // Buffer donation (Nx.donatable, exla/lib/exla/defn.ex:598-645): the result takes over the
+  // argument's buffer.  `in_place`: the result is written straight into the argument's memory
+  // (its only reader is the kernel that writes the result, at each thread's own positions);
+  // otherwise the result gets memory of its own and the argument's is released after the run.
+  // `window`: the program writes only a window of the result (put_slice); the rest of it is the
+  // argument's data, so a result that does not share the argument's memory is first copied from it.
+  struct Alias { int param, output; bool in_place; bool window = false; };
+  std::vector<Alias> aliases;
   std::string describe() const;
 };
 

@@ -162,7 +162,9 @@ def __compile__(key, templates, fun, opts):
     flat = []
     for t in templates:
         _flatten(t, flat)
-    args_key = tuple((t.type, t.shape) for t in flat)
+    # the donation marks are part of the key: a donating call must not reuse the
+    # non-donating executable (exla/lib/exla/defn.ex:337-353)
+    args_key = tuple((t.type, t.shape, bool(getattr(t, "donatable", False))) for t in flat)
     ck = (key, args_key, opts.get("device"))
     with _cache_lock:
         entry = _cache.get(ck)
@@ -170,7 +172,8 @@ def __compile__(key, templates, fun, opts):
         outs, ospec, params = _trace(fun, templates)
         # outputs that are parameters or constants still need a buffer of
         # their own: results are always fresh tensors (exla/lib/exla/defn.ex:387-393)
-        blob = E.serialize(outs, params)
+        donated = [i for i, t in enumerate(flat) if getattr(t, "donatable", False)]
+        blob = E.serialize(outs, params, alias_pairs(donated, params, outs))
         entry = (Program(blob), ospec)
         with _cache_lock:
             _cache.setdefault(ck, entry)
@@ -187,6 +190,24 @@ def __compile__(key, templates, fun, opts):
 
     runner.program = prog
     return runner
+
+
+def alias_pairs(donated, params, outs):
+    """(parameter, output) pairs for the donated parameters: each takes the first output of its
+    type and shape that no earlier donation took (exla/lib/exla/defn.ex:598-645)."""
+    reachable = {t.data.id for t in E.topo_order(outs)[0]}
+    pairs, used = [], set()
+    for i in donated:
+        p = params[i]
+        if p.data.id not in reachable:
+            raise ValueError("argument marked for donation is not used by the computation; only used inputs can be donated")
+        j = next((j for j, o in enumerate(outs) if j not in used and o.type == p.type and o.shape == p.shape), None)
+        if j is None:
+            raise ValueError(f"input marked for donation has no output with matching shape {p.shape} and type "
+                             f"{T.short(p.type)}; cannot alias this argument")
+        used.add(j)
+        pairs.append((i, j))
+    return pairs
 
 
 def __jit__(key, templates, fun, args_list, opts):

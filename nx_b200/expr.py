@@ -271,7 +271,7 @@ def topo_order(outputs):
     return order, seen
 
 
-def serialize(outputs, params=None):
+def serialize(outputs, params=None, aliases=None):
     """Flatten the DAG reachable from ``outputs`` (a list of tensors whose data
     are Expr nodes) into the program wire format.  ``params`` (the function's
     parameter nodes) are written even when no output depends on them, so that
@@ -297,4 +297,9 @@ def serialize(outputs, params=None):
         buf += struct.pack("<Q", len(e.blob)) + e.blob
     buf += struct.pack("<I", len(outputs))
     buf += struct.pack(f"<{len(outputs)}I", *[index[t.data.id] for t in outputs])
+    if aliases:
+        # buffer donation: (parameter index, output index) pairs, the result takes over the argument's memory
+        buf += struct.pack("<I", len(aliases))
+        for p, o in aliases:
+            buf += struct.pack("<II", p, o)
     return bytes(buf)

@@ -28,10 +28,11 @@ from . import types as T
 class Tensor:
     """``%Nx.Tensor{data, type, shape}`` (nx/lib/nx/tensor.ex:41-42).  ``data``
     is an `expr.Expr` node, a `backend.DeviceBuffer`, or a `HostData`."""
-    __slots__ = ("data", "type", "shape")
+    __slots__ = ("data", "type", "shape", "donatable")
 
-    def __init__(self, data, type, shape):
+    def __init__(self, data, type, shape, donatable=False):
         self.data, self.type, self.shape = data, type, tuple(int(d) for d in shape)
+        self.donatable = donatable      # %Nx.Tensor{donatable?: ...} (nx/lib/nx/tensor.ex:41-42)
 
     @property
     def rank(self):
@@ -119,6 +120,23 @@ def tensor(value, type=None):
         with np.errstate(invalid="ignore"):
             raw = np.ascontiguousarray(arr).astype(_NP[type]).tobytes()
     return from_binary(raw, type, arr.shape)
+
+
+def donatable(t):
+    """``Nx.donatable/1`` (nx/lib/nx.ex:1064-1068): marks a tensor (or every tensor of a tuple /
+    list / dict) as one whose buffer a compiled function may take over for a result of the same
+    type and shape.  The mark applies to that argument only; results are never donatable."""
+    if isinstance(t, (tuple, list)):
+        return type(t)(donatable(x) for x in t)
+    if isinstance(t, dict):
+        return {k: donatable(v) for k, v in t.items()}
+    t = tensor(t)
+    return Tensor(t.data, t.type, t.shape, donatable=True)
+
+
+def is_donatable(t):
+    """``Nx.donatable?/1``."""
+    return bool(getattr(t, "donatable", False))
 
 
 def from_binary(raw, type, shape=None):

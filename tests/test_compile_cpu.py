@@ -51,3 +51,24 @@ def test_unsupported_op_is_reported():
         + struct.pack("<I", 1) + struct.pack("<I", 0)
     with pytest.raises(nif.Unsupported):
         defn.Program(blob)
+
+
+def test_donation_pairs_and_plans():
+    """Nx.donatable bookkeeping without a GPU: pairing rules (exla/lib/exla/defn.ex:598-645) and what
+    the planner decides for each pair."""
+    from nx_b200 import expr as E, nx
+    t = [defn.template((4, 64, 16), "f32"), defn.template((4, 1, 16), "f32"), defn.template((), "s32")]
+    outs, _, params = defn._trace(lambda c, n, p: nx.put_slice(c, [0, p, 0], n), t)
+    d = defn.Program(E.serialize(outs, params, defn.alias_pairs([0], params, outs))).describe()
+    assert "space={4,1,16}" in d and "argument 0 -> result 0 (written in place)" in d      # only the window is written
+    outs, _, params = defn._trace(lambda a: nx.transpose(a) + a, [defn.template((32, 32), "f32")])
+    d = defn.Program(E.serialize(outs, params, defn.alias_pairs([0], params, outs))).describe()
+    assert "own buffer" in d                                                                # a transposed read forbids in-place
+    outs, _, params = defn._trace(lambda a, b: (a + b, a - b), [defn.template((3,), "s32")] * 2)
+    assert defn.alias_pairs([0, 1], params, outs) == [(0, 0), (1, 1)]
+    outs, _, params = defn._trace(lambda a: nx.sum(a), [defn.template((4,), "s32")])
+    with pytest.raises(ValueError, match="no output with matching shape"):
+        defn.alias_pairs([0], params, outs)
+    outs, _, params = defn._trace(lambda a, b: b + 1, [defn.template((2,), "s32")] * 2)
+    with pytest.raises(ValueError, match="not used by the computation"):
+        defn.alias_pairs([0], params, outs)
