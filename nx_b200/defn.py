@@ -173,23 +173,69 @@ def __compile__(key, templates, fun, opts):
         # outputs that are parameters or constants still need a buffer of
         # their own: results are always fresh tensors (exla/lib/exla/defn.ex:387-393)
         donated = [i for i, t in enumerate(flat) if getattr(t, "donatable", False)]
-        blob = E.serialize(outs, params, alias_pairs(donated, params, outs))
-        entry = (Program(blob), ospec)
+        entry = (_make_runner(outs, params, alias_pairs(donated, params, outs)), ospec)
         with _cache_lock:
             _cache.setdefault(ck, entry)
-    prog, ospec = entry
+    run_graph, ospec = entry
     device = B._device_of(opts.get("device"))
 
     def runner(args_list):
         results = []
         for thunks in args_list:
             args = [B.backend_transfer(th() if callable(th) else th, device) for th in thunks]
-            outs = prog.run(args, device)
+            outs = run_graph(args, device)
             results.append(_unflatten(ospec, iter(outs)))
         return results
 
-    runner.program = prog
+    runner.program = run_graph.program
     return runner
+
+
+def _make_runner(outs, params, aliases=None):
+    """A callable ``(device tensors, device) -> result tensors`` for a traced graph.  Without control
+    flow that is one program.  A graph with ``while`` nodes is cut at them: one program computes a
+    loop's initial state and captured values, the host iterates the condition and body programs
+    (reading the one-byte predicate back), and the final state enters the programs after it as
+    extra parameters."""
+    order = E.topo_order(outs)[0]
+    groups, seen = [], set()
+    for t in order:
+        if t.data.op == "while" and id(t.data.payload) not in seen:
+            seen.add(id(t.data.payload))
+            groups.append(t.data.payload)
+    if not groups:
+        prog = Program(E.serialize(outs, params, aliases))
+
+        def run_one(vals, device):
+            return prog.run(vals, device)
+        run_one.program = prog
+        return run_one
+
+    from . import nx
+    all_params = list(params)
+    repl, stages = {}, []
+    for g in groups:
+        stage = _make_runner(E.substitute(g.inputs, repl), list(all_params))
+        cond = _make_runner(g.cond_outs, g.sub_params)
+        body = _make_runner(g.body_outs, g.sub_params)
+        stages.append((stage, cond, body, g.n_state))
+        for r in g.results:                       # the final state: parameters of everything downstream
+            p = E.parameter(r.type, r.shape, len(all_params))
+            all_params.append(p)
+            repl[r.data.id] = p
+    final = _make_runner(E.substitute(outs, repl), list(all_params))
+
+    def run_segments(vals, device):
+        vals = list(vals)
+        for stage, cond, body, k in stages:
+            ins = stage(vals, device)
+            state, caps = list(ins[:k]), list(ins[k:])
+            while nx.to_number(cond(state + caps, device)[0]):
+                state = list(body(state + caps, device))
+            vals += state
+        return final(vals, device)
+    run_segments.program = None
+    return run_segments
 
 
 def alias_pairs(donated, params, outs):
@@ -272,8 +318,8 @@ def build_program(fun, templates):
 # ---- control flow (nx/lib/nx/defn/kernel.ex while/cond; Expr :while / :cond) --------------------
 # Host-orchestrated: the condition and the body are compiled programs and the loop runs on the
 # host, reading the one-byte predicate back each iteration (what Nx.Defn.Evaluator does with a
-# device backend).  This covers loops at the top of a computation - an autoregressive decode
-# loop over a KV cache - where each iteration is a whole program anyway.
+# device backend).  A loop at the top level (an autoregressive decode loop over a KV cache) runs
+# as is; a loop inside a traced defn cuts the traced graph into the programs around it.
 
 def _traced(values):
     flat = []
@@ -298,7 +344,7 @@ def while_loop(cond_fun, body_fun, init, max_iterations=None, **opts):
     from . import nx
     state = tuple(init)
     if _traced(state):
-        raise NotImplementedError("while inside a traced defn is not compiled yet: run the loop at the top level")
+        return _traced_while(cond_fun, body_fun, state)
     state = tuple(_map_tensors(nx.tensor, s) for s in state)
     want = _signature(state)
     cond_c, body_c = jit(cond_fun, **opts), jit(body_fun, **opts)
@@ -318,6 +364,74 @@ def while_loop(cond_fun, body_fun, init, max_iterations=None, **opts):
             raise ValueError(f"the do-block in while must return tensors with the same shape, type, and names as the initial arguments: {got} vs {want}")
         state = new
         n += 1
+
+
+class _WhileGroup:
+    """What a traced ``while`` carries to the compiler: its inputs in the enclosing graph (initial
+    state, then the enclosing values its functions captured), the condition and body graphs over
+    parameters ``state ++ captures``, and its result nodes."""
+    __slots__ = ("inputs", "cond_outs", "body_outs", "sub_params", "n_state", "results")
+
+
+def _traced_while(cond_fun, body_fun, state):
+    """``while`` inside a traced defn (Expr :while, nx/lib/nx/defn/expr.ex while/4): both functions are
+    traced over fresh parameters; enclosing values they use become extra, loop-invariant parameters."""
+    from . import nx
+    flat = []
+    spec = [_flatten(x, flat) for x in state]
+    flat = [B.to_expr(nx.tensor(t) if not isinstance(t, Tensor) else t) for t in flat]
+    k = len(flat)
+    mark = E.watermark()
+    sub = [E.parameter(t.type, t.shape, i) for i, t in enumerate(flat)]
+    it = iter(sub)
+    args = [_unflatten(sp, it) for sp in spec]
+    with B.trace_scope():
+        c = B.to_expr(cond_fun(*args))
+        body = body_fun(*args)
+        body = tuple(body) if isinstance(body, (tuple, list)) else (body,)
+        bflat = []
+        bspec = [_flatten(x, bflat) for x in body]
+        bflat = [B.to_expr(nx.tensor(t) if not isinstance(t, Tensor) else t) for t in bflat]
+    if c.shape != ():
+        raise ValueError(f"condition must be a scalar tensor, got shape {c.shape}")
+    if [(t.type, t.shape) for t in bflat] != [(t.type, t.shape) for t in flat] or repr(bspec) != repr(spec):
+        raise ValueError("the do-block in while must return tensors with the same shape, type, and names as the initial arguments")
+    # values of the enclosing trace used inside: nodes older than the watermark
+    own = {p.data.id for p in sub}
+    captures, repl = [], {}
+    for t in E.topo_order([c] + bflat)[0]:
+        e = t.data
+        if isinstance(e.id, int) and e.id < mark and e.id not in own and e.id not in repl and e.op not in ("constant",):
+            # only the outermost captured node of a chain matters; inner ones are cut off by the substitution
+            repl[e.id] = None
+    # keep only captures that are not reachable solely through other captures
+    def frontier(roots):
+        found, seen = [], set()
+        stack = list(roots)
+        while stack:
+            t = stack.pop()
+            e = t.data
+            if e.id in seen:
+                continue
+            seen.add(e.id)
+            if e.id in repl:
+                found.append(t)
+                continue
+            stack.extend(e.args)
+        return found
+    for t in frontier([c] + bflat):
+        if not any(t.data.id == x.data.id for x in captures):
+            captures.append(t)
+    repl = {t.data.id: E.parameter(t.type, t.shape, k + j) for j, t in enumerate(captures)}
+    g = _WhileGroup()
+    g.n_state = k
+    g.inputs = flat + captures
+    g.sub_params = sub + [repl[t.data.id] for t in captures]
+    g.cond_outs = E.substitute([c], repl)
+    g.body_outs = E.substitute(bflat, repl)
+    g.results = [Tensor(E.Expr("while", g.inputs, ints=[i, k], payload=g), t.type, t.shape) for i, t in enumerate(flat)]
+    it = iter(g.results)
+    return tuple(_unflatten(sp, it) for sp in spec)
 
 
 def cond(pred, then_fun, else_fun, *operands):

@@ -36,10 +36,11 @@ AGGREGATES = ["sum", "product", "reduce_max", "reduce_min", "all", "any"]
 
 class Expr:
     """One node of the graph (expr.ex:59-60)."""
-    __slots__ = ("id", "op", "args", "ints", "flts", "blob")
+    __slots__ = ("id", "op", "args", "ints", "flts", "blob", "payload")
 
-    def __init__(self, op, args=(), ints=(), flts=(), blob=b"", id=None):
+    def __init__(self, op, args=(), ints=(), flts=(), blob=b"", id=None, payload=None):
         self.id = next(_ids) if id is None else id
+        self.payload = payload      # host-side attachment of control-flow nodes (never serialised)
         self.op = op
         self.args = list(args)      # Tensor operands (each with .data an Expr)
         self.ints = [int(i) for i in ints]
@@ -48,6 +49,33 @@ class Expr:
 
     def __repr__(self):
         return f"Expr<{self.op}#{self.id}>"
+
+
+def watermark():
+    """An id larger than every node created so far (nodes made later have larger ids)."""
+    return next(_ids)
+
+
+def substitute(outputs, repl):
+    """Copy of the DAG under ``outputs`` with the nodes whose id is in ``repl`` replaced by the given
+    tensors (sub-graphs that contain none of them are shared, not copied)."""
+    from .nx import Tensor
+    memo = {}
+
+    def go(t):
+        e = t.data
+        if e.id in repl:
+            return repl[e.id]
+        if e.id in memo:
+            return memo[e.id]
+        new_args = [go(a) for a in e.args]
+        if all(n is a for n, a in zip(new_args, e.args)):
+            r = t
+        else:
+            r = Tensor(Expr(e.op, new_args, e.ints, e.flts, e.blob, payload=e.payload), t.type, t.shape)
+        memo[e.id] = r
+        return r
+    return [go(o) for o in outputs]
 
 
 def _tensor(data, type, shape):

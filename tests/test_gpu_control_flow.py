@@ -38,6 +38,44 @@ def test_while_rejects_a_body_that_changes_the_state_template():
         defn.while_loop(lambda i: nx.greater_equal(i, 0), lambda i: (i + 1,), (nx.tensor(0),), max_iterations=5)
 
 
+def test_while_inside_a_jitted_defn():
+    """The loop is cut out of the traced graph: a program before it (initial state + captured
+    values), the loop over condition/body programs, a program after it."""
+    def f(x, n):
+        y = x * 2.0                                                     # computed before the loop, used inside it
+        i, acc = defn.while_loop(lambda i, a: nx.less(i, n), lambda i, a: (i + 1, a + y), (nx.tensor(0), x))
+        return acc + 1.0, i                                             # the loop's result is used afterwards
+
+    jf = defn.jit(f)
+    a, i = jf(nx.tensor([1.0, 2.0, 3.0, 4.0]), nx.tensor(5))
+    assert np.array_equal(nx.to_numpy(a), [12.0, 23.0, 34.0, 45.0]) and nx.to_number(i) == 5
+    a, i = jf(nx.tensor([1.0, 2.0, 3.0, 4.0]), nx.tensor(0))           # same executable, zero iterations
+    assert np.array_equal(nx.to_numpy(a), [2.0, 3.0, 4.0, 5.0]) and nx.to_number(i) == 0
+
+    def two_loops(x):
+        (a,) = defn.while_loop(lambda a: nx.less(nx.sum(a), 100.0), lambda a: (a * 2.0,), (x,))
+        # the second loop starts from the first one's result and nests a third
+        def body(j, b):
+            (c,) = defn.while_loop(lambda c: nx.less(nx.reduce_max(c), 1000.0), lambda c: (c * 10.0,), (b,))
+            return j + 1, c / 1000.0
+        j, b = defn.while_loop(lambda j, b: nx.less(j, 3), body, (nx.tensor(0), a))
+        return a, b, j
+
+    a, b, j = defn.jit(two_loops)(nx.tensor([1.0, 2.0]))
+    ra = np.array([1.0, 2.0])
+    while ra.sum() < 100.0:
+        ra = ra * 2.0
+    rb = ra.copy()
+    for _ in range(3):
+        c = rb.copy()
+        while c.max() < 1000.0:
+            c = c * 10.0
+        rb = c / 1000.0
+    np.testing.assert_allclose(nx.to_numpy(a), ra)
+    np.testing.assert_allclose(nx.to_numpy(b), rb, rtol=1e-6)
+    assert nx.to_number(j) == 3
+
+
 def test_cond_eager_and_inside_a_defn():
     x = nx.tensor([1.0, 2.0, 3.0])
     f = lambda t, p: defn.cond(p, lambda v: v * 2.0, lambda v: v + 1.0, t)
