@@ -120,7 +120,9 @@ int nxb200_buffer_release(nxb200_buffer *buf);
  * dynamic starts the node has 1 + rank arguments: the tensor, then one scalar
  * integer start per axis, and the starts attribute is ignored); gather [axes…]
  * (arguments: tensor, indices); put_slice none (arguments: tensor, slice, one
- * scalar integer start per axis); concatenate [axis]; everything else none.
+ * scalar integer start per axis); pad [lows…, highs…, interiors…] (arguments:
+ * tensor, scalar pad value); reverse [axes…]; concatenate [axis]; everything
+ * else none.
  *
  * Building needs no GPU (kernels are generated and compiled for sm_100a on
  * the host); the first run on a device loads them. */

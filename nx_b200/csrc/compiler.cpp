@@ -51,7 +51,7 @@ const std::set<std::string> kView = {"reshape", "squeeze", "broadcast", "transpo
 bool is_reduce(const Node& n) { return kReduce.count(n.op) || kArgReduce.count(n.op); }
 bool is_inline(const Node& n) {   // can be generated inside a consumer's kernel
   return kUnaryMath.count(n.op) || kUnaryOther.count(n.op) || kBinary.count(n.op) || kView.count(n.op) ||
-         n.op == "select" || n.op == "clip" || n.op == "constant" || n.op == "iota" || n.op == "gather" || n.op == "put_slice";
+         n.op == "select" || n.op == "clip" || n.op == "constant" || n.op == "iota" || n.op == "gather" || n.op == "put_slice" || n.op == "pad" || n.op == "reverse";
 }
 
 const char* storage_type(DType t) {
@@ -650,6 +650,43 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
       tidx[nd.ints[i]] = o;
     }
     return value(nd.args[0], tidx);
+  }
+  if (op == "reverse") {
+    // ints: the reversed axes.  index = dim - 1 - i along each
+    const Node& a = g_.nodes[nd.args[0]];
+    std::vector<Aff> ai = idx;
+    for (int64_t ax : nd.ints) {
+      Aff& x = ai[ax];
+      if (x.opaque) x.expr = "((" + idx_t() + ")" + std::to_string(a.shape[ax] - 1) + " - " + x.expr + ")";
+      else { x.c = a.shape[ax] - 1 - x.c; for (auto& kk : x.k) kk = -kk; }
+    }
+    return value(nd.args[0], ai);
+  }
+  if (op == "pad") {
+    // args: tensor, scalar pad value; ints: low..., high..., interior... (Nx.pad, negative edges crop).
+    // out[i] is x[(i - low) / (interior + 1)] where that position exists, else the pad value.
+    const Node& a = g_.nodes[nd.args[0]];
+    const size_t r = idx.size();
+    std::vector<Aff> ai;
+    std::string inside;
+    for (size_t j = 0; j < r; ++j) {
+      const int64_t lo = nd.ints[j], hi = nd.ints[r + j], in = nd.ints[2 * r + j];
+      if (lo == 0 && in == 0 && hi <= 0) { ai.push_back(idx[j]); continue; }     // a cropped or untouched tail: same index
+      const std::string c = "((long long)(" + affstr(idx[j], false) + ") - " + std::to_string(lo) + "LL)";
+      std::string cond = "(" + c + " >= 0 && " + c + " < " + std::to_string((a.shape[j] - 1) * (in + 1) + 1) + "LL";
+      if (in > 0) cond += " && " + c + " % " + std::to_string(in + 1) + "LL == 0";
+      cond += ")";
+      inside += (inside.empty() ? "" : " && ") + cond;
+      Aff o;
+      o.opaque = true;
+      o.k.assign(nv_, 0);
+      o.expr = "(" + idx_t() + ")nx_clamp_index(" + c + " / " + std::to_string(in + 1) + "LL, (long long)" + std::to_string(a.shape[j]) + ")";
+      ai.push_back(o);
+    }
+    Val x = value(nd.args[0], ai);
+    if (inside.empty()) return def(x.elem, t, cvt(x.v, a.dt, t));
+    Val pv = value(nd.args[1], {});
+    return def(true, t, "(" + inside + ") ? " + cvt(x.v, a.dt, t) + " : " + cvt(pv.v, g_.nodes[nd.args[1]].dt, t));
   }
   if (op == "put_slice") {
     // args: tensor, slice, one scalar start per axis (clamped so that the slice fits)

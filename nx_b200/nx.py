@@ -572,6 +572,69 @@ def take(x, indices, axis=0):
     return transpose(g, perm)
 
 
+def pad(x, pad_value, padding_config):
+    """``Nx.pad/3`` (nx/lib/nx.ex pad; shape rule nx/lib/nx/shape.ex:1038-1090): per axis
+    ``(low, high, interior)``; negative edges crop."""
+    x, pv = _as_operand(x), _as_operand(_num(pad_value))
+    if pv.shape != ():
+        raise ValueError("padding value must be a scalar")
+    cfg = [tuple(int(v) for v in c) for c in padding_config]
+    if len(cfg) != x.rank or _b.any(len(c) != 3 for c in cfg):
+        raise ValueError("invalid padding configuration, rank of padding configuration and shape must match")
+    shape = []
+    for d, (lo, hi, it) in zip(x.shape, cfg):
+        if it < 0:
+            raise ValueError("interior padding must be non-negative")
+        n = d + lo + hi + _b.max(d - 1, 0) * it
+        if n < 0:
+            raise ValueError("invalid padding widths, padding width can't be less than the dimension it pads")
+        shape.append(n)
+    out = _out(_binary_type(x, pv if not isinstance(pad_value, Tensor) else pad_value), shape)
+    ints = [c[0] for c in cfg] + [c[1] for c in cfg] + [c[2] for c in cfg]
+    if x.rank == 0:
+        return as_type(x, out.type)
+    return _dispatch(lambda a, v: E.node(out, "pad", [a, v], ints=ints), [x, pv])
+
+
+def reverse(x, axes=None):
+    """``Nx.reverse/2`` (nx/lib/nx.ex reverse): all axes by default."""
+    x = _as_operand(x)
+    axes = list(range(x.rank)) if axes is None else sorted(set(_norm_axes(x.rank, axes)))
+    axes = [a for a in axes if x.shape[a] > 1]
+    if not axes:
+        return x
+    out = _out(x.type, x.shape)
+    return _dispatch(lambda a: E.node(out, "reverse", [a], ints=axes), [x])
+
+
+def stack(tensors, axis=0):
+    """``Nx.stack/2``: a new axis, then concatenate."""
+    ts = [_as_operand(t) for t in tensors]
+    a = axis if axis >= 0 else axis + ts[0].rank + 1
+    return concatenate([reshape(t, t.shape[:a] + (1,) + t.shape[a:]) for t in ts], axis=a)
+
+
+def new_axis(x, axis):
+    """``Nx.new_axis/2``."""
+    x = _as_operand(x)
+    a = axis if axis >= 0 else axis + x.rank + 1
+    return reshape(x, x.shape[:a] + (1,) + x.shape[a:])
+
+
+def take_along_axis(x, indices, axis=0):
+    """``Nx.take_along_axis/3`` (nx/lib/nx.ex take_along_axis): `indices` has the shape of `x`
+    except along `axis`; lowered to `gather` over iotas like the reference does."""
+    x, indices = _as_operand(x), _as_operand(indices)
+    if not T.is_integer(indices.type):
+        raise ValueError(f"indices must be an integer tensor, got {indices.type}")
+    a = _norm_axis(x.rank, axis)
+    if indices.rank != x.rank or _b.any(i != a and indices.shape[i] != x.shape[i] for i in range(x.rank)):
+        raise ValueError(f"expected indices shape {indices.shape} to match tensor shape {x.shape} except along axis {a}")
+    cols = [indices if i == a else as_type(iota(indices.shape, axis=i), indices.type) for i in range(x.rank)]
+    full = concatenate([reshape(c, indices.shape + (1,)) for c in cols], axis=x.rank)
+    return gather(x, full)
+
+
 def slice_along_axis(x, start, length, axis=0, strides=1):
     x = _as_operand(x)
     a = _norm_axis(x.rank, axis)

@@ -523,6 +523,29 @@ def evaluate(nodes, outs, params, mode="xla_like", all_reduce=None):
             if len(arg) > 1:      # dynamic starts, clamped so that the window fits
                 st = [min(max(int(s), 0), d - l) for s, d, l in zip(arg[1:], arg[0].shape, ln)]
             v = arg[0][tuple(slice(s, s + l, d) for s, l, d in zip(st, ln, sd))]
+        elif op == "reverse":
+            v = np.flip(arg[0], axis=tuple(nd.ints))
+        elif op == "pad":
+            # nx/lib/nx/binary_backend.ex:326-348: interior, then edges (negative edges crop)
+            r = arg[0].ndim
+            lo, hi, it = nd.ints[:r], nd.ints[r:2 * r], nd.ints[2 * r:3 * r]
+            x = convert(arg[0], at[0], t, mode)
+            pv = convert(arg[1], at[1], t, mode)
+            for ax in range(r):
+                d = x.shape[ax]
+                n = d + max(d - 1, 0) * it[ax]
+                sh = list(x.shape)
+                sh[ax] = n
+                y = np.full(sh, pv, dtype=x.dtype)
+                sl = [slice(None)] * r
+                sl[ax] = slice(0, n, it[ax] + 1)
+                y[tuple(sl)] = x
+                pads = [(0, 0)] * r
+                pads[ax] = (max(lo[ax], 0), max(hi[ax], 0))
+                y = np.pad(y, pads, constant_values=pv)
+                sl[ax] = slice(max(-lo[ax], 0), y.shape[ax] - max(-hi[ax], 0))
+                x = y[tuple(sl)]
+            v = x
         elif op == "gather":
             # nx/lib/nx/binary_backend.ex:1903-1940 (indexed axes first, then a contiguous
             # copy per index row); coordinates clamped as XLA's gather does

@@ -218,3 +218,35 @@ case("slice dynamic starts", "nx/lib/nx.ex:14077-14084", lambda t, a, b: nx.slic
      [([[1, 2, 3], [4, 5, 6]], "s32"), (1, "s32"), (2, "s32")], [([[6]], "s32")])
 case("slice dynamic start is clipped", "nx/lib/nx.ex:14105-14125", lambda t, a: nx.slice(t, [a, 0], [2, 2]),
      [([[1, 2], [3, 4], [5, 6]], "s32"), (2, "s32")], [([[3, 4], [5, 6]], "s32")])
+
+# ---- pad / reverse / take_along_axis: exla/test/exla/defn/expr_test.exs:3095-3182, 3498-3540; nx/lib/nx.ex doctests ----
+case("pad vector", "exla/test/exla/defn/expr_test.exs:3108-3110", lambda t: nx.pad(t, 0, [(1, 1, 0)]),
+     [([1, 2, 3], "s32")], [([0, 1, 2, 3, 0], "s32")])
+case("pad matrix", "exla/test/exla/defn/expr_test.exs:3112-3117", lambda t: nx.pad(t, 0, [(1, 1, 0), (1, 1, 0)]),
+     [([[1, 2, 3], [4, 5, 6]], "s32")], [([[0, 0, 0, 0, 0], [0, 1, 2, 3, 0], [0, 4, 5, 6, 0], [0, 0, 0, 0, 0]], "s32")])
+_PADDED = [[[0.0] * 3] * 3, [[0.0] * 3, [1.0, 2.0, 0.0], [3.0, 4.0, 0.0]], [[0.0] * 3, [5.0, 6.0, 0.0], [7.0, 8.0, 0.0]],
+           [[0.0] * 3] * 3, [[0.0] * 3] * 3]
+case("pad tensor, float pad value on integers", "exla/test/exla/defn/expr_test.exs:3119-3156",
+     lambda t: nx.pad(t, 0.0, [(1, 2, 0), (1, 0, 0), (0, 1, 0)]), [([[[1, 2], [3, 4]], [[5, 6], [7, 8]]], "s32")], [(_PADDED, "f32")])
+case("pad interior", "nx/lib/nx.ex:4055-4063", lambda t: nx.pad(t, 0, [(0, 0, 1), (0, 0, 1)]),
+     [([[1, 2, 3], [4, 5, 6]], "s32")], [([[1, 0, 2, 0, 3], [0, 0, 0, 0, 0], [4, 0, 5, 0, 6]], "s32")])
+case("pad negative vector", "exla/test/exla/defn/expr_test.exs:3159-3162", lambda t: nx.pad(t, 0.0, [(-1, -1, 0)]),
+     [([1.0, 1.0, 2.0, 3.0, 0.0], "f32")], [([1.0, 2.0, 3.0], "f32")])
+case("pad negative matrix", "exla/test/exla/defn/expr_test.exs:3164-3167", lambda t: nx.pad(t, 0, [(0, 0, 0), (-1, 1, 0)]),
+     [([[0, 1, 2, 3], [0, 4, 5, 6]], "s32")], [([[1, 2, 3, 0], [4, 5, 6, 0]], "s32")])
+case("pad negative tensor", "exla/test/exla/defn/expr_test.exs:3169-3180",
+     lambda t: nx.pad(t, 0, [(-1, 0, 0), (-1, -1, 0), (0, -1, 0)]),
+     [([[[0, 0, 0]] * 4, [[0, 0, 0], [1, 2, 0], [3, 4, 0], [0, 0, 0]], [[0, 0, 0], [5, 6, 0], [7, 8, 0], [0, 0, 0]]], "s32")],
+     [([[[1, 2], [3, 4]], [[5, 6], [7, 8]]], "s32")])
+case("reverse all dims", "exla/test/exla/defn/expr_test.exs:3506-3507", lambda t: nx.reverse(t),
+     [([[0, 1, 2, 3], [4, 5, 6, 7]], "s32")], [([[7, 6, 5, 4], [3, 2, 1, 0]], "s32")])
+case("reverse one dim", "exla/test/exla/defn/expr_test.exs:3529-3530", lambda t: nx.reverse(t, axes=[1]),
+     [([[0, 1, 2], [3, 4, 5]], "s32")], [([[2, 1, 0], [5, 4, 3]], "s32")])
+case("take_along_axis 1", "nx/lib/nx.ex:14839-14847", lambda t, i: nx.take_along_axis(t, i, axis=1),
+     [([[1, 2, 3], [4, 5, 6]], "s32"), ([[0, 0, 2, 2, 1, 1], [2, 2, 1, 1, 0, 0]], "s32")],
+     [([[1, 1, 3, 3, 2, 2], [6, 6, 5, 5, 4, 4]], "s32")])
+case("take_along_axis 0", "nx/lib/nx.ex:14849-14858", lambda t, i: nx.take_along_axis(t, i, axis=0),
+     [([[1, 2, 3], [4, 5, 6]], "s32"), ([[0, 1, 1], [1, 0, 0], [0, 1, 0]], "s32")],
+     [([[1, 5, 6], [4, 2, 3], [1, 5, 3]], "s32")])
+case("stack", "nx/lib/nx.ex stack doctest", lambda a, b: nx.stack([a, b], axis=1),
+     [([1, 2, 3], "s32"), ([4, 5, 6], "s32")], [([[1, 4], [2, 5], [3, 6]], "s32")])

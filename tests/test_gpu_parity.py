@@ -363,3 +363,18 @@ def test_repeated_runs_replay_a_graph_and_still_read_current_data():
         outs = mlp.run([x_dev[0], w], 0) if outs is None else mlp.run_into([x_dev[0], w], outs, 0)
         want = np.tanh(x.astype(np.float64) @ nx.to_numpy(w).astype(np.float64)) + x.sum(axis=1, keepdims=True)
         assert_close(nx.to_numpy(outs[0]), want, rtol=1e-5, atol=1e-5, what=f"run {i}")
+
+
+def test_pad_and_reverse_fuse_into_consumers():
+    rng = np.random.default_rng(31)
+    x = rng.normal(0, 1, (5, 7, 9)).astype(np.float32)
+    for cfg in ([(1, 2, 0), (0, 0, 0), (3, 1, 0)], [(0, 1, 2), (2, 0, 1), (-1, -2, 0)], [(-2, 3, 1), (0, -1, 0), (1, 1, 3)]):
+        check(run_both(lambda t: nx.exp(nx.pad(t, -1.5, cfg)) * 2.0, [x], ["f32"]), f"pad {cfg}")
+    check(run_both(lambda t: nx.sum(nx.pad(t, 0.0, [(0, 0, 0), (1, 1, 0), (0, 7, 0)]), axes=[2]), [x], ["bf16"]), "pad + row sum bf16")
+    for axes in (None, [0], [2], [0, 2], [1]):
+        res = run_both(lambda t: (nx.reverse(t, axes=axes), nx.reverse(t, axes=axes) + t), [x], ["f32"])
+        assert np.array_equal(res[0][0], res[0][1])
+        check(res[1:], f"reverse {axes}")
+    idx = rng.integers(0, 9, (5, 7, 4))
+    res = run_both(lambda t, i: nx.take_along_axis(t, i, axis=2), [x, idx], ["f32", "s32"])
+    assert np.array_equal(res[0][0], np.take_along_axis(x, idx, axis=2)) and np.array_equal(res[0][0], res[0][1])
