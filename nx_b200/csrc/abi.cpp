@@ -187,6 +187,9 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         void* params[4] = {tl.map_a, tl.map_b, tl.map_c, tl.params};
         check_cu(drv.cuLaunchKernel(L.functions[as.jit_kernel], tl.grid, 1, 1, 320, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
                  ("launching " + ks.name).c_str());
+      } else if (step.kind == Step::SORT) {
+        const SortSpec& ss = plan.sorts[step.index];
+        launch_sort_rows(ptr[ss.in_slot], ptr[ss.out_slot], ss.rows, ss.len, ss.dt, ss.out_dt, ss.descending, ss.indices, d.sm_count, d.stream);
       } else if (step.kind == Step::ALLREDUCE) {
         if (held) throw NotReplayable();
         const CollectiveSpec& cs = plan.collectives[step.index];

@@ -51,7 +51,8 @@ const std::set<std::string> kView = {"reshape", "squeeze", "broadcast", "transpo
 bool is_reduce(const Node& n) { return kReduce.count(n.op) || kArgReduce.count(n.op); }
 bool is_inline(const Node& n) {   // can be generated inside a consumer's kernel
   return kUnaryMath.count(n.op) || kUnaryOther.count(n.op) || kBinary.count(n.op) || kView.count(n.op) ||
-         n.op == "select" || n.op == "clip" || n.op == "constant" || n.op == "iota" || n.op == "gather" || n.op == "put_slice" || n.op == "pad" || n.op == "reverse";
+         n.op == "select" || n.op == "clip" || n.op == "constant" || n.op == "iota" || n.op == "gather" || n.op == "put_slice" || n.op == "pad" || n.op == "reverse" ||
+         n.op == "window_sum" || n.op == "window_max" || n.op == "window_min" || n.op == "window_product";
 }
 
 const char* storage_type(DType t) {
@@ -650,6 +651,70 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
       tidx[nd.ints[i]] = o;
     }
     return value(nd.args[0], tidx);
+  }
+  if (op == "window_sum" || op == "window_max" || op == "window_min" || op == "window_product") {
+    // ints: window dims, strides, low padding, high padding, dilations (rank entries each).  The
+    // window is unrolled: each of its positions is an index expression of the output position
+    // (pooling windows are small); positions in the padding contribute the operation's identity.
+    const Node& a = g_.nodes[nd.args[0]];
+    const size_t r = idx.size();
+    int64_t vol = 1;
+    for (size_t j = 0; j < r; ++j) vol *= nd.ints[j];
+    if (vol > 256) fail(NXB_ERR_UNSUPPORTED, "window reductions over more than 256 positions are not implemented");
+    const std::string RT = reg_type(t);
+    std::string ident;
+    if (op == "window_sum") ident = "(" + RT + ")0";
+    else if (op == "window_product") ident = "(" + RT + ")1";
+    else {
+      const bool mx = op == "window_max";
+      if (dtype_is_float(t)) ident = std::string(mx ? "-" : "") + (t == NXB_F64 ? "(double)NXB_INF" : "NXB_INF");
+      else {
+        const int bits = (int)dtype_size(t) * 8;
+        const int64_t lo = dtype_is_signed(t) ? -(int64_t)((uint64_t)1 << (bits - 1)) : 0;
+        const int64_t hi = dtype_is_signed(t) ? (int64_t)(((uint64_t)1 << (bits - 1)) - 1) : (bits == 64 ? -1 : (int64_t)(((uint64_t)1 << bits) - 1));
+        ident = literal(0, mx ? lo : hi, false, t);
+      }
+    }
+    std::string acc;
+    bool elem = false;
+    std::vector<int64_t> w(r, 0);
+    for (int64_t pos = 0; pos < vol; ++pos) {
+      std::vector<Aff> ai;
+      std::string inside;
+      for (size_t j = 0; j < r; ++j) {
+        const int64_t stride = nd.ints[r + j], lo = nd.ints[2 * r + j], hi = nd.ints[3 * r + j], dil = nd.ints[4 * r + j];
+        const int64_t off = w[j] * dil - lo;
+        if (lo == 0 && hi == 0 && !idx[j].opaque) {
+          Aff x = idx[j];
+          x.c = x.c * stride + off;
+          for (auto& kk : x.k) kk *= stride;
+          ai.push_back(x);
+          continue;
+        }
+        const std::string c = "((long long)(" + affstr(idx[j], false) + ") * " + std::to_string(stride) + "LL + " + std::to_string(off) + "LL)";
+        if (lo != 0 || hi != 0) inside += (inside.empty() ? "" : " && ") + std::string("(") + c + " >= 0 && " + c + " < " + std::to_string(a.shape[j]) + "LL)";
+        Aff o;
+        o.opaque = true;
+        o.k.assign(nv_, 0);
+        o.expr = "(" + idx_t() + ")nx_clamp_index(" + c + ", (long long)" + std::to_string(a.shape[j]) + ")";
+        ai.push_back(o);
+      }
+      Val x = value(nd.args[0], ai);
+      elem = elem || x.elem;
+      std::string term = cvt(x.v, a.dt, t);
+      if (!inside.empty()) { term = "((" + inside + ") ? " + term + " : " + ident + ")"; elem = true; }
+      if (acc.empty()) acc = term;
+      else if (op == "window_sum") acc = "(" + acc + " + " + term + ")";
+      else if (op == "window_product") acc = "(" + acc + " * " + term + ")";
+      else acc = std::string(op == "window_max" ? "nx_max" : "nx_min") + "(" + acc + ", " + term + ")";
+      if (pos % 8 == 7 || pos + 1 == vol) {        // keep expressions short: a statement every few terms
+        Val part = def(true, t, acc);
+        acc = part.v;
+        elem = true;
+      }
+      for (int j = (int)r - 1; j >= 0; --j) { if (++w[j] < nd.ints[j]) break; w[j] = 0; }
+    }
+    return {acc, true};
   }
   if (op == "reverse") {
     // ints: the reversed axes.  index = dim - 1 - i along each
@@ -1436,14 +1501,14 @@ struct Planner {
     int d = 0;
     for (int a : g.nodes[n].args) {
       const std::string& op = g.nodes[a].op;
-      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention") ? 1 : 0));
+      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention" || op == "sort" || op == "argsort") ? 1 : 0));
     }
     return depth_memo[n] = d;
   }
 
   bool is_leaf(int n) const {
     const std::string& op = g.nodes[n].op;
-    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention";
+    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention" || op == "sort" || op == "argsort";
   }
 
   // Nodes reachable backwards through everything a kernel can generate inline
@@ -1465,6 +1530,7 @@ std::string Plan::describe() const {
     if (st.kind == Step::KERNEL) o << kernels[st.index].desc << "\n";
     else if (st.kind == Step::GEMM) o << gemms[st.index].desc << "\n";
     else if (st.kind == Step::ATTENTION) o << attentions[st.index].desc << "\n";
+    else if (st.kind == Step::SORT) o << sorts[st.index].desc << "\n";
     else o << collectives[st.index].desc << "\n";
   }
   for (auto& a : aliases)
@@ -1474,6 +1540,7 @@ std::string Plan::describe() const {
 
 // implemented in gemm_plan.cpp
 bool plan_dot(Plan& plan, int node, std::vector<int>& need_materialised, GemmSpec* out);
+bool sort_rows_supported(int64_t len);   // sort_rows.cu
 void canonicalize_dots(Graph& g);
 void rewrite_quantised_linears(Graph& g);
 void rewrite_attention(Graph& g);
@@ -1612,7 +1679,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       const Node& nd = g.nodes[n];
       if (!nd.live) continue;
       bool ok = is_inline(nd) || is_reduce(nd) || nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" ||
-                nd.op == "all_reduce" || nd.op == "attention";
+                nd.op == "all_reduce" || nd.op == "attention" || nd.op == "sort" || nd.op == "argsort";
       if (!ok) fail(NXB_ERR_UNSUPPORTED, "Nx op :" + nd.op + " is not implemented by the B200 compiler");
       if (nd.op == "slice" && nd.args.size() != 1 && nd.args.size() != 1 + nd.shape.size())
         fail(NXB_ERR_INVALID_ARGUMENT, "slice with dynamic start indices takes one start per axis");
@@ -1663,7 +1730,12 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       const std::string& aop = g.nodes[nd.args[0]].op;
       if (aop != "parameter" && aop != "tensor") P.mat[nd.args[0]] = 1;
     }
-    if (nd.op == "all_reduce") {
+    if (nd.op == "sort" || nd.op == "argsort") {
+      // a library step like the all-reduce: one buffer in, one out (ints: descending[, stable])
+      if (nd.args.size() != 1 || nd.shape.empty() || !sort_rows_supported(nd.shape.back()))
+        fail(NXB_ERR_UNSUPPORTED, "sort is implemented along a last axis of at most 16384 elements");
+    }
+    if (nd.op == "all_reduce" || nd.op == "sort" || nd.op == "argsort") {
       P.mat[n] = 1;
       allreduces.push_back(n);
       const std::string& aop = g.nodes[nd.args[0]].op;
@@ -1771,7 +1843,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         for (int n = 0; n < N; ++n) {
           const Node& nd = g.nodes[n];
           if (!nd.live || !P.mat[n]) continue;
-          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || nd.op == "all_reduce" || nd.op == "attention" || is_reduce(nd)) continue;
+          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || nd.op == "all_reduce" || nd.op == "attention" || nd.op == "sort" || nd.op == "argsort" || is_reduce(nd)) continue;
           roots.push_back(n);
         }
         for (int n : roots) {
@@ -1886,7 +1958,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           bool later = false;
           for (int l : leaves) {
             const std::string& lop = g.nodes[l].op;
-            if (l != D && (lop == "concatenate" || lop == "all_reduce" || lop == "attention") && P.depth(l) > P.depth(D)) later = true;
+            if (l != D && (lop == "concatenate" || lop == "all_reduce" || lop == "attention" || lop == "sort" || lop == "argsort") && P.depth(l) > P.depth(D)) later = true;
           }
           if (later) continue;
           const Node& dn = g.nodes[D];
@@ -2070,6 +2142,22 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           as.jit_kernel = (int)pl.kernels.size() - 1;
           pl.attentions.push_back(as);
           pl.steps.push_back({Step::ATTENTION, (int)pl.attentions.size() - 1});
+        } else if (u.kind == Unit::ALLREDUCE && (g.nodes[u.gemm_node].op == "sort" || g.nodes[u.gemm_node].op == "argsort")) {
+          const Node& nd = g.nodes[u.gemm_node];
+          const Node& in = g.nodes[nd.args[0]];
+          SortSpec ss;
+          ss.in_slot = in.slot;
+          ss.out_slot = nd.slot;
+          ss.len = nd.shape.back();
+          ss.rows = shape_numel(nd.shape) / std::max<int64_t>(ss.len, 1);
+          ss.dt = in.dt;
+          ss.out_dt = nd.dt;
+          ss.descending = !nd.ints.empty() && nd.ints[0] != 0;
+          ss.indices = nd.op == "argsort";
+          ss.desc = nd.op + "#" + std::to_string(u.gemm_node) + " " + dtype_name(in.dt) + shape_str(in.shape) + " along the last axis, " +
+                    (ss.descending ? "descending" : "ascending") + " (bitonic network over (key, position) pairs in shared memory)";
+          pl.sorts.push_back(ss);
+          pl.steps.push_back({Step::SORT, (int)pl.sorts.size() - 1});
         } else if (u.kind == Unit::ALLREDUCE) {
           const Node& nd = g.nodes[u.gemm_node];
           CollectiveSpec cs;
@@ -2190,6 +2278,9 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           const AttentionSpec& as = pl.attentions[step.index];
           const KernelSpec& ks = pl.kernels[as.jit_kernel];
           if (as.q_slot == sp || as.k_slot == sp || as.v_slot == sp || as.out_slot == so || std::count(ks.arg_slots.begin(), ks.arg_slots.end(), sp)) other = true;
+        } else if (step.kind == Step::SORT) {
+          const SortSpec& ss = pl.sorts[step.index];
+          if (ss.in_slot == sp || ss.out_slot == so) other = true;
         } else {
           const CollectiveSpec& cs = pl.collectives[step.index];
           if (cs.in_slot == sp || cs.out_slot == so) other = true;

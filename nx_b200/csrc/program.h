@@ -101,8 +101,16 @@ struct CollectiveSpec {
   std::string desc;
 };
 
+struct SortSpec {
+  int in_slot = -1, out_slot = -1;
+  int64_t rows = 0, len = 0;
+  DType dt = NXB_F32, out_dt = NXB_F32;
+  bool descending = false, indices = false;
+  std::string desc;
+};
+
 struct Step {
-  enum Kind { KERNEL, GEMM, ALLREDUCE, ATTENTION } kind = KERNEL;
+  enum Kind { KERNEL, GEMM, ALLREDUCE, ATTENTION, SORT } kind = KERNEL;
   int index = 0;
 };
 
@@ -114,6 +122,7 @@ struct Plan {
   std::vector<GemmSpec> gemms;
   std::vector<CollectiveSpec> collectives;
   std::vector<AttentionSpec> attentions;
+  std::vector<SortSpec> sorts;
   std::vector<int> param_slots;   // by parameter index (-1 when unused)
   std::vector<int> output_slots;  // by output index
   // Buffer donation (Nx.donatable, exla/lib/exla/defn.ex:598-645): the result takes over the

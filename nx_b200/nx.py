@@ -572,6 +572,189 @@ def take(x, indices, axis=0):
     return transpose(g, perm)
 
 
+def _window(op, x, window_dimensions, strides, padding, window_dilations):
+    """nx/lib/nx.ex:11007-11051 (aggregate_window_op) with Nx.Shape.pool (nx/lib/nx/shape.ex:860-886)."""
+    x = _as_operand(x)
+    win = [int(w) for w in window_dimensions]
+    r = x.rank
+    if len(win) != r:
+        raise ValueError(f"invalid window dimensions, rank of shape ({r}) does not match rank of window ({len(win)})")
+    strides = [strides] * r if isinstance(strides, int) else [int(s) for s in strides]
+    dil = [window_dilations] * r if isinstance(window_dilations, int) else [int(d) for d in window_dilations]
+    if len(strides) != r or len(dil) != r:
+        raise ValueError("invalid stride or dilation dimensions, rank must match the shape")
+    if _b.any(d < 1 for d in dil):
+        raise ValueError(f"dilation rates must be greater than or equal to 1 got {dil}")
+    kern = [(w - 1) * d + 1 for w, d in zip(win, dil)]
+    if padding == "valid":
+        pads = [(0, 0)] * r
+    elif padding == "same":
+        pads = [((k - 1) // 2, (k - 1) - (k - 1) // 2) for k in kern]
+    else:
+        pads = [(int(lo), int(hi)) for lo, hi in padding]
+        if len(pads) != r or _b.any(lo < 0 or hi < 0 for lo, hi in pads):
+            raise ValueError("padding must be a list of non-negative {low, high} pairs, one per axis")
+    shape = []
+    for d, k, s, (lo, hi) in zip(x.shape, kern, strides, pads):
+        n = (d + lo + hi - k) // s + 1
+        if n <= 0:
+            raise ValueError("window dimensions would result in empty tensor which is not currently supported in Nx")
+        shape.append(n)
+    out = _out(x.type, shape)
+    ints = win + strides + [p[0] for p in pads] + [p[1] for p in pads] + dil
+    return _dispatch(lambda a: E.node(out, op, [a], ints=ints), [x])
+
+
+def window_sum(x, window_dimensions, strides=1, padding="valid", window_dilations=1):
+    """``Nx.window_sum/3``."""
+    return _window("window_sum", x, window_dimensions, strides, padding, window_dilations)
+
+
+def window_max(x, window_dimensions, strides=1, padding="valid", window_dilations=1):
+    """``Nx.window_max/3``: padding contributes the type's minimum (-inf for floats)."""
+    return _window("window_max", x, window_dimensions, strides, padding, window_dilations)
+
+
+def window_min(x, window_dimensions, strides=1, padding="valid", window_dilations=1):
+    """``Nx.window_min/3``."""
+    return _window("window_min", x, window_dimensions, strides, padding, window_dilations)
+
+
+def window_product(x, window_dimensions, strides=1, padding="valid", window_dilations=1):
+    """``Nx.window_product/3``."""
+    return _window("window_product", x, window_dimensions, strides, padding, window_dilations)
+
+
+def window_mean(x, window_dimensions, strides=1, padding="valid", window_dilations=1):
+    """``Nx.window_mean/3``: the window sum over the window's element count."""
+    s = window_sum(x, window_dimensions, strides, padding, window_dilations)
+    return divide(s, math.prod(int(w) for w in window_dimensions))
+
+
+def _to_last(x, axis):
+    a = _norm_axis(x.rank, axis)
+    perm = [i for i in range(x.rank) if i != a] + [a]
+    inv = [0] * x.rank
+    for i, p in enumerate(perm):
+        inv[p] = i
+    return (x if a == x.rank - 1 else transpose(x, perm)), (None if a == x.rank - 1 else inv)
+
+
+def _direction(direction):
+    if direction not in ("asc", "desc"):
+        raise ValueError(f"unknown value for :direction, expected :asc or :desc, got: {direction!r}")
+    return 1 if direction == "desc" else 0
+
+
+def sort(x, axis=0, direction="asc"):
+    """``Nx.sort/2`` (nx/lib/nx.ex:15600-15720): NaN sorts higher than any other value.  The kernel
+    sorts the last axis; another axis is moved there and back."""
+    x = _as_operand(x)
+    if x.rank == 0:
+        raise ValueError("cannot sort a scalar")
+    desc = _direction(direction)
+    t, inv = _to_last(x, axis)
+    out = _out(t.type, t.shape)
+    r = _dispatch(lambda a: E.node(out, "sort", [a], ints=[desc]), [t])
+    return r if inv is None else transpose(r, inv)
+
+
+def argsort(x, axis=0, direction="asc", stable=False, type="s32"):
+    """``Nx.argsort/2`` (nx/lib/nx.ex:15949-15990).  The result is always the stable permutation
+    (ties keep their order), which is also a valid answer when ``stable`` is false."""
+    x = _as_operand(x)
+    if x.rank == 0:
+        raise ValueError("cannot sort a scalar")
+    desc = _direction(direction)
+    t, inv = _to_last(x, axis)
+    out = _out(T.normalize(type), t.shape)
+    r = _dispatch(lambda a: E.node(out, "argsort", [a], ints=[desc, 1 if stable else 0]), [t])
+    return r if inv is None else transpose(r, inv)
+
+
+def top_k(x, k=1):
+    """``Nx.top_k/2`` (nx/lib/nx.ex top_k): the k largest entries along the last axis and their
+    indices (the first k of the descending sort / argsort)."""
+    x = _as_operand(x)
+    if x.rank == 0 or not 1 <= k <= x.shape[-1]:
+        raise ValueError(f"top_k input must have at least rank 1 and k must be in 1..{x.shape[-1] if x.rank else 0}")
+    last = x.rank - 1
+    values = slice_along_axis(sort(x, axis=last, direction="desc"), 0, k, axis=last)
+    indices = slice_along_axis(argsort(x, axis=last, direction="desc"), 0, k, axis=last)
+    return values, indices
+
+
+def conv(x, kernel, strides=1, padding="valid", input_dilation=1, kernel_dilation=1, feature_group_size=1,
+         batch_group_size=1, input_permutation=None, kernel_permutation=None, output_permutation=None):
+    """``Nx.conv/3`` (nx/lib/nx.ex:13757-13860; shape rule nx/lib/nx/shape.ex conv): input {N, C, spatial…},
+    kernel {Cout, C / groups, spatial…}, result {N, Cout, spatial…} in the floating type both merge to.
+
+    Lowered to ops the compiler already has: the input is padded (interior padding is the input
+    dilation), one strided slice per kernel position gives the patches, and a `dot` over (channel,
+    kernel position) does the arithmetic - on the tensor cores for 16-bit types."""
+    x, kernel = _as_operand(x), _as_operand(kernel)
+    if x.rank < 3 or kernel.rank != x.rank:
+        raise ValueError(f"input and kernel must have the same rank of at least 3, got {x.shape} and {kernel.shape}")
+    if batch_group_size != 1:
+        raise NotImplementedError("conv with batch_group_size > 1 is not implemented")
+    type = T.to_floating(T.merge(x.type, kernel.type))
+    nsp = x.rank - 2
+    if input_permutation is not None:
+        x = transpose(x, list(input_permutation))
+    if kernel_permutation is not None:
+        kernel = transpose(kernel, list(kernel_permutation))
+    x, kernel = as_type(x, type), as_type(kernel, type)
+    many = lambda v: [int(v)] * nsp if isinstance(v, int) else [int(i) for i in v]
+    strides, idil, kdil = many(strides), many(input_dilation), many(kernel_dilation)
+    n, c = x.shape[:2]
+    cout, cin = kernel.shape[:2]
+    ks = list(kernel.shape[2:])
+    groups = int(feature_group_size)
+    if c != cin * groups or cout % groups != 0:
+        raise ValueError(f"size of input channels divided by feature groups must match size of kernel channels, got {c} / {groups} != {cin}")
+    kd = [(k - 1) * d + 1 for k, d in zip(ks, kdil)]
+    if padding == "valid":
+        pads = [(0, 0)] * nsp
+    elif padding == "same":
+        pads = [((k - 1) // 2, (k - 1) - (k - 1) // 2) for k in kd]
+    else:
+        pads = [(int(lo), int(hi)) for lo, hi in padding]
+        if len(pads) != nsp:
+            raise ValueError("padding must have one {low, high} pair per spatial dimension")
+    xp = pad(x, 0.0, [(0, 0, 0), (0, 0, 0)] + [(lo, hi, d - 1) for (lo, hi), d in zip(pads, idil)])
+    xp = as_type(xp, type)
+    osp = []
+    for d, k, s in zip(xp.shape[2:], kd, strides):
+        o = (d - k) // s + 1
+        if o <= 0:
+            raise ValueError("convolution would result in an empty tensor")
+        osp.append(o)
+    import itertools
+    patches = []
+    for pos in itertools.product(*[range(k) for k in ks]):
+        starts = [0, 0] + [p * d for p, d in zip(pos, kdil)]
+        lengths = [n, c] + [(o - 1) * s + 1 for o, s in zip(osp, strides)]
+        patches.append(slice(xp, starts, lengths, [1, 1] + strides))
+    kvol = len(patches)
+    cols = stack(patches, axis=2)                                        # {N, C, K, spatial…}
+    w = reshape(kernel, (cout, cin, kvol))
+    outs = []
+    cg = cout // groups
+    for g in range(groups):
+        xg = cols if groups == 1 else slice_along_axis(cols, g * cin, cin, axis=1)
+        wg = w if groups == 1 else slice_along_axis(w, g * cg, cg, axis=0)
+        outs.append(dot(xg, [1, 2], [], wg, [1, 2], []))                 # {N, spatial…, Cout / groups}
+    y = outs[0] if groups == 1 else concatenate(outs, axis=nsp + 1)
+    y = transpose(y, [0, nsp + 1] + list(range(1, nsp + 1)))             # {N, Cout, spatial…}
+    if output_permutation is not None:
+        perm = list(output_permutation)
+        inv = [0] * len(perm)
+        for i, p in enumerate(perm):
+            inv[p] = i
+        y = transpose(y, inv)
+    return y
+
+
 def pad(x, pad_value, padding_config):
     """``Nx.pad/3`` (nx/lib/nx.ex pad; shape rule nx/lib/nx/shape.ex:1038-1090): per axis
     ``(low, high, interior)``; negative edges crop."""

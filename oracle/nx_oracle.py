@@ -523,6 +523,40 @@ def evaluate(nodes, outs, params, mode="xla_like", all_reduce=None):
             if len(arg) > 1:      # dynamic starts, clamped so that the window fits
                 st = [min(max(int(s), 0), d - l) for s, d, l in zip(arg[1:], arg[0].shape, ln)]
             v = arg[0][tuple(slice(s, s + l, d) for s, l, d in zip(st, ln, sd))]
+        elif op in ("window_sum", "window_max", "window_min", "window_product"):
+            # nx/lib/nx/binary_backend.ex:1447-1530: pad with the identity, then reduce each window
+            r = arg[0].ndim
+            win, st, lo, hi, dil = (nd.ints[i * r:(i + 1) * r] for i in range(5))
+            npt = NP[t]
+            if op == "window_sum":
+                ident = 0
+            elif op == "window_product":
+                ident = 1
+            elif np.issubdtype(npt, np.floating):
+                ident = -np.inf if op == "window_max" else np.inf
+            else:
+                ident = np.iinfo(npt).min if op == "window_max" else np.iinfo(npt).max
+            x = np.pad(arg[0], list(zip(lo, hi)), constant_values=ident)
+            fn = {"window_sum": np.add, "window_product": np.multiply, "window_max": np.maximum, "window_min": np.minimum}[op]
+            acc = None
+            for pos in np.ndindex(*win):
+                sl = tuple(slice(p * d, p * d + (n - 1) * s + 1, s) for p, d, n, s in zip(pos, dil, nd.shape, st))
+                term = x[sl].astype(npt)
+                with np.errstate(over="ignore"):
+                    acc = term if acc is None else fn(acc, term).astype(npt)
+            v = _store(acc.astype(np.float64) if is_float(t) else acc, t, mode) if is_float(t) else acc
+        elif op in ("sort", "argsort"):
+            # nx/lib/nx.ex:15676-15689: NaN sorts higher than any other value; ties keep their order
+            a = arg[0]
+            desc = bool(nd.ints[0])
+            pos = np.broadcast_to(np.arange(a.shape[-1]), a.shape)
+            if is_float(at[0]):
+                nan = np.isnan(a)
+                val = np.where(nan, 0.0, a).astype(np.float64)
+                order = np.lexsort((pos, -val, ~nan) if desc else (pos, val, nan), axis=-1)
+            else:
+                order = np.lexsort((pos, ~a if desc else a), axis=-1)       # ~v reverses integer order without overflow
+            v = np.take_along_axis(a, order, axis=-1) if op == "sort" else order.astype(NP[t])
         elif op == "reverse":
             v = np.flip(arg[0], axis=tuple(nd.ints))
         elif op == "pad":

@@ -250,3 +250,61 @@ case("take_along_axis 0", "nx/lib/nx.ex:14849-14858", lambda t, i: nx.take_along
      [([[1, 5, 6], [4, 2, 3], [1, 5, 3]], "s32")])
 case("stack", "nx/lib/nx.ex stack doctest", lambda a, b: nx.stack([a, b], axis=1),
      [([1, 2, 3], "s32"), ([4, 5, 6], "s32")], [([[1, 4], [2, 5], [3, 6]], "s32")])
+
+# ---- window reductions: exla/test/exla/defn/expr_test.exs:2309-2600 -------------------------------------
+W3 = [[[1, 2, 3], [4, 5, 6]], [[1, 2, 3], [4, 5, 6]]]
+WF = [[[4.0, 2.0, 3.0], [2.0, 5.0, 6.5]], [[1.2, 2.2, 3.2], [4.0, 5.0, 6.2]]]
+_P2 = dict(strides=[1, 2, 3], padding=[(0, 1), (2, 0), (1, 1)])
+_P3 = dict(strides=[2, 1, 1], padding=[(1, 1), (0, 0), (1, 1)])
+case("window_sum", "exla/test/exla/defn/expr_test.exs:2323-2326", lambda t: nx.window_sum(t, (1, 2, 1)), [(W3, "s32")],
+     [([[[5, 7, 9]], [[5, 7, 9]]], "s32")])
+case("window_sum strides + padding", "exla/test/exla/defn/expr_test.exs:2328-2331", lambda t: nx.window_sum(t, (2, 2, 1), **_P2),
+     [(W3, "s32")], [([[[0, 0], [0, 18]], [[0, 0], [0, 9]]], "s32")])
+case("window_sum float padding", "exla/test/exla/defn/expr_test.exs:2333-2341", lambda t: nx.window_sum(t, (2, 1, 1), **_P3),
+     [(WF, "f32")], [([[[0.0, 4.0, 2.0, 3.0, 0.0], [0.0, 2.0, 5.0, 6.5, 0.0]], [[0.0, 1.2, 2.2, 3.2, 0.0], [0.0, 4.0, 5.0, 6.2, 0.0]]], "f32")])
+case("window_max", "exla/test/exla/defn/expr_test.exs:2428-2431", lambda t: nx.window_max(t, (1, 2, 1)), [(W3, "s32")],
+     [([[[4, 5, 6]], [[4, 5, 6]]], "s32")])
+_MIN = -2147483648
+case("window_max strides + padding", "exla/test/exla/defn/expr_test.exs:2433-2445", lambda t: nx.window_max(t, (2, 2, 1), **_P2),
+     [(W3, "s32")], [([[[_MIN, _MIN], [_MIN, 6]], [[_MIN, _MIN], [_MIN, 6]]], "s32")])
+case("window_max float padding", "exla/test/exla/defn/expr_test.exs:2447-2461", lambda t: nx.window_max(t, (2, 1, 1), **_P3),
+     [(WF, "f32")], [([[[-INF, 4.0, 2.0, 3.0, -INF], [-INF, 2.0, 5.0, 6.5, -INF]], [[-INF, 1.2, 2.2, 3.2, -INF], [-INF, 4.0, 5.0, 6.2, -INF]]], "f32")])
+case("window_min", "exla/test/exla/defn/expr_test.exs:2493-2496", lambda t: nx.window_min(t, (1, 2, 1)), [(W3, "s32")],
+     [([[[1, 2, 3]], [[1, 2, 3]]], "s32")])
+case("window_product", "exla/test/exla/defn/expr_test.exs:2563-2566", lambda t: nx.window_product(t, (1, 2, 1)), [(W3, "s32")],
+     [([[[4, 10, 18]], [[4, 10, 18]]], "s32")])
+case("window_mean", "nx/lib/nx.ex:11235-11250", lambda t: nx.window_mean(t, (1, 2, 1)), [(W3, "s32")],
+     [([[[2.5, 3.5, 4.5]], [[2.5, 3.5, 4.5]]], "f32")])
+
+# ---- conv: nx/lib/nx.ex:13684-13740 (doctests) ---------------------------------------------------------
+_I33 = [[[[0, 1, 2], [3, 4, 5], [6, 7, 8]]]]
+case("conv 1x1 kernels", "nx/lib/nx.ex:13684-13713", lambda a, b: nx.conv(a, b, strides=[1, 1]),
+     [(_I33, "s32"), ([[[[0]]], [[[1]]], [[[2]]], [[[3]]]], "s32")],
+     [([[[[0.0] * 3] * 3, [[0.0, 1.0, 2.0], [3.0, 4.0, 5.0], [6.0, 7.0, 8.0]], [[0.0, 2.0, 4.0], [6.0, 8.0, 10.0], [12.0, 14.0, 16.0]],
+         [[0.0, 3.0, 6.0], [9.0, 12.0, 15.0], [18.0, 21.0, 24.0]]]], "f32")])
+case("conv strides, same padding, kernel dilation", "nx/lib/nx.ex:13715-13740",
+     lambda a, b: nx.conv(a, b, strides=2, padding="same", kernel_dilation=[2, 1]),
+     [(_I33, "s32"), ([[[[0], [1]]], [[[2], [3]]], [[[4], [5]]], [[[6], [7]]]], "s32")],
+     [([[[[3.0, 5.0], [0.0, 0.0]], [[9.0, 15.0], [6.0, 10.0]], [[15.0, 25.0], [12.0, 20.0]], [[21.0, 35.0], [18.0, 30.0]]]], "f32")])
+
+# ---- sort / argsort / top_k: nx/lib/nx.ex:15538-15689, 15730-15800, 15880-15945 -------------------------
+_S23 = [[3, 1, 7], [2, 5, 4]]
+_S233 = [[[4, 9, 8], [2, 1, 3], [2, 0, 2]], [[1, 5, 2], [2, 5, 3], [5, 1, 4]]]
+case("sort 1d", "nx/lib/nx.ex:15538-15542", lambda t: nx.sort(t), [([16, 23, 42, 4, 8, 15], "s32")], [([4, 8, 15, 16, 23, 42], "s32")])
+case("sort axis 0", "nx/lib/nx.ex:15544-15552", lambda t: nx.sort(t, axis=0), [(_S23, "s32")], [([[2, 1, 4], [3, 5, 7]], "s32")])
+case("sort axis 1", "nx/lib/nx.ex:15554-15562", lambda t: nx.sort(t, axis=1), [(_S23, "s32")], [([[1, 3, 7], [2, 4, 5]], "s32")])
+case("sort rank 3 axis 0", "nx/lib/nx.ex:15627-15642", lambda t: nx.sort(t, axis=0), [(_S233, "s32")],
+     [([[[1, 5, 2], [2, 1, 3], [2, 0, 2]], [[4, 9, 8], [2, 5, 3], [5, 1, 4]]], "s32")])
+case("sort rank 3 axis 1", "nx/lib/nx.ex:15643-15658", lambda t: nx.sort(t, axis=1), [(_S233, "s32")],
+     [([[[2, 0, 2], [2, 1, 3], [4, 9, 8]], [[1, 1, 2], [2, 5, 3], [5, 5, 4]]], "s32")])
+case("sort rank 3 axis 2", "nx/lib/nx.ex:15659-15674", lambda t: nx.sort(t, axis=2), [(_S233, "s32")],
+     [([[[4, 8, 9], [1, 2, 3], [0, 2, 2]], [[1, 2, 5], [2, 3, 5], [1, 4, 5]]], "s32")])
+case("sort NaN and infinities", "nx/lib/nx.ex:15679-15684", lambda t: nx.sort(t), [([NAN, -INF, 0.0, INF], "f32")],
+     [([-INF, 0.0, INF, NAN], "f32")])
+case("sort desc NaN first", "nx/lib/nx.ex:15685-15689", lambda t: nx.sort(t, direction="desc"), [([NAN, -INF, 0.0, INF], "f32")],
+     [([NAN, INF, 0.0, -INF], "f32")])
+case("argsort 1d", "nx/lib/nx.ex argsort doctest", lambda t: nx.argsort(t), [([16, 23, 42, 4, 8, 15], "s32")], [([3, 4, 5, 0, 1, 2], "s32")])
+case("argsort ties are stable", "nx/lib/nx.ex argsort stable: true", lambda t: nx.argsort(t, axis=1, direction="desc", stable=True),
+     [([[1, 3, 3, 1], [2, 2, 5, 2]], "s32")], [([[1, 2, 0, 3], [2, 0, 1, 3]], "s32")])
+case("top_k", "nx/lib/nx.ex top_k doctest", lambda t: nx.top_k(t, k=2), [([[1, 5, 3], [9, 2, 7]], "s32")],
+     [([[5, 3], [9, 7]], "s32"), ([[1, 2], [0, 2]], "s32")])

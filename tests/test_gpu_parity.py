@@ -378,3 +378,58 @@ def test_pad_and_reverse_fuse_into_consumers():
     idx = rng.integers(0, 9, (5, 7, 4))
     res = run_both(lambda t, i: nx.take_along_axis(t, i, axis=2), [x, idx], ["f32", "s32"])
     assert np.array_equal(res[0][0], np.take_along_axis(x, idx, axis=2)) and np.array_equal(res[0][0], res[0][1])
+
+
+def test_window_reductions_pooling_shapes():
+    """2x2 / 3x3 pooling over {N,C,H,W} as a CNN uses it, with strides, :same padding and dilation."""
+    rng = np.random.default_rng(41)
+    x = rng.normal(0, 1, (2, 3, 17, 20)).astype(np.float32)
+    for fn in (nx.window_max, nx.window_sum, nx.window_min, nx.window_mean):
+        check(run_both(lambda t: fn(t, (1, 1, 2, 2), strides=[1, 1, 2, 2]), [x], ["f32"]), "2x2 stride 2")
+        check(run_both(lambda t: fn(t, (1, 1, 3, 3), strides=[1, 1, 2, 1], padding="same"), [x], ["f32"]), "3x3 same")
+        check(run_both(lambda t: fn(t, (1, 1, 2, 3), padding=[(0, 0), (0, 0), (1, 2), (3, 0)], window_dilations=[1, 1, 2, 2]), [x], ["f32"]), "dilated")
+    xi = rng.integers(-50, 50, (4, 9, 11))
+    for fn in (nx.window_max, nx.window_sum, nx.window_product):
+        check(run_both(lambda t: fn(t, (2, 3, 1), strides=[1, 2, 3], padding=[(0, 1), (2, 0), (1, 1)]), [xi], ["s32"]), "integers")
+    check(run_both(lambda t: nx.exp(nx.window_max(t, (1, 1, 2, 2), strides=[1, 1, 2, 2])) + 1.0, [x], ["bf16"]), "bf16 pooled then exp")
+
+
+def test_conv_on_the_device():
+    """Nx.conv (lowered to pad / strided slices / dot): f32 and bf16 images, strides, padding, dilation, groups."""
+    rng = np.random.default_rng(51)
+    x = rng.normal(0, 1, (2, 8, 14, 12)).astype(np.float32)
+    w = rng.normal(0, 0.3, (16, 8, 3, 3)).astype(np.float32)
+    for opts in (dict(), dict(strides=[2, 1], padding="same"), dict(padding=[(1, 0), (-1, 2)], kernel_dilation=[2, 1]),
+                 dict(padding="same", input_dilation=[1, 2])):
+        check(run_both(lambda a, b: nx.conv(a, b, **opts), [x, w], ["f32", "f32"]), f"conv {opts}")
+    wg = rng.normal(0, 0.3, (16, 2, 3, 3)).astype(np.float32)
+    check(run_both(lambda a, b: nx.conv(a, b, feature_group_size=4, padding="same"), [x, wg], ["f32", "f32"]), "grouped conv")
+    res = run_both(lambda a, b: nx.max(nx.conv(a, b, padding="same"), 0.0), [x, w], ["bf16", "bf16"])
+    assert res[0][2] == ("bf", 16)
+    check(res, "bf16 conv + relu")
+
+
+def test_sort_argsort_top_k():
+    """Bitonic rows in shared memory: every element type, both directions, ties (stable), NaN / -0.0,
+    lengths around the powers of two, another axis, and top_k as a sampling step would use it."""
+    rng = np.random.default_rng(61)
+    for length in (1, 2, 31, 32, 33, 1000, 4096, 5000, 16384):
+        x = rng.normal(0, 1, (3, length)).astype(np.float32)
+        x[0, : length // 3] = x[0, 0]                                        # ties
+        if length > 4:
+            x[1, 1], x[1, 3], x[2, 0], x[2, 2] = np.nan, np.inf, -0.0, 0.0
+        for d in ("asc", "desc"):
+            res = run_both(lambda t: (nx.sort(t, axis=1, direction=d), nx.argsort(t, axis=1, direction=d)), [x], ["f32"])
+            assert np.array_equal(res[0][0], res[0][1], equal_nan=True), (length, d)
+            assert np.array_equal(res[1][0], res[1][1]), (length, d, "argsort")
+    for ty in ("s8", "u8", "s16", "u32", "s64", "u64", "f64", "bf16", "f16"):
+        a = rng.integers(-100, 100, (5, 77)) if ty[0] == "s" else rng.integers(0, 200, (5, 77)) if ty[0] == "u" else rng.normal(0, 3, (5, 77))
+        res = run_both(lambda t: (nx.sort(t, axis=1, direction="desc"), nx.argsort(t, axis=1)), [a], [ty])
+        assert np.array_equal(res[0][0], res[0][1]) and np.array_equal(res[1][0], res[1][1]), ty
+    y = rng.normal(0, 1, (4, 50, 6)).astype(np.float32)
+    res = run_both(lambda t: (nx.sort(t, axis=1), nx.argsort(t, axis=0, direction="desc", type="s64")), [y], ["f32"])
+    assert np.array_equal(res[0][0], np.sort(y, axis=1)) and np.array_equal(res[1][0], res[1][1]) and res[1][2] == ("s", 64)
+    logits = rng.normal(0, 1, (8, 8000)).astype(np.float32)
+    res = run_both(lambda t: nx.top_k(nx.exp(t) / nx.sum(nx.exp(t), axes=[1], keep_axes=True), k=40), [logits], ["f32"])
+    assert np.array_equal(res[1][0], np.argsort(-logits, axis=1, kind="stable")[:, :40])
+    check(res[:1], "top-k probabilities")
