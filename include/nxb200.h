@@ -121,8 +121,10 @@ int nxb200_buffer_release(nxb200_buffer *buf);
  * integer start per axis, and the starts attribute is ignored); gather [axes…]
  * (arguments: tensor, indices); put_slice none (arguments: tensor, slice, one
  * scalar integer start per axis); pad [lows…, highs…, interiors…] (arguments:
- * tensor, scalar pad value); reverse [axes…]; concatenate [axis]; everything
- * else none.
+ * tensor, scalar pad value); reverse [axes…]; window_sum/max/min/product
+ * [window…, strides…, low padding…, high padding…, dilations…]; sort
+ * [descending] and argsort [descending, stable], both along the last axis;
+ * concatenate [axis]; everything else none.
  *
  * Building needs no GPU (kernels are generated and compiled for sm_100a on
  * the host); the first run on a device loads them. */
