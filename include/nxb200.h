@@ -85,6 +85,16 @@ int nxb200_buffer_info(nxb200_buffer *buf, nxb200_dtype *dtype, int64_t *dims, i
 /* Raw device address, for interop and benchmarks (get_buffer_device_pointer,
  * exla.cc:325-389, :local mode only). */
 int nxb200_buffer_device_pointer(nxb200_buffer *buf, void **ptr);
+/* Nx.from_pointer / Nx.to_pointer (exla/lib/exla/backend.ex:86-181; create_buffer_from_device_pointer
+ * and get_buffer_device_pointer, exla.cc:325-437).  from_pointer wraps device memory the caller owns
+ * (never freed by the library).  ipc_export gives the CUDA IPC handle of a tensor this library
+ * allocated; from_ipc, in ANOTHER process, maps it (unmapped again by deallocate / release). */
+#define NXB_IPC_HANDLE_BYTES 64
+int nxb200_buffer_from_pointer(int device, nxb200_dtype dtype, const int64_t *dims, int rank,
+                               void *device_ptr, nxb200_buffer **out);
+int nxb200_buffer_ipc_export(nxb200_buffer *buf, uint8_t handle[NXB_IPC_HANDLE_BYTES]);
+int nxb200_buffer_from_ipc(int device, nxb200_dtype dtype, const int64_t *dims, int rank,
+                           const uint8_t handle[NXB_IPC_HANDLE_BYTES], nxb200_buffer **out);
 /* deallocate_device_mem (exla.cc:462-475): frees the device memory now; a
  * second call returns NXB_ERR_ALREADY_DEALLOCATED; any later use of the
  * handle fails with NXB_ERR_RUNTIME.  The handle itself stays valid until

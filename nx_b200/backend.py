@@ -11,6 +11,7 @@ implementation to fall back to.
 from __future__ import annotations
 
 import ctypes as C
+import math
 import threading
 
 from . import expr as E
@@ -120,6 +121,54 @@ def to_host(t):
     if isinstance(t.data, HostData):
         return t
     return Tensor(HostData(to_binary(t)), t.type, t.shape)
+
+
+class Pointer:
+    """``%Nx.Pointer{kind, address, handle, data_size}`` (nx/lib/nx/pointer.ex)."""
+    __slots__ = ("kind", "address", "handle", "data_size")
+
+    def __init__(self, kind, address=None, handle=None, data_size=0):
+        self.kind, self.address, self.handle, self.data_size = kind, address, handle, data_size
+
+
+def to_pointer(t, mode="local"):
+    """``Nx.to_pointer/2`` (exla/lib/exla/backend.ex:86-134): ``"local"`` gives the device address,
+    ``"ipc"`` a CUDA IPC handle another process can map (``address`` then holds the device id)."""
+    if not isinstance(t.data, DeviceBuffer):
+        raise ValueError("tensor must be allocated on the device")
+    size = t.size * T.itemsize(t.type)
+    l = nif.lib()
+    if mode == "local":
+        p = C.c_void_p()
+        nif.check(l.nxb200_buffer_device_pointer(t.data.handle, C.byref(p)))
+        return Pointer("local", address=p.value, data_size=size)
+    if mode == "ipc":
+        h = C.create_string_buffer(64)
+        nif.check(l.nxb200_buffer_ipc_export(t.data.handle, h))
+        return Pointer("ipc", address=t.data.device, handle=h.raw, data_size=size)
+    raise ValueError(f"expected one of :local, :ipc, got: {mode!r}")
+
+
+def from_pointer(pointer, type, shape, device=None):
+    """``Nx.from_pointer/5`` (exla/lib/exla/backend.ex:137-181): a tensor over memory someone else
+    owns - a device address of this process, or an IPC handle exported by another one."""
+    from .nx import Tensor
+    type = T.normalize(type)
+    shape = tuple(int(d) for d in shape)
+    want = math.prod(shape) * T.itemsize(type)
+    if pointer.data_size != want:
+        raise ValueError(f"invalid pointer data_size for shape, expected: {want}, got: {pointer.data_size}")
+    dev = _device_of(device)
+    l = nif.lib()
+    h = C.c_void_p()
+    dims = nif.dims_array(shape)
+    if pointer.kind == "local":
+        nif.check(l.nxb200_buffer_from_pointer(dev, T.DTYPE_CODES[type], dims, len(shape), C.c_void_p(pointer.address), C.byref(h)))
+    elif pointer.kind == "ipc":
+        nif.check(l.nxb200_buffer_from_ipc(dev, T.DTYPE_CODES[type], dims, len(shape), pointer.handle, C.byref(h)))
+    else:
+        raise ValueError(f"unknown pointer kind {pointer.kind!r}")
+    return Tensor(DeviceBuffer(h.value, dev), type, shape)
 
 
 def backend_deallocate(t):

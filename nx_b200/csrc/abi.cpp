@@ -138,7 +138,7 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         // a result that takes over a donated argument's buffer is written straight into it
         void* taken = nullptr;
         for (auto& al : plan.aliases)
-          if (al.output == i && al.in_place && !args[al.param]->deallocated.load()) taken = args[al.param]->ptr;
+          if (al.output == i && al.in_place && !args[al.param]->deallocated.load() && !args[al.param]->borrowed) taken = args[al.param]->ptr;
         b->ptr = taken ? taken : d.alloc.alloc(sl.nbytes);
         ptr[plan.output_slots[i]] = b->ptr;
         made.push_back(b.release());
@@ -512,6 +512,74 @@ int nxb200_buffer_device_pointer(nxb200_buffer* buf, void** ptr) {
   });
 }
 
+/* create_buffer_from_device_pointer, :local mode (exla/lib/exla/backend.ex:137-181, exla.cc:391-437) */
+int nxb200_buffer_from_pointer(int dev, nxb200_dtype dtype, const int64_t* dims, int rank, void* device_ptr, nxb200_buffer** out) {
+  return guarded([&] {
+    if (!out || !device_ptr) fail(NXB_ERR_INVALID_ARGUMENT, "out or the device pointer is NULL");
+    if (rank < 0 || rank > NXB_MAX_RANK) fail(NXB_ERR_INVALID_ARGUMENT, "rank out of range");
+    if ((int)dtype < 0 || dtype > NXB_F64) fail(NXB_ERR_INVALID_ARGUMENT, "unknown element type");
+    nxb::device(dev);
+    cudaPointerAttributes at{};
+    if (cudaPointerGetAttributes(&at, device_ptr) != cudaSuccess || at.type != cudaMemoryTypeDevice || at.device != dev) {
+      (void)cudaGetLastError();
+      fail(NXB_ERR_INVALID_ARGUMENT, "the address is not device memory of device " + std::to_string(dev));
+    }
+    auto b = std::make_unique<nxb200_buffer>();
+    b->device = dev;
+    b->dtype = (DType)dtype;
+    for (int i = 0; i < rank; ++i) {
+      if (dims[i] < 0) fail(NXB_ERR_INVALID_ARGUMENT, "negative dimension");
+      b->dims.push_back(dims[i]);
+    }
+    b->nbytes = (size_t)shape_numel(b->dims) * dtype_size(b->dtype);
+    b->ptr = device_ptr;
+    b->borrowed = true;
+    *out = b.release();
+  });
+}
+
+/* get_buffer_device_pointer, :cuda_ipc mode (exla.cc:325-389; exla_cuda.cc) */
+int nxb200_buffer_ipc_export(nxb200_buffer* buf, uint8_t handle[NXB_IPC_HANDLE_BYTES]) {
+  return guarded([&] {
+    nxb200_buffer* b = check_buffer(buf);
+    if (!handle) fail(NXB_ERR_INVALID_ARGUMENT, "handle is NULL");
+    if (b->borrowed) fail(NXB_ERR_INVALID_ARGUMENT, "only memory this library allocated can be exported");
+    Device& d = nxb::device(b->device);
+    NXB_CUDA(cudaStreamSynchronize(d.stream));          // the importer sees finished data
+    cudaIpcMemHandle_t h;
+    NXB_CUDA(cudaIpcGetMemHandle(&h, b->ptr));
+    static_assert(sizeof h == NXB_IPC_HANDLE_BYTES, "IPC handle size");
+    memcpy(handle, &h, sizeof h);
+  });
+}
+
+/* create_buffer_from_device_pointer, :cuda_ipc mode: maps another process's allocation */
+int nxb200_buffer_from_ipc(int dev, nxb200_dtype dtype, const int64_t* dims, int rank, const uint8_t handle[NXB_IPC_HANDLE_BYTES], nxb200_buffer** out) {
+  return guarded([&] {
+    if (!out || !handle) fail(NXB_ERR_INVALID_ARGUMENT, "out or handle is NULL");
+    if (rank < 0 || rank > NXB_MAX_RANK) fail(NXB_ERR_INVALID_ARGUMENT, "rank out of range");
+    if ((int)dtype < 0 || dtype > NXB_F64) fail(NXB_ERR_INVALID_ARGUMENT, "unknown element type");
+    nxb::device(dev);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof h);
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      (void)cudaGetLastError();
+      fail(NXB_ERR_RUNTIME, std::string("the IPC handle could not be opened: ") + cudaGetErrorString(e));
+    }
+    auto b = std::make_unique<nxb200_buffer>();
+    b->device = dev;
+    b->dtype = (DType)dtype;
+    for (int i = 0; i < rank; ++i) b->dims.push_back(dims[i]);
+    b->nbytes = (size_t)shape_numel(b->dims) * dtype_size(b->dtype);
+    b->ptr = p;
+    b->borrowed = true;
+    b->ipc_base = p;
+    *out = b.release();
+  });
+}
+
 int nxb200_buffer_deallocate(nxb200_buffer* buf) {
   return guarded([&] {
     nxb200_buffer* b = check_buffer(buf, false);
@@ -520,7 +588,12 @@ int nxb200_buffer_deallocate(nxb200_buffer* buf) {
     Device& d = nxb::device(b->device);
     std::lock_guard<std::mutex> g(d.mu);
     order_after_downloads(d);      // whoever gets this memory next writes it on the compute stream
-    d.alloc.free(b->ptr);
+    if (b->ipc_base) {
+      cudaStreamSynchronize(d.stream);
+      cudaIpcCloseMemHandle(b->ipc_base);
+      b->ipc_base = nullptr;
+    }
+    d.alloc.free(b->ptr);          // (a no-op for memory the allocator does not know)
     b->ptr = nullptr;
   });
 }
@@ -538,6 +611,10 @@ int nxb200_buffer_release(nxb200_buffer* buf) {
     if (!b->deallocated.exchange(true) && b->ptr) {
       Device& d = nxb::device(b->device);
       std::lock_guard<std::mutex> g(d.mu);
+      if (b->ipc_base) {
+        cudaStreamSynchronize(d.stream);
+        cudaIpcCloseMemHandle(b->ipc_base);
+      }
       d.alloc.free(b->ptr);
     }
     b->magic = 0;

@@ -129,4 +129,8 @@ struct nxb200_buffer {
   void* ptr = nullptr;
   size_t nbytes = 0;
   std::atomic<bool> deallocated{false};
+  // Memory the library does not own: a pointer the caller lent (from_pointer), or another
+  // process's allocation mapped through CUDA IPC (`ipc_base` is then what has to be unmapped).
+  bool borrowed = false;
+  void* ipc_base = nullptr;
 };

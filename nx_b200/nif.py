@@ -78,6 +78,9 @@ def _declare(l):
         "nxb200_device_stream": [i32, p(vp)],
         "nxb200_memory_stats": [i32, p(C.c_uint64), p(C.c_uint64), p(C.c_uint64)],
         "nxb200_memory_reset_peak": [i32],
+        "nxb200_buffer_from_pointer": [i32, i32, C.POINTER(C.c_int64), i32, vp, C.POINTER(vp)],
+        "nxb200_buffer_ipc_export": [vp, C.c_char_p],
+        "nxb200_buffer_from_ipc": [i32, i32, C.POINTER(C.c_int64), i32, C.c_char_p, C.POINTER(vp)],
         "nxb200_comm_id": [C.c_char_p],
         "nxb200_comm_init": [i32, i32, i32, C.c_char_p],
         "nxb200_comm_all_reduce_sum": [vp],
