@@ -33,7 +33,7 @@ class DeviceBuffer:
 
     def __del__(self):
         h, self.handle = self.handle, None
-        if h and nif._LIB is not None:
+        if h and getattr(nif, "_LIB", None) is not None:
             try:
                 nif._LIB.nxb200_buffer_release(h)
             except Exception:

@@ -278,6 +278,13 @@ private:
     while (a >= 0 && g_.nodes[a].alias >= 0) a = g_.nodes[a].alias;
     return a == acc_node;
   }
+  // the value (or the value a reshape / squeeze / metadata chain renames) is computed by this kernel:
+  // it must be taken from registers, its buffer is not written yet
+  bool made_here(int n) const {
+    for (int a = n; a >= 0; a = g_.nodes[a].alias)
+      if (produced.count(a) || std::count(reduces.begin(), reduces.end(), a)) return true;
+    return false;
+  }
   int level(int n);
   Val value(int n, const std::vector<Aff>& idx);
   Val load(int n, const std::vector<Aff>& idx);
@@ -385,7 +392,7 @@ int KernelBuilder::level(int n) {
   if (it != level_memo_.end()) return it->second;
   const Node& nd = g_.nodes[n];
   int l = 0;
-  bool ext = (nd.slot >= 0 && !produced.count(n) && !std::count(reduces.begin(), reduces.end(), n) && !aliases_acc(n)) || n == acc_node;
+  bool ext = (nd.slot >= 0 && !made_here(n) && !aliases_acc(n)) || n == acc_node;
   if (!ext) {
     if (is_reduce(nd)) {
       if (!std::count(reduces.begin(), reduces.end(), n)) throw FusionError("reduction outside the kernel is not materialised");
@@ -488,7 +495,6 @@ KernelBuilder::Val KernelBuilder::load(int n, const std::vector<Aff>& idx) {
 
 KernelBuilder::Val KernelBuilder::value(int n, const std::vector<Aff>& idx) {
   const Node& nd = g_.nodes[n];
-  bool in_red = std::count(reduces.begin(), reduces.end(), n) > 0;
   if (n == acc_node) {
     // the product's own element: only legal at the position this thread's accumulator holds
     auto st = cstrides(nd.shape);
@@ -512,7 +518,7 @@ KernelBuilder::Val KernelBuilder::value(int n, const std::vector<Aff>& idx) {
     elem_memo_[phase_][key] = v;
     return {v, true};
   }
-  if (nd.slot >= 0 && !produced.count(n) && !in_red && !aliases_acc(n)) return load(n, idx);
+  if (nd.slot >= 0 && !made_here(n) && !aliases_acc(n)) return load(n, idx);
   if (nd.op == "constant") {
     bool isf = !nd.flts.empty();
     return {literal(isf ? nd.flts[0] : 0.0, isf ? 0 : nd.ints[0], isf, nd.dt), false};
@@ -582,8 +588,18 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
     else {
       a = aff_const(nv_, 0);
       auto st = cstrides(nd.shape);
+      bool any_opaque = false;
+      for (auto& i : idx) any_opaque = any_opaque || i.opaque;
+      if (any_opaque) {                           // position computed from the index expressions themselves
+        std::string s;
+        for (size_t j = 0; j < idx.size(); ++j) {
+          if (nd.shape[j] == 1) continue;
+          s += (s.empty() ? "" : " + ") + std::string("(long long)") + std::to_string(st[j]) + " * (long long)" + affstr(idx[j], false);
+        }
+        if (s.empty()) s = "0ll";
+        return def(true, t, cvt("(" + s + ")", NXB_S64, t));
+      }
       for (size_t j = 0; j < idx.size(); ++j) {
-        if (idx[j].opaque) throw FusionError("iota over an opaque index");
         a.c += idx[j].c * st[j];
         for (int v = 0; v < nv_; ++v) a.k[v] += idx[j].k[v] * st[j];
       }
@@ -1045,7 +1061,7 @@ void KernelBuilder::configure() {
     if (!seen.insert(n).second) return;
     const Node& nd = g_.nodes[n];
     if (n == acc_node) return;
-    if (nd.slot >= 0 && !produced.count(n) && !std::count(reduces.begin(), reduces.end(), n) && !aliases_acc(n)) {
+    if (nd.slot >= 0 && !made_here(n) && !aliases_acc(n)) {
       if (strip_units(nd.shape) == strip_units(F_)) minsz = std::min(minsz, dtype_size(nd.dt));
       return;
     }

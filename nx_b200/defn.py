@@ -49,9 +49,10 @@ class Program:
 
     def __del__(self):
         h, self.handle = getattr(self, "handle", None), None
-        if h and nif._LIB is not None:
+        lib = getattr(nif, "_LIB", None)          # the module is already torn down at interpreter exit
+        if h and lib is not None:
             try:
-                nif._LIB.nxb200_program_release(h)
+                lib.nxb200_program_release(h)
             except Exception:
                 pass
 
@@ -459,3 +460,8 @@ def _map_tensors(fun, c):
     if isinstance(c, dict):
         return {k: _map_tensors(fun, v) for k, v in c.items()}
     return fun(c)
+
+
+# Nx.Defn.grad / value_and_grad (nx/lib/nx/defn.ex:760-850) live in grad.py; re-exported here because
+# that is where a caller of the reference looks for them.
+from .grad import grad, value_and_grad  # noqa: E402,F401
