@@ -166,7 +166,8 @@ def __compile__(key, templates, fun, opts):
     # the donation marks are part of the key: a donating call must not reuse the
     # non-donating executable (exla/lib/exla/defn.ex:337-353)
     args_key = tuple((t.type, t.shape, bool(getattr(t, "donatable", False))) for t in flat)
-    ck = (key, args_key, opts.get("device"))
+    hooks = opts.get("hooks") or {}
+    ck = (key, args_key, opts.get("device"), tuple(sorted((k, id(v)) for k, v in hooks.items())))
     with _cache_lock:
         entry = _cache.get(ck)
     if entry is None:
@@ -174,7 +175,7 @@ def __compile__(key, templates, fun, opts):
         # outputs that are parameters or constants still need a buffer of
         # their own: results are always fresh tensors (exla/lib/exla/defn.ex:387-393)
         donated = [i for i, t in enumerate(flat) if getattr(t, "donatable", False)]
-        entry = (_make_runner(outs, params, alias_pairs(donated, params, outs)), ospec)
+        entry = (_make_runner(outs, params, alias_pairs(donated, params, outs), hooks), ospec)
         with _cache_lock:
             _cache.setdefault(ck, entry)
     run_graph, ospec = entry
@@ -192,16 +193,59 @@ def __compile__(key, templates, fun, opts):
     return runner
 
 
-def _make_runner(outs, params, aliases=None):
+def _make_runner(outs, params, aliases=None, hooks=None):
     """A callable ``(device tensors, device) -> result tensors`` for a traced graph.  Without control
-    flow that is one program.  A graph with ``while`` nodes is cut at them: one program computes a
-    loop's initial state and captured values, the host iterates the condition and body programs
-    (reading the one-byte predicate back), and the final state enters the programs after it as
-    extra parameters."""
+    flow or host calls that is one program.  ``io_call`` nodes become extra outputs of the program whose
+    values are handed to their callbacks after it ran.  A graph with ``while`` or ``runtime_call`` nodes
+    is cut at them: one program computes a loop's initial state and captured values (a host call's
+    arguments), the host iterates the condition and body programs reading the one-byte predicate back
+    (calls the function), and the results enter the programs after it as extra parameters."""
+    hooks = hooks or {}
     order = E.topo_order(outs)[0]
+    taps = {}
+    for t in order:
+        if t.data.op == "io_call":
+            taps.setdefault(id(t.data.payload), (t.data.payload, {}))[1][t.data.ints[0]] = t
+    if taps:
+        repl, calls, extra = {}, [], []
+        # in the order the calls were traced (api_test.exs "executes independent io_calls in program
+        # order"); a tap inside a tapped value was traced before it, so inner taps come first
+        for tap, leaves in sorted(taps.values(), key=lambda entry: entry[0].seq):
+            # the value as this graph holds it; a leaf the result does not use is taken as traced
+            values = E.substitute([leaves[i].data.args[0] if i in leaves else v for i, v in enumerate(tap.values)], repl)
+            for i, node in leaves.items():
+                repl[node.data.id] = values[i]
+            fun = hooks.get(tap.name, tap.fun) if tap.name is not None else tap.fun
+            if fun is None:                           # a named tap nobody listens to costs nothing
+                continue
+            guards = E.substitute([g for g, _ in tap.guards], repl)
+            calls.append((fun, tap, values, guards, [want for _, want in tap.guards]))
+        # a tapped value that is a result anyway is read from that result, not computed twice
+        new_outs = E.substitute(outs, repl)
+        n = len(outs)
+        slot = {}
+        for i, t in enumerate(new_outs):
+            slot.setdefault(t.data.id, i)
+        for _, _, values, guards, _ in calls:
+            for t in values + guards:
+                if t.data.id not in slot:
+                    slot[t.data.id] = n + len(extra)
+                    extra.append(t)
+        inner = _make_runner(new_outs + extra, params, aliases, hooks)
+
+        def run_tapped(vals, device):
+            from . import nx
+            res = inner(vals, device)
+            for fun, tap, values, guards, wants in calls:
+                if all(bool(nx.to_number(res[slot[g.data.id]])) == w for g, w in zip(guards, wants)):
+                    fun(_unflatten(tap.spec, iter([res[slot[v.data.id]] for v in values])))
+            return res[:n]
+        run_tapped.program = inner.program
+        return run_tapped
+
     groups, seen = [], set()
     for t in order:
-        if t.data.op == "while" and id(t.data.payload) not in seen:
+        if t.data.op in ("while", "runtime_call") and id(t.data.payload) not in seen:
             seen.add(id(t.data.payload))
             groups.append(t.data.payload)
     if not groups:
@@ -216,20 +260,27 @@ def _make_runner(outs, params, aliases=None):
     all_params = list(params)
     repl, stages = {}, []
     for g in groups:
-        stage = _make_runner(E.substitute(g.inputs, repl), list(all_params))
-        cond = _make_runner(g.cond_outs, g.sub_params)
-        body = _make_runner(g.body_outs, g.sub_params)
-        stages.append((stage, cond, body, g.n_state))
-        for r in g.results:                       # the final state: parameters of everything downstream
+        stage = _make_runner(E.substitute(g.inputs, repl), list(all_params), None, hooks)
+        if isinstance(g, _WhileGroup):
+            cond = _make_runner(g.cond_outs, g.sub_params, None, hooks)
+            body = _make_runner(g.body_outs, g.sub_params, None, hooks)
+            stages.append((stage, g, cond, body))
+        else:
+            stages.append((stage, g, None, None))
+        for r in g.results:                       # the results: parameters of everything downstream
             p = E.parameter(r.type, r.shape, len(all_params))
             all_params.append(p)
             repl[r.data.id] = p
-    final = _make_runner(E.substitute(outs, repl), list(all_params))
+    final = _make_runner(E.substitute(outs, repl), list(all_params), None, hooks)
 
     def run_segments(vals, device):
         vals = list(vals)
-        for stage, cond, body, k in stages:
+        for stage, g, cond, body in stages:
             ins = stage(vals, device)
+            if cond is None:
+                vals += g.call(ins, device)
+                continue
+            k = g.n_state
             state, caps = list(ins[:k]), list(ins[k:])
             while nx.to_number(cond(state + caps, device)[0]):
                 state = list(body(state + caps, device))
@@ -400,7 +451,9 @@ def _traced_while(cond_fun, body_fun, state):
     # values of the enclosing trace used inside: nodes older than the watermark
     own = {p.data.id for p in sub}
     captures, repl = [], {}
-    for t in E.topo_order([c] + bflat)[0]:
+    inner_taps = _taps_since(mark, [c] + bflat)
+    guard_roots = [g for tap in inner_taps for g, _ in tap.guards]
+    for t in E.topo_order([c] + bflat + guard_roots)[0]:
         e = t.data
         if isinstance(e.id, int) and e.id < mark and e.id not in own and e.id not in repl and e.op not in ("constant",):
             # only the outermost captured node of a chain matters; inner ones are cut off by the substitution
@@ -420,10 +473,13 @@ def _traced_while(cond_fun, body_fun, state):
                 continue
             stack.extend(e.args)
         return found
-    for t in frontier([c] + bflat):
+    for t in frontier([c] + bflat + guard_roots):
         if not any(t.data.id == x.data.id for x in captures):
             captures.append(t)
     repl = {t.data.id: E.parameter(t.type, t.shape, k + j) for j, t in enumerate(captures)}
+    for tap in inner_taps:
+        tap.guards = [(E.substitute([g], repl)[0], want) for g, want in tap.guards]
+        tap.values = E.substitute(tap.values, repl)
     g = _WhileGroup()
     g.n_state = k
     g.inputs = flat + captures
@@ -446,12 +502,27 @@ def cond(pred, then_fun, else_fun, *operands):
         raise ValueError(f"condition must be a scalar tensor, got shape {p.shape}")
     if not _traced((p,) + tuple(operands)):
         return then_fun(*operands) if nx.to_number(p) else else_fun(*operands)
-    a, b = then_fun(*operands), else_fun(*operands)
+    p = B.to_expr(p)
+    mark = E.watermark()
+    a = then_fun(*operands)
     fa, fb = [], []
-    spec_a, spec_b = _flatten(a, fa), _flatten(b, fb)
-    if [(t.type, t.shape) for t in fa] != [(t.type, t.shape) for t in fb] or repr(spec_a) != repr(spec_b):
+    spec_a = _flatten(a, fa)
+    for tap in _taps_since(mark, [B.to_expr(t) for t in fa]):
+        tap.guards.append((p, True))                  # a tap fires only in the branch that is taken
+    mark = E.watermark()
+    b = else_fun(*operands)
+    spec_b = _flatten(b, fb)
+    for tap in _taps_since(mark, [B.to_expr(t) for t in fb]):
+        tap.guards.append((p, False))
+    if repr(spec_a) != repr(spec_b):
         raise ValueError("cond expects all branches to return compatible tensor types and shapes")
-    return _unflatten(spec_a, iter([nx.select(p, x, y) for x, y in zip(fa, fb)]))
+    out = []
+    for x, y in zip(fa, fb):
+        # branches are brought to a common type and shape (nx/lib/nx/defn/expr.ex:251-290)
+        ty, shape = T.merge(x.type, y.type), nx.binary_broadcast(x.shape, y.shape)
+        x, y = (nx.broadcast(nx.as_type(v, ty), shape) for v in (x, y))
+        out.append(nx.select(p, x, y))
+    return _unflatten(spec_a, iter(out))
 
 
 def _map_tensors(fun, c):
@@ -460,6 +531,89 @@ def _map_tensors(fun, c):
     if isinstance(c, dict):
         return {k: _map_tensors(fun, v) for k, v in c.items()}
     return fun(c)
+
+
+# ---- host callbacks: Nx.runtime_call/4 and Nx.Defn.Kernel.io_call (hook) ------------------------------
+
+def _check_call_result(result, output):
+    """nx/lib/nx.ex ensure_call_compatible!: same container structure, types and shapes."""
+    got, want = [], []
+    gs, ws = _flatten(result, got), _flatten(output, want)
+    if repr(gs) != repr(ws) or [(t.type, t.shape) for t in got] != [(t.type, t.shape) for t in want]:
+        raise ValueError("expected the runtime_call function to match the given output template "
+                         f"{[(T.short(t.type), t.shape) for t in want]}, got: {[(T.short(t.type), t.shape) for t in got]}")
+    return got
+
+
+class _HostCall:
+    """What a traced ``runtime_call`` carries to the compiler: its argument nodes, the host function
+    and the templates of what it returns."""
+    __slots__ = ("inputs", "spec", "fun", "opts", "output", "results")
+
+    def call(self, ins, device):
+        from . import nx
+        arg = _unflatten(self.spec, iter(ins))
+        flat = _check_call_result(self.fun(arg, self.opts), self.output)
+        return [B.backend_transfer(t if not isinstance(t.data, E.Expr) else nx.tensor(nx.to_numpy(t), t.type), device) for t in flat]
+
+
+def runtime_call(output, tensor_or_container, fun, opts=None):
+    """``Nx.runtime_call(output, tensor_or_container, opts, fun)`` (nx/lib/nx.ex:2394-2419): run the
+    host function ``fun(tensors, opts)`` in the middle of a computation.  ``output`` is a template
+    (or container of templates, see `template`) the result must match.  Outside a traced function
+    the function is simply called; inside, the graph is cut at the call."""
+    flat = []
+    spec = _flatten(tensor_or_container, flat)
+    if not _traced(flat):
+        result = fun(tensor_or_container, opts)
+        _check_call_result(result, output)
+        return result
+    g = _HostCall()
+    g.inputs = [B.to_expr(t) for t in flat]
+    g.spec, g.fun, g.opts, g.output = spec, fun, opts, output
+    want = []
+    ospec = _flatten(output, want)
+    g.results = [Tensor(E.Expr("runtime_call", g.inputs, ints=[i], payload=g), t.type, t.shape) for i, t in enumerate(want)]
+    return _unflatten(ospec, iter(g.results))
+
+
+class _Tap:
+    """What a traced ``io_call`` carries to the compiler: the tapped values (the leaves of the
+    container; identity nodes stand for them in the graph), the name and default function, and the
+    predicates of the `cond` branches it was traced in (it fires only when they all held)."""
+    __slots__ = ("name", "fun", "spec", "values", "guards", "seq")
+
+
+def io_call(expr, name_or_function, function=None):
+    """``Nx.Defn.Kernel.io_call/2,3`` (nx/lib/nx/defn/kernel.ex:1318-1430; `hook` is its older name):
+    hand the runtime value of ``expr`` (a tensor or container) to a host function and return ``expr``.
+    A name lets ``jit(fun, hooks={name: function})`` supply or override the function; a named call
+    without any function is dropped and its value never leaves the device.  As in the reference the
+    result of ``io_call`` must be used by the function's result for the call to happen.  The values
+    leave the device as extra results of the program they are computed in and the functions run, in
+    the order the calls were traced, when that program has finished."""
+    name, fun = (None, name_or_function) if callable(name_or_function) else (name_or_function, function)
+    flat = []
+    spec = _flatten(expr, flat)
+    if not _traced(flat):
+        if fun is not None:
+            fun(expr)
+        return expr
+    tap = _Tap()
+    tap.name, tap.fun, tap.spec, tap.guards, tap.seq = name, fun, spec, [], E.watermark()
+    tap.values = [B.to_expr(t) for t in flat]
+    return _unflatten(spec, iter([Tensor(E.Expr("io_call", [v], ints=[i], payload=tap), v.type, v.shape) for i, v in enumerate(tap.values)]))
+
+
+def _taps_since(mark, roots):
+    found = []
+    for t in E.topo_order(roots)[0]:
+        if t.data.op == "io_call" and t.data.id > mark and not any(t.data.payload is f for f in found):
+            found.append(t.data.payload)
+    return found
+
+
+hook = io_call
 
 
 # Nx.Defn.grad / value_and_grad (nx/lib/nx/defn.ex:760-850) live in grad.py; re-exported here because

@@ -52,6 +52,8 @@ def _rule(t, g):
     op, a = e.op, e.args
     if op in ("parameter", "constant", "tensor", "iota", "metadata"):
         return []                                                        # leaves; metadata = stop_grad (nx.ex:18407-18414)
+    if op == "io_call":
+        return [(a[0], g)]                                               # grad_test.exs:72-86: a tap is transparent
     if not T.is_float(t.type):
         return []                                                        # integer / predicate results carry no gradient
     ans = t

@@ -1002,3 +1002,9 @@ def dot(a, *args):
     out = _out(T.merge(a.type, b.type), shape)
     ints = [len(c1)] + c1 + [len(b1)] + b1 + [len(c2)] + c2 + [len(b2)] + b2
     return _dispatch(lambda x, y: E.node(out, "dot", [x, y], ints=ints), [a, b])
+
+
+def runtime_call(output, tensor_or_container, fun, opts=None):
+    """``Nx.runtime_call/4`` (nx/lib/nx.ex:2394-2419); the graph cutting lives with the compiler mirror."""
+    from . import defn
+    return defn.runtime_call(output, tensor_or_container, fun, opts)
