@@ -296,6 +296,8 @@ def main():
                     help="run only an N^3 bf16 dense product with the fused bias+gelu epilogue (ncu captures of the tensor-core kernel)")
     ap.add_argument("--profile-decoder", type=int, default=0, metavar="B",
                     help="run only the decoder block on a batch of B sequences (ncu launch lists)")
+    ap.add_argument("--profile-quantised", type=int, default=0, metavar="M",
+                    help="run only the s8-weight linear {M,4096}x{11008,4096} (ncu captures of the small-batch kernels)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -319,6 +321,12 @@ def main():
         ms_, prog_ = time_program(timer, configs.make_decoder_block(), configs.decoder_inputs(batch=args.profile_decoder), local, steps=args.steps)
         print(json.dumps({"workload": f"decoder block bf16 {{{args.profile_decoder},2048,4096}}", "ms": round(ms_, 4),
                           "tokens_per_s": round(args.profile_decoder * 2048 / ms_ * 1e3), "plan": prog_.describe().strip().split("\n")}))
+        return
+    if args.profile_quantised:
+        m_ = args.profile_quantised
+        ms_, prog_ = time_program(timer, configs.quantised_linear, configs.quantised_inputs(m=m_)[0], local, steps=args.steps)
+        print(json.dumps({"workload": f"s8-weight linear bf16 {{{m_},4096}} x s8 {{11008,4096}}", "us": round(ms_ * 1e3, 2),
+                          "w_stream_gbs": round(11008 * 4096 / ms_ / 1e6), "plan": prog_.describe().strip().split("\n")}))
         return
     if args.profile_gemm:
         n = args.profile_gemm

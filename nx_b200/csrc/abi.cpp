@@ -217,7 +217,7 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         if (ga.scale && ga.db == NXB_S8 && ga.da == NXB_BF16) {
           // s8 weights converted inside the product kernel (few rows of x)
           if (!wq_linear_supported(ga)) fail(NXB_ERR_RUNTIME, "internal: quantised linear outside the in-kernel conversion path");
-          launch_wq_linear(ga, d.status_dev, d.stream);
+          launch_wq_linear(ga, d.status_dev, d.sm_count, d.stream);
           goto step_done;
         }
         const bool on_tensor_cores = tc_gemm_supported(fin);

@@ -1766,6 +1766,17 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     plan_dot(*plan, n, need, &gs);
     for (int m : need) P.mat[m] = 1;
   }
+  // a reshape / squeeze / metadata chain over a parameter or literal is that buffer under another
+  // shape: nothing to compute (results still get memory of their own)
+  {
+    std::set<int> outs(g.outputs.begin(), g.outputs.end());
+    for (int n = 0; n < N; ++n) {
+      if (!g.nodes[n].live || !P.mat[n] || outs.count(n)) continue;
+      int a = n;
+      while ((g.nodes[a].op == "reshape" || g.nodes[a].op == "squeeze" || g.nodes[a].op == "metadata") && !g.nodes[a].args.empty()) a = g.nodes[a].args[0];
+      if (a != n && (g.nodes[a].op == "parameter" || g.nodes[a].op == "tensor")) P.mat[n] = 0;
+    }
+  }
   // contiguous reshapes / metadata over materialised values share the buffer
   auto propagate_alias = [&]() {
     for (int n = 0; n < N; ++n) {

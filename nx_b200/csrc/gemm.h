@@ -70,7 +70,7 @@ bool launch_tc_gemm_allreduce(const GemmArgs& g, void* out, int* status_word, in
 // is a single stream over W.
 constexpr int64_t WQ_LINEAR_MAX_ROWS = 512;
 bool wq_linear_supported(const GemmArgs& g);
-void launch_wq_linear(const GemmArgs& g, int* status_word, cudaStream_t stream);
+void launch_wq_linear(const GemmArgs& g, int* status_word, int sm_count, cudaStream_t stream);
 // Sort / argsort of `rows` rows of `len` elements each (the last axis), see sort_rows.cu.
 bool sort_rows_supported(int64_t len);
 void launch_sort_rows(const void* in, void* out, int64_t rows, int64_t len, DType dt, DType out_dt, bool descending, bool want_indices,

@@ -269,6 +269,224 @@ wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   }
 }
 
+// ---- M <= 16: a pure stream over W ---------------------------------------------------------------
+// With at most 16 rows of x the tcgen05 pipeline above is paced by its per-k-block hand-offs
+// (TMA -> converter warps -> shared memory -> MMA issuer) and only N/128 CTAs have work.  Here every
+// SM streams its share of W and converts it in registers on its way to the tensor cores:
+//   * a CTA of 16 warps owns groups of 16 output channels (all 148 SMs take groups round-robin);
+//     the 16 rows of a group (k bytes each, contiguous) arrive by sixteen bulk copies issued by one
+//     thread into a ring of 3 stages, two groups (128 KiB) ahead.  Rows are laid 64 bytes further
+//     apart than their length so that the 16-byte reads below do not collide on banks.  Every
+//     round ends in a CTA-wide hand-over (partial sums through shared memory), whose latency all
+//     warps pay in lockstep: with 8 channels per round the kernel took 20.5 us, with 16 it takes 16.5
+//   * warp w owns the 64-wide k chunks {i*16 + w}, i < 4; the x fragments of its chunks are loaded
+//     once and stay in registers (64 of them) for every group
+//   * per group a lane reads four 16-byte pieces of W (row lane/4, 16 consecutive k each), turns
+//     them into bf16 pairs and feeds mma.sync m16n8k16 (rows = the padded batch, columns = 8
+//     channels; two such tiles per group).  Which k lands in which slot of the MMA's contraction
+//     index does not matter as long as x uses the same order, so the bytes are taken as they come: even bytes of a word form one
+//     pair, odd bytes the other (x is permuted accordingly, once).  s8 -> bf16 without converts: with
+//     v = lo - 128*b7, both 128 + lo and 128 + 128*b7 are bf16 bit patterns made by one logic
+//     operation each (0x4300 | bits), and their bf16x2 difference is exact: 7 instructions per word
+//   * the 16 partial tiles are summed through shared memory in a fixed order (deterministic)
+// tcgen05 would not help: at 16 rows the tensor work is a fraction of a percent of the pipe's
+// capacity.  Measured, the kernel is bound by neither HBM (2.7 TB/s of W stream) nor a pipe (ALU 40 %)
+// but by the per-round latency chain above.
+constexpr int GV_WARPS = 16, GV_IT = 4, GV_MAX_K = GV_WARPS * GV_IT * 64;
+constexpr int GV_TILES = 2;                                   // 8-channel MMA tiles per group
+constexpr int GV_ROWS = 8 * GV_TILES;                         // channels per group
+constexpr int GV_DEPTH = 3;                                   // ring stages: 2 groups (128 KiB) in flight
+constexpr int GV_ROW_BYTES = GV_MAX_K + 64;                   // row pitch in the ring
+constexpr int GV_STAGE_BYTES = GV_ROWS * GV_ROW_BYTES;
+
+struct GvParams {
+  const signed char* w;
+  const unsigned short* x;
+  const float* scale;
+  void* out;
+  int* status;
+  int m, n, k, groups, out_dt;
+  long long ldw, ldx;
+};
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  // not volatile: a pure function of its operands, so the compiler may interleave the chains
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// bytes 0 and 2 of w -> `even` (a bf16 pair), bytes 1 and 3 -> `odd`; exact.  The difference is taken
+// by the fused multiply-add (x * 1 + (-c)), which is a native bf16x2 instruction
+__device__ __forceinline__ void s8x4_to_bf16_pairs(uint32_t w, uint32_t& even, uint32_t& odd) {
+  const uint32_t w1 = w >> 8;
+  const uint32_t pe = (w & 0x007F007Fu) | 0x43004300u, ce = (w & 0x00800080u) | 0xC300C300u;
+  const uint32_t po = (w1 & 0x007F007Fu) | 0x43004300u, co = (w1 & 0x00800080u) | 0xC300C300u;
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(even) : "r"(pe), "r"(0x3F803F80u), "r"(ce));
+  asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(odd) : "r"(po), "r"(0x3F803F80u), "r"(co));
+}
+
+// x values k+0..k+3 as loaded (pairs (0,1), (2,3)) -> pairs (0,2), (1,3), the order the weights use
+__device__ __forceinline__ void pair_even_odd(uint32_t& p01, uint32_t& p23) {
+  const uint32_t e = __byte_perm(p01, p23, 0x5410), o = __byte_perm(p01, p23, 0x7632);
+  p01 = e; p23 = o;
+}
+
+template <bool HI>      // HI: rows 8..15 of the batch exist
+__global__ void __launch_bounds__(GV_WARPS * 32, 1) wq_stream_kernel(GvParams p) {
+  __shared__ float red[GV_WARPS][32][4 * GV_TILES];
+  __shared__ __align__(8) unsigned long long full_bar[GV_DEPTH];
+  __shared__ int abort_word;
+  extern __shared__ __align__(128) unsigned char gv_ring[];
+  volatile int* abort_flag = &abort_word;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const uint32_t ring = smem_u32(gv_ring), bars = smem_u32(full_bar);
+  if (threadIdx.x == 0) {
+    abort_word = 0;
+    for (int s = 0; s < GV_DEPTH; ++s) mbar_init(bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // the eight rows of a group: one bulk copy each, completion counted on the stage's barrier
+  auto issue = [&](int grp, int stage) {
+    if (grp >= p.groups) return;
+    const int rows = min(GV_ROWS, p.n - grp * GV_ROWS);
+    mbar_expect_tx(bars + 8 * stage, (uint32_t)(rows * p.k));
+    for (int r = 0; r < rows; ++r) {
+      const signed char* src = p.w + ((long long)grp * GV_ROWS + r) * p.ldw;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(ring + (uint32_t)(stage * GV_STAGE_BYTES + r * GV_ROW_BYTES)), "l"(src), "r"((uint32_t)p.k), "r"(bars + 8 * stage)
+                   : "memory");
+    }
+  };
+  int grp = (int)blockIdx.x;
+  if (threadIdx.x == 0)
+    for (int d = 0; d < GV_DEPTH - 1; ++d) issue(grp + d * (int)gridDim.x, d);
+  // x fragments: 16 consecutive k of row g (and g + 8) per chunk, paired like the weights
+  uint32_t xa[GV_IT][8], xb[HI ? GV_IT : 1][8];
+#pragma unroll
+  for (int it = 0; it < GV_IT; ++it) {
+    const int kb = (it * GV_WARPS + warp) * 64 + q * 16;
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+    if (kb < p.k && g < p.m) {
+      const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)g * p.ldx + kb);
+      lo = src[0]; hi = src[1];
+    }
+    xa[it][0] = lo.x; xa[it][1] = lo.y; xa[it][2] = lo.z; xa[it][3] = lo.w;
+    xa[it][4] = hi.x; xa[it][5] = hi.y; xa[it][6] = hi.z; xa[it][7] = hi.w;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) pair_even_odd(xa[it][2 * j], xa[it][2 * j + 1]);
+    if (HI) {
+      lo = make_uint4(0, 0, 0, 0); hi = lo;
+      if (kb < p.k && g + 8 < p.m) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.x + (long long)(g + 8) * p.ldx + kb);
+        lo = src[0]; hi = src[1];
+      }
+      xb[it][0] = lo.x; xb[it][1] = lo.y; xb[it][2] = lo.z; xb[it][3] = lo.w;
+      xb[it][4] = hi.x; xb[it][5] = hi.y; xb[it][6] = hi.z; xb[it][7] = hi.w;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pair_even_odd(xb[it][2 * j], xb[it][2 * j + 1]);
+    }
+  }
+  const uint32_t my_piece = ring + (uint32_t)(g * GV_ROW_BYTES + warp * 64 + q * 16);
+  for (int round = 0; grp < p.groups; grp += (int)gridDim.x, ++round) {
+    const int stage = round % GV_DEPTH;
+    // the stage read in the previous round is free (every warp passed that round's barrier)
+    if (threadIdx.x == 0) issue(grp + (GV_DEPTH - 1) * (int)gridDim.x, (round + GV_DEPTH - 1) % GV_DEPTH);
+    // this thread's share of the epilogue: output (row m, channel nn) of the group, partial sums of
+    // eight warps; the scale is fetched now so that its latency hides behind the products
+    const int o = threadIdx.x >> 1, part = threadIdx.x & 1;
+    const int m = o / GV_ROWS, nn = o % GV_ROWS;
+    const long long n = (long long)grp * GV_ROWS + nn;
+    const float sc = n < p.n ? p.scale[n] : 0.f;
+    const bool ok = mbar_wait_warp_tight(bars + 8 * stage, (uint32_t)((round / GV_DEPTH) & 1), abort_flag);
+    float acc[GV_TILES][2][4];                // two dependency chains per tile (even / odd chunks)
+#pragma unroll
+    for (int t = 0; t < GV_TILES; ++t)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) acc[t][h][0] = acc[t][h][1] = acc[t][h][2] = acc[t][h][3] = 0.f;
+    const unsigned char* my_stage = gv_ring + (my_piece - ring) + stage * GV_STAGE_BYTES;
+#pragma unroll
+    for (int it = 0; it < GV_IT; ++it) {
+      // warp-uniform: the whole 64-wide chunk lies inside k or outside; rows beyond n hold stale
+      // bytes, their columns are never stored
+      if (ok && (it * GV_WARPS + warp) * 64 < p.k) {
+        uint4 words[GV_TILES];
+#pragma unroll
+        for (int t = 0; t < GV_TILES; ++t)     // ordinary loads: ordered after the wait above, free to move among the MMAs
+          words[t] = *reinterpret_cast<const uint4*>(my_stage + t * 8 * GV_ROW_BYTES + it * GV_WARPS * 64);
+#pragma unroll
+        for (int t = 0; t < GV_TILES; ++t) {
+          const uint32_t wj[4] = {words[t].x, words[t].y, words[t].z, words[t].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t b0, b1;
+            s8x4_to_bf16_pairs(wj[j], b0, b1);
+            mma_bf16_16816(acc[t][it & 1], xa[it][2 * j], HI ? xb[HI ? it : 0][2 * j] : 0u, xa[it][2 * j + 1], HI ? xb[HI ? it : 0][2 * j + 1] : 0u, b0, b1);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < GV_TILES; ++t)
+      *reinterpret_cast<float4*>(&red[warp][lane][4 * t]) =
+          make_float4(acc[t][0][0] + acc[t][1][0], acc[t][0][1] + acc[t][1][1], acc[t][0][2] + acc[t][1][2], acc[t][0][3] + acc[t][1][3]);
+    __syncthreads();
+    {
+      // per tile, acc[0..1]: row g, channels 2q, 2q+1; acc[2..3]: row g + 8.  All 512 threads take
+      // part: two lanes per output, each sums eight warps' partials in a fixed order
+      const int n8 = nn & 7, t = nn >> 3;
+      const int src_lane = (m & 7) * 4 + (n8 >> 1), c = 4 * t + (m >> 3) * 2 + (n8 & 1);
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < GV_WARPS / 2; ++w) sum += red[part * (GV_WARPS / 2) + w][src_lane][c];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      if (part == 0 && m < p.m && n < p.n && !*abort_flag) {
+        const float y = sum * sc;
+        if (p.out_dt == NXB_F32) reinterpret_cast<float*>(p.out)[(long long)m * p.n + n] = y;
+        else reinterpret_cast<unsigned short*>(p.out)[(long long)m * p.n + n] = f32_to_bf16_bits(y);
+      }
+    }
+    __syncthreads();                         // the partial sums are rewritten in the next round
+  }
+  __syncthreads();
+  if (*abort_flag) {
+    // a copy never arrived: report it, give the copies still in flight time to land before the
+    // shared memory is handed to another CTA
+    if (threadIdx.x == 0) *(volatile int*)p.status = 1;
+    const long long t0 = now_cycles();
+    while (now_cycles() - t0 < 400000ll) { }
+  }
+}
+
+bool wq_stream_usable(const GemmArgs& g) {
+  return g.m <= 16 && g.k % 64 == 0 && g.k <= GV_MAX_K && !getenv("NXB200_NO_WQ_STREAM");
+}
+
+void launch_wq_stream(const GemmArgs& g, int* status_word, int sm_count, cudaStream_t stream) {
+  GvParams p{};
+  p.w = (const signed char*)g.b;
+  p.x = (const unsigned short*)g.a;
+  p.scale = (const float*)g.scale;
+  p.out = g.c;
+  p.m = (int)g.m; p.n = (int)g.n; p.k = (int)g.k;
+  p.groups = (int)((g.n + GV_ROWS - 1) / GV_ROWS);
+  p.out_dt = (int)g.dc;
+  p.ldw = g.ldb; p.ldx = g.lda;
+  p.status = status_word;
+  const unsigned grid = (unsigned)std::min<int64_t>(p.groups, sm_count);
+  const int smem = GV_DEPTH * GV_STAGE_BYTES;
+  if (g.m > 8) {
+    NXB_CUDA(cudaFuncSetAttribute(wq_stream_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    wq_stream_kernel<true><<<grid, GV_WARPS * 32, smem, stream>>>(p);
+  } else {
+    NXB_CUDA(cudaFuncSetAttribute(wq_stream_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    wq_stream_kernel<false><<<grid, GV_WARPS * 32, smem, stream>>>(p);
+  }
+  NXB_CUDA(cudaGetLastError());
+}
+
 CUtensorMap wq_map(const void* ptr, CUtensorMapDataType type, size_t es, int64_t k, int64_t rows, int64_t ld, int box_rows, CUtensorMapSwizzle sw) {
   const DriverApi& drv = driver();
   if (!drv.cuTensorMapEncodeTiled) fail(NXB_ERR_RUNTIME, "cuTensorMapEncodeTiled is unavailable");
@@ -291,7 +509,8 @@ bool wq_linear_supported(const GemmArgs& g) {
          ((uintptr_t)g.a % 16) == 0 && ((uintptr_t)g.b % 16) == 0;
 }
 
-void launch_wq_linear(const GemmArgs& g, int* status_word, cudaStream_t stream) {
+void launch_wq_linear(const GemmArgs& g, int* status_word, int sm_count, cudaStream_t stream) {
+  if (wq_stream_usable(g)) { launch_wq_stream(g, status_word, sm_count, stream); return; }
   WqParams p{};
   p.out = g.c;
   p.scale = (const float*)g.scale;

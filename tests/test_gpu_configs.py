@@ -127,10 +127,14 @@ def test_quantised_linear_reduced(m):
     assert ti == ("s", 32) and np.array_equal(gi, ri)
 
 
-@pytest.mark.parametrize("m,n,k", [(5, 1000, 528), (48, 136, 4096), (300, 392, 80), (512, 128, 64), (513, 256, 128)])
+@pytest.mark.parametrize("m,n,k", [(5, 1000, 528), (48, 136, 4096), (300, 392, 80), (512, 128, 64), (513, 256, 128),
+                                   # up to 16 rows and k a multiple of 64 up to 4096: the register-streaming kernel
+                                   (3, 1003, 576), (9, 520, 4096), (16, 136, 1024), (8, 2052, 64), (13, 1000, 4160)])
 def test_quantised_linear_ragged(m, n, k):
     """Edges of the in-kernel conversion path: rows that do not fill a batch tile, a second batch
-    tile, channels and k that end inside a tile, and (513 rows) the hand-over to the general path."""
+    tile, channels and k that end inside a tile, and (513 rows) the hand-over to the general path; for
+    the streaming kernel: channels that end inside a group of 8, k chunks that leave warps idle, 8 and
+    9 rows (with and without the upper half of the fragment), and k beyond its reach."""
     f_in, _ = configs.quantised_inputs(m=m, n=n, k=k)
     (g, r, t), = run_both(configs.quantised_linear, f_in)
     assert t == ("f", 32) and g.shape == (m, n)
