@@ -189,6 +189,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The same load without the wait: the registers hold the data only after tmem_ld_wait().  Lets the
+// next chunk's load run while the current chunk is converted and stored.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -254,6 +268,17 @@ __device__ __forceinline__ unsigned short f32_to_bf16_bits(float f) {
   unsigned short h;
   asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(h) : "f"(f));
   return h;
+}
+// (lo, hi) -> one register holding both 16-bit values, lo in the low half
+__device__ __forceinline__ uint32_t f32x2_to_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ uint32_t f32x2_to_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
 }
 __device__ __forceinline__ unsigned short f32_to_f16_bits(float f) {
   unsigned short h;
@@ -558,15 +583,13 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       tc_fence_after();
       const long long m = (long long)mt * BM + q * 32 + lane;
       const bool staged = Epi::kStaged && p.tma_store != 0;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN + c * 32), v);
+      const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN);
+      auto chunk = [&](int c, uint32_t (&v)[32]) {
         const long long n0 = (long long)nt * BN + c * 32;
         if (staged) {
           // 32 rows x 32 columns of this warp go to a swizzled staging tile; one lane hands the
           // tile to the TMA unit, which writes full lines and clips at the matrix edges.
-          if ((long long)mt * BM + q * 32 >= p.m || n0 >= p.n) continue;      // warp-uniform
+          if ((long long)mt * BM + q * 32 >= p.m || n0 >= p.n) return;        // warp-uniform
           // each warp owns 8 KB of staging: four 2 KB tiles for 2-byte results, two 4 KB tiles otherwise
           const bool two_byte = p.out_dt == NXB_BF16 || p.out_dt == NXB_F16;
           const uint32_t buf = sStore + (uint32_t)(warp - 2) * 8192u + (two_byte ? (store_iter & 3) * 2048u : (store_iter & 1) * 4096u);
@@ -586,12 +609,12 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
             // rows of 64 bytes, 64-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              unsigned short h[8];
+              uint32_t h[4];                 // one packed convert per pair
 #pragma unroll
-              for (int e = 0; e < 8; ++e) h[e] = p.out_dt == NXB_BF16 ? f32_to_bf16_bits(f[j * 8 + e]) : f32_to_f16_bits(f[j * 8 + e]);
+              for (int e = 0; e < 4; ++e)
+                h[e] = p.out_dt == NXB_BF16 ? f32x2_to_bf16x2(f[j * 8 + 2 * e], f[j * 8 + 2 * e + 1]) : f32x2_to_f16x2(f[j * 8 + 2 * e], f[j * 8 + 2 * e + 1]);
               const uint32_t dst = buf + (uint32_t)lane * 64u + (uint32_t)((j ^ ((lane >> 1) & 3)) * 16);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(h[0] | ((uint32_t)h[1] << 16)), "r"(h[2] | ((uint32_t)h[3] << 16)),
-                           "r"(h[4] | ((uint32_t)h[5] << 16)), "r"(h[6] | ((uint32_t)h[7] << 16)) : "memory");
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
             }
           } else {
             // 4-byte results: rows of 128 bytes, 128-byte swizzle: chunk j of row r sits at chunk j ^ (r & 7)
@@ -609,7 +632,7 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
           __syncwarp();
           if (lane == 0) tma_store_3d(&map_c, buf, (int)n0, mt * BM + q * 32, b);
           ++store_iter;
-          continue;
+          return;
         }
         if (m < p.m && n0 < p.n) {
           float f[32];
@@ -621,6 +644,18 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
           }
           Epi::store(p, f, v, (long long)b, m, n0);
         }
+      };
+      // two register sets: the load of the next 32 columns is in flight while these are handled
+      uint32_t va[32], vb[32];
+      tmem_ld32_issue(tacc, va);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c += 2) {
+        tmem_ld_wait();
+        tmem_ld32_issue(tacc + (uint32_t)((c + 1) * 32), vb);
+        chunk(c, va);
+        tmem_ld_wait();
+        if (c + 2 < BN / 32) tmem_ld32_issue(tacc + (uint32_t)((c + 2) * 32), va);
+        chunk(c + 1, vb);
       }
       tc_fence_before();
       __syncwarp();
