@@ -294,6 +294,8 @@ def main():
     ap.add_argument("--all-configs", action="store_true")
     ap.add_argument("--profile-gemm", type=int, default=0, metavar="N",
                     help="run only an N^3 bf16 dense product with the fused bias+gelu epilogue (ncu captures of the tensor-core kernel)")
+    ap.add_argument("--profile-batched", action="store_true",
+                    help="run only the batched bf16 product {64,2048,128} x {64,128,2048} (ncu captures of the short-k tensor-core kernel)")
     ap.add_argument("--profile-decoder", type=int, default=0, metavar="B",
                     help="run only the decoder block on a batch of B sequences (ncu launch lists)")
     ap.add_argument("--profile-quantised", type=int, default=0, metavar="M",
@@ -333,6 +335,12 @@ def main():
         ms_, prog_ = time_program(timer, configs.dense_bias_gelu, configs.dense_inputs(m=n, n=n, k=n), local, steps=args.steps)
         print(json.dumps({"workload": f"dense bf16 {n}^3 + bias + gelu", "ms": round(ms_, 4), "tflops": round(2 * n ** 3 / ms_ / 1e9, 1),
                           "plan": prog_.describe().strip().split("\n")}))
+        return
+    if args.profile_batched:
+        ms_, prog_ = time_program(timer, configs.batched_dot, configs.batched_inputs(), local, steps=args.steps)
+        byt = (2 * 64 * 2048 * 128 + 64 * 2048 * 2048) * 2
+        print(json.dumps({"workload": "batched bf16 {64,2048,128} x {64,128,2048}", "ms": round(ms_, 4), "gbs": round(byt / ms_ / 1e6, 1),
+                          "tflops": round(2 * 64 * 2048 * 2048 * 128 / ms_ / 1e9, 1), "plan": prog_.describe().strip().split("\n")}))
         return
     rows = args.rows
     x_host = configs.fused_rows_input(rows, COLS, SEED)

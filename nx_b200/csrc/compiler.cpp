@@ -1563,6 +1563,7 @@ void rewrite_attention(Graph& g);
 int attn_smem_bytes();
 int tc_pick_bn(int64_t m, int64_t n, int64_t batch, int sm_count);
 int tc_smem_bytes(int bn);
+int tc_block_threads(int64_t k);
 
 std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
   auto plan = std::make_unique<Plan>();
@@ -2223,13 +2224,13 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           o << "    const " << I << " flat0 = (" << I << ")((b * p.m + m) * p.n + n0);\n";
           o << "    if (n0 + 32 <= p.n) {\n#pragma unroll\n      for (int j = 0; j < 32; j += " << V << ") " << kname << "_epiv(f + j, flat0 + j, p.ep);\n    } else {\n";
           o << "      for (int j = 0; j < 32 && n0 + j < p.n; ++j) " << kname << "_epi1(f + j, flat0 + j, p.ep);\n    }\n  }\n};\n";
-          o << "extern \"C\" __global__ void __launch_bounds__(192, 1) " << kname
+          o << "extern \"C\" __global__ void __launch_bounds__(320, 1) " << kname
             << "(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const __grid_constant__ CUtensorMap map_c, const nxb_gemm::TcParams p) {\n"
             << "  nxb_gemm::tc_gemm_body<" << (ta == NXB_BF16 ? "nxb_gemm::KIND_BF16" : "nxb_gemm::KIND_F16") << ", " << gs.bn << ", EpiGen>(map_a, map_b, map_c, p);\n}\n";
           KernelSpec ks;
           ks.name = kname;
           ks.source = o.str();
-          ks.block = 192;
+          ks.block = (unsigned)tc_block_threads(gs.k);
           ks.smem = (unsigned)tc_smem_bytes(gs.bn);
           ks.arg_slots = fv.arg_slots;
           ks.arg_offsets.assign(ks.arg_slots.size(), 0);

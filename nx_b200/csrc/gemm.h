@@ -40,6 +40,9 @@ struct TcLaunch {
 };
 int tc_pick_bn(int64_t m, int64_t n, int64_t batch, int sm_count);
 int tc_smem_bytes(int bn);
+// Threads per block of the tensor-core product: 192, or 320 (eight epilogue warps) when the contracted
+// extent is short enough that writing the tile out takes longer than computing it.
+int tc_block_threads(int64_t k);
 void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int* status_word, int sm_count, TcLaunch* out);
 const char* gemm_device_source();
 const char* attention_device_source();

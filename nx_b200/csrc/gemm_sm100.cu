@@ -25,8 +25,10 @@ namespace {
 
 using namespace nxb_gemm;
 
+// Launched with 192 threads (four epilogue warps) or, when the k loop is short and the epilogue bounds
+// the tile time, with 320 (eight epilogue warps in two groups).
 template <int KIND, int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const __grid_constant__ CUtensorMap map_c, TcParams p) {
   tc_gemm_body<KIND, BN, EpiStore>(map_a, map_b, map_c, p);
@@ -170,6 +172,7 @@ int tc_pick_bn(int64_t m, int64_t n, int64_t batch, int sm_count) {
 }
 
 int tc_smem_bytes(int bn) { return smem_bytes_for(bn); }
+int tc_block_threads(int64_t k) { return k <= 1024 ? 320 : 192; }
 
 static TcParams make_params(const GemmArgs& g, int bn, int* status_word) {
   TcParams p{};
@@ -218,7 +221,7 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
   unsigned grid = (unsigned)std::min<long long>(tiles, sm_count);
   auto launch = [&](auto kern, int smem) {
     NXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, 192, smem, stream>>>(ma, mb, mc, p);
+    kern<<<grid, tc_block_threads(g.k), smem, stream>>>(ma, mb, mc, p);
     NXB_CUDA(cudaGetLastError());
   };
 #define NXB_LAUNCH_KIND(K)                                                      \

@@ -280,6 +280,18 @@ __device__ __forceinline__ uint32_t f32x2_to_f16x2(float lo, float hi) {
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// Volatile forms: kept inside the branch that selected the type (a pure asm on both sides of a
+// type test is computed twice and selected).
+__device__ __forceinline__ uint32_t bits2_to_bf16x2(uint32_t lo, uint32_t hi) {
+  uint32_t r;
+  asm volatile("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+  return r;
+}
+__device__ __forceinline__ uint32_t bits2_to_f16x2(uint32_t lo, uint32_t hi) {
+  uint32_t r;
+  asm volatile("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(hi)), "f"(__uint_as_float(lo)));
+  return r;
+}
 __device__ __forceinline__ unsigned short f32_to_f16_bits(float f) {
   unsigned short h;
   asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f));
@@ -487,9 +499,12 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
   volatile int* abort_flag = (volatile int*)(gen_base + (tmem_slot - base) + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // A block of ten warps (without the exchange role) has two groups of four epilogue warps; each group
+  // takes half of the tile's columns.  Products with a short k loop are bound by the epilogue.
+  const int epi_groups = (!COMM && blockDim.x >= 320) ? 2 : 1;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4 * epi_groups); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -569,8 +584,18 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
   } else if (COMM && warp >= 6) {
     comm_role<BN>(p, *cm, abort_flag);
   } else {
-    // epilogue warps 2..5; a warp may only read the TMEM lanes of its quarter (warp id mod 4)
+    // epilogue warps 2..5 (and 6..9 as a second group); a warp may only read the TMEM lanes of its
+    // quarter (warp id mod 4)
     const int q = warp & 3;
+    const int grp = (warp - 2) >> 2;
+    const int c_per = (BN / 32) / epi_groups, c0 = grp * c_per, c1 = c0 + c_per;
+    const uint32_t stage_bytes = 8192u / (uint32_t)epi_groups;     // staging memory of one warp
+    // Plain 16-bit results without a scale take a short path: packed converts straight from the
+    // accumulator registers, store offsets of this lane computed once.
+    const bool lean = KIND != KIND_S8 && Epi::kStaged && p.tma_store != 0 && !p.scale && (p.out_dt == NXB_BF16 || p.out_dt == NXB_F16);
+    const uint32_t lean_slots = stage_bytes / 2048u;                // 4 or 2
+    const uint32_t lean_base = sStore + (uint32_t)(warp - 2) * stage_bytes + (uint32_t)lane * 64u;
+    const uint32_t lean_sw = (uint32_t)((lane >> 1) & 3);
     uint32_t store_iter = 0;
     int a = 0;
     uint32_t aph = 0;
@@ -586,16 +611,44 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       const uint32_t tacc = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(a * BN);
       auto chunk = [&](int c, uint32_t (&v)[32]) {
         const long long n0 = (long long)nt * BN + c * 32;
+        if (lean) {
+          if ((long long)mt * BM + q * 32 >= p.m || n0 >= p.n) return;        // warp-uniform
+          uint32_t h[16];
+          if (p.out_dt == NXB_BF16) {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) h[e] = bits2_to_bf16x2(v[2 * e], v[2 * e + 1]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 16; ++e) h[e] = bits2_to_f16x2(v[2 * e], v[2 * e + 1]);
+          }
+          const uint32_t buf = lean_base + (store_iter & (lean_slots - 1)) * 2048u;    // this lane's 64-byte row
+          if (lane == 0) {   // the tile about to be overwritten must have been read by the TMA unit
+            if (lean_slots == 4) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          }
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 4; ++j)      // 64-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(buf + (((uint32_t)j ^ lean_sw) << 4)), "r"(h[4 * j]), "r"(h[4 * j + 1]),
+                         "r"(h[4 * j + 2]), "r"(h[4 * j + 3]) : "memory");
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) tma_store_3d(&map_c, buf, (int)n0, mt * BM + q * 32, b);
+          ++store_iter;
+          return;
+        }
         if (staged) {
           // 32 rows x 32 columns of this warp go to a swizzled staging tile; one lane hands the
           // tile to the TMA unit, which writes full lines and clips at the matrix edges.
           if ((long long)mt * BM + q * 32 >= p.m || n0 >= p.n) return;        // warp-uniform
-          // each warp owns 8 KB of staging: four 2 KB tiles for 2-byte results, two 4 KB tiles otherwise
+          // each warp owns 8 KB of staging (4 KB with two groups): tiles of 2 KB for 2-byte results, of 4 KB otherwise
           const bool two_byte = p.out_dt == NXB_BF16 || p.out_dt == NXB_F16;
-          const uint32_t buf = sStore + (uint32_t)(warp - 2) * 8192u + (two_byte ? (store_iter & 3) * 2048u : (store_iter & 1) * 4096u);
+          const uint32_t slots = stage_bytes / (two_byte ? 2048u : 4096u);      // 4, 2 or 1
+          const uint32_t buf = sStore + (uint32_t)(warp - 2) * stage_bytes + (store_iter & (slots - 1)) * (two_byte ? 2048u : 4096u);
           if (lane == 0) {   // the tile about to be overwritten must have been read by the TMA unit
-            if (two_byte) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
-            else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            if (slots == 4) asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+            else if (slots == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
           }
           __syncwarp();
           float f[32];
@@ -647,15 +700,17 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
       };
       // two register sets: the load of the next 32 columns is in flight while these are handled
       uint32_t va[32], vb[32];
-      tmem_ld32_issue(tacc, va);
+      tmem_ld32_issue(tacc + (uint32_t)(c0 * 32), va);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; c += 2) {
+      for (int c = c0; c < c1; c += 2) {
         tmem_ld_wait();
-        tmem_ld32_issue(tacc + (uint32_t)((c + 1) * 32), vb);
+        if (c + 1 < c1) tmem_ld32_issue(tacc + (uint32_t)((c + 1) * 32), vb);
         chunk(c, va);
-        tmem_ld_wait();
-        if (c + 2 < BN / 32) tmem_ld32_issue(tacc + (uint32_t)((c + 2) * 32), va);
-        chunk(c + 1, vb);
+        if (c + 1 < c1) {
+          tmem_ld_wait();
+          if (c + 2 < c1) tmem_ld32_issue(tacc + (uint32_t)((c + 2) * 32), va);
+          chunk(c + 1, vb);
+        }
       }
       tc_fence_before();
       __syncwarp();
