@@ -245,9 +245,9 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
               if (!ep[a]) fail(NXB_ERR_RUNTIME, "internal: epilogue of " + ks.name + " reads a buffer that was never produced");
             }
             TcLaunch tl;
-            tc_prepare_launch(ga, gs.bn, ep.data(), (int)ep.size(), d.status_dev, d.sm_count, &tl);
+            tc_prepare_launch(ga, gs.bn, ep.data(), (int)ep.size(), d.status_dev, d.sm_count, &tl, gs.staged_arg, gs.staged_dt);
             void* params[4] = {tl.map_a, tl.map_b, tl.map_c, tl.params};
-            check_cu(drv.cuLaunchKernel(L.functions[gs.jit_kernel], tl.grid, 1, 1, 192, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
+            check_cu(drv.cuLaunchKernel(L.functions[gs.jit_kernel], tl.grid, 1, 1, ks.block, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
                      ("launching " + ks.name).c_str());
           } else {
             // a row-parallel product whose only reader is the sum over ranks: one kernel does

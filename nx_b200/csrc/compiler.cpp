@@ -119,6 +119,9 @@ class KernelBuilder {
   std::vector<int> seed_args;   // EPI: argument order to reuse (so both widths see the same pointers)
   int ret_node = -1;            // EPI: generate `float f(acc, batch, row, col, ep)` returning this node's value
                                 // at index (batch..., row, col) instead of a storing epilogue
+  bool epi_to_regs = false;     // EPI: the one stored value is handed back in `out[v]` (the product kernel stores
+                                // the tile through shared memory) instead of being written by the function
+  bool epi_regs_ok = true;      // cleared when the store is not a float value at the thread's own position
   std::string idx_type() const { return idx_t(); }
   KernelBuilder(Plan& plan, Mode mode, std::vector<int64_t> F, int k, std::vector<int> perm)
       : plan_(plan), g_(plan.g), mode_(mode), F_(std::move(F)), k_(k), perm_(std::move(perm)) {
@@ -1035,6 +1038,16 @@ void KernelBuilder::emit_store(int n) {
     dyn += " + " + o;
     dyn_aligned = false;
   }
+  if (mode_ == EPI && epi_to_regs) {
+    bool ident = full && addr.c == 0 && shape_numel(nd.shape) == numel_ && nd.window_axes.empty() && nd.out_strides.empty();
+    const std::vector<int64_t> fs = cstrides(F_);
+    for (int q = 0; q < nv_; ++q) if (F_[q] != 1 && addr.k[q] != fs[q]) ident = false;     // extents of 1 carry no index
+    if (ident && (nd.dt == NXB_BF16 || nd.dt == NXB_F16 || nd.dt == NXB_F32)) {
+      lane_sec_[phase_] += "        out[v] = " + v.v + ";\n";
+      return;
+    }
+    epi_regs_ok = false;
+  }
   if (mode_ == ROW && !full) {
     // one value per row: lane 0 of the row writes it
     row_sec_[phase_] += "        if (tid == 0) st1<" + S + ">(" + p + " + " + affstr(addr, false) + ", " + v.v + ");\n";
@@ -1283,7 +1296,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
       o << "  const " << storage_type(sl.dt) << "* __restrict__ p" << i << " = (const " << storage_type(sl.dt) << "*)ep[" << i << "];\n";
     }
   } else if (mode_ == EPI) {
-    o << "__device__ __forceinline__ void " << name << "(const float* acc, const " << I << " flat0, void* const* ep) {\n";
+    o << "__device__ __forceinline__ void " << name << "(const float* acc, const " << I << " flat0, void* const* ep" << (epi_to_regs ? ", float* out" : "") << ") {\n";
     for (size_t i = 0; i < arg_slots_.size(); ++i) {
       const Slot& sl = plan_.slots[arg_slots_[i]];
       o << "  " << (is_written(arg_slots_[i]) ? "" : "const ") << storage_type(sl.dt) << "* __restrict__ p" << i << " = (" <<
@@ -2220,7 +2233,40 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           const DType ta = g.nodes[g.nodes[u.gemm_node].args[0]].dt;
           std::ostringstream o;
           o << fv.source << f1.source;
-          o << "struct EpiGen {\n  static constexpr bool kStaged = false;\n  static __device__ __forceinline__ void store(const nxb_gemm::TcParams& p, float (&f)[32], const uint32_t (&raw)[32], long long b, long long m, long long n0) {\n";
+          // One float result at the product's own position: the generated functions hand the value back and
+          // the tile leaves through shared memory and TMA stores (full lines instead of 16 bytes per lane).
+          bool to_regs = false;
+          int staged_arg = -1;
+          if (u.stores.size() == 1) {
+            const Node& sn = g.nodes[u.stores[0]];
+            const int64_t es = (int64_t)dtype_size(sn.dt);
+            if ((sn.dt == NXB_BF16 || sn.dt == NXB_F16 || sn.dt == NXB_F32) && (gs.n * es) % 16 == 0) {
+              KernelBuilder kr1(pl, KernelBuilder::EPI, u.F, 0, {});
+              kr1.stores = u.stores; kr1.acc_node = u.gemm_node; kr1.force_v = 1; kr1.seed_args = fv.arg_slots; kr1.epi_to_regs = true;
+              KernelSpec r1 = kr1.build(kname + "_reg1");
+              KernelBuilder krv(pl, KernelBuilder::EPI, u.F, 0, {});
+              krv.stores = u.stores; krv.acc_node = u.gemm_node; krv.force_v = ksv.vec_width(); krv.seed_args = fv.arg_slots; krv.epi_to_regs = true;
+              KernelSpec rv = krv.build(kname + "_regv");
+              if (kr1.epi_regs_ok && krv.epi_regs_ok && r1.arg_slots == fv.arg_slots && rv.arg_slots == fv.arg_slots) {
+                for (size_t i = 0; i < fv.arg_slots.size(); ++i) if (fv.arg_slots[i] == sn.slot) staged_arg = (int)i;
+                if (staged_arg >= 0) {
+                  to_regs = true;
+                  o << rv.source << r1.source;
+                  gs.staged_arg = staged_arg;
+                  gs.staged_dt = sn.dt;
+                }
+              }
+            }
+          }
+          o << "struct EpiGen {\n  static constexpr bool kStaged = " << (to_regs ? "true" : "false") << ";\n  static constexpr bool kTransform = " << (to_regs ? "true" : "false") << ";\n";
+          o << "  static __device__ __forceinline__ void transform(const nxb_gemm::TcParams& p, float (&f)[32], long long b, long long m, long long n0) {\n";
+          if (to_regs) {
+            o << "    const " << I << " flat0 = (" << I << ")((b * p.m + m) * p.n + n0);\n";
+            o << "    if (n0 + 32 <= p.n) {\n#pragma unroll\n      for (int j = 0; j < 32; j += " << V << ") " << kname << "_regv(f + j, flat0 + j, p.ep, f + j);\n    } else {\n";
+            o << "      for (int j = 0; j < 32 && n0 + j < p.n; ++j) " << kname << "_reg1(f + j, flat0 + j, p.ep, f + j);\n    }\n";
+          }
+          o << "  }\n";
+          o << "  static __device__ __forceinline__ void store(const nxb_gemm::TcParams& p, float (&f)[32], const uint32_t (&raw)[32], long long b, long long m, long long n0) {\n";
           o << "    const " << I << " flat0 = (" << I << ")((b * p.m + m) * p.n + n0);\n";
           o << "    if (n0 + 32 <= p.n) {\n#pragma unroll\n      for (int j = 0; j < 32; j += " << V << ") " << kname << "_epiv(f + j, flat0 + j, p.ep);\n    } else {\n";
           o << "      for (int j = 0; j < 32 && n0 + j < p.n; ++j) " << kname << "_epi1(f + j, flat0 + j, p.ep);\n    }\n  }\n};\n";
@@ -2238,7 +2284,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           std::ostringstream d;
           d << gs.desc << " tile=128x" << gs.bn << " fused epilogue -> stores=[";
           for (size_t i = 0; i < u.stores.size(); ++i) d << (i ? "," : "") << g.nodes[u.stores[i]].op << "#" << u.stores[i];
-          d << "] (" << kname << ")";
+          d << "]" << (to_regs ? " staged TMA store" : "") << " (" << kname << ")";
           ks.desc = d.str();
           gs.desc = ks.desc;
           pl.kernels.push_back(std::move(ks));

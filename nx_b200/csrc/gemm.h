@@ -43,7 +43,10 @@ int tc_smem_bytes(int bn);
 // Threads per block of the tensor-core product: 192, or 320 (eight epilogue warps) when the contracted
 // extent is short enough that writing the tile out takes longer than computing it.
 int tc_block_threads(int64_t k);
-void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int* status_word, int sm_count, TcLaunch* out);
+// `staged_arg` >= 0: ep[staged_arg] is the one result (of type `staged_dt`) that the kernel stores itself through
+// shared memory and TMA; the tensor map of the result is then built over that buffer.
+void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int* status_word, int sm_count, TcLaunch* out,
+                       int staged_arg = -1, DType staged_dt = NXB_F32);
 const char* gemm_device_source();
 const char* attention_device_source();
 int attn_smem_bytes();

@@ -190,7 +190,8 @@ static TcParams make_params(const GemmArgs& g, int bn, int* status_word) {
   return p;
 }
 
-void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int* status_word, int sm_count, TcLaunch* out) {
+void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int* status_word, int sm_count, TcLaunch* out,
+                       int staged_arg, DType staged_dt) {
   static_assert(sizeof(CUtensorMap) == 128 && sizeof(TcParams) <= sizeof(out->params), "launch block too small");
   CUtensorMap ma = g.ta ? make_map_mn(g.a, g.da, g.k, g.m, g.batch, g.lda, g.bsa) : make_map(g.a, g.da, g.k, g.m, g.batch, g.lda, g.bsa, BM);
   CUtensorMap mb = g.tb ? make_map_mn(g.b, g.db, g.k, g.n, g.batch, g.ldb, g.bsb) : make_map(g.b, g.db, g.k, g.n, g.batch, g.ldb, g.bsb, bn);
@@ -198,8 +199,16 @@ void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int
   if (n_ep > (int)(sizeof(p.ep) / sizeof(p.ep[0]))) fail(NXB_ERR_UNSUPPORTED, "fused epilogue reads too many buffers");
   for (int i = 0; i < n_ep; ++i) p.ep[i] = ep[i];
   bool c_ok = false;
-  CUtensorMap mc = make_map_c(nullptr, g.dc, g.m, g.n, g.batch, &c_ok);    // generated epilogues store by themselves
-  p.tma_store = 0;
+  CUtensorMap mc;
+  if (staged_arg >= 0 && staged_arg < n_ep) {
+    // the epilogue hands its result back; the kernel converts to `staged_dt` and stores the tile
+    mc = make_map_c(ep[staged_arg], staged_dt, g.m, g.n, g.batch, &c_ok);
+    p.out_dt = staged_dt;
+    p.tma_store = c_ok ? 1 : 0;
+  } else {
+    mc = make_map_c(nullptr, g.dc, g.m, g.n, g.batch, &c_ok);    // the generated epilogue stores by itself
+    p.tma_store = 0;
+  }
   memcpy(out->map_a, &ma, 128);
   memcpy(out->map_b, &mb, 128);
   memcpy(out->map_c, &mc, 128);

@@ -308,6 +308,8 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t sr
 // and store them (128-bit stores when the segment is complete and rows are 16-byte aligned).
 struct EpiStore {
   static constexpr bool kStaged = true;     // may leave through the shared-memory staged TMA store
+  static constexpr bool kTransform = false; // a generated epilogue sets this and rewrites the 32 values in place before a staged store
+  static __device__ __forceinline__ void transform(const TcParams&, float (&)[32], long long, long long, long long) {}
   static __device__ __forceinline__ void store(const TcParams& p, float (&f)[32], const uint32_t (&v)[32], long long b, long long m, long long n0) {
     const long long rowoff = (b * p.m + m) * p.n;
     const bool vec_ok = (p.n % 8) == 0;
@@ -592,7 +594,7 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
     const uint32_t stage_bytes = 8192u / (uint32_t)epi_groups;     // staging memory of one warp
     // Plain 16-bit results without a scale take a short path: packed converts straight from the
     // accumulator registers, store offsets of this lane computed once.
-    const bool lean = KIND != KIND_S8 && Epi::kStaged && p.tma_store != 0 && !p.scale && (p.out_dt == NXB_BF16 || p.out_dt == NXB_F16);
+    const bool lean = KIND != KIND_S8 && Epi::kStaged && !Epi::kTransform && p.tma_store != 0 && !p.scale && (p.out_dt == NXB_BF16 || p.out_dt == NXB_F16);
     const uint32_t lean_slots = stage_bytes / 2048u;                // 4 or 2
     const uint32_t lean_base = sStore + (uint32_t)(warp - 2) * stage_bytes + (uint32_t)lane * 64u;
     const uint32_t lean_sw = (uint32_t)((lane >> 1) & 3);
@@ -658,6 +660,7 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
 #pragma unroll
             for (int j = 0; j < 32; ++j) if (n0 + j < p.n) f[j] *= p.scale[n0 + j];
           }
+          if (Epi::kTransform && m < p.m) Epi::transform(p, f, (long long)b, m, n0);
           if (p.out_dt == NXB_BF16 || p.out_dt == NXB_F16) {
             // rows of 64 bytes, 64-byte swizzle: 16-byte chunk j of row r sits at chunk j ^ ((r >> 1) & 3)
 #pragma unroll

@@ -84,6 +84,10 @@ struct GemmSpec {
   // consumers of this product; the product itself is then never written to memory
   int jit_kernel = -1;
   int bn = 256;
+  // >= 0: the generated epilogue hands its one result back in registers and the kernel stores the tile
+  // itself; index (among the kernel's buffer arguments) and type of that result
+  int staged_arg = -1;
+  DType staged_dt = NXB_F32;
 };
 
 struct AttentionSpec {

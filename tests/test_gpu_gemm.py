@@ -70,6 +70,32 @@ def test_bf16_batched_dot():
     assert_close(g, r, rtol=2 ** -7, atol=2 ** -9, what="batched bf16 dot")
 
 
+@pytest.mark.parametrize("m,n,k,out", [(130, 264, 72, "bf16"), (257, 520, 136, "f32"), (64, 1000, 2048, "bf16"), (384, 100, 512, "bf16"),
+                                       (3, 200, 136, "f32")])
+def test_fused_epilogue_ragged(m, n, k, out):
+    """relu(x . w + bias) * gate as one kernel: the epilogue's result leaves through the staged TMA
+    store when rows are 16-byte aligned (tiles clipped at both edges) and through per-lane stores otherwise
+    (n = 100: 200-byte rows)."""
+    rng = np.random.default_rng(6)
+    a = rng.normal(0, 1 / np.sqrt(k), (m, k)).astype(np.float32)
+    b = rng.normal(0, 1, (k, n)).astype(np.float32)
+    bias = rng.normal(0, 0.5, (n,)).astype(np.float32)
+    gate = rng.normal(0, 1, (m, n)).astype(np.float32)
+
+    def fun(x, w, c, gt):
+        y = nx.max(nx.dot(x, w) + c, 0.0) * gt
+        return nx.as_type(y, out)
+
+    types = ["bf16", "bf16", "bf16", "bf16"]
+    (g, r, t), = run_both(fun, [a, b, bias, gate], types)
+    assert g.shape == (m, n)
+    assert_close(g, r, rtol=2e-2, atol=1e-2, what=f"fused epilogue {m}x{n}x{k} -> {out}")
+    prog = defn.compile(fun, [defn.template(x.shape, "bf16") for x in (a, b, bias, gate)]).program
+    d = prog.describe()
+    assert "fused epilogue" in d
+    assert ("staged TMA store" in d) == ((n * (2 if out == "bf16" else 4)) % 16 == 0)
+
+
 def test_f16_dot():
     rng = np.random.default_rng(4)
     a = rng.normal(0, 0.1, (200, 264)).astype(np.float32)
