@@ -187,6 +187,10 @@ static TcParams make_params(const GemmArgs& g, int bn, int* status_word) {
   p.ntiles = (int)((g.n + bn - 1) / bn);
   p.out_dt = g.dc;
   p.epilogue = g.epilogue;
+  // The wave of sm_count tiles in flight covers panel_m x (sm_count / panel_m) tiles; its operand footprint
+  // panel_m * BM + (sm_count / panel_m) * bn rows is smallest near sqrt(sm_count * bn / BM).
+  p.panel_m = bn == 256 ? 16 : bn == 128 ? 12 : 8;
+  if (const char* e = getenv("NXB200_PANEL_M")) { const int v = atoi(e); if (v >= 1) p.panel_m = v; }
   return p;
 }
 

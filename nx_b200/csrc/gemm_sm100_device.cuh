@@ -14,7 +14,6 @@ enum { NXB_U8 = 0, NXB_U16 = 1, NXB_U32 = 2, NXB_U64 = 3, NXB_S8 = 4, NXB_S16 = 
 namespace nxb_gemm {
 
 constexpr int BM = 128;
-constexpr int PANEL_M = 16;                            // row tiles per panel of the tile walk
 constexpr int ROW_BYTES = 128;                        // one swizzle row: 64 bf16 or 128 s8
 constexpr int A_STAGE = BM * ROW_BYTES;
 // The tile width BN is 256 for large products; narrow outputs (few rows, e.g. a linear layer
@@ -40,6 +39,7 @@ struct TcParams {
   int epilogue;
   int a_mn, b_mn;    // operand stored with its free index contiguous ([k][m] / [k][n]) instead of k
   int tma_store;     // results leave through shared memory and a TMA store (rows of C 16-byte aligned)
+  int panel_m;       // row tiles per panel of the tile walk (>= 1)
   void* ep[14];      // buffers of a generated epilogue, in its argument order
 };
 
@@ -358,14 +358,14 @@ __device__ __forceinline__ void tile_coords(long long t, const TcParams& p, cons
     const long long tiles_per_batch = (long long)p.mtiles * p.ntiles;
     b = (int)(t / tiles_per_batch);
     const int r = (int)(t % tiles_per_batch);
-    // Panels of PANEL_M row tiles, walked column by column: the 148 tiles in flight then cover about
+    // Panels of `panel_m` row tiles, walked column by column: the 148 tiles in flight then cover about
     // 16 x 9 tiles, so one wave touches a few tens of MB of the operands (they stay in L2 from wave to
     // wave) instead of every row of A.
-    const int per_panel = PANEL_M * p.ntiles;
+    const int per_panel = p.panel_m * p.ntiles;
     const int panel = r / per_panel, j = r % per_panel;
-    const int rows = min(PANEL_M, p.mtiles - panel * PANEL_M);
+    const int rows = min(p.panel_m, p.mtiles - panel * p.panel_m);
     nt = j / rows;
-    mt = panel * PANEL_M + j % rows;
+    mt = panel * p.panel_m + j % rows;
   } else {
     const int mpo = p.mtiles / cm->world;
     const long long per_owner = (long long)mpo * p.ntiles;
