@@ -341,10 +341,28 @@ struct EpiStore {
       }
     } else if (p.out_dt == NXB_S32 || p.out_dt == NXB_U32) {
       int* out = (int*)p.c + rowoff + n0;
-      for (int j = 0; j < 32 && n0 + j < p.n; ++j) out[j] = (int)v[j];
+      if (full && (p.n % 4) == 0 && ((unsigned long long)p.c & 15ull) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(out + j) = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (n0 + j < p.n) out[j] = (int)v[j];
+      }
     } else {   // 8-bit integer result: the 32-bit sum written modulo 2^8
       unsigned char* out = (unsigned char*)p.c + rowoff + n0;
-      for (int j = 0; j < 32 && n0 + j < p.n; ++j) out[j] = (unsigned char)v[j];
+      if (full && (p.n % 16) == 0 && ((unsigned long long)p.c & 15ull) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 16) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            w[e] = (v[j + 4 * e] & 0xFFu) | ((v[j + 4 * e + 1] & 0xFFu) << 8) | ((v[j + 4 * e + 2] & 0xFFu) << 16) | (v[j + 4 * e + 3] << 24);
+          *reinterpret_cast<uint4*>(out + j) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (n0 + j < p.n) out[j] = (unsigned char)v[j];
+      }
     }
   }
 };
