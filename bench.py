@@ -278,6 +278,15 @@ def other_configs(timer, device, pk):
         ms, prog = time_program(timer, configs.quantised_linear, f_in, device)
         byt = 11008 * 4096 + 11008 * 4 + m * 4096 * 2 + m * 11008 * 4
         res[f"quantised_linear_M{m}"] = {"ms": round(ms, 4), "tflops": round(2 * m * 4096 * 11008 / ms / 1e9, 2), "gbs": round(byt / ms / 1e6, 1)}
+    # the integer-accumulate products (random s8 data): x {4096,4096} . W {11008,4096}^T with an s32 result, and s8 8192^3
+    nx_ = configs.nx
+    _, i_in = configs.quantised_inputs(m=4096)
+    ms, prog = time_program(timer, configs.integer_linear, i_in, device)
+    res["s8_dot_s32_4096x11008x4096"] = {"ms": round(ms, 4), "tops": round(2 * 4096 * 4096 * 11008 / ms / 1e9, 1), "plan": prog.describe().strip().split("\n")}
+    rng = np.random.default_rng(7)
+    sq = [(rng.integers(-127, 128, (8192, 8192)).astype(np.int8), "s8") for _ in range(2)]
+    ms, prog = time_program(timer, lambda x, w: nx_.dot(x, [1], w, [1]), sq, device)
+    res["s8_dot_s8_8192^3"] = {"ms": round(ms, 4), "tops": round(2 * 8192 ** 3 / ms / 1e9, 1)}
     return res
 
 
