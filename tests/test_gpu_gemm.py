@@ -37,8 +37,9 @@ def run_both(fun, arrays, types):
     return [(nx.to_numpy(g), r[0], r[1]) for g, r in zip(outs, ref)]
 
 
+# the last two have more row tiles than one panel of the tile walk, the final panel being partial
 SHAPES = [(128, 256, 64), (1, 8, 8), (130, 260, 72), (257, 513, 136), (64, 1000, 4096), (384, 768, 512),
-          (1024, 1024, 1024)]
+          (1024, 1024, 1024), (1100, 200, 64), (4500, 2056, 136)]
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)
