@@ -383,6 +383,7 @@ __device__ __forceinline__ void tile_coords(long long t, const TcParams& p, cons
     const int panel = r / per_panel, j = r % per_panel;
     const int rows = min(p.panel_m, p.mtiles - panel * p.panel_m);
     nt = j / rows;
+    if (panel & 1) nt = p.ntiles - 1 - nt;     // odd panels walk back: the columns of B just used are still in L2
     mt = panel * p.panel_m + j % rows;
   } else {
     const int mpo = p.mtiles / cm->world;
