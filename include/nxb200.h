@@ -176,11 +176,14 @@ int nxb200_program_launch_count(nxb200_program *prog, int *count);
  * NXB_ERR_INVALID_ARGUMENT.  Every GPU that loads the library holds those 32 MiB
  * until the process exits.
  *
- * The first call on a device looks up the array's device address (set-up that has
- * to happen outside any stream capture, so make that first call before capturing).
+ * The first call on a device looks up the array's device address; that first call
+ * should come before any stream capture.  Every call enqueues on `stream` (a
+ * cudaStream_t, or NULL for the default stream), reads a status word back and waits
+ * for `stream` to drain before it returns, so the result is complete on return.
+ * All arguments are checked before anything is enqueued: a rejected call leaves the
+ * scratch and the stream untouched.  The caller's current device is restored.
  * All calls share the one array: calls that overlap on the same GPU (different
- * streams or threads) race on it.  The call enqueues on `stream` (a cudaStream_t, or
- * NULL for the default stream) and returns after the result is complete. */
+ * streams or threads) race on it. */
 int nxb200_dot_bf16_static_scratch(int device, const void *a, const void *b, void *c,
                                    int64_t m, int64_t n, int64_t k, void *stream);
 

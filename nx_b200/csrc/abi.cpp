@@ -139,6 +139,15 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         void* taken = nullptr;
         for (auto& al : plan.aliases)
           if (al.output == i && al.in_place && !args[al.param]->deallocated.load() && !args[al.param]->borrowed) taken = args[al.param]->ptr;
+        // The plan proved "one reader, same position" per parameter slot, not per address: a buffer that
+        // is also passed as another argument, or was already taken for an earlier result, keeps its memory
+        // and this result gets its own.
+        if (taken) {
+          int uses = 0;
+          for (int a2 = 0; a2 < n_args; ++a2) if (args[a2]->ptr == taken) ++uses;
+          for (auto* mb : made) if (mb->ptr == taken) ++uses;
+          if (uses > 1) taken = nullptr;
+        }
         b->ptr = taken ? taken : d.alloc.alloc(sl.nbytes);
         ptr[plan.output_slots[i]] = b->ptr;
         made.push_back(b.release());
@@ -532,6 +541,20 @@ int nxb200_buffer_from_pointer(int dev, nxb200_dtype dtype, const int64_t* dims,
       b->dims.push_back(dims[i]);
     }
     b->nbytes = (size_t)shape_numel(b->dims) * dtype_size(b->dtype);
+    // Generated kernels and tensor maps take vector accesses from element offsets alone: the base has
+    // to sit on a 16-byte boundary, and the tensor has to lie inside the allocation it points into.
+    if (((uintptr_t)device_ptr) % 16 != 0)
+      fail(NXB_ERR_INVALID_ARGUMENT, "the device address must be 16-byte aligned");
+    if (driver().cuMemGetAddressRange) {
+      CUdeviceptr base = 0;
+      size_t size = 0;
+      if (driver().cuMemGetAddressRange(&base, &size, (CUdeviceptr)(uintptr_t)device_ptr) == CUDA_SUCCESS) {
+        const size_t before = (size_t)((CUdeviceptr)(uintptr_t)device_ptr - base);
+        if (before > size || b->nbytes > size - before)
+          fail(NXB_ERR_INVALID_ARGUMENT, "the tensor needs " + std::to_string(b->nbytes) + " bytes, the allocation holds " +
+                                             std::to_string(size - std::min(before, size)) + " from that address");
+      }
+    }
     b->ptr = device_ptr;
     b->borrowed = true;
     *out = b.release();
@@ -611,6 +634,7 @@ int nxb200_buffer_release(nxb200_buffer* buf) {
     if (!b->deallocated.exchange(true) && b->ptr) {
       Device& d = nxb::device(b->device);
       std::lock_guard<std::mutex> g(d.mu);
+      order_after_downloads(d);    // as in deallocate: the next owner of this memory writes it on the compute stream
       if (b->ipc_base) {
         cudaStreamSynchronize(d.stream);
         cudaIpcCloseMemHandle(b->ipc_base);
@@ -666,13 +690,14 @@ int nxb200_program_release(nxb200_program* prog) {
       if (cudaSetDevice(kv.first) != cudaSuccess) { (void)cudaGetLastError(); continue; }
       Device& d = nxb::device(kv.first);
       cudaStreamSynchronize(d.stream);
-      for (auto m : kv.second.modules) driver().cuModuleUnload(m);
       std::lock_guard<std::mutex> g(d.mu);
-      for (auto& l : kv.second.literals) d.alloc.free(l.second);
+      // the captured graphs refer to kernels of the modules: they go first
       for (auto& r : kv.second.replays) {
         cudaGraphExecDestroy(r.exec);
         for (void* h : r.held) d.alloc.free(h);
       }
+      for (auto m : kv.second.modules) driver().cuModuleUnload(m);
+      for (auto& l : kv.second.literals) d.alloc.free(l.second);
     }
     p->magic = 0;
     delete p;

@@ -75,6 +75,7 @@ struct DriverApi {
                                      const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                      const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
+  CUresult (*cuMemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr) = nullptr;
 };
 const DriverApi& driver();
 void check_cu(CUresult r, const char* what);

@@ -393,7 +393,22 @@ extern "C" int nxb200_dot_bf16_static_scratch(int device, const void* a, const v
     if (need > NOALLOC_SCRATCH_BYTES)
       fail(NXB_ERR_INVALID_ARGUMENT, "operand b has " + std::to_string(need) + " bytes; the built-in scratch holds at most " +
                                          std::to_string(NOALLOC_SCRATCH_BYTES) + " (k*n <= " + std::to_string(NOALLOC_SCRATCH_BYTES / 2) + " elements)");
-    NXB_CUDA(cudaSetDevice(device));
+    // every check comes before the first enqueue: a rejected call leaves the shared scratch untouched
+    if (((uintptr_t)a) % 16 || ((uintptr_t)b) % 16 || ((uintptr_t)c) % 16)
+      fail(NXB_ERR_INVALID_ARGUMENT, "a, b and c must be 16-byte aligned device pointers");
+    if (m >= (int64_t(1) << 31) || n >= (int64_t(1) << 31) || k >= (int64_t(1) << 31))
+      fail(NXB_ERR_INVALID_ARGUMENT, "m, n and k must be below 2^31");
+    // the caller's current device is put back on every way out
+    struct DeviceGuard {
+      int prev = -1;
+      ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+    } guard;
+    {
+      int cur = -1;
+      NXB_CUDA(cudaGetDevice(&cur));
+      NXB_CUDA(cudaSetDevice(device));
+      if (cur != device) guard.prev = cur;
+    }
     NoAllocDevice dev;
     {
       // One-time set-up per device, with that device current: in host code the array's
@@ -409,9 +424,6 @@ extern "C" int nxb200_dot_bf16_static_scratch(int device, const void* a, const v
       }
       dev = it->second;
     }
-    // the status word must start at zero; the scratch is fully rewritten before it is read
-    NXB_CUDA(cudaMemsetAsync(dev.status, 0, sizeof(int), stream));
-    launch_transpose(b, dev.scratch, 1, k, n, 2, stream);          // B {k,n} -> {n,k}
     GemmArgs g{};
     g.a = a; g.b = dev.scratch; g.c = c;
     g.batch = 1; g.m = m; g.n = n; g.k = k;
@@ -419,6 +431,9 @@ extern "C" int nxb200_dot_bf16_static_scratch(int device, const void* a, const v
     g.ta = g.tb = false;
     g.da = g.db = g.dc = NXB_BF16;
     if (!tc_gemm_supported(g)) fail(NXB_ERR_INVALID_ARGUMENT, "operands must be 16-byte aligned");
+    // the status word must start at zero; the scratch is fully rewritten before it is read
+    NXB_CUDA(cudaMemsetAsync(dev.status, 0, sizeof(int), stream));
+    launch_transpose(b, dev.scratch, 1, k, n, 2, stream);          // B {k,n} -> {n,k}
     launch_tc_gemm(g, dev.status, dev.sm_count, stream);
     int status = 0;
     NXB_CUDA(cudaMemcpyAsync(&status, dev.status, sizeof(int), cudaMemcpyDeviceToHost, stream));

@@ -313,7 +313,9 @@ struct EpiStore {
   static __device__ __forceinline__ void transform(const TcParams&, float (&)[32], long long, long long, long long) {}
   static __device__ __forceinline__ void store(const TcParams& p, float (&f)[32], const uint32_t (&v)[32], long long b, long long m, long long n0) {
     const long long rowoff = (b * p.m + m) * p.n;
-    const bool vec_ok = (p.n % 8) == 0;
+    // vector stores need 16-byte aligned rows: the row length and the base of C both count
+    const bool base_ok = ((unsigned long long)p.c & 15ull) == 0;
+    const bool vec_ok = (p.n % 8) == 0 && base_ok;
     const bool full = n0 + 32 <= p.n;
     if (p.out_dt == NXB_BF16 || p.out_dt == NXB_F16) {
       unsigned short* out = (unsigned short*)p.c + rowoff + n0;
@@ -333,7 +335,7 @@ struct EpiStore {
       }
     } else if (p.out_dt == NXB_F32) {
       float* out = (float*)p.c + rowoff + n0;
-      if (full && (p.n % 4) == 0) {
+      if (full && (p.n % 4) == 0 && base_ok) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(out + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
       } else {
@@ -341,7 +343,7 @@ struct EpiStore {
       }
     } else if (p.out_dt == NXB_S32 || p.out_dt == NXB_U32) {
       int* out = (int*)p.c + rowoff + n0;
-      if (full && (p.n % 4) == 0 && ((unsigned long long)p.c & 15ull) == 0) {
+      if (full && (p.n % 4) == 0 && base_ok) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4*>(out + j) = make_int4((int)v[j], (int)v[j + 1], (int)v[j + 2], (int)v[j + 3]);
       } else {
@@ -350,7 +352,7 @@ struct EpiStore {
       }
     } else {   // 8-bit integer result: the 32-bit sum written modulo 2^8
       unsigned char* out = (unsigned char*)p.c + rowoff + n0;
-      if (full && (p.n % 16) == 0 && ((unsigned long long)p.c & 15ull) == 0) {
+      if (full && (p.n % 16) == 0 && base_ok) {
 #pragma unroll
         for (int j = 0; j < 32; j += 16) {
           uint32_t w[4];

@@ -63,6 +63,7 @@ const DriverApi& driver() {
     get("cuFuncSetAttribute", (void**)&g_driver.cuFuncSetAttribute);
     get("cuGetErrorString", (void**)&g_driver.cuGetErrorString);
     get("cuTensorMapEncodeTiled", (void**)&g_driver.cuTensorMapEncodeTiled);
+    get("cuMemGetAddressRange", (void**)&g_driver.cuMemGetAddressRange);
   });
   return g_driver;
 }

@@ -72,3 +72,20 @@ def test_donation_pairs_and_plans():
     outs, _, params = defn._trace(lambda a, b: b + 1, [defn.template((2,), "s32")] * 2)
     with pytest.raises(ValueError, match="not used by the computation"):
         defn.alias_pairs([0], params, outs)
+
+
+def test_static_scratch_product_checks_arguments_before_touching_a_device():
+    """Every argument check of the allocation-free product runs on the host before
+    the first CUDA call, so a refused call cannot have written the shared scratch
+    or enqueued anything (the addresses below are never dereferenced)."""
+    lib = nif.lib()
+    ok = ctypes.c_void_p(0x7F0000001000)
+    odd = ctypes.c_void_p(0x7F0000001002)
+    call = lib.nxb200_dot_bf16_static_scratch
+    for a, b, c in [(odd, ok, ok), (ok, odd, ok), (ok, ok, odd)]:
+        assert call(0, a, b, c, 128, 128, 128, None) == nif.ERR_INVALID
+        assert "16-byte aligned" in nif.last_error()
+    assert call(0, ok, ok, ok, 8, 8192, 4096, None) == nif.ERR_INVALID      # k*n beyond the built-in scratch
+    assert "scratch" in nif.last_error()
+    assert call(0, ok, ok, ok, 8, 8, 12, None) == nif.ERR_INVALID           # rows not on 16-byte boundaries
+    assert call(0, ok, ok, None, 8, 8, 8, None) == nif.ERR_INVALID

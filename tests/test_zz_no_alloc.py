@@ -6,7 +6,8 @@ point with buffers they own; its scratch is a fixed array inside the library.
 The test drives it through the C ABI twice in a row on different data (the
 array keeps the previous call's contents, so the second call proves nothing
 stale is read) and checks both results bit for bit against the regular
-`program_run` path, which runs the same tensor-core kernel.
+`program_run` path, which runs the same tensor-core kernel, and against the
+CPU oracle within the bf16 tolerance (rtol 2e-2, atol 1e-2).
 
 This file sorts last on purpose: a run that stops at the first failure has
 already executed every other test.
@@ -16,6 +17,8 @@ import ctypes as C
 import numpy as np
 import pytest
 
+import nx_oracle as O
+from helpers import assert_close
 from nx_b200 import backend, defn, nif, nx
 
 pytestmark = pytest.mark.gpu
@@ -43,6 +46,9 @@ def test_static_scratch_dot_matches_regular_path_twice():
             st = lib.nxb200_dot_bf16_static_scratch(0, _raw_pointer(a), _raw_pointer(b), _raw_pointer(out), m, n, k, stream)
             nif.check(st)
             assert nx.to_binary(out) == want, f"{m}x{n}x{k}: differs from the regular entry point"
+            blob, _ = defn.build_program(lambda x, y: nx.dot(x, y), [defn.template((m, k), "bf16"), defn.template((k, n), "bf16")])
+            (ref, _, _), = O.run_program(blob, [nx.to_binary(a), nx.to_binary(b)], "xla_like")
+            assert_close(nx.to_numpy(out), ref, 2e-2, 1e-2, f"{m}x{n}x{k} against the oracle")
     finally:
         backend.set_default_backend(None)
 
@@ -59,5 +65,10 @@ def test_static_scratch_dot_rejects_what_does_not_fit():
         # rows that would not start on 16-byte boundaries
         assert lib.nxb200_dot_bf16_static_scratch(0, p, p, p, 8, 8, 12, None) == nif.ERR_INVALID
         assert lib.nxb200_dot_bf16_static_scratch(0, None, p, p, 8, 8, 8, None) == nif.ERR_INVALID
+        # a result pointer that is not 16-byte aligned is refused on the host; nothing is launched
+        odd = C.c_void_p(p.value + 2)
+        assert lib.nxb200_dot_bf16_static_scratch(0, p, p, odd, 8, 8, 8, None) == nif.ERR_INVALID
+        assert "aligned" in nif.last_error()
+        assert lib.nxb200_dot_bf16_static_scratch(0, p, odd, p, 8, 8, 8, None) == nif.ERR_INVALID
     finally:
         backend.set_default_backend(None)
