@@ -18,9 +18,16 @@ configuration (the decoder block) is timed in the same run and reported under
 tensor-parallel linears with an NCCL all-reduce after each row-parallel product.
 
 ``--impl reference`` times the CPU restatement of the same graph
-(oracle/rows_oracle.c, all host threads).  ``--all-configs`` adds device-time
-measurements of the other configurations (MLP, dense dot, batched dot,
-quantised linear) under ``"configs"``.
+(oracle/rows_oracle.c, all host threads); each of its K steps runs a bounded
+sample of the rows so that the run ends within a minute or so.
+
+At N = 1 the line also carries ``"configs"``: device-time measurements of the
+other configurations (MLP, dense dot, batched dot, quantised linear, integer
+dot), each over at least 100 timed launches with its own clock sample and its
+roofline fraction; ``--no-configs`` leaves them out.  At N > 1 the decoder
+section checks every rank's sharded result against the single-GPU program's and
+prints the outcome under ``"decoder": {"parity": ...}``; a mismatch aborts the
+run without a line.
 """
 from __future__ import annotations
 
@@ -44,11 +51,24 @@ SEED = 1
 METRIC, UNIT = "fused-op HBM GB/s", "GB/s"
 WORKLOAD = "fused row defn f32 {%d,32768} (max, exp, sum, logsumexp, softmax, argmax, tanh*sigmoid chain)"
 
-# DRAM bytes per launch of the row kernel from one ncu capture of a 1024-row case
-# (dram__bytes_read.sum + dram__bytes_write.sum = 134.3 MB + 343.8 MB), scaled by the
-# row count; reads match the algorithmic 128 MiB exactly, writes are below the
-# algorithmic 384 MiB because the last ~59 MB were still dirty in L2 when the kernel ended.
-NCU_TRAFFIC_BYTES_PER_1024_ROWS = 134_280_448 + 343_771_136
+# DRAM traffic of one launch of the row kernel, derived from an ncu capture of a 1024-row case
+# (dram__bytes_read.sum = 134,280,448, dram__bytes_write.sum = 343,771,136): reads grow with the
+# rows (every row is read once); writes are the algorithmic output bytes less what was still
+# dirty in L2 when the kernel ended, which is a constant of the cache, not of the row count.
+NCU_READ_BYTES_PER_ROW = 134_280_448 / 1024
+NCU_L2_RESIDUE_BYTES = (3 * 1024 * 32768 * 4 + 1024 * 16) - 343_771_136
+
+
+def row_kernel_traffic(rows, cols):
+    writes = 3 * rows * cols * 4 + rows * 16
+    return int(NCU_READ_BYTES_PER_ROW * rows * (cols / 32768) + max(0, writes - NCU_L2_RESIDUE_BYTES))
+
+
+def workload_config(rows, world):
+    """The `config` object of the line; both arms print the same one."""
+    return {"workload": WORKLOAD % rows, "seed": SEED,
+            "parallelism": "replicas only" if world > 1 else "single GPU",
+            "l2": "input (1 GiB) and outputs (3 GiB) per step exceed L2 (126 MB); no flush needed"}
 
 
 def algorithmic_bytes(rows, cols):
@@ -70,11 +90,11 @@ class ClockSampler:
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index):
+    def __init__(self, index, period_ms=50):
         self.rows, self.proc = [], None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                          "--format=csv,noheader,nounits", "-lms", str(period_ms)],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -143,26 +163,34 @@ def cpu_baseline(x):
 
 
 def run_reference(args, rank):
+    """The CPU arm: K steps, each over a bounded sample of the rows (a contiguous block that
+    moves through the matrix), sized from a first pass so that the K steps take about a minute."""
     if rank != 0:
         return
     from nx_b200 import configs
-    rows = ROWS
-    x = configs.fused_rows_input(rows, COLS, SEED)
-    f = CpuRows(rows, COLS)
-    for _ in range(max(1, min(args.warmup, 2))):
-        f(x[:256])
-    steps = max(1, min(args.steps, 10))             # each step is the whole workload (under a second per step)
-    times = [f(x) for _ in range(steps)]
+    x = configs.fused_rows_input(ROWS, COLS, SEED)
+    f = CpuRows(ROWS, COLS)
+    f(x[:256])
+    per_row = f(x[:1024]) / 1024
+    for _ in range(max(0, min(args.warmup, 3) - 1)):
+        f(x[:1024])
+    steps = max(1, args.steps)
+    sample = int(60.0 / steps / per_row) // 256 * 256
+    sample = max(1024, min(ROWS, sample))
+    times = []
+    for i in range(steps):
+        r0 = (i * sample) % (ROWS - sample + 1)
+        times.append(f(x[r0:r0 + sample]))
     dt = sum(times) / len(times)
-    gbs = algorithmic_bytes(rows, COLS) / dt / 1e9
+    gbs = algorithmic_bytes(sample, COLS) / dt / 1e9
     cores = f.lib.rows_oracle_threads()
+    what = f"{sample} of {ROWS} rows per step ({sample * COLS * 16 >> 20} MiB of traffic, beyond the host caches), {steps} steps"
     line = {"impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": UNIT, "n_gpus": args.gpus,
             "steps": steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD % rows, "seed": SEED,
-                       "note": "CPU restatement of the reference's evaluator path (one pass per output), all host threads"},
-            "cpu_baseline": {"value": round(gbs, 3), "unit": UNIT, "cores": cores, "kind": "port",
-                             "sample": f"whole workload per step, {steps} steps"},
+            "config": workload_config(ROWS, args.gpus),
+            "note": "CPU restatement of the reference's evaluator path (one pass per output), all host threads",
+            "cpu_baseline": {"value": round(gbs, 3), "unit": UNIT, "cores": cores, "kind": "port", "sample": what},
             "e2e": {"value": round(gbs, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))
@@ -200,14 +228,149 @@ def time_program(timer, fun, inputs, device, steps=10):
     return timer.time(lambda: prog.run_into(dev, outs, device), steps), prog
 
 
+class StreamTimer:
+    """Per-launch device times with an L2 flush before every launch: events of the library's compute
+    stream (wrapped as a torch stream) bracket the launch alone, the flush (a write of a buffer twice
+    the size of L2) sits outside them."""
+
+    def __init__(self, lib, device, torch):
+        from nx_b200 import nif
+        h = C.c_void_p()
+        nif.check(lib.nxb200_device_stream(device, C.byref(h)))
+        self.torch, self.lib, self.device = torch, lib, device
+        self.stream = torch.cuda.ExternalStream(h.value, device=device)
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=f"cuda:{device}")
+
+    def flushed(self, fn, iters=30):
+        torch = self.torch
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+        with torch.cuda.stream(self.stream):
+            for a, b in evs:
+                self.flush.zero_()
+                a.record(self.stream)
+                fn()
+                b.record(self.stream)
+        self.stream.synchronize()
+        return statistics.median(a.elapsed_time(b) for a, b in evs)
+
+
+def timed_config(timer, device, fun, inputs, work, bound, peak, unit, min_iters=100, min_ms=300.0, flusher=None):
+    """One configuration: at least `min_iters` timed launches lasting at least `min_ms` in total, with
+    the SM clock sampled during them.  `work` is flop (tensor bound) or algorithmic bytes (hbm bound)."""
+    from nx_b200 import backend, defn
+    dev = device_inputs(inputs)
+    prog = defn.compile(fun, [defn.template(a.shape, t) for a, t in inputs], device=device).program
+    outs = prog.run(dev, device)
+    run = lambda: prog.run_into(dev, outs, device)
+    probe = timer.time(run, 10, warmup=5)                       # a short burst: sizes the loop
+    iters = int(max(min_iters, min(20000, min_ms / max(probe, 1e-4))))
+    sampler = ClockSampler(device, period_ms=20)
+    ms = timer.time(run, iters, warmup=3)
+    clocks = sampler.stop()
+    rate = work / ms / 1e9 if bound == "tensor" else work / ms / 1e6
+    res = {"ms": round(ms, 5), "iters": iters, "burst_ms": round(probe, 5), "launches": prog.launch_count(),
+           "roofline": {"bound": bound, "achieved": round(rate, 1), "peak": peak, "unit": unit, "frac": round(rate / peak, 4)},
+           "clocks": clocks}
+    if flusher is not None:
+        res["ms_l2_flushed"] = round(flusher.flushed(run), 5)
+    for t_ in dev + outs:
+        backend.backend_deallocate(t_)
+    return res, prog
+
+
+def int8_yardstick(torch, device):
+    """A library integer product as the denominator for the s8 rates: torch._int_mm 8192^3 -> s32,
+    best of 10 (used by the benchmark only, never by the product path)."""
+    try:
+        a = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device=f"cuda:{device}")
+        b = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device=f"cuda:{device}").t()
+        for _ in range(3):
+            torch._int_mm(a, b)
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        del a, b
+        torch.cuda.empty_cache()
+        return {"tops": round(2 * 8192 ** 3 / best / 1e9, 1), "how": "torch._int_mm s8 8192^3 -> s32, best of 10"}
+    except Exception as e:   # noqa: BLE001 - the yardstick is optional
+        return {"tops": None, "how": f"torch._int_mm unavailable: {type(e).__name__}"}
+
+
+def other_configs(timer, device, pk, torch):
+    """Device-time measurements of the other configurations, each with clocks and a roofline."""
+    from nx_b200 import configs, nif
+    nx_ = configs.nx
+    flusher = StreamTimer(nif.lib(), device, torch)
+    hbm, tf_burst, tf_sus = float(pk["hbm_gbs"]), float(pk["bf16_tflops"]), float(pk.get("bf16_tflops_sustained", pk["bf16_tflops"]))
+    res = {"peaks": {"hbm_gbs": hbm, "bf16_tflops_burst": tf_burst, "bf16_tflops_sustained": tf_sus,
+                     "note": "roofline.frac of the tensor-bound entries is against the burst figure; loops of 0.3 s and more "
+                             "run under the power cap, where the sustained figure is the library's own ceiling"}}
+    r, _ = timed_config(timer, device, configs.mlp, configs.mlp_inputs(), 2 * 64 * (784 * 128 + 128 * 10), "tensor", tf_burst, "TFLOP/s")
+    r["note"] = "launch bound: four kernels replayed as one CUDA graph"
+    res["mlp_f32_64x784x128x10"] = r
+
+    def tensor_entry(name, fun, inputs, flop, peak=tf_burst, unit="TFLOP/s"):
+        r, prog = timed_config(timer, device, fun, inputs, flop, "tensor", peak, unit)
+        if unit == "TFLOP/s":
+            r["roofline"]["frac_of_sustained"] = round(r["roofline"]["achieved"] / tf_sus, 4)
+            r["burst_tflops"] = round(flop / r["burst_ms"] / 1e9, 1)
+        r["plan"] = prog.describe().strip().split("\n")
+        res[name] = r
+
+    dense = configs.dense_inputs()
+    tensor_entry("dense_bf16_8192^3_bias_gelu", configs.dense_bias_gelu, dense, 2 * 8192 ** 3)
+    tensor_entry("dot_bf16_8192^3_kmajor", lambda a, b: nx_.dot(a, [1], b, [1]), [dense[0], dense[0]], 2 * 8192 ** 3)
+    del dense
+    byt = (2 * 64 * 2048 * 128 + 64 * 2048 * 2048) * 2
+    r, _ = timed_config(timer, device, configs.batched_dot, configs.batched_inputs(), byt, "hbm", hbm, "GB/s")
+    r["tflops"] = round(2 * 64 * 2048 * 2048 * 128 / r["ms"] / 1e9, 1)
+    res["batched_bf16_64x2048x128x2048"] = r
+    for m in (1, 16, 256, 4096):
+        f_in, _ = configs.quantised_inputs(m=m)
+        byt = 11008 * 4096 + 11008 * 4 + m * 4096 * 2 + m * 11008 * 4
+        flop = 2 * m * 4096 * 11008
+        if m <= 16:
+            r, prog = timed_config(timer, device, configs.quantised_linear, f_in, byt, "hbm", hbm, "GB/s", flusher=flusher)
+            r["roofline"]["achieved_l2_flushed"] = round(byt / r["ms_l2_flushed"] / 1e6, 1)
+            r["roofline"]["frac_l2_flushed"] = round(byt / r["ms_l2_flushed"] / 1e6 / hbm, 4)
+            r["note"] = "ms: back-to-back launches (W, 45 MB, stays in L2); ms_l2_flushed: median single launch after an L2 flush"
+        else:
+            r, prog = timed_config(timer, device, configs.quantised_linear, f_in, flop, "tensor", tf_burst, "TFLOP/s")
+            r["roofline"]["frac_of_sustained"] = round(r["roofline"]["achieved"] / tf_sus, 4)
+            r["gbs"] = round(byt / r["ms"] / 1e6, 1)
+        r["plan"] = prog.describe().strip().split("\n")
+        res[f"quantised_linear_M{m}"] = r
+    # the integer-accumulate products (random s8 data) against a measured library integer product
+    yard = int8_yardstick(torch, device)
+    res["int8_yardstick"] = yard
+    ipeak, iunit = (yard["tops"], "TOP/s") if yard["tops"] else (4500.0, "TOP/s")
+    _, i_in = configs.quantised_inputs(m=4096)
+    tensor_entry("s8_dot_s32_4096x11008x4096", configs.integer_linear, i_in, 2 * 4096 * 4096 * 11008, ipeak, iunit)
+    rng = np.random.default_rng(7)
+    sq = [(rng.integers(-127, 128, (8192, 8192)).astype(np.int8), "s8") for _ in range(2)]
+    tensor_entry("s8_dot_s8_8192^3", lambda x, w: nx_.dot(x, [1], w, [1]), sq, 2 * 8192 ** 3, ipeak, iunit)
+    for k in ("s8_dot_s32_4096x11008x4096", "s8_dot_s8_8192^3"):
+        res[k]["roofline"]["peak_source"] = "measured yardstick (int8_yardstick)" if yard["tops"] else "nominal 4.5 POP/s"
+    return res
+
+
 def decoder_section(timer, device, rank, world, dist, torch):
-    """Decoder block tokens/s: single GPU, batch data-parallel and tensor-parallel."""
-    from nx_b200 import backend as B, configs, defn, nx, sharding
+    """Decoder block tokens/s: single GPU, batch data-parallel, tensor-parallel and {dp, tp} meshes.
+    At N > 1 every sharded result is compared with the single-GPU program's result on this rank's GPU."""
+    from nx_b200 import backend as B, configs, defn, nif, nx, sharding
+    import zlib
+    lib = nif.lib()
     block = configs.make_decoder_block()
     batch, seq = 8, 2048
     inputs = configs.decoder_inputs(batch=batch, seq=seq)
     out = {"tokens_per_step": batch * seq, "flops_per_token": 438.4e6,
            "note": "bf16 {8,2048,4096}, 32 heads, SwiGLU 11008; FLOP count uses full (unmasked) attention"}
+    parity = {}
 
     def sync_max(ms):
         if dist is None:
@@ -216,7 +379,40 @@ def decoder_section(timer, device, rank, world, dist, torch):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    def run_sharded(mesh, shardings, label):
+    reference = {}
+
+    def single_reference():
+        """The single-GPU program's result for the whole batch, computed on this rank's GPU."""
+        if "out" not in reference:
+            dev = device_inputs(inputs)
+            prog = defn.compile(block, [defn.template(a.shape, t) for a, t in inputs], device=device).program
+            o, = prog.run(dev, device)
+            reference["out"] = nx.to_numpy(o)
+            for t_ in dev + [o]:
+                B.backend_deallocate(t_)
+        return reference["out"]
+
+    def check_parity(label, got, batch_slice, replicated_over):
+        """bf16 tolerance against the single-GPU result; results that are replicated over a
+        tensor-parallel group must be bit-identical within it."""
+        want = single_reference()[batch_slice]
+        err = np.abs(got - want)
+        ok = bool(np.all(err <= 1e-2 + 2e-2 * np.abs(want)))
+        mine = {"ok": ok, "max_abs_err": float(err.max()), "bit_identical_to_single": bool(np.array_equal(got, want)),
+                "crc": zlib.crc32(got.tobytes()), "group": replicated_over}
+        rows = [None] * world
+        dist.all_gather_object(rows, mine)
+        groups = {}
+        for r_ in rows:
+            groups.setdefault(r_["group"], set()).add(r_["crc"])
+        same = all(len(v) == 1 for v in groups.values())
+        parity[label] = {"ok": all(r_["ok"] for r_ in rows), "ranks_checked": world,
+                         "tolerance": "rtol 2e-2 atol 1e-2 (bf16), every element of every rank's result",
+                         "max_abs_err": max(r_["max_abs_err"] for r_ in rows),
+                         "bit_identical_to_single_gpu": all(r_["bit_identical_to_single"] for r_ in rows),
+                         "bit_identical_across_group": same}
+
+    def run_sharded(mesh, shardings, label, check=True, batch_axis=None, group_axis=None):
         def shard(a, sh):
             for dim, axes in sh.items():
                 n = mesh.shape[axes[0]]
@@ -236,58 +432,58 @@ def decoder_section(timer, device, rank, world, dist, torch):
         ms = sync_max(timer.time(lambda: prog.run_into(dev, outs, device), 5, warmup=2))
         out[label] = {"ms_per_step": round(ms, 3), "tokens_per_s": round(batch * seq / ms * 1e3),
                       "tflops": round(438.4e6 * batch * seq / ms / 1e9, 1), "launches_per_step": prog.launch_count()}
+        if check and dist is not None:
+            coords = mesh.coords(rank)
+            if batch_axis is None:
+                sl, grp = slice(0, batch), "all"
+            else:
+                per = batch // mesh.shape[batch_axis]
+                sl = slice(coords[batch_axis] * per, (coords[batch_axis] + 1) * per)
+                grp = f"dp{coords[batch_axis]}" if group_axis is not None else f"rank{rank}"
+            check_parity(label, nx.to_numpy(outs[0]), sl, grp)
+        for t_ in dev + outs:
+            B.backend_deallocate(t_)
+
+    def tensor_parallel(mesh, tp_axis, dp_axis, label, also_nccl):
+        ex = sharding.torch_exchange()
+        b_local = batch // (mesh.shape[dp_axis] if dp_axis is not None else 1)
+        peer = sharding.init_tensor_parallel_group(mesh, tp_axis, rank, device, ex, gather=sharding.torch_gather(),
+                                                   peer_elems=b_local * seq * 4096)
+        xs = {0: [dp_axis]} if dp_axis is not None else {}
+        col, row = {1: [tp_axis]}, {0: [tp_axis]}
+        tp = [xs, col, col, col, row, col, col, row, {}, {}]
+        kw = dict(batch_axis=dp_axis, group_axis=tp_axis)
+        if also_nccl:
+            # the two all-reduces as NCCL calls after their products, then fused into the products over peer memory
+            os.environ["NXB200_FUSED_ALLREDUCE"] = "never"
+            run_sharded(mesh, tp, label + "_nccl", **kw)
+            del os.environ["NXB200_FUSED_ALLREDUCE"]           # automatic choice per product
+        before = sharding.fused_all_reduce_launches()
+        run_sharded(mesh, tp, label, **kw)
+        fused = (sharding.fused_all_reduce_launches() - before) // 8 if peer else 0      # 1 + 2 + 5 runs
+        out[label]["all_reduce"] = f"{fused} of 2 fused into their products over peer memory, the rest NCCL"
+        if fused and label in parity:
+            # the fused kernel reduces every tile once, in rank order, on its owner: the copies must agree bit for bit
+            parity[label]["ok"] = parity[label]["ok"] and parity[label]["bit_identical_across_group"]
+        nif.check(lib.nxb200_device_synchronize(device))
+        dist.barrier()
+        nif.check(lib.nxb200_comm_destroy())
+        dist.barrier()
 
     if world == 1:
-        run_sharded(sharding.Mesh("one", (1,)), [{}] * 10, "single")
+        run_sharded(sharding.Mesh("one", (1,)), [{}] * 10, "single", check=False)
     else:
-        run_sharded(sharding.Mesh("dp", (world,)), [{0: [0]}] + [{}] * 9, f"dp{world}")
-        mesh = sharding.Mesh("tp", (world,))
-        ex = sharding.torch_exchange()
-        peer = sharding.init_tensor_parallel_group(mesh, 0, rank, device, ex, gather=sharding.torch_gather(),
-                                                   peer_elems=batch * seq * 4096)
-        tp = [{}, {1: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {1: [0]}, {1: [0]}, {0: [0]}, {}, {}]
-        # the two all-reduces as NCCL calls after their products, then fused into the products over peer memory
-        os.environ["NXB200_FUSED_ALLREDUCE"] = "never"
-        run_sharded(mesh, tp, f"tp{world}_nccl")
-        del os.environ["NXB200_FUSED_ALLREDUCE"]           # automatic choice per product
-        before = sharding.fused_all_reduce_launches()
-        run_sharded(mesh, tp, f"tp{world}")
-        fused = (sharding.fused_all_reduce_launches() - before) // 8 if peer else 0      # 1 + 2 + 5 runs
-        out[f"tp{world}"]["all_reduce"] = f"{fused} of 2 fused into their products over peer memory, the rest NCCL"
+        run_sharded(sharding.Mesh("dp", (world,)), [{0: [0]}] + [{}] * 9, f"dp{world}", batch_axis=0)
+        tensor_parallel(sharding.Mesh("tp", (world,)), 0, None, f"tp{world}", also_nccl=True)
+        for dp in (2, 4):
+            tp_ = world // dp
+            if tp_ >= 2 and dp * tp_ == world:
+                tensor_parallel(sharding.Mesh("dp_tp", (dp, tp_)), 1, 0, f"dp{dp}xtp{tp_}", also_nccl=False)
+        out["parity"] = parity
+        best = min((k for k in out if isinstance(out[k], dict) and "ms_per_step" in out[k]), key=lambda k: out[k]["ms_per_step"])
+        out["best"] = best
+    reference.clear()
     return out
-
-
-def other_configs(timer, device, pk):
-    from nx_b200 import configs
-    res = {}
-    ms, prog = time_program(timer, configs.mlp, configs.mlp_inputs(), device, steps=50)
-    res["mlp_f32_64x784x128x10"] = {"ms": round(ms, 4), "launches": prog.launch_count()}
-    ms, prog = time_program(timer, configs.dense_bias_gelu, configs.dense_inputs(), device)
-    tf = 2 * 8192 ** 3 / ms / 1e9
-    res["dense_bf16_8192^3_bias_gelu"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / pk["bf16_tflops"], 3),
-                                           "plan": prog.describe().strip().split("\n")}
-    ms, prog = time_program(timer, lambda a, b: configs.nx.dot(a, [1], b, [1]), [configs.dense_inputs()[0], configs.dense_inputs()[0]], device)
-    tf = 2 * 8192 ** 3 / ms / 1e9
-    res["dot_bf16_8192^3_kmajor"] = {"ms": round(ms, 4), "tflops": round(tf, 1), "frac_of_measured_bf16_peak": round(tf / pk["bf16_tflops"], 3)}
-    ms, prog = time_program(timer, configs.batched_dot, configs.batched_inputs(), device)
-    byt = (2 * 64 * 2048 * 128 + 64 * 2048 * 2048) * 2
-    res["batched_bf16_64x2048x128x2048"] = {"ms": round(ms, 4), "tflops": round(2 * 64 * 2048 * 2048 * 128 / ms / 1e9, 1),
-                                            "gbs": round(byt / ms / 1e6, 1), "frac_of_measured_hbm": round(byt / ms / 1e6 / pk["hbm_gbs"], 3)}
-    for m in (1, 16, 256, 4096):
-        f_in, i_in = configs.quantised_inputs(m=m)
-        ms, prog = time_program(timer, configs.quantised_linear, f_in, device)
-        byt = 11008 * 4096 + 11008 * 4 + m * 4096 * 2 + m * 11008 * 4
-        res[f"quantised_linear_M{m}"] = {"ms": round(ms, 4), "tflops": round(2 * m * 4096 * 11008 / ms / 1e9, 2), "gbs": round(byt / ms / 1e6, 1)}
-    # the integer-accumulate products (random s8 data): x {4096,4096} . W {11008,4096}^T with an s32 result, and s8 8192^3
-    nx_ = configs.nx
-    _, i_in = configs.quantised_inputs(m=4096)
-    ms, prog = time_program(timer, configs.integer_linear, i_in, device)
-    res["s8_dot_s32_4096x11008x4096"] = {"ms": round(ms, 4), "tops": round(2 * 4096 * 4096 * 11008 / ms / 1e9, 1), "plan": prog.describe().strip().split("\n")}
-    rng = np.random.default_rng(7)
-    sq = [(rng.integers(-127, 128, (8192, 8192)).astype(np.int8), "s8") for _ in range(2)]
-    ms, prog = time_program(timer, lambda x, w: nx_.dot(x, [1], w, [1]), sq, device)
-    res["s8_dot_s8_8192^3"] = {"ms": round(ms, 4), "tops": round(2 * 8192 ** 3 / ms / 1e9, 1)}
-    return res
 
 
 def main():
@@ -300,7 +496,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-decoder", action="store_true")
-    ap.add_argument("--all-configs", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="leave out the per-configuration measurements (N = 1)")
+    ap.add_argument("--all-configs", action="store_true", help="accepted for compatibility: the configurations are on by default")
     ap.add_argument("--profile-gemm", type=int, default=0, metavar="N",
                     help="run only an N^3 bf16 dense product with the fused bias+gelu epilogue (ncu captures of the tensor-core kernel)")
     ap.add_argument("--profile-batched", action="store_true",
@@ -436,25 +633,35 @@ def main():
     if not args.no_decoder and rows == ROWS:
         decoder = decoder_section(timer, local, rank, world, dist, torch)
 
+    if decoder is not None and world > 1:
+        bad = [k for k, v in decoder.get("parity", {}).items() if not v["ok"]]
+        if bad:
+            if rank == 0:
+                print("sharded decoder results differ from the single-GPU program: " + json.dumps({k: decoder["parity"][k] for k in bad}),
+                      file=sys.stderr)
+            dist.barrier()
+            dist.destroy_process_group()
+            raise SystemExit(3)
+
     if rank == 0:
         pk, which = peaks()
         peak = float(pk["hbm_gbs"])
         line = {"metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": WORKLOAD % rows, "seed": SEED,
-                           "parallelism": "replicas only" if world > 1 else "single GPU",
-                           "l2": "input (1 GiB) and outputs (3 GiB) per step exceed L2 (126 MB); no flush needed"},
+                "config": workload_config(rows, world),
                 "roofline": {"bound": "hbm", "achieved": round(per_gpu, 2), "peak": peak, "unit": "GB/s",
                              "frac": round(per_gpu / peak, 4),
-                             "traffic": int(NCU_TRAFFIC_BYTES_PER_1024_ROWS * rows / 1024),
+                             "traffic": row_kernel_traffic(rows, COLS),
+                             "traffic_source": "ncu capture of a 1024-row launch of this kernel: reads scaled by the rows, writes = "
+                                               "algorithmic output bytes less the 58.9 MB still dirty in L2 when the kernel ends",
                              "peak_source": f"of {which}", "kernel": "nxb_k0_row",
                              "algorithmic_bytes_per_launch": nbytes},
                 "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "plan": plan}
         if decoder is not None:
             line["decoder"] = decoder
-        if args.all_configs and world == 1:
-            line["configs"] = other_configs(timer, local, pk)
+        if not args.no_configs and world == 1 and rows == ROWS:
+            line["configs"] = other_configs(timer, local, pk, torch)
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(x_host)
         print(json.dumps(line))

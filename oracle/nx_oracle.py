@@ -406,7 +406,15 @@ def _dot(a, ta, c1, b1, b, tb, c2, b2, out_t, mode):
                 acc = np.matmul(Ac, Bc).astype(np.float32)
             r = _store(acc, out_t, mode)
         else:
-            acc = np.matmul(A.astype(np.int64), B.astype(np.int64))
+            # Exact integer sums.  When every partial sum is below 2^53 in magnitude the same
+            # integers come out of a float64 product (every term and every partial sum is then
+            # exactly representable), which runs through BLAS; otherwise int64 arithmetic.
+            amax = int(np.abs(A.astype(np.int64)).max(initial=0))
+            bmax = int(np.abs(B.astype(np.int64)).max(initial=0))
+            if k * amax * bmax < (1 << 53) and A.size * B.shape[-1] > (1 << 22):
+                acc = np.matmul(A.astype(np.float64), B.astype(np.float64)).astype(np.int64)
+            else:
+                acc = np.matmul(A.astype(np.int64), B.astype(np.int64))
             r = acc.astype(NP[out_t])          # wraps modulo 2^bits (shared.ex:190-194)
     return r.reshape(bs + m + n)
 

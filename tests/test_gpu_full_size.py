@@ -1,0 +1,204 @@
+"""The configurations at their stated sizes on the GPU, against the CPU oracles.
+
+Every launch here has the grid, the tile walk and the index widths of the
+benchmarked run, so an overflow or a bad edge in the full-size walk fails a
+test instead of only being timed.
+
+* fused rows f32 {8192,32768}: all seven outputs against the C restatement
+  (oracle/rows_oracle.c, pinned to the numpy oracle by tests/test_rows_oracle_cpu.py);
+  f32 within rtol 1e-5, argmax and the row maximum bit for bit.
+* dense bf16 8192^3 + bias + gelu and the batched {64,2048,128} x {64,128,2048}
+  product: sampled output rows (the first and last 128-row tile of every panel of
+  the tile walk, plus random rows; all columns) against the numpy oracle run on
+  exactly those rows of the left operand; bf16 tolerance rtol 2e-2 / atol 1e-2.
+* quantised linear {M,4096} . {11008,4096}^T for M in 1, 16, 256 (whole result) and
+  4096 (sampled rows), f32 within rtol 1e-5 of the result's scale; the integer
+  path (s8 widened to s32) bit for bit.
+* decoder block bf16 {8,2048,4096}: one whole sequence (one batch element, the
+  block is independent along the batch axis) against the numpy oracle.
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import nx_oracle as O
+from helpers import assert_close
+from nx_b200 import backend, configs, defn, nx
+
+pytestmark = pytest.mark.gpu
+BF16 = dict(rtol=2e-2, atol=1e-2)
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _device():
+    backend.set_default_backend("b200", 0)
+    yield
+    backend.set_default_backend(None)
+
+
+def host(a, t):
+    prev = backend.default_backend()
+    backend.set_default_backend(None)
+    try:
+        return nx.tensor(a, t)
+    finally:
+        backend.set_default_backend(*prev) if prev else None
+
+
+def on_device(fun, inputs):
+    """Runs `fun` on the device; returns the outputs as arrays and frees the device memory."""
+    dev = [nx.tensor(a, t) for a, t in inputs]
+    out = defn.jit(fun)(*dev)
+    outs = list(out) if isinstance(out, (tuple, list)) else [out]
+    res = [nx.to_numpy(o) for o in outs]
+    for t in dev + outs:
+        backend.backend_deallocate(t)
+    return res
+
+
+def oracle(fun, inputs, mode="xla_like"):
+    h = [host(a, t) for a, t in inputs]
+    blob, _ = defn.build_program(fun, h)
+    return [r[0] for r in O.run_program(blob, [x.data.raw for x in h], mode)]
+
+
+def panel_rows(m, tile=128, panel_tiles=16, extra=64, seed=0):
+    """Rows in the first and last tile of every panel of `panel_tiles` row tiles, and random ones."""
+    rows = set()
+    panel = tile * panel_tiles
+    for p0 in range(0, m, panel):
+        p1 = min(m, p0 + panel)
+        rows.update(range(p0, min(p0 + 32, m)))
+        rows.update(range(max(p1 - 32, 0), p1))
+    rng = np.random.default_rng(seed)
+    rows.update(int(r) for r in rng.integers(0, m, extra))
+    return np.array(sorted(rows))
+
+
+# ---- fused rows ---------------------------------------------------------------------------
+
+def _rows_oracle(x):
+    path = os.path.join(ROOT, "oracle", "librows_oracle.so")
+    if not os.path.exists(path):
+        subprocess.run(["make", "-s", "-C", os.path.join(ROOT, "oracle")], check=True)
+    lib = C.CDLL(path)
+    lib.rows_oracle.restype = None
+    lib.rows_oracle.argtypes = [C.c_void_p, C.c_int64, C.c_int64] + [C.c_void_p] * 7
+    lib.rows_oracle_set_threads(len(os.sched_getaffinity(0)))
+    r, c = x.shape
+    outs = [np.empty(r, np.float32), np.empty((r, c), np.float32), np.empty(r, np.float32), np.empty(r, np.float32),
+            np.empty((r, c), np.float32), np.empty(r, np.int32), np.empty((r, c), np.float32)]
+    lib.rows_oracle(x.ctypes.data, r, c, *[o.ctypes.data for o in outs])
+    return outs
+
+
+def _close_f32(got, want, rtol, atol, what, chunk=1 << 24):
+    g, w = got.reshape(-1), want.reshape(-1)
+    for i in range(0, g.size, chunk):
+        gi, wi = g[i:i + chunk], w[i:i + chunk]
+        bad = ~(np.abs(gi - wi) <= atol + rtol * np.abs(wi))
+        if bad.any():
+            j = i + int(np.argmax(bad))
+            raise AssertionError(f"{what}: {int(bad.sum())} values of this chunk outside rtol={rtol} atol={atol}; "
+                                 f"first at flat {j}: got {g[j]!r} want {w[j]!r}")
+
+
+def test_fused_rows_at_full_size():
+    x = configs.fused_rows_input(8192, 32768, seed=1)
+    xt = nx.tensor(x)
+    outs = defn.jit(configs.fused_rows)(xt)
+    want = _rows_oracle(x)
+    names = ["max", "exp", "sum", "logsumexp", "softmax", "argmax", "chain"]
+    for n, o, w in zip(names, outs, want):
+        g = nx.to_numpy(o)
+        backend.backend_deallocate(o)
+        assert g.shape == w.shape, n
+        if n in ("argmax", "max"):
+            assert np.array_equal(g, w), f"{n}: {int((g != w).sum())} rows differ"
+        else:
+            # the floor covers exp/softmax values far below the row's scale (products of rounded factors)
+            _close_f32(g, w, 1e-5, 1e-9 if n in ("exp", "softmax") else 1e-6, n)
+        del g
+    backend.backend_deallocate(xt)
+
+
+# ---- dense products -----------------------------------------------------------------------------
+
+def test_dense_bias_gelu_at_full_size():
+    (a, ta), (b, tb), (bias, tbias) = configs.dense_inputs()
+    got, = on_device(configs.dense_bias_gelu, [(a, ta), (b, tb), (bias, tbias)])
+    assert got.shape == (8192, 8192)
+    rows = panel_rows(8192)
+    assert len(rows) >= 256
+    want, = oracle(configs.dense_bias_gelu, [(a[rows], ta), (b, tb), (bias, tbias)])
+    assert_close(got[rows], want, what="dense 8192^3 + bias + gelu, sampled rows", **BF16)
+    assert np.isfinite(got).all()
+
+
+def test_dense_k_major_right_operand_at_full_size():
+    """{8192,8192} . {8192,8192}^T (both operands with the contracted index contiguous)."""
+    (a, ta), (b, tb), _ = configs.dense_inputs()
+    fun = lambda x, w: nx.dot(x, [1], w, [1])
+    got, = on_device(fun, [(a, ta), (b, tb)])
+    rows = panel_rows(8192, seed=1)
+    want, = oracle(fun, [(a[rows], ta), (b, tb)])
+    assert_close(got[rows], want, what="dense 8192^3 K-major, sampled rows", **BF16)
+
+
+def test_batched_dot_at_full_size():
+    (a, ta), (b, tb) = configs.batched_inputs()
+    got, = on_device(configs.batched_dot, [(a, ta), (b, tb)])
+    assert got.shape == (64, 2048, 2048)
+    rows = panel_rows(2048, extra=16)          # one panel per batch entry: its first and last tile
+    want, = oracle(configs.batched_dot, [(np.ascontiguousarray(a[:, rows]), ta), (b, tb)])
+    assert_close(got[:, rows], want, what="batched {64,2048,128}x{64,128,2048}, sampled rows", **BF16)
+
+
+# ---- quantised linear ----------------------------------------------------------------------------
+
+@pytest.mark.parametrize("m", [1, 16, 256, 4096])
+def test_quantised_linear_at_full_size(m):
+    f_in, i_in = configs.quantised_inputs(m=m)
+    got, = on_device(configs.quantised_linear, f_in)
+    assert got.shape == (m, 11008) and got.dtype == np.float32
+    rows = np.arange(m) if m <= 256 else panel_rows(m)
+    (x, tx), w, s = f_in
+    want, = oracle(configs.quantised_linear, [(x[rows], tx), w, s])
+    assert_close(got[rows], want, rtol=1e-5, atol=1e-5 * float(np.abs(want).max()), what=f"quantised linear M={m}")
+    # the integer-accumulate path: s8 x s8 widened to s32, bit for bit
+    goti, = on_device(configs.integer_linear, i_in)
+    (xq, tq), wq = i_in
+    wanti, = oracle(configs.integer_linear, [(xq[rows], tq), wq])
+    assert goti.dtype == np.int32 and np.array_equal(goti[rows], wanti), f"integer linear M={m}"
+
+
+def test_s8_square_product_wraps_like_the_reference():
+    """s8 {8192,8192} . s8 {8192,8192}^T -> s8: the 32-bit sums written modulo 2^8 (nx/lib/nx/shared.ex:190-194)."""
+    rng = np.random.default_rng(7)
+    a = rng.integers(-127, 128, (8192, 8192)).astype(np.int8)
+    b = rng.integers(-127, 128, (8192, 8192)).astype(np.int8)
+    fun = lambda x, w: nx.dot(x, [1], w, [1])
+    got, = on_device(fun, [(a, "s8"), (b, "s8")])
+    rows = panel_rows(8192, seed=2)
+    want, = oracle(fun, [(a[rows], "s8"), (b, "s8")])
+    assert got.dtype == np.int8 and np.array_equal(got[rows], want)
+
+
+# ---- decoder block ----------------------------------------------------------------------------------
+
+def test_decoder_block_at_full_size():
+    block = configs.make_decoder_block()
+    inputs = configs.decoder_inputs()
+    got, = on_device(block, inputs)
+    assert got.shape == (8, 2048, 4096) and np.isfinite(got).all()
+    e = 5                                      # one whole sequence
+    (x, tx), weights = inputs[0], inputs[1:]
+    want, = oracle(block, [(x[e:e + 1], tx)] + weights)
+    assert_close(got[e:e + 1], want, what="decoder block {8,2048,4096}, batch element 5", **BF16)
+    # another batch element run alone (a different grid and tile walk) agrees with its slice of the full run
+    alone, = on_device(block, [(x[2:3], tx)] + weights)
+    assert_close(alone, got[2:3], what="batch element 2 run alone against its slice of the full run", **BF16)
