@@ -230,8 +230,10 @@ def time_program(timer, fun, inputs, device, steps=10):
 
 class StreamTimer:
     """Per-launch device times with an L2 flush before every launch: events of the library's compute
-    stream (wrapped as a torch stream) bracket the launch alone, the flush (a write of a buffer twice
-    the size of L2) sits outside them."""
+    stream (wrapped as a torch stream) bracket the launch alone, the flush sits outside them.  The
+    flush READS a buffer twice the size of L2: the cache is then full of clean lines, as it is when
+    other layers' weights have streamed through it.  (A flush by writes leaves 126 MB of dirty lines
+    whose write-back competes with the timed kernel's reads.)"""
 
     def __init__(self, lib, device, torch):
         from nx_b200 import nif
@@ -239,14 +241,14 @@ class StreamTimer:
         nif.check(lib.nxb200_device_stream(device, C.byref(h)))
         self.torch, self.lib, self.device = torch, lib, device
         self.stream = torch.cuda.ExternalStream(h.value, device=device)
-        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=f"cuda:{device}")
+        self.flush = torch.zeros(64 << 20, dtype=torch.int32, device=f"cuda:{device}")
 
     def flushed(self, fn, iters=30):
         torch = self.torch
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
         with torch.cuda.stream(self.stream):
             for a, b in evs:
-                self.flush.zero_()
+                self.flush.sum()
                 a.record(self.stream)
                 fn()
                 b.record(self.stream)

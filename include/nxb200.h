@@ -160,6 +160,11 @@ size_t nxb200_program_describe(nxb200_program *prog, char *dst, size_t cap);
 /* Generated CUDA source of the i-th fused kernel (diagnostics; 0 when i is out
  * of range).  Returns the number of bytes needed. */
 size_t nxb200_program_kernel_source(nxb200_program *prog, int i, char *dst, size_t cap);
+/* Where the build time went, in seconds: planning (parse, fusion, code generation) and
+ * compilation of the generated sources (NVRTC).  The reference reports the same split in its
+ * [:exla, :compilation] telemetry event (eval_time / compile_time / total_time,
+ * exla/lib/exla/defn.ex:515-523). */
+int nxb200_program_build_times(nxb200_program *prog, double *plan_seconds, double *codegen_seconds);
 /* Number of kernels one run launches. */
 int nxb200_program_launch_count(nxb200_program *prog, int *count);
 
@@ -193,6 +198,12 @@ int nxb200_device_synchronize(int device);
  * device's stream (CUDA events).  end returns elapsed milliseconds. */
 int nxb200_timer_begin(int device);
 int nxb200_timer_end(int device, float *ms);
+/* Self-test of the failure path every kernel shares: one thread waits, with the same bounded
+ * wait the fused kernels use on flags their peers set, for a flag that nothing sets.  After
+ * `limit_us` microseconds the wait gives up, the kernel returns normally and reports through the
+ * device's status word; the call then answers NXB_ERR_TIMEOUT (anything else means the failure path
+ * is broken).  The device stays usable.  No counterpart in the reference. */
+int nxb200_selftest_bounded_wait(int device, uint32_t limit_us);
 /* The device's compute stream as a cudaStream_t, for callers that interleave
  * their own work (e.g. an L2 flush in a benchmark). */
 int nxb200_device_stream(int device, void **stream);

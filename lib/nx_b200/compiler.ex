@@ -1,0 +1,347 @@
+defmodule NxB200 do
+  @moduledoc """
+  `Nx.Defn.Compiler` for B200 GPUs over `libnxb200.so`.
+
+      config :nx, default_backend: NxB200.Backend
+      config :nx, :default_defn_options, compiler: NxB200
+
+  Callback contract: `nx/lib/nx/defn/compiler.ex:29-101`; behaviour modelled on `EXLA.Defn`
+  (`exla/lib/exla/defn.ex:15-72,151-191`): the traced expression is walked once per cache key,
+  memoised by node id (`defn.ex:659-668`), and turned into the byte string
+  `nxb200_program_build` consumes (layout in `include/nxb200.h`); every later call resolves the
+  argument thunks to device buffers, runs the program and wraps the result buffers in the output
+  templates.  Results are always fresh tensors on `NxB200.Backend` (`defn.ex:387-393`).
+
+  Not lowered into one program: `:while`, `:cond` with tensor-valued branches that need control
+  flow, `:fun`, `:runtime_call` — the expression is cut at those nodes and the pieces are run from
+  the host, as `nx_b200/defn.py` does in the tested stand-in.  Anything else the device cannot run
+  raises `ArgumentError` naming the operation; there is no CPU fallback.
+
+  Not compiled in this repository's build (no Elixir in the image).
+  """
+  @behaviour Nx.Defn.Compiler
+
+  alias Nx.Defn.{Composite, Expr}
+  alias Nx.Tensor, as: T
+  alias NxB200.NIF
+
+  @cache :nx_b200_programs
+
+  ## public conveniences (EXLA.jit/2, EXLA.jit_apply/3: exla/lib/exla.ex)
+
+  def jit(fun, opts \\ []), do: Nx.Defn.jit(fun, Keyword.put(opts, :compiler, __MODULE__))
+  def jit_apply(fun, args, opts \\ []), do: Nx.Defn.jit_apply(fun, args, Keyword.put(opts, :compiler, __MODULE__))
+
+  ## Nx.Defn.Compiler callbacks
+
+  @impl true
+  def __partitions_options__(opts) do
+    for device <- 0..(NIF.device_count() - 1)//1, do: Keyword.put(opts, :device, device)
+  end
+
+  @impl true
+  def __to_backend__(opts), do: {NxB200.Backend, [device: opts[:device] || 0]}
+
+  @impl true
+  def __jit__(key, vars, fun, args_list, opts), do: __compile__(key, vars, fun, opts).(args_list)
+
+  @impl true
+  def __compile__(key, vars, fun, opts) do
+    device = opts[:device] || 0
+    # the donation marks are part of the key: a donating call must not reuse the
+    # non-donating executable (exla/lib/exla/defn.ex:337-353)
+    args_key = for %T{} = v <- vars, do: {v.type, v.shape, v.names, v.vectorized_axes, v.donatable?}
+
+    {program, outputs} =
+      cached({key, args_key, Keyword.drop(opts, [:device])}, fn ->
+        t0 = System.monotonic_time()
+        expr = fun.(vars)
+        t1 = System.monotonic_time()
+        outputs = Composite.flatten_list([expr])
+        program = NIF.program_build(serialize(outputs, vars))
+        t2 = System.monotonic_time()
+
+        :telemetry.execute(
+          [:nx_b200, :compilation],
+          %{eval_time: t1 - t0, compile_time: t2 - t1, total_time: t2 - t0},
+          %{key: key}
+        )
+
+        {program, expr}
+      end)
+
+    fn args_list ->
+      for args <- args_list do
+        buffers =
+          for thunk <- args do
+            case thunk.() do
+              %T{data: %NxB200.Backend{ref: ref, device: ^device}} -> ref
+              %T{data: %NxB200.Backend{}} = t -> Nx.backend_copy(t, {NxB200.Backend, device: device}).data.ref
+              %T{data: %Nx.BinaryBackend{}} = t -> Nx.backend_copy(t, {NxB200.Backend, device: device}).data.ref
+              %T{data: %other{}} -> raise ArgumentError, "cannot run on NxB200 a tensor allocated on #{inspect(other)}"
+            end
+          end
+
+        refs = NIF.program_run(program, device, buffers)
+
+        {result, []} =
+          Composite.traverse(outputs, refs, fn %T{} = template, [ref | rest] ->
+            {%{Nx.to_template(template) | data: %NxB200.Backend{ref: ref, device: device}}, rest}
+          end)
+
+        result
+      end
+    end
+  end
+
+  ## program cache: one build per key, concurrent callers of the same key wait for it
+  ## (the role of EXLA.Defn.LockedCache, exla/lib/exla/defn/locked_cache.ex:35-59)
+
+  defp cached(key, fun) do
+    table = ensure_table()
+
+    case :ets.lookup(table, key) do
+      [{^key, value}] ->
+        value
+
+      [] ->
+        :global.trans({{__MODULE__, key}, self()}, fn ->
+          case :ets.lookup(table, key) do
+            [{^key, value}] ->
+              value
+
+            [] ->
+              value = fun.()
+              :ets.insert(table, {key, value})
+              value
+          end
+        end, [node()])
+    end
+  end
+
+  defp ensure_table do
+    case :ets.whereis(@cache) do
+      :undefined ->
+        try do
+          :ets.new(@cache, [:named_table, :public, :set, read_concurrency: true])
+        rescue
+          ArgumentError -> @cache
+        end
+
+      _ ->
+        @cache
+    end
+  end
+
+  ## Expr -> program bytes
+
+  @doc false
+  def serialize(outputs, vars) do
+    # parameters first, in argument order, so that the program keeps the function's arity
+    state = %{nodes: [], index: %{}, count: 0}
+
+    state =
+      vars
+      |> Composite.flatten_list()
+      |> Enum.with_index()
+      |> Enum.reduce(state, fn {%T{} = v, i}, st ->
+        {_, st} = emit(st, {:parameter, i}, "parameter", v, [], [i], [], <<>>)
+        st
+      end)
+
+    {out_indices, state} = Enum.map_reduce(outputs, state, &visit/2)
+    donated = donation_pairs(vars, outputs)
+
+    [
+      "NXB1",
+      <<state.count::little-32>>,
+      Enum.reverse(state.nodes),
+      <<length(out_indices)::little-32>>,
+      for(i <- out_indices, do: <<i::little-32>>),
+      if(donated == [], do: [], else: [<<length(donated)::little-32>>, for({p, o} <- donated, do: <<p::little-32, o::little-32>>)])
+    ]
+  end
+
+  # pairs each donated argument with the first unused output of its type and shape
+  # (exla/lib/exla/defn.ex:598-645)
+  defp donation_pairs(vars, outputs) do
+    outs = Enum.with_index(outputs)
+
+    {pairs, _used} =
+      vars
+      |> Composite.flatten_list()
+      |> Enum.with_index()
+      |> Enum.filter(fn {v, _} -> v.donatable? end)
+      |> Enum.map_reduce(MapSet.new(), fn {v, p}, used ->
+        case Enum.find(outs, fn {o, i} -> not MapSet.member?(used, i) and o.type == v.type and o.shape == v.shape end) do
+          {_, i} ->
+            {{p, i}, MapSet.put(used, i)}
+
+          nil ->
+            raise ArgumentError,
+                  "a tensor of type #{inspect(v.type)} and shape #{inspect(v.shape)} was marked as donatable " <>
+                    "but no output with the same type and shape is available to take over its buffer"
+        end
+      end)
+
+    pairs
+  end
+
+  defp visit(%T{data: %Expr{id: id}} = t, state) do
+    case state.index do
+      %{^id => i} -> {i, state}
+      %{} -> lower(Nx.devectorize(t), state)
+    end
+  end
+
+  defp emit(state, id, op, %T{type: type, shape: shape}, args, ints, flts, blob) do
+    dims = Tuple.to_list(shape)
+
+    node = [
+      <<byte_size(op)::8>>, op,
+      <<NIF.type_code(type)::8, length(dims)::8>>, for(d <- dims, do: <<d::little-signed-64>>),
+      <<length(args)::little-16>>, for(a <- args, do: <<a::little-32>>),
+      <<length(ints)::little-16>>, for(i <- ints, do: <<i::little-signed-64>>),
+      <<length(flts)::little-16>>, for(f <- flts, do: encode_float(f)),
+      <<byte_size(blob)::little-64>>, blob
+    ]
+
+    i = state.count
+    {i, %{state | nodes: [node | state.nodes], index: Map.put(state.index, id, i), count: i + 1}}
+  end
+
+  defp encode_float(:nan), do: <<0x7FF8000000000000::little-64>>
+  defp encode_float(:infinity), do: <<0x7FF0000000000000::little-64>>
+  defp encode_float(:neg_infinity), do: <<0xFFF0000000000000::little-64>>
+  defp encode_float(f), do: <<f * 1.0::little-float-64>>
+
+  defp args(tensors, state), do: Enum.map_reduce(tensors, state, &visit/2)
+
+  defp simple(%T{data: %Expr{id: id, op: op}} = t, tensors, ints, state) do
+    {idx, state} = args(tensors, state)
+    emit(state, id, Atom.to_string(op), t, idx, ints, [], <<>>)
+  end
+
+  @elementwise [:exp, :expm1, :log, :log1p, :sigmoid, :cos, :sin, :tan, :cosh, :sinh, :tanh, :acos, :asin, :atan,
+                :acosh, :asinh, :atanh, :sqrt, :rsqrt, :cbrt, :erf, :erfc, :erf_inv, :abs, :bitwise_not, :ceil, :floor,
+                :negate, :round, :sign, :count_leading_zeros, :population_count, :is_nan, :is_infinity, :as_type,
+                :add, :subtract, :multiply, :divide, :pow, :remainder, :atan2, :min, :max, :quotient, :bitwise_and,
+                :bitwise_or, :bitwise_xor, :left_shift, :right_shift, :equal, :not_equal, :greater, :less,
+                :greater_equal, :less_equal, :logical_and, :logical_or, :logical_xor, :select, :clip, :reshape]
+
+  defp lower(%T{data: %Expr{id: id, op: :parameter, args: [i]}}, state) do
+    # written up front by serialize/2
+    {Map.fetch!(state.index, {:parameter, i}), %{state | index: Map.put(state.index, id, Map.fetch!(state.index, {:parameter, i}))}}
+  end
+
+  defp lower(%T{data: %Expr{id: id, op: :constant, args: [number]}, type: type} = t, state) do
+    if Nx.Type.float?(type),
+      do: emit(state, id, "constant", t, [], [], [number], <<>>),
+      else: emit(state, id, "constant", t, [], [number], [], <<>>)
+  end
+
+  defp lower(%T{data: %Expr{id: id, op: :tensor, args: [literal]}} = t, state) do
+    emit(state, id, "tensor", t, [], [], [], Nx.to_binary(literal))
+  end
+
+  defp lower(%T{data: %Expr{id: id, op: :metadata, args: [inner, _meta]}} = t, state) do
+    {[i], state} = args([inner], state)
+    emit(state, id, "metadata", t, [i], [], [], <<>>)
+  end
+
+  defp lower(%T{data: %Expr{op: op, args: tensors}} = t, state) when op in @elementwise do
+    simple(t, tensors, [], state)
+  end
+
+  defp lower(%T{data: %Expr{op: op, args: [x, opts]}} = t, state)
+       when op in [:sum, :product, :reduce_max, :reduce_min, :all, :any] do
+    axes = opts[:axes] || Nx.axes(x)
+    simple(t, [x], [bool(opts[:keep_axes]), length(axes) | axes], state)
+  end
+
+  defp lower(%T{data: %Expr{op: op, args: [x, opts]}} = t, state) when op in [:argmax, :argmin] do
+    simple(t, [x], [bool(opts[:tie_break] == :high), opts[:axis] || -1, bool(opts[:keep_axis])], state)
+  end
+
+  defp lower(%T{data: %Expr{op: :dot, args: [a, c1, b1, b, c2, b2]}} = t, state) do
+    simple(t, [a, b], Enum.flat_map([c1, b1, c2, b2], &[length(&1) | &1]), state)
+  end
+
+  defp lower(%T{data: %Expr{op: :squeeze, args: [x, axes]}} = t, state), do: simple(t, [x], [length(axes) | axes], state)
+  defp lower(%T{data: %Expr{op: :broadcast, args: [x, _shape, axes]}} = t, state), do: simple(t, [x], [length(axes) | axes], state)
+  defp lower(%T{data: %Expr{op: :transpose, args: [x, perm]}} = t, state), do: simple(t, [x], perm, state)
+  defp lower(%T{data: %Expr{op: :reverse, args: [x, axes]}} = t, state), do: simple(t, [x], axes, state)
+  defp lower(%T{data: %Expr{op: :iota, args: [axis]}} = t, state), do: simple(t, [], [axis || -1], state)
+
+  defp lower(%T{data: %Expr{op: op, args: [tensors, axis]}} = t, state) when op in [:concatenate, :stack] do
+    simple(t, tensors, [axis], state)
+  end
+
+  defp lower(%T{data: %Expr{op: :slice, args: [x, starts, lengths, strides]}} = t, state) do
+    if Enum.all?(starts, &is_integer/1) do
+      simple(t, [x], starts ++ lengths ++ strides, state)
+    else
+      # dynamic starts: one scalar tensor per axis follows the operand, the attribute is ignored
+      scalars = for s <- starts, do: if(is_integer(s), do: Expr.constant(Nx.template({}, {:s, 32}), s, []), else: s)
+      simple(t, [x | scalars], List.duplicate(0, length(starts)) ++ lengths ++ strides, state)
+    end
+  end
+
+  defp lower(%T{data: %Expr{op: :put_slice, args: [x, starts, slice]}} = t, state) do
+    scalars = for s <- starts, do: if(is_integer(s), do: Expr.constant(Nx.template({}, {:s, 32}), s, []), else: s)
+    simple(t, [x, slice | scalars], [], state)
+  end
+
+  defp lower(%T{data: %Expr{op: :pad, args: [x, value, config]}} = t, state) do
+    {lo, hi, interior} = config |> Enum.map(&Tuple.to_list/1) |> Enum.zip() |> Enum.map(&Tuple.to_list/1) |> List.to_tuple()
+    simple(t, [x, value], lo ++ hi ++ interior, state)
+  end
+
+  defp lower(%T{data: %Expr{op: :gather, args: [x, indices, opts]}} = t, state), do: simple(t, [x, indices], opts[:axes], state)
+
+  defp lower(%T{data: %Expr{op: op, args: [x, indices, updates, opts]}} = t, state) when op in [:indexed_add, :indexed_put] do
+    simple(t, [x, indices, updates], opts[:axes], state)
+  end
+
+  defp lower(%T{data: %Expr{op: op, args: [x, window, opts]}} = t, state)
+       when op in [:window_sum, :window_max, :window_min, :window_product] do
+    rank = tuple_size(window)
+    {lo, hi} = opts[:padding] |> Enum.unzip()
+    dil = List.wrap(opts[:window_dilations] || List.duplicate(1, rank))
+    simple(t, [x], Tuple.to_list(window) ++ opts[:strides] ++ lo ++ hi ++ dil, state)
+  end
+
+  defp lower(%T{data: %Expr{op: :sort, args: [x, opts]}} = t, state) do
+    last_axis!(x, opts[:axis])
+    simple(t, [x], [bool(opts[:direction] == :desc)], state)
+  end
+
+  defp lower(%T{data: %Expr{op: :argsort, args: [x, opts]}} = t, state) do
+    last_axis!(x, opts[:axis])
+    simple(t, [x], [bool(opts[:direction] == :desc), bool(opts[:stable])], state)
+  end
+
+  defp lower(%T{data: %Expr{op: :elem, args: [tuple, i]}}, state) do
+    # multi-output nodes do not exist on the device: project at trace level
+    visit(elem(tuple_of(tuple), i), state)
+  end
+
+  defp lower(%T{data: %Expr{op: op}}, _state) do
+    raise ArgumentError,
+          "NxB200 cannot compile the operation :#{op} (there is no CPU fallback; run it on another backend " <>
+            "or outside of the compiled function)"
+  end
+
+  defp tuple_of(%T{data: %Expr{op: :metadata, args: [inner, _]}}), do: tuple_of(inner)
+  defp tuple_of(tuple) when is_tuple(tuple), do: tuple
+  defp tuple_of(%T{data: %Expr{op: op}}), do: raise(ArgumentError, "NxB200 cannot compile the operation :#{op}")
+
+  defp last_axis!(x, axis) do
+    unless axis == Nx.rank(x) - 1 do
+      raise ArgumentError, "NxB200 sorts along the last axis only; transpose the tensor first (got axis #{axis})"
+    end
+  end
+
+  defp bool(true), do: 1
+  defp bool(_), do: 0
+end

@@ -726,6 +726,14 @@ size_t nxb200_program_kernel_source(nxb200_program* prog, int i, char* dst, size
   return s.size();
 }
 
+int nxb200_program_build_times(nxb200_program* prog, double* plan_seconds, double* codegen_seconds) {
+  return guarded([&] {
+    nxb200_program* p = check_program(prog);
+    if (plan_seconds) *plan_seconds = p->plan->plan_seconds;
+    if (codegen_seconds) *codegen_seconds = p->plan->codegen_seconds;
+  });
+}
+
 int nxb200_program_launch_count(nxb200_program* prog, int* count) {
   return guarded([&] {
     nxb200_program* p = check_program(prog);
@@ -762,6 +770,37 @@ int nxb200_timer_end(int dev, float* ms) {
     float t = 0;
     NXB_CUDA(cudaEventElapsedTime(&t, d.ev0, d.ev1));
     if (ms) *ms = t;
+  });
+}
+
+int nxb200_selftest_bounded_wait(int dev, uint32_t limit_us) {
+  return guarded([&] {
+    Device& d = nxb::device(dev);
+    if (limit_us == 0 || limit_us > 2000000) fail(NXB_ERR_INVALID_ARGUMENT, "limit must be between 1 microsecond and 2 seconds");
+    uint32_t* flag = nullptr;
+    {
+      std::lock_guard<std::mutex> g(d.mu);
+      flag = (uint32_t*)d.alloc.alloc(sizeof(uint32_t));
+    }
+    cudaError_t e = cudaMemsetAsync(flag, 0, sizeof(uint32_t), d.stream);
+    int khz = 1965000;
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev);
+    if (e == cudaSuccess) {
+      try {
+        launch_wait_probe(flag, (long long)limit_us * (long long)khz / 1000, d.status_dev, d.stream);
+      } catch (...) {
+        std::lock_guard<std::mutex> g(d.mu);
+        d.alloc.free(flag);
+        throw;
+      }
+      e = cudaStreamSynchronize(d.stream);
+    }
+    {
+      std::lock_guard<std::mutex> g(d.mu);
+      d.alloc.free(flag);
+    }
+    NXB_CUDA(e);
+    check_device_status(d);      // the wait gave up: NXB_ERR_TIMEOUT
   });
 }
 

@@ -89,12 +89,14 @@ class Allocator {
   void* alloc(size_t nbytes);
   void free(void* p);
   void release_cached();
+  // `allocated` / `peak` count the bytes callers asked for (what the reference's counters report,
+  // exla/test/exla/memory_tracking_test.exs); `reserved` counts what was taken from the device
   uint64_t allocated = 0, peak = 0, reserved = 0;
 
  private:
   static size_t round_size(size_t n);
   std::multimap<size_t, void*> cache_;
-  std::map<void*, size_t> live_;
+  std::map<void*, std::pair<size_t, size_t>> live_;   // block -> (size class, bytes asked for)
 };
 
 struct Device {

@@ -17,6 +17,7 @@
 //
 // All shapes are compile-time constants of the generated source (programs are
 // specialised per argument signature, as in the reference).
+#include <chrono>
 #include <algorithm>
 #include <cstdio>
 #include <cstdlib>
@@ -1579,6 +1580,7 @@ int tc_smem_bytes(int bn);
 int tc_block_threads(int64_t k);
 
 std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
+  const auto t_start = std::chrono::steady_clock::now();
   auto plan = std::make_unique<Plan>();
   plan->g = parse_graph(bytes, nbytes);
   Graph& g = plan->g;
@@ -2370,7 +2372,11 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     pl.aliases.push_back(a);
   }
 
+  const auto t_planned = std::chrono::steady_clock::now();
   for (auto& ks : plan->kernels) ks.cubin = compile_to_cubin(ks.source, ks.name, ks.tensor_core, ks.attention);
+  const auto t_done = std::chrono::steady_clock::now();
+  plan->plan_seconds = std::chrono::duration<double>(t_planned - t_start).count();
+  plan->codegen_seconds = std::chrono::duration<double>(t_done - t_planned).count();
   return plan;
 }
 

@@ -346,6 +346,21 @@ void attn_prepare_launch(const void* q, const void* k, const void* v, void* out,
   outl->smem = attn_smem_bytes();
 }
 
+// One thread waits, with the bounded wait the fused kernels use on their peers' flags, for a flag
+// that nothing sets; when the limit passes the wait returns false and the kernel reports it the way
+// every kernel does: through the device's status word.
+__global__ void wait_probe_kernel(const uint32_t* flag, uint32_t epoch, long long limit_cycles, int* status) {
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) abort_word = 0;
+  __syncthreads();
+  if (threadIdx.x == 0 && !nxb_gemm::flag_wait(flag, epoch, &abort_word, limit_cycles)) *(volatile int*)status = 1;
+}
+
+void launch_wait_probe(const uint32_t* flag, long long limit_cycles, int* status_word, cudaStream_t stream) {
+  wait_probe_kernel<<<1, 32, 0, stream>>>(flag, 1u, limit_cycles, status_word);
+  NXB_CUDA(cudaGetLastError());
+}
+
 const char* gemm_device_source() {
   static const char* src =
 #include "gemm_device_embed.inc"

@@ -137,7 +137,8 @@ __device__ __forceinline__ uint4 ld_sys_v4(const void* p) {
   return v;
 }
 // Bounded wait until a flag (possibly in a peer's memory) has reached `epoch`.
-__device__ __forceinline__ bool flag_wait(const uint32_t* f, uint32_t epoch, volatile int* abort_flag) {
+__device__ __forceinline__ bool flag_wait(const uint32_t* f, uint32_t epoch, volatile int* abort_flag,
+                                          long long limit_cycles = 15 * WAIT_LIMIT_CYCLES) {
   const long long t0 = now_cycles();
   for (;;) {
     for (int i = 0; i < 16; ++i) {
@@ -145,8 +146,8 @@ __device__ __forceinline__ bool flag_wait(const uint32_t* f, uint32_t epoch, vol
       __nanosleep(200);
     }
     if (*abort_flag) return false;
-    // ranks may reach the kernel seconds apart (host-side skew): about half a minute
-    if (now_cycles() - t0 > 15 * WAIT_LIMIT_CYCLES) {
+    // ranks may reach the kernel seconds apart (host-side skew): by default about half a minute
+    if (now_cycles() - t0 > limit_cycles) {
       *abort_flag = 1;
       return false;
     }

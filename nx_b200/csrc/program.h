@@ -137,6 +137,8 @@ struct Plan {
   // argument's data, so a result that does not share the argument's memory is first copied from it.
   struct Alias { int param, output; bool in_place; bool window = false; };
   std::vector<Alias> aliases;
+  // seconds spent building: parsing + planning + code generation, and NVRTC (source -> cubin)
+  double plan_seconds = 0, codegen_seconds = 0;
   std::string describe() const;
 };
 

@@ -103,8 +103,8 @@ void* Allocator::alloc(size_t nbytes) {
     }
     reserved += sz;
   }
-  live_[p] = sz;
-  allocated += sz;
+  live_[p] = {sz, nbytes};
+  allocated += nbytes;
   if (allocated > peak) peak = allocated;
   return p;
 }
@@ -112,8 +112,8 @@ void* Allocator::alloc(size_t nbytes) {
 void Allocator::free(void* p) {
   auto it = live_.find(p);
   if (it == live_.end()) return;
-  allocated -= it->second;
-  cache_.emplace(it->second, p);
+  allocated -= it->second.second;
+  cache_.emplace(it->second.first, p);
   live_.erase(it);
 }
 

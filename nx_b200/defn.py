@@ -20,6 +20,7 @@ from __future__ import annotations
 
 import ctypes as C
 import threading
+import time
 
 from . import backend as B
 from . import expr as E
@@ -75,6 +76,12 @@ class Program:
             l.nxb200_program_kernel_source(self.handle, i, buf, n + 1)
             out.append(buf.value.decode())
             i += 1
+
+    def build_times(self):
+        """Seconds spent planning (parse, fusion, code generation) and compiling the generated sources."""
+        a, b = C.c_double(), C.c_double()
+        nif.check(nif.lib().nxb200_program_build_times(self.handle, C.byref(a), C.byref(b)))
+        return {"plan_time": a.value, "codegen_time": b.value}
 
     def launch_count(self):
         n = C.c_int()
@@ -133,6 +140,35 @@ def _unflatten(spec, it):
 _cache = {}
 _cache_lock = threading.Lock()
 
+# ---- compile telemetry -----------------------------------------------------------------
+# The reference emits ``[:exla, :compilation]`` once per cache miss with ``eval_time`` (tracing the
+# function into an expression), ``compile_time`` (lowering + compiling) and ``total_time``
+# (exla/lib/exla/defn.ex:515-523).  Handlers attached here get the same three measurements, in
+# seconds, under the event name ``("b200", "compilation")``, plus ``plan_time`` / ``codegen_time``
+# (how compile_time splits into planning and NVRTC) and the cache key as metadata.
+_telemetry_handlers = []
+
+
+def attach_telemetry(handler):
+    """``:telemetry.attach/4`` for the compilation event: ``handler(event, measurements, metadata)``."""
+    _telemetry_handlers.append(handler)
+    return handler
+
+
+def detach_telemetry(handler):
+    if handler in _telemetry_handlers:
+        _telemetry_handlers.remove(handler)
+
+
+def _emit_compilation(key, eval_time, compile_time, program):
+    if not _telemetry_handlers:
+        return
+    m = {"eval_time": eval_time, "compile_time": compile_time, "total_time": eval_time + compile_time}
+    if program is not None:
+        m.update(program.build_times())
+    for h in list(_telemetry_handlers):
+        h(("b200", "compilation"), m, {"key": key})
+
 
 def trace(fun, templates):
     """Run ``fun`` with parameter nodes in place of its tensor arguments
@@ -171,11 +207,14 @@ def __compile__(key, templates, fun, opts):
     with _cache_lock:
         entry = _cache.get(ck)
     if entry is None:
+        t0 = time.perf_counter()
         outs, ospec, params = _trace(fun, templates)
+        t1 = time.perf_counter()
         # outputs that are parameters or constants still need a buffer of
         # their own: results are always fresh tensors (exla/lib/exla/defn.ex:387-393)
         donated = [i for i, t in enumerate(flat) if getattr(t, "donatable", False)]
         entry = (_make_runner(outs, params, alias_pairs(donated, params, outs), hooks), ospec)
+        _emit_compilation(key, t1 - t0, time.perf_counter() - t1, getattr(entry[0], "program", None))
         with _cache_lock:
             _cache.setdefault(ck, entry)
     run_graph, ospec = entry

@@ -72,10 +72,12 @@ def _declare(l):
         "nxb200_program_run_into": [vp, i32, p(vp), i32, p(vp), i32],
         "nxb200_program_release": [vp],
         "nxb200_program_launch_count": [vp, p(i32)],
+        "nxb200_program_build_times": [vp, p(C.c_double), p(C.c_double)],
         "nxb200_device_synchronize": [i32],
         "nxb200_timer_begin": [i32],
         "nxb200_timer_end": [i32, p(C.c_float)],
         "nxb200_device_stream": [i32, p(vp)],
+        "nxb200_selftest_bounded_wait": [i32, C.c_uint32],
         "nxb200_memory_stats": [i32, p(C.c_uint64), p(C.c_uint64), p(C.c_uint64)],
         "nxb200_memory_reset_peak": [i32],
         "nxb200_buffer_from_pointer": [i32, i32, C.POINTER(C.c_int64), i32, vp, C.POINTER(vp)],

@@ -7,9 +7,13 @@
  * (nx/lib/nx/defn/evaluator.ex:363-388): reduce_max (nx/lib/nx/binary_backend.ex:1344-1355),
  * exp(x - max), sum (:1316-1324), Nx.logsumexp (nx/lib/nx.ex:18400-18433), the
  * softmax division, argmax with the lowest index on ties (:1415-1431) and the
- * chain tanh(x*0.5+0.1)*sigmoid(x), all in f32 arithmetic (XLA-style numerics;
- * the f64 BinaryBackend mode lives in nx_oracle.py).  Rows are independent and
- * are spread over OpenMP threads.
+ * chain tanh(x*0.5+0.1)*sigmoid(x).  Elementwise arithmetic is f32 (XLA-style
+ * numerics; the f64 BinaryBackend mode lives in nx_oracle.py); the two row sums
+ * are accumulated in double and rounded once, as the reference's reducer does
+ * (bin_reduce folds Erlang floats, nx/lib/nx/binary_backend.ex:2342-2360): a
+ * sequential f32 sum over 32768 terms would carry an error of the order of the
+ * tolerance itself and could not serve as the expected value.  Rows are
+ * independent and are spread over OpenMP threads.
  */
 #include <math.h>
 #include <stdint.h>
@@ -35,14 +39,15 @@ void rows_oracle(const float *x, int64_t rows, int64_t cols, float *rowmax, floa
     rowmax[r] = m;
     /* exp(x - max) materialised, then its sum */
     for (int64_t c = 0; c < cols; ++c) er[c] = expf(xr[c] - m);
-    float s = 0.f;
-    for (int64_t c = 0; c < cols; ++c) s += er[c];
+    double sd = 0.0;
+    for (int64_t c = 0; c < cols; ++c) sd += (double)er[c];
+    const float s = (float)sd;
     sum[r] = s;
     /* logsumexp: the max is replaced by 0 when it is infinite */
     float m2 = isinf(m) ? 0.f : m;
-    float s2 = 0.f;
-    for (int64_t c = 0; c < cols; ++c) s2 += expf(xr[c] - m2);
-    lse[r] = logf(s2) + m2;
+    double s2d = 0.0;
+    for (int64_t c = 0; c < cols; ++c) s2d += (double)expf(xr[c] - m2);
+    lse[r] = logf((float)s2d) + m2;
     for (int64_t c = 0; c < cols; ++c) sr[c] = er[c] / s;
     /* argmax: a candidate replaces the current one if strictly greater or NaN */
     int64_t best = 0;

@@ -89,3 +89,27 @@ def test_static_scratch_product_checks_arguments_before_touching_a_device():
     assert "scratch" in nif.last_error()
     assert call(0, ok, ok, ok, 8, 8, 12, None) == nif.ERR_INVALID           # rows not on 16-byte boundaries
     assert call(0, ok, ok, None, 8, 8, 8, None) == nif.ERR_INVALID
+
+
+def test_compilation_telemetry_fires_once_per_cache_miss():
+    """[:exla, :compilation] of the reference (exla/lib/exla/defn.ex:515-523): eval_time, compile_time
+    and total_time on a cache miss, nothing on a hit."""
+    from nx_b200 import nx
+    events = []
+    handler = defn.attach_telemetry(lambda event, measurements, metadata: events.append((event, measurements, metadata)))
+    try:
+        fun = lambda x: nx.exp(x) + 1.0
+        first = defn.compile(fun, [defn.template((4, 4), "f32")])
+        assert len(events) == 1
+        event, m, meta = events[0]
+        assert event == ("b200", "compilation") and "key" in meta
+        assert m["eval_time"] > 0 and m["compile_time"] > 0
+        assert abs(m["total_time"] - (m["eval_time"] + m["compile_time"])) < 1e-9
+        assert 0 < m["codegen_time"] <= m["compile_time"] and m["plan_time"] > 0
+        defn.compile(fun, [defn.template((4, 4), "f32")])              # same function, same signature: a cache hit
+        assert len(events) == 1
+        defn.compile(fun, [defn.template((8, 4), "f32")])              # another signature: compiled again
+        assert len(events) == 2
+        assert first.program.build_times()["codegen_time"] == m["codegen_time"]
+    finally:
+        defn.detach_telemetry(handler)
