@@ -129,7 +129,8 @@ int nxb200_buffer_release(nxb200_buffer *buf);
  * [n, axes…]; transpose [perm…]; slice [starts…, lengths…, strides…] (with
  * dynamic starts the node has 1 + rank arguments: the tensor, then one scalar
  * integer start per axis, and the starts attribute is ignored); gather [axes…]
- * (arguments: tensor, indices); put_slice none (arguments: tensor, slice, one
+ * (arguments: tensor, indices); indexed_add / indexed_put [axes…] (arguments: tensor and
+ * updates already of the result's type, indices s32 or s64 {n, axes}); put_slice none (arguments: tensor, slice, one
  * scalar integer start per axis); pad [lows…, highs…, interiors…] (arguments:
  * tensor, scalar pad value); reverse [axes…]; window_sum/max/min/product
  * [window…, strides…, low padding…, high padding…, dilations…]; sort

@@ -199,6 +199,9 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
       } else if (step.kind == Step::SORT) {
         const SortSpec& ss = plan.sorts[step.index];
         launch_sort_rows(ptr[ss.in_slot], ptr[ss.out_slot], ss.rows, ss.len, ss.dt, ss.out_dt, ss.descending, ss.indices, d.sm_count, d.stream);
+      } else if (step.kind == Step::SCATTER) {
+        const ScatterSpec& sc = plan.scatters[step.index];
+        launch_scatter(sc, ptr[sc.target_slot], ptr[sc.indices_slot], ptr[sc.updates_slot], ptr[sc.out_slot], d.sm_count, d.stream);
       } else if (step.kind == Step::ALLREDUCE) {
         if (held) throw NotReplayable();
         const CollectiveSpec& cs = plan.collectives[step.index];

@@ -1531,14 +1531,15 @@ struct Planner {
     int d = 0;
     for (int a : g.nodes[n].args) {
       const std::string& op = g.nodes[a].op;
-      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention" || op == "sort" || op == "argsort") ? 1 : 0));
+      d = std::max(d, depth(a) + ((op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention" || op == "sort" || op == "argsort" || op == "indexed_add" || op == "indexed_put") ? 1 : 0));
     }
     return depth_memo[n] = d;
   }
 
   bool is_leaf(int n) const {
     const std::string& op = g.nodes[n].op;
-    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention" || op == "sort" || op == "argsort";
+    return op == "parameter" || op == "tensor" || op == "dot" || op == "concatenate" || op == "all_reduce" || op == "attention" || op == "sort" || op == "argsort" ||
+           op == "indexed_add" || op == "indexed_put";
   }
 
   // Nodes reachable backwards through everything a kernel can generate inline
@@ -1561,6 +1562,7 @@ std::string Plan::describe() const {
     else if (st.kind == Step::GEMM) o << gemms[st.index].desc << "\n";
     else if (st.kind == Step::ATTENTION) o << attentions[st.index].desc << "\n";
     else if (st.kind == Step::SORT) o << sorts[st.index].desc << "\n";
+    else if (st.kind == Step::SCATTER) o << scatters[st.index].desc << "\n";
     else o << collectives[st.index].desc << "\n";
   }
   for (auto& a : aliases)
@@ -1711,7 +1713,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       const Node& nd = g.nodes[n];
       if (!nd.live) continue;
       bool ok = is_inline(nd) || is_reduce(nd) || nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" ||
-                nd.op == "all_reduce" || nd.op == "attention" || nd.op == "sort" || nd.op == "argsort";
+                nd.op == "all_reduce" || nd.op == "attention" || nd.op == "sort" || nd.op == "argsort" || nd.op == "indexed_add" || nd.op == "indexed_put";
       if (!ok) fail(NXB_ERR_UNSUPPORTED, "Nx op :" + nd.op + " is not implemented by the B200 compiler");
       if (nd.op == "slice" && nd.args.size() != 1 && nd.args.size() != 1 + nd.shape.size())
         fail(NXB_ERR_INVALID_ARGUMENT, "slice with dynamic start indices takes one start per axis");
@@ -1723,6 +1725,18 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       }
       if (nd.op == "put_slice" && nd.args.size() != 2 + nd.shape.size())
         fail(NXB_ERR_INVALID_ARGUMENT, "put_slice takes (tensor, slice, one start per axis)");
+      if (nd.op == "indexed_add" || nd.op == "indexed_put") {
+        if (nd.args.size() != 3 || nd.ints.empty()) fail(NXB_ERR_INVALID_ARGUMENT, nd.op + " takes (tensor, indices, updates) and its indexed axes");
+        const Node &tg = g.nodes[nd.args[0]], &ix = g.nodes[nd.args[1]], &up = g.nodes[nd.args[2]];
+        if ((ix.dt != NXB_S32 && ix.dt != NXB_S64) || ix.shape.size() != 2 || ix.shape[1] != (int64_t)nd.ints.size())
+          fail(NXB_ERR_INVALID_ARGUMENT, nd.op + ": indices must be s32 or s64 {n, indexed axes}");
+        if (tg.dt != nd.dt || up.dt != nd.dt || tg.shape != nd.shape || up.shape.empty() || up.shape[0] != ix.shape[0] ||
+            up.shape.size() - 1 + nd.ints.size() != nd.shape.size())
+          fail(NXB_ERR_INVALID_ARGUMENT, nd.op + ": target and updates must have the result's type, updates {n, slice...}");
+        for (size_t k = 0; k < nd.ints.size(); ++k)
+          if (nd.ints[k] < 0 || nd.ints[k] >= (int64_t)nd.shape.size() || (k && nd.ints[k] <= nd.ints[k - 1]))
+            fail(NXB_ERR_INVALID_ARGUMENT, nd.op + ": axes must be ascending axes of the target");
+      }
     }
   }
 
@@ -1767,11 +1781,14 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       if (nd.args.size() != 1 || nd.shape.empty() || !sort_rows_supported(nd.shape.back()))
         fail(NXB_ERR_UNSUPPORTED, "sort is implemented along a last axis of at most 16384 elements");
     }
-    if (nd.op == "all_reduce" || nd.op == "sort" || nd.op == "argsort") {
+    if (nd.op == "all_reduce" || nd.op == "sort" || nd.op == "argsort" || nd.op == "indexed_add" || nd.op == "indexed_put") {
+      // library steps: buffers in, one buffer out
       P.mat[n] = 1;
       allreduces.push_back(n);
-      const std::string& aop = g.nodes[nd.args[0]].op;
-      if (aop != "parameter" && aop != "tensor") P.mat[nd.args[0]] = 1;
+      for (int a : nd.args) {
+        const std::string& aop = g.nodes[a].op;
+        if (aop != "parameter" && aop != "tensor") P.mat[a] = 1;
+      }
     }
   }
   // dot operands: decided by the GEMM planner (it may accept a transposed view directly)
@@ -1886,7 +1903,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         for (int n = 0; n < N; ++n) {
           const Node& nd = g.nodes[n];
           if (!nd.live || !P.mat[n]) continue;
-          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || nd.op == "all_reduce" || nd.op == "attention" || nd.op == "sort" || nd.op == "argsort" || is_reduce(nd)) continue;
+          if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "dot" || nd.op == "concatenate" || nd.op == "all_reduce" || nd.op == "attention" || nd.op == "sort" || nd.op == "argsort" || nd.op == "indexed_add" || nd.op == "indexed_put" || is_reduce(nd)) continue;
           roots.push_back(n);
         }
         for (int n : roots) {
@@ -2001,7 +2018,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           bool later = false;
           for (int l : leaves) {
             const std::string& lop = g.nodes[l].op;
-            if (l != D && (lop == "concatenate" || lop == "all_reduce" || lop == "attention" || lop == "sort" || lop == "argsort") && P.depth(l) > P.depth(D)) later = true;
+            if (l != D && (lop == "concatenate" || lop == "all_reduce" || lop == "attention" || lop == "sort" || lop == "argsort" || lop == "indexed_add" || lop == "indexed_put") && P.depth(l) > P.depth(D)) later = true;
           }
           if (later) continue;
           const Node& dn = g.nodes[D];
@@ -2059,7 +2076,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         if (u.kind == Unit::ALLREDUCE) {
           const Node& nd = g.nodes[u.gemm_node];
           u.writes.insert(nd.slot);
-          u.reads.insert(g.nodes[nd.args[0]].slot);
+          for (int a : nd.args) u.reads.insert(g.nodes[a].slot);
           return;
         }
         if (u.kind == Unit::ATTN) {
@@ -2201,6 +2218,23 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
                     (ss.descending ? "descending" : "ascending") + " (bitonic network over (key, position) pairs in shared memory)";
           pl.sorts.push_back(ss);
           pl.steps.push_back({Step::SORT, (int)pl.sorts.size() - 1});
+        } else if (u.kind == Unit::ALLREDUCE && (g.nodes[u.gemm_node].op == "indexed_add" || g.nodes[u.gemm_node].op == "indexed_put")) {
+          const Node& nd = g.nodes[u.gemm_node];
+          ScatterSpec sc;
+          sc.target_slot = g.nodes[nd.args[0]].slot;
+          sc.indices_slot = g.nodes[nd.args[1]].slot;
+          sc.updates_slot = g.nodes[nd.args[2]].slot;
+          sc.out_slot = nd.slot;
+          sc.dt = nd.dt;
+          sc.index_dt = g.nodes[nd.args[1]].dt;
+          sc.add = nd.op == "indexed_add";
+          sc.target_shape = nd.shape;
+          sc.update_shape = g.nodes[nd.args[2]].shape;
+          for (auto a : nd.ints) sc.axes.push_back((int)a);
+          sc.desc = nd.op + "#" + std::to_string(u.gemm_node) + " " + dtype_name(nd.dt) + shape_str(nd.shape) + " <- " + std::to_string(sc.update_shape[0]) +
+                    " slices " + shape_str(sc.update_shape) + (sc.add ? " (copy of the target, then atomic adds)" : " (copy of the target, then stores)");
+          pl.scatters.push_back(sc);
+          pl.steps.push_back({Step::SCATTER, (int)pl.scatters.size() - 1});
         } else if (u.kind == Unit::ALLREDUCE) {
           const Node& nd = g.nodes[u.gemm_node];
           CollectiveSpec cs;
@@ -2357,6 +2391,9 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
         } else if (step.kind == Step::SORT) {
           const SortSpec& ss = pl.sorts[step.index];
           if (ss.in_slot == sp || ss.out_slot == so) other = true;
+        } else if (step.kind == Step::SCATTER) {
+          const ScatterSpec& sc = pl.scatters[step.index];
+          if (sc.target_slot == sp || sc.indices_slot == sp || sc.updates_slot == sp || sc.out_slot == so) other = true;
         } else {
           const CollectiveSpec& cs = pl.collectives[step.index];
           if (cs.in_slot == sp || cs.out_slot == so) other = true;

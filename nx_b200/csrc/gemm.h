@@ -81,6 +81,10 @@ void launch_wq_linear(const GemmArgs& g, int* status_word, int sm_count, cudaStr
 bool sort_rows_supported(int64_t len);
 void launch_sort_rows(const void* in, void* out, int64_t rows, int64_t len, DType dt, DType out_dt, bool descending, bool want_indices,
                       int sm_count, cudaStream_t stream);
+// indexed_add / indexed_put (scatter.cu): copies the target into `out` (unless they are the same memory)
+// and applies the updates.
+void launch_scatter(const ScatterSpec& ss, const void* target, const void* indices, const void* updates, void* out, int sm_count,
+                    cudaStream_t stream);
 // Self-test of the bounded wait: see nxb200_selftest_bounded_wait.
 void launch_wait_probe(const uint32_t* flag, long long limit_cycles, int* status_word, cudaStream_t stream);
 void launch_transpose(const void* in, void* out, int64_t batch, int64_t rows, int64_t cols, size_t elem_size, cudaStream_t stream);

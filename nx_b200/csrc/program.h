@@ -113,8 +113,18 @@ struct SortSpec {
   std::string desc;
 };
 
+// indexed_add / indexed_put: the result is a copy of the target with the updates applied (scatter.cu)
+struct ScatterSpec {
+  int target_slot = -1, indices_slot = -1, updates_slot = -1, out_slot = -1;
+  DType dt = NXB_F32, index_dt = NXB_S32;
+  bool add = true;
+  std::vector<int64_t> target_shape, update_shape;
+  std::vector<int> axes;
+  std::string desc;
+};
+
 struct Step {
-  enum Kind { KERNEL, GEMM, ALLREDUCE, ATTENTION, SORT } kind = KERNEL;
+  enum Kind { KERNEL, GEMM, ALLREDUCE, ATTENTION, SORT, SCATTER } kind = KERNEL;
   int index = 0;
 };
 
@@ -127,6 +137,7 @@ struct Plan {
   std::vector<CollectiveSpec> collectives;
   std::vector<AttentionSpec> attentions;
   std::vector<SortSpec> sorts;
+  std::vector<ScatterSpec> scatters;
   std::vector<int> param_slots;   // by parameter index (-1 when unused)
   std::vector<int> output_slots;  // by output index
   // Buffer donation (Nx.donatable, exla/lib/exla/defn.ex:598-645): the result takes over the

@@ -14,10 +14,12 @@
 //               as zeros) into a deep ring (up to 16 stages: the stream is latency bound, a CTA
 //               needs ~100 KB in flight to draw its share of the memory bandwidth)
 //   12 warps    converters (every warp outside scheduler partition 0): s8 -> bf16 (exact), written
-//               as the 128-byte-swizzled K-major A tile into a second ring.  All twelve work on the
-//               same k block, one 16-byte piece (16 weights of one channel) per thread, so the
-//               hand-over latency per k block is that of one short sequence.  Afterwards the same
-//               warps are the epilogue (tcgen05.ld, scale per lane, store)
+//               as 128-byte-swizzled K-major A tiles into a second ring.  Three groups of four warps
+//               take the ring stages round-robin; a stage holds up to four k blocks, because what a
+//               hand-over between the roles costs (barrier polls, proxy fence: ~800 cycles per pass,
+//               ~230 cycles per copy instruction, ~100 per MMA instruction) does not depend on how
+//               much data it covers.  Afterwards the same warps are the epilogue (tcgen05.ld, scale
+//               per lane, store)
 //   warps 4,8,12 MMA issuers (scheduler partition 0, like the producer): one thread each (three
 //               for narrow batches, else one), k blocks round-robin, own accumulators; tcgen05.mma
 //               M=128, N=padded batch, K=16, f32 accumulators in TMEM summed by the epilogue
@@ -41,7 +43,11 @@ struct WqParams {
   int* status;
   int m, n, k;
   int mb;        // rows of x per CTA: a multiple of 16, at most 256
-  int ch;        // output channels per CTA (rows of the W tile), at most 128
+  int ch;        // output channels per CTA (rows of the W tile): a multiple of 8, at most 128
+  int g;         // k blocks of 64 per ring stage (one hand-over between the roles per stage): 1, 2 or 4
+  int raw_bytes; // bytes of the raw W part of a stage: g slabs of ch x 64, rounded up to 1024
+  int conv_slab; // bytes of one converted tile: ch rows of 128 bytes, rounded up to 1024
+  int blocked;   // the tensor maps count k blocks in their third coordinate (else: k offset in the first, g == 1)
   int out_dt;
   int stages;    // depth of the {raw W, x} ring
   int conv_stages;   // depth of the converted-tile ring
@@ -86,10 +92,16 @@ __global__ void __launch_bounds__(WQ_THREADS, 1)
 wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, WqParams p) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t x_bytes = (uint32_t)p.mb * 128u;
-  const uint32_t stage_bytes = WQ_RAW + x_bytes;
-  const uint32_t wb0 = base + (uint32_t)p.stages * stage_bytes;
-  const uint32_t bars = wb0 + (uint32_t)p.conv_stages * WQ_WB;
+  // a ring stage holds g k blocks: [g slabs of raw W, ch x 64 bytes each][g slabs of x, mb x 128 bytes each];
+  // a stage of the converted ring holds g tiles of ch rows x 128 bytes.  The converted ring comes first:
+  // the MMA reads 128 rows of every tile, and what it reads beyond the band (the next tile, or the start
+  // of the other ring) only reaches accumulator lanes that are never stored.
+  const uint32_t x_bytes = (uint32_t)p.mb * 128u, raw_slab = (uint32_t)p.ch * 64u;
+  const uint32_t stage_bytes = (uint32_t)p.raw_bytes + (uint32_t)p.g * x_bytes;
+  const uint32_t conv_slab = (uint32_t)p.conv_slab, conv_bytes = (uint32_t)p.g * conv_slab;
+  const uint32_t wb0 = base;
+  const uint32_t ring0 = base + (uint32_t)p.conv_stages * conv_bytes;
+  const uint32_t bars = ring0 + (uint32_t)p.stages * stage_bytes;
   const uint32_t full0 = bars, empty0 = bars + 128, conv0 = bars + 256, wbe0 = bars + 320, acc_full = bars + 384, tmem_slot = bars + 392;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + (tmem_slot - base));
@@ -98,10 +110,11 @@ wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = (int)blockIdx.x * p.ch, m0 = (int)blockIdx.y * p.mb;
   const int kblocks = (p.k + 63) / 64;
+  const int nst = (kblocks + p.g - 1) / p.g;       // ring stages to go through; k blocks beyond the last arrive as zeros
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int c = 0; c < p.conv_stages; ++c) { mbar_init(conv0 + 8 * c, 12); mbar_init(wbe0 + 8 * c, 1); }
+    for (int c = 0; c < p.conv_stages; ++c) { mbar_init(conv0 + 8 * c, 4); mbar_init(wbe0 + 8 * c, 1); }
     mbar_init(acc_full, p.issuers);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -130,19 +143,22 @@ wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     int s = which % p.stages, c = which % p.conv_stages;
     uint32_t cph = (uint32_t)((which / p.conv_stages) & 1);
     bool ok = true;
-    for (int kb = which; kb < kblocks; kb += step) {
+    for (int st = which; st < nst; st += step) {
       // the converters arrive on conv only after the stage's TMA data (x included) has landed
       if (!mbar_wait(conv0 + 8 * c, cph, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const uint64_t adesc = make_desc(wb0 + (uint32_t)c * WQ_WB), bdesc = make_desc(base + (uint32_t)s * stage_bytes + WQ_RAW);
-      // consecutive MMAs go to different accumulators: accumulating into the columns the
-      // previous one is still writing would serialise them on the pipeline's latency
+      for (int gi = 0; gi < p.g; ++gi) {
+        const uint64_t adesc = make_desc(wb0 + (uint32_t)c * conv_bytes + (uint32_t)gi * conv_slab);
+        const uint64_t bdesc = make_desc(ring0 + (uint32_t)s * stage_bytes + (uint32_t)p.raw_bytes + (uint32_t)gi * x_bytes);
+        // consecutive MMAs go to different accumulators: accumulating into the columns the
+        // previous one is still writing would serialise them on the pipeline's latency
 #pragma unroll
-      for (int k4 = 0; k4 < 4; ++k4) {
-        tc_mma(acc, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, fresh > 0 ? 0u : 1u, false);
-        if (fresh > 0) --fresh;
-        acc += (uint32_t)p.mb;
-        if (acc == acc_end) acc = acc0;
+        for (int k4 = 0; k4 < 4; ++k4) {
+          tc_mma(acc, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, fresh > 0 ? 0u : 1u, false);
+          if (fresh > 0) --fresh;
+          acc += (uint32_t)p.mb;
+          if (acc == acc_end) acc = acc0;
+        }
       }
       tc_commit(empty0 + 8 * s);
       tc_commit(wbe0 + 8 * c);
@@ -158,12 +174,13 @@ wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
-      for (int kb = 0; kb < kblocks; ++kb) {
+      for (int st = 0; st < nst; ++st) {
         if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag)) break;
-        const uint32_t st = base + (uint32_t)s * stage_bytes;
-        mbar_expect_tx(full0 + 8 * s, (uint32_t)p.ch * 64u + x_bytes);
-        tma_load_3d(st, &map_w, full0 + 8 * s, kb * 64, n0, 0);
-        tma_load_3d(st + WQ_RAW, &map_x, full0 + 8 * s, kb * 64, m0, 0);
+        const uint32_t sb = ring0 + (uint32_t)s * stage_bytes;
+        // one copy each for W and x: the third coordinate of both maps counts k blocks
+        mbar_expect_tx(full0 + 8 * s, (uint32_t)p.g * (raw_slab + x_bytes));
+        tma_load_3d(sb, &map_w, full0 + 8 * s, p.blocked ? 0 : st * 64, n0, p.blocked ? st * p.g : 0);
+        tma_load_3d(sb + (uint32_t)p.raw_bytes, &map_x, full0 + 8 * s, p.blocked ? 0 : st * 64, m0, p.blocked ? st * p.g : 0);
         if (++s == p.stages) { s = 0; ph ^= 1; }
       }
     }
@@ -175,46 +192,51 @@ wq_linear_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     __syncwarp();
     // The converter warps are the twelve outside scheduler partition 0 (where the producer and
     // the MMA issuers live: a single thread issuing MMAs loses most of its issue slots to busy
-    // warps on the same scheduler).  All of them work on the same k block: thread t takes the 16-byte
-    // piece t & 3 of row t >> 2 of the raw tile (and, for bands of more than 96 channels, the piece
-    // 384 further on), i.e. 16 weights of one channel, and writes them as 32 bytes of bf16.
+    // warps on the same scheduler).  Three groups of four warps take the ring stages round-robin:
+    // one pass of a group (wait, load, convert, store, proxy fence, arrive) is some 800 cycles of
+    // latency whatever the amount of data, so three passes are in flight at a time and each covers
+    // g k blocks.  Within a group, thread t takes the 16-byte pieces t, t + 128, ... of the stage:
+    // piece (k block, row, quarter) = 16 weights of one channel, written as 32 bytes of bf16.
     const bool converter = (warp & 3) != 0;
-    const int ct = ((warp >> 2) * 3 + (warp & 3) - 1) * 32 + lane;      // 0..383
-    int s = 0, cs = 0;
-    uint32_t ph = 0, cph = 0;
+    const int ci = (warp >> 2) * 3 + (warp & 3) - 1;      // 0..11
+    const int grp = ci >> 2;
+    const int ct = (ci & 3) * 32 + lane;                  // 0..127 inside the group
+    int s = grp % p.stages, cs = grp % p.conv_stages;
+    uint32_t ph = (uint32_t)((grp / p.stages) & 1), cph = (uint32_t)((grp / p.conv_stages) & 1);
     bool ok = true;
-    for (int kb = 0; converter && kb < kblocks && ok; ++kb) {
+    const int tasks = p.g * p.ch * 4;               // 16-byte pieces of raw W per stage
+    for (int st = grp; converter && st < nst && ok; st += 3) {
       // one lane per warp polls the barriers
       int okw = 1;
       if (lane == 0) okw = mbar_wait_relaxed(full0 + 8 * s, ph, abort_flag) && mbar_wait_relaxed(wbe0 + 8 * cs, cph ^ 1, abort_flag);
       okw = __shfl_sync(0xffffffffu, okw, 0);
       __syncwarp();
       if (!okw) { ok = false; break; }
-      const uint32_t st = base + (uint32_t)s * stage_bytes;
-      const uint32_t wb = wb0 + (uint32_t)cs * WQ_WB;
-#pragma unroll
-      for (int rep = 0; rep < 2; ++rep) {
-        const int t = ct + rep * 384;
-        const int r = t >> 2, c = t & 3;
-        if (r < p.ch) {
-          uint32_t w[4], o[8];
-          const uint32_t src = st + (uint32_t)r * 64u + (uint32_t)((c ^ ((r >> 1) & 3)) * 16);
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(src));
-          s8x4_to_bf16x4(w[0], o[0], o[1]);
-          s8x4_to_bf16x4(w[1], o[2], o[3]);
-          s8x4_to_bf16x4(w[2], o[4], o[5]);
-          s8x4_to_bf16x4(w[3], o[6], o[7]);
-          const uint32_t row = wb + (uint32_t)r * 128u;
-          const uint32_t d0 = row + (uint32_t)(((2 * c) ^ (r & 7)) * 16), d1 = row + (uint32_t)(((2 * c + 1) ^ (r & 7)) * 16);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
-        }
+      const uint32_t sb = ring0 + (uint32_t)s * stage_bytes;
+      const uint32_t wb = wb0 + (uint32_t)cs * conv_bytes;
+#pragma unroll 2
+      for (int t = ct; t < tasks; t += 128) {
+        const int gi = t / (p.ch * 4), rc = t - gi * (p.ch * 4);
+        const int r = rc >> 2, c = rc & 3;
+        uint32_t w[4], o[8];
+        const uint32_t src = sb + (uint32_t)gi * raw_slab + (uint32_t)r * 64u + (uint32_t)((c ^ ((r >> 1) & 3)) * 16);
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(src));
+        s8x4_to_bf16x4(w[0], o[0], o[1]);
+        s8x4_to_bf16x4(w[1], o[2], o[3]);
+        s8x4_to_bf16x4(w[2], o[4], o[5]);
+        s8x4_to_bf16x4(w[3], o[6], o[7]);
+        const uint32_t row = wb + (uint32_t)gi * conv_slab + (uint32_t)r * 128u;
+        const uint32_t d0 = row + (uint32_t)(((2 * c) ^ (r & 7)) * 16), d1 = row + (uint32_t)(((2 * c + 1) ^ (r & 7)) * 16);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d0), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]) : "memory");
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(d1), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(conv0 + 8 * cs);
-      if (++s == p.stages) { s = 0; ph ^= 1; }
-      if (++cs == p.conv_stages) { cs = 0; cph ^= 1; }
+      s += 3;
+      while (s >= p.stages) { s -= p.stages; ph ^= 1; }
+      cs += 3;
+      while (cs >= p.conv_stages) { cs -= p.conv_stages; cph ^= 1; }
     }
     // epilogue: lane = output channel, columns = rows of x
     int acc_ok = 1;
@@ -495,13 +517,24 @@ void launch_wq_stream(const GemmArgs& g, int* status_word, int sm_count, cudaStr
   NXB_CUDA(cudaGetLastError());
 }
 
-CUtensorMap wq_map(const void* ptr, CUtensorMapDataType type, size_t es, int64_t k, int64_t rows, int64_t ld, int box_rows, CUtensorMapSwizzle sw) {
+// Tensor map over a row-major [rows][k] matrix in units of 64 k: coordinates (k within the block, row,
+// k block).  `blocked`: the third dimension walks the k blocks of a row (stride 64 elements), so a box
+// of `g` blocks arrives as g consecutive tiles of [box_rows][64 k]; needs k % 64 == 0.  Otherwise the
+// map is the plain two-dimensional view (third dimension of extent 1) and the first coordinate is the k
+// offset itself, with out-of-range k filled with zeros.
+CUtensorMap wq_map(const void* ptr, CUtensorMapDataType type, size_t es, int64_t k, int64_t rows, int64_t ld, int box_rows, int g, bool blocked,
+                   CUtensorMapSwizzle sw) {
   const DriverApi& drv = driver();
   if (!drv.cuTensorMapEncodeTiled) fail(NXB_ERR_RUNTIME, "cuTensorMapEncodeTiled is unavailable");
   CUtensorMap m;
   cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, 1};
   cuuint64_t strides[2] = {(cuuint64_t)(ld * es), (cuuint64_t)(ld * es) * (cuuint64_t)rows};
   cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  if (blocked) {
+    dims[0] = 64; dims[2] = (cuuint64_t)(k / 64);
+    strides[1] = (cuuint64_t)(64 * es);
+    box[2] = (cuuint32_t)g;
+  }
   cuuint32_t estr[3] = {1, 1, 1};
   check_cu(drv.cuTensorMapEncodeTiled(&m, type, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
@@ -526,26 +559,41 @@ void launch_wq_linear(const GemmArgs& g, int* status_word, int sm_count, cudaStr
   p.m = (int)g.m; p.n = (int)g.n; p.k = (int)g.k;
   p.mb = (int)std::min<int64_t>(256, (g.m + 15) / 16 * 16);
   p.out_dt = (int)g.dc;
-  const int stage = WQ_RAW + p.mb * 128;
-  const char* cs_env = getenv("NXB200_WQ_CONV_STAGES");
-  p.conv_stages = cs_env ? std::max(2, std::min(WQ_MAX_CONV_STAGES, atoi(cs_env))) : (p.mb <= 64 ? 8 : 4);
-  p.stages = std::min(WQ_MAX_STAGES, (WQ_SMEM_LIMIT - p.conv_stages * WQ_WB) / stage);
+  // one band of channels per SM (a multiple of 8 channels, at most 128)
+  p.ch = (int)std::min<int64_t>(128, ((g.n + sm_count - 1) / sm_count + 7) / 8 * 8);
+  if (const char* e = getenv("NXB200_WQ_BAND")) { const int v = atoi(e); if (v >= 8 && v <= 128 && v % 8 == 0) p.ch = v; }
   const int kblocks = (p.k + 63) / 64;
+  // Several k blocks per ring stage cut the hand-overs between the roles (and the copies to issue) per
+  // byte of W; the x part of a stage grows with the batch, which bounds it.  A k that ends inside a
+  // block needs the zero fill of the two-dimensional view, i.e. one block per stage.
+  p.g = p.mb <= 32 ? 4 : p.mb <= 128 ? 2 : 1;
+  if (p.k % 64 != 0) p.g = 1;
+  if (const char* e = getenv("NXB200_WQ_KBLOCKS")) { const int v = atoi(e); if ((v == 1 || v == 2 || v == 4) && p.k % 64 == 0) p.g = v; }
+  p.raw_bytes = (p.g * p.ch * 64 + 1023) / 1024 * 1024;
+  const int stage = p.raw_bytes + p.g * p.mb * 128;
+  p.conv_slab = (p.ch * 128 + 1023) / 1024 * 1024;
+  const int conv_stage = p.g * p.conv_slab;
+  const char* cs_env = getenv("NXB200_WQ_CONV_STAGES");
+  p.conv_stages = cs_env ? std::max(2, std::min(WQ_MAX_CONV_STAGES, atoi(cs_env))) : (p.g > 1 ? 3 : (p.mb <= 64 ? 8 : 4));
+  p.stages = std::max(3, std::min(WQ_MAX_STAGES, (WQ_SMEM_LIMIT - p.conv_stages * conv_stage) / stage));
+  const int nst = (kblocks + p.g - 1) / p.g;
   // narrow batches are bound by the rate at which MMAs can be issued: up to three issuing threads
   const char* iss_env = getenv("NXB200_WQ_ISSUERS");
   p.issuers = iss_env ? std::max(1, std::min(3, atoi(iss_env))) : (p.mb <= 64 ? 3 : 1);
-  p.issuers = std::min(p.issuers, std::max(1, kblocks));
+  p.issuers = std::min(p.issuers, std::max(1, nst));
   p.issuers = std::min(p.issuers, 512 / p.mb);          // one accumulator each must fit the 512 TMEM columns
   const int per_issuer = std::max(1, std::min(std::min(8, 512 / p.mb) / p.issuers, 4));
   p.nacc = per_issuer * p.issuers;
   p.tmem_cols = 32;
   while (p.tmem_cols < p.nacc * p.mb) p.tmem_cols *= 2;
-  // one band of channels per SM (at most 128 wide, a whole number of bands covers n)
-  p.ch = (int)std::min<int64_t>(128, (g.n + sm_count - 1) / sm_count);
-  if (const char* e = getenv("NXB200_WQ_BAND")) { const int v = atoi(e); if (v >= 1 && v <= 128) p.ch = v; }
-  CUtensorMap mw = wq_map(g.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.k, g.n, g.ldb, p.ch, CU_TENSOR_MAP_SWIZZLE_64B);
-  CUtensorMap mx = wq_map(g.a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g.k, g.m, g.lda, p.mb, CU_TENSOR_MAP_SWIZZLE_128B);
-  const int smem = p.stages * stage + p.conv_stages * WQ_WB + 1024 + 512;
+  // W and x as [k block][row][64 k]: the third coordinate counts k blocks, so one copy brings g of them.
+  // (With a k that is not a multiple of 64 the blocked view would run into the next row: then g is 1 and
+  // the plain two-dimensional view zero-fills the ragged end.)
+  p.blocked = (p.g > 1) ? 1 : 0;
+  CUtensorMap mw = wq_map(g.b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, g.k, g.n, g.ldb, p.ch, p.g, p.blocked != 0, CU_TENSOR_MAP_SWIZZLE_64B);
+  CUtensorMap mx = wq_map(g.a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, g.k, g.m, g.lda, p.mb, p.g, p.blocked != 0, CU_TENSOR_MAP_SWIZZLE_128B);
+  const int smem = p.stages * stage + p.conv_stages * conv_stage + 1024 + 512;
+  if (smem > 232448) fail(NXB_ERR_RUNTIME, "internal: quantised linear stage sizes exceed shared memory");
   NXB_CUDA(cudaFuncSetAttribute(wq_linear_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((unsigned)((g.n + p.ch - 1) / p.ch), (unsigned)((g.m + p.mb - 1) / p.mb));
   wq_linear_kernel<<<grid, WQ_THREADS, smem, stream>>>(mw, mx, p);

@@ -3,8 +3,10 @@
 nothing new: backward products arrive as `dot` with other contracted axes (served by the
 MN-major operand path of the tensor-core kernel), un-broadcasting as `sum`, and so on.
 
-Rules follow the reference's (file:line quoted per rule).  Not differentiable here (raises):
-gather / take, put_slice, window max / min / product, sort, product, loops.
+Rules follow the reference's (file:line quoted per rule).  Lookups differentiate into scatters:
+gather / take / take_along_axis into `indexed_add`, a slice at computed positions into `put_slice`,
+and the scatters back into gathers.  Not differentiable here (raises): window max / min / product,
+product, loops.
 """
 from . import backend as B
 from . import expr as E
@@ -131,7 +133,13 @@ def _rule(t, g):
     if op == "slice":                                                    # :752-759: zeros around (and between) the taken elements
         x = a[0]
         if len(a) > 1:
-            raise NotImplementedError("gradient of a slice with tensor start indices")
+            # starts computed at run time (:761-768): the gradient, spread over the strides, is put
+            # back at the same position of a tensor of zeros
+            r = x.rank
+            sd = e.ints[2 * r:3 * r]
+            spread = nx.pad(g, 0.0, [(0, 0, k - 1) for k in sd]) if any(k != 1 for k in sd) else g
+            zeros = nx.broadcast(E.constant(x.type, (), 0.0), x.shape)
+            return [(x, nx.put_slice(zeros, list(a[1:]), spread))]
         r = x.rank
         st, ln, sd = e.ints[:r], e.ints[r:2 * r], e.ints[2 * r:3 * r]
         cfg = []
@@ -147,6 +155,42 @@ def _rule(t, g):
         gx = nx.slice(inner, [0] * r, list(inner.shape), [i + 1 for i in it])
         gv = nx.sum(g) - nx.sum(gx)
         return [(x, gx), (v, gv)]
+    if op == "put_slice":                                                # :770-777
+        x, piece, starts = a[0], a[1], list(a[2:])
+        out = []
+        if T.is_float(x.type):
+            out.append((x, nx.as_type(nx.put_slice(g, starts, nx.broadcast(E.constant(g.type, (), 0.0), piece.shape)), x.type)))
+        if T.is_float(piece.type):
+            out.append((piece, nx.as_type(nx.slice(g, starts, list(piece.shape)), piece.type)))
+        return out
+    if op == "gather":                                                   # :970-988: the lookups scatter their gradients back
+        x, idx = a
+        axes = list(e.ints)
+        depth = idx.shape[-1]
+        num = 1
+        for d in idx.shape[:-1]:
+            num *= d
+        rest = [d for i, d in enumerate(x.shape) if i not in axes]
+        zeros = nx.broadcast(E.constant(x.type, (), 0.0), x.shape)
+        return [(x, nx.indexed_add(zeros, nx.reshape(idx, (num, depth)), nx.reshape(g, (num, *rest)), axes=axes))]
+    if op in ("indexed_add", "indexed_put"):                             # :779-795
+        target, idx, upd = a
+        axes = list(e.ints)
+        looked_up = nx.gather(g, idx, axes=axes)                         # {n} ++ the axes that are not indexed
+        if looked_up.shape != upd.shape:                                 # a slice narrower than the target starts at 0
+            looked_up = nx.slice(looked_up, [0] * upd.rank, list(upd.shape))
+        out = [(upd, looked_up)]
+        if op == "indexed_add":
+            out.append((target, g))
+        else:
+            out.append((target, nx.indexed_put(g, idx, nx.broadcast(E.constant(g.type, (), 0.0), upd.shape), axes=axes)))
+        return out
+    if op == "sort":                                                     # :962-968 (the sorted axis is the last one here)
+        x = a[0]
+        last = x.rank - 1
+        order = nx.argsort(x, axis=last, direction="desc" if e.ints[0] else "asc", stable=True)
+        back = nx.argsort(order, axis=last, direction="asc", stable=True)
+        return [(x, nx.take_along_axis(g, back, axis=last))]
     if op == "concatenate":                                              # :946-960
         axis = e.ints[0]
         out, off = [], 0

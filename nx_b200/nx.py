@@ -201,6 +201,10 @@ def _dispatch(builder, operands):
         return builder(*[backend.to_expr(o) for o in operands])
     if _b.all(_is_expr(o) for o in operands) and operands:
         return builder(*operands)          # constants only: folds at trace time
+    if backend.tracing():
+        # inside a traced function every operation is a graph node, also on tensors the function
+        # captured from the host (they become literal nodes, nx/lib/nx/defn/expr.ex:1352-1357)
+        return builder(*[backend.to_expr(o) for o in operands])
     return backend.eager(builder, operands)
 
 
@@ -556,6 +560,66 @@ def gather(x, indices, axes=None):
     shape = tuple(indices.shape[:-1]) + tuple(d for i, d in enumerate(x.shape) if i not in axes)
     out = _out(x.type, shape)
     return _dispatch(lambda a, i: E.node(out, "gather", [a, i], ints=list(axes)), [x, indices])
+
+
+def _indexed_op(op, target, indices, updates, axes):
+    """``Nx.indexed_add/4`` / ``Nx.indexed_put/4`` (nx/lib/nx.ex:8277,8466; shape rules
+    nx/lib/nx/shape.ex:937-973): `indices` {n, i} names, per row, a position along the i indexed
+    axes (default: the leading ones); `updates` {n, ...} holds the slice that lands there, starting
+    at 0 along the other axes.  The result has the merged type of target and updates
+    (both are converted first, exla/lib/exla/defn.ex:1829-1848).  Rows with a coordinate outside the
+    target are dropped, as the compiled (XLA) path does."""
+    type = _binary_type(target if isinstance(target, Tensor) else _num(target), updates if isinstance(updates, Tensor) else _num(updates))
+    target, indices, updates = _as_operand(target), _as_operand(indices), _as_operand(updates)
+    if not T.is_integer(indices.type):
+        raise ValueError(f"indices must be an integer tensor, got type: {indices.type}")
+    if indices.rank == 1:
+        # one index row, one scalar update (nx/lib/nx.ex:8470-8475)
+        if updates.rank != 0 or indices.shape[0] != target.rank:
+            raise ValueError("a rank-1 index updates a single entry: it needs one coordinate per axis and a scalar update")
+        indices, updates = reshape(indices, (1,) + indices.shape), reshape(updates, (1,))
+    if indices.rank != 2:
+        raise ValueError(f"indices must be a rank 1 or 2 tensor, got: {indices.rank}")
+    n, depth = indices.shape
+    if axes is None:
+        axes = list(range(depth))
+    else:
+        axes = _norm_axes(target.rank, axes)
+        if axes != sorted(axes) or len(set(axes)) != len(axes):
+            raise ValueError(":axes must be an ordered list")
+        if len(axes) != depth:
+            raise ValueError(":axes must have the same number of elements as the last dimension of indices")
+    if updates.shape[:1] != (n,):
+        raise ValueError(f"expected the leading axis of indices ({indices.shape}) and leading axis of updates ({updates.shape}) to match")
+    if updates.rank - 1 + depth != target.rank:
+        raise ValueError(f"expected the rank of the input ({target.rank}) to be equal to the rank of the updates ({updates.rank}) "
+                         f"plus the trailing axis of indices ({indices.shape}) minus one")
+    rest = [a for a in range(target.rank) if a not in axes]
+    for j, a in enumerate(rest):
+        if updates.shape[1 + j] > target.shape[a]:
+            raise ValueError(f"axis ({1 + j}) of updates ({updates.shape}) must be less than or equal to the axis ({a}) of {target.shape})")
+    out = _out(type, target.shape)
+    if target.type != type:
+        target = as_type(target, type)
+    if updates.type != type:
+        updates = as_type(updates, type)
+    # the kernel reads 32- or 64-bit signed coordinates
+    want = T.S64 if indices.type in (T.S64, T.U64, T.U32) else T.S32
+    if indices.type != want:
+        indices = as_type(indices, want)
+    return _dispatch(lambda t, i, u: E.node(out, op, [t, i, u], ints=list(axes)), [target, indices, updates])
+
+
+def indexed_add(target, indices, updates, axes=None):
+    """``Nx.indexed_add/4``: adds the slices of `updates` at the positions in `indices`; repeated
+    positions accumulate."""
+    return _indexed_op("indexed_add", target, indices, updates, axes)
+
+
+def indexed_put(target, indices, updates, axes=None):
+    """``Nx.indexed_put/4``: writes the slices of `updates` at the positions in `indices`.  With
+    repeated positions the result is one of the written values (nx/lib/nx.ex:8452-8454)."""
+    return _indexed_op("indexed_put", target, indices, updates, axes)
 
 
 def take(x, indices, axis=0):

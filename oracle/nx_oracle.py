@@ -602,6 +602,33 @@ def evaluate(nodes, outs, params, mode="xla_like", all_reduce=None):
             st = [min(max(int(s), 0), d - l) for s, d, l in zip(arg[2:], base.shape, piece.shape)]
             v = np.array(base, copy=True)
             v[tuple(slice(s, s + l) for s, l in zip(st, piece.shape))] = piece
+        elif op in ("indexed_add", "indexed_put"):
+            # nx/lib/nx/binary_backend.ex indexed_op: every row of `indices` names a position along the
+            # indexed axes; the matching slice of `updates` lands there (starting at 0 along the other
+            # axes) and is added to, or replaces, what the target holds.  Rows are applied in order (with
+            # repeated indices indexed_put keeps the last row, what a sequential evaluator does); rows
+            # with a coordinate outside the target are dropped, as XLA's scatter drops them.
+            axes = list(nd.ints)
+            base, upd = convert(arg[0], at[0], t, mode), convert(arg[2], at[2], t, mode)
+            idx = arg[1].astype(np.int64)
+            rest = [j for j in range(base.ndim) if j not in axes]
+            v = np.array(base, copy=True)
+            work = v.astype(_compute_dtype(t, mode)) if op == "indexed_add" else v
+            for row in range(idx.shape[0]):
+                if any(idx[row, k] < 0 or idx[row, k] >= base.shape[a] for k, a in enumerate(axes)):
+                    continue
+                sl = [None] * base.ndim
+                for k, a in enumerate(axes):
+                    sl[a] = int(idx[row, k])
+                piece = upd[row]
+                for j, a in enumerate(rest):
+                    sl[a] = slice(0, piece.shape[j])
+                if op == "indexed_add":
+                    with np.errstate(all="ignore"):
+                        work[tuple(sl)] = _store(work[tuple(sl)] + piece.astype(work.dtype), t, mode).astype(work.dtype)
+                else:
+                    work[tuple(sl)] = piece
+            v = _store(work, t, mode) if op == "indexed_add" else work
         elif op == "concatenate":
             v = np.concatenate([convert(a, ta, t, mode) for a, ta in zip(arg, at)], axis=nd.ints[0])
         else:

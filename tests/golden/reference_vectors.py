@@ -308,3 +308,41 @@ case("argsort ties are stable", "nx/lib/nx.ex argsort stable: true", lambda t: n
      [([[1, 3, 3, 1], [2, 2, 5, 2]], "s32")], [([[1, 2, 0, 3], [2, 0, 1, 3]], "s32")])
 case("top_k", "nx/lib/nx.ex top_k doctest", lambda t: nx.top_k(t, k=2), [([[1, 5, 3], [9, 2, 7]], "s32")],
      [([[5, 3], [9, 7]], "s32"), ([[1, 2], [0, 2]], "s32")])
+
+# ---- indexed_add / indexed_put: exla/test/exla/defn/expr_test.exs:1776-1920, nx/lib/nx.ex:8166-8440 ----
+_Z234 = [[[0] * 4 for _ in range(3)] for _ in range(2)]
+case("indexed_add multi-dim", "exla/test/exla/defn/expr_test.exs:1781-1822", lambda t, i, u: nx.indexed_add(t, i, u),
+     [(_Z234, "s32"), ([[0, 0, 0], [0, 0, 1], [0, 0, 0], [0, 1, 1], [1, 2, 2], [1, 2, 3], [1, 0, 3]], "s32"), ([1, 1, -1, 2, -1, 3, 4], "s32")],
+     [([[[0, 1, 0, 0], [0, 2, 0, 0], [0, 0, 0, 0]], [[0, 0, 0, 4], [0, 0, 0, 0], [0, 0, -1, 3]]], "s32")])
+case("indexed_add s32 + s32", "exla/test/exla/defn/expr_test.exs:1825-1829", lambda t, i, u: nx.indexed_add(t, i, u),
+     [([0], "s32"), ([[0]], "s32"), ([1], "s32")], [([1], "s32")])
+case("indexed_add s32 + f32", "exla/test/exla/defn/expr_test.exs:1831-1835", lambda t, i, u: nx.indexed_add(t, i, u),
+     [([0], "s32"), ([[0]], "s32"), ([1.0], "f32")], [([1.0], "f32")])
+case("indexed_add f32 + s32", "exla/test/exla/defn/expr_test.exs:1837-1841", lambda t, i, u: nx.indexed_add(t, i, u),
+     [([0.0], "f32"), ([[0]], "s32"), ([1], "s32")], [([1.0], "f32")])
+case("indexed_add f64 + f32", "exla/test/exla/defn/expr_test.exs:1843-1847", lambda t, i, u: nx.indexed_add(t, i, u),
+     [([0.0], "f64"), ([[0]], "s32"), ([1.0], "f32")], [([1.0], "f64")])
+case("indexed_add repeated index accumulates", "nx/lib/nx.ex:8214-8218", lambda t, i, u: nx.indexed_add(t, i, u),
+     [([1.0], "f32"), ([[0], [0]], "s32"), ([1, 1], "s32")], [([3.0], "f32")])
+case("indexed_add s32 + s64", "nx/lib/nx.ex:8226-8230", lambda t, i, u: nx.indexed_add(t, i, u),
+     [([1], "s32"), ([[0], [0]], "s32"), ([1, 1], "s64")], [([3], "s64")])
+case("indexed_add rank-1 index, scalar update", "nx/lib/nx.ex:8182-8189", lambda t, i: nx.indexed_add(t, i, 8),
+     [([[1], [2]], "s32"), ([1, 0], "s32")], [([[1], [10]], "s32")])
+case("indexed_add iota {1,2,3}", "nx/lib/nx.ex:8193-8212", lambda t, i, u: nx.indexed_add(t, i, u),
+     [([[[0, 1, 2], [3, 4, 5]]], "s32"), ([[0, 0, 0], [0, 1, 1], [0, 0, 0], [0, 0, 2], [0, 1, 2]], "s32"), ([1, 3, 1, -2, 5], "s32")],
+     [([[[2, 1, 0], [3, 7, 10]]], "s32")])
+case("indexed_put multi-dim", "exla/test/exla/defn/expr_test.exs:1859-1896", lambda t, i, u: nx.indexed_put(t, i, u),
+     [(_Z234, "s32"), ([[0, 0, 1], [0, 0, 0], [0, 1, 1], [1, 2, 2], [1, 2, 3], [1, 0, 3]], "s32"), ([1, -1, 2, -1, 3, 4], "s32")],
+     [([[[-1, 1, 0, 0], [0, 2, 0, 0], [0, 0, 0, 0]], [[0, 0, 0, 4], [0, 0, 0, 0], [0, 0, -1, 3]]], "s32")])
+case("indexed_put s32 <- f32", "exla/test/exla/defn/expr_test.exs:1905-1909", lambda t, i, u: nx.indexed_put(t, i, u),
+     [([0], "s32"), ([[0]], "s32"), ([1.0], "f32")], [([1.0], "f32")])
+case("indexed_put f64 <- f32", "exla/test/exla/defn/expr_test.exs:1917-1921", lambda t, i, u: nx.indexed_put(t, i, u),
+     [([0.0], "f64"), ([[0]], "s32"), ([1.0], "f32")], [([1.0], "f64")])
+case("indexed_put rows on a given dimension", "nx/lib/nx.ex:8348-8370", lambda t, i, u: nx.indexed_put(t, i, u),
+     [([[[0, 1], [2, 3], [4, 5]]], "s32"), ([[0, 0], [0, 2]], "s32"), ([[0, 10], [40, 50]], "s32")],
+     [([[[0, 10], [2, 3], [40, 50]]], "s32")])
+case("indexed_put axes [0, 2]", "nx/lib/nx.ex:8376-8404", lambda t, i, u: nx.indexed_put(t, i, u, axes=[0, 2]),
+     [([[[0, 1, 2], [3, 4, 5]]], "s32"), ([[0, 0], [0, 2]], "s32"), ([[0, 30], [20, 50]], "s32")],
+     [([[[0, 1, 20], [30, 4, 50]]], "s32")])
+case("indexed_put rank-1 index, scalar update", "nx/lib/nx.ex:8306-8313", lambda t, i: nx.indexed_put(t, i, 10),
+     [([[1], [2]], "s32"), ([1, 0], "s32")], [([[1], [10]], "s32")])

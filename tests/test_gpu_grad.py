@@ -83,3 +83,85 @@ def test_training_loop_with_donated_parameters_learns():
         losses.append(float(nx.to_number(loss)))
     assert losses[0] > 2.0 and losses[-1] < 0.25 * losses[0], losses
     assert all(b <= a * 1.05 for a, b in zip(losses, losses[1:])), losses
+
+
+def test_scatter_matches_the_oracle_with_repeated_positions():
+    """indexed_add / indexed_put at sizes where many updates land on the same element: integer sums are
+    exact whatever the order of the atomic adds; float sums agree up to their rounding order."""
+    rng = np.random.default_rng(5)
+    n, rows, cols = 20000, 300, 64
+    idx = np.stack([rng.integers(0, rows, n), rng.integers(0, cols, n)], axis=1).astype(np.int32)
+    idx[:50, 0] = rows + 5                                            # outside the target: dropped
+    idx[50:60, 1] = -1
+    for type, tol in (("s32", None), ("f32", 1e-5), ("s8", None), ("u16", None), ("s64", None), ("bf16", None)):
+        kind = np.float32 if type in ("f32", "bf16") else np.int64
+        target = rng.integers(-3, 4, (rows, cols)).astype(kind)
+        upd = rng.integers(-2, 3, n).astype(kind)                      # small integers: exact in every type
+        if type == "u16":
+            target, upd = np.abs(target), np.abs(upd)
+        if type == "f32":
+            upd = upd + rng.normal(0, 0.1, n).astype(np.float32)
+        fun = lambda t, i, u: nx.indexed_add(t, i, u)
+        args = [(target, type), (idx, "s32"), (upd, type)]
+        backend.set_default_backend(None)
+        hargs = [nx.tensor(a, t) for a, t in args]
+        backend.set_default_backend("b200", 0)
+        blob, _ = defn.build_program(fun, hargs)
+        (want, _, _), = O.run_program(blob, [h.data.raw for h in hargs], "xla_like")
+        got = nx.to_numpy(defn.jit(fun)(*[backend.backend_transfer(h) for h in hargs]))
+        if tol is None:
+            assert np.array_equal(got, want), f"indexed_add {type}"
+        else:
+            assert_close(got, want, rtol=tol, atol=1e-5, what=f"indexed_add {type}")
+    # rows of a table (one indexed axis), distinct positions so that indexed_put is deterministic
+    table = rng.normal(0, 1, (512, 96)).astype(np.float32)
+    pos = rng.permutation(512)[:100].astype(np.int64).reshape(100, 1)
+    new = rng.normal(0, 1, (100, 96)).astype(np.float32)
+    got = nx.to_numpy(defn.jit(lambda t, i, u: nx.indexed_put(t, i, u))(nx.tensor(table), nx.tensor(pos), nx.tensor(new)))
+    want = table.copy()
+    want[pos[:, 0]] = new
+    assert np.array_equal(got, want)
+
+
+def test_embedding_table_learns():
+    """A lookup table trained by gradient descent: the gradient of `take` is a scatter-add into the table
+    (nx/lib/nx/defn/grad.ex:970-988).  Checked against the oracle's evaluation of the same gradient graph
+    and by the loss going down."""
+    rng = np.random.default_rng(9)
+    vocab, dim, n, classes = 50, 16, 400, 5
+    ids = rng.integers(0, vocab, n).astype(np.int32)
+    labels = (ids * 7 + 3) % classes                                  # a function of the id: learnable by the table alone
+    y = np.eye(classes, dtype=np.float32)[labels]
+    table = rng.normal(0, 0.1, (vocab, dim)).astype(np.float32)
+    w = rng.normal(0, 0.3, (dim, classes)).astype(np.float32)
+
+    def loss(table, w, ids, y):
+        h = nx.take(table, ids, axis=0)
+        logits = nx.dot(nx.tanh(h), w)
+        logp = logits - nx.logsumexp(logits, axes=[1], keep_axes=True)
+        return nx.negate(nx.mean(nx.sum(logp * y, axes=[1])))
+
+    step = lambda table, w, ids, y: defn.value_and_grad(lambda tw: loss(tw[0], tw[1], ids, y))((table, w))
+    backend.set_default_backend(None)
+    hargs = [nx.tensor(table), nx.tensor(w), nx.tensor(ids), nx.tensor(y)]
+    backend.set_default_backend("b200", 0)
+    blob, _ = defn.build_program(step, hargs)
+    ref = O.run_program(blob, [h.data.raw for h in hargs], "xla_like")
+    dev = [backend.backend_transfer(h) for h in hargs]
+    l0, (g_table, g_w) = defn.jit(step)(*dev)
+    assert_close(nx.to_numpy(l0), ref[0][0], rtol=1e-5, atol=1e-6, what="loss")
+    assert_close(nx.to_numpy(g_table), ref[1][0], rtol=1e-4, atol=1e-6, what="d loss / d table")
+    assert_close(nx.to_numpy(g_w), ref[2][0], rtol=1e-4, atol=1e-6, what="d loss / d w")
+    unused = np.setdiff1d(np.arange(vocab), ids)
+    assert np.all(nx.to_numpy(g_table)[unused] == 0)                  # rows never looked up get no gradient
+
+    def sgd(table, w, ids, y):
+        l, (gt, gw) = step(table, w, ids, y)
+        return table - 2.0 * gt, w - 2.0 * gw, l
+    train = defn.jit(sgd)
+    t, ww = dev[0], dev[1]
+    losses = []
+    for _ in range(60):
+        t, ww, l = train(nx.donatable(t), nx.donatable(ww), dev[2], dev[3])
+        losses.append(float(nx.to_number(l)))
+    assert losses[-1] < 0.5 * losses[0], losses

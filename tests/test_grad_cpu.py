@@ -236,8 +236,8 @@ def test_grad_of_grad():
 
 
 def test_unsupported_op_raises():
-    with pytest.raises(NotImplementedError, match="gradient of :sort"):
-        run(grad(lambda t: nx.sum(nx.sort(t, axis=0))), [[3.0, 1.0, 2.0]])
+    with pytest.raises(NotImplementedError, match="gradient of :window_max"):
+        run(grad(lambda t: nx.sum(nx.window_max(t, (2,)))), [[3.0, 1.0, 2.0]])
 
 
 def test_stored_row_maximum_is_not_reloaded_by_its_own_kernel():
@@ -257,3 +257,70 @@ def test_stored_row_maximum_is_not_reloaded_by_its_own_kernel():
     stored = [tok.split("(")[1].split(" ")[0] for tok in body.split("st1<float>")[1:]]
     for p in stored:
         assert f"ld1<float>({p} " not in body and f">({p} +" not in body.replace("st1<float>(" + p, ""), body
+
+
+# ---- lookups and scatters (grad.ex:761-795, :962-988) -------------------------------------------------
+
+def test_gather_take_and_embedding_lookup():
+    table = np.arange(12.0).reshape(4, 3) / 7.0
+    ids = np.array([2, 0, 2, 3])
+    w = np.linspace(-1, 1, 12).reshape(4, 3)
+
+    def loss(table):
+        return nx.sum(nx.take(table, nx.tensor(ids, "s32"), axis=0) * nx.tensor(w, "f64"))
+
+    got = run(grad(loss), [table])[0]
+    want = np.zeros_like(table)
+    np.add.at(want, ids, w)                                             # repeated ids accumulate
+    assert_close(got, want, 1e-12, 0, "gradient of an embedding lookup")
+    check(loss, [table])
+    # general gather over two axes, and take_along_axis
+    idx = np.array([[0, 1], [3, 2], [3, 2], [1, 0]])
+    check(lambda t: nx.sum(nx.pow(nx.gather(nx.reshape(t, (4, 3, 1)), nx.tensor(idx, "s32"), axes=[0, 1]), 2)), [table])
+    along = np.array([[2, 0], [1, 1], [0, 2], [2, 2]])
+    check(lambda t: nx.sum(nx.sin(nx.take_along_axis(t, nx.tensor(along, "s32"), axis=1))), [table])
+
+
+def test_put_slice_and_dynamic_slice():
+    x = np.arange(20.0).reshape(4, 5) / 9.0
+    piece = np.array([[1.5, -2.0], [0.5, 3.0]])
+    f = lambda x, p: nx.sum(nx.pow(nx.put_slice(x, [1, 2], p), 2) * nx.tensor(np.arange(20.0).reshape(4, 5), "f64"))
+    check(f, [x, piece], wrt=0)
+    check(f, [x, piece], wrt=1)
+    # a slice whose start is a tensor: the gradient is put back at that position
+    start = nx.tensor(2, "s32")
+    g = lambda x: nx.sum(nx.pow(nx.slice(x, [start, 1], [2, 3]), 3))
+    check(g, [x])
+    g2 = lambda x: nx.sum(nx.exp(nx.slice(x, [nx.tensor(0, "s32"), nx.tensor(0, "s32")], [3, 5], [2, 2])))
+    check(g2, [x])
+
+
+def test_indexed_add_and_put():
+    target = np.arange(12.0).reshape(3, 4) / 5.0
+    idx = np.array([[0, 1], [2, 3], [0, 1], [1, 0]])
+    upd = np.array([0.5, -1.0, 2.0, 0.25])
+    w = np.arange(12.0).reshape(3, 4)
+    f = lambda t, u: nx.sum(nx.pow(nx.indexed_add(t, nx.tensor(idx, "s32"), u), 2) * nx.tensor(w, "f64"))
+    check(f, [target, upd], wrt=0)
+    check(f, [target, upd], wrt=1)
+    # indexed_put (distinct positions): the target loses the gradient where it was overwritten
+    idx2 = np.array([[0, 1], [2, 3], [1, 0]])
+    h = lambda t, u: nx.sum(nx.pow(nx.indexed_put(t, nx.tensor(idx2, "s32"), u), 2) * nx.tensor(w, "f64"))
+    check(h, [target, upd[:3]], wrt=0)
+    check(h, [target, upd[:3]], wrt=1)
+    # rows on one axis
+    rows = np.array([[2], [0]])
+    k = lambda t, u: nx.sum(nx.sin(nx.indexed_add(t, nx.tensor(rows, "s32"), u)))
+    check(k, [target, np.ones((2, 4)) * 0.3], wrt=1)
+
+
+def test_sort_gradient_follows_the_permutation():
+    x = np.array([[0.3, -1.0, 2.0, 0.1], [5.0, 4.0, -3.0, 0.0]])
+    w = np.array([1.0, 10.0, 100.0, 1000.0])
+    f = lambda t: nx.sum(nx.sort(t, axis=1) * nx.tensor(w, "f64"))
+    got = run(grad(f), [x])[0]
+    want = np.zeros_like(x)
+    for r in range(2):
+        want[r, np.argsort(x[r])] = w
+    assert_close(got, want, 0, 0, "gradient of sort")
+    check(lambda t: nx.sum(nx.pow(nx.sort(t, axis=0, direction="desc"), 2) * nx.tensor(np.arange(8.0).reshape(2, 4), "f64")), [x])
