@@ -1644,10 +1644,31 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     for (auto& al : g.aliases) {
       const int o = g.outputs[al.second];
       Node& nd = g.nodes[o];
-      if (nd.op != "put_slice" || uses[o] != 1) continue;
+      if (nd.op != "put_slice") continue;
       const int p = nd.args[0];
-      if (g.nodes[p].op != "parameter" || g.nodes[p].ints.at(0) != al.first || uses[p] != 1 || g.nodes[p].dt != nd.dt) continue;
+      if (g.nodes[p].op != "parameter" || g.nodes[p].ints.at(0) != al.first || g.nodes[p].dt != nd.dt) continue;
       const int piece = nd.args[1];
+      // Readers of the result are fine (they run after the window was written, on the same memory).
+      // The argument itself may only be read by this put_slice and by slices of exactly the window
+      // it writes (same start operands, the piece's shape, unit strides): the kernel that writes a
+      // window element then reads the old value of that very element, before it stores.
+      {
+        int others = 0;
+        const size_t r = nd.shape.size();
+        for (size_t u = 0; u < g.nodes.size(); ++u) {
+          const Node& un = g.nodes[u];
+          const int reads = (int)std::count(un.args.begin(), un.args.end(), p);
+          if (!reads) continue;
+          if ((int)u == o && reads == 1) continue;
+          bool window_read = un.op == "slice" && reads == 1 && un.args.size() == 1 + r && un.args[0] == p && un.shape == g.nodes[piece].shape &&
+                             un.ints.size() == 3 * r;
+          for (size_t j = 0; window_read && j < r; ++j)
+            if (un.args[1 + j] != nd.args[2 + j] || un.ints[2 * r + j] != 1) window_read = false;
+          if (!window_read) ++others;
+        }
+        if (std::count(g.outputs.begin(), g.outputs.end(), p)) ++others;
+        if (others) continue;
+      }
       Node w;
       w.op = g.nodes[piece].dt == nd.dt ? "copy" : "as_type";
       w.dt = nd.dt;

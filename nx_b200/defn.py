@@ -19,6 +19,7 @@ traced graph is built into a native program once per key.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import threading
 import time
 
@@ -321,12 +322,82 @@ def _make_runner(outs, params, aliases=None, hooks=None):
                 continue
             k = g.n_state
             state, caps = list(ins[:k]), list(ins[k:])
-            while nx.to_number(cond(state + caps, device)[0]):
-                state = list(body(state + caps, device))
+            ahead = _look_ahead_step(g)
+            if ahead is None:
+                while nx.to_number(cond(state + caps, device)[0]):
+                    loop_stats["iterations"] += 1
+                    loop_stats["host_syncs"] += 1
+                    state = list(body(state + caps, device))
+                loop_stats["host_syncs"] += 1
+            else:
+                # The loop stays on the device for LOOK_AHEAD iterations at a time: every step computes
+                # the condition on the state it receives and keeps that state when it is false, so
+                # steps queued past the end of the loop change nothing, and only the last step's
+                # predicate is read back.  The state buffers are donated from step to step.
+                while True:
+                    for _ in range(LOOK_AHEAD):
+                        out = ahead.run([nx.donatable(t) for t in state] + caps, device)
+                        state, pred = list(out[:k]), out[k]
+                    loop_stats["iterations"] += LOOK_AHEAD
+                    loop_stats["host_syncs"] += 1
+                    if not nx.to_number(pred):
+                        break
             vals += state
         return final(vals, device)
     run_segments.program = None
     return run_segments
+
+
+# How many iterations of a `while` are queued before the host looks at the condition again, and what
+# the loops of this process have cost so far (read by tests and diagnostics).
+_eager_loops = {}
+LOOK_AHEAD = max(1, int(os.environ.get("NXB200_WHILE_AHEAD", "8")))
+loop_stats = {"iterations": 0, "host_syncs": 0}
+
+
+def _look_ahead_step(g):
+    """The program ``(state ++ captures) -> (next state ++ [condition])`` of a while group in which
+    the next state is the body's result where the condition holds and the unchanged state where it
+    does not.  The reference lowers a loop into the executable, one dispatch per loop
+    (exla/lib/exla/defn.ex:670-723); here the host queues several of these steps per look at the
+    condition.  None when the loop has host effects that must follow the real iteration count (taps,
+    host calls, nested loops): those keep the iteration-by-iteration path."""
+    if hasattr(g, "ahead"):
+        return g.ahead
+    from . import nx
+    g.ahead = None
+    k = g.n_state
+    if any(t.data.op in ("io_call", "while", "runtime_call") for t in E.topo_order(g.cond_outs + g.body_outs)[0]):
+        return None
+    with B.trace_scope():
+        pred = g.cond_outs[0]
+        # A window update of a state element (a KV cache written by put_slice) is guarded at the window:
+        # the slice written is the new piece where the condition holds and the old content where it
+        # does not.  The guarded tensor also replaces the updated one inside the body (what the body
+        # computes from it is discarded anyway when the condition is false), so that one tensor per
+        # cache exists and the donated buffer is updated in place, a window at a time.
+        position = {t.data.id: n for n, t in enumerate(E.topo_order(g.body_outs)[0])}
+        repl, outs = {}, [None] * k
+        for i in sorted(range(k), key=lambda i: position.get(g.body_outs[i].data.id, -1)):
+            old, new = g.sub_params[i], E.substitute([g.body_outs[i]], repl)[0]
+            e = new.data
+            if e.id == old.data.id:
+                outs[i] = new                                             # passed through unchanged
+            elif e.op == "put_slice" and e.args[0].data.id == old.data.id and new.type == old.type:
+                piece, starts = e.args[1], list(e.args[2:])
+                kept = nx.slice(old, starts, list(piece.shape))
+                outs[i] = nx.put_slice(old, starts, nx.select(pred, piece, nx.as_type(kept, piece.type)))
+                repl[g.body_outs[i].data.id] = outs[i]
+            else:
+                outs[i] = nx.select(pred, new, old)
+        outs.append(nx.not_equal(pred, 0))
+    outs = [B.to_expr(o) for o in outs]
+    try:
+        pairs = alias_pairs(list(range(k)), g.sub_params, outs)
+    except ValueError:
+        pairs = None                                                     # a state element nothing reads: no donation
+    g.ahead = Program(E.serialize(outs, g.sub_params, pairs))
+    return g.ahead
 
 
 def alias_pairs(donated, params, outs):
@@ -438,6 +509,13 @@ def while_loop(cond_fun, body_fun, init, max_iterations=None, **opts):
         return _traced_while(cond_fun, body_fun, state)
     state = tuple(_map_tensors(nx.tensor, s) for s in state)
     want = _signature(state)
+    if max_iterations is None:
+        # the same loop as a traced one: its steps are queued several at a time (see _look_ahead_step)
+        key = (cond_fun, body_fun, tuple(sorted(opts.items())))
+        loop = _eager_loops.get(key)
+        if loop is None:
+            loop = _eager_loops.setdefault(key, jit(lambda *st: while_loop(cond_fun, body_fun, st), **opts))
+        return tuple(loop(*state))
     cond_c, body_c = jit(cond_fun, **opts), jit(body_fun, **opts)
     n = 0
     while True:
@@ -461,7 +539,7 @@ class _WhileGroup:
     """What a traced ``while`` carries to the compiler: its inputs in the enclosing graph (initial
     state, then the enclosing values its functions captured), the condition and body graphs over
     parameters ``state ++ captures``, and its result nodes."""
-    __slots__ = ("inputs", "cond_outs", "body_outs", "sub_params", "n_state", "results")
+    __slots__ = ("inputs", "cond_outs", "body_outs", "sub_params", "n_state", "results", "ahead")
 
 
 def _traced_while(cond_fun, body_fun, state):

@@ -113,3 +113,45 @@ def test_compilation_telemetry_fires_once_per_cache_miss():
         assert first.program.build_times()["codegen_time"] == m["codegen_time"]
     finally:
         defn.detach_telemetry(handler)
+
+
+def test_loop_step_program_guards_the_state_and_updates_a_cache_window_in_place():
+    """A `while` whose body writes one row of a cache per iteration (put_slice at a computed position):
+    the step program the host queues several times per look at the condition keeps the state when the
+    condition is false, and writes the donated cache in place, a window at a time."""
+    import numpy as np
+    import nx_oracle as O
+    from nx_b200 import nx
+    T_, H = 12, 8
+    w = np.linspace(-1, 1, H).astype(np.float32)
+
+    def step(toks, pos, cache):
+        tok = nx.slice(toks, [pos], [1])
+        k = nx.as_type(nx.broadcast(tok, (1, H)), "f32") * nx.tensor(w) + 0.5
+        cache = nx.put_slice(cache, [pos, 0], k)
+        nxt = nx.as_type(nx.argmax(nx.dot(k, [1], cache, [1]), axis=1), "s32") + 1
+        return nx.put_slice(toks, [pos + 1], nxt), pos + 1, cache
+
+    tm = [defn.template((T_,), "s32"), defn.template((), "s32"), defn.template((T_, H), "f32")]
+    outs, _, _ = defn._trace(lambda t, p, c: defn.while_loop(lambda t, p, c: nx.less(p, T_ - 1), step, (t, p, c)), tm)
+    prog = defn._look_ahead_step(outs[0].data.payload)
+    plan = prog.describe()
+    assert "argument 2 -> result 2 (written in place)" in plan, plan
+    assert "space={1,8}" in plan and "space={12,8}" not in plan, plan        # the cache is never copied
+    # semantics, with the oracle as the executor: steps queued past the end of the loop change nothing
+    toks, pos, cache = np.array([3] + [0] * (T_ - 1), np.int32), np.array(0, np.int32), np.zeros((T_, H), np.float32)
+    rt, rp, rk = toks.copy(), 0, cache.copy()
+    while rp < T_ - 1:
+        k = rt[rp].astype(np.float32) * w + 0.5
+        rk[rp] = k
+        rt[rp + 1] = int(np.argmax(rk @ k)) + 1
+        rp += 1
+    state, looks = [toks, pos, cache], 0
+    while True:
+        for _ in range(8):
+            res = O.run_program(prog.blob, [x.tobytes() for x in state])
+            state, pred = [r[0] for r in res[:3]], res[3][0]
+        looks += 1
+        if not pred:
+            break
+    assert looks == 2 and np.array_equal(state[0], rt) and int(state[1]) == rp and np.allclose(state[2], rk)

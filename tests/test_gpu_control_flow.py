@@ -127,8 +127,12 @@ def test_greedy_decode_loop_over_a_kv_cache():
 
     init = (nx.tensor(np.array([7] + [0] * (T - 1), np.int32)), nx.tensor(0), nx.tensor(np.zeros((T, H), np.float32)),
             nx.tensor(np.zeros((T, H), np.float32)))
+    before = dict(defn.loop_stats)
     toks, pos, kcache, vcache = defn.while_loop(lambda t, p, k, v: nx.less(p, T - 1), step, init)
     assert nx.to_number(pos) == T - 1
+    # the loop runs on the device several tokens at a time: fewer than one look at the condition per 8 tokens
+    syncs = defn.loop_stats["host_syncs"] - before["host_syncs"]
+    assert syncs <= (T - 1 + 7) // 8, (syncs, T)
     assert np.array_equal(nx.to_numpy(toks), tokens)
     np.testing.assert_allclose(nx.to_numpy(kcache), kc, rtol=1e-4, atol=1e-5)
     np.testing.assert_allclose(nx.to_numpy(vcache), vc, rtol=1e-4, atol=1e-5)
