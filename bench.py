@@ -451,6 +451,14 @@ def decoder_section(timer, device, rank, world, dist, torch):
         b_local = batch // (mesh.shape[dp_axis] if dp_axis is not None else 1)
         peer = sharding.init_tensor_parallel_group(mesh, tp_axis, rank, device, ex, gather=sharding.torch_gather(),
                                                    peer_elems=b_local * seq * 4096)
+        # the collective alone: the sum over the group of one {b_local, seq, 4096} bf16 activation, which each
+        # of the block's two row-parallel products needs (NCCL on the compute stream, device-timed)
+        msg = nx.tensor(np.zeros((b_local, seq, 4096), np.float32), "bf16")
+        for _ in range(2):
+            nif.check(lib.nxb200_comm_all_reduce_sum(msg.data.handle))
+        dist.barrier()
+        ar_ms = sync_max(timer.time(lambda: nif.check(lib.nxb200_comm_all_reduce_sum(msg.data.handle)), 5, warmup=1))
+        B.backend_deallocate(msg)
         xs = {0: [dp_axis]} if dp_axis is not None else {}
         col, row = {1: [tp_axis]}, {0: [tp_axis]}
         tp = [xs, col, col, col, row, col, col, row, {}, {}]
@@ -464,6 +472,11 @@ def decoder_section(timer, device, rank, world, dist, torch):
         run_sharded(mesh, tp, label, **kw)
         fused = (sharding.fused_all_reduce_launches() - before) // 8 if peer else 0      # 1 + 2 + 5 runs
         out[label]["all_reduce"] = f"{fused} of 2 fused into their products over peer memory, the rest NCCL"
+        nbytes_msg = b_local * seq * 4096 * 2
+        n_tp = mesh.shape[tp_axis]
+        out[label]["all_reduce_alone"] = {"ms": round(ar_ms, 3), "message_bytes": nbytes_msg, "ranks": n_tp,
+                                          "bus_gbs": round(nbytes_msg * 2 * (n_tp - 1) / n_tp / ar_ms / 1e6, 1),
+                                          "note": "two of these per block; NCCL all-reduce timed alone on the same group"}
         if fused and label in parity:
             # the fused kernel reduces every tile once, in rank order, on its owner: the copies must agree bit for bit
             parity[label]["ok"] = parity[label]["ok"] and parity[label]["bit_identical_across_group"]

@@ -67,6 +67,17 @@ int nxb200_device_count(int *count);
  * host memory may be reused. */
 int nxb200_buffer_from_host(int device, nxb200_dtype dtype, const int64_t *dims, int rank,
                             const void *src, size_t nbytes, nxb200_buffer **out);
+/* The same without waiting: the call returns as soon as the upload is queued.  A thread of the library
+ * copies the source through pinned staging buffers (the caller's memory need not be pinned: an Erlang
+ * binary is not) and calls `on_done(ctx)`, from that thread, once the last byte of `src` has been read;
+ * until then `src` must stay alive and unchanged.  This is the reference's zero-copy upload with its
+ * completion callback (exla/c_src/exla/exla_client.cc:118-151: the binary is held in a private
+ * environment until the transfer is done).  The tensor may be used at once: its first use waits until
+ * the copies are queued and orders the device's work after them.  `on_done` may be NULL. */
+typedef void (*nxb200_upload_done)(void *ctx);
+int nxb200_buffer_from_host_async(int device, nxb200_dtype dtype, const int64_t *dims, int rank,
+                                  const void *src, size_t nbytes, nxb200_upload_done on_done,
+                                  void *ctx, nxb200_buffer **out);
 /* Uninitialised device tensor (used for outputs and by benchmarks). */
 int nxb200_buffer_alloc(int device, nxb200_dtype dtype, const int64_t *dims, int rank,
                         nxb200_buffer **out);

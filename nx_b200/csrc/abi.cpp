@@ -33,6 +33,7 @@ template <typename F> int guarded(F&& f) {
 nxb200_buffer* check_buffer(nxb200_buffer* b, bool need_live = true) {
   if (!b || b->magic != 0x4e584242) fail(NXB_ERR_INVALID_ARGUMENT, "not a buffer handle");
   if (need_live && b->deallocated.load()) fail(NXB_ERR_RUNTIME, "buffer has been deallocated (use after free)");
+  if (b->upload) upload_join(b);       // an asynchronous upload: from here on the compute stream is ordered after it
   return b;
 }
 
@@ -439,6 +440,29 @@ int nxb200_buffer_from_host(int dev, nxb200_dtype dtype, const int64_t* dims, in
   });
 }
 
+int nxb200_buffer_from_host_async(int dev, nxb200_dtype dtype, const int64_t* dims, int rank, const void* src, size_t nbytes,
+                                  nxb200_upload_done on_done, void* ctx, nxb200_buffer** out) {
+  return guarded([&] {
+    if (!out) fail(NXB_ERR_INVALID_ARGUMENT, "out is NULL");
+    Device& d = nxb::device(dev);
+    nxb200_buffer* b = make_buffer(d, dtype, dims, rank);
+    if (nbytes != b->nbytes || (nbytes && !src)) {
+      size_t want = b->nbytes;
+      { std::lock_guard<std::mutex> g(d.mu); d.alloc.free(b->ptr); }
+      delete b;
+      fail(NXB_ERR_INVALID_ARGUMENT, "binary has " + std::to_string(nbytes) + " bytes, tensor needs " + std::to_string(want));
+    }
+    try {
+      upload_enqueue(d, b, src, nbytes, on_done, ctx);
+    } catch (...) {
+      { std::lock_guard<std::mutex> g(d.mu); d.alloc.free(b->ptr); }
+      delete b;
+      throw;
+    }
+    *out = b;
+  });
+}
+
 int nxb200_buffer_to_host(nxb200_buffer* buf, void* dst, size_t nbytes) {
   return guarded([&] {
     nxb200_buffer* b = check_buffer(buf);
@@ -611,6 +635,7 @@ int nxb200_buffer_deallocate(nxb200_buffer* buf) {
     nxb200_buffer* b = check_buffer(buf, false);
     bool was = b->deallocated.exchange(true);
     if (was) fail(NXB_ERR_ALREADY_DEALLOCATED, "buffer was already deallocated");
+    if (b->upload) upload_join(b);
     Device& d = nxb::device(b->device);
     std::lock_guard<std::mutex> g(d.mu);
     order_after_downloads(d);      // whoever gets this memory next writes it on the compute stream
@@ -634,6 +659,7 @@ int nxb200_buffer_is_deallocated(nxb200_buffer* buf, int* flag) {
 int nxb200_buffer_release(nxb200_buffer* buf) {
   return guarded([&] {
     nxb200_buffer* b = check_buffer(buf, false);
+    if (b->upload) upload_join(b);
     if (!b->deallocated.exchange(true) && b->ptr) {
       Device& d = nxb::device(b->device);
       std::lock_guard<std::mutex> g(d.mu);

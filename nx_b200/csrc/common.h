@@ -17,6 +17,8 @@
 
 #include "../../include/nxb200.h"
 
+struct nxb200_buffer;
+
 namespace nxb {
 
 struct Error : std::exception {
@@ -121,6 +123,11 @@ void check_device_status(Device& d);   // throws NXB_ERR_TIMEOUT if a kernel rep
 int device_count();
 Device& device(int id);       // makes the device current on the calling thread
 
+// Asynchronous upload from pageable host memory through a pinned staging ring (uploader.cpp).
+typedef void (*UploadDone)(void* ctx);
+void upload_enqueue(Device& d, nxb200_buffer* b, const void* src, size_t nbytes, UploadDone on_done, void* ctx);
+void upload_join(nxb200_buffer* b);     // no-op unless an upload is pending; afterwards the compute stream is ordered after it
+
 }  // namespace nxb
 
 // Handle types behind the opaque pointers of the C ABI.
@@ -136,4 +143,9 @@ struct nxb200_buffer {
   // process's allocation mapped through CUDA IPC (`ipc_base` is then what has to be unmapped).
   bool borrowed = false;
   void* ipc_base = nullptr;
+  // An upload in progress (nxb200_buffer_from_host_async): the copies are enqueued by the device's
+  // uploader thread; `ready` is recorded after the last one.  The first use of the buffer waits (on the
+  // host) until they are enqueued and makes the compute stream wait for `ready`.
+  struct Upload;
+  std::shared_ptr<Upload> upload;
 };

@@ -46,6 +46,9 @@ def lib():
     return _LIB
 
 
+UPLOAD_DONE = C.CFUNCTYPE(None, C.c_void_p)      # void (*nxb200_upload_done)(void *ctx)
+
+
 def _declare(l):
     vp, i32, sz = C.c_void_p, C.c_int, C.c_size_t
     p = C.POINTER
@@ -56,6 +59,7 @@ def _declare(l):
         "nxb200_device_count": [p(i32)],
         "nxb200_buffer_from_host": [i32, i32, p(C.c_int64), i32, vp, sz, p(vp)],
         "nxb200_buffer_alloc": [i32, i32, p(C.c_int64), i32, p(vp)],
+        "nxb200_buffer_from_host_async": [i32, i32, p(C.c_int64), i32, vp, sz, UPLOAD_DONE, vp, p(vp)],
         "nxb200_buffer_to_host": [vp, vp, sz],
         "nxb200_buffer_write_async": [vp, vp, sz],
         "nxb200_buffer_read_async": [vp, vp, sz],

@@ -155,3 +155,42 @@ def test_released_memory_is_not_reused_under_a_download_in_flight():
     nif.check(lib.nxb200_device_synchronize(0))
     assert np.array_equal(pinned.numpy(), src)
     backend.backend_deallocate(other)
+
+
+def test_asynchronous_upload_from_pageable_memory():
+    """nxb200_buffer_from_host_async: the call returns at once, the library's uploader thread streams the
+    (unpinned) source through its staging buffers and calls back when it has read the last byte; the
+    tensor can be used immediately, the device's work is ordered after the copies
+    (exla/c_src/exla/exla_client.cc:118-151)."""
+    import threading
+    from nx_b200 import types as T
+    from nx_b200.nx import Tensor
+    lib = nif.lib()
+    n = 24 << 20                                                      # 96 MiB of f32: two dozen staging chunks
+    src = np.arange(n, dtype=np.float32)
+    done, seen = threading.Event(), []
+
+    def on_done(ctx):
+        seen.append(ctx)
+        done.set()
+    cb = nif.UPLOAD_DONE(on_done)
+    h = C.c_void_p()
+    nif.check(lib.nxb200_buffer_from_host_async(0, 10, nif.dims_array((n,)), 1, src.ctypes.data, src.nbytes, cb, 1234, C.byref(h)))
+    t = Tensor(backend.DeviceBuffer(h.value, 0), T.F32, (n,))
+    y = t * 2.0 + 1.0                                                 # queued behind the upload, no explicit wait
+    assert done.wait(30), "the completion callback never fired"
+    assert seen == [1234]
+    assert np.array_equal(nx.to_numpy(y), src * 2.0 + 1.0)
+    assert np.array_equal(nx.to_numpy(t), src)
+    # several uploads in flight, released without ever being read
+    hs = []
+    small = np.ones(1 << 20, np.float32)
+    for _ in range(4):
+        h2 = C.c_void_p()
+        nif.check(lib.nxb200_buffer_from_host_async(0, 10, nif.dims_array((1 << 20,)), 1, small.ctypes.data, small.nbytes, nif.UPLOAD_DONE(0), None, C.byref(h2)))
+        hs.append(h2)
+    for h2 in hs:
+        nif.check(lib.nxb200_buffer_release(h2))
+    # a binary of the wrong size is refused before anything is queued
+    bad = C.c_void_p()
+    assert lib.nxb200_buffer_from_host_async(0, 10, nif.dims_array((8,)), 1, src.ctypes.data, 16, cb, None, C.byref(bad)) == nif.ERR_INVALID
