@@ -193,7 +193,7 @@ void run_program(nxb200_program* p, int device, nxb200_buffer* const* args, int 
         for (size_t a = 0; a < ks.arg_slots.size(); ++a) ep[a] = ptr[ks.arg_slots[a]];
         TcLaunch tl;
         attn_prepare_launch(ptr[as.q_slot], ptr[as.k_slot], ptr[as.v_slot], ptr[as.out_slot], as.batch_heads, as.sq, as.sk, as.causal, ep.data(),
-                            (int)ep.size(), d.status_dev, &tl);
+                            (int)ep.size(), d.status_dev, &tl, as.heads, as.v_bshd, as.out_bshd);
         void* params[4] = {tl.map_a, tl.map_b, tl.map_c, tl.params};
         check_cu(drv.cuLaunchKernel(L.functions[as.jit_kernel], tl.grid, 1, 1, 320, 1, 1, (unsigned)tl.smem, (CUstream)d.stream, params, nullptr),
                  ("launching " + ks.name).c_str());

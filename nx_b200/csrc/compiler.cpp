@@ -1820,15 +1820,16 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     plan_dot(*plan, n, need, &gs);
     for (int m : need) P.mat[m] = 1;
   }
-  // a reshape / squeeze / metadata chain over a parameter or literal is that buffer under another
-  // shape: nothing to compute (results still get memory of their own)
+  // a reshape / squeeze / metadata chain over a parameter, a literal or a value that is a buffer anyway
+  // (a product, an attention, ...) is that buffer under another shape: nothing to compute (results
+  // still get memory of their own)
   {
     std::set<int> outs(g.outputs.begin(), g.outputs.end());
     for (int n = 0; n < N; ++n) {
       if (!g.nodes[n].live || !P.mat[n] || outs.count(n)) continue;
       int a = n;
       while ((g.nodes[a].op == "reshape" || g.nodes[a].op == "squeeze" || g.nodes[a].op == "metadata") && !g.nodes[a].args.empty()) a = g.nodes[a].args[0];
-      if (a != n && (g.nodes[a].op == "parameter" || g.nodes[a].op == "tensor")) P.mat[n] = 0;
+      if (a != n && (g.nodes[a].op == "parameter" || g.nodes[a].op == "tensor" || P.mat[a])) P.mat[n] = 0;
     }
   }
   // contiguous reshapes / metadata over materialised values share the buffer
@@ -2214,9 +2215,13 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           as.sk = nd.ints[4];
           as.causal = (int)nd.ints[2];
           as.batch_heads = shape_numel(nd.shape) / (as.sq * 128);
+          as.heads = nd.ints.size() > 5 ? nd.ints[5] : 1;
+          as.v_bshd = nd.ints.size() > 6 && nd.ints[6] != 0;
+          as.out_bshd = nd.ints.size() > 7 && nd.ints[7] != 0;
           std::ostringstream d;
           d << "attention#" << u.gemm_node << " fused QK^T -> transform(" << g.nodes[xnode].op << "#" << xnode << ") -> softmax -> PV, batch*heads=" << as.batch_heads
-            << " Sq=" << as.sq << " Sk=" << as.sk << " head_dim=128 bf16" << (as.causal ? " causal (key blocks above the diagonal skipped)" : "") << " (" << kname << ")";
+            << " Sq=" << as.sq << " Sk=" << as.sk << " head_dim=128 bf16" << (as.causal ? " causal (key blocks above the diagonal skipped)" : "")
+            << (as.v_bshd ? " v read as {batch,key,head,dim}" : "") << (as.out_bshd ? " result written as {batch,row,head,dim}" : "") << " (" << kname << ")";
           as.desc = d.str();
           ks.desc = as.desc;
           pl.kernels.push_back(std::move(ks));

@@ -50,10 +50,13 @@ void tc_prepare_launch(const GemmArgs& g, int bn, void* const* ep, int n_ep, int
 const char* gemm_device_source();
 const char* attention_device_source();
 int attn_smem_bytes();
-// Launch block of a generated attention kernel: tensor maps of q, k, v ([batch*heads][S][128] bf16)
-// and its parameter block.
+// Launch block of a generated attention kernel: tensor maps of q, k ([batch*heads][S][128] bf16) and v,
+// and its parameter block.  `heads` splits batch_heads into (batch, head); `v_bshd`: v is stored
+// {batch, key, head, 128} (a projection's own layout) instead of {batch, head, key, 128}; `out_bshd`: the
+// result is written as {batch, row, head, 128}, which is what the projection after it reads.
 void attn_prepare_launch(const void* q, const void* k, const void* v, void* out, int64_t batch_heads, int64_t sq, int64_t sk, int causal,
-                         void* const* ep, int n_ep, int* status_word, TcLaunch* outl);
+                         void* const* ep, int n_ep, int* status_word, TcLaunch* outl, int64_t heads = 1, bool v_bshd = false,
+                         bool out_bshd = false);
 // Peer memory of the tensor-parallel group (comm.cpp): one region per rank, mapped into every
 // process, holding [partial product][reduced tiles][ready flags][reduced flags].
 struct PeerView {

@@ -240,10 +240,33 @@ void rewrite_attention(Graph& g) {
     A.shape = D2.shape;
     A.args = {q, k, v};
     for (int ex : extras) A.args.push_back(ex);
-    A.ints = {x, d1, causal, Sq, Sk};
+    // {batch, head, rows, 128}: the head transposes around the attention are folded into its addressing.
+    // v = transpose({batch, key, head, 128}, [0,2,1,3]) is read in place through a four-dimensional tensor
+    // map; a result whose only reader is transpose(., [0,2,1,3]) is written in that order directly.
+    const std::vector<int64_t> swap12{0, 2, 1, 3};
+    int64_t heads = 1, v_bshd = 0;
+    int vsrc = v;
+    if (r == 4) {
+      heads = D2.shape[1];
+      const Node& V = g.nodes[v];
+      if (V.op == "transpose" && V.ints == swap12 && g.nodes[V.args[0]].dt == NXB_BF16) { vsrc = V.args[0]; v_bshd = 1; }
+    }
+    A.args[2] = vsrc;
+    A.ints = {x, d1, causal, Sq, Sk, heads, v_bshd, 0};
     g.nodes[n] = A;
     // the product that computed the scores is no longer part of the program
     for (int a : g.nodes[d1].args) uses[a]--;
+    if (r == 4 && uses[n] == 1) {
+      for (size_t t = n + 1; t < N; ++t) {
+        Node& T = g.nodes[t];
+        if (T.op != "transpose" || T.args.size() != 1 || T.args[0] != (int)n || T.ints != swap12) continue;
+        Node B = g.nodes[n];
+        B.shape = T.shape;
+        B.ints[7] = 1;
+        g.nodes[t] = B;                  // the transpose IS the attention now; node n is dead
+        break;
+      }
+    }
   }
 }
 

@@ -317,20 +317,40 @@ struct AttnParamsHost {
   void* ep[14];
 };
 
-int attn_smem_bytes() { return 128 * 128 * 2 * 6 + 1024 + 256 + 3072; }
+int attn_smem_bytes() { return 128 * 128 * 2 * 7 + 1024 + 256; }      // Q x 2, K x 2, V, P x 2 (attn_sm100_device.cuh)
+
+// V as (head dim, key, head, batch) with the strides of either layout: boxes of 64 dims x 128 keys
+static CUtensorMap make_map_v4(const void* ptr, int64_t sk, int64_t heads, int64_t batch, bool bshd) {
+  const DriverApi& drv = driver();
+  if (!drv.cuTensorMapEncodeTiled) fail(NXB_ERR_RUNTIME, "cuTensorMapEncodeTiled is unavailable");
+  CUtensorMap m;
+  const cuuint64_t row = 128 * 2;
+  cuuint64_t dims[4] = {128, (cuuint64_t)sk, (cuuint64_t)heads, (cuuint64_t)batch};
+  // {batch, head, key, dim}: key rows are adjacent; {batch, key, head, dim}: the heads of one key are adjacent
+  cuuint64_t strides[3] = {bshd ? row * (cuuint64_t)heads : row, bshd ? row : row * (cuuint64_t)sk, row * (cuuint64_t)sk * (cuuint64_t)heads};
+  cuuint32_t box[4] = {64, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  check_cu(drv.cuTensorMapEncodeTiled(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+           "cuTensorMapEncodeTiled (values)");
+  return m;
+}
 
 void attn_prepare_launch(const void* q, const void* k, const void* v, void* out, int64_t batch_heads, int64_t sq, int64_t sk, int causal,
-                         void* const* ep, int n_ep, int* status_word, TcLaunch* outl) {
+                         void* const* ep, int n_ep, int* status_word, TcLaunch* outl, int64_t heads, bool v_bshd, bool out_bshd) {
   static_assert(sizeof(AttnParamsHost) <= sizeof(outl->params), "launch block too small");
+  if (heads < 1 || batch_heads % heads != 0) fail(NXB_ERR_RUNTIME, "internal: attention head count does not divide batch * heads");
+  const int64_t batch = batch_heads / heads;
   CUtensorMap mq = make_map(q, NXB_BF16, 128, sq, batch_heads, 128, sq * 128, 128);
   CUtensorMap mk = make_map(k, NXB_BF16, 128, sk, batch_heads, 128, sk * 128, 128);
-  CUtensorMap mv = make_map(v, NXB_BF16, 128, sk, batch_heads, 128, sk * 128, 128);
+  CUtensorMap mv = make_map_v4(v, sk, heads, batch, v_bshd);
   AttnParamsHost p{};
   p.out = out;
-  p.heads = 1;
-  p.out_bh_hi = sq * 128;
-  p.out_bh_lo = 0;
-  p.out_row = 128;
+  p.heads = (int)heads;
+  // address of output row (b, h, i) in elements: b * hi + h * lo + i * out_row
+  if (out_bshd) { p.out_bh_hi = sq * heads * 128; p.out_bh_lo = 128; p.out_row = heads * 128; }
+  else { p.out_bh_hi = heads * sq * 128; p.out_bh_lo = sq * 128; p.out_row = 128; }
   p.status = status_word;
   p.batch_heads = (int)batch_heads;
   p.sq = (int)sq;
@@ -342,7 +362,7 @@ void attn_prepare_launch(const void* q, const void* k, const void* v, void* out,
   memcpy(outl->map_b, &mk, 128);
   memcpy(outl->map_c, &mv, 128);
   memcpy(outl->params, &p, sizeof p);
-  outl->grid = (unsigned)(batch_heads * ((sq + 127) / 128));
+  outl->grid = (unsigned)(batch_heads * (((sq + 127) / 128 + 1) / 2));      // two blocks of 128 query rows per CTA
   outl->smem = attn_smem_bytes();
 }
 

@@ -105,8 +105,17 @@ std::string compile_to_cubin(const std::string& source, const std::string& name,
   if (nvrtcCreateProgram(&prog, full.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS)
     fail(NXB_ERR_RUNTIME, "nvrtcCreateProgram failed");
   const char* opts[] = {"-arch=sm_100a", "-std=c++17", "-lineinfo", "--use_fast_math=false", "-default-device"};
-  const char* use[] = {opts[0], opts[1], opts[2]};
-  nvrtcResult r = nvrtcCompileProgram(prog, 3, use);
+  // NXB200_PTXAS_INFO=1: registers, spills and shared memory of every generated kernel on stderr
+  static const bool ptxas_info = getenv("NXB200_PTXAS_INFO") != nullptr;
+  const char* use[] = {opts[0], opts[1], opts[2], "--ptxas-options=-v"};
+  nvrtcResult r = nvrtcCompileProgram(prog, ptxas_info ? 4 : 3, use);
+  if (ptxas_info && r == NVRTC_SUCCESS) {
+    size_t n = 0;
+    nvrtcGetProgramLogSize(prog, &n);
+    std::string log(n, '\0');
+    nvrtcGetProgramLog(prog, &log[0]);
+    fprintf(stderr, "[nxb200] %s:\n%s\n", name.c_str(), log.c_str());
+  }
   if (r != NVRTC_SUCCESS) {
     size_t n = 0;
     nvrtcGetProgramLogSize(prog, &n);

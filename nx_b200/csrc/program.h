@@ -94,6 +94,8 @@ struct AttentionSpec {
   int q_slot = -1, k_slot = -1, v_slot = -1, out_slot = -1;
   int64_t batch_heads = 1, sq = 0, sk = 0;
   int causal = 0;
+  int64_t heads = 1;                      // size of the axis before the rows (1: one leading axis)
+  bool v_bshd = false, out_bshd = false;  // v read / result written as {batch, row, head, 128}
   int jit_kernel = -1;
   std::string desc;
 };

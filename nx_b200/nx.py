@@ -905,7 +905,52 @@ def concatenate(tensors, axis=0):
     shape = list(tensors[0].shape)
     shape[a] = _b.sum(t.shape[a] for t in tensors)
     out = _out(type, shape)
+    if _rearranges_one_source(tensors):
+        return _concatenate_by_selection(tensors, a, type, shape)
     return _dispatch(lambda *ts: E.node(out, "concatenate", list(ts), ints=[a]), tensors)
+
+
+_POINTWISE_VIEWS = set(E.UNARY_MATH) | set(E.UNARY_OTHER) | {"as_type", "slice"}
+
+
+def _rearranges_one_source(tensors):
+    """True inside a traced function when every piece is a static slice of the same tensor, possibly under
+    pointwise functions (the rotate-half of a rotary embedding: ``concatenate([-x2, x1])``).  Such a
+    concatenation is an index selection on one source: it is traced as selects over padded pieces, which
+    the compiler generates inside the consumer's kernel, instead of a node of its own whose pieces are
+    written to memory first.  (Pieces that are whole tensors stay a concatenate node: its result is a
+    buffer, which is what a small table repeated and then broadcast over a large consumer should be.)"""
+    from . import backend
+    if not backend.tracing() or len(tensors) > 4 or not _b.all(_is_expr(t) for t in tensors):
+        return False
+    roots = set()
+    for t in tensors:
+        e, sliced = t.data, False
+        while e.op in _POINTWISE_VIEWS and len(e.args) == 1:
+            sliced = sliced or e.op == "slice"
+            e = e.args[0].data
+        if e.op == "constant" or not sliced:
+            return False
+        roots.add(e.id)
+    return len(roots) == 1
+
+
+def _concatenate_by_selection(tensors, a, type, shape):
+    position = iota(shape, axis=a)
+    total, offsets, off = shape[a], [], 0
+    for t in tensors:
+        offsets.append(off)
+        off += t.shape[a]
+    padded = []
+    for t, o in zip(tensors, offsets):
+        t = as_type(t, type) if t.type != type else t
+        cfg = [(0, 0, 0)] * len(shape)
+        cfg[a] = (o, total - o - t.shape[a], 0)
+        padded.append(pad(t, 0, cfg))
+    acc = padded[-1]
+    for k in range(len(tensors) - 2, -1, -1):
+        acc = select(less(position, offsets[k + 1]), padded[k], acc)
+    return acc
 
 
 def iota(shape, axis=None, type=T.S32):

@@ -139,8 +139,10 @@ class _Part:
         if op == "parameter":
             spec = param_specs[e.ints[0]]
             return E.parameter(gt.type, self.local(gshape, spec), e.ints[0]), spec
-        if op in ("constant", "tensor", "iota"):
+        if op in ("constant", "tensor"):
             return gt, rep
+        if op == "iota":
+            return gt, rep            # replicated; a consumer that is split takes its slice of it
         if op == "metadata":
             return args[0]
 
@@ -248,6 +250,14 @@ class _Part:
                         raise ShardingError("slice along a split dimension")
                     ln[d] = t.shape[d]
             return self.node(gt.type, self.local(gshape, s), op, [t], st + ln + sd), s
+        if op == "pad":
+            # padding along dimensions that are not split; the split ones pass through unchanged
+            (t, s), (pv, _) = args
+            r = len(s)
+            lo, hi, it = e.ints[:r], e.ints[r:2 * r], e.ints[2 * r:3 * r]
+            if any(s[d] is not None and (lo[d] or hi[d] or it[d]) for d in range(r)):
+                raise ShardingError("pad along a split dimension")
+            return self.node(gt.type, self.local(gshape, s), op, [t, pv], e.ints), s
         if op == "concatenate":
             ax = e.ints[0]
             spec = [None] * rank
