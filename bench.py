@@ -361,6 +361,12 @@ def other_configs(timer, device, pk, torch):
     return res
 
 
+def progress(rank, what):
+    """One line per phase on stderr (rank 0): a run that stalls shows where."""
+    if rank == 0:
+        print(f"[bench {time.strftime('%H:%M:%S')}] {what}", file=sys.stderr, flush=True)
+
+
 def decoder_section(timer, device, rank, world, dist, torch):
     """Decoder block tokens/s: single GPU, batch data-parallel, tensor-parallel and {dp, tp} meshes.
     At N > 1 every sharded result is compared with the single-GPU program's result on this rank's GPU."""
@@ -422,19 +428,24 @@ def decoder_section(timer, device, rank, world, dist, torch):
                 step = a.shape[dim] // n
                 a = np.take(a, range(c * step, (c + 1) * step), axis=dim)
             return np.ascontiguousarray(a)
+        progress(rank, f"decoder {label}: partition + build")
         local = [(shard(a, sh), t) for (a, t), sh in zip(inputs, shardings)]
         blob, _, _ = sharding.partition(block, mesh, shardings, [defn.template(a.shape, t) for a, t in local], rank)
         prog = defn.Program(blob)
         dev = device_inputs(local)
         if dist is not None:
             dist.barrier()          # every rank has built its program: kernels that wait on peers are bounded
+        progress(rank, f"decoder {label}: first run")
         outs = prog.run(dev, device)
+        nif.check(lib.nxb200_device_synchronize(device))
         if dist is not None:
             dist.barrier()
+        progress(rank, f"decoder {label}: timing")
         ms = sync_max(timer.time(lambda: prog.run_into(dev, outs, device), 5, warmup=2))
         out[label] = {"ms_per_step": round(ms, 3), "tokens_per_s": round(batch * seq / ms * 1e3),
                       "tflops": round(438.4e6 * batch * seq / ms / 1e9, 1), "launches_per_step": prog.launch_count()}
         if check and dist is not None:
+            progress(rank, f"decoder {label}: parity against the single-GPU program")
             coords = mesh.coords(rank)
             if batch_axis is None:
                 sl, grp = slice(0, batch), "all"
@@ -447,6 +458,7 @@ def decoder_section(timer, device, rank, world, dist, torch):
             B.backend_deallocate(t_)
 
     def tensor_parallel(mesh, tp_axis, dp_axis, label, also_nccl):
+        progress(rank, f"decoder {label}: communicator + peer memory")
         ex = sharding.torch_exchange()
         b_local = batch // (mesh.shape[dp_axis] if dp_axis is not None else 1)
         peer = sharding.init_tensor_parallel_group(mesh, tp_axis, rank, device, ex, gather=sharding.torch_gather(),
@@ -480,6 +492,7 @@ def decoder_section(timer, device, rank, world, dist, torch):
         if fused and label in parity:
             # the fused kernel reduces every tile once, in rank order, on its owner: the copies must agree bit for bit
             parity[label]["ok"] = parity[label]["ok"] and parity[label]["bit_identical_across_group"]
+        progress(rank, f"decoder {label}: releasing the communicator")
         nif.check(lib.nxb200_device_synchronize(device))
         dist.barrier()
         nif.check(lib.nxb200_comm_destroy())
@@ -564,6 +577,7 @@ def main():
                           "tflops": round(2 * 64 * 2048 * 2048 * 128 / ms_ / 1e9, 1), "plan": prog_.describe().strip().split("\n")}))
         return
     rows = args.rows
+    progress(rank, "headline: inputs + build")
     x_host = configs.fused_rows_input(rows, COLS, SEED)
     x = nx.tensor(x_host)
     prog = defn.compile(configs.fused_rows, [defn.template((rows, COLS), "f32")], device=local).program
@@ -597,6 +611,7 @@ def main():
     per_gpu = nbytes / (ms.value / args.steps * 1e-3) / 1e9
 
     # ---- end to end: host buffers in, host buffers out, through the same public call ----
+    progress(rank, "headline: timed; end to end")
     e2e = None
     if not args.no_e2e:
         pin_in = torch.empty(x_host.nbytes, dtype=torch.uint8, pin_memory=True)
@@ -676,6 +691,7 @@ def main():
         if decoder is not None:
             line["decoder"] = decoder
         if not args.no_configs and world == 1 and rows == ROWS:
+            progress(rank, "other configurations")
             line["configs"] = other_configs(timer, local, pk, torch)
         if not args.no_cpu and world == 1:
             line["cpu_baseline"] = cpu_baseline(x_host)

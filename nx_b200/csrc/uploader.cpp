@@ -50,12 +50,15 @@ struct Uploader {
   int next = 0;
 };
 
+// The uploaders live until the process ends and are never destroyed: their threads are detached and
+// wait on the condition variables inside, and destroying a condition variable that has a waiter blocks
+// (a process that had uploaded anything would hang at exit in the static destructors).
 Uploader& uploader(int dev) {
-  static std::mutex mu;
-  static std::map<int, std::unique_ptr<Uploader>> all;
-  std::lock_guard<std::mutex> g(mu);
-  auto& u = all[dev];
-  if (!u) u = std::make_unique<Uploader>();
+  static std::mutex* mu = new std::mutex;
+  static std::map<int, Uploader*>* all = new std::map<int, Uploader*>;
+  std::lock_guard<std::mutex> g(*mu);
+  Uploader*& u = (*all)[dev];
+  if (!u) u = new Uploader;
   return *u;
 }
 
