@@ -7,15 +7,21 @@
 // the other block's softmax runs, and every K / V block is fetched once per 256 query rows:
 //   warp 0      TMA producer: both Q tiles once, then K_j into a two-stage ring and V_j into a
 //               single buffer (V_j is needed late in step j and released at its end)
-//   warp 1      MMA issuer, per key block j and query tile t:  S_t(j+1) = Q_t K_{j+1}^T into the
-//               tile's score accumulator as soon as the softmax has taken S_t(j) into registers,
-//               then PV_t(j) = P_t V_j into the tile's output accumulator (P from shared memory,
-//               V with its head-dim index contiguous, i.e. an MN-major B operand)
+//   warp 1      MMA issuer, per key block j and query tile t, back to back:  S_t(j+1) = Q_t K_{j+1}^T
+//               into the tile's score accumulator as soon as the softmax has read S_t(j), then
+//               PV_t(j) = P_t V_j into the tile's output accumulator (P from shared memory, V with its
+//               head-dim index contiguous, i.e. an MN-major B operand)
 //   warps 2..5  softmax of tile 0, warps 6..9 of tile 1: one thread per query row (a row is one
-//               TMEM lane, so maxima and sums need no exchange between threads): running maximum m
-//               and running sum l; the output row O accumulates in TMEM across key blocks and is read
-//               back and rescaled only when the maximum moves by more than a threshold (rare after
-//               the first blocks)
+//               TMEM lane, so maxima and sums need no exchange between threads).  The row's 128
+//               scores are read from tensor memory twice, 32 at a time with the next 32 in flight:
+//               once for the maximum, once for the probabilities (no spills, rolled loops, a small
+//               instruction footprint).  Running maximum m and running sum l; the output row O
+//               accumulates in TMEM across key blocks and is read back and rescaled only when the
+//               maximum moves by more than a threshold (rare after the first blocks).
+// Three forms of the score transform are compiled in: the full one; with a proven causal mask
+// X = select(row >= col, Y, -inf), Y alone for key blocks entirely below the diagonal; and when
+// Y = c * scores with a positive constant c, a form that takes maxima of the raw scores (3-input max)
+// and folds c into the exponent's multiply-add, two scores per instruction (f32x2).
 // Tensor memory: S_0, S_1, O_0, O_1, 128 columns each.  Keys beyond a causal diagonal are skipped
 // block-wise when the planner proved the mask is causal (the two tiles then differ by one key
 // block; the tile of the later rows is tile 0).  Every mbarrier wait is bounded; on expiry the CTA
@@ -42,6 +48,160 @@ constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int TILE = 128 * 128 * 2;                 // one 128 x 128 bf16 tile = two 16 KB halves
 constexpr int ATTN_SMEM = 2 * TILE /*Q x 2*/ + 2 * TILE /*K x 2 stages*/ + TILE /*V*/ + 2 * TILE /*P x 2*/ + 1024 + 256;
 
+// 32 consecutive columns of one TMEM lane per thread, without waiting for them ...
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+// ... and the wait.  The registers are passed through it so that no use of them is scheduled before it.
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+        "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]),
+        "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
+        "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+      :: "memory");
+}
+
+// One score after the generated transform.  MODE 0: the variant of the transform without its causal
+// mask (the caller knows the mask holds), 1: the transform, 2: the transform, and keys >= sk give -inf.
+template <class Xform, int MODE>
+__device__ __forceinline__ float score_of(uint32_t raw, long long bh, long long qi, long long kj, const AttnParams& p) {
+  if (MODE == 0) return Xform::plain(__uint_as_float(raw), bh, qi, kj, p.ep);
+  float x = Xform::apply(__uint_as_float(raw), bh, qi, kj, p.ep);
+  if (MODE == 2) x = (kj < p.sk) ? x : -NXB_INF;
+  return x;
+}
+
+// Maximum of the 128 transformed scores of this thread's row.  On entry the load of columns 0..31
+// into `xa` is in flight; on exit the same load has been started again (for row_probs).  While one
+// block of 32 is worked on the next one is on its way.  The loops over blocks stay rolled (two blocks
+// per trip, for the two buffers): unrolled, the softmax of one key block is about 18 KB of straight-line
+// code per warp, and the warps then wait for instruction fetch more than for anything else.
+template <class Xform, int MODE>
+__device__ __forceinline__ void max32(float (&mxs)[4], const uint32_t (&x)[32], int bh, long long qi, long long kj, const AttnParams& p) {
+  if constexpr (MODE == 3) {
+    // raw scores (the transform is a multiplication by a positive constant, applied to the maximum later)
+#if NXB_NVRTC_VERSION >= 1209
+    // three-input max: PTX ISA 8.8
+#pragma unroll
+    for (int e = 0; e < 32; e += 2)
+      asm("max.NaN.f32 %0, %0, %1, %2;" : "+f"(mxs[(e >> 1) & 3]) : "f"(__uint_as_float(x[e])), "f"(__uint_as_float(x[e + 1])));
+#else
+#pragma unroll
+    for (int e = 0; e < 32; ++e) mxs[e & 3] = nx_max(mxs[e & 3], __uint_as_float(x[e]));
+#endif
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) mxs[e & 3] = nx_max(mxs[e & 3], score_of<Xform, MODE>(x[e], bh, qi, kj + e, p));
+  }
+}
+template <class Xform, int MODE>
+__device__ __forceinline__ float row_max(uint32_t tS, uint32_t (&xa)[32], uint32_t (&xc)[32], int bh, long long qi, long long kj0, const AttnParams& p) {
+  float mxs[4] = {-NXB_INF, -NXB_INF, -NXB_INF, -NXB_INF};
+#pragma unroll 1
+  for (int cc = 0; cc < 2; ++cc) {
+    tmem_ld_wait(xa);
+    tmem_ld32_issue(tS + (uint32_t)(cc * 64 + 32), xc);
+    max32<Xform, MODE>(mxs, xa, bh, qi, kj0 + cc * 64, p);
+    tmem_ld_wait(xc);
+    tmem_ld32_issue(tS + (uint32_t)((cc * 64 + 64) & 127), xa);
+    max32<Xform, MODE>(mxs, xc, bh, qi, kj0 + cc * 64 + 32, p);
+  }
+  const float mx = nx_max(nx_max(mxs[0], mxs[1]), nx_max(mxs[2], mxs[3]));
+  return MODE == 3 ? mx * Xform::scale() : mx;
+}
+
+// Probabilities ex2(x * log2(e) + off) of 32 scores in bf16 into their place in the row's 128-byte
+// swizzled rows of P (`dst0`: the row's 64-key half; `g0`: first of the four 16-byte groups), and their sums.
+template <class Xform, int MODE>
+__device__ __forceinline__ void probs32(float (&ls)[4], const uint32_t (&x)[32], int bh, long long qi, long long kj, const AttnParams& p,
+                                        float off, uint32_t dst0, uint32_t g0, uint32_t row7) {
+  constexpr float LOG2E = 1.4426950408889634f;
+  if constexpr (MODE == 3) {
+    // ex2(s * (scale * log2 e) + off), two scores per multiply-add and per addition (f32x2)
+    const float c2 = Xform::scale() * LOG2E;
+    unsigned long long cc, oo;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(cc) : "f"(c2));
+    asm("mov.b64 %0, {%1, %1};" : "=l"(oo) : "f"(off));
+    unsigned long long acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) asm("mov.b64 %0, {%1, %2};" : "=l"(acc[u]) : "f"(ls[u]), "f"(0.f));
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      uint32_t pk[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = g * 8 + u * 2;
+        unsigned long long xx, yy;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(xx) : "r"(x[e]), "r"(x[e + 1]));
+        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(yy) : "l"(xx), "l"(cc), "l"(oo));
+        float y0, y1;
+        asm("mov.b64 {%0, %1}, %2;" : "=f"(y0), "=f"(y1) : "l"(yy));
+        const float e0 = nx_exp2(y0), e1 = nx_exp2(y1);
+        unsigned long long ee;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(ee) : "f"(e0), "f"(e1));
+        asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc[u]) : "l"(ee));
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[u]) : "f"(e1), "f"(e0));
+      }
+      const uint32_t dst = dst0 + (((g0 + (uint32_t)g) ^ row7) * 16u);
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float a0, a1;
+      asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc[u]));
+      ls[u] = a0 + a1;
+    }
+    return;
+  }
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    uint32_t pk[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = g * 8 + u * 2;
+      const float e0 = nx_exp2(fmaf(score_of<Xform, MODE>(x[e], bh, qi, kj + e, p), LOG2E, off));
+      const float e1 = nx_exp2(fmaf(score_of<Xform, MODE>(x[e + 1], bh, qi, kj + e + 1, p), LOG2E, off));
+      ls[u] += e0 + e1;
+      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[u]) : "f"(e1), "f"(e0));
+    }
+    const uint32_t dst = dst0 + (((g0 + (uint32_t)g) ^ row7) * 16u);
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
+  }
+}
+// The whole row.  On entry the load of columns 0..31 into `xa` is in flight.  When the last block has
+// arrived the score accumulator is released to the next product (s_empty).
+template <class Xform, int MODE>
+__device__ __forceinline__ float row_probs(uint32_t tS, uint32_t (&xa)[32], uint32_t (&xc)[32], int bh, long long qi, long long kj0, const AttnParams& p,
+                                           float off, uint32_t rowbase, uint32_t row7, uint32_t s_empty) {
+  float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+  for (int cc = 0; cc < 2; ++cc) {
+    const uint32_t dst0 = rowbase + (uint32_t)cc * (uint32_t)(TILE / 2);
+    tmem_ld_wait(xa);
+    tmem_ld32_issue(tS + (uint32_t)(cc * 64 + 32), xc);
+    probs32<Xform, MODE>(ls, xa, bh, qi, kj0 + cc * 64, p, off, dst0, 0u, row7);
+    tmem_ld_wait(xc);
+    if (cc == 0) {
+      tmem_ld32_issue(tS + 64u, xa);
+    } else {
+      tc_fence_before();
+      __syncwarp();
+      if ((threadIdx.x & 31) == 0) mbar_arrive(s_empty);
+    }
+    probs32<Xform, MODE>(ls, xc, bh, qi, kj0 + cc * 64 + 32, p, off, dst0, 4u, row7);
+  }
+  return (ls[0] + ls[1]) + (ls[2] + ls[3]);
+}
+
 template <class Xform>
 __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const AttnParams& p) {
   extern __shared__ unsigned char smem_raw[];
@@ -59,8 +219,11 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
   // pairs of query blocks, heavy (late) pairs first: with a causal mask block i needs i+1 key blocks.
   // Tile 0 is the later block of the pair, tile 1 the one before it (absent for the last pair of an odd count).
   const int nqb = (p.sq + BQ - 1) / BQ, npairs = (nqb + 1) / 2;
-  const int pi = (int)(blockIdx.x % npairs);
-  const int bh = (int)(blockIdx.x / npairs);
+  // The grid runs in block order: the heaviest pair of every (batch, head) first, the lightest last, so
+  // that the last wave is made of short CTAs (measured at {8,32,2048,128}: 0.38 ms against 0.40 with the
+  // pairs of one (batch, head) next to each other, although keys and values are then fetched once per pair).
+  const int pi = (int)(blockIdx.x / (unsigned)p.batch_heads);
+  const int bh = (int)(blockIdx.x % (unsigned)p.batch_heads);
   const int qb0 = nqb - 1 - 2 * pi;
   const int ntiles = qb0 >= 1 ? 2 : 1;
   const int nkv_all = (p.sk + BKV - 1) / BKV;
@@ -152,38 +315,52 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
         for (int t = 0; t < ntiles; ++t) issue_s(t, 0);
         tc_commit(k_empty0);
       }
+      // Per key block the products of one tile are issued back to back as soon as that tile's softmax
+      // lets go: S_t(j+1) when it has read S_t(j), PV_t(j) when it has written P_t(j) (a moment later).
+      // The two tiles run half a step apart, so one tile's products execute under the other's softmax.
+      auto issue_pv = [&](int t, int j) {
+        const uint32_t pt = sP + t * TILE, d = tmem_base + 256u + (uint32_t)(t * 128);
+#pragma unroll
+        for (int k8 = 0; k8 < 8; ++k8) {
+          // A = P: two 64-key halves, 32 bytes per step.  B = V: 8-key groups are 1024 bytes apart
+          // inside a head-dim half (16 KB), the two halves 16 KB apart (leading offset).
+          const uint64_t adesc = make_desc(pt + (k8 >> 2) * (TILE / 2)) + (uint64_t)((k8 & 3) * 2);
+          const uint64_t bdesc = ((uint64_t)(((sV + k8 * 2048) & 0x3FFFF) >> 4)) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+                                 ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+          tc_mma(d, adesc, bdesc, idesc_pv, (j > 0 || k8 > 0) ? 1u : 0u, false);
+        }
+        tc_commit(pv_full0 + 8 * t);
+      };
       for (int j = 0; j < nkv_max && ok; ++j) {
-        if (j + 1 < nkv_max) {
-          const int s = (j + 1) & 1;
-          if (!mbar_wait(k_full0 + 8 * s, (uint32_t)(((j + 1) >> 1) & 1), abort_flag)) { ok = false; break; }
-          for (int t = 0; t < ntiles && ok; ++t) {
-            if (j + 1 >= nkv[t]) continue;
-            // the softmax has taken S_t(j) into registers
+        const bool more = j + 1 < nkv_max;
+        bool k_ready = false, v_ready = false;
+        for (int t = 0; t < ntiles && ok; ++t) {
+          if (j + 1 < nkv[t]) {
+            if (!k_ready) {
+              if (!mbar_wait(k_full0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag)) { ok = false; break; }
+              k_ready = true;
+            }
+            // the softmax has read S_t(j)
             if (!mbar_wait(s_empty0 + 8 * t, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
             tc_fence_after();
             issue_s(t, j + 1);
           }
-          if (!ok) break;
-          tc_commit(k_empty0 + 8 * s);
-        }
-        if (!mbar_wait(v_full, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
-        for (int t = 0; t < ntiles && ok; ++t) {
-          if (j >= nkv[t]) continue;
-          if (!mbar_wait(p_full0 + 8 * t, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t pt = sP + t * TILE, d = tmem_base + 256u + (uint32_t)(t * 128);
-#pragma unroll
-          for (int k8 = 0; k8 < 8; ++k8) {
-            // A = P: two 64-key halves, 32 bytes per step.  B = V: 8-key groups are 1024 bytes apart
-            // inside a head-dim half (16 KB), the two halves 16 KB apart (leading offset).
-            const uint64_t adesc = make_desc(pt + (k8 >> 2) * (TILE / 2)) + (uint64_t)((k8 & 3) * 2);
-            const uint64_t bdesc = ((uint64_t)(((sV + k8 * 2048) & 0x3FFFF) >> 4)) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
-                                   ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-            tc_mma(d, adesc, bdesc, idesc_pv, (j > 0 || k8 > 0) ? 1u : 0u, false);
+          if (j < nkv[t]) {
+            if (!v_ready) {
+              if (!mbar_wait(v_full, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+              v_ready = true;
+            }
+            if (!mbar_wait(p_full0 + 8 * t, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, j);
           }
-          tc_commit(pv_full0 + 8 * t);
         }
         if (!ok) break;
+        if (more) {
+          // the producer loads K_{j+1} whenever there is a block j+1, also when only one tile still uses it
+          if (!k_ready && !mbar_wait(k_full0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag)) { ok = false; break; }
+          tc_commit(k_empty0 + 8 * ((j + 1) & 1));
+        }
         tc_commit(v_empty);
       }
     }
@@ -205,46 +382,39 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
     constexpr float LOG2E = 1.4426950408889634f, RESCALE_STEP = 5.545177444f;
     float m = -NXB_INF, l = 0.f;
     bool ok = true;
+    const long long q_first = (long long)(qb0 - t) * BQ;
     for (int j = 0; j < my_nkv && ok; ++j) {
       // one lane polls on behalf of its warp; the tensor-memory loads below need the whole warp
       if (!mbar_wait_warp_tight(s_full, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
       tc_fence_after();
-      // the 128 scores of this row, as loaded (their bits; read and written as floats below)
-      uint32_t xb[128];
-      tmem_ld32x2(tS, reinterpret_cast<uint32_t (&)[64]>(xb[0]));
-      tmem_ld32x2(tS + 64u, reinterpret_cast<uint32_t (&)[64]>(xb[64]));
-      // the scores are in registers: the accumulator may take the next block's product
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty);
-      float mx = -NXB_INF;
       const long long kj0 = (long long)j * BKV;
-      if (kj0 + BKV <= p.sk) {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          const float xv = Xform::apply(__uint_as_float(xb[c]), (long long)bh, qi, kj0 + c, p.ep);
-          xb[c] = __float_as_uint(xv);
-          mx = nx_max(mx, xv);
-        }
-      } else {
-        // the last key block: columns beyond the keys contribute nothing
-#pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          float xv = Xform::apply(__uint_as_float(xb[c]), (long long)bh, qi, kj0 + c, p.ep);
-          xv = (kj0 + c < p.sk) ? xv : -NXB_INF;
-          xb[c] = __float_as_uint(xv);
-          mx = nx_max(mx, xv);
-        }
-      }
+      // how the scores of this block are read: 0 = the mask is known to hold for every element (a block
+      // entirely below a proven causal diagonal) and all keys exist, 1 = the full transform, all keys
+      // exist, 2 = the full transform and columns beyond the last key contribute nothing, 3 = as 0 when the
+      // unmasked transform is a multiplication by a positive constant (folded into the exponent's multiply-add)
+      const bool unmasked = Xform::kPlainAlways || (Xform::kHasPlain && p.causal && kj0 + BKV - 1 <= q_first);
+      const int mode = (kj0 + BKV > p.sk) ? 2 : !unmasked ? 1 : Xform::kScaleOnly ? 3 : Xform::kHasPlain ? 0 : 1;
+      // A row's 128 scores are read from tensor memory twice, 32 at a time: once for the maximum, once
+      // for the probabilities.  Holding all 128 (plus the packed probabilities) in registers does not
+      // fit beside three warps per scheduler, and spilled scores cost more than the second read.
+      uint32_t xa[32], xc[32];
+      float mx;
+      tmem_ld32_issue(tS, xa);
+      if (mode == 3) mx = row_max<Xform, 3>(tS, xa, xc, bh, qi, kj0, p);
+      else if (mode == 0) mx = row_max<Xform, 0>(tS, xa, xc, bh, qi, kj0, p);
+      else if (mode == 1) mx = row_max<Xform, 1>(tS, xa, xc, bh, qi, kj0, p);
+      else mx = row_max<Xform, 2>(tS, xa, xc, bh, qi, kj0, p);
+      // (the last step of row_max started the load of columns 0..31 again, into xa)
       const float m_seen = nx_max(m, mx);
       const bool move = m_seen > m + RESCALE_STEP || m == -NXB_INF;
       const float m_use = move ? m_seen : m;
       if (j > 0) {
         // PV of the previous block is complete: P's buffer is free, and O may be touched
-        if (!mbar_wait_warp_tight(pv_full, (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp_tight(pv_full, (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; tmem_ld_wait(xa); break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, move && m != -NXB_INF)) {
           const float alpha = (move && m != -NXB_INF) ? nx_exp2(m * LOG2E - m_use * LOG2E) : 1.f;
+          tmem_ld_wait(xa);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             uint32_t ov[32];
@@ -262,19 +432,12 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
       // every x is -inf too, and with a zero offset ex2(-inf) = 0 without a NaN.
       const float off = (m == -NXB_INF) ? 0.f : -m * LOG2E;
       const uint32_t rowbase = sP + (uint32_t)t * TILE + (uint32_t)row * 128u;
-#pragma unroll
-      for (int g = 0; g < 16; ++g) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const float e0 = nx_exp2(fmaf(__uint_as_float(xb[g * 8 + u * 2]), LOG2E, off));
-          const float e1 = nx_exp2(fmaf(__uint_as_float(xb[g * 8 + u * 2 + 1]), LOG2E, off));
-          l += e0 + e1;
-          asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[u]) : "f"(e1), "f"(e0));
-        }
-        const uint32_t dst = rowbase + (uint32_t)(g >> 3) * (TILE / 2) + ((((uint32_t)g & 7u) ^ (uint32_t)(row & 7)) * 16u);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
-      }
+      float ls;
+      if (mode == 3) ls = row_probs<Xform, 3>(tS, xa, xc, bh, qi, kj0, p, off, rowbase, (uint32_t)(row & 7), s_empty);
+      else if (mode == 0) ls = row_probs<Xform, 0>(tS, xa, xc, bh, qi, kj0, p, off, rowbase, (uint32_t)(row & 7), s_empty);
+      else if (mode == 1) ls = row_probs<Xform, 1>(tS, xa, xc, bh, qi, kj0, p, off, rowbase, (uint32_t)(row & 7), s_empty);
+      else ls = row_probs<Xform, 2>(tS, xa, xc, bh, qi, kj0, p, off, rowbase, (uint32_t)(row & 7), s_empty);
+      l += ls;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       __syncwarp();

@@ -2192,8 +2192,56 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
           KernelSpec fx = kx.build(kname + "_xform");
           std::ostringstream o;
           o << fx.source;
-          o << "struct AttnXform {\n  static __device__ __forceinline__ float apply(float s, long long bh, long long qi, long long kj, void* const* ep) { return "
-            << kname << "_xform(s, bh, qi, kj, ep); }\n};\n";
+          // With a proven causal mask  X = select(row >= col, Y, -inf)  the kernel reads Y directly in the
+          // key blocks that lie entirely below the diagonal (same buffers, same order, as the full transform).
+          bool has_plain = false;
+          if (nd.ints[2] && g.nodes[xnode].op == "select" && g.nodes[xnode].args.size() == 3) {
+            KernelBuilder kp(pl, KernelBuilder::EPI, g.nodes[d1].shape, 0, {});
+            kp.acc_node = d1;
+            kp.force_v = 1;
+            kp.ret_node = g.nodes[xnode].args[1];
+            kp.seed_args = fx.arg_slots;
+            KernelSpec fp = kp.build(kname + "_plain");
+            if (fp.arg_slots == fx.arg_slots) { o << fp.source; has_plain = true; }
+          }
+          // The unmasked transform  Y = c * scores  with a positive constant c (the usual 1/sqrt(d)): the kernel
+          // then folds c into the exponent's multiply-add and takes maxima of the raw scores.  Only with
+          // intermediate values kept in f32 (the default); with strict rounding Y is rounded to bf16 first.
+          bool scale_only = false, plain_always = false;
+          float scale_value = 1.f;
+          {
+            const int y = has_plain ? g.nodes[xnode].args[1] : xnode;
+            const Node& Y = g.nodes[y];
+            auto scalar_constant = [&](int n, float* out) {
+              while (g.nodes[n].op == "broadcast" || g.nodes[n].op == "metadata" || g.nodes[n].op == "reshape") n = g.nodes[n].args[0];
+              const Node& c = g.nodes[n];
+              if (c.op != "constant" || c.flts.empty() || !dtype_is_float(c.dt) || c.dt == NXB_F64) return false;
+              float v = (float)c.flts[0];
+              if (c.dt == NXB_BF16) v = to_bf16_rne(v);
+              if (c.dt == NXB_F16) return false;
+              *out = v;
+              return true;
+            };
+            if (getenv("NXB200_STRICT_ROUNDING") == nullptr && Y.op == "multiply" && Y.args.size() == 2 && fx.arg_slots.empty()) {
+              const int other = Y.args[0] == d1 ? Y.args[1] : Y.args[1] == d1 ? Y.args[0] : -1;
+              float c = 0.f;
+              if (other >= 0 && other != d1 && scalar_constant(other, &c) && c > 0.f && c < 1e30f) {
+                scale_only = true;
+                scale_value = c;
+                plain_always = !has_plain && y == xnode;
+              }
+            }
+          }
+          uint32_t scale_bits;
+          memcpy(&scale_bits, &scale_value, 4);
+          o << "struct AttnXform {\n  static constexpr bool kHasPlain = " << (has_plain ? "true" : "false") << ";\n"
+            << "  static constexpr bool kScaleOnly = " << (scale_only ? "true" : "false") << ";\n"
+            << "  static constexpr bool kPlainAlways = " << (plain_always ? "true" : "false") << ";\n"
+            << "  static __device__ __forceinline__ float scale() { return __uint_as_float(0x" << std::hex << scale_bits << std::dec << "u); }\n"
+            << "  static __device__ __forceinline__ float apply(float s, long long bh, long long qi, long long kj, void* const* ep) { return "
+            << kname << "_xform(s, bh, qi, kj, ep); }\n"
+            << "  static __device__ __forceinline__ float plain(float s, long long bh, long long qi, long long kj, void* const* ep) { return "
+            << kname << (has_plain ? "_plain" : "_xform") << "(s, bh, qi, kj, ep); }\n};\n";
           o << "extern \"C\" __global__ void __launch_bounds__(320, 1) " << kname
             << "(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const nxb_attn::AttnParams p) {\n"
             << "  nxb_attn::attn_body<AttnXform>(map_q, map_k, map_v, p);\n}\n";

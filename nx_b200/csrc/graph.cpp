@@ -107,8 +107,18 @@ std::string compile_to_cubin(const std::string& source, const std::string& name,
   const char* opts[] = {"-arch=sm_100a", "-std=c++17", "-lineinfo", "--use_fast_math=false", "-default-device"};
   // NXB200_PTXAS_INFO=1: registers, spills and shared memory of every generated kernel on stderr
   static const bool ptxas_info = getenv("NXB200_PTXAS_INFO") != nullptr;
-  const char* use[] = {opts[0], opts[1], opts[2], "--ptxas-options=-v"};
-  nvrtcResult r = nvrtcCompileProgram(prog, ptxas_info ? 4 : 3, use);
+  // NXB200_KERNEL_DEFINE=NAME[=VALUE]: one preprocessor definition for every generated kernel (diagnostics)
+  static const char* extra_define = getenv("NXB200_KERNEL_DEFINE");
+  static const std::string define_opt = std::string("-D") + (extra_define ? extra_define : "NXB_NO_EXTRA_DEFINE");
+  // The process may have loaded another NVRTC than the one this library was built beside (a Python package
+  // imported earlier can bring its own); kernels test NXB_NVRTC_VERSION before using newer PTX instructions.
+  static const std::string version_opt = [] {
+    int major = 0, minor = 0;
+    nvrtcVersion(&major, &minor);
+    return "-DNXB_NVRTC_VERSION=" + std::to_string(major * 100 + minor);
+  }();
+  const char* use[] = {opts[0], opts[1], opts[2], define_opt.c_str(), version_opt.c_str(), "--ptxas-options=-v"};
+  nvrtcResult r = nvrtcCompileProgram(prog, ptxas_info ? 6 : 5, use);
   if (ptxas_info && r == NVRTC_SUCCESS) {
     size_t n = 0;
     nvrtcGetProgramLogSize(prog, &n);

@@ -102,11 +102,26 @@ class _Part:
         from .nx import Tensor
         return Tensor(E.Expr(op, args, ints, flts), type, tuple(shape))
 
+    def _split_extent(self, extent, axis):
+        n = self.mesh.shape[axis]
+        if extent % n:
+            raise ShardingError(f"dimension of size {extent} is not divisible by mesh axis of size {n}")
+        return extent // n
+
     def reshard_replicated(self, t, gshape, spec_have, spec_want):
         """A value replicated along a dim the consumer has split: take this
         partition's slice (pure index arithmetic, fused into the consumer)."""
         if spec_have == spec_want:
             return t
+        e = t.data
+        if getattr(e, "op", None) == "broadcast":
+            # a dimension the broadcast created holds the same values at every index: broadcast to the
+            # local extent instead of slicing the full one (and a mask stays recognisable as a broadcast)
+            src, axes = e.args[0], list(e.ints[1:])
+            made = lambda d: d not in axes or src.shape[axes.index(d)] == 1
+            if all(h == w or (h is None and made(d)) for d, (h, w) in enumerate(zip(spec_have, spec_want))):
+                shape = [n if h == w else self._split_extent(gshape[d], w) for d, (n, h, w) in enumerate(zip(t.shape, spec_have, spec_want))]
+                return self.node(t.type, shape, "broadcast", [src], e.ints)
         starts, lengths = [], []
         for d, (h, w) in enumerate(zip(spec_have, spec_want)):
             if h == w:

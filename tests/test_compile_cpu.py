@@ -155,3 +155,25 @@ def test_loop_step_program_guards_the_state_and_updates_a_cache_window_in_place(
         if not pred:
             break
     assert looks == 2 and np.array_equal(state[0], rt) and int(state[1]) == rp and np.allclose(state[2], rk)
+
+
+def test_kernels_compile_with_the_runtime_compiler_another_package_loaded_first():
+    """A process that imported torch before this library runs its kernels through torch's copy of the
+    runtime compiler, one CUDA release older than the toolkit's: the generated tensor-core kernels
+    (attention with the scale folded into the exponent among them) must build there too."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (
+        "import torch, sys\n"
+        f"sys.path.insert(0, {root!r})\n"
+        "from nx_b200 import configs, defn\n"
+        "block = configs.make_decoder_block(n_heads=4)\n"
+        "inputs = configs.decoder_inputs(batch=1, seq=256, hidden=512, inter=688)\n"
+        "prog = defn.compile(block, [defn.template(a.shape, t) for a, t in inputs]).program\n"
+        "assert 'attention' in prog.describe()\n"
+        "f_in, _ = configs.quantised_inputs(m=16, n=1024, k=512)\n"
+        "defn.compile(configs.quantised_linear, [defn.template(a.shape, t) for a, t in f_in])\n"
+        "print('built')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "built" in r.stdout, r.stderr[-2000:]

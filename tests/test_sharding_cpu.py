@@ -75,6 +75,30 @@ def test_batch_data_parallel_needs_no_collective():
     np.testing.assert_array_equal(np.concatenate(parts, axis=0), full)
 
 
+def test_partitioned_decoder_keeps_the_causal_attention_kernel():
+    """The mask of a partitioned block must still be recognised as causal (the partition of a broadcast
+    is a broadcast to the local extent, not a slice of the global one): the fused attention then skips
+    the key blocks above the diagonal exactly as the single-device program does."""
+    block = configs.make_decoder_block(n_heads=4)
+    inputs = configs.decoder_inputs(batch=2, seq=256, hidden=512, inter=688)
+    single = defn.compile(block, [defn.template(a.shape, t) for a, t in inputs]).program.describe()
+    assert "causal" in single
+    col, row = {1: [0]}, {0: [0]}
+    cases = {"dp": [{0: [0]}] + [{}] * 9, "tp": [{}, col, col, col, row, col, col, row, {}, {}]}
+    for name, shardings in cases.items():
+        mesh = sharding.Mesh(name, (2,))
+        local = []
+        for (a, t), sh in zip(inputs, shardings):
+            shape = list(a.shape)
+            for dim in sh:
+                shape[dim] //= 2
+            local.append(defn.template(tuple(shape), t))
+        blob, _, _ = sharding.partition(block, mesh, shardings, local, 1)
+        plan = defn.Program(blob).describe()
+        lines = [l for l in plan.split("\n") if "attention" in l]
+        assert len(lines) == 1 and "causal" in lines[0], (name, plan)
+
+
 WORKER = r"""
 import os, sys
 import numpy as np
