@@ -46,7 +46,7 @@ struct AttnParams {
 
 constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int TILE = 128 * 128 * 2;                 // one 128 x 128 bf16 tile = two 16 KB halves
-constexpr int ATTN_SMEM = 2 * TILE /*Q x 2*/ + 2 * TILE /*K x 2 stages*/ + TILE /*V*/ + 2 * TILE /*P x 2*/ + 1024 + 256;
+constexpr int ATTN_SMEM = 2 * TILE /*Q x 2*/ + 2 * TILE /*K x 2 stages*/ + 2 * TILE /*V x 2 stages*/ + 1024 + 256;
 
 // 32 consecutive columns of one TMEM lane per thread, without waiting for them ...
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
@@ -68,6 +68,25 @@ __device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
         "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]), "+r"(r[24]),
         "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
       :: "memory");
+}
+
+// 16 consecutive columns of one TMEM lane per thread, written without waiting for the write
+__device__ __forceinline__ void tmem_st16_issue(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+        "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from tensor memory (row = lane, two 16-bit
+// elements of consecutive k per 32-bit column)
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
 }
 
 // One score after the generated transform.  MODE 0: the variant of the transform without its causal
@@ -119,11 +138,12 @@ __device__ __forceinline__ float row_max(uint32_t tS, uint32_t (&xa)[32], uint32
   return MODE == 3 ? mx * Xform::scale() : mx;
 }
 
-// Probabilities ex2(x * log2(e) + off) of 32 scores in bf16 into their place in the row's 128-byte
-// swizzled rows of P (`dst0`: the row's 64-key half; `g0`: first of the four 16-byte groups), and their sums.
+// Probabilities ex2(x * log2(e) + off) of 32 scores, in bf16 pairs into 16 columns of the row's lane of
+// tensor memory at `tP` (the A operand of P V), and their sums.
 template <class Xform, int MODE>
 __device__ __forceinline__ void probs32(float (&ls)[4], const uint32_t (&x)[32], int bh, long long qi, long long kj, const AttnParams& p,
-                                        float off, uint32_t dst0, uint32_t g0, uint32_t row7) {
+                                        float off, uint32_t tP) {
+  uint32_t pk16[16];
   constexpr float LOG2E = 1.4426950408889634f;
   if constexpr (MODE == 3) {
     // ex2(s * (scale * log2 e) + off), two scores per multiply-add and per addition (f32x2)
@@ -136,7 +156,7 @@ __device__ __forceinline__ void probs32(float (&ls)[4], const uint32_t (&x)[32],
     for (int u = 0; u < 4; ++u) asm("mov.b64 %0, {%1, %2};" : "=l"(acc[u]) : "f"(ls[u]), "f"(0.f));
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      uint32_t pk[4];
+      uint32_t (&pk)[4] = reinterpret_cast<uint32_t (&)[4]>(pk16[g * 4]);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int e = g * 8 + u * 2;
@@ -151,8 +171,6 @@ __device__ __forceinline__ void probs32(float (&ls)[4], const uint32_t (&x)[32],
         asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc[u]) : "l"(ee));
         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[u]) : "f"(e1), "f"(e0));
       }
-      const uint32_t dst = dst0 + (((g0 + (uint32_t)g) ^ row7) * 16u);
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -160,11 +178,12 @@ __device__ __forceinline__ void probs32(float (&ls)[4], const uint32_t (&x)[32],
       asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc[u]));
       ls[u] = a0 + a1;
     }
+    tmem_st16_issue(tP, pk16);
     return;
   }
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
-    uint32_t pk[4];
+    uint32_t (&pk)[4] = reinterpret_cast<uint32_t (&)[4]>(pk16[g * 4]);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int e = g * 8 + u * 2;
@@ -173,32 +192,26 @@ __device__ __forceinline__ void probs32(float (&ls)[4], const uint32_t (&x)[32],
       ls[u] += e0 + e1;
       asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[u]) : "f"(e1), "f"(e0));
     }
-    const uint32_t dst = dst0 + (((g0 + (uint32_t)g) ^ row7) * 16u);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]) : "memory");
   }
+  tmem_st16_issue(tP, pk16);
 }
-// The whole row.  On entry the load of columns 0..31 into `xa` is in flight.  When the last block has
-// arrived the score accumulator is released to the next product (s_empty).
+// The whole row.  On entry the load of columns 0..31 into `xa` is in flight.  P overwrites the first 64
+// columns of the scores it was computed from: the 16 columns of block c lie below the columns of block
+// c + 1, the only ones still to be read when they are written.
 template <class Xform, int MODE>
 __device__ __forceinline__ float row_probs(uint32_t tS, uint32_t (&xa)[32], uint32_t (&xc)[32], int bh, long long qi, long long kj0, const AttnParams& p,
-                                           float off, uint32_t rowbase, uint32_t row7, uint32_t s_empty) {
+                                           float off) {
   float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 1
   for (int cc = 0; cc < 2; ++cc) {
-    const uint32_t dst0 = rowbase + (uint32_t)cc * (uint32_t)(TILE / 2);
     tmem_ld_wait(xa);
     tmem_ld32_issue(tS + (uint32_t)(cc * 64 + 32), xc);
-    probs32<Xform, MODE>(ls, xa, bh, qi, kj0 + cc * 64, p, off, dst0, 0u, row7);
+    probs32<Xform, MODE>(ls, xa, bh, qi, kj0 + cc * 64, p, off, tS + (uint32_t)(cc * 32));
     tmem_ld_wait(xc);
-    if (cc == 0) {
-      tmem_ld32_issue(tS + 64u, xa);
-    } else {
-      tc_fence_before();
-      __syncwarp();
-      if ((threadIdx.x & 31) == 0) mbar_arrive(s_empty);
-    }
-    probs32<Xform, MODE>(ls, xc, bh, qi, kj0 + cc * 64 + 32, p, off, dst0, 4u, row7);
+    if (cc == 0) tmem_ld32_issue(tS + 64u, xa);
+    probs32<Xform, MODE>(ls, xc, bh, qi, kj0 + cc * 64 + 32, p, off, tS + (uint32_t)(cc * 32 + 16));
   }
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
   return (ls[0] + ls[1]) + (ls[2] + ls[3]);
 }
 
@@ -206,11 +219,11 @@ template <class Xform>
 __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const AttnParams& p) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sQ = base, sK = base + 2 * TILE, sV = sK + 2 * TILE, sP = sV + TILE;
-  const uint32_t bars = sP + 2 * TILE;
-  // barriers (8 bytes each): q_full, k_full[2], k_empty[2], v_full, v_empty, then per tile s_full, s_empty, p_full, pv_full
-  const uint32_t q_full = bars, k_full0 = bars + 8, k_empty0 = bars + 24, v_full = bars + 40, v_empty = bars + 48;
-  const uint32_t s_full0 = bars + 56, s_empty0 = bars + 72, p_full0 = bars + 88, pv_full0 = bars + 104, tmem_slot = bars + 120;
+  const uint32_t sQ = base, sK = base + 2 * TILE, sV = sK + 2 * TILE;
+  const uint32_t bars = sV + 2 * TILE;
+  // barriers (8 bytes each): q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], then per tile s_full, p_full, pv_full
+  const uint32_t q_full = bars, k_full0 = bars + 8, k_empty0 = bars + 24, v_full0 = bars + 40, v_empty0 = bars + 56;
+  const uint32_t s_full0 = bars + 72, p_full0 = bars + 88, pv_full0 = bars + 104, tmem_slot = bars + 120;
   unsigned char* gen_base = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + (tmem_slot - base));
   volatile int* abort_flag = (volatile int*)(gen_base + (tmem_slot - base) + 8);
@@ -239,12 +252,12 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1); }
-    mbar_init(v_full, 1);
-    mbar_init(v_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1);
+      mbar_init(v_full0 + 8 * s, 1); mbar_init(v_empty0 + 8 * s, 1);
+    }
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full0 + 8 * t, 1);
-      mbar_init(s_empty0 + 8 * t, 4);
       mbar_init(p_full0 + 8 * t, 4);
       mbar_init(pv_full0 + 8 * t, 1);
     }
@@ -276,23 +289,19 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
         return true;
       };
       auto load_v = [&](int j) {
-        if (!mbar_wait(v_empty, (uint32_t)((j & 1) ^ 1), abort_flag)) return false;
-        mbar_expect_tx(v_full, TILE);
+        const int s = j & 1;
+        if (!mbar_wait(v_empty0 + 8 * s, (uint32_t)(((j >> 1) & 1) ^ 1), abort_flag)) return false;
+        mbar_expect_tx(v_full0 + 8 * s, TILE);
         // V_j: rows are keys, 64 head-dim elements per 128-byte row, one box per head-dim half.  The map
         // of V is four-dimensional (head dim, key, head, batch): V may be stored {batch, key, head, dim},
         // as a projection leaves it, without a transposed copy.
-        tma_load_4d(sV, &map_v, v_full, 0, j * BKV, bh % p.heads, bh / p.heads);
-        tma_load_4d(sV + TILE / 2, &map_v, v_full, 64, j * BKV, bh % p.heads, bh / p.heads);
+        tma_load_4d(sV + s * TILE, &map_v, v_full0 + 8 * s, 0, j * BKV, bh % p.heads, bh / p.heads);
+        tma_load_4d(sV + s * TILE + TILE / 2, &map_v, v_full0 + 8 * s, 64, j * BKV, bh % p.heads, bh / p.heads);
         return true;
       };
-      // K runs two blocks ahead of V: K_{j+1} is wanted early in step j (as soon as the softmax has taken
-      // S(j)), V_j only near its end
-      bool ok = nkv_max > 0 && load_k(0);
-      if (ok && nkv_max > 1) ok = load_k(1);
-      for (int j = 0; j < nkv_max && ok; ++j) {
-        ok = load_v(j);
-        if (ok && j + 2 < nkv_max) ok = load_k(j + 2);
-      }
+      // both rings run one block ahead of the products: K_{j+1} and V_{j+1} are requested during step j
+      bool ok = nkv_max > 0 && load_k(0) && load_v(0);
+      for (int j = 1; j < nkv_max && ok; ++j) ok = load_k(j) && load_v(j);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -315,44 +324,43 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
         for (int t = 0; t < ntiles; ++t) issue_s(t, 0);
         tc_commit(k_empty0);
       }
-      // Per key block the products of one tile are issued back to back as soon as that tile's softmax
-      // lets go: S_t(j+1) when it has read S_t(j), PV_t(j) when it has written P_t(j) (a moment later).
-      // The two tiles run half a step apart, so one tile's products execute under the other's softmax.
+      // Per key block and tile, back to back as soon as the tile's softmax has written P_t(j) over the
+      // scores it came from:  PV_t(j) = P_t V_j  with P read from tensor memory, then  S_t(j+1)  into the
+      // same columns (the tensor pipe executes in issue order, so the product that reads P is done with
+      // it before the next scores land there).  The two tiles run half a step apart: one tile's products
+      // execute under the other's softmax.
       auto issue_pv = [&](int t, int j) {
-        const uint32_t pt = sP + t * TILE, d = tmem_base + 256u + (uint32_t)(t * 128);
+        const uint32_t v = sV + (j & 1) * TILE;
+        const uint32_t d = tmem_base + 256u + (uint32_t)(t * 128), a = tmem_base + (uint32_t)(t * 128);
 #pragma unroll
         for (int k8 = 0; k8 < 8; ++k8) {
-          // A = P: two 64-key halves, 32 bytes per step.  B = V: 8-key groups are 1024 bytes apart
-          // inside a head-dim half (16 KB), the two halves 16 KB apart (leading offset).
-          const uint64_t adesc = make_desc(pt + (k8 >> 2) * (TILE / 2)) + (uint64_t)((k8 & 3) * 2);
-          const uint64_t bdesc = ((uint64_t)(((sV + k8 * 2048) & 0x3FFFF) >> 4)) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+          // A = P: 16 keys = 8 columns per step.  B = V: 8-key groups are 1024 bytes apart inside a
+          // head-dim half (16 KB), the two halves 16 KB apart (leading offset).
+          const uint64_t bdesc = ((uint64_t)(((v + k8 * 2048) & 0x3FFFF) >> 4)) | ((uint64_t)(16384 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
                                  ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-          tc_mma(d, adesc, bdesc, idesc_pv, (j > 0 || k8 > 0) ? 1u : 0u, false);
+          tc_mma_ts(d, a + (uint32_t)(k8 * 8), bdesc, idesc_pv, (j > 0 || k8 > 0) ? 1u : 0u);
         }
-        tc_commit(pv_full0 + 8 * t);
       };
       for (int j = 0; j < nkv_max && ok; ++j) {
         const bool more = j + 1 < nkv_max;
         bool k_ready = false, v_ready = false;
         for (int t = 0; t < ntiles && ok; ++t) {
+          if (j >= nkv[t]) continue;
+          if (!v_ready) {
+            if (!mbar_wait(v_full0 + 8 * (j & 1), (uint32_t)((j >> 1) & 1), abort_flag)) { ok = false; break; }
+            v_ready = true;
+          }
+          if (!mbar_wait(p_full0 + 8 * t, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          issue_pv(t, j);
           if (j + 1 < nkv[t]) {
             if (!k_ready) {
               if (!mbar_wait(k_full0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag)) { ok = false; break; }
               k_ready = true;
             }
-            // the softmax has read S_t(j)
-            if (!mbar_wait(s_empty0 + 8 * t, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            issue_s(t, j + 1);
-          }
-          if (j < nkv[t]) {
-            if (!v_ready) {
-              if (!mbar_wait(v_full, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
-              v_ready = true;
-            }
-            if (!mbar_wait(p_full0 + 8 * t, (uint32_t)(j & 1), abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv(t, j);
+            issue_s(t, j + 1);              // its commit covers PV_t(j) too
+          } else {
+            tc_commit(pv_full0 + 8 * t);    // the tile's last product
           }
         }
         if (!ok) break;
@@ -361,7 +369,7 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
           if (!k_ready && !mbar_wait(k_full0 + 8 * ((j + 1) & 1), (uint32_t)(((j + 1) >> 1) & 1), abort_flag)) { ok = false; break; }
           tc_commit(k_empty0 + 8 * ((j + 1) & 1));
         }
-        tc_commit(v_empty);
+        tc_commit(v_empty0 + 8 * (j & 1));
       }
     }
   } else {
@@ -373,7 +381,7 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
     const long long b_idx = bh / p.heads, h_idx = bh % p.heads;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const uint32_t tS = tmem_base + (uint32_t)(t * 128) + lane_addr, tO = tmem_base + 256u + (uint32_t)(t * 128) + lane_addr;
-    const uint32_t s_full = s_full0 + 8 * t, s_empty = s_empty0 + 8 * t, p_full = p_full0 + 8 * t, pv_full = pv_full0 + 8 * t;
+    const uint32_t s_full = s_full0 + 8 * t, p_full = p_full0 + 8 * t, pv_full = pv_full0 + 8 * t;
     const int my_nkv = nkv[t];
     // The output row stays in its TMEM accumulator: PV products accumulate there, and it is only
     // read back and rescaled when the running maximum moves by more than RESCALE_STEP (until then
@@ -409,9 +417,7 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
       const bool move = m_seen > m + RESCALE_STEP || m == -NXB_INF;
       const float m_use = move ? m_seen : m;
       if (j > 0) {
-        // PV of the previous block is complete: P's buffer is free, and O may be touched
-        if (!mbar_wait_warp_tight(pv_full, (uint32_t)((j - 1) & 1), abort_flag)) { ok = false; tmem_ld_wait(xa); break; }
-        tc_fence_after();
+        // S_t(j) was issued after PV_t(j-1) and its completion (s_full) covers it: O may be touched
         if (__any_sync(0xffffffffu, move && m != -NXB_INF)) {
           const float alpha = (move && m != -NXB_INF) ? nx_exp2(m * LOG2E - m_use * LOG2E) : 1.f;
           tmem_ld_wait(xa);
@@ -427,24 +433,23 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
         }
       }
       m = m_use;
-      // probabilities of the 128 keys (one FMA and one ex2 each), their sum, and P in bf16: the A
-      // operand of PV, two 64-key halves of 128-byte swizzled rows.  A fully masked row has m = -inf:
-      // every x is -inf too, and with a zero offset ex2(-inf) = 0 without a NaN.
+      // probabilities of the 128 keys (one FMA and one ex2 each), their sum, and P in bf16 over the
+      // first 64 columns of the scores: the A operand of PV.  A fully masked row has m = -inf: every x
+      // is -inf too, and with a zero offset ex2(-inf) = 0 without a NaN.
       const float off = (m == -NXB_INF) ? 0.f : -m * LOG2E;
-      const uint32_t rowbase = sP + (uint32_t)t * TILE + (uint32_t)row * 128u;
       float ls;
-      if (mode == 3) ls = row_probs<Xform, 3>(tS, xa, xc, bh, qi, kj0, p, off, rowbase, (uint32_t)(row & 7), s_empty);
-      else if (mode == 0) ls = row_probs<Xform, 0>(tS, xa, xc, bh, qi, kj0, p, off, rowbase, (uint32_t)(row & 7), s_empty);
-      else if (mode == 1) ls = row_probs<Xform, 1>(tS, xa, xc, bh, qi, kj0, p, off, rowbase, (uint32_t)(row & 7), s_empty);
-      else ls = row_probs<Xform, 2>(tS, xa, xc, bh, qi, kj0, p, off, rowbase, (uint32_t)(row & 7), s_empty);
+      if (mode == 3) ls = row_probs<Xform, 3>(tS, xa, xc, bh, qi, kj0, p, off);
+      else if (mode == 0) ls = row_probs<Xform, 0>(tS, xa, xc, bh, qi, kj0, p, off);
+      else if (mode == 1) ls = row_probs<Xform, 1>(tS, xa, xc, bh, qi, kj0, p, off);
+      else ls = row_probs<Xform, 2>(tS, xa, xc, bh, qi, kj0, p, off);
       l += ls;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full);
     }
     if (ok && my_nkv > 0) {
-      if (mbar_wait_warp_tight(pv_full, (uint32_t)((my_nkv - 1) & 1), abort_flag)) {
+      // the tile's last product commits pv_full (once)
+      if (mbar_wait_warp_tight(pv_full, 0u, abort_flag)) {
         tc_fence_after();
         const float inv = 1.f / l;
         unsigned short* out = (unsigned short*)p.out + b_idx * p.out_bh_hi + h_idx * p.out_bh_lo + qi * p.out_row;

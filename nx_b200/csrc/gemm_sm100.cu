@@ -317,7 +317,7 @@ struct AttnParamsHost {
   void* ep[14];
 };
 
-int attn_smem_bytes() { return 128 * 128 * 2 * 7 + 1024 + 256; }      // Q x 2, K x 2, V, P x 2 (attn_sm100_device.cuh)
+int attn_smem_bytes() { return 128 * 128 * 2 * 6 + 1024 + 256; }      // Q x 2, K x 2, V x 2 (attn_sm100_device.cuh)
 
 // V as (head dim, key, head, batch) with the strides of either layout: boxes of 64 dims x 128 keys
 static CUtensorMap make_map_v4(const void* ptr, int64_t sk, int64_t heads, int64_t batch, bool bshd) {
