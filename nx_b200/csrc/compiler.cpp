@@ -1574,6 +1574,7 @@ std::string Plan::describe() const {
 bool plan_dot(Plan& plan, int node, std::vector<int>& need_materialised, GemmSpec* out);
 bool sort_rows_supported(int64_t len);   // sort_rows.cu
 void canonicalize_dots(Graph& g);
+void share_shifted_exp_sums(Graph& g);
 void rewrite_quantised_linears(Graph& g);
 void rewrite_attention(Graph& g);
 int attn_smem_bytes();
@@ -1609,6 +1610,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
     }
     for (int& o : g.outputs) o = remap[o];
   }
+  if (!getenv("NXB200_NO_SIMPLIFY")) share_shifted_exp_sums(g);
   rewrite_quantised_linears(g);
   rewrite_attention(g);
   canonicalize_dots(g);

@@ -1,5 +1,7 @@
 """The five configurations trace, serialise, evaluate on the oracle (reduced
 sizes) and compile for sm_100a without a GPU."""
+import os
+
 import numpy as np
 import pytest
 
@@ -68,3 +70,23 @@ def test_decoder_block_full_size_compiles():
     plan = prog.describe()
     # seven linear layers as tensor-core products, the attention as one fused kernel
     assert plan.count("gemm#") == 7 and plan.count("attention#") == 1, plan
+
+
+def test_logsumexp_shares_the_softmax_sum():
+    """The planner replaces logsumexp's own sum(exp(x - m0)) by the softmax's sum(exp(x - m)) (selected
+    against the infinite-maximum cases): the generated kernel evaluates one exponential per element for
+    the two of them, and NXB200_NO_SIMPLIFY=1 keeps the graph as written."""
+    import subprocess
+    import sys
+    prog = defn.compile(configs.fused_rows, [defn.template((64, 4096), "f32")]).program
+    assert prog.launch_count() == 1
+    src = prog.kernel_sources()[0]
+    assert src.count("nx_exp(") == 1, src
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = (f"import sys; sys.path.insert(0, {root!r})\n"
+            "from nx_b200 import configs, defn\n"
+            "p = defn.compile(configs.fused_rows, [defn.template((64, 4096), 'f32')]).program\n"
+            "print(p.kernel_sources()[0].count('nx_exp('))\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, NXB200_NO_SIMPLIFY="1"))
+    assert r.returncode == 0 and r.stdout.strip() == "2", r.stdout + r.stderr[-500:]

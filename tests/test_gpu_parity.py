@@ -69,6 +69,32 @@ def test_fused_row_program_f32(shape):
     check(run_both(fused_rows, [x], ["f32"]), f"rows {shape}")
 
 
+def test_fused_row_program_with_infinite_and_nan_rows():
+    """Rows whose maximum is +inf, -inf or NaN: the planner takes logsumexp's sum from the softmax's sum
+    where the maximum is finite and from the sign of the maximum where it is not; the oracle evaluates
+    the graph as written (nx/lib/nx.ex:18400-18433)."""
+    rng = np.random.default_rng(3)
+    x = rng.normal(0, 2, (9, 700)).astype(np.float32)
+    x[1] = -np.inf                         # every element -inf: maximum -inf, sum(exp(x - 0)) = 0
+    x[2, 17] = np.inf                      # one +inf
+    x[3, 5] = x[3, 600] = np.inf           # several +inf
+    x[4, 9] = np.nan                       # NaN: the maximum is NaN, not infinite
+    x[5, 9] = np.nan
+    x[5, 10] = np.inf                      # NaN and +inf
+    x[6, :350] = -np.inf                   # -inf among finite values: finite maximum
+    x[7, 3] = 88.0                         # exp(x) overflows without the shift
+    x[8] = 0.0
+    results = run_both(fused_rows, [x], ["f32"])
+    for i, (g, r, t) in enumerate(results):
+        assert np.array_equal(np.isnan(g), np.isnan(r)), f"output {i}: NaN pattern"
+        assert np.array_equal(np.isinf(g), np.isinf(r)) and np.array_equal(np.sign(g[np.isinf(g)]), np.sign(r[np.isinf(r)])), f"output {i}: infinities"
+        fin = np.isfinite(r)
+        if t[0] in ("s", "u"):
+            assert np.array_equal(g, r), f"output {i}"
+        else:
+            assert_close(g[fin], r[fin], what=f"output {i}", **F32_TOL)
+
+
 def test_fused_row_program_is_one_launch():
     prog = defn.compile(fused_rows, [defn.template((64, 1024), "f32")]).program
     assert prog.launch_count() == 1, prog.describe()
