@@ -37,7 +37,8 @@ struct TcParams {
   int mtiles, ntiles;
   int out_dt;        // nxb200_dtype of C
   int epilogue;
-  int a_mn, b_mn;    // operand stored with its free index contiguous ([k][m] / [k][n]) instead of k
+  int a_mn, b_mn;    // operand stored with its free index contiguous ([k][m] / [k][n]) instead of k: 1 = one copy per
+                     // 64 rows of the tile (3-D map), 2 = one copy per tile (4-D map {64 rows, k, row group, batch})
   int tma_store;     // results leave through shared memory and a TMA store (rows of C 16-byte aligned)
   int panel_m;       // row tiles per panel of the tile walk (>= 1)
   void* ep[14];      // buffers of a generated epilogue, in its argument order
@@ -571,12 +572,16 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
           mbar_expect_tx(full0 + 8 * s, A_STAGE + B_STAGE);
           if (!p.a_mn) {
             tma_load_3d(sA + s * A_STAGE, &map_a, full0 + 8 * s, kb * BK, mt * BM, b);
+          } else if (p.a_mn == 2) {
+            // [k][m] operand: groups of 64 m x 64 k, 8 KB each, all groups of the tile in one copy
+            tma_load_4d(sA + s * A_STAGE, &map_a, full0 + 8 * s, 0, kb * BK, mt * (BM / 64), b);
           } else {
-            // [k][m] operand: boxes of 64 m x 64 k, one per 64 rows of the tile
             for (int j = 0; j < BM / 64; ++j) tma_load_3d(sA + s * A_STAGE + j * 8192, &map_a, full0 + 8 * s, mt * BM + j * 64, kb * BK, b);
           }
           if (!p.b_mn) {
             tma_load_3d(sB + s * B_STAGE, &map_b, full0 + 8 * s, kb * BK, nt * BN, b);
+          } else if (p.b_mn == 2) {
+            tma_load_4d(sB + s * B_STAGE, &map_b, full0 + 8 * s, 0, kb * BK, nt * (BN / 64), b);
           } else {
             for (int j = 0; j < BN / 64; ++j) tma_load_3d(sB + s * B_STAGE + j * 8192, &map_b, full0 + 8 * s, nt * BN + j * 64, kb * BK, b);
           }
