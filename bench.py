@@ -86,12 +86,30 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons during the timed region."""
+    """SM clock and throttle reasons of one GPU DURING a timed region.  A thread reads them through NVML
+    (what nvidia-smi itself reads; a query takes well under a millisecond, so regions of a few
+    milliseconds still get samples) and stamps every sample with the host clock; `begin()` / `end()`
+    mark the region, and only samples taken inside it are reported.  Without the NVML module the
+    recipe's `nvidia-smi -lms` loop is used, its samples stamped on arrival."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, index, period_ms=50):
-        self.rows, self.proc = [], None
+        self.samples, self.proc, self.nvml, self.max_mhz = [], None, None, None
+        self.t0, self.t1, self.running = None, None, True
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.period = min(period_ms, 2) / 1e3
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
                                           "--format=csv,noheader,nounits", "-lms", str(period_ms)],
@@ -101,25 +119,54 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        while self.running:
+            try:
+                mhz = float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                self.samples.append((time.perf_counter(), mhz, {k for k, b in self.BITS.items() if mask & b}))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
     def _read(self):
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            r = [c.strip() for c in line.split(",")]
+            if len(r) >= 6 and r[0].replace(".", "").isdigit():
+                if r[1].replace(".", "").isdigit():
+                    self.max_mhz = max(self.max_mhz or 0.0, float(r[1]))
+                self.samples.append((time.perf_counter(), float(r[0]), {n for n, v in zip(names, r[2:6]) if v.lower().startswith("active")}))
+
+    def begin(self):
+        self.t0 = time.perf_counter()
+
+    def end(self):
+        self.t1 = time.perf_counter()
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.1)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
-        sm = [float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit()]
-        mx = [float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 6 for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+        if self.nvml is None and not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["neither NVML nor nvidia-smi available"], "samples": 0}
+        if self.t1 is None:
+            self.t1 = time.perf_counter()
+        if self.nvml is None:
+            time.sleep(0.1)                      # the last lines of the nvidia-smi loop
+        self.running = False
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+        else:
+            self.t.join(timeout=1)
+        t0 = self.t0 if self.t0 is not None else 0.0
+        inside = [s_ for s_ in self.samples if t0 <= s_[0] <= self.t1]
+        sm = [s_[1] for s_ in inside]
+        reasons = sorted(set().union(*[s_[2] for s_ in inside])) if inside else []
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self.max_mhz, "reasons": reasons,
+                "samples": len(sm), "source": "NVML, sampled inside the timed region" if self.nvml else "nvidia-smi -lms, sampled inside the timed region"}
 
 
 # ---- CPU arm -----------------------------------------------------------------------------
@@ -602,15 +649,17 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    sampler = ClockSampler(local)                     # started before the warm-up: it is polling when the timed region begins
     for _ in range(args.warmup):
         prog.run_into([x], outs, local)
     barrier()
-    sampler = ClockSampler(local)
     nif.check(lib.nxb200_timer_begin(local))
+    sampler.begin()
     for _ in range(args.steps):
         prog.run_into([x], outs, local)
     ms = C.c_float()
     nif.check(lib.nxb200_timer_end(local, C.byref(ms)))
+    sampler.end()
     barrier()
     clocks = sampler.stop()
     elapsed_ms = ms.value
