@@ -1525,6 +1525,7 @@ struct Planner {
   // Members of one fused kernel must share it: then no path between two members can
   // leave the kernel through a boundary and come back, i.e. no dependency cycle.
   std::vector<int> depth_memo;
+  std::vector<char> table;     // elementwise values materialised as tables (see build_plan)
   int depth(int n) {
     if (depth_memo.size() != g.nodes.size()) depth_memo.assign(g.nodes.size(), -1);
     if (depth_memo[n] >= 0) return depth_memo[n];
@@ -1546,8 +1547,10 @@ struct Planner {
   // (elementwise, views, reductions); `leaves` collects the buffers it ends at.
   void cone(int n, std::set<int>& seen, std::set<int>& leaves, std::set<int>& reds, bool root) {
     if (is_leaf(n)) { leaves.insert(n); return; }
-    if (!seen.insert(n).second) return;
     const Node& nd = g.nodes[n];
+    // an elementwise value that is a buffer anyway (a table computed once) ends the cone like a parameter
+    if (!root && table[n]) { leaves.insert(n); return; }
+    if (!seen.insert(n).second) return;
     if (is_reduce(nd) && !root) reds.insert(n);
     for (int a : nd.args) cone(a, seen, leaves, reds, false);
   }
@@ -1766,6 +1769,7 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
   // slots for leaves
   plan->param_slots.assign(g.n_params, -1);
   P.mat.assign(N, 0);
+  P.table.assign(N, 0);
   for (int n = 0; n < N; ++n) {
     Node& nd = g.nodes[n];
     if (!nd.live) continue;
@@ -1811,6 +1815,37 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
       for (int a : nd.args) {
         const std::string& aop = g.nodes[a].op;
         if (aop != "parameter" && aop != "tensor") P.mat[a] = 1;
+      }
+    }
+  }
+  // A value with transcendental functions in it that a much larger consumer broadcasts (the cos / sin
+  // table of a rotary embedding under {batch, head, position, dim}) is computed once into a buffer: inline,
+  // every element of the consumer would evaluate it again (256 times per table entry in the decoder
+  // block, with the full-range cosf / sinf).  Only where it pays: a consumer of at least a million
+  // elements, sixteen of them per table entry, and nothing in the value that needs a kernel of its own.
+  if (!getenv("NXB200_NO_TABLES")) {
+    std::function<int(int)> expensive_ops = [&](int a) -> int {     // -1: not a plain elementwise value
+      const Node& nd = g.nodes[a];
+      if (nd.op == "parameter" || nd.op == "tensor" || nd.op == "constant" || nd.op == "iota" || P.mat[a]) return 0;
+      if (!is_inline(nd) || nd.op == "gather" || nd.op == "put_slice") return -1;
+      int total = kUnaryMath.count(nd.op) || nd.op == "pow" || nd.op == "atan2" ? 1 : 0;
+      for (int x : nd.args) {
+        const int sub = expensive_ops(x);
+        if (sub < 0) return -1;
+        total += sub;
+      }
+      return total;
+    };
+    for (int n = 0; n < N; ++n) {
+      const Node& nd = g.nodes[n];
+      if (!nd.live || !is_inline(nd)) continue;
+      const int64_t big = shape_numel(nd.shape);
+      if (big < (1 << 20)) continue;
+      for (int a : nd.args) {
+        const Node& an = g.nodes[a];
+        const int64_t small = shape_numel(an.shape);
+        if (P.mat[a] || small < 256 || small * 16 > big || an.op == "parameter" || an.op == "tensor") continue;
+        if (expensive_ops(a) > 0) { P.mat[a] = 1; P.table[a] = 1; }
       }
     }
   }
@@ -1984,6 +2019,8 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
                 // merging is only safe if neither root depends on the other
                 if (s2.count(n) || seen.count(s)) { merged = -2; break; }
                 for (int l : leaves) if (l2.count(l)) merged = (int)ui;
+                // two values computed from indices and constants alone (the cos and sin tables of one angle)
+                if (leaves.empty() && l2.empty()) merged = (int)ui;
               }
               if (merged == -2) merged = -1;
             }

@@ -905,6 +905,15 @@ def concatenate(tensors, axis=0):
     shape = list(tensors[0].shape)
     shape[a] = _b.sum(t.shape[a] for t in tensors)
     out = _out(type, shape)
+    from . import backend
+    if backend.tracing() and _b.all(_is_expr(t) and t.data.id == tensors[0].data.id for t in tensors):
+        # k copies of ONE traced value side by side (the angle table of a rotary embedding,
+        # ``concatenate([freqs, freqs])``): a broadcast over a new axis folded into the concatenation
+        # axis, i.e. index arithmetic inside whatever reads it, with no buffer and no kernel of its own
+        x = tensors[0]
+        k, n = len(tensors), x.shape[a]
+        tiled = broadcast(reshape(x, x.shape[:a] + (1,) + x.shape[a:]), x.shape[:a] + (k,) + x.shape[a:])
+        return as_type(reshape(tiled, tuple(shape)), type)
     if _rearranges_one_source(tensors):
         return _concatenate_by_selection(tensors, a, type, shape)
     return _dispatch(lambda *ts: E.node(out, "concatenate", list(ts), ints=[a]), tensors)
@@ -918,8 +927,7 @@ def _rearranges_one_source(tensors):
     pointwise functions (the rotate-half of a rotary embedding: ``concatenate([-x2, x1])``).  Such a
     concatenation is an index selection on one source: it is traced as selects over padded pieces, which
     the compiler generates inside the consumer's kernel, instead of a node of its own whose pieces are
-    written to memory first.  (Pieces that are whole tensors stay a concatenate node: its result is a
-    buffer, which is what a small table repeated and then broadcast over a large consumer should be.)"""
+    written to memory first.  (Different whole tensors side by side stay a concatenate node.)"""
     from . import backend
     if not backend.tracing() or len(tensors) > 4 or not _b.all(_is_expr(t) for t in tensors):
         return False
