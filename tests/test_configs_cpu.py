@@ -7,7 +7,7 @@ import pytest
 
 import nx_oracle as O
 from helpers import host_tensor
-from nx_b200 import configs, defn
+from nx_b200 import configs, defn, nx
 
 
 def build(fun, inputs):
@@ -90,3 +90,31 @@ def test_logsumexp_shares_the_softmax_sum():
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
                        env=dict(os.environ, NXB200_NO_SIMPLIFY="1"))
     assert r.returncode == 0 and r.stdout.strip() == "2", r.stdout + r.stderr[-500:]
+
+
+def test_rotary_tables_are_computed_once_and_identical_pieces_need_no_buffer():
+    """The decoder block's plan: the angle table concatenate([freqs, freqs]) is index arithmetic (no
+    concatenate node), cos and sin of it are ONE small kernel writing two tables, and the kernel that
+    rotates q and k loads them instead of evaluating cosf / sinf for every element of {batch, head,
+    position, dim}.  NXB200_NO_TABLES=1 keeps them inline."""
+    block = configs.make_decoder_block(n_heads=4)
+    inputs = configs.decoder_inputs(batch=8, seq=512, hidden=512, inter=688)     # rope space 2 M elements
+    prog = defn.compile(block, [defn.template(a.shape, t) for a, t in inputs]).program
+    plan = prog.describe()
+    assert "concatenate" not in plan
+    ew = [l for l in plan.split("\n") if "_ew" in l]
+    assert len(ew) == 2 and "space={512,128}" in ew[0] and ew[0].count("as_type#") == 2, plan
+    rope = [s for s in prog.kernel_sources() if "space" not in s and "nxb_k2_ew" in s]
+    assert rope and "cosf" not in rope[0] and "sinf" not in rope[0]
+    assert prog.launch_count() == 12, plan
+
+
+def test_identical_pieces_side_by_side_match_the_oracle():
+    x = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    for axis in (0, 1, 2, -1):
+        fun = lambda t: nx.concatenate([t * 2.0, t * 2.0][:1] * 3, axis=axis) + 1.0
+        blob, _ = defn.build_program(fun, [defn.template(x.shape, "f32")])
+        nodes, _ = O.parse_program(blob)
+        assert not [n for n in nodes if n.op == "concatenate"]
+        (got, _, _), = O.run_program(blob, [x.tobytes()], "xla_like")
+        np.testing.assert_array_equal(got, np.concatenate([x * 2.0] * 3, axis=axis) + 1.0)
