@@ -745,7 +745,7 @@ def main():
                              "frac": round(per_gpu / peak, 4),
                              "traffic": row_kernel_traffic(rows, COLS),
                              "traffic_source": "ncu capture of a 1024-row launch of this kernel: reads scaled by the rows, writes = "
-                                               "algorithmic output bytes less the 58.9 MB still dirty in L2 when the kernel ends",
+                                               f"algorithmic output bytes less the {NCU_L2_RESIDUE_BYTES / 1e6:.1f} MB still dirty in L2 when the kernel ends",
                              "peak_source": f"of {which}", "kernel": "nxb_k0_row",
                              "algorithmic_bytes_per_launch": nbytes},
                 "clocks": clocks, "gpu_launches": launches, "e2e": e2e, "plan": plan}

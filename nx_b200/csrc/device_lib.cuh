@@ -321,7 +321,8 @@ NXB_DEV void arg_step(ArgPair<T>& acc, T v, long long i) {
   bool take;
   if (TIE_HIGH) take = IS_MAX ? (v >= acc.v) : (v <= acc.v);
   else take = IS_MAX ? (v > acc.v) : (v < acc.v);
-  take = (take && !is_nan_any(acc.v)) || is_nan_any(v) || acc.i < 0;
+  // (an ordered comparison with a NaN accumulator is false by itself: a NaN, once taken, is only replaced by a later NaN)
+  take = take || is_nan_any(v) || acc.i < 0;
   acc.v = take ? v : acc.v;
   acc.i = take ? i : acc.i;
 }
