@@ -1159,6 +1159,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
   int scratch_slots = 2;
 
   std::vector<int> row_stores;
+  static const bool defer_off = getenv("NXB200_NO_DEFERRED_STORES") != nullptr;
   for (phase_ = 0; phase_ < nphases_; ++phase_) {
     for (int r : reduces) {
       if (red_phase[r] != phase_) continue;
@@ -1214,7 +1215,13 @@ KernelSpec KernelBuilder::build(const std::string& name) {
         bool full;
         index_for_shape(g_.nodes[s].shape, &full);
         if (!full) { if (phase_ == 0) row_stores.push_back(s); continue; }
-        if (level(s) != phase_) continue;
+        // A full-size result that depends on no reduction could be stored in the first phase.  With the row
+        // in registers it is stored in the second instead: the first phase then only reduces (no stores
+        // queue up behind the load of the next row), and the result's arithmetic runs between the stores
+        // of the second phase (measured on the fused row configuration: 0.736 -> 0.715 ms).
+        int sp = level(s);
+        if (sp == 0 && nphases_ > 1 && cache_ && !defer_off) sp = 1;
+        if (sp != phase_) continue;
       }
       emit_store(s);
     }
