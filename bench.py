@@ -52,11 +52,11 @@ METRIC, UNIT = "fused-op HBM GB/s", "GB/s"
 WORKLOAD = "fused row defn f32 {%d,32768} (max, exp, sum, logsumexp, softmax, argmax, tanh*sigmoid chain)"
 
 # DRAM traffic of one launch of the row kernel, derived from an ncu capture of a 1024-row case
-# (dram__bytes_read.sum = 134,253,568, dram__bytes_write.sum = 342,654,976): reads grow with the
+# (dram__bytes_read.sum = 134,252,032, dram__bytes_write.sum = 343,617,792): reads grow with the
 # rows (every row is read once); writes are the algorithmic output bytes less what was still
 # dirty in L2 when the kernel ended, which is a constant of the cache, not of the row count.
-NCU_READ_BYTES_PER_ROW = 134_253_568 / 1024
-NCU_L2_RESIDUE_BYTES = (3 * 1024 * 32768 * 4 + 1024 * 16) - 342_654_976
+NCU_READ_BYTES_PER_ROW = 134_252_032 / 1024
+NCU_L2_RESIDUE_BYTES = (3 * 1024 * 32768 * 4 + 1024 * 16) - 343_617_792
 
 
 def row_kernel_traffic(rows, cols):
