@@ -122,6 +122,28 @@ CUtensorMap make_map_c(void* ptr, DType dt, int64_t m, int64_t n, int64_t batch,
   return t;
 }
 
+// The same result for the plain 16-bit epilogue, which hands `groups` neighbouring 32 x 32 staging tiles
+// of a warp to the TMA unit in ONE store: a four-dimensional view {32 columns, m, group of 32 columns,
+// batch}.  (One store per 32 x 32 tile kept an epilogue warp ~200 cycles per tile in the store's issue;
+// with a short k loop the epilogue, not the tensor pipe, sets the tile time.)  Needs n % 32 == 0.
+CUtensorMap make_map_c_grouped(void* ptr, DType dt, int64_t m, int64_t n, int64_t batch, int groups, bool* ok) {
+  const DriverApi& drv = driver();
+  CUtensorMap t;
+  memset(&t, 0, sizeof t);
+  const size_t es = dtype_size(dt);
+  *ok = ptr && es == 2 && n % 32 == 0 && ((uintptr_t)ptr) % 16 == 0 && (dt == NXB_BF16 || dt == NXB_F16) && groups > 1 && !getenv("NXB200_NO_GROUPED_TMA");
+  if (!*ok) return t;
+  cuuint64_t dims[4] = {32, (cuuint64_t)m, (cuuint64_t)(n / 32), (cuuint64_t)batch};
+  cuuint64_t strides[3] = {(cuuint64_t)(n * es), (cuuint64_t)(32 * es), (cuuint64_t)(m * n * es)};
+  cuuint32_t box[4] = {32, 32, (cuuint32_t)groups, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = drv.cuTensorMapEncodeTiled(&t, dt == NXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, ptr, dims, strides,
+                                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  *ok = r == CUDA_SUCCESS;
+  return t;
+}
+
 // out[b][c][r] = in[b][r][c] for 1- and 2-byte elements (operands whose reduction index is
 // not contiguous are brought to K-major form before the tensor-core product).
 template <typename T>
@@ -246,6 +268,16 @@ void launch_tc_gemm(const GemmArgs& g, int* status_word, int sm_count, cudaStrea
   bool c_ok = false;
   CUtensorMap mc = make_map_c(g.c, g.dc, g.m, g.n, g.batch, &c_ok);
   p.tma_store = c_ok ? 1 : 0;
+  if (c_ok && !g.scale && (g.da == NXB_BF16 || g.da == NXB_F16) && (g.dc == NXB_BF16 || g.dc == NXB_F16)) {
+    // the plain 16-bit epilogue: all staging tiles of a warp leave in one store when they divide its columns
+    const int epi_groups = tc_block_threads(g.k) >= 320 ? 2 : 1;
+    const int slots = (8192 / epi_groups) / 2048, c_per = (bn / 32) / epi_groups;
+    bool g_ok = false;
+    if (slots > 1 && c_per % slots == 0) {
+      CUtensorMap mg = make_map_c_grouped(g.c, g.dc, g.m, g.n, g.batch, slots, &g_ok);
+      if (g_ok) { mc = mg; p.tma_store = 2; }
+    }
+  }
   long long tiles = (long long)p.mtiles * p.ntiles * p.batch;
   unsigned grid = (unsigned)std::min<long long>(tiles, sm_count);
   auto launch = [&](auto kern, int smem) {

@@ -39,7 +39,8 @@ struct TcParams {
   int epilogue;
   int a_mn, b_mn;    // operand stored with its free index contiguous ([k][m] / [k][n]) instead of k: 1 = one copy per
                      // 64 rows of the tile (3-D map), 2 = one copy per tile (4-D map {64 rows, k, row group, batch})
-  int tma_store;     // results leave through shared memory and a TMA store (rows of C 16-byte aligned)
+  int tma_store;     // results leave through shared memory and a TMA store (rows of C 16-byte aligned); 2: the plain 16-bit
+                     // epilogue stores all staging tiles of a warp at once (map_c is the four-dimensional grouped view)
   int panel_m;       // row tiles per panel of the tile walk (>= 1)
   void* ep[14];      // buffers of a generated epilogue, in its argument order
 };
@@ -310,6 +311,12 @@ __device__ __forceinline__ unsigned short f32_to_f16_bits(float f) {
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, uint32_t src, int x, int y, int z) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
                ::"l"((unsigned long long)map), "r"(src), "r"(x), "r"(y), "r"(z) : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, uint32_t src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"((unsigned long long)map), "r"(src), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
@@ -662,6 +669,27 @@ __device__ __forceinline__ void tc_gemm_body(const CUtensorMap& map_a, const CUt
           } else {
 #pragma unroll
             for (int e = 0; e < 16; ++e) h[e] = bits2_to_f16x2(v[2 * e], v[2 * e + 1]);
+          }
+          if (p.tma_store == 2) {
+            // all staging tiles of this warp are one group: written side by side, handed over in ONE store
+            // through the four-dimensional map {32 columns, m, group of 32 columns, batch}
+            const uint32_t slot = (uint32_t)(c - c0) & (lean_slots - 1);
+            const uint32_t gbuf = lean_base + slot * 2048u;
+            if (slot == 0) {
+              if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous group has been read
+              __syncwarp();
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(gbuf + (((uint32_t)j ^ lean_sw) << 4)), "r"(h[4 * j]), "r"(h[4 * j + 1]),
+                           "r"(h[4 * j + 2]), "r"(h[4 * j + 3]) : "memory");
+            if (slot == lean_slots - 1 || n0 + 32 >= p.n) {
+              asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+              __syncwarp();
+              if (lane == 0)
+                tma_store_4d(&map_c, sStore + (uint32_t)(warp - 2) * stage_bytes, 0, mt * BM + q * 32, (int)(n0 / 32) - (int)slot, b);
+            }
+            return;
           }
           const uint32_t buf = lean_base + (store_iter & (lean_slots - 1)) * 2048u;    // this lane's 64-byte row
           if (lane == 0) {   // the tile about to be overwritten must have been read by the TMA unit
