@@ -106,6 +106,55 @@ def test_fused_attention(b, h, sq, sk, causal):
     assert_close(g, r, what="fused attention", **BF16)
 
 
+def _attention_with(q, k, v, transform):
+    s = transform(nx.dot(q, [3], [0, 1], k, [3], [0, 1]))
+    m = nx.reduce_max(s, axes=[-1], keep_axes=True)
+    e = nx.exp(s - m)
+    p = e / nx.sum(e, axes=[-1], keep_axes=True)
+    return nx.dot(p, [3], [0, 1], v, [2], [0, 1])
+
+
+def _causal(s):
+    sq, sk = s.shape[2], s.shape[3]
+    mask = nx.greater_equal(nx.iota((sq, sk), axis=0), nx.iota((sq, sk), axis=1))
+    return nx.select(nx.broadcast(mask, s.shape), s, float("-inf"))
+
+
+@pytest.mark.parametrize("name", ["causal_no_scale", "causal_scale_and_bias", "causal_negative_scale", "bias_only", "scale_only"])
+def test_fused_attention_forms_of_the_score_transform(name):
+    """The kernel compiles the score transform in up to three forms (full; without a proven causal mask
+    for key blocks below the diagonal; scale folded into the exponent when the unmasked transform is a
+    multiplication by a positive constant).  Each case here takes another combination of them; 384 rows
+    give key blocks below, on and (skipped) above the diagonal."""
+    rng = np.random.default_rng(31)
+    b, h, sq = 1, 2, 384
+    # unscaled scores keep a standard deviation near 1 (q and k at 0.3): the oracle rounds every node to
+    # bf16, the kernel keeps f32 in between, and with scores of 10 and more that alone moves probabilities by 10 %
+    sd = 0.3 if name == "causal_no_scale" else 1.0
+    q, k = (rng.normal(0, sd, (b, h, sq, 128)).astype(np.float32) for _ in range(2))
+    v = rng.normal(0, 1, (b, h, sq, 128)).astype(np.float32)
+    bias = rng.normal(0, 1, (h, sq, sq)).astype(np.float32)
+    inputs = [(q, "bf16"), (k, "bf16"), (v, "bf16")]
+    if name == "causal_no_scale":
+        fun = lambda q, k, v: _attention_with(q, k, v, _causal)
+    elif name == "causal_scale_and_bias":
+        inputs.append((bias, "bf16"))
+        fun = lambda q, k, v, bb: _attention_with(q, k, v, lambda s: _causal(s * 0.0884 + nx.broadcast(bb, s.shape, axes=[1, 2, 3])))
+    elif name == "causal_negative_scale":
+        fun = lambda q, k, v: _attention_with(q, k, v, lambda s: _causal(s * -0.0884))
+    elif name == "bias_only":
+        inputs.append((bias, "bf16"))
+        fun = lambda q, k, v, bb: _attention_with(q, k, v, lambda s: s * 0.0884 + nx.broadcast(bb, s.shape, axes=[1, 2, 3]))
+    else:
+        fun = lambda q, k, v: _attention_with(q, k, v, lambda s: s * 0.0884)
+    prog = defn.compile(fun, [defn.template(a.shape, t) for a, t in inputs]).program
+    assert "attention" in prog.describe(), prog.describe()
+    (g, r, t), = run_both(fun, inputs)
+    # two more bf16 roundings per score than the scale-only form (the sum with the bias, the bias itself):
+    # the absolute tolerance is doubled; a missing bias or mask would move every row by tens of percent
+    assert_close(g, r, what=f"fused attention ({name})", rtol=BF16["rtol"], atol=2 * BF16["atol"])
+
+
 def test_dense_bias_gelu_reduced():
     inputs = configs.dense_inputs(m=384, n=512, k=1024)
     (g, r, t), = run_both(configs.dense_bias_gelu, inputs)
