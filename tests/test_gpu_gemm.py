@@ -38,8 +38,10 @@ def run_both(fun, arrays, types):
 
 
 # the last two have more row tiles than one panel of the tile walk, the final panel being partial
+# (200, 320, ..), (130, 576, ..), (96, 288, ..): n is a multiple of 64 / 32 but not of the tile width, so the
+# four-dimensional tensor maps of a [k][n] operand and of the result clip whole groups at the right edge
 SHAPES = [(128, 256, 64), (1, 8, 8), (130, 260, 72), (257, 513, 136), (64, 1000, 4096), (384, 768, 512),
-          (1024, 1024, 1024), (1100, 200, 64), (4500, 2056, 136)]
+          (1024, 1024, 1024), (1100, 200, 64), (4500, 2056, 136), (200, 320, 192), (130, 576, 72), (96, 288, 64)]
 
 
 @pytest.mark.parametrize("m,n,k", SHAPES)
@@ -57,17 +59,31 @@ def test_bf16_dot(m, n, k):
         assert_close(g, r, rtol=2 ** -7, atol=2 ** -9, what=f"bf16 dot {m}x{n}x{k} (1 ulp)")
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (192, 320, 136), (130, 200, 72), (320, 64, 264)])
+def test_bf16_dot_with_both_operands_stored_k_first(m, n, k):
+    """x^T . w with x stored {k,m} and w stored {k,n}: both operands reach the tensor cores with their
+    free index contiguous (the layout of a weight gradient).  m and n a multiple of 64: one TMA copy per
+    tile through the four-dimensional map, including tiles whose groups are clipped; otherwise one per 64 rows."""
+    rng = np.random.default_rng(9)
+    a = rng.normal(0, 1 / np.sqrt(k), (k, m)).astype(np.float32)
+    b = rng.normal(0, 1, (k, n)).astype(np.float32)
+    (g, r, t), = run_both(lambda x, y: nx.dot(x, [0], y, [0]), [a, b], ["bf16", "bf16"])
+    assert g.shape == (m, n)
+    assert_close(g, r, rtol=2 ** -7, atol=2 ** -9, what=f"bf16 dot, k-first operands {m}x{n}x{k}")
+
+
 def test_bf16_dot_uses_tensor_cores():
     prog = defn.compile(lambda x, y: nx.dot(x, y), [defn.template((256, 512), "bf16"), defn.template((512, 256), "bf16")]).program
     assert "gemm" in prog.describe()
 
 
-def test_bf16_batched_dot():
+@pytest.mark.parametrize("n", [300, 320])
+def test_bf16_batched_dot(n):
     rng = np.random.default_rng(3)
     a = rng.normal(0, 0.2, (5, 200, 72)).astype(np.float32)
-    b = rng.normal(0, 1, (5, 72, 300)).astype(np.float32)
+    b = rng.normal(0, 1, (5, 72, n)).astype(np.float32)
     (g, r, t), = run_both(lambda x, y: nx.dot(x, [2], [0], y, [1], [0]), [a, b], ["bf16", "bf16"])
-    assert g.shape == (5, 200, 300)
+    assert g.shape == (5, 200, n)
     assert_close(g, r, rtol=2 ** -7, atol=2 ** -9, what="batched bf16 dot")
 
 
