@@ -68,6 +68,14 @@ NXB_DEV void st_vec(S* __restrict__ p, const typename Repr<S>::R (&src)[V]) {
   Pack<S, V> t;
 #pragma unroll
   for (int i = 0; i < V; ++i) t.v[i] = Repr<S>::store(src[i]);
+#if defined(NXB_STREAMING_STORES)
+  // results larger than the cache, read by nobody soon: evict-first (the planner defines this per kernel)
+  if constexpr (sizeof(Pack<S, V>) == 16) {
+    const uint4 w = *reinterpret_cast<const uint4*>(&t);
+    asm volatile("st.global.cs.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(w.x), "r"(w.y), "r"(w.z), "r"(w.w) : "memory");
+    return;
+  }
+#endif
   *reinterpret_cast<Pack<S, V>*>(p) = t;
 }
 template <typename S> NXB_DEV typename Repr<S>::R ld1(const S* __restrict__ p) { return Repr<S>::load(*p); }

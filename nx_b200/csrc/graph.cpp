@@ -98,9 +98,9 @@ const char* device_lib_source() {
 const char* gemm_device_source();
 const char* attention_device_source();
 
-std::string compile_to_cubin(const std::string& source, const std::string& name, bool tensor_core, bool attention) {
+std::string compile_to_cubin(const std::string& source, const std::string& name, bool tensor_core, bool attention, const std::string& prologue) {
   nvrtcProgram prog;
-  std::string full = std::string(device_lib_source()) + "\n" + (tensor_core ? std::string(gemm_device_source()) + "\n" : std::string()) +
+  std::string full = prologue + std::string(device_lib_source()) + "\n" + (tensor_core ? std::string(gemm_device_source()) + "\n" : std::string()) +
                      (attention ? std::string(attention_device_source()) + "\n" : std::string()) + source;
   if (nvrtcCreateProgram(&prog, full.c_str(), (name + ".cu").c_str(), 0, nullptr, nullptr) != NVRTC_SUCCESS)
     fail(NXB_ERR_RUNTIME, "nvrtcCreateProgram failed");

@@ -55,6 +55,7 @@ struct KernelSpec {
   std::vector<int> arg_slots;     // one pointer argument per entry
   std::vector<size_t> arg_offsets;  // byte offset added to the slot's base pointer
   std::vector<int> written_slots;   // slots this kernel stores to
+  std::string prologue;             // preprocessor definitions placed before the device library (per-kernel switches)
   std::vector<int> inplace_ok;      // read slots whose every load is at the loading thread's own position
                                     // (s >= 0), and written slots stored there (encoded -1 - s)
   bool tensor_core = false;       // a generated matrix-product kernel (needs the GEMM device source)
@@ -158,7 +159,8 @@ struct Plan {
 std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes);
 
 // NVRTC: compile CUDA source to an sm_100a cubin (needs no GPU).
-std::string compile_to_cubin(const std::string& source, const std::string& name, bool tensor_core = false, bool attention = false);
+std::string compile_to_cubin(const std::string& source, const std::string& name, bool tensor_core = false, bool attention = false,
+                             const std::string& prologue = std::string());
 const char* device_lib_source();
 
 }  // namespace nxb

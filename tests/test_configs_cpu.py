@@ -118,3 +118,9 @@ def test_identical_pieces_side_by_side_match_the_oracle():
         assert not [n for n in nodes if n.op == "concatenate"]
         (got, _, _), = O.run_program(blob, [x.tobytes()], "xla_like")
         np.testing.assert_array_equal(got, np.concatenate([x * 2.0] * 3, axis=axis) + 1.0)
+
+
+def test_results_far_larger_than_the_cache_are_stored_with_the_streaming_hint():
+    big = defn.compile(configs.fused_rows, [defn.template((8192, 32768), "f32")]).program.describe()
+    small = defn.compile(configs.fused_rows, [defn.template((64, 32768), "f32")]).program.describe()
+    assert "streaming-stores" in big and "streaming-stores" not in small
