@@ -44,9 +44,9 @@ struct AttnParams {
   void* ep[14];        // buffers read by the generated score transform
 };
 
-constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int BQ = 128, BKV = 128;          // head dim 128
 constexpr int TILE = 128 * 128 * 2;                 // one 128 x 128 bf16 tile = two 16 KB halves
-constexpr int ATTN_SMEM = 2 * TILE /*Q x 2*/ + 2 * TILE /*K x 2 stages*/ + 2 * TILE /*V x 2 stages*/ + 1024 + 256;
+// shared memory: Q x 2, K x 2 stages, V x 2 stages, 1 KB of alignment slack, barriers (the host's attn_smem_bytes())
 
 // 32 consecutive columns of one TMEM lane per thread, without waiting for them ...
 __device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
@@ -178,19 +178,18 @@ __device__ __forceinline__ void probs32(float (&ls)[4], const uint32_t (&x)[32],
       asm("mov.b64 {%0, %1}, %2;" : "=f"(a0), "=f"(a1) : "l"(acc[u]));
       ls[u] = a0 + a1;
     }
-    tmem_st16_issue(tP, pk16);
-    return;
-  }
+  } else {
 #pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    uint32_t (&pk)[4] = reinterpret_cast<uint32_t (&)[4]>(pk16[g * 4]);
+    for (int g = 0; g < 4; ++g) {
+      uint32_t (&pk)[4] = reinterpret_cast<uint32_t (&)[4]>(pk16[g * 4]);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int e = g * 8 + u * 2;
-      const float e0 = nx_exp2(fmaf(score_of<Xform, MODE>(x[e], bh, qi, kj + e, p), LOG2E, off));
-      const float e1 = nx_exp2(fmaf(score_of<Xform, MODE>(x[e + 1], bh, qi, kj + e + 1, p), LOG2E, off));
-      ls[u] += e0 + e1;
-      asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[u]) : "f"(e1), "f"(e0));
+      for (int u = 0; u < 4; ++u) {
+        const int e = g * 8 + u * 2;
+        const float e0 = nx_exp2(fmaf(score_of<Xform, MODE>(x[e], bh, qi, kj + e, p), LOG2E, off));
+        const float e1 = nx_exp2(fmaf(score_of<Xform, MODE>(x[e + 1], bh, qi, kj + e + 1, p), LOG2E, off));
+        ls[u] += e0 + e1;
+        asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(pk[u]) : "f"(e1), "f"(e0));
+      }
     }
   }
   tmem_st16_issue(tP, pk16);
@@ -231,7 +230,7 @@ __device__ __forceinline__ void attn_body(const CUtensorMap& map_q, const CUtens
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // pairs of query blocks, heavy (late) pairs first: with a causal mask block i needs i+1 key blocks.
   // Tile 0 is the later block of the pair, tile 1 the one before it (absent for the last pair of an odd count).
-  const int nqb = (p.sq + BQ - 1) / BQ, npairs = (nqb + 1) / 2;
+  const int nqb = (p.sq + BQ - 1) / BQ;                 // (nqb + 1) / 2 pairs per (batch, head): the grid's second factor
   // The grid runs in block order: the heaviest pair of every (batch, head) first, the lightest last, so
   // that the last wave is made of short CTAs (measured at {8,32,2048,128}: 0.38 ms against 0.40 with the
   // pairs of one (batch, head) next to each other, although keys and values are then fetched once per pair).
