@@ -346,3 +346,88 @@ case("indexed_put axes [0, 2]", "nx/lib/nx.ex:8376-8404", lambda t, i, u: nx.ind
      [([[[0, 1, 20], [30, 4, 50]]], "s32")])
 case("indexed_put rank-1 index, scalar update", "nx/lib/nx.ex:8306-8313", lambda t, i: nx.indexed_put(t, i, 10),
      [([[1], [2]], "s32"), ([1, 0], "s32")], [([[1], [10]], "s32")])
+
+# ---- element-wise binary operators: doctests of nx/lib/nx.ex -----------------------------------------
+case("remainder tensor, scalar", "nx/lib/nx.ex:6407-6411", lambda t: nx.remainder(t, 2), [([1, 2, 3], "s32")], [([1, 0, 1], "s32")])
+case("remainder scalar, f32 tensor", "nx/lib/nx.ex:6413-6417", lambda t: nx.remainder(2, t), [([1.0, 2.0, 3.0], "f32")], [([0.0, 0.0, 2.0], "f32")])
+case("remainder broadcast", "nx/lib/nx.ex:6421-6430", lambda a, b: nx.remainder(a, b), [([[10], [20]], "s32"), ([[3, 4]], "s32")],
+     [([[1, 2], [2, 0]], "s32")])
+case("remainder s8 by u8 keeps the dividend's sign", "nx/lib/nx.ex:6440-6451",
+     lambda a, b: (nx.remainder(a, b), nx.remainder(nx.add(a, nx.tensor(20, "s8")), b)), [(-11, "s8"), (10, "u8")], [(-1, "s16"), (9, "s16")])
+case("remainder u8", "nx/lib/nx.ex:6452-6462",
+     lambda a, b: (nx.remainder(a, b), nx.remainder(nx.add(a, nx.tensor(20, "u8")), b)), [(9, "u8"), (10, "u8")], [(9, "u8"), (9, "u8")])
+case("quotient tensor, scalar", "nx/lib/nx.ex:6593-6597", lambda t: nx.quotient(t, 2), [([2, 4, 5], "s32")], [([1, 2, 2], "s32")])
+case("quotient scalar, tensor", "nx/lib/nx.ex:6599-6603", lambda t: nx.quotient(10, t), [([1, 2, 3], "s32")], [([10, 5, 3], "s32")])
+case("quotient broadcast s8", "nx/lib/nx.ex:6618-6627", lambda a, b: nx.quotient(a, b), [([[10, 20]], "s8"), ([[1], [2]], "s8")],
+     [([[10, 20], [5, 10]], "s8")])
+case("quotient u8 by u32", "nx/lib/nx.ex:6629-6638", lambda a, b: nx.quotient(a, b), [([[10, 20]], "u8"), ([[1], [2]], "u32")],
+     [([[10, 20], [5, 10]], "u32")])
+case("pow tensor, scalar", "nx/lib/nx.ex:6357-6361", lambda t: nx.pow(t, 2), [([1, 2, 3], "s32")], [([1, 4, 9], "s32")])
+case("pow scalar, f32 tensor", "nx/lib/nx.ex:6363-6367", lambda t: nx.pow(2, t), [([1.0, 2.0, 3.0], "f32")], [([2.0, 4.0, 8.0], "f32")],
+     exact=False)
+case("pow broadcast", "nx/lib/nx.ex:6371-6379", lambda a, b: nx.pow(a, b), [([[2], [3]], "s32"), ([[4, 5]], "s32")],
+     [([[16, 32], [81, 243]], "s32")])
+case("atan2 tensor, scalar", "nx/lib/nx.ex:6668-6672", lambda t: nx.atan2(t, 1), [([1, 2, 3], "s32")],
+     [([0.7853982, 1.1071488, 1.2490457], "f32")], exact=False)
+case("atan2 scalar, tensor", "nx/lib/nx.ex:6674-6678", lambda t: nx.atan2(1, t), [([1.0, 2.0, 3.0], "f32")],
+     [([0.7853982, 0.4636476, 0.32175055], "f32")], exact=False)
+case("atan2 signed zeros f64", "nx/lib/nx.ex:6682-6692", lambda a, b: nx.atan2(a, b), [([[-0.0], [0.0]], "f64"), ([-0.0, 0.0], "f64")],
+     [([[-3.141592653589793, -0.0], [3.141592653589793, 0.0]], "f64")], exact=False)
+case("max broadcast s8", "nx/lib/nx.ex:6745-6754", lambda a, b: nx.max(a, b), [([[1], [2]], "s8"), ([[10, 20]], "s8")],
+     [([[10, 20], [10, 20]], "s8")])
+case("max broadcast f32", "nx/lib/nx.ex:6756-6765", lambda a, b: nx.max(a, b), [([[1], [2]], "f32"), ([[10, 20]], "f32")],
+     [([[10.0, 20.0], [10.0, 20.0]], "f32")])
+case("bitwise_and tensor, scalar", "nx/lib/nx.ex:6883-6887", lambda t: nx.bitwise_and(t, 1), [([0, 1, 2], "s32")], [([0, 1, 0], "s32")])
+case("bitwise_and negative", "nx/lib/nx.ex:6889-6893", lambda t: nx.bitwise_and(t, -1), [([0, -1, -2], "s32")], [([0, -1, -2], "s32")])
+case("bitwise_and tensors", "nx/lib/nx.ex:6897-6901", lambda a, b: nx.bitwise_and(a, b), [([0, 0, 1, 1], "s32"), ([0, 1, 0, 1], "s32")],
+     [([0, 0, 0, 1], "s32")])
+case("bitwise_xor tensor, scalar", "nx/lib/nx.ex:6988-6992", lambda t: nx.bitwise_xor(t, 2), [([1, 2, 3], "s32")], [([3, 0, 1], "s32")])
+case("bitwise_xor negative", "nx/lib/nx.ex:6994-6998", lambda t: nx.bitwise_xor(t, 2), [([-1, -2, -3], "s32")], [([-3, -4, -1], "s32")])
+case("left_shift tensor, scalar", "nx/lib/nx.ex:7045-7049", lambda t: nx.left_shift(t, 2), [([1, 2, 3], "s32")], [([4, 8, 12], "s32")])
+case("left_shift tensors", "nx/lib/nx.ex:7053-7059", lambda a, b: nx.left_shift(a, b), [([1, 1, -1, -1], "s32"), ([1, 2, 3, 4], "s32")],
+     [([2, 4, -8, -16], "s32")])
+case("right_shift tensor, scalar", "nx/lib/nx.ex:7103-7107", lambda t: nx.right_shift(t, 2), [([2, 4, 8], "s32")], [([0, 1, 2], "s32")])
+case("right_shift tensors (arithmetic for signed)", "nx/lib/nx.ex:7111-7117", lambda a, b: nx.right_shift(a, b),
+     [([16, 32, -64, -128], "s32"), ([1, 2, 3, 4], "s32")], [([8, 8, -8, -8], "s32")])
+case("logical_and scalar, tensor", "nx/lib/nx.ex:7196-7200", lambda t: nx.logical_and(1, t), [([-1, 0, 1], "s32")], [([1, 0, 1], "u8")])
+case("logical_and broadcast, f32 with s32", "nx/lib/nx.ex:7214-7225", lambda a, b: nx.logical_and(a, b),
+     [([-1.0, 0.0, 1.0], "f32"), ([[-1], [0], [1]], "s32")], [([[1, 0, 1], [0, 0, 0], [1, 0, 1]], "u8")])
+case("logical_xor scalar, tensor", "nx/lib/nx.ex:7287-7291", lambda t: nx.logical_xor(0, t), [([-1, 0, 1], "s32")], [([1, 0, 1], "u8")])
+case("logical_xor broadcast", "nx/lib/nx.ex:7293-7304", lambda a, b: nx.logical_xor(a, b),
+     [([-1, 0, 1], "s32"), ([[-1], [0], [1]], "s32")], [([[0, 1, 0], [1, 0, 1], [0, 1, 0]], "u8")])
+
+# ---- clip: nx/lib/nx.ex:13906-13955 --------------------------------------------------------------------
+_T23 = [[1, 2, 3], [4, 5, 6]]
+case("clip s32", "nx/lib/nx.ex:13906-13914", lambda t: nx.clip(t, 2, 4), [(_T23, "s32")], [([[2, 2, 3], [4, 4, 4]], "s32")])
+case("clip s32 by a float bound", "nx/lib/nx.ex:13916-13924", lambda t: nx.clip(t, 2.0, 3), [(_T23, "s32")],
+     [([[2.0, 2.0, 3.0], [3.0, 3.0, 3.0]], "f32")])
+case("clip f32", "nx/lib/nx.ex:13936-13944", lambda t: nx.clip(t, 2, 6.0), [(_T23, "f32")], [([[2.0, 2.0, 3.0], [4.0, 5.0, 6.0]], "f32")])
+case("clip f32 integer bounds", "nx/lib/nx.ex:13946-13954", lambda t: nx.clip(t, 1, 4), [(_T23, "f32")],
+     [([[1.0, 2.0, 3.0], [4.0, 4.0, 4.0]], "f32")])
+
+# ---- reduce_min, product, all, any: nx/lib/nx.ex doctests ------------------------------------------------
+case("reduce_min", "nx/lib/nx.ex:10530-10534", lambda t: nx.reduce_min(t), [([1, 2, 3], "s32")], [(1, "s32")])
+case("reduce_min axis 0", "nx/lib/nx.ex:10538-10543", lambda t: nx.reduce_min(t, axes=[0]), [([[3, 1, 4], [2, 1, 1]], "s32")], [([2, 1, 1], "s32")])
+case("reduce_min axis 1", "nx/lib/nx.ex:10545-10550", lambda t: nx.reduce_min(t, axes=[1]), [([[3, 1, 4], [2, 1, 1]], "s32")], [([1, 1], "s32")])
+_M222 = [[[1, 2], [4, 5]], [[2, 4], [3, 8]]]
+case("reduce_min axes 0,2", "nx/lib/nx.ex:10552-10557", lambda t: nx.reduce_min(t, axes=[0, 2]), [(_M222, "s32")], [([1, 3], "s32")])
+case("reduce_min axes 0,2 keep", "nx/lib/nx.ex:10561-10572", lambda t: nx.reduce_min(t, axes=[0, 2], keep_axes=True), [(_M222, "s32")],
+     [([[[1], [3]]], "s32")])
+case("product", "nx/lib/nx.ex:10290-10294", lambda t: nx.product(t), [([1, 2, 3], "s32")], [(6, "s32")])
+case("product f32", "nx/lib/nx.ex:10296-10300", lambda t: nx.product(t), [([[1.0, 2.0], [3.0, 4.0]], "f32")], [(24.0, "f32")])
+case("product u8 -> u32", "nx/lib/nx.ex:10305-10309", lambda t: nx.product(t), [([[10, 20], [30, 40]], "u8")], [(240000, "u32")])
+case("product s8 -> s32", "nx/lib/nx.ex:10311-10315", lambda t: nx.product(t), [([[10, 20], [30, 40]], "s8")], [(240000, "s32")])
+_I223 = [[[0, 1, 2], [3, 4, 5]], [[6, 7, 8], [9, 10, 11]]]
+case("product axis 0", "nx/lib/nx.ex:10327-10335", lambda t: nx.product(t, axes=[0]), [(_I223, "s32")], [([[0, 7, 16], [27, 40, 55]], "s32")])
+case("product axis 1", "nx/lib/nx.ex:10336-10343", lambda t: nx.product(t, axes=[1]), [(_I223, "s32")], [([[0, 4, 10], [54, 70, 88]], "s32")])
+case("product axes 0,2", "nx/lib/nx.ex:10344-10348", lambda t: nx.product(t, axes=[0, 2]), [(_I223, "s32")], [([0, 59400], "s32")])
+case("all", "nx/lib/nx.ex:9155-9159", lambda t: nx.all(t), [([0, 1, 2], "s32")], [(0, "u8")])
+case("all axis 0", "nx/lib/nx.ex:9161-9165", lambda t: nx.all(t, axes=[0]), [([[-1, 0, 1], [2, 3, 4]], "s32")], [([1, 0, 1], "u8")])
+case("all axis 1", "nx/lib/nx.ex:9167-9171", lambda t: nx.all(t, axes=[1]), [([[-1, 0, 1], [2, 3, 4]], "s32")], [([0, 1], "u8")])
+case("all axis 1 keep", "nx/lib/nx.ex:9175-9182", lambda t: nx.all(t, axes=[1], keep_axes=True), [([[-1, 0, 1], [2, 3, 4]], "s32")],
+     [([[0], [1]], "u8")])
+case("any", "nx/lib/nx.ex:9228-9232", lambda t: nx.any(t), [([0, 1, 2], "s32")], [(1, "u8")])
+case("any axis 0", "nx/lib/nx.ex:9234-9238", lambda t: nx.any(t, axes=[0]), [([[0, 1, 0], [0, 1, 2]], "s32")], [([0, 1, 1], "u8")])
+case("any axis 1", "nx/lib/nx.ex:9240-9244", lambda t: nx.any(t, axes=[1]), [([[0, 1, 0], [0, 1, 2]], "s32")], [([1, 1], "u8")])
+case("any axis 1 keep", "nx/lib/nx.ex:9248-9255", lambda t: nx.any(t, axes=[1], keep_axes=True), [([[0, 1, 0], [0, 1, 2]], "s32")],
+     [([[1], [1]], "u8")])
