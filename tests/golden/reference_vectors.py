@@ -431,3 +431,46 @@ case("any axis 0", "nx/lib/nx.ex:9234-9238", lambda t: nx.any(t, axes=[0]), [([[
 case("any axis 1", "nx/lib/nx.ex:9240-9244", lambda t: nx.any(t, axes=[1]), [([[0, 1, 0], [0, 1, 2]], "s32")], [([1, 1], "u8")])
 case("any axis 1 keep", "nx/lib/nx.ex:9248-9255", lambda t: nx.any(t, axes=[1], keep_axes=True), [([[0, 1, 0], [0, 1, 2]], "s32")],
      [([[1], [1]], "u8")])
+
+# ---- element-wise unary operators and predicates: doctests of nx/lib/nx.ex --------------------------------
+case("sign", "nx/lib/nx.ex:8719-8723", lambda t: nx.sign(t), [([-2, -1, 0, 1, 2], "s32")], [([-1, -1, 0, 1, 1], "s32")])
+case("abs", "nx/lib/nx.ex:8738-8742", lambda t: nx.abs(t), [([-2, -1, 0, 1, 2], "s32")], [([2, 1, 0, 1, 2], "s32")])
+case("negate s32", "nx/lib/nx.ex:8681-8685", lambda t: nx.negate(t), [([-1, 0, 1], "s32")], [([1, 0, -1], "s32")])
+case("negate f32", "nx/lib/nx.ex:8687-8691", lambda t: nx.negate(t), [([1.0, 2.0, 3.0], "f32")], [([-1.0, -2.0, -3.0], "f32")])
+case("negate u8 wraps", "nx/lib/nx.ex:8695-8699", lambda t: nx.negate(t), [([0, 1, 2], "u8")], [([0, 255, 254], "u8")])
+case("bitwise_not s8", "nx/lib/nx.ex:8961-8965", lambda t: nx.bitwise_not(t), [([-1, 0, 1], "s8")], [([0, -1, -2], "s8")])
+case("bitwise_not u8", "nx/lib/nx.ex:8967-8971", lambda t: nx.bitwise_not(t), [([0, 1, 254, 255], "u8")], [([255, 254, 1, 0], "u8")])
+case("population_count s32", "nx/lib/nx.ex:9003-9007", lambda t: nx.population_count(t), [([0, 1, 254, 255], "s32")], [([0, 1, 7, 8], "s32")])
+case("population_count s8", "nx/lib/nx.ex:9009-9013", lambda t: nx.population_count(t), [([0, 1, 126, 127, -1, -127, -128], "s8")],
+     [([0, 1, 6, 7, 8, 2, 1], "s8")])
+case("count_leading_zeros s32", "nx/lib/nx.ex:9045-9049", lambda t: nx.count_leading_zeros(t), [([0, 0xF, 0xFF, 0xFFFF], "s32")],
+     [([32, 28, 24, 16], "s32")])
+case("count_leading_zeros s64", "nx/lib/nx.ex:9057-9061", lambda t: nx.count_leading_zeros(t), [([0, 0xF, 0xFF, 0xFFFF], "s64")],
+     [([64, 60, 56, 48], "s64")])
+case("count_leading_zeros s16", "nx/lib/nx.ex:9063-9067", lambda t: nx.count_leading_zeros(t), [([0, 0xF, 0xFF, 0xFFFF], "s16")],
+     [([16, 12, 8, 0], "s16")])
+case("is_nan", "nx/lib/nx.ex:8609-8613", lambda t: nx.is_nan(t), [([NAN, 1, 0], "f32")], [([1, 0, 0], "u8")])
+case("is_infinity", "nx/lib/nx.ex:8642-8646", lambda t: nx.is_infinity(t), [([INF, NAN, -INF, 1, 0], "f32")], [([1, 0, 1, 0, 0], "u8")])
+case("less tensors", "nx/lib/nx.ex:7519-7523", lambda a, b: nx.less(a, b), [([1, 2, 1], "s32"), ([1, 2, 2], "s32")], [([0, 0, 1], "u8")])
+case("less f32 with s32, broadcast", "nx/lib/nx.ex:7525-7532", lambda a, b: nx.less(a, b),
+     [([[1.0, 2.0, 3.0], [4.0, 2.0, 1.0]], "f32"), ([1, 2, 3], "s32")], [([[0, 0, 0], [0, 0, 1]], "u8")])
+
+# ---- shape operators: doctests of nx/lib/nx.ex -----------------------------------------------------------
+_I234 = [[[0, 1, 2, 3], [4, 5, 6, 7], [8, 9, 10, 11]], [[12, 13, 14, 15], [16, 17, 18, 19], [20, 21, 22, 23]]]
+_I234_T = [[[0, 12], [4, 16], [8, 20]], [[1, 13], [5, 17], [9, 21]], [[2, 14], [6, 18], [10, 22]], [[3, 15], [7, 19], [11, 23]]]
+case("transpose default (reverse axes)", "nx/lib/nx.ex:13283-13308", lambda t: nx.transpose(t), [(_I234, "s32")], [(_I234_T, "s32")])
+case("transpose axes [2,1,0]", "nx/lib/nx.ex:13316-13341", lambda t: nx.transpose(t, axes=[2, 1, 0]), [(_I234, "s32")], [(_I234_T, "s32")])
+case("broadcast column to the shape of a tensor", "nx/lib/nx.ex:3792-3799", lambda a: nx.broadcast(a, (2, 2)), [([[1], [2]], "s32")],
+     [([[1, 1], [2, 2]], "s32")])
+case("broadcast row", "nx/lib/nx.ex:3801-3808", lambda a: nx.broadcast(a, (2, 2)), [([[1, 2]], "s32")], [([[1, 2], [1, 2]], "s32")])
+case("broadcast with axes", "nx/lib/nx.ex:3838-3847", lambda t: nx.broadcast(t, (3, 2), axes=[0]), [([1, 2, 3], "s32")],
+     [([[1, 1], [2, 2], [3, 3]], "s32")])
+case("concatenate merges types", "nx/lib/nx.ex:15241-15264", lambda a, b, c: nx.concatenate([a, b, c], axis=0),
+     [([[[0, 1], [2, 3]], [[4, 5], [6, 7]]], "f32"), ([[[0, 1], [2, 3]]], "u8"), ([[[0, 1], [2, 3]]], "s64")],
+     [([[[0.0, 1.0], [2.0, 3.0]], [[4.0, 5.0], [6.0, 7.0]], [[0.0, 1.0], [2.0, 3.0]], [[0.0, 1.0], [2.0, 3.0]]], "f32")])
+case("concatenate axis 1", "nx/lib/nx.ex:15269-15285", lambda a, b, c: nx.concatenate([a, b, c], axis=1),
+     [([[[0, 1], [2, 3], [4, 5]]], "s32"), ([[[0, 1]]], "s32"), ([[[0, 1], [2, 3]]], "s32")],
+     [([[[0, 1], [2, 3], [4, 5], [0, 1], [0, 1], [2, 3]]], "s32")])
+case("iota over all axes / along an axis", "nx/lib/nx.ex:1118-1145",
+     lambda t: (nx.add(nx.iota((3, 2, 3)), t), nx.add(nx.iota((3, 3), axis=1), t)), [(0, "s32")],
+     [([[[0, 1, 2], [3, 4, 5]], [[6, 7, 8], [9, 10, 11]], [[12, 13, 14], [15, 16, 17]]], "s32"), ([[0, 1, 2], [0, 1, 2], [0, 1, 2]], "s32")])
