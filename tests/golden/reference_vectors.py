@@ -474,3 +474,29 @@ case("concatenate axis 1", "nx/lib/nx.ex:15269-15285", lambda a, b, c: nx.concat
 case("iota over all axes / along an axis", "nx/lib/nx.ex:1118-1145",
      lambda t: (nx.add(nx.iota((3, 2, 3)), t), nx.add(nx.iota((3, 3), axis=1), t)), [(0, "s32")],
      [([[[0, 1, 2], [3, 4, 5]], [[6, 7, 8], [9, 10, 11]], [[12, 13, 14], [15, 16, 17]]], "s32"), ([[0, 1, 2], [0, 1, 2], [0, 1, 2]], "s32")])
+
+# ---- mean, logical_not, comparisons, slice_along_axis: doctests of nx/lib/nx.ex ----------------------------
+case("mean", "nx/lib/nx.ex:9650-9654", lambda t: nx.mean(t), [([1, 2, 3], "s32")], [(2.0, "f32")], exact=False)
+case("mean u8 axis 0", "nx/lib/nx.ex:9664-9668", lambda t: nx.mean(t, axes=[0]), [([1, 2, 3], "u8")], [(2.0, "f32")], exact=False)
+case("mean axis 0 of iota {2,2,3}", "nx/lib/nx.ex:9670-9678", lambda t: nx.mean(t, axes=[0]), [(_I223, "s32")],
+     [([[3.0, 4.0, 5.0], [6.0, 7.0, 8.0]], "f32")], exact=False)
+case("mean axes 0,2", "nx/lib/nx.ex:9680-9685", lambda t: nx.mean(t, axes=[0, 2]), [(_I223, "s32")], [([4.0, 7.0], "f32")], exact=False)
+case("mean axis -1", "nx/lib/nx.ex:9687-9695", lambda t: nx.mean(t, axes=[-1]), [(_I223, "s32")], [([[1.0, 4.0], [7.0, 10.0]], "f32")],
+     exact=False)
+case("mean axis -1 keep", "nx/lib/nx.ex:9699-9715", lambda t: nx.mean(t, axes=[-1], keep_axes=True), [(_I223, "s32")],
+     [([[[1.0], [4.0]], [[7.0], [10.0]]], "f32")], exact=False)
+case("logical_not s32", "nx/lib/nx.ex:7332-7336", lambda t: nx.logical_not(t), [([-1, 0, 1], "s32")], [([0, 1, 0], "u8")])
+case("logical_not f32", "nx/lib/nx.ex:7338-7342", lambda t: nx.logical_not(t), [([-1.0, 0.0, 1.0], "f32")], [([0, 1, 0], "u8")])
+case("not_equal", "nx/lib/nx.ex:7413-7419", lambda a, b: nx.not_equal(a, b), [([1, 1, 2], "s32"), ([1, 2, 3], "s32")], [([0, 1, 1], "u8")])
+case("not_equal matrices", "nx/lib/nx.ex:7421-7430", lambda a, b: nx.not_equal(a, b),
+     [([[1, 4, 2], [4, 5, 6]], "s32"), ([[1, 3, 2], [4, 2, 1]], "s32")], [([[0, 1, 0], [0, 1, 1]], "u8")])
+_I52 = [[0, 1], [2, 3], [4, 5], [6, 7], [8, 9]]
+_I25 = [[0, 1, 2, 3, 4], [5, 6, 7, 8, 9]]
+case("slice_along_axis axis 0", "nx/lib/nx.ex:14324-14331", lambda t: nx.slice_along_axis(t, 1, 2, axis=0), [(_I52, "s32")],
+     [([[2, 3], [4, 5]], "s32")])
+case("slice_along_axis axis 1", "nx/lib/nx.ex:14333-14340", lambda t: nx.slice_along_axis(t, 1, 2, axis=1), [(_I25, "s32")],
+     [([[1, 2], [6, 7]], "s32")])
+case("slice_along_axis tensor start", "nx/lib/nx.ex:14350-14356", lambda t, s: nx.slice_along_axis(t, s, 1, axis=0), [(_I25, "s32"), (0, "s32")],
+     [([[0, 1, 2, 3, 4]], "s32")])
+case("slice_along_axis strides", "nx/lib/nx.ex:14358-14365", lambda t: nx.slice_along_axis(t, 0, 3, axis=-1, strides=2), [(_I25, "s32")],
+     [([[0, 2], [5, 7]], "s32")])
