@@ -500,3 +500,22 @@ case("slice_along_axis tensor start", "nx/lib/nx.ex:14350-14356", lambda t, s: n
      [([[0, 1, 2, 3, 4]], "s32")])
 case("slice_along_axis strides", "nx/lib/nx.ex:14358-14365", lambda t: nx.slice_along_axis(t, 0, 3, axis=-1, strides=2), [(_I25, "s32")],
      [([[0, 2], [5, 7]], "s32")])
+
+# ---- binary broadcast: nx/test/nx_test.exs:37-147 (each pair in both orders, as the test's `commute` does) ----
+_BROADCASTS = [
+    ("{2,1} + {1,2}", "nx/test/nx_test.exs:38-47", [[1], [2]], [[10, 20]], [[11, 21], [12, 22]]),
+    ("{2} + {2,2}", "nx/test/nx_test.exs:49-58", [1, 2], [[1, 2], [3, 4]], [[2, 4], [4, 6]]),
+    ("{1,2,1} + {2,1,2}", "nx/test/nx_test.exs:60-74", [[[10], [20]]], [[[1, 2]], [[3, 4]]], [[[11, 12], [21, 22]], [[13, 14], [23, 24]]]),
+    ("{1,3,1} + {4,1,3}", "nx/test/nx_test.exs:76-96", [[[100], [200], [300]]], [[[1, 2, 3]], [[4, 5, 6]], [[7, 8, 9]], [[10, 11, 12]]],
+     [[[101, 102, 103], [201, 202, 203], [301, 302, 303]], [[104, 105, 106], [204, 205, 206], [304, 305, 306]],
+      [[107, 108, 109], [207, 208, 209], [307, 308, 309]], [[110, 111, 112], [210, 211, 212], [310, 311, 312]]]),
+    ("{1,2,2,1} + {2,1,2}", "nx/test/nx_test.exs:98-112", [[[[10], [20]], [[30], [40]]]], [[[1, 2]], [[3, 4]]],
+     [[[[11, 12], [21, 22]], [[33, 34], [43, 44]]]]),
+    ("{1,2,2,1} + {2,1,1,2}", "nx/test/nx_test.exs:114-130", [[[[10], [20]], [[30], [40]]]], [[[[1, 2]]], [[[3, 4]]]],
+     [[[[11, 12], [21, 22]], [[31, 32], [41, 42]]], [[[13, 14], [23, 24]], [[33, 34], [43, 44]]]]),
+    ("{2,2,1} + {2,1,2}", "nx/test/nx_test.exs:132-146", [[[10], [20]], [[30], [40]]], [[[1, 2]], [[3, 4]]],
+     [[[11, 12], [21, 22]], [[33, 34], [43, 44]]]),
+]
+for _name, _cite, _a, _b, _want in _BROADCASTS:
+    case("broadcast add " + _name, _cite, lambda a, b: nx.add(a, b), [(_a, "s32"), (_b, "s32")], [(_want, "s32")])
+    case("broadcast add " + _name + " (commuted)", _cite, lambda a, b: nx.add(a, b), [(_b, "s32"), (_a, "s32")], [(_want, "s32")])
