@@ -519,3 +519,12 @@ _BROADCASTS = [
 for _name, _cite, _a, _b, _want in _BROADCASTS:
     case("broadcast add " + _name, _cite, lambda a, b: nx.add(a, b), [(_a, "s32"), (_b, "s32")], [(_want, "s32")])
     case("broadcast add " + _name + " (commuted)", _cite, lambda a, b: nx.add(a, b), [(_b, "s32"), (_a, "s32")], [(_want, "s32")])
+
+# ---- reduce_min / reduce_max over non-finite rows: nx/test/nx_test.exs:1645-1744 -------------------------
+case("reduce_min non-finite", "nx/test/nx_test.exs:1646-1678", lambda t: nx.reduce_min(t, axes=[1]), [(NONFINITE, "f32")],
+     [([-INF, NAN, -INF, -INF, 1, NAN, -INF, 0, NAN, NAN, NAN, NAN], "f32")])
+case("reduce_max non-finite", "nx/test/nx_test.exs:1711-1743", lambda t: nx.reduce_max(t, axes=[1]), [(NONFINITE, "f32")],
+     [([INF, NAN, 1, 1, INF, NAN, INF, INF, NAN, NAN, NAN, NAN], "f32")])
+case("reduce_min all axes / axis 0 / keep", "nx/test/nx_test.exs:1680-1707",
+     lambda t: (nx.reduce_min(t), nx.reduce_min(t, axes=[0]), nx.reduce_min(t, axes=[0], keep_axes=True), nx.reduce_min(t, keep_axes=True)),
+     [([[1, 2, 3], [3, 1, 2]], "s32")], [(1, "s32"), ([1, 1, 2], "s32"), ([[1, 1, 2]], "s32"), ([[1]], "s32")])
