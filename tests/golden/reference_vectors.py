@@ -528,3 +528,28 @@ case("reduce_max non-finite", "nx/test/nx_test.exs:1711-1743", lambda t: nx.redu
 case("reduce_min all axes / axis 0 / keep", "nx/test/nx_test.exs:1680-1707",
      lambda t: (nx.reduce_min(t), nx.reduce_min(t, axes=[0]), nx.reduce_min(t, axes=[0], keep_axes=True), nx.reduce_min(t, keep_axes=True)),
      [([[1, 2, 3], [3, 1, 2]], "s32")], [(1, "s32"), ([1, 1, 2], "s32"), ([[1, 1, 2]], "s32"), ([[1]], "s32")])
+
+# ---- dot with general contraction and batch axes: nx/test/nx_test.exs:1877-1975 -----------------------------
+case("dot by a scalar", "nx/test/nx_test.exs:1878-1884", lambda t: nx.dot(t, 3), [([[1, 2, 3]], "s32")], [([[3, 6, 9]], "s32")])
+case("dot/4 keeps the order of the contracting axes", "nx/test/nx_test.exs:1888-1910",
+     lambda a, b: nx.dot(a, [3, 1, 2], [], b, [2, 3, 1], []),
+     [(_iota_list((2, 7, 8, 3, 1)), "s32"), (_iota_list((1, 8, 3, 7, 3)), "s32")],
+     [([[[[3731448, 3745476, 3759504]]], [[[10801560, 10843812, 10886064]]]], "s32")])
+case("dot/6 batched, different free sizes", "nx/test/nx_test.exs:1914-1920",
+     lambda a, b: nx.dot(a, [1, 2], [0], b, [2, 1], [0]),
+     [(_iota_list((3, 2, 4, 1)), "s32"), (_iota_list((3, 4, 2, 2)), "s32")], [([[[252, 280]], [[2172, 2264]], [[6140, 6296]]], "s32")])
+case("dot/6 two batch axes", "nx/test/nx_test.exs:1922-1966",
+     lambda a, b: nx.dot(a, [2], [0, 1], b, [3], [0, 1]),
+     [(_iota_list((3, 2, 1, 3, 2)), "s32"), (_iota_list((3, 2, 1, 1, 4)), "s32")],
+     [([[[[[[0, 0, 0, 0]], [[0, 1, 2, 3]]], [[[0, 2, 4, 6]], [[0, 3, 6, 9]]], [[[0, 4, 8, 12]], [[0, 5, 10, 15]]]],
+         [[[[24, 30, 36, 42]], [[28, 35, 42, 49]]], [[[32, 40, 48, 56]], [[36, 45, 54, 63]]], [[[40, 50, 60, 70]], [[44, 55, 66, 77]]]]],
+        [[[[[96, 108, 120, 132]], [[104, 117, 130, 143]]], [[[112, 126, 140, 154]], [[120, 135, 150, 165]]],
+          [[[128, 144, 160, 176]], [[136, 153, 170, 187]]]],
+         [[[[216, 234, 252, 270]], [[228, 247, 266, 285]]], [[[240, 260, 280, 300]], [[252, 273, 294, 315]]],
+          [[[264, 286, 308, 330]], [[276, 299, 322, 345]]]]],
+        [[[[[384, 408, 432, 456]], [[400, 425, 450, 475]]], [[[416, 442, 468, 494]], [[432, 459, 486, 513]]],
+          [[[448, 476, 504, 532]], [[464, 493, 522, 551]]]],
+         [[[[600, 630, 660, 690]], [[620, 651, 682, 713]]], [[[640, 672, 704, 736]], [[660, 693, 726, 759]]],
+          [[[680, 714, 748, 782]], [[700, 735, 770, 805]]]]]], "s32")])
+case("dot/6 batch axis of size 1", "nx/test/nx_test.exs:1968-1971", lambda t: nx.dot(t, [2], [0], t, [2], [0]),
+     [([[[1, 2, 3], [4, 5, 6]]], "s32")], [([[[14, 32], [32, 77]]], "s32")])
