@@ -553,3 +553,10 @@ case("dot/6 two batch axes", "nx/test/nx_test.exs:1922-1966",
           [[[680, 714, 748, 782]], [[700, 735, 770, 805]]]]]], "s32")])
 case("dot/6 batch axis of size 1", "nx/test/nx_test.exs:1968-1971", lambda t: nx.dot(t, [2], [0], t, [2], [0]),
      [([[[1, 2, 3], [4, 5, 6]]], "s32")], [([[[14, 32], [32, 77]]], "s32")])
+
+# ---- clip with infinite bounds, concatenate along a middle axis: nx/test/nx_test.exs:2308-2344 -------------
+case("clip with infinite bounds", "nx/test/nx_test.exs:2308-2311", lambda t: nx.clip(t, -INF, INF), [([1.0, 2.0, 3.0], "f32")],
+     [([1.0, 2.0, 3.0], "f32")])
+case("concatenate middle axis", "nx/test/nx_test.exs:2317-2342",
+     lambda t: nx.concatenate([t, nx.add(t, 10), nx.add(t, 20)], axis=1), [(_iota_list((2, 2, 2)), "s32")],
+     [([[[0, 1], [2, 3], [10, 11], [12, 13], [20, 21], [22, 23]], [[4, 5], [6, 7], [14, 15], [16, 17], [24, 25], [26, 27]]], "s32")])
