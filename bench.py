@@ -101,7 +101,17 @@ class ClockSampler:
         try:
             import pynvml
             pynvml.nvmlInit()
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.handle = None
+            try:
+                # the CUDA device's PCI address: NVML numbers devices without regard to CUDA_VISIBLE_DEVICES
+                import torch
+                pr = torch.cuda.get_device_properties(index)
+                bus_id = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+                self.handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+            except Exception:
+                self.handle = None
+            if self.handle is None:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
             self.nvml = pynvml
             self.period = min(period_ms, 2) / 1e3
