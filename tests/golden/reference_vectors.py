@@ -560,3 +560,42 @@ case("clip with infinite bounds", "nx/test/nx_test.exs:2308-2311", lambda t: nx.
 case("concatenate middle axis", "nx/test/nx_test.exs:2317-2342",
      lambda t: nx.concatenate([t, nx.add(t, 10), nx.add(t, 20)], axis=1), [(_iota_list((2, 2, 2)), "s32")],
      [([[[0, 1], [2, 3], [10, 11], [12, 13], [20, 21], [22, 23]], [[4, 5], [6, 7], [14, 15], [16, 17], [24, 25], [26, 27]]], "s32")])
+
+# ---- window aggregates with "same" padding, strides and dilations: nx/test/nx_test.exs:828-960 -------------
+case("window_sum strides, padding, dilations", "nx/test/nx_test.exs:829-855",
+     lambda t: nx.window_sum(t, (2, 1, 2), strides=[2, 1, 1], padding=[(2, 1), (3, 1), (1, 0)], window_dilations=[1, 2, 2]),
+     [([[[4, 2, 1, 3], [4, 2, 1, 7]], [[1, 2, 5, 7], [1, 8, 9, 2]]], "s32")],
+     [([[[0, 0, 0]] * 6, [[0, 0, 0], [0, 0, 0], [0, 0, 0], [4, 11, 14], [10, 15, 19], [0, 0, 0]]], "s32")])
+_I33 = _iota_list((3, 3))
+case("window_sum same f64", "nx/test/nx_test.exs:857-862", lambda t: nx.window_sum(t, (2, 1), padding="same"), [(_I33, "f64")],
+     [([[3.0, 5.0, 7.0], [9.0, 11.0, 13.0], [6.0, 7.0, 8.0]], "f64")])
+case("window_product same f64", "nx/test/nx_test.exs:864-869", lambda t: nx.window_product(t, (2, 1), padding="same"), [(_I33, "f64")],
+     [([[0.0, 4.0, 10.0], [18.0, 28.0, 40.0], [6.0, 7.0, 8.0]], "f64")])
+case("window_max same f64", "nx/test/nx_test.exs:871-876", lambda t: nx.window_max(t, (2, 1), padding="same"), [(_I33, "f64")],
+     [([[3, 4, 5], [6, 7, 8], [6, 7, 8]], "f64")])
+case("window_min same f64", "nx/test/nx_test.exs:941-946", lambda t: nx.window_min(t, (2, 1), padding="same"), [(_I33, "f64")],
+     [([[0.0, 1.0, 2.0], [3.0, 4.0, 5.0], [6.0, 7.0, 8.0]], "f64")])
+case("window_max same, large kernel, strides", "nx/test/nx_test.exs:878-888",
+     lambda t: nx.window_max(t, (1, 3, 3, 1), padding="same", strides=[1, 2, 2, 1]), [(_iota_list((1, 4, 4, 1)), "f32")],
+     [([[[[5.0], [7.0]], [[13.0], [15.0]]]], "f32")])
+case("window_max same, asymmetric kernel", "nx/test/nx_test.exs:890-900",
+     lambda t: nx.window_max(t, (1, 2, 3, 1), padding="same", strides=[1, 2, 2, 1]), [(_iota_list((1, 4, 6, 1)), "f32")],
+     [([[[[7.0], [9.0], [11.0]], [[19.0], [21.0], [23.0]]]], "f32")])
+case("window_max same, kernel larger than input", "nx/test/nx_test.exs:902-907",
+     lambda t: nx.window_max(t, (1, 3, 3, 1), padding="same", strides=[1, 1, 1, 1]), [(_iota_list((1, 2, 2, 1)), "f32")],
+     [([[[[3.0], [3.0]], [[3.0], [3.0]]]], "f32")])
+case("window_max same, kernel equal to input", "nx/test/nx_test.exs:909-914",
+     lambda t: nx.window_max(t, (4, 4), padding="same", strides=[2, 2]), [(_iota_list((4, 4)), "f32")], [([[10.0, 11.0], [14.0, 15.0]], "f32")])
+case("window_max same 1D", "nx/test/nx_test.exs:916-921", lambda t: nx.window_max(t, (3,), padding="same", strides=[2]),
+     [(_iota_list((8,)), "f32")], [([1.0, 3.0, 5.0, 7.0], "f32")])
+case("window_max same 2D", "nx/test/nx_test.exs:923-928", lambda t: nx.window_max(t, (3, 3), padding="same", strides=[2, 2]),
+     [(_iota_list((4, 4)), "f32")], [([[5.0, 7.0], [13.0, 15.0]], "f32")])
+case("window_max same, stride larger than kernel", "nx/test/nx_test.exs:930-935",
+     lambda t: nx.window_max(t, (1, 2, 2, 1), padding="same", strides=[1, 3, 3, 1]), [(_iota_list((1, 6, 6, 1)), "f32")],
+     [([[[[7.0], [10.0]], [[25.0], [28.0]]]], "f32")])
+case("window_min same, large kernel", "nx/test/nx_test.exs:937-942",
+     lambda t: nx.window_min(t, (1, 3, 3, 1), padding="same", strides=[1, 2, 2, 1]), [(_iota_list((1, 4, 4, 1)), "f32")],
+     [([[[[0.0], [1.0]], [[4.0], [5.0]]]], "f32")])
+case("window_max dilations, strides, same", "nx/test/nx_test.exs:948-958",
+     lambda t: nx.window_max(t, (1, 2, 2, 1), padding="same", strides=[1, 2, 2, 1], window_dilations=[1, 2, 2, 1]),
+     [(_iota_list((1, 4, 4, 1)), "f32")], [([[[[5.0], [7.0]], [[13.0], [15.0]]]], "f32")])
