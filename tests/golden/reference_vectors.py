@@ -599,3 +599,11 @@ case("window_min same, large kernel", "nx/test/nx_test.exs:937-942",
 case("window_max dilations, strides, same", "nx/test/nx_test.exs:948-958",
      lambda t: nx.window_max(t, (1, 2, 2, 1), padding="same", strides=[1, 2, 2, 1], window_dilations=[1, 2, 2, 1]),
      [(_iota_list((1, 4, 4, 1)), "f32")], [([[[[5.0], [7.0]], [[13.0], [15.0]]]], "f32")])
+
+# ---- sort / argsort along a leading axis: nx/test/nx_test.exs:2350-2466 ---------------------------------
+_S432 = [[[4, 5], [2, 5], [5, 0]], [[1, 9], [2, 1], [2, 1]], [[0, -1], [-1, 0], [0, -1]], [[-1, 0], [0, -1], [-1, 0]]]
+case("sort 1D", "nx/test/nx_test.exs:2351-2354", lambda t: nx.sort(t), [([3, 2, 1, 0], "s32")], [([0, 1, 2, 3], "s32")])
+case("sort axis 0 of {4,3,2}", "nx/test/nx_test.exs:2356-2410", lambda t: nx.sort(t, axis=0), [(_S432, "s32")],
+     [([[[-1, -1], [-1, -1], [-1, -1]], [[0, 0], [0, 0], [0, 0]], [[1, 5], [2, 1], [2, 0]], [[4, 9], [2, 5], [5, 1]]], "s32")])
+case("argsort axis 0 of {4,3,2}", "nx/test/nx_test.exs:2428-2466", lambda t: nx.argsort(t, axis=0), [(_S432, "s32")],
+     [([[[3, 2], [2, 3], [3, 2]], [[2, 3], [3, 2], [2, 0]], [[1, 0], [0, 1], [1, 3]], [[0, 1], [1, 0], [0, 1]]], "s32")])
