@@ -607,3 +607,21 @@ case("sort axis 0 of {4,3,2}", "nx/test/nx_test.exs:2356-2410", lambda t: nx.sor
      [([[[-1, -1], [-1, -1], [-1, -1]], [[0, 0], [0, 0], [0, 0]], [[1, 5], [2, 1], [2, 0]], [[4, 9], [2, 5], [5, 1]]], "s32")])
 case("argsort axis 0 of {4,3,2}", "nx/test/nx_test.exs:2428-2466", lambda t: nx.argsort(t, axis=0), [(_S432, "s32")],
      [([[[3, 2], [2, 3], [3, 2]], [[2, 3], [3, 2], [2, 0]], [[1, 0], [0, 1], [1, 3]], [[0, 1], [1, 0], [0, 1]]], "s32")])
+
+# ---- convolution, valid padding: nx/test/nx_test.exs:155-258 ----------------------------------------------
+_C2244 = _iota_list((2, 2, 4, 4))
+case("conv valid, 2x2 kernel", "nx/test/nx_test.exs:156-180", lambda t, k: nx.conv(t, k, strides=[1, 1], padding="valid"),
+     [(_C2244, "f32"), (_iota_list((1, 2, 2, 2)), "f32")],
+     [([[[[440.0, 468.0, 496.0], [552.0, 580.0, 608.0], [664.0, 692.0, 720.0]]],
+        [[[1336.0, 1364.0, 1392.0], [1448.0, 1476.0, 1504.0], [1560.0, 1588.0, 1616.0]]]], "f32")], exact=False)
+case("conv valid, kernel as large as the input, 8 filters", "nx/test/nx_test.exs:182-207",
+     lambda t, k: nx.conv(t, k, strides=[1, 1], padding="valid"), [(_C2244, "f32"), (_iota_list((8, 2, 4, 4)), "f32")],
+     [([[[[10416.0]], [[26288.0]], [[42160.0]], [[58032.0]], [[73904.0]], [[89776.0]], [[105648.0]], [[121520.0]]],
+        [[[26288.0]], [[74928.0]], [[123568.0]], [[172208.0]], [[220848.0]], [[269488.0]], [[318128.0]], [[366768.0]]]], "f32")], exact=False)
+case("conv valid, 3x3 kernel, 2 filters", "nx/test/nx_test.exs:209-236", lambda t, k: nx.conv(t, k, strides=[1, 1], padding="valid"),
+     [(_C2244, "f32"), (_iota_list((2, 2, 3, 3)), "f32")],
+     [([[[[2793.0, 2946.0], [3405.0, 3558.0]], [[7005.0, 7482.0], [8913.0, 9390.0]]],
+        [[[7689.0, 7842.0], [8301.0, 8454.0]], [[22269.0, 22746.0], [24177.0, 24654.0]]]], "f32")], exact=False)
+case("conv valid, strides 2x1", "nx/test/nx_test.exs:239-258", lambda t, k: nx.conv(t, k, strides=[2, 1], padding="valid"),
+     [(_C2244, "f32"), (_iota_list((1, 2, 2, 2)), "f32")],
+     [([[[[440.0, 468.0, 496.0], [664.0, 692.0, 720.0]]], [[[1336.0, 1364.0, 1392.0], [1560.0, 1588.0, 1616.0]]]], "f32")], exact=False)
