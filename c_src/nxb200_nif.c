@@ -227,6 +227,111 @@ static ERL_NIF_TERM from_ipc(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]
   return st ? raise_status(env, st) : wrap_buf(env, b);
 }
 
+/* buffer_alloc(device, type_code, shape): an uninitialised device tensor (outputs of program_run_into) */
+static ERL_NIF_TERM buffer_alloc(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  int dev, dtype, rank;
+  int64_t dims[NXB_MAX_RANK];
+  if (argc != 3 || !enif_get_int(env, argv[0], &dev) || !enif_get_int(env, argv[1], &dtype) || !get_shape(env, argv[2], dims, &rank))
+    return BADARG(env);
+  nxb200_buffer *b = NULL;
+  int st = nxb200_buffer_alloc(dev, (nxb200_dtype)dtype, dims, rank, &b);
+  return st ? raise_status(env, st) : wrap_buf(env, b);
+}
+
+/* from_binary_async(device, type_code, shape, binary, pid, ref): the upload is queued and the call
+ * returns; the binary is held in a private environment until the library has read its last byte, then
+ * `{:nxb200_upload_done, ref}` is sent to `pid` and the environment is freed (exla_client.cc:118-151). */
+typedef struct { ErlNifEnv *env; ErlNifPid to; ERL_NIF_TERM ref; } upload_ctx;
+
+static void upload_done(void *p) {
+  upload_ctx *u = p;
+  ERL_NIF_TERM msg = enif_make_tuple2(u->env, enif_make_atom(u->env, "nxb200_upload_done"), u->ref);
+  enif_send(NULL, &u->to, u->env, msg);      /* from a thread of the library: no calling environment */
+  enif_free_env(u->env);                     /* releases the binary */
+  enif_free(u);
+}
+
+static ERL_NIF_TERM from_binary_async(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  int dev, dtype, rank;
+  int64_t dims[NXB_MAX_RANK];
+  ErlNifBinary bin;
+  upload_ctx *u;
+  if (argc != 6 || !enif_get_int(env, argv[0], &dev) || !enif_get_int(env, argv[1], &dtype) || !get_shape(env, argv[2], dims, &rank))
+    return BADARG(env);
+  u = enif_alloc(sizeof *u);
+  u->env = enif_alloc_env();
+  ERL_NIF_TERM held = enif_make_copy(u->env, argv[3]);          /* refc binaries are shared, not copied */
+  u->ref = enif_make_copy(u->env, argv[5]);
+  if (!enif_get_local_pid(env, argv[4], &u->to) || !enif_inspect_binary(u->env, held, &bin)) {
+    enif_free_env(u->env);
+    enif_free(u);
+    return BADARG(env);
+  }
+  nxb200_buffer *b = NULL;
+  int st = nxb200_buffer_from_host_async(dev, (nxb200_dtype)dtype, dims, rank, bin.data, bin.size, upload_done, u, &b);
+  if (st) {                                                     /* nothing was queued: the callback will not run */
+    enif_free_env(u->env);
+    enif_free(u);
+    return raise_status(env, st);
+  }
+  return wrap_buf(env, b);
+}
+
+/* Transfers that complete at the next device_synchronize.  The host side of such a transfer is a
+ * page-locked region owned by a resource (host_region), so that its address is stable and the BEAM
+ * never sees it move; region_binary gives its bytes after the synchronisation. */
+static ErlNifResourceType *HOST_TYPE;
+typedef struct { void *ptr; size_t size; } host_res;
+static void host_dtor(ErlNifEnv *env, void *p) { (void)env; host_res *r = p; if (r->ptr) enif_free(r->ptr); }
+
+static ERL_NIF_TERM host_region(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  ErlNifUInt64 n;
+  if (argc != 1 || !enif_get_uint64(env, argv[0], &n)) return BADARG(env);
+  host_res *r = enif_alloc_resource(HOST_TYPE, sizeof *r);
+  r->ptr = enif_alloc((size_t)n);          /* (a production build registers the pages with cudaHostRegister) */
+  r->size = (size_t)n;
+  ERL_NIF_TERM t = enif_make_resource(env, r);
+  enif_release_resource(r);
+  return t;
+}
+
+static ERL_NIF_TERM region_write(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  host_res *r;
+  ErlNifBinary bin;
+  if (argc != 2 || !enif_get_resource(env, argv[0], HOST_TYPE, (void **)&r) || !enif_inspect_binary(env, argv[1], &bin) || bin.size > r->size)
+    return BADARG(env);
+  memcpy(r->ptr, bin.data, bin.size);
+  return atom_ok;
+}
+
+static ERL_NIF_TERM region_binary(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  host_res *r;
+  if (argc != 1 || !enif_get_resource(env, argv[0], HOST_TYPE, (void **)&r)) return BADARG(env);
+  return enif_make_resource_binary(env, r, r->ptr, r->size);
+}
+
+static ERL_NIF_TERM write_async(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  nxb200_buffer *b;
+  host_res *r;
+  ErlNifUInt64 n;
+  if (argc != 3 || !(b = get_buf(env, argv[0])) || !enif_get_resource(env, argv[1], HOST_TYPE, (void **)&r) ||
+      !enif_get_uint64(env, argv[2], &n) || n > r->size)
+    return BADARG(env);
+  int st = nxb200_buffer_write_async(b, r->ptr, (size_t)n);
+  return st ? raise_status(env, st) : atom_ok;
+}
+
+static ERL_NIF_TERM read_async(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  nxb200_buffer *b;
+  host_res *r;
+  ErlNifUInt64 n;
+  if (argc != 3 || !(b = get_buf(env, argv[0])) || !enif_get_resource(env, argv[1], HOST_TYPE, (void **)&r) ||
+      !enif_get_uint64(env, argv[2], &n) || n > r->size)
+    return BADARG(env);
+  int st = nxb200_buffer_read_async(b, r->ptr, (size_t)n);
+  return st ? raise_status(env, st) : atom_ok;
+}
+
 /* ---- programs ------------------------------------------------------------------------------------------ */
 
 /* program_build(iodata): the serialised expression -> executable.  Replaces the thirteen MLIR builder
@@ -313,6 +418,102 @@ static ERL_NIF_TERM program_build_times(ErlNifEnv *env, int argc, const ERL_NIF_
   return st ? raise_status(env, st) : enif_make_tuple2(env, enif_make_double(env, a), enif_make_double(env, b));
 }
 
+/* program_run_into(program, device, [argument], [result]): results written into the given buffers */
+static ERL_NIF_TERM program_run_into(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  nxb200_program *p;
+  int dev;
+  unsigned n_args, n_outs;
+  if (argc != 4 || !(p = get_prog(env, argv[0])) || !enif_get_int(env, argv[1], &dev) || !enif_get_list_length(env, argv[2], &n_args) ||
+      !enif_get_list_length(env, argv[3], &n_outs))
+    return BADARG(env);
+  nxb200_buffer **bufs = enif_alloc(sizeof(*bufs) * (n_args + n_outs + 1));
+  ERL_NIF_TERM head, tail = argv[2];
+  for (unsigned i = 0; i < n_args + n_outs; ++i) {
+    if (i == n_args) tail = argv[3];
+    enif_get_list_cell(env, tail, &head, &tail);
+    if (!(bufs[i] = get_buf(env, head))) { enif_free(bufs); return BADARG(env); }
+  }
+  int st = nxb200_program_run_into(p, dev, bufs, (int)n_args, bufs + n_args, (int)n_outs);
+  enif_free(bufs);
+  return st ? raise_status(env, st) : atom_ok;
+}
+
+/* generated CUDA source of the i-th kernel (diagnostics); <<>> past the last one */
+static ERL_NIF_TERM program_kernel_source(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  nxb200_program *p;
+  int i;
+  if (argc != 2 || !(p = get_prog(env, argv[0])) || !enif_get_int(env, argv[1], &i)) return BADARG(env);
+  size_t n = nxb200_program_kernel_source(p, i, NULL, 0);
+  char *tmp = enif_alloc(n + 1);
+  nxb200_program_kernel_source(p, i, tmp, n + 1);
+  ERL_NIF_TERM out;
+  memcpy(enif_make_new_binary(env, n, &out), tmp, n);
+  enif_free(tmp);
+  return out;
+}
+
+static ERL_NIF_TERM program_launch_count(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  nxb200_program *p;
+  int n = 0;
+  if (argc != 1 || !(p = get_prog(env, argv[0]))) return BADARG(env);
+  int st = nxb200_program_launch_count(p, &n);
+  return st ? raise_status(env, st) : enif_make_int(env, n);
+}
+
+/* dot_bf16_static_scratch(device, a, b, c, m, n, k): the allocation-free product on three tensors of
+ * the library, enqueued on the device's compute stream; complete on return */
+static ERL_NIF_TERM dot_bf16_static_scratch(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  int dev;
+  nxb200_buffer *a, *b, *c;
+  ErlNifSInt64 m, n, k;
+  void *pa, *pb, *pc, *stream;
+  if (argc != 7 || !enif_get_int(env, argv[0], &dev) || !(a = get_buf(env, argv[1])) || !(b = get_buf(env, argv[2])) ||
+      !(c = get_buf(env, argv[3])) || !enif_get_int64(env, argv[4], &m) || !enif_get_int64(env, argv[5], &n) || !enif_get_int64(env, argv[6], &k))
+    return BADARG(env);
+  int st = nxb200_buffer_device_pointer(a, &pa);
+  if (!st) st = nxb200_buffer_device_pointer(b, &pb);
+  if (!st) st = nxb200_buffer_device_pointer(c, &pc);
+  if (!st) st = nxb200_device_stream(dev, &stream);
+  if (!st) st = nxb200_dot_bf16_static_scratch(dev, pa, pb, pc, m, n, k, stream);
+  return st ? raise_status(env, st) : atom_ok;
+}
+
+/* ---- device timing and self-test ---------------------------------------------------------------------- */
+
+static ERL_NIF_TERM timer_begin(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  int dev;
+  if (argc != 1 || !enif_get_int(env, argv[0], &dev)) return BADARG(env);
+  int st = nxb200_timer_begin(dev);
+  return st ? raise_status(env, st) : atom_ok;
+}
+
+static ERL_NIF_TERM timer_end(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  int dev;
+  float ms = 0;
+  if (argc != 1 || !enif_get_int(env, argv[0], &dev)) return BADARG(env);
+  int st = nxb200_timer_end(dev, &ms);
+  return st ? raise_status(env, st) : enif_make_double(env, ms);
+}
+
+/* the device's compute stream as an integer (for NIFs of other libraries that enqueue on it) */
+static ERL_NIF_TERM device_stream(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  int dev;
+  void *stream = NULL;
+  if (argc != 1 || !enif_get_int(env, argv[0], &dev)) return BADARG(env);
+  int st = nxb200_device_stream(dev, &stream);
+  return st ? raise_status(env, st) : enif_make_uint64(env, (ErlNifUInt64)(uintptr_t)stream);
+}
+
+/* selftest_bounded_wait(device, limit_us) -> :timeout when the bounded wait gave up as it must */
+static ERL_NIF_TERM selftest_bounded_wait(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  int dev;
+  unsigned us;
+  if (argc != 2 || !enif_get_int(env, argv[0], &dev) || !enif_get_uint(env, argv[1], &us)) return BADARG(env);
+  int st = nxb200_selftest_bounded_wait(dev, us);
+  if (st == NXB_ERR_TIMEOUT) return enif_make_atom(env, "timeout");
+  return st ? raise_status(env, st) : atom_ok;
+}
+
 /* ---- memory counters (exla.cc:655-686) ---------------------------------------------------------------- */
 
 static ERL_NIF_TERM memory_stats(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
@@ -369,6 +570,22 @@ static ERL_NIF_TERM comm_peer_open(ErlNifEnv *env, int argc, const ERL_NIF_TERM 
   return st ? raise_status(env, st) : (enabled ? atom_true : atom_false);
 }
 
+/* the sum over the group of one tensor, in place, on the compute stream (NCCL) */
+static ERL_NIF_TERM comm_all_reduce_sum(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  nxb200_buffer *b;
+  if (argc != 1 || !(b = get_buf(env, argv[0]))) return BADARG(env);
+  int st = nxb200_comm_all_reduce_sum(b);
+  return st ? raise_status(env, st) : atom_ok;
+}
+
+/* how many products ran fused with their exchange since the process started (diagnostics) */
+static ERL_NIF_TERM comm_fused_launches(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
+  (void)argc; (void)argv;
+  uint64_t n = 0;
+  int st = nxb200_comm_fused_launches(&n);
+  return st ? raise_status(env, st) : enif_make_uint64(env, n);
+}
+
 static ERL_NIF_TERM comm_destroy(ErlNifEnv *env, int argc, const ERL_NIF_TERM argv[]) {
   (void)argc; (void)argv;
   int st = nxb200_comm_destroy();
@@ -382,12 +599,13 @@ static int load(ErlNifEnv *env, void **priv, ERL_NIF_TERM info) {
   ErlNifResourceFlags f = ERL_NIF_RT_CREATE | ERL_NIF_RT_TAKEOVER;
   BUF_TYPE = enif_open_resource_type(env, NULL, "nxb200_buffer", buf_dtor, f, NULL);
   PROG_TYPE = enif_open_resource_type(env, NULL, "nxb200_program", prog_dtor, f, NULL);
+  HOST_TYPE = enif_open_resource_type(env, NULL, "nxb200_host_region", host_dtor, f, NULL);
   atom_ok = enif_make_atom(env, "ok");
   atom_error = enif_make_atom(env, "error");
   atom_already_deallocated = enif_make_atom(env, "already_deallocated");
   atom_true = enif_make_atom(env, "true");
   atom_false = enif_make_atom(env, "false");
-  return BUF_TYPE && PROG_TYPE ? 0 : -1;
+  return BUF_TYPE && PROG_TYPE && HOST_TYPE ? 0 : -1;
 }
 
 static ErlNifFunc funcs[] = {
@@ -403,17 +621,34 @@ static ErlNifFunc funcs[] = {
     {"from_pointer", 4, from_pointer, 0},
     {"ipc_export", 1, ipc_export, ERL_NIF_DIRTY_JOB_IO_BOUND},
     {"from_ipc", 4, from_ipc, ERL_NIF_DIRTY_JOB_IO_BOUND},
+    {"buffer_alloc", 3, buffer_alloc, ERL_NIF_DIRTY_JOB_IO_BOUND},
+    {"from_binary_async", 6, from_binary_async, 0},
+    {"host_region", 1, host_region, 0},
+    {"region_write", 2, region_write, ERL_NIF_DIRTY_JOB_IO_BOUND},
+    {"region_binary", 1, region_binary, 0},
+    {"write_async", 3, write_async, 0},
+    {"read_async", 3, read_async, 0},
     {"program_build", 1, program_build, ERL_NIF_DIRTY_JOB_CPU_BOUND},
     {"program_outputs", 1, program_outputs, 0},
     {"program_run", 3, program_run, ERL_NIF_DIRTY_JOB_IO_BOUND},
     {"program_describe", 1, program_describe, 0},
     {"program_build_times", 1, program_build_times, 0},
+    {"program_run_into", 4, program_run_into, ERL_NIF_DIRTY_JOB_IO_BOUND},
+    {"program_kernel_source", 2, program_kernel_source, 0},
+    {"program_launch_count", 1, program_launch_count, 0},
+    {"dot_bf16_static_scratch", 7, dot_bf16_static_scratch, ERL_NIF_DIRTY_JOB_IO_BOUND},
+    {"timer_begin", 1, timer_begin, 0},
+    {"timer_end", 1, timer_end, ERL_NIF_DIRTY_JOB_IO_BOUND},
+    {"device_stream", 1, device_stream, 0},
+    {"selftest_bounded_wait", 2, selftest_bounded_wait, ERL_NIF_DIRTY_JOB_IO_BOUND},
     {"memory_stats", 1, memory_stats, 0},
     {"memory_reset_peak", 1, memory_reset_peak, 0},
     {"comm_id", 0, comm_id, 0},
     {"comm_init", 4, comm_init, ERL_NIF_DIRTY_JOB_IO_BOUND},
     {"comm_peer_alloc", 2, comm_peer_alloc, ERL_NIF_DIRTY_JOB_IO_BOUND},
     {"comm_peer_open", 1, comm_peer_open, ERL_NIF_DIRTY_JOB_IO_BOUND},
+    {"comm_all_reduce_sum", 1, comm_all_reduce_sum, ERL_NIF_DIRTY_JOB_IO_BOUND},
+    {"comm_fused_launches", 0, comm_fused_launches, 0},
     {"comm_destroy", 0, comm_destroy, ERL_NIF_DIRTY_JOB_IO_BOUND},
 };
 

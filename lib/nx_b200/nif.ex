@@ -31,6 +31,15 @@ defmodule NxB200.NIF do
   def from_pointer(_device, _type_code, _shape, _address), do: err()
   def ipc_export(_buffer), do: err()
   def from_ipc(_device, _type_code, _shape, _handle), do: err()
+  def buffer_alloc(_device, _type_code, _shape), do: err()
+  # queued upload: `{:nxb200_upload_done, ref}` arrives at `pid` when the binary has been read
+  def from_binary_async(_device, _type_code, _shape, _binary, _pid, _ref), do: err()
+  # transfers that complete at the next device_synchronize, through a host region of the shim
+  def host_region(_bytes), do: err()
+  def region_write(_region, _binary), do: err()
+  def region_binary(_region), do: err()
+  def write_async(_buffer, _region, _bytes), do: err()
+  def read_async(_buffer, _region, _bytes), do: err()
 
   # programs
   def program_build(_iodata), do: err()
@@ -38,6 +47,16 @@ defmodule NxB200.NIF do
   def program_run(_program, _device, _buffers), do: err()
   def program_describe(_program), do: err()
   def program_build_times(_program), do: err()
+  def program_run_into(_program, _device, _arguments, _results), do: err()
+  def program_kernel_source(_program, _index), do: err()
+  def program_launch_count(_program), do: err()
+  def dot_bf16_static_scratch(_device, _a, _b, _c, _m, _n, _k), do: err()
+
+  # device timing, stream, self-test
+  def timer_begin(_device), do: err()
+  def timer_end(_device), do: err()
+  def device_stream(_device), do: err()
+  def selftest_bounded_wait(_device, _limit_us), do: err()
 
   # memory counters
   def memory_stats(_device), do: err()
@@ -48,6 +67,8 @@ defmodule NxB200.NIF do
   def comm_init(_device, _rank, _world, _id), do: err()
   def comm_peer_alloc(_device, _elems), do: err()
   def comm_peer_open(_blobs), do: err()
+  def comm_all_reduce_sum(_buffer), do: err()
+  def comm_fused_launches, do: err()
   def comm_destroy, do: err()
 
   defp err, do: :erlang.nif_error(:undef)

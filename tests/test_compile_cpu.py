@@ -177,3 +177,24 @@ def test_kernels_compile_with_the_runtime_compiler_another_package_loaded_first(
         "print('built')\n")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "built" in r.stdout, r.stderr[-2000:]
+
+
+def test_the_nif_shim_and_the_elixir_stubs_cover_every_entry_point():
+    """`c_src/nxb200_nif.c` (not compiled here) must call every function `include/nxb200.h` declares, and
+    `lib/nx_b200/nif.ex` must hold a stub of the same arity for every NIF the shim registers."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    header = open(os.path.join(root, "include", "nxb200.h")).read()
+    shim = open(os.path.join(root, "c_src", "nxb200_nif.c")).read()
+    stubs = open(os.path.join(root, "lib", "nx_b200", "nif.ex")).read()
+    declared = set(re.findall(r"\b(?:int|size_t)\s+(nxb200_[a-z0-9_]+)\s*\(", header))
+    assert len(declared) >= 40
+    missing = sorted(f for f in declared if not re.search(r"\b" + f + r"\s*\(", shim))
+    assert not missing, missing
+    registered = re.findall(r'\{"([a-z0-9_]+)",\s*(\d+),\s*([a-z0-9_]+),', shim)
+    assert len(registered) >= 40
+    for name, arity, fun in registered:
+        assert re.search(r"static ERL_NIF_TERM " + fun + r"\(", shim), fun
+        m = re.search(r"def " + name + r"(\(([^)]*)\))?, do: err\(\)", stubs)
+        assert m, f"no Elixir stub for {name}/{arity}"
+        got = 0 if not m.group(2) else len([a for a in m.group(2).split(",") if a.strip()])
+        assert got == int(arity), (name, arity, got)
