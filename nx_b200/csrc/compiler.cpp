@@ -1354,6 +1354,7 @@ KernelSpec KernelBuilder::build(const std::string& name) {
     o << "  for (" << I << " g = (" << I << ")blockIdx.x * " << block_ << " + threadIdx.x; g < nvec; g += (" << I << ")gridDim.x * " << block_ << ") {\n";
     o << "        const " << I << " flat0 = g * " << V_ << ";\n";
     decomp(0, nv_, "flat0", true);
+    o << row_sec_[0];          // values that depend on no index (e.g. a comparison of two literals)
     o << pre_sec_[0];
     o << "#pragma unroll\n      for (int v = 0; v < " << V_ << "; ++v) {\n";
     if (used_vars_.count(nv_ - 1)) o << "        const " << I << " i" << nv_ - 1 << " = ib + v;\n";

@@ -974,6 +974,18 @@ def iota(shape, axis=None, type=T.S32):
     return backend.eager(lambda: E.node(out, "iota", [], ints=[a]), [])
 
 
+def eye(shape, type=T.S32):
+    """``Nx.eye/2`` (nx/lib/nx.ex:1262-1390): the identity on the last two axes of ``shape`` (an integer
+    ``n`` means ``{n, n}``), repeated over the leading ones.  The reference's compilers lower it to
+    ``iota(rows) == iota(columns)`` (exla/lib/exla/defn.ex:1126-1130); so does this front-end: it is index
+    arithmetic inside whatever kernel reads it."""
+    shape = (shape, shape) if isinstance(shape, int) else tuple(shape)
+    if len(shape) < 2:
+        raise ValueError(f"eye/2 expects a shape with at least 2 dimensions or an integer, got: {shape!r}")
+    rank = len(shape)
+    return as_type(equal(iota(shape, axis=rank - 2), iota(shape, axis=rank - 1)), type)
+
+
 # ---- aggregates ---------------------------------------------------------------------
 
 

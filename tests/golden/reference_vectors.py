@@ -625,3 +625,12 @@ case("conv valid, 3x3 kernel, 2 filters", "nx/test/nx_test.exs:209-236", lambda 
 case("conv valid, strides 2x1", "nx/test/nx_test.exs:239-258", lambda t, k: nx.conv(t, k, strides=[2, 1], padding="valid"),
      [(_C2244, "f32"), (_iota_list((1, 2, 2, 2)), "f32")],
      [([[[[440.0, 468.0, 496.0], [664.0, 692.0, 720.0]]], [[[1336.0, 1364.0, 1392.0], [1560.0, 1588.0, 1616.0]]]], "f32")], exact=False)
+
+# ---- eye: exla/test/exla/defn/expr_test.exs:3260-3272, nx/lib/nx.ex:1278-1332 ------------------------------
+case("eye 2", "exla/test/exla/defn/expr_test.exs:3261-3265", lambda t: nx.add(nx.eye(2), t), [(0, "s32")], [([[1, 0], [0, 1]], "s32")])
+case("eye with type", "exla/test/exla/defn/expr_test.exs:3267-3271", lambda t: nx.add(nx.eye(1, type="f32"), t), [(0.0, "f32")], [([[1.0]], "f32")])
+case("eye f32 3", "nx/lib/nx.ex:1287-1295", lambda t: nx.add(nx.eye(3, type="f32"), t), [(0.0, "f32")],
+     [([[1.0, 0.0, 0.0], [0.0, 1.0, 0.0], [0.0, 0.0, 1.0]], "f32")])
+case("eye {1,2}", "nx/lib/nx.ex:1299-1305", lambda t: nx.add(nx.eye((1, 2)), t), [(0, "s32")], [([[1, 0]], "s32")])
+case("eye batched {2,4,3}", "nx/lib/nx.ex:1310-1327", lambda t: nx.add(nx.eye((2, 4, 3)), t), [(0, "s32")],
+     [([[[1, 0, 0], [0, 1, 0], [0, 0, 1], [0, 0, 0]]] * 2, "s32")])
