@@ -12,10 +12,11 @@ defmodule NxB200 do
   argument thunks to device buffers, runs the program and wraps the result buffers in the output
   templates.  Results are always fresh tensors on `NxB200.Backend` (`defn.ex:387-393`).
 
-  Not lowered into one program: `:while`, `:cond` with tensor-valued branches that need control
-  flow, `:fun`, `:runtime_call` — the expression is cut at those nodes and the pieces are run from
-  the host, as `nx_b200/defn.py` does in the tested stand-in.  Anything else the device cannot run
-  raises `ArgumentError` naming the operation; there is no CPU fallback.
+  Not lowered by this module: `:while`, `:cond`, `:fun`, `:runtime_call`, hooks (the tested stand-in
+  `nx_b200/defn.py` cuts the expression at those nodes and runs the pieces from the host; this walker
+  does not do that yet) and `:conv` (the stand-in's front-end lowers it to pad + slices + dot before
+  the compiler sees it).  These, and anything else the device cannot run, raise `ArgumentError`
+  naming the operation; there is no CPU fallback.
 
   Not compiled in this repository's build (no Elixir in the image).
   """
@@ -217,6 +218,10 @@ defmodule NxB200 do
 
   defp args(tensors, state), do: Enum.map_reduce(tensors, state, &visit/2)
 
+  # node `i` (the value of `tensor`) as `type`: itself, or an as_type node filed under `id`
+  defp converted(state, _id, i, %T{type: type}, type), do: {i, state}
+  defp converted(state, id, i, %T{} = tensor, type), do: emit(state, id, "as_type", %{tensor | type: type}, [i], [], [], <<>>)
+
   defp simple(%T{data: %Expr{id: id, op: op}} = t, tensors, ints, state) do
     {idx, state} = args(tensors, state)
     emit(state, id, Atom.to_string(op), t, idx, ints, [], <<>>)
@@ -273,8 +278,33 @@ defmodule NxB200 do
   defp lower(%T{data: %Expr{op: :reverse, args: [x, axes]}} = t, state), do: simple(t, [x], axes, state)
   defp lower(%T{data: %Expr{op: :iota, args: [axis]}} = t, state), do: simple(t, [], [axis || -1], state)
 
-  defp lower(%T{data: %Expr{op: op, args: [tensors, axis]}} = t, state) when op in [:concatenate, :stack] do
-    simple(t, tensors, [axis], state)
+  # pieces are converted to the result's type first (exla/lib/exla/defn.ex, :concatenate and :stack)
+  defp lower(%T{data: %Expr{id: id, op: :concatenate, args: [tensors, axis]}, type: type} = t, state) do
+    {pieces, state} =
+      tensors
+      |> Enum.with_index()
+      |> Enum.map_reduce(state, fn {piece, k}, st ->
+        {i, st} = visit(piece, st)
+        converted(st, {:piece, id, k}, i, piece, type)
+      end)
+
+    emit(state, id, "concatenate", t, pieces, [axis], [], <<>>)
+  end
+
+  # the device has no :stack: every piece gets a new axis of extent 1 (a reshape, which costs
+  # nothing), then the pieces are concatenated along it
+  defp lower(%T{data: %Expr{id: id, op: :stack, args: [tensors, axis]}, type: type} = t, state) do
+    {pieces, state} =
+      tensors
+      |> Enum.with_index()
+      |> Enum.map_reduce(state, fn {piece, k}, st ->
+        {i, st} = visit(piece, st)
+        {i, st} = converted(st, {:piece, id, k}, i, piece, type)
+        shape = piece.shape |> Tuple.to_list() |> List.insert_at(axis, 1) |> List.to_tuple()
+        emit(st, {:lifted, id, k}, "reshape", %{piece | type: type, shape: shape}, [i], [], [], <<>>)
+      end)
+
+    emit(state, id, "concatenate", t, pieces, [axis], [], <<>>)
   end
 
   defp lower(%T{data: %Expr{op: :slice, args: [x, starts, lengths, strides]}} = t, state) do
@@ -319,6 +349,17 @@ defmodule NxB200 do
   defp lower(%T{data: %Expr{op: :argsort, args: [x, opts]}} = t, state) do
     last_axis!(x, opts[:axis])
     simple(t, [x], [bool(opts[:direction] == :desc), bool(opts[:stable])], state)
+  end
+
+  # ones where the last two coordinates agree: two iotas compared, as the reference lowers it
+  # (exla/lib/exla/defn.ex:1120)
+  defp lower(%T{data: %Expr{id: id, op: :eye, args: []}, shape: shape} = t, state) do
+    rank = tuple_size(shape)
+    index = %{t | type: {:s, 32}}
+    {rows, state} = emit(state, {:eye_rows, id}, "iota", index, [], [rank - 2], [], <<>>)
+    {cols, state} = emit(state, {:eye_cols, id}, "iota", index, [], [rank - 1], [], <<>>)
+    {same, state} = emit(state, {:eye_same, id}, "equal", %{t | type: {:u, 8}}, [rows, cols], [], [], <<>>)
+    emit(state, id, "as_type", t, [same], [], [], <<>>)
   end
 
   defp lower(%T{data: %Expr{op: :elem, args: [tuple, i]}}, state) do
