@@ -243,7 +243,7 @@ defmodule NxB200.Backend do
   def slice(out, tensor, start_indices, lengths, strides) do
     out = Nx.to_template(out)
     # dynamic start indices are tensor arguments of the one-node program
-    {dynamic, static} = Enum.split_with(start_indices, &is_struct(&1, T))
+    dynamic = Enum.filter(start_indices, &is_struct(&1, T))
 
     jit(
       [],
@@ -254,7 +254,6 @@ defmodule NxB200.Backend do
       [tensor, List.to_tuple(dynamic)],
       [tensor | dynamic]
     )
-    |> tap(fn _ -> static end)
   end
 
   @impl true
