@@ -12,9 +12,9 @@ defmodule NxB200 do
   argument thunks to device buffers, runs the program and wraps the result buffers in the output
   templates.  Results are always fresh tensors on `NxB200.Backend` (`defn.ex:387-393`).
 
-  Not lowered by this module: `:while`, `:cond`, `:fun`, `:runtime_call`, hooks (the tested stand-in
-  `nx_b200/defn.py` cuts the expression at those nodes and runs the pieces from the host; this walker
-  does not do that yet) and `:conv` (the stand-in's front-end lowers it to pad + slices + dot before
+  `:cond` is lowered to every branch plus selects.  Not lowered by this module: `:while`, `:fun`,
+  `:runtime_call`, hooks (the tested stand-in `nx_b200/defn.py` cuts the expression at those nodes and
+  runs the pieces from the host; this walker does not do that yet) and `:conv` (the stand-in's front-end lowers it to pad + slices + dot before
   the compiler sees it).  These, and anything else the device cannot run, raise `ArgumentError`
   naming the operation; there is no CPU fallback.
 
@@ -362,6 +362,18 @@ defmodule NxB200 do
     emit(state, id, "as_type", t, [same], [], [], <<>>)
   end
 
+  # :cond inside one program: every branch is computed and the first clause whose predicate holds is
+  # selected (what `defn.cond` of the tested stand-in does inside a traced function).  A branch that
+  # holds a loop or a host call raises from that node.
+  defp lower(%T{data: %Expr{id: id, op: :cond, args: [clauses, last]}} = t, state) when not is_tuple(last) do
+    select_chain(id, t, clauses, last, state)
+  end
+
+  defp lower(%T{data: %Expr{id: id, op: :elem, args: [%T{data: %Expr{op: :cond, args: [clauses, last]}}, i]}} = t, state) do
+    clauses = for {pred, body} <- clauses, do: {pred, elem(body, i)}
+    select_chain(id, t, clauses, elem(last, i), state)
+  end
+
   defp lower(%T{data: %Expr{op: :elem, args: [tuple, i]}}, state) do
     # multi-output nodes do not exist on the device: project at trace level
     visit(elem(tuple_of(tuple), i), state)
@@ -371,6 +383,28 @@ defmodule NxB200 do
     raise ArgumentError,
           "NxB200 cannot compile the operation :#{op} (there is no CPU fallback; run it on another backend " <>
             "or outside of the compiled function)"
+  end
+
+  # select(pred_1, body_1, select(pred_2, body_2, … last)), built from the last clause up; the
+  # scalar predicates are broadcast to the result's shape first
+  defp select_chain(id, %T{shape: shape} = t, clauses, last, state) do
+    {acc, state} = visit(last, state)
+    n = length(clauses)
+
+    clauses
+    |> Enum.reverse()
+    |> Enum.with_index(1)
+    |> Enum.reduce({acc, state}, fn {{pred, body}, k}, {acc, st} ->
+      {p, st} = visit(pred, st)
+
+      {p, st} =
+        if shape == {},
+          do: {p, st},
+          else: emit(st, {:cond_pred, id, k}, "broadcast", %{pred | shape: shape}, [p], [0], [], <<>>)
+
+      {b, st} = visit(body, st)
+      emit(st, if(k == n, do: id, else: {:cond_step, id, k}), "select", t, [p, b, acc], [], [], <<>>)
+    end)
   end
 
   defp tuple_of(%T{data: %Expr{op: :metadata, args: [inner, _]}}), do: tuple_of(inner)
