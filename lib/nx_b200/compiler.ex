@@ -12,11 +12,14 @@ defmodule NxB200 do
   argument thunks to device buffers, runs the program and wraps the result buffers in the output
   templates.  Results are always fresh tensors on `NxB200.Backend` (`defn.ex:387-393`).
 
-  `:cond` is lowered to every branch plus selects.  Not lowered by this module: `:while`, `:fun`,
-  `:runtime_call`, hooks (the tested stand-in `nx_b200/defn.py` cuts the expression at those nodes and
-  runs the pieces from the host; this walker does not do that yet) and `:conv` (the stand-in's front-end lowers it to pad + slices + dot before
-  the compiler sees it).  These, and anything else the device cannot run, raise `ArgumentError`
-  naming the operation; there is no CPU fallback.
+  `:cond` is lowered to every branch plus selects, `:block` to its default implementation.  A function
+  that holds a `:while`, a hook or a `:runtime_call` is not one program: it is walked by
+  `Nx.Defn.Evaluator` over tensors of this backend, one program per operation (the tested stand-in
+  `nx_b200/defn.py` cuts the expression at those nodes and compiles the pieces whole; that is not
+  ported).  Not lowered: custom reducers (`:reduce`, `:window_reduce`, `:fun`) and `:conv` (the
+  stand-in's front-end lowers it to pad + slices + dot before the compiler sees it).  These, and
+  anything else the device cannot run, raise `ArgumentError` naming the operation; no operation
+  is computed on the host.
 
   Not compiled in this repository's build (no Elixir in the image).
   """
@@ -53,40 +56,43 @@ defmodule NxB200 do
     # non-donating executable (exla/lib/exla/defn.ex:337-353)
     args_key = for %T{} = v <- vars, do: {v.type, v.shape, v.names, v.vectorized_axes, v.donatable?}
 
-    {program, outputs} =
+    built =
       cached({key, args_key, Keyword.drop(opts, [:device])}, fn ->
         t0 = System.monotonic_time()
         expr = fun.(vars)
         t1 = System.monotonic_time()
         outputs = Composite.flatten_list([expr])
-        program = NIF.program_build(serialize(outputs, vars))
-        t2 = System.monotonic_time()
 
-        :telemetry.execute(
-          [:nx_b200, :compilation],
-          %{eval_time: t1 - t0, compile_time: t2 - t1, total_time: t2 - t0},
-          %{key: key}
-        )
+        if host_control?(outputs) do
+          :host
+        else
+          program = NIF.program_build(serialize(outputs, vars))
+          t2 = System.monotonic_time()
 
-        {program, expr}
+          :telemetry.execute(
+            [:nx_b200, :compilation],
+            %{eval_time: t1 - t0, compile_time: t2 - t1, total_time: t2 - t0},
+            %{key: key}
+          )
+
+          {program, expr}
+        end
       end)
 
+    case built do
+      :host -> host_runner(key, vars, fun, opts, device)
+      {program, expr} -> program_runner(program, expr, device)
+    end
+  end
+
+  defp program_runner(program, expr, device) do
     fn args_list ->
       for args <- args_list do
-        buffers =
-          for thunk <- args do
-            case thunk.() do
-              %T{data: %NxB200.Backend{ref: ref, device: ^device}} -> ref
-              %T{data: %NxB200.Backend{}} = t -> Nx.backend_copy(t, {NxB200.Backend, device: device}).data.ref
-              %T{data: %Nx.BinaryBackend{}} = t -> Nx.backend_copy(t, {NxB200.Backend, device: device}).data.ref
-              %T{data: %other{}} -> raise ArgumentError, "cannot run on NxB200 a tensor allocated on #{inspect(other)}"
-            end
-          end
-
+        buffers = for thunk <- args, do: on_device(thunk.(), device).data.ref
         refs = NIF.program_run(program, device, buffers)
 
         {result, []} =
-          Composite.traverse(outputs, refs, fn %T{} = template, [ref | rest] ->
+          Composite.traverse(expr, refs, fn %T{} = template, [ref | rest] ->
             {%{Nx.to_template(template) | data: %NxB200.Backend{ref: ref, device: device}}, rest}
           end)
 
@@ -94,6 +100,56 @@ defmodule NxB200 do
       end
     end
   end
+
+  # A function with a loop or a host call in it (`:while`, `:io_call`, `:runtime_call`) is not one
+  # program.  It is walked by `Nx.Defn.Evaluator` over tensors of this backend: every operation is
+  # still a program on the device (`NxB200.Backend` runs each callback through this compiler), and
+  # the loop condition, the hooks and the callbacks run on the host between them.  (The tested
+  # stand-in `nx_b200/defn.py` does better: it cuts the expression at those nodes and compiles the
+  # pieces whole.)
+  defp host_runner(key, vars, fun, opts, device) do
+    evaluate = Nx.Defn.Evaluator.__compile__(key, vars, fun, Keyword.take(opts, [:hooks, :garbage_collect]))
+
+    fn args_list ->
+      for args <- args_list do
+        [result] = evaluate.([for(thunk <- args, do: fn -> on_device(thunk.(), device) end)])
+        Composite.traverse(result, &on_device(&1, device))
+      end
+    end
+  end
+
+  defp on_device(%T{data: %NxB200.Backend{device: device}} = t, device), do: t
+  defp on_device(%T{data: %NxB200.Backend{}} = t, device), do: Nx.backend_copy(t, {NxB200.Backend, device: device})
+  defp on_device(%T{data: %Nx.BinaryBackend{}} = t, device), do: Nx.backend_copy(t, {NxB200.Backend, device: device})
+
+  defp on_device(%T{data: %other{}}, _device) do
+    raise ArgumentError, "cannot run on NxB200 a tensor allocated on #{inspect(other)}"
+  end
+
+  @host_ops [:while, :io_call, :runtime_call]
+
+  defp host_control?(outputs) do
+    {found, _seen} = Enum.reduce(outputs, {false, %{}}, &scan/2)
+    found
+  end
+
+  defp scan(_tensor, {true, seen}), do: {true, seen}
+
+  defp scan(%T{data: %Expr{id: id, op: op}} = t, {false, seen}) do
+    cond do
+      is_map_key(seen, id) ->
+        {false, seen}
+
+      op in @host_ops ->
+        {true, seen}
+
+      true ->
+        {_args, acc} = Nx.Defn.Tree.apply_args(t, {false, Map.put(seen, id, true)}, fn arg, acc -> {arg, scan(arg, acc)} end)
+        acc
+    end
+  end
+
+  defp scan(_other, acc), do: acc
 
   ## program cache: one build per key, concurrent callers of the same key wait for it
   ## (the role of EXLA.Defn.LockedCache, exla/lib/exla/defn/locked_cache.ex:35-59)
@@ -139,15 +195,17 @@ defmodule NxB200 do
   @doc false
   def serialize(outputs, vars) do
     # parameters first, in argument order, so that the program keeps the function's arity
-    state = %{nodes: [], index: %{}, count: 0}
+    # `scope` maps a parameter position to the node that carries its value: the program's own
+    # parameters at the top, a block's arguments while its default implementation is lowered
+    state = %{nodes: [], index: %{}, count: 0, scope: %{}}
 
     state =
       vars
       |> Composite.flatten_list()
       |> Enum.with_index()
       |> Enum.reduce(state, fn {%T{} = v, i}, st ->
-        {_, st} = emit(st, {:parameter, i}, "parameter", v, [], [i], [], <<>>)
-        st
+        {node, st} = emit(st, {:parameter, i}, "parameter", v, [], [i], [], <<>>)
+        %{st | scope: Map.put(st.scope, i, node)}
       end)
 
     {out_indices, state} = Enum.map_reduce(outputs, state, &visit/2)
@@ -235,8 +293,9 @@ defmodule NxB200 do
                 :greater_equal, :less_equal, :logical_and, :logical_or, :logical_xor, :select, :clip, :reshape]
 
   defp lower(%T{data: %Expr{id: id, op: :parameter, args: [i]}}, state) do
-    # written up front by serialize/2
-    {Map.fetch!(state.index, {:parameter, i}), %{state | index: Map.put(state.index, id, Map.fetch!(state.index, {:parameter, i}))}}
+    # written up front by serialize/2, or an argument of the block being lowered
+    node = Map.fetch!(state.scope, i)
+    {node, %{state | index: Map.put(state.index, id, node)}}
   end
 
   defp lower(%T{data: %Expr{id: id, op: :constant, args: [number]}, type: type} = t, state) do
@@ -362,6 +421,21 @@ defmodule NxB200 do
     emit(state, id, "as_type", t, [same], [], [], <<>>)
   end
 
+  # :block (take, take_along_axis, top_k, logical_not, all_close, cumulative operations, …: nx/lib/nx.ex
+  # `block/4`; nx/lib/nx/defn/expr.ex:826-842): the default implementation is lowered in place, its
+  # parameters standing for the block's tensor arguments (the reference compiles it as a sub-computation
+  # called with those arguments, exla/lib/exla/defn.ex:1055-1086).  An operation inside it that the
+  # device lacks raises from its own node.
+  defp lower(%T{data: %Expr{id: id, op: :block, args: [_struct, in_args, expr, _fun]}}, state) when not is_tuple(expr) do
+    {node, state} = in_block_scope(in_args, state, &visit(expr, &1))
+    {node, %{state | index: Map.put(state.index, id, node)}}
+  end
+
+  defp lower(%T{data: %Expr{id: id, op: :elem, args: [%T{data: %Expr{op: :block, args: [_struct, in_args, exprs, _fun]}}, i]}}, state) do
+    {node, state} = in_block_scope(in_args, state, &visit(elem(exprs, i), &1))
+    {node, %{state | index: Map.put(state.index, id, node)}}
+  end
+
   # :cond inside one program: every branch is computed and the first clause whose predicate holds is
   # selected (what `defn.cond` of the tested stand-in does inside a traced function).  A branch that
   # holds a loop or a host call raises from that node.
@@ -383,6 +457,17 @@ defmodule NxB200 do
     raise ArgumentError,
           "NxB200 cannot compile the operation :#{op} (there is no CPU fallback; run it on another backend " <>
             "or outside of the compiled function)"
+  end
+
+  # runs `fun` with the block's tensor arguments (the leading elements of `in_args`; option lists
+  # follow them) as parameters 0, 1, …, then restores the enclosing scope
+  defp in_block_scope(in_args, state, fun) do
+    {tensors, _opts} = Enum.split_while(in_args, &(not is_list(&1)))
+    {nodes, state} = args(tensors, state)
+    outer = state.scope
+    inner = nodes |> Enum.with_index() |> Map.new(fn {node, pos} -> {pos, node} end)
+    {result, state} = fun.(%{state | scope: inner})
+    {result, %{state | scope: outer}}
   end
 
   # select(pred_1, body_1, select(pred_2, body_2, … last)), built from the last clause up; the
