@@ -198,3 +198,41 @@ def test_the_nif_shim_and_the_elixir_stubs_cover_every_entry_point():
         assert m, f"no Elixir stub for {name}/{arity}"
         got = 0 if not m.group(2) else len([a for a in m.group(2).split(",") if a.strip()])
         assert got == int(arity), (name, arity, got)
+
+
+def test_the_elixir_walker_emits_only_operations_the_library_knows():
+    """`lib/nx_b200/compiler.ex` (not compiled here) writes operation names into the program bytes: literal
+    strings given to `emit`, and the atoms of the clauses that go through `simple`.  Each of them must be a
+    name the planner accepts (its operation tables and its support check in `csrc/compiler.cpp`); an Expr
+    operation the device lacks (`:stack`, `:eye`, `:cond`, `:block`) must be lowered to other operations,
+    never emitted under its own name."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    walker = open(os.path.join(root, "lib", "nx_b200", "compiler.ex")).read()
+    planner = open(os.path.join(root, "nx_b200", "csrc", "compiler.cpp")).read()
+
+    known = set()
+    for table in re.findall(r"const std::set<std::string> k\w+ = \{([^}]*)\}", planner):
+        known |= set(re.findall(r'"([a-z0-9_]+)"', table))
+    known |= set(re.findall(r'\.op == "([a-z0-9_]+)"', planner))
+    assert {"add", "reshape", "dot", "concatenate", "gather", "sort"} <= known
+
+    emitted = set(re.findall(r'emit\([^\n]*?, "([a-z0-9_]+)",', walker))
+    table = re.search(r"@elementwise \[(.*?)\]", walker, re.S).group(1)
+    emitted |= set(re.findall(r":([a-z0-9_]+)", table))
+    # clauses whose body calls simple(...) emit the clause's own operation name(s)
+    for clause in re.split(r"\n  defp lower\(", walker)[1:]:
+        head, _, body = clause.partition(" do")
+        if "simple(" not in body.split("\n  defp ")[0] and "simple(" not in head:
+            continue
+        one = re.search(r"op: :([a-z0-9_]+)", head)
+        if one:
+            emitted.add(one.group(1))
+        for guard in re.findall(r"when op in \[([^\]]*)\]", head):
+            emitted |= set(re.findall(r":([a-z0-9_]+)", guard))
+    emitted.discard("elementwise")
+    assert len(emitted) > 80, sorted(emitted)
+    unknown = sorted(emitted - known)
+    assert not unknown, unknown
+    for lowered in ("stack", "eye", "cond", "block"):
+        assert lowered not in emitted
+        assert re.search(r"op: :" + lowered + r"\b", walker), lowered
