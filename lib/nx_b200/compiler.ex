@@ -388,8 +388,16 @@ defmodule NxB200 do
 
   defp lower(%T{data: %Expr{op: :gather, args: [x, indices, opts]}} = t, state), do: simple(t, [x, indices], opts[:axes], state)
 
-  defp lower(%T{data: %Expr{op: op, args: [x, indices, updates, opts]}} = t, state) when op in [:indexed_add, :indexed_put] do
-    simple(t, [x, indices, updates], opts[:axes], state)
+  # the device scatters into a copy of the target: target and updates arrive in the result's type,
+  # the positions as s32 or s64 (the reference converts in its lowering too, exla/lib/exla/defn.ex:1829-1848)
+  defp lower(%T{data: %Expr{id: id, op: op, args: [x, indices, updates, opts]}, type: type} = t, state)
+       when op in [:indexed_add, :indexed_put] do
+    {[xi, ii, ui], state} = args([x, indices, updates], state)
+    {xi, state} = converted(state, {:target, id}, xi, x, type)
+    {ui, state} = converted(state, {:updates, id}, ui, updates, type)
+    index_type = if indices.type in [{:s, 64}, {:u, 64}], do: {:s, 64}, else: {:s, 32}
+    {ii, state} = converted(state, {:positions, id}, ii, indices, index_type)
+    emit(state, id, Atom.to_string(op), t, [xi, ii, ui], opts[:axes], [], <<>>)
   end
 
   defp lower(%T{data: %Expr{op: op, args: [x, window, opts]}} = t, state)
