@@ -300,7 +300,7 @@ class _Server:
         self.ready = deque()        # merged batches waiting for a partition
         self.running = True
         self.executed = []          # (partition, size, padded) per execution, for inspection
-        self.workers = [threading.Thread(target=self._work, args=(i, o), daemon=True) for i, o in enumerate(partition_options)]
+        self.workers = [threading.Thread(target=self._partition_loop, args=(i, o), daemon=True) for i, o in enumerate(partition_options)]
         self.timer = threading.Thread(target=self._tick, daemon=True)
 
     def start(self):
@@ -368,7 +368,7 @@ class _Server:
                 wait = 0.05 if self.deadline is None else max(0.0, min(0.05, self.deadline - time.monotonic()))
                 self.cv.wait(timeout=wait)
 
-    def _work(self, index, options):
+    def _partition_loop(self, index, options):
         fn = None
         while True:
             with self.cv:
