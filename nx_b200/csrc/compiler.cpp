@@ -1593,7 +1593,28 @@ int tc_pick_bn(int64_t m, int64_t n, int64_t batch, int sm_count);
 int tc_smem_bytes(int bn);
 int tc_block_threads(int64_t k);
 
+static std::unique_ptr<Plan> build_plan_from(const uint8_t* bytes, size_t nbytes, int first_level);
+
 std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
+  try {
+    return build_plan_from(bytes, nbytes, 2);
+  } catch (const Error& first) {
+    // A fused row kernel that the runtime compiler rejects (a value the generator placed in a section the
+    // kernel does not have): plan again with one kernel per materialised value.  Graphs whose fused plan
+    // compiles never come here.
+    if (first.status != NXB_ERR_RUNTIME || first.msg.find("failed to compile") == std::string::npos) throw;
+    if (getenv("NXB200_NO_REPLAN")) throw;    // diagnostics: show the rejected kernel instead
+    try {
+      return build_plan_from(bytes, nbytes, 1);
+    } catch (const Error&) {
+      throw first;
+    }
+  }
+}
+
+// first_level 2: fused row kernels, falling back to level 1 when the units depend on each other;
+// first_level 1: one kernel per materialised value from the start
+static std::unique_ptr<Plan> build_plan_from(const uint8_t* bytes, size_t nbytes, int first_level) {
   const auto t_start = std::chrono::steady_clock::now();
   auto plan = std::make_unique<Plan>();
   plan->g = parse_graph(bytes, nbytes);
@@ -1891,7 +1912,9 @@ std::unique_ptr<Plan> build_plan(const uint8_t* bytes, size_t nbytes) {
 
   // ---- fusion: decide units ----------------------------------------------------------------
   // `level 2` = fused row kernels; `level 1` = one kernel per materialised value (always valid)
-  for (int fusion = 2; fusion >= 1; --fusion) {
+  if (first_level < 2)
+    for (int n = 0; n < N; ++n) if (g.nodes[n].live && is_reduce(g.nodes[n])) P.mat[n] = 1;
+  for (int fusion = first_level; fusion >= 1; --fusion) {
     try {
       // reset planner state that depends on the fusion attempt
       Plan& pl = *plan;
