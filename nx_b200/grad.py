@@ -5,8 +5,10 @@ MN-major operand path of the tensor-core kernel), un-broadcasting as `sum`, and 
 
 Rules follow the reference's (file:line quoted per rule).  Lookups differentiate into scatters:
 gather / take / take_along_axis into `indexed_add`, a slice at computed positions into `put_slice`,
-and the scatters back into gathers.  Not differentiable here (raises): window max / min / product,
-product, loops.
+and the scatters back into gathers.  Not differentiable here (raises): window max / min / product
+(the reference scatters through `window_scatter_max/min`, which the device lacks) and loops.  An
+integer-valued node (`quotient`, comparisons, `argmax` …) carries no gradient: the walk stops there,
+where the reference raises for `quotient`.
 """
 from . import backend as B
 from . import expr as E
@@ -77,6 +79,13 @@ def _rule(t, g):
         gx = g * y * nx.pow(x, y - 1.0)
         gy = g * ans * nx.log(nx.select(nx.equal(x, 0.0), 1.0, x))
         return [(x, _unbroadcast(x, gx, ans.shape)), (y, _unbroadcast(y, gy, ans.shape))]
+    if op == "atan2":                                                    # :1048-1055
+        x, y = a
+        den = x * x + y * y
+        return [(x, _unbroadcast(x, g * (y / den), ans.shape)), (y, _unbroadcast(y, g * nx.negate(x / den), ans.shape))]
+    if op == "remainder":                                                # :1020-1025
+        x, y = a
+        return [(x, _unbroadcast(x, g, ans.shape)), (y, _unbroadcast(y, g * nx.negate(nx.floor(x / y)), ans.shape))]
     if op in ("max", "min"):                                             # :1057-1075
         x, y = a
         lhs = nx.select(nx.equal(x, ans), 1.0, 0.0) / nx.select(nx.equal(y, ans), 2.0, 1.0)
@@ -106,6 +115,12 @@ def _rule(t, g):
         "sinh": lambda x: g * nx.cosh(x),
         "cosh": lambda x: g * nx.sinh(x),
         "atan": lambda x: g / (1.0 + x * x),
+        "asin": lambda x: g * nx.rsqrt(1.0 - x * x),                     # :1178
+        "acos": lambda x: g * nx.negate(nx.rsqrt(1.0 - x * x)),          # :1202
+        "asinh": lambda x: g * nx.rsqrt(x * x + 1.0),                    # :1186
+        "acosh": lambda x: g * nx.rsqrt(x * x - 1.0),                    # :1190
+        "atanh": lambda x: g / (1.0 - x * x),                            # :1194
+        "erf_inv": lambda x: g * (nx.exp(ans * ans) * 0.886226925452758),        # :1248-1251  (sqrt(pi) / 2)
         "abs": lambda x: g * nx.select(nx.greater_equal(x, 0.0), 1.0, -1.0),     # :1127
         "erf": lambda x: g * nx.exp(nx.negate(x * x)) * 1.1283791670955126,      # :1226-1235  (2 / sqrt(pi))
         "erfc": lambda x: g * nx.exp(nx.negate(x * x)) * -1.1283791670955126,
@@ -210,6 +225,22 @@ def _rule(t, g):
         return [(x, nx.window_sum(gp, win, strides=[1] * r, padding=[(0, 0)] * r, window_dilations=dil))]
     if op == "sum":                                                      # :791-793
         return [(a[0], _reduce_g(a[0], e.ints, g))]
+    if op == "product":                                                  # :795-826
+        # the product without x_i is ans / x_i; with exactly one zero among the factors only that factor
+        # has a gradient (the product of the others), with more than one nobody has
+        x = a[0]
+        n = e.ints[1]
+        axes = list(e.ints[2:2 + n]) or list(range(x.rank))
+        unit = [1 if i in axes else d for i, d in enumerate(x.shape)]
+        gb, ansb = nx.reshape(g, unit), nx.reshape(ans, unit)
+        zero = nx.equal(x, 0.0)
+        without = nx.select(zero, 1.0, x)
+        rest = nx.product(without, axes=axes, keep_axes=True)
+        zeros = nx.sum(nx.as_type(zero, "s32"), axes=axes, keep_axes=True)
+        dx = gb * (ansb / without)
+        dx = nx.select(nx.logical_and(zero, nx.equal(zeros, 1)), gb * rest, dx)
+        dx = nx.select(nx.logical_and(zero, nx.greater(zeros, 1)), 0.0, dx)
+        return [(x, nx.as_type(dx, x.type))]
     if op in ("reduce_max", "reduce_min"):                               # :828-844
         x = a[0]
         keep, n = e.ints[0], e.ints[1]

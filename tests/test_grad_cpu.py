@@ -324,3 +324,54 @@ def test_sort_gradient_follows_the_permutation():
         want[r, np.argsort(x[r])] = w
     assert_close(got, want, 0, 0, "gradient of sort")
     check(lambda t: nx.sum(nx.pow(nx.sort(t, axis=0, direction="desc"), 2) * nx.tensor(np.arange(8.0).reshape(2, 4), "f64")), [x])
+
+
+# ---- rules added after random compositions were checked against finite differences -----------------
+
+def test_reference_atan2_remainder_and_erf_inv():
+    # grad_test.exs:318-323, 395-400
+    assert_close(run(grad(lambda t: nx.remainder(nx.tanh(t), t)), [1.0])[0], 0.41997434161402614, 1e-12, 0)
+    assert_close(run(grad(lambda t: nx.atan2(nx.tanh(t), t)), [1.0])[0], -0.21621156120382867, 1e-12, 0)
+    # grad_test.exs:2225-2242: the curve is too sharp near 1 for finite differences
+    for x, want in [(0.9, 3.43), (0.98, 13.26), (0.99, 24.45), (0.995, 45.56), (0.999, 198.94)]:
+        assert abs(run(grad(nx.erf_inv), [x])[0] - want) < 0.01
+
+
+def test_reference_product():
+    # grad_test.exs:4222-4290
+    total = lambda **o: grad(lambda t: nx.sum(nx.product(t, **o)))
+    a = [[[[1.0, 2, 3, 4], [2, 1, 3, -1]]]]
+    assert_close(run(total(), [a])[0], [[[[-144.0, -72, -48, -36], [-72, -144, -48, 144]]]], 1e-12, 0)
+    b = [[[[1.0, 2, 3, 4], [2, 1, 3, -1], [3, 2, 3, 0]]]]
+    assert_close(run(total(), [b])[0], [[[[0.0] * 4, [0.0] * 4, [0.0, 0, 0, -2592]]]], 1e-12, 0)
+    c = [[[[1.0, 2, 3, 4], [2, 1, 3, -1], [3, 2, 3, 0], [0, 2, 3, 0]]]]
+    assert_close(run(total(axes=[3]), [c])[0], [[[[24.0, 12, 8, 6], [-3, -6, -2, 6], [0, 0, 0, 18], [0, 0, 0, 0]]]], 1e-12, 0)
+    assert_close(run(total(keep_axes=True), [a])[0], [[[[-144.0, -72, -48, -36], [-72, -144, -48, 144]]]], 1e-12, 0)
+    assert_close(run(total(axes=[3], keep_axes=True), [a])[0], [[[[24.0, 12, 8, 6], [-3, -6, -2, 6]]]], 1e-12, 0)
+    composed = grad(lambda t: nx.sum(nx.sin(nx.product(nx.cos(t)))))
+    assert_close(run(composed, [a])[0], [[[[0.0272486, -0.03822973, -0.00249401, 0.02025739],
+                                           [-0.03822973, 0.0272486, -0.00249401, -0.0272486]]]], 1e-5, 1e-8)
+
+
+@pytest.mark.parametrize("name", ["asin", "acos", "atanh", "asinh", "acosh", "erf_inv", "atan2_l", "atan2_r", "rem_l", "rem_r", "product"])
+def test_added_rules_against_finite_differences(name):
+    rng = np.random.default_rng(11)
+    inside = rng.uniform(-0.8, 0.8, (3, 4))
+    wide = rng.standard_normal((3, 4)) * 2.0
+    other = rng.standard_normal((4,)) + 3.0
+    w = rng.standard_normal((3, 4))
+    if name in ("asin", "acos", "atanh", "erf_inv"):
+        check(lambda x: nx.sum(getattr(nx, name)(x) * nx.tensor(w, "f64")), [inside], rtol=1e-5, atol=1e-6)
+    elif name == "asinh":
+        check(lambda x: nx.sum(nx.asinh(x) * nx.tensor(w, "f64")), [wide])
+    elif name == "acosh":
+        check(lambda x: nx.sum(nx.acosh(x) * nx.tensor(w, "f64")), [np.abs(wide) + 1.5])
+    elif name.startswith("atan2"):
+        check(lambda x, y: nx.sum(nx.atan2(x, y) * nx.tensor(w, "f64")), [wide, other], wrt=0 if name.endswith("l") else 1)
+    elif name.startswith("rem"):
+        # positive operands: the reference's rule for the divisor is -floor(x / y) (grad.ex:1020-1025), which is
+        # the derivative of the truncating remainder only where x / y is positive
+        check(lambda x, y: nx.sum(nx.remainder(x, y) * nx.tensor(w, "f64")), [np.abs(wide) * 3.0 + 0.1, other],
+              wrt=0 if name.endswith("l") else 1)
+    else:
+        check(lambda x: nx.sum(nx.product(x, axes=[1]) * nx.tensor(w[:, 0], "f64")), [wide])
