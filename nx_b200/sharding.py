@@ -142,6 +142,11 @@ class _Part:
         if e.id in self.memo:
             return self.memo[e.id]
         res = self._visit(gt, e, param_specs)
+        used = [a for a in res[1] if a is not None]
+        if len(set(used)) != len(used):
+            # e.g. x + transpose(x) with x split along its rows: every partition would hold a diagonal
+            # block only, and the other blocks need rows that live on another partition
+            raise ShardingError(f"{e.op}: the same mesh axis would split two dimensions of the result (needs an all-gather)")
         self.memo[e.id] = res
         return res
 
