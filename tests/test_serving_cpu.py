@@ -119,3 +119,48 @@ def test_errors():
             S.Serving.new(boom).start("boom", batch_size=1)
     finally:
         S.stop("boom")
+
+
+def test_many_concurrent_callers_each_get_exactly_their_rows():
+    """Eight clients, forty requests each of 1 to 20 entries (up to 2.5 batches), three partitions, a 5 ms
+    timeout: every caller's result must be the function of its own rows, in order, whatever the stacking,
+    splitting and padding did around them; nobody may be left waiting."""
+    import random
+
+    def builder(opts):
+        def run(batch):
+            time.sleep(0.0005)
+            return batch * 2.0 + 1.0, batch.sum(axis=1)
+        return run
+
+    srv = S.Serving.new(builder).start("stress", batch_size=8, batch_timeout_ms=5,
+                                       partition_options=[{"device": 0}, {"device": 1}, {"device": 2}])
+    wrong = []
+
+    def client(cid):
+        r = random.Random(cid)
+        data = np.random.default_rng(cid)
+        for i in range(40):
+            n = r.randint(1, 20)
+            x = data.standard_normal((n, 5))
+            try:
+                y, total = S.batched_run("stress", S.Batch.concatenate([x]))
+                if y.shape != (n, 5) or not np.array_equal(y, x * 2.0 + 1.0) or not np.allclose(total, x.sum(axis=1)):
+                    wrong.append((cid, i, n, y.shape))
+            except Exception as e:          # noqa: BLE001 - reported below
+                wrong.append((cid, i, repr(e)))
+            if r.random() < 0.3:
+                time.sleep(r.random() * 0.004)
+
+    try:
+        clients = [threading.Thread(target=client, args=(c,)) for c in range(8)]
+        for t in clients:
+            t.start()
+        for t in clients:
+            t.join(timeout=60)
+        assert not [t for t in clients if t.is_alive()], "a caller never got its result"
+        assert not wrong, wrong[:3]
+        assert {p for p, _, _ in srv.executed} == {0, 1, 2}
+        assert all(size + pad == 8 or pad == 0 for _, size, pad in srv.executed)
+    finally:
+        S.stop("stress")
