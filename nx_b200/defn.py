@@ -283,11 +283,16 @@ def _make_runner(outs, params, aliases=None, hooks=None):
         run_tapped.program = inner.program
         return run_tapped
 
-    groups, seen = [], set()
+    # the loops and host calls of this graph, and their result nodes AS THIS GRAPH HOLDS THEM: a graph
+    # that went through a substitution (the body of an enclosing loop, whose captured values became
+    # parameters) holds rebuilt nodes with other ids and other arguments than the ones traced
+    groups, members = [], {}
     for t in order:
-        if t.data.op in ("while", "runtime_call") and id(t.data.payload) not in seen:
-            seen.add(id(t.data.payload))
-            groups.append(t.data.payload)
+        if t.data.op in ("while", "runtime_call"):
+            if id(t.data.payload) not in members:
+                members[id(t.data.payload)] = {}
+                groups.append(t.data.payload)
+            members[id(t.data.payload)][t.data.ints[0]] = t
     if not groups:
         prog = Program(E.serialize(outs, params, aliases))
 
@@ -300,17 +305,21 @@ def _make_runner(outs, params, aliases=None, hooks=None):
     all_params = list(params)
     repl, stages = {}, []
     for g in groups:
-        stage = _make_runner(E.substitute(g.inputs, repl), list(all_params), None, hooks)
+        held = members[id(g)]
+        inputs = next(iter(held.values())).data.args
+        stage = _make_runner(E.substitute(inputs, repl), list(all_params), None, hooks)
         if isinstance(g, _WhileGroup):
             cond = _make_runner(g.cond_outs, g.sub_params, None, hooks)
             body = _make_runner(g.body_outs, g.sub_params, None, hooks)
             stages.append((stage, g, cond, body))
         else:
             stages.append((stage, g, None, None))
-        for r in g.results:                       # the results: parameters of everything downstream
+        for i, r in enumerate(g.results):         # the results: parameters of everything downstream
             p = E.parameter(r.type, r.shape, len(all_params))
             all_params.append(p)
             repl[r.data.id] = p
+            if i in held:
+                repl[held[i].data.id] = p
     final = _make_runner(E.substitute(outs, repl), list(all_params), None, hooks)
 
     def run_segments(vals, device):
