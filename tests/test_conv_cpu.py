@@ -85,3 +85,35 @@ def test_conv_groups_permutations_and_3d():
     assert outs[0].type == ("f", 32) and outs[0].shape == (1, 4, 3, 3)           # integers convolve in f32
     with pytest.raises(ValueError, match="feature groups"):
         defn.trace(lambda a, b: nx.conv(a, b, feature_group_size=2), [defn.template(x.shape, "f32"), defn.template(w.shape, "f32")])
+
+
+@pytest.mark.parametrize("seed", range(80))
+def test_random_conv_configurations(seed):
+    """One to three spatial dimensions, strides, signed explicit padding, both dilations and feature groups
+    drawn at random, with the operands handed over in a random layout."""
+    import random
+    r = random.Random(seed)
+    nsp = r.choice([1, 2, 2, 3])
+    groups = r.choice([1, 1, 2, 3])
+    ci, cg, n = r.randint(1, 3), r.randint(1, 2), r.randint(1, 2)
+    sp = [r.randint(3, 7) for _ in range(nsp)]
+    ks = [r.randint(1, 3) for _ in range(nsp)]
+    strides = [r.randint(1, 3) for _ in range(nsp)]
+    pads = [(r.randint(-1, 2), r.randint(-1, 2)) for _ in range(nsp)]
+    idil = [r.randint(1, 2) for _ in range(nsp)]
+    kdil = [r.randint(1, 2) for _ in range(nsp)]
+    extent = [(d - 1) * i + 1 + lo + hi for d, i, (lo, hi) in zip(sp, idil, pads)]
+    if any(d < (k - 1) * kd + 1 for d, k, kd in zip(extent, ks, kdil)):
+        pytest.skip("the window does not fit the padded input")
+    rng = np.random.default_rng(seed)
+    x = rng.normal(0, 1, [n, ci * groups] + sp).astype(np.float32)
+    w = rng.normal(0, 1, [cg * groups, ci] + ks).astype(np.float32)
+    want = conv_direct(x.astype(np.float64), w.astype(np.float64), strides, pads, idil, kdil, groups)
+    # the caller's layouts: `permutation[i]` names the caller's axis that holds canonical axis i
+    perm_x, perm_w, perm_o = (r.sample(range(nsp + 2), nsp + 2) for _ in range(3))
+    x_given = np.ascontiguousarray(x.transpose(np.argsort(perm_x)))
+    w_given = np.ascontiguousarray(w.transpose(np.argsort(perm_w)))
+    got = run_oracle(lambda a, b: nx.conv(a, b, strides=strides, padding=pads, input_dilation=idil, kernel_dilation=kdil,
+                                          feature_group_size=groups, input_permutation=perm_x, kernel_permutation=perm_w,
+                                          output_permutation=perm_o), [x_given, w_given], ["f32", "f32"])
+    np.testing.assert_allclose(got, want.transpose(np.argsort(perm_o)), rtol=1e-4, atol=1e-4)
