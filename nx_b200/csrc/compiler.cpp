@@ -984,7 +984,12 @@ KernelBuilder::Val KernelBuilder::emit_op(int n, const std::vector<Aff>& idx) {
       else if (op == "remainder") e = "nx_irem<" + RT + ">(" + xv + ", " + yv + ")";
       else if (op == "pow") e = "nx_ipow<" + RT + ">(" + xv + ", " + yv + ")";
       else if (op == "left_shift") e = "nx_shl<" + RT + ">(" + xv + ", " + yv + ")";
-      else if (op == "right_shift") e = "nx_shr<" + RT + ">(" + xv + ", " + yv + ")";
+      else if (op == "right_shift") {
+        // the reference shifts logically when the RESULT type is unsigned, whatever signed type the operands
+        // were merged to (a u64 tensor shifted by a number is computed in s64): exla/lib/exla/defn.ex:1328-1335
+        if (!dtype_is_signed(t) && dtype_is_signed(ct)) e = "(" + RT + ")nx_shr<" + UT + ">((" + UT + ")" + xv + ", (" + UT + ")" + yv + ")";
+        else e = "nx_shr<" + RT + ">(" + xv + ", " + yv + ")";
+      }
       else fail(NXB_ERR_INVALID_ARGUMENT, "op " + op + " is not defined for " + dtype_name(ct));
     }
     return def(elem, t, cvt(e, ct, t));

@@ -485,7 +485,16 @@ def evaluate(nodes, outs, params, mode="xla_like", all_reduce=None):
                 a, b = _load(arg[0], at[0], ct, mode), _load(arg[1], at[1], ct, mode)
                 if mode == "binary_backend" and a.dtype != b.dtype:
                     a, b = a.astype(np.float64), b.astype(np.float64)
-            r = _binary(op, _bcast(a, nd.shape), _bcast(b, nd.shape), ct)
+            if op == "right_shift" and mode == "xla_like" and t[0] == "u" and a.dtype.kind == "i":
+                # The reference shifts logically when the RESULT type is unsigned, whatever signed type the
+                # operands were merged to (exla/lib/exla/defn.ex:1328-1335): a u64 tensor shifted by a
+                # number is computed in s64, and its values with the top bit set are not sign-extended.
+                wide = {1: np.uint8, 2: np.uint16, 4: np.uint32, 8: np.uint64}[a.dtype.itemsize]
+                bits = np.asarray(_bcast(b, nd.shape)).astype(wide)
+                shifted = np.where(bits >= a.dtype.itemsize * 8, wide(0), _bcast(a, nd.shape).astype(wide) >> np.minimum(bits, wide(a.dtype.itemsize * 8 - 1)))
+                r = shifted.astype(a.dtype)
+            else:
+                r = _binary(op, _bcast(a, nd.shape), _bcast(b, nd.shape), ct)
             if op in PRED_OPS:
                 v = r.astype(np.uint8)
             elif mode == "binary_backend":

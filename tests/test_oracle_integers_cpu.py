@@ -1,0 +1,102 @@
+"""Integer semantics of the front-end and the oracle (wrapping arithmetic, bit operations, shifts,
+conversions between widths and signs, comparisons, sums in the aggregate type) against numpy's fixed-width
+integers on random compositions over all eight integer types, with the extreme values of every type among
+the inputs.  Mixed types are merged by the reference's rule (`Nx.Type.merge`) before numpy computes."""
+import random
+
+import numpy as np
+import pytest
+
+import nx_oracle as O
+from helpers import host_tensor
+from nx_b200 import defn, nx, types as T
+
+NP = {"u8": np.uint8, "u16": np.uint16, "u32": np.uint32, "u64": np.uint64, "s8": np.int8, "s16": np.int16, "s32": np.int32, "s64": np.int64}
+OPS = {"add": np.add, "subtract": np.subtract, "multiply": np.multiply, "bitwise_and": np.bitwise_and, "bitwise_or": np.bitwise_or,
+       "bitwise_xor": np.bitwise_xor, "max": np.maximum, "min": np.minimum}
+CMP = {"equal": np.equal, "less": np.less, "greater_equal": np.greater_equal, "not_equal": np.not_equal}
+
+
+def npt(t):
+    return NP[T.short(t)]
+
+
+def _case(seed):
+    r = random.Random(seed)
+    rng = np.random.default_rng(seed)
+    n = r.choice([1, 5, 8])
+    arrays, types = [], []
+    for _ in range(r.randint(2, 3)):
+        t = r.choice(list(NP))
+        info = np.iinfo(NP[t])
+        a = rng.integers(info.min, info.max, n, dtype=NP[t], endpoint=True)
+        if r.random() < 0.5:
+            a[: max(1, n // 3)] = r.choice([info.min, info.max, 0, 1])
+        arrays.append(a)
+        types.append(t)
+    steps, op_seed = r.randint(1, 8), seed * 7 + 1
+    expected = []
+
+    def fun(*tensors):
+        rr = random.Random(op_seed)
+        vals = list(zip(tensors, arrays))
+        for _ in range(steps):
+            (x, a), (y, b) = rr.choice(vals), rr.choice(vals)
+            kind = rr.choice(["op", "op", "cmp", "cast", "neg", "abs", "sum", "not", "shift"])
+            if kind == "op":
+                name = rr.choice(list(OPS))
+                out = npt(T.merge(x.type, y.type))
+                vals.append((getattr(nx, name)(x, y), OPS[name](a.astype(out), b.astype(out)).astype(out)))
+            elif kind == "cmp":
+                name = rr.choice(list(CMP))
+                out = npt(T.merge(x.type, y.type))
+                vals.append((getattr(nx, name)(x, y), CMP[name](a.astype(out), b.astype(out)).astype(np.uint8)))
+            elif kind == "cast":
+                t = rr.choice(list(NP))
+                vals.append((nx.as_type(x, t), a.astype(NP[t])))
+            elif kind == "neg":
+                vals.append((nx.negate(x), (np.zeros_like(a) - a).astype(a.dtype)))
+            elif kind == "abs":
+                vals.append((nx.abs(x), np.abs(a) if a.dtype.kind == "i" else a))
+            elif kind == "not":
+                vals.append((nx.bitwise_not(x), np.bitwise_not(a)))
+            elif kind == "shift":
+                # by a number: the operands are merged to a signed type for unsigned tensors, and the shift of
+                # an unsigned RESULT is still logical (exla/lib/exla/defn.ex:1328-1335)
+                k = rr.randint(0, a.dtype.itemsize * 8 - 1)
+                name = rr.choice(["left_shift", "right_shift"])
+                twin = np.left_shift if name == "left_shift" else np.right_shift
+                vals.append((getattr(nx, name)(x, k), twin(a, np.array(k, a.dtype)).astype(a.dtype)))
+            else:
+                out = npt(T.to_aggregate(x.type))
+                vals.append((nx.sum(x), np.sum(a.astype(out), dtype=out)))
+        made = vals[len(tensors):]
+        del expected[:]
+        expected.extend(w for _, w in made)
+        return tuple(v for v, _ in made)
+
+    host = [host_tensor(a, t) for a, t in zip(arrays, types)]
+    with np.errstate(all="ignore"):
+        blob, _ = defn.build_program(fun, host)
+        results = O.run_program(blob, [h.data.raw for h in host], "xla_like")
+    return results, list(expected)
+
+
+@pytest.mark.parametrize("seed", range(400))
+def test_integer_results_are_numpys_fixed_width_results(seed):
+    results, expected = _case(seed)
+    assert len(results) == len(expected)
+    for (value, type_, _raw), want in zip(results, expected):
+        want = np.asarray(want)
+        assert npt(type_) == want.dtype, (type_, want.dtype)
+        np.testing.assert_array_equal(np.asarray(value).astype(want.dtype), want)
+
+
+def test_right_shift_of_an_unsigned_result_is_logical_whatever_the_operands_were_merged_to():
+    a = np.array([2**64 - 1, 2**63, 5, 2**63 + 12345], dtype=np.uint64)
+    h = host_tensor(a, "u64")
+    for k in (0, 1, 58, 63, 64, 200):
+        blob, _ = defn.build_program(lambda x: nx.right_shift(x, k), [h])
+        defn.Program(blob)                                   # the generated kernel compiles
+        got = O.run_program(blob, [h.data.raw], "xla_like")[0][0]
+        np.testing.assert_array_equal(got, (a >> np.uint64(k)) if k < 64 else np.zeros_like(a))
