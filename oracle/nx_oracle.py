@@ -211,21 +211,40 @@ def _clz(a, bits):
 
 
 def _int_pow(a, b):
+    """Integer power by squaring, wrapping; a negative exponent gives 1 for base 1, +-1 for base -1 and 0
+    otherwise (what XLA's integer pow returns; Nx.BinaryBackend raises there)."""
     res = np.ones_like(a)
     base = a.copy()
-    e = b.copy()
+    e = np.where(b < 0, 0, b).astype(b.dtype) if b.dtype.kind == "i" else b.copy()
     with np.errstate(all="ignore"):
         for _ in range(64):
             res = np.where(e & 1, res * base, res)
             base = base * base
             e = e >> 1
+        if b.dtype.kind == "i":
+            minus_one = a == np.array(-1).astype(a.dtype)
+            negative = np.where(a == 1, 1, np.where(minus_one, np.where(b & 1, -1, 1), 0)).astype(a.dtype)
+            res = np.where(b < 0, negative, res)
     return res
 
 
 def _quotient(a, b):
+    """Truncating integer division at the operands' own width; x / 0 is all ones (-1) and the most
+    negative value divided by -1 is itself, as XLA defines them (Nx.BinaryBackend raises for a zero divisor)."""
     with np.errstate(all="ignore"):
-        q = np.abs(a.astype(np.int64)) // np.maximum(np.abs(b.astype(np.int64)), 1)
-        return (np.sign(a.astype(np.int64)) * np.sign(b.astype(np.int64)) * q).astype(a.dtype)
+        safe = np.where(b == 0, 1, b).astype(b.dtype)
+        q = a // safe
+        if a.dtype.kind == "i":
+            r = a - q * safe
+            q = np.where((r != 0) & ((a < 0) != (safe < 0)), q + 1, q)
+        return np.where(b == 0, np.array(-1).astype(a.dtype), q).astype(a.dtype)
+
+
+def _int_remainder(a, b):
+    """Sign of the dividend; x rem 0 is x (XLA)."""
+    with np.errstate(all="ignore"):
+        safe = np.where(b == 0, 1, b).astype(b.dtype)
+        return np.where(b == 0, a, np.fmod(a, safe)).astype(a.dtype)
 
 
 def _binary(op, a, b, t):
@@ -239,7 +258,7 @@ def _binary(op, a, b, t):
         if op == "max": return np.maximum(a, b)          # NaN wins (binary_backend.ex:719-725)
         if op == "min": return np.minimum(a, b)
         if op == "pow": return np.power(a, b) if fl else _int_pow(a, b)
-        if op == "remainder": return np.fmod(a, b)        # sign of the dividend (rem / :math.fmod)
+        if op == "remainder": return np.fmod(a, b) if fl else _int_remainder(a, b)    # sign of the dividend (rem / :math.fmod)
         if op == "atan2": return np.arctan2(a, b)
         if op == "quotient": return _quotient(a, b)
         if op == "bitwise_and": return a & b

@@ -21,6 +21,33 @@ def npt(t):
     return NP[T.short(t)]
 
 
+def _xla_quotient(a, b):
+    """Truncating division in Python integers, wrapped to the width; x / 0 is all ones, as XLA defines it."""
+    info = np.iinfo(a.dtype)
+    out = []
+    for p, q in zip(a.ravel().tolist(), b.ravel().tolist()):
+        v = -1 if q == 0 else abs(p) // abs(q) * (1 if (p < 0) == (q < 0) else -1)
+        out.append((v - info.min) % (1 << info.bits) + info.min)
+    return np.array(out, dtype=object).astype(a.dtype).reshape(a.shape)
+
+
+def _xla_remainder(a, b):
+    out = [p if q == 0 else (abs(p) % abs(q)) * (1 if p >= 0 else -1) for p, q in zip(a.ravel().tolist(), b.ravel().tolist())]
+    return np.array(out, dtype=object).astype(a.dtype).reshape(a.shape)
+
+
+def _xla_pow(a, b):
+    info = np.iinfo(a.dtype)
+    out = []
+    for p, q in zip(a.ravel().tolist(), b.ravel().tolist()):
+        v = pow(p, q) if q >= 0 else (1 if p == 1 else ((-1 if q % 2 else 1) if p == -1 else 0))
+        out.append((v - info.min) % (1 << info.bits) + info.min)
+    return np.array(out, dtype=object).astype(a.dtype).reshape(a.shape)
+
+
+DIVISIONS = {"quotient": _xla_quotient, "remainder": _xla_remainder, "pow": _xla_pow}
+
+
 def _case(seed):
     r = random.Random(seed)
     rng = np.random.default_rng(seed)
@@ -42,7 +69,7 @@ def _case(seed):
         vals = list(zip(tensors, arrays))
         for _ in range(steps):
             (x, a), (y, b) = rr.choice(vals), rr.choice(vals)
-            kind = rr.choice(["op", "op", "cmp", "cast", "neg", "abs", "sum", "not", "shift"])
+            kind = rr.choice(["op", "op", "cmp", "cast", "neg", "abs", "sum", "not", "shift", "division"])
             if kind == "op":
                 name = rr.choice(list(OPS))
                 out = npt(T.merge(x.type, y.type))
@@ -51,6 +78,13 @@ def _case(seed):
                 name = rr.choice(list(CMP))
                 out = npt(T.merge(x.type, y.type))
                 vals.append((getattr(nx, name)(x, y), CMP[name](a.astype(out), b.astype(out)).astype(np.uint8)))
+            elif kind == "division":
+                name = rr.choice(list(DIVISIONS))
+                out = npt(T.merge(x.type, y.type))
+                p, q = np.broadcast_arrays(a.astype(out), b.astype(out))
+                if name == "pow":                      # small exponents (the low bits mean the same in every type)
+                    y, q = nx.bitwise_and(y, 3), q & np.array(3, q.dtype)
+                vals.append((getattr(nx, name)(x, y), DIVISIONS[name](p, q)))
             elif kind == "cast":
                 t = rr.choice(list(NP))
                 vals.append((nx.as_type(x, t), a.astype(NP[t])))
@@ -100,3 +134,22 @@ def test_right_shift_of_an_unsigned_result_is_logical_whatever_the_operands_were
         defn.Program(blob)                                   # the generated kernel compiles
         got = O.run_program(blob, [h.data.raw], "xla_like")[0][0]
         np.testing.assert_array_equal(got, (a >> np.uint64(k)) if k < 64 else np.zeros_like(a))
+
+
+def test_zero_divisors_negative_exponents_and_the_most_negative_value():
+    """What XLA defines where Elixir's integers raise: x / 0 is all ones, x rem 0 is x, the most negative
+    value divided by -1 is itself, and a negative exponent gives 1, +-1 or 0 by the base."""
+    a = np.array([-128, 127, -7, 0, 7, -7, 1, -1, -1, 5], dtype=np.int8)
+    b = np.array([-1, 0, 2, 0, -2, -2, -3, -3, -4, -1], dtype=np.int8)
+    ha, hb = host_tensor(a, "s8"), host_tensor(b, "s8")
+    for name, want in [("quotient", [-128, -1, -3, -1, -3, 3, 0, 0, 0, -5]), ("remainder", [0, 127, -1, 0, 1, -1, 1, -1, -1, 0]),
+                       ("pow", [0, 1, 49, 1, 0, 0, 1, -1, 1, 0])]:
+        blob, _ = defn.build_program(lambda x, y: getattr(nx, name)(x, y), [ha, hb])
+        defn.Program(blob)
+        np.testing.assert_array_equal(O.run_program(blob, [ha.data.raw, hb.data.raw], "xla_like")[0][0], np.array(want, np.int8), name)
+    u = host_tensor(np.array([200, 0, 7], np.uint8), "u8")
+    z = host_tensor(np.array([0, 0, 2], np.uint8), "u8")
+    blob, _ = defn.build_program(lambda x, y: (nx.quotient(x, y), nx.remainder(x, y)), [u, z])
+    q, r = (o[0] for o in O.run_program(blob, [u.data.raw, z.data.raw], "xla_like"))
+    np.testing.assert_array_equal(q, np.array([255, 255, 3], np.uint8))
+    np.testing.assert_array_equal(r, np.array([200, 0, 1], np.uint8))
