@@ -131,7 +131,11 @@ def convert(arr, src, dst, mode):
                 wrapped = np.array([((int(v) - lo) % span) + lo for v in ints], dtype=object)
                 res = wrapped.astype(NP[dst]).reshape(a.shape)
             else:                              # saturating, like a hardware convert
-                res = np.clip(tr, lo, hi).astype(NP[dst])
+                # the limits of the 64-bit types are not doubles: compare first, convert what lies inside
+                inside = (tr > float(lo)) & (tr < float(hi))
+                res = np.where(inside, tr, 0.0).astype(NP[dst])
+                res = np.where(tr >= float(hi), np.array(hi, NP[dst]), res)
+                res = np.where(tr <= float(lo), np.array(lo, NP[dst]), res)
             res = np.where(np.isnan(a), np.array(0, NP[dst]), res)
             res = np.where(a == np.inf, np.array(hi, NP[dst]), res)
             res = np.where(a == -np.inf, np.array(lo, NP[dst]), res)

@@ -153,3 +153,28 @@ def test_zero_divisors_negative_exponents_and_the_most_negative_value():
     q, r = (o[0] for o in O.run_program(blob, [u.data.raw, z.data.raw], "xla_like"))
     np.testing.assert_array_equal(q, np.array([255, 255, 3], np.uint8))
     np.testing.assert_array_equal(r, np.array([200, 0, 1], np.uint8))
+
+
+@pytest.mark.parametrize("src", ["f32", "f64", "bf16", "f16"])
+def test_float_to_integer_conversion_truncates_and_saturates(src):
+    """NaN becomes 0, anything at or beyond a limit becomes the limit (the limits of the 64-bit types are
+    not representable as floats), everything else loses its fraction: exla/test/exla/defn/expr_test.exs:1117-1130."""
+    rng = np.random.default_rng(0)
+    special = [np.nan, np.inf, -np.inf, 0.0, -0.0, 0.5, -0.5, 0.999, -0.999, 1.5, -1.5, 2.5, 127.0, 127.9, 128.0, -128.0,
+               -128.9, -129.0, 255.0, 255.5, 256.0, 32767.5, -32768.5, 65535.9, 65536.0, 2147483647.0, 2147483648.0,
+               -2147483648.0, -2147483904.0, 4294967295.0, 4294967296.0, 9.2233720368547758e18, -9.2233720368547758e18,
+               1.8446744073709552e19, 1e30, -1e30, 3e-40, 123456.789]
+    values = np.concatenate([special, rng.standard_normal(200) * rng.choice([1, 1e3, 1e6, 1e10, 1e19], 200)])
+    with np.errstate(all="ignore"):
+        x = values.astype({"f32": np.float32, "f64": np.float64, "bf16": np.float32, "f16": np.float16}[src])
+    if src == "bf16":
+        x = (x.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
+    h = host_tensor(x.astype(np.float64), src)
+    for dst, dtype in NP.items():
+        blob, _ = defn.build_program(lambda t: nx.as_type(t, dst), [h])
+        with np.errstate(all="ignore"):
+            got = O.run_program(blob, [h.data.raw], "xla_like")[0][0]
+        info = np.iinfo(dtype)
+        want = [0 if v != v else info.max if v >= info.max else info.min if v <= info.min else int(v)
+                for v in x.astype(np.float64).tolist()]
+        np.testing.assert_array_equal(got, np.array(want, dtype=object).astype(dtype), f"{src} -> {dst}")
