@@ -147,7 +147,9 @@ def _compute_dtype(t, mode):
     """The width arithmetic runs at."""
     if mode == "binary_backend":
         return np.float64 if is_float(t) else np.int64
-    if t == ("bf", 16):
+    if t in (("bf", 16), ("f", 16)):
+        # 16-bit floats are computed in f32 and rounded once (for + - * / that IS the correctly rounded 16-bit
+        # result; numpy's own float16 functions are a few units off for the transcendental ones)
         return np.float32
     return NP[t]
 
