@@ -743,9 +743,38 @@ def top_k(x, k=1):
     if x.rank == 0 or not 1 <= k <= x.shape[-1]:
         raise ValueError(f"top_k input must have at least rank 1 and k must be in 1..{x.shape[-1] if x.rank else 0}")
     last = x.rank - 1
+    n = x.shape[-1]
+    if n > SORT_LIMIT:
+        return _top_k_of_long_rows(x, k)
     values = slice_along_axis(sort(x, axis=last, direction="desc"), 0, k, axis=last)
     indices = slice_along_axis(argsort(x, axis=last, direction="desc"), 0, k, axis=last)
     return values, indices
+
+
+# the row kernel of sort / argsort keeps a whole row in shared memory
+SORT_LIMIT = 16384
+
+
+def _top_k_of_long_rows(x, k):
+    """top_k over rows longer than one sorted row may be (a vocabulary): every row is cut into equal
+    chunks, each chunk gives its own k best, and the k best of those candidates are the answer.  The
+    sorts are stable and the candidates stay in chunk order, so among equal values the lowest position
+    wins, exactly as in the one-pass form.  Positions past the end of a row are filled with the lowest
+    value of the type; they lie behind every real position and can never be among the first k."""
+    n, last = x.shape[-1], x.rank - 1
+    chunks = -(-n // SORT_LIMIT)
+    width = -(-n // chunks)
+    if k > width or chunks * k > SORT_LIMIT:
+        raise ValueError(f"top_k over {n} entries supports k up to {min(width, SORT_LIMIT // chunks)}, got {k}")
+    lowest = float("-inf") if T.is_float(x.type) else T.min_value(x.type)
+    padded = pad(x, lowest, [(0, 0, 0)] * last + [(0, chunks * width - n, 0)])
+    pieces = reshape(padded, x.shape[:-1] + (chunks, width))
+    best = slice_along_axis(sort(pieces, axis=last + 1, direction="desc"), 0, k, axis=last + 1)
+    where = slice_along_axis(argsort(pieces, axis=last + 1, direction="desc"), 0, k, axis=last + 1)
+    where = where + iota(where.shape, axis=last, type="s32") * width            # position in the whole row
+    best, where = (reshape(t, x.shape[:-1] + (chunks * k,)) for t in (best, where))
+    order = slice_along_axis(argsort(best, axis=last, direction="desc"), 0, k, axis=last)
+    return take_along_axis(best, order, axis=last), take_along_axis(where, order, axis=last)
 
 
 def conv(x, kernel, strides=1, padding="valid", input_dilation=1, kernel_dilation=1, feature_group_size=1,

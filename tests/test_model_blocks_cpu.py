@@ -105,4 +105,33 @@ def test_lookups_convolutions_pooling_and_sorting_compile():
     assert plan(lambda x: nx.window_max(x, (1, 1, 3, 3), strides=[1, 1, 2, 2], padding="same"), [tm((2, 64, 112, 112), "f32")])[0] == 1
     assert plan(lambda l: nx.argsort(l, axis=1, direction="desc"), [tm((4, 16000), "f32")])[0] >= 1
     with pytest.raises(Exception, match="at most 16384"):
-        plan(lambda l: nx.top_k(l, k=50), [tm((4, 32000), "f32")])
+        plan(lambda l: nx.sort(l, axis=1), [tm((4, 32000), "f32")])
+
+
+@pytest.mark.parametrize("n,k,type", [(32000, 50, "f32"), (50257, 40, "f32"), (151936, 64, "f32"), (20000, 7, "s32"),
+                                      (16385, 1, "f32"), (40000, 100, "bf16")])
+def test_top_k_over_a_vocabulary_longer_than_one_sorted_row(n, k, type):
+    """Sampling takes the k best of 32,000 to 150,000 logits: more than the sort kernel holds in one row.
+    The front-end sorts chunks and then the chunks' candidates; values, positions and the order among equal
+    values (lowest position first, NaN highest) must be those of one stable descending sort."""
+    import numpy as np
+    import nx_oracle as O
+    from helpers import host_tensor
+    rng = np.random.default_rng(n)
+    x = rng.integers(-1000, 1000, (3, n)) if type == "s32" else rng.standard_normal((3, n)).astype(np.float32)
+    if type != "s32":
+        x[0, 100:200] = x[0, 100]
+        x[1, 5], x[1, n - 1] = np.nan, np.inf
+        x[2, :] = np.round(x[2] * 4) / 4
+    h = host_tensor(x, type)
+    blob, _ = defn.build_program(lambda t: nx.top_k(t, k=k), [h])
+    assert defn.Program(blob).launch_count() >= 1
+    (values, _, _), (positions, position_type, _) = O.run_program(blob, [h.data.raw], "xla_like")
+    stored = np.asarray(O.run_program(defn.build_program(lambda t: t + 0, [h])[0], [h.data.raw], "xla_like")[0][0], np.float64)
+    want = np.stack([sorted(range(n), key=lambda j: (not np.isnan(row[j]), -row[j] if not np.isnan(row[j]) else 0.0, j))[:k]
+                     for row in stored])
+    assert position_type == ("s", 32)
+    np.testing.assert_array_equal(np.asarray(positions), want)
+    np.testing.assert_array_equal(np.asarray(values, np.float64), np.take_along_axis(stored, want, axis=1))
+    with pytest.raises(ValueError, match="supports k up to"):
+        nx.top_k(h, k=9000)
