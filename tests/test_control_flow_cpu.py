@@ -191,7 +191,7 @@ def _random_loop(seed):
     return fun, twin, x, np.array(trips, np.int32)
 
 
-@pytest.mark.parametrize("seed", range(60))
+@pytest.mark.parametrize("seed", range(30))
 def test_random_loop_matches_its_numpy_statement(on_the_oracle, seed):
     fun, twin, x, n = _random_loop(seed)
     i, a, b = on_the_oracle(fun, [x, n], ["f32", "s32"])

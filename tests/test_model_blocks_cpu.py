@@ -108,7 +108,7 @@ def test_lookups_convolutions_pooling_and_sorting_compile():
         plan(lambda l: nx.sort(l, axis=1), [tm((4, 32000), "f32")])
 
 
-@pytest.mark.parametrize("n,k,type", [(32000, 50, "f32"), (50257, 40, "f32"), (151936, 64, "f32"), (20000, 7, "s32"),
+@pytest.mark.parametrize("n,k,type", [(32000, 50, "f32"), (151936, 64, "f32"), (20000, 7, "s32"),
                                       (16385, 1, "f32"), (40000, 100, "bf16")])
 def test_top_k_over_a_vocabulary_longer_than_one_sorted_row(n, k, type):
     """Sampling takes the k best of 32,000 to 150,000 logits: more than the sort kernel holds in one row.
