@@ -751,6 +751,75 @@ def top_k(x, k=1):
     return values, indices
 
 
+# ---- cumulative operations (nx/lib/nx.ex:12044-12057) --------------------------------------------
+# The reference's default is a recursive pairwise scan (nx.ex:12186-12286) whose every level reads the
+# level before twice; generated inline that doubles the arithmetic per level.  Here a row is cut into
+# blocks: inside a block a running window (window reductions pad with the operation's identity) gives the
+# running value, a reduction gives each block's total, the totals are scanned the same way, and every
+# block adds what came before it.  Integers give the reference's result exactly (they wrap alike);
+# floats differ from it by the order of summation only.
+
+_CUMULATIVE_BLOCK = 32
+_CUMULATIVE = {"sum": ("window_sum", "sum", "add", lambda t: 0),
+               "product": ("window_product", "product", "multiply", lambda t: 1),
+               "max": ("window_max", "reduce_max", "max", lambda t: float("-inf") if T.is_float(t) else T.min_value(t)),
+               "min": ("window_min", "reduce_min", "min", lambda t: float("inf") if T.is_float(t) else T.max_value(t))}
+
+
+def _running(kind, x):
+    """Running `kind` along the last axis."""
+    window_op, reduce_op, combine, identity = _CUMULATIVE[kind]
+    g = globals()
+    n, lead = x.shape[-1], list(x.shape[:-1])
+    ones = [1] * len(lead)
+    if n <= 2 * _CUMULATIVE_BLOCK:
+        return g[window_op](x, ones + [n], padding=[(0, 0)] * len(lead) + [(n - 1, 0)])
+    w = _CUMULATIVE_BLOCK
+    blocks = -(-n // w)
+    fill = identity(x.type)
+    padded = pad(x, fill, [(0, 0, 0)] * len(lead) + [(0, blocks * w - n, 0)])
+    tiles = reshape(padded, tuple(lead + [blocks, w]))
+    inside = g[window_op](tiles, ones + [1, w], padding=[(0, 0)] * (len(lead) + 1) + [(w - 1, 0)])
+    totals = as_type(g[reduce_op](tiles, axes=[-1]), x.type)
+    before = _running(kind, totals)                                    # inclusive over the blocks
+    before = pad(slice_along_axis(before, 0, blocks - 1, axis=-1), fill, [(0, 0, 0)] * len(lead) + [(1, 0, 0)])
+    whole = g[combine](inside, new_axis(before, -1))
+    return slice_along_axis(reshape(whole, tuple(lead + [blocks * w])), 0, n, axis=-1)
+
+
+def _cumulative(kind, x, axis, reverse_):
+    x = _as_operand(x)
+    if x.rank == 0:
+        raise ValueError("cumulative operations need a tensor of rank 1 or more")
+    t, inv = _to_last(x, axis)
+    if reverse_:
+        t = reverse(t, axes=[t.rank - 1])
+    r = as_type(_running(kind, t), x.type)
+    if reverse_:
+        r = reverse(r, axes=[r.rank - 1])
+    return r if inv is None else transpose(r, inv)
+
+
+def cumulative_sum(x, axis=0, reverse=False):
+    """``Nx.cumulative_sum/2`` (nx/lib/nx.ex:11742-11786): same type and shape as the input."""
+    return _cumulative("sum", x, axis, reverse)
+
+
+def cumulative_product(x, axis=0, reverse=False):
+    """``Nx.cumulative_product/2`` (nx/lib/nx.ex:11819-11863)."""
+    return _cumulative("product", x, axis, reverse)
+
+
+def cumulative_min(x, axis=0, reverse=False):
+    """``Nx.cumulative_min/2``."""
+    return _cumulative("min", x, axis, reverse)
+
+
+def cumulative_max(x, axis=0, reverse=False):
+    """``Nx.cumulative_max/2``."""
+    return _cumulative("max", x, axis, reverse)
+
+
 # the row kernel of sort / argsort keeps a whole row in shared memory
 SORT_LIMIT = 16384
 
