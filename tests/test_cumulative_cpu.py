@@ -61,3 +61,42 @@ def test_the_running_sum_is_differentiable():
     w = np.cos(np.arange(70) * 0.3)
     got, _, _ = run(grad(lambda t: nx.sum(nx.cumulative_sum(t) * nx.tensor(w, "f64"))), x, "f64", build=False)
     np.testing.assert_allclose(got, np.cumsum(w[::-1])[::-1], rtol=1e-12)
+
+
+def test_nucleus_sampling_step_over_a_vocabulary():
+    """The decoding step a serving loop runs after the block: the 50 best of 50,257 logits, their softmax,
+    the running sum that cuts the nucleus at p = 0.9, and the choice given a uniform draw — one traced
+    function, checked against numpy."""
+    rng = np.random.default_rng(5)
+    logits = (rng.standard_normal((4, 50257)) * 3.0).astype(np.float32)
+    draw = rng.uniform(0, 1, (4, 1)).astype(np.float32)
+
+    def step(l, u):
+        values, tokens = nx.top_k(l, k=50)
+        e = nx.exp(values - nx.reduce_max(values, axes=[1], keep_axes=True))
+        p = e / nx.sum(e, axes=[1], keep_axes=True)
+        running = nx.cumulative_sum(p, axis=1)
+        inside = nx.less(running - p, 0.9)                           # the nucleus: everything before 0.9 is reached
+        kept = nx.select(inside, p, 0.0)
+        total = nx.reduce_max(nx.select(inside, running, 0.0), axes=[1], keep_axes=True)
+        kept_running = nx.select(inside, running, total)              # the running sum of `kept`, without a second scan
+        threshold = u * total
+        pick = nx.argmax(nx.greater_equal(kept_running, threshold), axis=1, keep_axis=True)      # first position reaching the draw
+        return nx.squeeze(nx.take_along_axis(tokens, pick, axis=1), [1]), kept
+
+    hosts = [host_tensor(logits, "f32"), host_tensor(draw, "f32")]
+    blob, _ = defn.build_program(step, hosts)
+    assert defn.Program(blob).launch_count() >= 1
+    (token, token_type, _), (kept, _, _) = O.run_program(blob, [h.data.raw for h in hosts], "xla_like")
+
+    order = np.argsort(-logits, axis=1, kind="stable")[:, :50]
+    values = np.take_along_axis(logits, order, axis=1).astype(np.float64)
+    p = np.exp(values - values.max(axis=1, keepdims=True))
+    p /= p.sum(axis=1, keepdims=True)
+    running = np.cumsum(p, axis=1)
+    want_kept = np.where(running - p < 0.9, p, 0.0)
+    kept_running = np.cumsum(want_kept, axis=1)
+    pick = np.argmax(kept_running >= draw * kept_running[:, -1:], axis=1)
+    np.testing.assert_allclose(np.asarray(kept), want_kept, rtol=1e-4, atol=1e-6)
+    assert token_type == ("s", 32)
+    np.testing.assert_array_equal(np.asarray(token), order[np.arange(4), pick])
