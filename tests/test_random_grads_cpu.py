@@ -144,7 +144,10 @@ def apply(r, kind, x, vals):
         idx = nx.reshape(nx.remainder(nx.iota((k,), type="s32") * 2, x.shape[0]), (k, 1))
         cands = [v for v in vals if v.shape == (k,)]
         upd = r.choice(cands) if cands else nx.broadcast(nx.as_type(2.0, "f64"), (k,))
-        return r.choice([nx.indexed_add, nx.indexed_put])(x, idx, upd)
+        scatter = r.choice([nx.indexed_add, nx.indexed_put])
+        if scatter is nx.indexed_put and len({(2 * j) % x.shape[0] for j in range(k)}) < k:
+            scatter = nx.indexed_add                  # two writes to one place: which one stays is not specified
+        return scatter(x, idx, upd)
     raise AssertionError(kind)
 
 
